@@ -1,0 +1,176 @@
+// Direct (non-dispatched) C entry points: plain pointers and sizes in, a
+// status code out.  The custom calls of ral/calls.cc land on the same launch
+// functions.
+#include <cstring>
+#include <string>
+
+#include "../../include/disc_b200_ral.h"
+#include "kernels/qgemm.h"
+#include "kernels/rowops.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int32_t finish(cudaError_t st, const char* what, const char* detail) {
+  if (st == cudaSuccess) {
+    return 0;
+  }
+  g_last_error = std::string(what) + ": " + (detail ? detail : cudaGetErrorString(st));
+  return static_cast<int32_t>(st);
+}
+
+disc_b200::QGemmParams to_params(const disc_b200_qgemm_args* a) {
+  disc_b200::QGemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.a = a->a;
+  p.w = a->w;
+  p.out = a->out;
+  p.M = a->M;
+  p.N = a->N;
+  p.K = a->K;
+  p.lda = a->lda > 0 ? a->lda : a->K;
+  p.ldw = a->ldw > 0 ? a->ldw : a->K;
+  p.ldo = a->ldo > 0 ? a->ldo : a->N;
+  p.x_scale = a->x_scale;
+  p.w_scale = a->w_scale;
+  p.out_scale = a->out_scale;
+  p.bias = a->bias;
+  p.x_scale_kind = a->x_scale ? a->x_scale_kind : disc_b200::kScaleNone;
+  p.w_scale_kind = a->w_scale ? a->w_scale_kind : disc_b200::kScaleNone;
+  p.out_scale_kind = a->out_scale ? a->out_scale_kind : disc_b200::kScaleNone;
+  p.bias_kind = a->bias ? a->bias_kind : disc_b200::kBiasNone;
+  p.fold_out_scale = a->fold_out_scale;
+  p.div_out_scale = a->div_out_scale;
+  p.act = a->act;
+  p.out_dtype = a->out_dtype;
+  p.path = a->path;
+  p.split_k = a->split_k;
+  p.splitk_ws = static_cast<int32_t*>(a->splitk_ws);
+  p.splitk_ws_bytes = a->splitk_ws_bytes;
+  return p;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t disc_b200_qgemm(const disc_b200_qgemm_args* args, void* stream) {
+  if (!args) {
+    g_last_error = "qgemm: null args";
+    return 1;
+  }
+  const char* detail = nullptr;
+  cudaError_t st = disc_b200::qgemm_launch(to_params(args), static_cast<cudaStream_t>(stream), &detail);
+  return finish(st, "qgemm", detail);
+}
+
+int64_t disc_b200_qgemm_scratch_bytes(int64_t M, int64_t N, int64_t K) {
+  return disc_b200::qgemm_splitk_ws_bytes(M, N, K);
+}
+
+int32_t disc_b200_qgemm_path(const disc_b200_qgemm_args* args) {
+  if (!args) return -1;
+  return disc_b200::qgemm_choose_path(to_params(args));
+}
+
+int32_t disc_b200_quantize(const void* x, int32_t in_type, int8_t* q, int64_t numel,
+                           const float* scale, const int32_t* zero_point, int64_t channels,
+                           int64_t inner, int32_t qmin, int32_t qmax, void* stream) {
+  disc_b200::QuantizeParams p;
+  p.x = x;
+  p.q = q;
+  p.numel = numel;
+  p.in_type = in_type;
+  p.scale = scale;
+  p.zero_point = zero_point;
+  p.channels = channels;
+  p.inner = inner;
+  p.qmin = qmin;
+  p.qmax = qmax;
+  const char* detail = nullptr;
+  return finish(disc_b200::quantize_launch(p, static_cast<cudaStream_t>(stream), &detail), "quantize",
+                detail);
+}
+
+int32_t disc_b200_dequantize(const int8_t* q, void* y, int32_t out_type, int64_t numel,
+                             const float* scale, const int32_t* zero_point, int64_t channels,
+                             int64_t inner, void* stream) {
+  disc_b200::DequantizeParams p;
+  p.q = q;
+  p.y = y;
+  p.numel = numel;
+  p.out_type = out_type;
+  p.scale = scale;
+  p.zero_point = zero_point;
+  p.channels = channels;
+  p.inner = inner;
+  const char* detail = nullptr;
+  return finish(disc_b200::dequantize_launch(p, static_cast<cudaStream_t>(stream), &detail),
+                "dequantize", detail);
+}
+
+int32_t disc_b200_dynamic_quantize(const void* x, int32_t in_type, int8_t* q, float* row_scale,
+                                   int64_t rows, int64_t cols, void* stream) {
+  disc_b200::DynQuantParams p;
+  p.x = x;
+  p.q = q;
+  p.row_scale = row_scale;
+  p.rows = rows;
+  p.cols = cols;
+  p.in_type = in_type;
+  const char* detail = nullptr;
+  return finish(disc_b200::dynamic_quantize_launch(p, static_cast<cudaStream_t>(stream), &detail),
+                "dynamic_quantize", detail);
+}
+
+int32_t disc_b200_norm(const disc_b200_norm_args* a, void* stream) {
+  if (!a) {
+    g_last_error = "norm: null args";
+    return 1;
+  }
+  disc_b200::NormParams p;
+  p.x = a->x;
+  p.residual = a->residual;
+  p.gamma = a->gamma;
+  p.beta = a->beta;
+  p.y = a->y;
+  p.sum_out = a->sum_out;
+  p.q_out = a->q_out;
+  p.q_scale = a->q_scale;
+  p.q_row_scale = a->q_row_scale;
+  p.rows = a->rows;
+  p.cols = a->cols;
+  p.eps = a->eps;
+  p.type = a->type;
+  p.rms = a->rms;
+  const char* detail = nullptr;
+  return finish(disc_b200::norm_launch(p, static_cast<cudaStream_t>(stream), &detail), "norm", detail);
+}
+
+int32_t disc_b200_softmax(const void* x, void* y, int32_t type, int64_t rows, int64_t cols,
+                          int64_t rows_per_batch, const int32_t* lens, const void* mask,
+                          float scale, int32_t log_softmax, void* stream) {
+  disc_b200::SoftmaxParams p;
+  p.x = x;
+  p.y = y;
+  p.rows = rows;
+  p.cols = cols;
+  p.rows_per_batch = rows_per_batch;
+  p.lens = lens;
+  p.mask = mask;
+  p.scale = scale;
+  p.type = type;
+  p.log_softmax = log_softmax;
+  const char* detail = nullptr;
+  return finish(disc_b200::softmax_launch(p, static_cast<cudaStream_t>(stream), &detail), "softmax",
+                detail);
+}
+
+const char* disc_b200_last_error_string(void) { return g_last_error.c_str(); }
+
+int32_t disc_b200_kernel_status(void) { return disc_b200::kernel_status_fetch_and_clear(); }
+
+const char* disc_b200_version(void) { return "disc-b200-ral 0.1 (sm_100a)"; }
+
+}  // extern "C"

@@ -1,0 +1,66 @@
+// Host-side description of one quantized-linear launch.  Plain C types only so
+// that the C-ABI layer can fill it in directly.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace disc_b200 {
+
+enum QGemmOut : int { kOutI8 = 0, kOutF16 = 1, kOutF32 = 2, kOutI32 = 3 };
+enum QGemmAct : int { kActNone = 0, kActGelu = 1, kActSilu = 2 };
+enum QGemmBias : int { kBiasNone = 0, kBiasF32 = 1, kBiasI8 = 2 };
+enum ScaleKind : int { kScaleNone = 0, kScaleScalar = 1, kScalePerCol = 2, kScalePerRow = 3 };
+enum QGemmPath : int { kPathAuto = 0, kPathTiled = 1, kPathSmallM = 2, kPathSimt = 3 };
+
+// out[m, n] = epilogue( sum_k a[m, k] * w[n, k] ), a and w int8, K-contiguous.
+//
+//   t  = float(acc) (* x_scale[m] when x_scale_kind == per-row)
+//   cs = x_scale(n) * w_scale(n)            (x_scale omitted when per-row)
+//   cs = cs / out_scale(n)                  when fold_out_scale (the reference's
+//                                           host-side "kernel scale", computed here
+//                                           on the device in the same order)
+//   v  = fma(t, cs, bias[n]);  v = act(v)
+//   v  = v / out_scale                      when div_out_scale (quantize-op form)
+//   out = int8: sat(rne(v)) | f16 | f32 ; kOutI32 stores acc unchanged.
+struct QGemmParams {
+  const int8_t* a;
+  const int8_t* w;
+  void* out;
+  int64_t M, N, K;
+  int64_t lda, ldw, ldo;  // row strides in elements
+  const float* x_scale;
+  const float* w_scale;
+  const float* out_scale;
+  const void* bias;
+  int x_scale_kind;    // ScaleKind (scalar | per-col | per-row | none = 1.0)
+  int w_scale_kind;    // scalar | per-col | none
+  int out_scale_kind;  // scalar | per-col (fold only) | none
+  int bias_kind;       // QGemmBias
+  int fold_out_scale;
+  int div_out_scale;
+  int act;        // QGemmAct
+  int out_dtype;  // QGemmOut
+  int path;       // QGemmPath (tests force a path; callers leave kPathAuto)
+  int split_k;    // small-M path: 0 = choose
+  // Scratch for the small-M split-K reduction (zero on entry, left zero on
+  // exit): int32 partial sums followed by one int32 arrival counter per
+  // 128-channel block.  Needed only when the launch splits K.
+  int32_t* splitk_ws;
+  int64_t splitk_ws_bytes;
+};
+
+// Bytes of zeroed scratch the small-M path may need for a given problem.
+int64_t qgemm_splitk_ws_bytes(int64_t M, int64_t N, int64_t K);
+
+// Launches on `stream`.  Returns cudaSuccess or the first error; `err` (if not
+// null) receives a static description for argument errors.
+cudaError_t qgemm_launch(const QGemmParams& p, cudaStream_t stream, const char** err);
+
+// Which path kPathAuto resolves to (exposed for tests and the bench).
+int qgemm_choose_path(const QGemmParams& p);
+
+// Reads and clears the device status word the kernels set when a bounded wait
+// ran out (0 = ok).  Synchronises the device.
+int kernel_status_fetch_and_clear();
+
+}  // namespace disc_b200

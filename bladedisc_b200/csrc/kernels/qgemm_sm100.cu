@@ -1,0 +1,821 @@
+// Int8 quantized linear for sm_100a: out = epilogue(A[M,K] . W[N,K]^T).
+//
+// This is the arithmetic of the reference's GPU custom call ral_pdll_qgemm
+// (tao_compiler/mlir/ral/context/quantized_gpu_kernel_impl.cc:328-422, a
+// cuBLASLt int8 GEMM with alpha and a bias epilogue) plus the dequantize /
+// GELU / quantize elementwise kernels DISC generates after it
+// (tao_compiler/mlir/disc/transforms/disc_lower_quantize_and_dequantize.cc:77-136),
+// done in one pass: the int32 accumulator never leaves the SM.
+//
+// Three paths, all computing the same function:
+//   tiled   (M > 64)  persistent CTAs, 128 x BN output tiles, TMA -> 128B-swizzled
+//                     smem ring -> tcgen05.mma kind::i8 -> two TMEM accumulators so
+//                     the epilogue of tile i overlaps the MMAs of tile i+1.
+//   small-M (M <= 64) operands swapped: 128 output channels sit on the MMA M
+//                     dimension, the few activation rows on the MMA N dimension, so
+//                     the weight streams at HBM rate; K may be split across CTAs,
+//                     partial sums meet in global scratch (plain stores, the last
+//                     CTA of a channel block adds them: integer, order-free, exact).
+//   simt              one thread per output; only for shapes TMA cannot address
+//                     (K not a multiple of 16, unaligned base) such as the
+//                     reference's 25x71 known-answer case.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "qgemm.h"
+#include "sm100_ptx.cuh"
+
+namespace disc_b200 {
+
+__device__ int g_kernel_status = 0;
+
+namespace {
+
+struct EpiParams {
+  void* out;
+  int64_t ldo;
+  int64_t M, N;
+  const float* x_scale;
+  const float* w_scale;
+  const float* out_scale;
+  const void* bias;
+  int x_kind, w_kind, o_kind, bias_kind, fold_out, div_out, act;
+};
+
+__device__ __forceinline__ float col_scale(const EpiParams& e, int64_t n) {
+  float sx = 1.f;
+  if (e.x_kind == kScaleScalar) sx = __ldg(e.x_scale);
+  else if (e.x_kind == kScalePerCol) sx = __ldg(e.x_scale + n);
+  float sw = 1.f;
+  if (e.w_kind == kScaleScalar) sw = __ldg(e.w_scale);
+  else if (e.w_kind == kScalePerCol) sw = __ldg(e.w_scale + n);
+  float s = __fmul_rn(sx, sw);
+  if (e.fold_out) {
+    const float so = (e.o_kind == kScalePerCol) ? __ldg(e.out_scale + n) : __ldg(e.out_scale);
+    s = __fdiv_rn(s, so);
+  }
+  return s;
+}
+
+__device__ __forceinline__ float col_bias(const EpiParams& e, int64_t n) {
+  if (e.bias_kind == kBiasF32) return __ldg(reinterpret_cast<const float*>(e.bias) + n);
+  if (e.bias_kind == kBiasI8)
+    return static_cast<float>(__ldg(reinterpret_cast<const int8_t*>(e.bias) + n));
+  return 0.f;
+}
+
+__device__ __forceinline__ float act_apply(float v, int act) {
+  if (act == kActGelu) return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
+  if (act == kActSilu) return v / (1.f + __expf(-v));
+  return v;
+}
+
+// acc -> real value, shared by every path.
+__device__ __forceinline__ float epi_value(int32_t acc, float rs, bool has_rs, float cs, float cb,
+                                           int act, bool div_out, float so) {
+  float t = __int2float_rn(acc);
+  if (has_rs) t = __fmul_rn(t, rs);
+  float v = __fmaf_rn(t, cs, cb);
+  v = act_apply(v, act);
+  if (div_out) v = __fdiv_rn(v, so);
+  return v;
+}
+
+__device__ __forceinline__ int8_t to_s8(float v) {
+  int r = __float2int_rn(v);
+  r = max(-128, min(127, r));
+  return static_cast<int8_t>(r);
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_one(OutT* p, float v, int32_t acc);
+template <>
+__device__ __forceinline__ void store_one<int8_t>(int8_t* p, float v, int32_t) {
+  *p = to_s8(v);
+}
+template <>
+__device__ __forceinline__ void store_one<__half>(__half* p, float v, int32_t) {
+  *p = __float2half_rn(v);
+}
+template <>
+__device__ __forceinline__ void store_one<float>(float* p, float v, int32_t) {
+  *p = v;
+}
+template <>
+__device__ __forceinline__ void store_one<int32_t>(int32_t* p, float, int32_t acc) {
+  *p = acc;
+}
+
+// Stores 32 consecutive outputs of one row with 16-byte stores.
+template <typename OutT>
+__device__ __forceinline__ void store_row32_vec(OutT* p, const float* v, const uint32_t* acc);
+template <>
+__device__ __forceinline__ void store_row32_vec<int8_t>(int8_t* p, const float* v,
+                                                        const uint32_t*) {
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint32_t b0 = static_cast<uint8_t>(to_s8(v[4 * i + 0]));
+    uint32_t b1 = static_cast<uint8_t>(to_s8(v[4 * i + 1]));
+    uint32_t b2 = static_cast<uint8_t>(to_s8(v[4 * i + 2]));
+    uint32_t b3 = static_cast<uint8_t>(to_s8(v[4 * i + 3]));
+    w[i] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+  }
+  uint4* q = reinterpret_cast<uint4*>(p);
+  q[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  q[1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+template <>
+__device__ __forceinline__ void store_row32_vec<__half>(__half* p, const float* v,
+                                                        const uint32_t*) {
+  uint4* q = reinterpret_cast<uint4*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __half2 h0 = __floats2half2_rn(v[8 * i + 0], v[8 * i + 1]);
+    __half2 h1 = __floats2half2_rn(v[8 * i + 2], v[8 * i + 3]);
+    __half2 h2 = __floats2half2_rn(v[8 * i + 4], v[8 * i + 5]);
+    __half2 h3 = __floats2half2_rn(v[8 * i + 6], v[8 * i + 7]);
+    q[i] = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
+                      *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
+  }
+}
+template <>
+__device__ __forceinline__ void store_row32_vec<float>(float* p, const float* v, const uint32_t*) {
+  float4* q = reinterpret_cast<float4*>(p);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) q[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+}
+template <>
+__device__ __forceinline__ void store_row32_vec<int32_t>(int32_t* p, const float*,
+                                                         const uint32_t* acc) {
+  uint4* q = reinterpret_cast<uint4*>(p);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) q[i] = make_uint4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+}
+
+// ------------------------------------------------------------------ tiled
+constexpr int kTileM = 128;        // MMA M, rows of the 128-row operand tile
+constexpr int kTileKBytes = 128;   // one 128-byte swizzle row of int8 = 128 k
+constexpr int kMmaK = 32;          // k per tcgen05.mma kind::i8
+constexpr int kThreads = 192;      // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+
+template <int BN, int STAGES>
+struct TiledSmem {
+  static constexpr int kABytes = kTileM * kTileKBytes;
+  static constexpr int kBBytes = BN * kTileKBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = STAGES * kStageBytes;
+  static constexpr int kNumBars = 2 * STAGES + 4;
+  static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;  // tmem slot, abort flag
+  static constexpr int kScaleOffset = kMiscOffset + 16;
+  static constexpr int kTotal = kScaleOffset + 4 * 2 * BN * 4;  // per epilogue warp: cs[BN], cb[BN]
+  static constexpr int kDynamic = kTotal + 1024;  // slack to align the base to 1024
+};
+
+template <int BN, int STAGES, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                   const __grid_constant__ CUtensorMap tmap_w, EpiParams ep, int num_kb, int tiles_m,
+                   int tiles_n, int vec_ok) {
+  using L = TiledSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::kBarOffset;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 4);
+  float* s_scale = reinterpret_cast<float*>(smem + L::kScaleOffset);  // [4 warps][2][BN]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t kTmemCols = 2 * BN;  // 128, 256 or 512: a power of two >= 32
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_w);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = tiles_m * tiles_n;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m_blk = tile / tiles_n;
+        const int n_blk = tile % tiles_n;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, &g_kernel_status,
+                         kStatusTimeoutEmpty);
+          if (!ok) break;
+          mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+          const uint32_t a_dst = smem_base + stage * L::kStageBytes;
+          tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * kTileKBytes, m_blk * kTileM);
+          tma_load_2d(a_dst + L::kABytes, &tmap_w, full_bar(stage), kb * kTileKBytes, n_blk * BN);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_i8_idesc(kTileM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc_buf = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        ok = mbar_wait(tempty_bar(acc_buf), acc_phase ^ 1, abort_flag, &g_kernel_status,
+                       kStatusTimeoutTmemEmpty);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc_buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(full_bar(stage), phase, abort_flag, &g_kernel_status, kStatusTimeoutFull);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * L::kStageBytes;
+          const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
+          const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + L::kABytes);
+#pragma unroll
+          for (int k = 0; k < kTileKBytes / kMmaK; ++k) {
+            umma_i8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(acc_buf));
+        acc_buf ^= 1;
+        if (acc_buf == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // Epilogue warps 2..5.  A warp may only touch the TMEM lane quadrant
+    // (warp id mod 4), which is also the 32-row slice of the tile it owns.
+    // Each warp keeps its own copy of the tile's column scale / bias so that
+    // the epilogue warps never wait on one another.
+    const int q = warp & 3;
+    float* cs = s_scale + q * 2 * BN;
+    float* cb = cs + BN;
+    int acc_buf = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    const bool has_rs = ep.x_kind == kScalePerRow;
+    const bool div_out = ep.div_out != 0;
+    float so = 1.f;
+    if (div_out) so = __ldg(ep.out_scale);
+    OutT* out = reinterpret_cast<OutT*>(ep.out);
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m_blk = tile / tiles_n;
+      const int n_blk = tile % tiles_n;
+      __syncwarp();
+      for (int j = lane; j < BN; j += 32) {
+        const int64_t n = static_cast<int64_t>(n_blk) * BN + j;
+        cs[j] = n < ep.N ? col_scale(ep, n) : 0.f;
+        cb[j] = n < ep.N ? col_bias(ep, n) : 0.f;
+      }
+      __syncwarp();
+      ok = mbar_wait(tfull_bar(acc_buf), acc_phase, abort_flag, &g_kernel_status,
+                     kStatusTimeoutTmemFull);
+      if (!ok) break;
+      tc_fence_after();
+      const int64_t m = static_cast<int64_t>(m_blk) * kTileM + q * 32 + lane;
+      const bool row_ok = m < ep.M;
+      float rs = 1.f;
+      if (has_rs && row_ok) rs = __ldg(ep.x_scale + m);
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc_buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int64_t n0 = static_cast<int64_t>(n_blk) * BN + c * 32;
+        if (n0 >= ep.N) break;  // uniform across the CTA
+        uint32_t r[32];
+        tmem_ld_x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        if (row_ok) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = epi_value(static_cast<int32_t>(r[j]), rs, has_rs, cs[c * 32 + j], cb[c * 32 + j],
+                             ep.act, div_out, so);
+          }
+          OutT* dst = out + m * ep.ldo + n0;
+          if (vec_ok && n0 + 32 <= ep.N) {
+            store_row32_vec<OutT>(dst, v, r);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (n0 + j < ep.N) store_one<OutT>(dst + j, v[j], static_cast<int32_t>(r[j]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc_buf));
+      acc_buf ^= 1;
+      if (acc_buf == 0) acc_phase ^= 1;
+    }
+  }
+
+  // Wind-down.  After an abort, give copies still in flight time to land
+  // before the shared memory is handed back.
+  __syncwarp();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------- small M
+constexpr int kSmallMaxStages = 8;
+constexpr int kSmallBarOffset = 200 * 1024;  // stages live below this offset
+constexpr int kSmallDynamic = kSmallBarOffset + 256 + 1024;
+
+// grid = (channel blocks of 128, K splits).  MT = activation rows padded to
+// 16/32/64/128 = the MMA N dimension.
+template <typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                    const __grid_constant__ CUtensorMap tmap_x, EpiParams ep, int MT, int stages,
+                    int num_kb, int32_t* ws, int32_t* counters) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + kSmallBarOffset;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kSmallMaxStages + s); };
+  const uint32_t tfull_bar = bar_base + 8u * (2 * kSmallMaxStages);
+  const uint32_t stored_bar = bar_base + 8u * (2 * kSmallMaxStages + 1);   // 4 warps stored partials
+  const uint32_t counted_bar = bar_base + 8u * (2 * kSmallMaxStages + 2);  // arrival count taken
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmallBarOffset + 8 * (2 * kSmallMaxStages + 3));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_blk = blockIdx.x;
+  const int split = gridDim.y;
+  const int ks = blockIdx.y;
+  const int kb_begin = static_cast<int>((static_cast<int64_t>(ks) * num_kb) / split);
+  const int kb_end = static_cast<int>((static_cast<int64_t>(ks + 1) * num_kb) / split);
+  const uint32_t w_bytes = kTileM * kTileKBytes;
+  const uint32_t x_bytes = static_cast<uint32_t>(MT) * kTileKBytes;
+  const uint32_t stage_bytes = w_bytes + x_bytes;  // multiples of 1024 (MT >= 16)
+  const uint32_t tmem_cols = MT < 32 ? 32u : static_cast<uint32_t>(MT);
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(tfull_bar, 1);
+    mbar_init(stored_bar, 4);
+    mbar_init(counted_bar, 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, &g_kernel_status,
+                       kStatusTimeoutEmpty))
+          break;
+        mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
+        const uint32_t w_dst = smem_base + stage * stage_bytes;
+        tma_load_2d(w_dst, &tmap_w, full_bar(stage), kb * kTileKBytes, n_blk * kTileM);
+        tma_load_2d(w_dst + w_bytes, &tmap_x, full_bar(stage), kb * kTileKBytes, 0);
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_i8_idesc(kTileM, MT);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        ok = mbar_wait(full_bar(stage), phase, abort_flag, &g_kernel_status, kStatusTimeoutFull);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t w_addr = smem_base + stage * stage_bytes;
+        const uint64_t a_desc = make_kmajor_sw128_desc(w_addr);
+        const uint64_t b_desc = make_kmajor_sw128_desc(w_addr + w_bytes);
+#pragma unroll
+        for (int k = 0; k < kTileKBytes / kMmaK; ++k) {
+          umma_i8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc,
+                  (kb != kb_begin || k != 0) ? 1u : 0u);
+        }
+        umma_commit(empty_bar(stage));
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok) umma_commit(tfull_bar);
+    }
+  } else {
+    const int q = warp & 3;
+    const int et = threadIdx.x - 64;
+    const int64_t n = static_cast<int64_t>(n_blk) * kTileM + q * 32 + lane;  // this thread's channel
+    const bool n_ok = n < ep.N;
+    const int64_t n_pad = static_cast<int64_t>(gridDim.x) * kTileM;
+    const bool has_rs = ep.x_kind == kScalePerRow;
+    const bool div_out = ep.div_out != 0;
+    const float so = div_out ? __ldg(ep.out_scale) : 1.f;
+    const float cs = n_ok ? col_scale(ep, n) : 0.f;
+    const float cb = n_ok ? col_bias(ep, n) : 0.f;
+    OutT* out = reinterpret_cast<OutT*>(ep.out);
+    const int Mrows = static_cast<int>(ep.M);
+
+    auto emit = [&](int m, int32_t acc) {
+      const float rs = has_rs ? __ldg(ep.x_scale + m) : 1.f;
+      const float v = epi_value(acc, rs, has_rs, cs, cb, ep.act, div_out, so);
+      store_one<OutT>(out + static_cast<int64_t>(m) * ep.ldo + n, v, acc);
+    };
+
+    bool ok = mbar_wait(tfull_bar, 0, abort_flag, &g_kernel_status, kStatusTimeoutTmemFull);
+    if (ok) {
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+      if (split == 1) {
+#pragma unroll 1
+        for (int c = 0; c < MT / 16; ++c) {
+          if (c * 16 >= Mrows) break;
+          uint32_t r[16];
+          tmem_ld_x16(t_row + c * 16, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = c * 16 + j;
+            if (m < Mrows && n_ok) emit(m, static_cast<int32_t>(r[j]));
+          }
+        }
+      } else {
+        // Partial sums: ws[ks][m][n_pad]; every slot this launch reads is
+        // written first, so the scratch needs no clearing between launches.
+        int32_t* my_ws = ws + static_cast<int64_t>(ks) * Mrows * n_pad;
+        const int64_t n_ws = static_cast<int64_t>(n_blk) * kTileM + q * 32 + lane;
+#pragma unroll 1
+        for (int c = 0; c < MT / 16; ++c) {
+          if (c * 16 >= Mrows) break;
+          uint32_t r[16];
+          tmem_ld_x16(t_row + c * 16, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = c * 16 + j;
+            if (m < Mrows) __stcg(my_ws + static_cast<int64_t>(m) * n_pad + n_ws, static_cast<int32_t>(r[j]));
+          }
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(stored_bar);
+        if (et == 0) {
+          if (mbar_wait(stored_bar, 0, abort_flag, &g_kernel_status, kStatusTimeoutSplitK)) {
+            const int old = atomicAdd(counters + n_blk, 1);
+            *last_flag = (old == split - 1) ? 1 : 0;
+            __threadfence_block();
+            mbar_arrive(counted_bar);
+          }
+        }
+        ok = mbar_wait(counted_bar, 0, abort_flag, &g_kernel_status, kStatusTimeoutSplitK);
+        if (ok && *last_flag) {
+          __threadfence();
+          for (int m = 0; m < Mrows; ++m) {
+            int32_t acc = 0;
+            for (int s = 0; s < split; ++s) {
+              acc += __ldcg(ws + (static_cast<int64_t>(s) * Mrows + m) * n_pad + n_ws);
+            }
+            if (n_ok) emit(m, acc);
+          }
+          if (et == 0) counters[n_blk] = 0;  // ready for the next launch
+        }
+      }
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// -------------------------------------------------------------------- simt
+template <typename OutT>
+__global__ void qgemm_simt_kernel(const int8_t* __restrict__ a, const int8_t* __restrict__ w,
+                                  int64_t K, int64_t lda, int64_t ldw, EpiParams ep) {
+  const int64_t n = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t m = blockIdx.y;
+  if (n >= ep.N || m >= ep.M) return;
+  const int8_t* ar = a + m * lda;
+  const int8_t* wr = w + n * ldw;
+  int32_t acc = 0;
+  for (int64_t k = 0; k < K; ++k) acc += static_cast<int32_t>(ar[k]) * static_cast<int32_t>(wr[k]);
+  const bool has_rs = ep.x_kind == kScalePerRow;
+  const float rs = has_rs ? ep.x_scale[m] : 1.f;
+  const bool div_out = ep.div_out != 0;
+  const float so = div_out ? ep.out_scale[0] : 1.f;
+  const float v = epi_value(acc, rs, has_rs, col_scale(ep, n), col_bias(ep, n), ep.act, div_out, so);
+  store_one<OutT>(reinterpret_cast<OutT*>(ep.out) + m * ep.ldo + n, v, acc);
+}
+
+// ------------------------------------------------------------------- host
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  });
+  return fn;
+}
+
+// int8 [rows, K] row-major (row stride ld bytes), box = box_rows x 128 bytes, 128B swizzle.
+bool make_tmap(CUtensorMap* tm, const int8_t* base, int64_t rows, int64_t K, int64_t ld,
+               int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kTileKBytes), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+EpiParams make_epi(const QGemmParams& p) {
+  EpiParams e;
+  e.out = p.out;
+  e.ldo = p.ldo;
+  e.M = p.M;
+  e.N = p.N;
+  e.x_scale = p.x_scale;
+  e.w_scale = p.w_scale;
+  e.out_scale = p.out_scale;
+  e.bias = p.bias;
+  e.x_kind = p.x_scale_kind;
+  e.w_kind = p.w_scale_kind;
+  e.o_kind = p.out_scale_kind;
+  e.bias_kind = p.bias_kind;
+  e.fold_out = p.fold_out_scale;
+  e.div_out = p.div_out_scale;
+  e.act = p.act;
+  return e;
+}
+
+int out_elem_bytes(int dt) { return dt == kOutI8 ? 1 : (dt == kOutF16 ? 2 : 4); }
+
+bool tma_ok(const QGemmParams& p) {
+  return p.K % 16 == 0 && p.lda % 16 == 0 && p.ldw % 16 == 0 &&
+         (reinterpret_cast<uintptr_t>(p.a) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.w) & 15) == 0;
+}
+
+int small_mt(int64_t M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
+
+int small_split(const QGemmParams& p) {
+  const int num_kb = static_cast<int>((p.K + kTileKBytes - 1) / kTileKBytes);
+  if (p.split_k > 0) return p.split_k < num_kb ? p.split_k : num_kb;
+  const int tiles_n = static_cast<int>((p.N + kTileM - 1) / kTileM);
+  int s = sm_count() / tiles_n;
+  if (s < 1) s = 1;
+  if (s > 8) s = 8;
+  if (s > num_kb) s = num_kb;
+  return s;
+}
+
+template <typename OutT, int BN, int STAGES>
+cudaError_t launch_tiled_t(const QGemmParams& p, cudaStream_t stream, const char** err) {
+  using L = TiledSmem<BN, STAGES>;
+  CUtensorMap ta, tw;
+  if (!make_tmap(&ta, p.a, p.M, p.K, p.lda, kTileM) || !make_tmap(&tw, p.w, p.N, p.K, p.ldw, BN)) {
+    if (err) *err = "cuTensorMapEncodeTiled failed";
+    return cudaErrorInvalidValue;
+  }
+  auto kern = qgemm_tiled_kernel<BN, STAGES, OutT>;
+  cudaError_t st =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+  if (st != cudaSuccess) return st;
+  const int tiles_m = static_cast<int>((p.M + kTileM - 1) / kTileM);
+  const int tiles_n = static_cast<int>((p.N + BN - 1) / BN);
+  const int num_kb = static_cast<int>((p.K + kTileKBytes - 1) / kTileKBytes);
+  const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n;
+  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  const int eb = out_elem_bytes(p.out_dtype);
+  const int vec_ok = ((p.ldo * eb) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+  kern<<<grid, kThreads, L::kDynamic, stream>>>(ta, tw, make_epi(p), num_kb, tiles_m, tiles_n, vec_ok);
+  return cudaGetLastError();
+}
+
+template <typename OutT>
+cudaError_t launch_tiled(const QGemmParams& p, cudaStream_t stream, const char** err) {
+  const int64_t tiles256 = ((p.M + kTileM - 1) / kTileM) * ((p.N + 255) / 256);
+  if (tiles256 >= sm_count()) return launch_tiled_t<OutT, 256, 4>(p, stream, err);
+  return launch_tiled_t<OutT, 128, 6>(p, stream, err);
+}
+
+template <typename OutT>
+cudaError_t launch_smallm(const QGemmParams& p, cudaStream_t stream, const char** err) {
+  const int MT = small_mt(p.M);
+  const int split = small_split(p);
+  const int tiles_n = static_cast<int>((p.N + kTileM - 1) / kTileM);
+  const int num_kb = static_cast<int>((p.K + kTileKBytes - 1) / kTileKBytes);
+  const int stage_bytes = (kTileM + MT) * kTileKBytes;
+  int stages = kSmallBarOffset / stage_bytes;
+  if (stages > kSmallMaxStages) stages = kSmallMaxStages;
+  int32_t* ws = nullptr;
+  int32_t* counters = nullptr;
+  if (split > 1) {
+    const int64_t n_pad = static_cast<int64_t>(tiles_n) * kTileM;
+    const int64_t need = (static_cast<int64_t>(split) * p.M * n_pad + tiles_n) * 4;
+    if (!p.splitk_ws || p.splitk_ws_bytes < need) {
+      if (err) *err = "small-M qgemm: split-K scratch missing or too small";
+      return cudaErrorInvalidValue;
+    }
+    counters = p.splitk_ws;  // counters first so their place does not depend on the split
+    ws = p.splitk_ws + tiles_n;
+  }
+  CUtensorMap tw, tx;
+  if (!make_tmap(&tw, p.w, p.N, p.K, p.ldw, kTileM) || !make_tmap(&tx, p.a, p.M, p.K, p.lda, MT)) {
+    if (err) *err = "cuTensorMapEncodeTiled failed";
+    return cudaErrorInvalidValue;
+  }
+  auto kern = qgemm_smallm_kernel<OutT>;
+  cudaError_t st =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmallDynamic);
+  if (st != cudaSuccess) return st;
+  dim3 grid(tiles_n, split);
+  kern<<<grid, kThreads, kSmallDynamic, stream>>>(tw, tx, make_epi(p), MT, stages, num_kb, ws,
+                                                  counters);
+  return cudaGetLastError();
+}
+
+template <typename OutT>
+cudaError_t launch_simt(const QGemmParams& p, cudaStream_t stream, const char** err) {
+  if (p.M > 65535) {
+    if (err) *err = "simt qgemm path: M too large";
+    return cudaErrorInvalidValue;
+  }
+  dim3 block(128);
+  dim3 grid(static_cast<unsigned>((p.N + 127) / 128), static_cast<unsigned>(p.M));
+  qgemm_simt_kernel<OutT><<<grid, block, 0, stream>>>(p.a, p.w, p.K, p.lda, p.ldw, make_epi(p));
+  return cudaGetLastError();
+}
+
+template <typename OutT>
+cudaError_t dispatch(const QGemmParams& p, int path, cudaStream_t stream, const char** err) {
+  switch (path) {
+    case kPathTiled: return launch_tiled<OutT>(p, stream, err);
+    case kPathSmallM: return launch_smallm<OutT>(p, stream, err);
+    default: return launch_simt<OutT>(p, stream, err);
+  }
+}
+
+}  // namespace
+
+int qgemm_choose_path(const QGemmParams& p) {
+  if (!tma_ok(p)) return kPathSimt;
+  if (p.path == kPathSimt) return kPathSimt;
+  if (p.path == kPathSmallM && p.M <= 128) return kPathSmallM;
+  if (p.path == kPathTiled) return kPathTiled;
+  return p.M <= 64 ? kPathSmallM : kPathTiled;
+}
+
+int64_t qgemm_splitk_ws_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M > 128) return 0;
+  const int64_t tiles_n = (N + kTileM - 1) / kTileM;
+  const int64_t num_kb = (K + kTileKBytes - 1) / kTileKBytes;
+  int64_t split = num_kb < 8 ? num_kb : 8;
+  return (split * M * tiles_n * kTileM + tiles_n) * 4;
+}
+
+cudaError_t qgemm_launch(const QGemmParams& p, cudaStream_t stream, const char** err) {
+  if (err) *err = nullptr;
+  if (p.M <= 0 || p.N <= 0) return cudaSuccess;  // empty result
+  if (p.K <= 0 || !p.a || !p.w || !p.out) {
+    if (err) *err = "qgemm: null operand or K <= 0";
+    return cudaErrorInvalidValue;
+  }
+  if (p.M > 0x7fffffff || p.N > 0x7fffffff || p.K > 0x7fffffff) {
+    if (err) *err = "qgemm: extent exceeds 2^31-1";
+    return cudaErrorInvalidValue;
+  }
+  if ((p.fold_out_scale || p.div_out_scale) && !p.out_scale) {
+    if (err) *err = "qgemm: out_scale required";
+    return cudaErrorInvalidValue;
+  }
+  if (p.div_out_scale && p.out_scale_kind == kScalePerCol) {
+    if (err) *err = "qgemm: per-channel out_scale only in folded form";
+    return cudaErrorInvalidValue;
+  }
+  const int path = qgemm_choose_path(p);
+  switch (p.out_dtype) {
+    case kOutI8: return dispatch<int8_t>(p, path, stream, err);
+    case kOutF16: return dispatch<__half>(p, path, stream, err);
+    case kOutF32: return dispatch<float>(p, path, stream, err);
+    case kOutI32: return dispatch<int32_t>(p, path, stream, err);
+    default:
+      if (err) *err = "qgemm: unknown out_dtype";
+      return cudaErrorInvalidValue;
+  }
+}
+
+int kernel_status_fetch_and_clear() {
+  int h = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(&h, g_kernel_status, sizeof(int)) != cudaSuccess) return -1;
+  if (h != 0) {
+    int z = 0;
+    cudaMemcpyToSymbol(g_kernel_status, &z, sizeof(int));
+  }
+  return h;
+}
+
+}  // namespace disc_b200

@@ -1,0 +1,93 @@
+// Bandwidth-bound kernels around the quantized linear: activation quantize /
+// dequantize and the row-reduction fusions (LayerNorm, RMSNorm, softmax) that
+// the reference compiler emits as generated kLoop / kStitch kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace disc_b200 {
+
+enum ElemType : int { kF32 = 0, kF16 = 1 };
+
+// q = clamp(rne(x / scale + zero_point), qmin, qmax) -> int8.
+// scale / zero_point: one value (per-tensor) or `channels` values applied along
+// an axis of a tensor viewed as [outer, channels, inner].  zero_point may be null (0).
+struct QuantizeParams {
+  const void* x;
+  int8_t* q;
+  int64_t numel;
+  int in_type;  // ElemType
+  const float* scale;
+  const int32_t* zero_point;
+  int64_t channels;  // 1 = per-tensor
+  int64_t inner;     // elements between consecutive channels (1 = last axis)
+  int qmin, qmax;
+};
+cudaError_t quantize_launch(const QuantizeParams& p, cudaStream_t s, const char** err);
+
+// y = float(q - zero_point) * scale -> f32 / f16.
+struct DequantizeParams {
+  const int8_t* q;
+  void* y;
+  int64_t numel;
+  int out_type;
+  const float* scale;
+  const int32_t* zero_point;
+  int64_t channels;
+  int64_t inner;
+};
+cudaError_t dequantize_launch(const DequantizeParams& p, cudaStream_t s, const char** err);
+
+// Per-row (per-token) symmetric quantize: scale[r] = max(max|x[r,:]| / 127, eps),
+// q = clamp(rne(x / scale[r]), -128, 127).  The row stays in registers between
+// the reduction and the write.
+struct DynQuantParams {
+  const void* x;
+  int8_t* q;
+  float* row_scale;
+  int64_t rows, cols;
+  int in_type;
+};
+cudaError_t dynamic_quantize_launch(const DynQuantParams& p, cudaStream_t s, const char** err);
+
+// y = LayerNorm(x [+ residual]) * gamma + beta over the last axis.
+// Optional second output: int8 copy quantized with a static per-tensor scale
+// (feeds the next quantized linear without another pass over y).
+// rms != 0 selects RMSNorm (no mean subtraction, beta ignored).
+// sum_out (optional) receives x + residual (the updated residual stream).
+// q_row_scale (optional, with q_out and no q_scale): per-row dynamic quantize of y.
+struct NormParams {
+  const void* x;
+  const void* residual;
+  const void* gamma;
+  const void* beta;
+  void* y;        // may be null when only the quantized output is wanted
+  void* sum_out;  // may be null
+  int8_t* q_out;  // may be null
+  const float* q_scale;
+  float* q_row_scale;
+  int64_t rows, cols;
+  float eps;
+  int type;  // ElemType of x / residual / gamma / beta / y
+  int rms;
+};
+cudaError_t norm_launch(const NormParams& p, cudaStream_t s, const char** err);
+
+// y = softmax(x * scale + mask) over the last axis.  Row r belongs to batch
+// r / rows_per_batch; `lens` (optional) gives the valid length per batch
+// (columns >= len get probability 0), `mask` (optional, [batches, cols], same
+// type as x) is added before the max.
+struct SoftmaxParams {
+  const void* x;
+  void* y;
+  int64_t rows, cols;
+  int64_t rows_per_batch;
+  const int32_t* lens;
+  const void* mask;
+  float scale;
+  int type;
+  int log_softmax;
+};
+cudaError_t softmax_launch(const SoftmaxParams& p, cudaStream_t s, const char** err);
+
+}  // namespace disc_b200

@@ -1,0 +1,648 @@
+// Custom calls registered with the dispatcher.
+//
+// Part 1 is the driver set a compiled executable and the kernels rely on
+// (reference: tao_compiler/mlir/ral/device/gpu/gpu_driver.cc:29-43 names,
+// tao_compiler/mlir/ral/context/base/cuda/cuda_context_impl.cc:258-510,627-764
+// behaviour, tao_compiler/mlir/ral/context/base/base_context.cc:136-235 I/O).
+// Part 2 is the quantized GEMM family with the reference's names, operand
+// order and result ownership (tao_compiler/mlir/ral/context/
+// quantized_gpu_kernel_impl.cc:197-481, stream_executor_based_impl.cc:427-483).
+// Part 3 registers the fused forms and the bandwidth kernels under new names a
+// PDLL pattern can target (any registered name is reachable from a
+// custom_call_v2: docs/developers/add_custom_call.md of the reference).
+#include <cstring>
+#include <memory>
+#include <tuple>
+
+#include "../kernels/qgemm.h"
+#include "../kernels/rowops.h"
+#include "abi.h"
+#include "context.h"
+#include "pdl_attr.h"
+
+namespace disc_b200 {
+namespace ral {
+namespace {
+
+cudaStream_t stream_of(ExecContext* ctx) { return ctx->ctx->stream; }
+
+bool check_stream_handle(ExecContext* ctx, void* handle) {
+  if (reinterpret_cast<intptr_t>(handle) != 0) {
+    ctx->signal_error("not a valid stream idx");
+    return false;
+  }
+  return true;
+}
+
+void report(ExecContext* ctx, cudaError_t st, const char* what, const char* detail) {
+  if (st == cudaSuccess) return;
+  std::string m = std::string(what) + ": " + (detail ? detail : cudaGetErrorString(st));
+  ctx->signal_error(m);
+}
+
+// ------------------------------------------------------------ 1. drivers
+void* ral_alloc(ExecContext* ctx, uint64_t bytes) { return ctx->alloc(bytes); }
+void ral_dealloc(ExecContext* ctx, void* p) { ctx->dealloc(p); }
+void* ral_alloc_persistent(ExecContext* ctx, uint64_t bytes) {
+  void* p = ctx->ctx->raw_alloc(bytes);
+  if (!p) {
+    ctx->signal_error("persistent device allocation failed");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> l(ctx->ctx->mu);
+  ctx->ctx->persistent.insert(p);
+  return p;
+}
+void ral_memset(ExecContext* ctx, void* handle, void* p, int32_t value, uint64_t bytes) {
+  if (!p) return;
+  report(ctx, cudaMemsetAsync(p, value, bytes, stream_of(ctx)), "memset", nullptr);
+}
+void* ral_get_stream(ExecContext* ctx, int32_t idx) {
+  if (idx < 0) {
+    ctx->signal_error("not a valid stream_id");
+    return nullptr;
+  }
+  if (idx > 0) {
+    ctx->signal_error("multi-stream not supported");
+    return nullptr;
+  }
+  return nullptr;  // handle of stream 0 is the integer 0
+}
+void* ral_as_cu_stream(ExecContext* ctx, void* handle) { return stream_of(ctx); }
+void ral_d2d(ExecContext* ctx, void* handle, void* from, void* to, uint64_t bytes) {
+  if (!check_stream_handle(ctx, handle)) return;
+  report(ctx, cudaMemcpyAsync(to, from, bytes, cudaMemcpyDeviceToDevice, stream_of(ctx)), "d2d", nullptr);
+}
+void ral_h2d(ExecContext* ctx, void* handle, const void* from, void* to, uint64_t bytes) {
+  report(ctx, cudaMemcpyAsync(to, from, bytes, cudaMemcpyHostToDevice, stream_of(ctx)), "h2d", nullptr);
+}
+void ral_d2h(ExecContext* ctx, void* handle, void* from, void* to, uint64_t bytes) {
+  report(ctx, cudaMemcpyAsync(to, from, bytes, cudaMemcpyDeviceToHost, stream_of(ctx)), "d2h", nullptr);
+}
+void ral_sync_on_stream(ExecContext* ctx, void* handle) {
+  if (!check_stream_handle(ctx, handle)) return;
+  report(ctx, cudaStreamSynchronize(stream_of(ctx)), "StreamSync", nullptr);
+}
+void ral_sync_all(ExecContext* ctx) { report(ctx, cudaDeviceSynchronize(), "DeviceSync", nullptr); }
+
+// Launching a compiler-generated cubin is the reference compiler's own code
+// generation; this runtime replaces those kernels with the calls of part 3.
+void ral_kernel_launch(ExecContext* ctx, void** blobs, uint64_t num_blobs, const char* name,
+                       int64_t gx, int64_t gy, int64_t gz, int64_t bx, int64_t by, int64_t bz,
+                       int32_t smem, void* stream, int32_t num_args, void** params) {
+  ctx->signal_error(std::string("ral_kernel_launch: generated kernel '") + (name ? name : "?") +
+                    "' cannot run here; lower it to a disc_b200_* custom call");
+}
+
+DISC_B200_RAL_API("alloc", "gpu", ral_alloc);
+DISC_B200_RAL_API("dealloc", "gpu", ral_dealloc);
+DISC_B200_RAL_API("ral_gpu_alloc_persistent", "gpu", ral_alloc_persistent);
+DISC_B200_RAL_API("ral_gpu_memset", "gpu", ral_memset);
+DISC_B200_RAL_API("ral_gpu_get_stream", "gpu", ral_get_stream);
+DISC_B200_RAL_API("ral_gpu_as_cu_stream", "gpu", ral_as_cu_stream);
+DISC_B200_RAL_API("d2d_", "gpu", ral_d2d);
+DISC_B200_RAL_API("h2d_", "gpu", ral_h2d);
+DISC_B200_RAL_API("d2h_", "gpu", ral_d2h);
+DISC_B200_RAL_API("sync_on_stream", "gpu", ral_sync_on_stream);
+DISC_B200_RAL_API("ral_gpu_sync_all", "gpu", ral_sync_all);
+DISC_B200_RAL_API("ral_kernel_launch", "gpu", ral_kernel_launch);
+
+template <typename T, int N>
+MemRef<T, N> ral_recv_input(ExecContext* ctx, int64_t idx) {
+  MemRef<T, N> m;
+  std::memset(&m, 0, sizeof(m));
+  auto it = ctx->inputs.find(idx);
+  if (it == ctx->inputs.end()) {
+    ctx->signal_error("invalid input index");
+    return m;
+  }
+  if (static_cast<int>(it->second.shape.size()) != N) {
+    ctx->signal_error("input rank does not match the compiled signature");
+    return m;
+  }
+  return make_memref<T, N>(static_cast<T*>(it->second.data), it->second.shape.data());
+}
+
+template <typename T, int N>
+void ral_send_output(ExecContext* ctx, int64_t idx, MemRef<T, N> m) {
+  BoundTensor t;
+  t.data = m.data;
+  if constexpr (N > 0) t.shape.assign(m.sizes, m.sizes + N);
+  ctx->outputs[idx] = t;
+}
+
+#define DISC_B200_REGISTER_IO(T, N)                                     \
+  DISC_B200_RAL_API("ral_recv_input", "cpu", ral_recv_input<T, N>);     \
+  DISC_B200_RAL_API("ral_send_output", "cpu", ral_send_output<T, N>)
+#define DISC_B200_REGISTER_IO_RANKS(T) \
+  DISC_B200_REGISTER_IO(T, 0);         \
+  DISC_B200_REGISTER_IO(T, 1);         \
+  DISC_B200_REGISTER_IO(T, 2);         \
+  DISC_B200_REGISTER_IO(T, 3);         \
+  DISC_B200_REGISTER_IO(T, 4)
+DISC_B200_REGISTER_IO_RANKS(float);
+DISC_B200_REGISTER_IO_RANKS(f16_t);
+DISC_B200_REGISTER_IO_RANKS(int8_t);
+DISC_B200_REGISTER_IO_RANKS(int32_t);
+DISC_B200_REGISTER_IO_RANKS(int64_t);
+DISC_B200_REGISTER_IO_RANKS(bool);
+
+// ------------------------------------------------------------ attr cache
+struct AttrCache {
+  std::mutex mu;
+  std::unordered_map<void*, std::unique_ptr<Attr>> map;
+};
+AttrCache& attr_cache() {
+  static AttrCache* c = new AttrCache;
+  return *c;
+}
+// Parsed once per blob address, like the reference (pdll_util.h:190-220).
+const Attr* attrs_of(ExecContext* ctx, void* blob) {
+  static const Attr kEmpty = [] {
+    Attr a;
+    a.kind = Attr::kDict;
+    return a;
+  }();
+  if (!blob) return &kEmpty;
+  AttrCache& c = attr_cache();
+  std::lock_guard<std::mutex> l(c.mu);
+  auto it = c.map.find(blob);
+  if (it == c.map.end()) {
+    const uint8_t* cur = static_cast<const uint8_t*>(blob);
+    auto a = parse_attr(&cur);
+    if (!a || a->kind != Attr::kDict) {
+      ctx->signal_error("fail to parse custom_attrs");
+      return nullptr;
+    }
+    it = c.map.emplace(blob, std::move(a)).first;
+  }
+  return it->second.get();
+}
+
+// ---------------------------------------------------- 2. reference qgemm
+template <int N>
+int64_t leading_rows(const MemRef<int8_t, N>& in, int64_t* result_sizes, int64_t n) {
+  int64_t m = 1;
+  for (int i = 0; i < N - 1; ++i) {
+    m *= in.sizes[i];
+    result_sizes[i] = in.sizes[i];
+  }
+  result_sizes[N - 1] = n;
+  return m;
+}
+
+bool run_qgemm(ExecContext* ctx, QGemmParams& p) {
+  if (p.M <= 128) {
+    const int64_t need = qgemm_splitk_ws_bytes(p.M, p.N, p.K);
+    p.splitk_ws = static_cast<int32_t*>(ctx->ctx->get_splitk_ws(need));
+    p.splitk_ws_bytes = p.splitk_ws ? ctx->ctx->splitk_ws_bytes : 0;
+  }
+  const char* detail = nullptr;
+  cudaError_t st = qgemm_launch(p, stream_of(ctx), &detail);
+  if (st != cudaSuccess) {
+    report(ctx, st, "qgemm", detail);
+    return false;
+  }
+  return true;
+}
+
+QGemmParams base_params(const int8_t* a, const int8_t* w, void* out, int64_t m, int64_t n,
+                        int64_t k) {
+  QGemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.a = a;
+  p.w = w;
+  p.out = out;
+  p.M = m;
+  p.N = n;
+  p.K = k;
+  p.lda = k;
+  p.ldw = k;
+  p.ldo = n;
+  return p;
+}
+
+// out_i8 = sat(rne(acc * (s_x * s_w / s_out) + bias)), zero points ignored
+// (symmetric), result allocated here and owned by the caller.
+template <int N, typename BiasT>
+MemRef<int8_t, N> pdll_qgemm_per_tensor(ExecContext* ctx, void* stream_handle,
+                                        MemRef<int8_t, N> input, MemRef<int8_t, 2> weight,
+                                        MemRef<BiasT, 1> bias, MemRef<float, 0> in_scale,
+                                        MemRef<int32_t, 0> in_zp, MemRef<float, 0> w_scale,
+                                        MemRef<int32_t, 0> w_zp, MemRef<float, 0> out_scale,
+                                        MemRef<int32_t, 0> out_zp, void* custom_attrs) {
+  const int64_t k = weight.sizes[1];
+  const int64_t n = weight.sizes[0];
+  int64_t rs[N];
+  const int64_t m = leading_rows<N>(input, rs, n);
+  if (memref_numel(input) == 0 || memref_numel(weight) == 0) {
+    return make_memref<int8_t, N>(nullptr, rs);
+  }
+  if (input.sizes[N - 1] != k) {
+    ctx->signal_error("ral_pdll_qgemm: input and weight disagree on K");
+    return make_memref<int8_t, N>(nullptr, rs);
+  }
+  int8_t* out = static_cast<int8_t*>(ctx->alloc(static_cast<size_t>(m * n)));
+  auto result = make_memref<int8_t, N>(out, rs);
+  if (!out) return result;
+  QGemmParams p = base_params(input.data, weight.data, out, m, n, k);
+  p.x_scale = in_scale.data;
+  p.w_scale = w_scale.data;
+  p.out_scale = out_scale.data;
+  p.x_scale_kind = kScaleScalar;
+  p.w_scale_kind = kScaleScalar;
+  p.out_scale_kind = kScaleScalar;
+  p.fold_out_scale = 1;
+  p.bias = bias.data;
+  p.bias_kind = std::is_same_v<BiasT, float> ? kBiasF32 : kBiasI8;
+  p.out_dtype = kOutI8;
+  run_qgemm(ctx, p);
+  return result;
+}
+
+// Per-channel form produced by the QKV-merge pass: every scale operand has N
+// entries, bias is int8.
+template <int N>
+MemRef<int8_t, N> pdll_qgemm_per_channel(ExecContext* ctx, void* stream_handle,
+                                         MemRef<int8_t, N> input, MemRef<int8_t, 2> weight,
+                                         MemRef<int8_t, 1> bias, MemRef<float, 1> in_scale,
+                                         MemRef<int32_t, 1> in_zp, MemRef<float, 1> w_scale,
+                                         MemRef<int32_t, 1> w_zp, MemRef<float, 1> out_scale,
+                                         MemRef<int32_t, 1> out_zp, void* custom_attrs) {
+  const int64_t k = weight.sizes[1];
+  const int64_t n = weight.sizes[0];
+  int64_t rs[N];
+  const int64_t m = leading_rows<N>(input, rs, n);
+  if (memref_numel(input) == 0 || memref_numel(weight) == 0) {
+    return make_memref<int8_t, N>(nullptr, rs);
+  }
+  if (input.sizes[N - 1] != k || in_scale.sizes[0] != n || w_scale.sizes[0] != n ||
+      out_scale.sizes[0] != n || bias.sizes[0] != n) {
+    ctx->signal_error("ral_pdll_qgemm_per_channel: operand extents disagree");
+    return make_memref<int8_t, N>(nullptr, rs);
+  }
+  int8_t* out = static_cast<int8_t*>(ctx->alloc(static_cast<size_t>(m * n)));
+  auto result = make_memref<int8_t, N>(out, rs);
+  if (!out) return result;
+  QGemmParams p = base_params(input.data, weight.data, out, m, n, k);
+  p.x_scale = in_scale.data;
+  p.w_scale = w_scale.data;
+  p.out_scale = out_scale.data;
+  p.x_scale_kind = kScalePerCol;
+  p.w_scale_kind = kScalePerCol;
+  p.out_scale_kind = kScalePerCol;
+  p.fold_out_scale = 1;
+  p.bias = bias.data;
+  p.bias_kind = kBiasI8;
+  p.out_dtype = kOutI8;
+  run_qgemm(ctx, p);
+  return result;
+}
+
+// Older form: result buffer passed in, no bias.  The GPU rewriter lays the
+// weight out as [N, K] (tp_b = true); other layouts are not produced for GPU.
+void ral_qgemm_gpu(ExecContext* ctx, void* stream_handle, MemRef<int8_t, 2> input,
+                   MemRef<int8_t, 2> weight, MemRef<float, 0> in_scale, MemRef<int32_t, 0> in_zp,
+                   MemRef<float, 0> w_scale, MemRef<int32_t, 0> w_zp, MemRef<float, 0> out_scale,
+                   MemRef<int32_t, 0> out_zp, MemRef<int8_t, 2> result, bool tp_a, bool tp_b,
+                   bool weight_is_const) {
+  if (memref_numel(input) == 0 || memref_numel(weight) == 0 || memref_numel(result) == 0) return;
+  if (tp_a || !tp_b) {
+    ctx->signal_error("ral_qgemm: only input [M,K] x weight [N,K] (tp_a = false, tp_b = true)");
+    return;
+  }
+  const int64_t m = input.sizes[0], k = input.sizes[1], n = weight.sizes[0];
+  if (weight.sizes[1] != k || result.sizes[0] != m || result.sizes[1] != n) {
+    ctx->signal_error("ral_qgemm: operand extents disagree");
+    return;
+  }
+  QGemmParams p = base_params(input.data, weight.data, result.data, m, n, k);
+  p.x_scale = in_scale.data;
+  p.w_scale = w_scale.data;
+  p.out_scale = out_scale.data;
+  p.x_scale_kind = kScaleScalar;
+  p.w_scale_kind = kScaleScalar;
+  p.out_scale_kind = kScaleScalar;
+  p.fold_out_scale = 1;
+  p.bias_kind = kBiasNone;
+  p.out_dtype = kOutI8;
+  run_qgemm(ctx, p);
+}
+
+DISC_B200_RAL_API("ral_pdll_qgemm", "gpu", pdll_qgemm_per_tensor<2, int8_t>);
+DISC_B200_RAL_API("ral_pdll_qgemm", "gpu", pdll_qgemm_per_tensor<3, int8_t>);
+DISC_B200_RAL_API("ral_pdll_qgemm", "gpu", pdll_qgemm_per_tensor<2, float>);
+DISC_B200_RAL_API("ral_pdll_qgemm", "gpu", pdll_qgemm_per_tensor<3, float>);
+DISC_B200_RAL_API("ral_pdll_qgemm_per_channel", "gpu", pdll_qgemm_per_channel<2>);
+DISC_B200_RAL_API("ral_pdll_qgemm_per_channel", "gpu", pdll_qgemm_per_channel<3>);
+DISC_B200_RAL_API("ral_qgemm", "gpu", ral_qgemm_gpu);
+
+// ------------------------------------------------------- 3. fused forms
+int act_from(const Attr* a) {
+  const std::string s = a->get_str("activation", "none");
+  if (s == "gelu") return kActGelu;
+  if (s == "silu") return kActSilu;
+  return kActNone;
+}
+
+template <typename T>
+constexpr int elem_type_of() {
+  return std::is_same_v<T, float> ? kF32 : kF16;
+}
+
+// y = act(acc * s_x * s_w[n] + bias[n]) as f16, or requantized to int8 at
+// out_scale: dequantize + bias + activation (+ quantize) of the reference
+// graph in the GEMM epilogue.  XS is MemRef<float,0> (static activation scale)
+// or MemRef<float,1> (one scale per row, from disc_b200_dynamic_quantize).
+template <int N, typename OutT, typename XS>
+MemRef<OutT, N> fused_qgemm(ExecContext* ctx, void* stream_handle, MemRef<int8_t, N> input,
+                            MemRef<int8_t, 2> weight, MemRef<float, 1> bias, XS x_scale,
+                            MemRef<float, 1> w_scale, MemRef<float, 0> out_scale,
+                            void* custom_attrs) {
+  const int64_t k = weight.sizes[1];
+  const int64_t n = weight.sizes[0];
+  int64_t rs[N];
+  const int64_t m = leading_rows<N>(input, rs, n);
+  if (memref_numel(input) == 0 || memref_numel(weight) == 0) {
+    return make_memref<OutT, N>(nullptr, rs);
+  }
+  const Attr* at = attrs_of(ctx, custom_attrs);
+  if (!at) return make_memref<OutT, N>(nullptr, rs);
+  if (input.sizes[N - 1] != k || w_scale.sizes[0] != n) {
+    ctx->signal_error("disc_b200_qgemm: operand extents disagree");
+    return make_memref<OutT, N>(nullptr, rs);
+  }
+  OutT* out = static_cast<OutT*>(ctx->alloc(static_cast<size_t>(m * n) * sizeof(OutT)));
+  auto result = make_memref<OutT, N>(out, rs);
+  if (!out) return result;
+  QGemmParams p = base_params(input.data, weight.data, out, m, n, k);
+  p.x_scale = x_scale.data;
+  p.x_scale_kind = std::is_same_v<XS, MemRef<float, 0>> ? kScaleScalar : kScalePerRow;
+  p.w_scale = w_scale.data;
+  p.w_scale_kind = kScalePerCol;
+  p.bias = memref_numel(bias) == n ? bias.data : nullptr;
+  p.bias_kind = p.bias ? kBiasF32 : kBiasNone;
+  p.act = act_from(at);
+  if constexpr (std::is_same_v<OutT, int8_t>) {
+    p.out_scale = out_scale.data;
+    p.out_scale_kind = kScaleScalar;
+    p.div_out_scale = 1;
+    p.out_dtype = kOutI8;
+  } else {
+    p.out_dtype = kOutF16;
+  }
+  run_qgemm(ctx, p);
+  return result;
+}
+
+DISC_B200_RAL_API("disc_b200_qgemm", "gpu", fused_qgemm<2, f16_t, MemRef<float, 0>>);
+DISC_B200_RAL_API("disc_b200_qgemm", "gpu", fused_qgemm<3, f16_t, MemRef<float, 0>>);
+DISC_B200_RAL_API("disc_b200_qgemm", "gpu", fused_qgemm<2, int8_t, MemRef<float, 0>>);
+DISC_B200_RAL_API("disc_b200_qgemm", "gpu", fused_qgemm<3, int8_t, MemRef<float, 0>>);
+DISC_B200_RAL_API("disc_b200_qgemm", "gpu", fused_qgemm<2, f16_t, MemRef<float, 1>>);
+DISC_B200_RAL_API("disc_b200_qgemm", "gpu", fused_qgemm<3, f16_t, MemRef<float, 1>>);
+DISC_B200_RAL_API("disc_b200_qgemm", "gpu", fused_qgemm<2, int8_t, MemRef<float, 1>>);
+DISC_B200_RAL_API("disc_b200_qgemm", "gpu", fused_qgemm<3, int8_t, MemRef<float, 1>>);
+
+template <typename T, int N>
+MemRef<int8_t, N> quantize_call(ExecContext* ctx, void* stream_handle, MemRef<T, N> x,
+                                MemRef<float, 0> scale, MemRef<int32_t, 0> zp, void* custom_attrs) {
+  const int64_t numel = memref_numel(x);
+  if (numel == 0) return make_memref<int8_t, N>(nullptr, x.sizes);
+  const Attr* at = attrs_of(ctx, custom_attrs);
+  if (!at) return make_memref<int8_t, N>(nullptr, x.sizes);
+  int8_t* q = static_cast<int8_t*>(ctx->alloc(static_cast<size_t>(numel)));
+  auto result = make_memref<int8_t, N>(q, x.sizes);
+  if (!q) return result;
+  QuantizeParams p;
+  p.x = x.data;
+  p.q = q;
+  p.numel = numel;
+  p.in_type = elem_type_of<T>();
+  p.scale = scale.data;
+  p.zero_point = zp.data;
+  p.channels = 1;
+  p.inner = 1;
+  p.qmin = static_cast<int>(at->get_int("quant_min", -128));
+  p.qmax = static_cast<int>(at->get_int("quant_max", 127));
+  const char* detail = nullptr;
+  report(ctx, quantize_launch(p, stream_of(ctx), &detail), "quantize", detail);
+  return result;
+}
+
+template <typename T, int N>
+std::tuple<MemRef<int8_t, N>, MemRef<float, 1>> dynamic_quantize_call(ExecContext* ctx,
+                                                                      void* stream_handle,
+                                                                      MemRef<T, N> x,
+                                                                      void* custom_attrs) {
+  const int64_t cols = x.sizes[N - 1];
+  const int64_t numel = memref_numel(x);
+  const int64_t rows = cols > 0 ? numel / cols : 0;
+  int64_t rsz[1] = {rows};
+  if (numel == 0) {
+    return std::make_tuple(make_memref<int8_t, N>(nullptr, x.sizes), make_memref<float, 1>(nullptr, rsz));
+  }
+  int8_t* q = static_cast<int8_t*>(ctx->alloc(static_cast<size_t>(numel)));
+  float* s = static_cast<float*>(ctx->alloc(static_cast<size_t>(rows) * sizeof(float)));
+  auto r0 = make_memref<int8_t, N>(q, x.sizes);
+  auto r1 = make_memref<float, 1>(s, rsz);
+  if (!q || !s) return std::make_tuple(r0, r1);
+  DynQuantParams p;
+  p.x = x.data;
+  p.q = q;
+  p.row_scale = s;
+  p.rows = rows;
+  p.cols = cols;
+  p.in_type = elem_type_of<T>();
+  const char* detail = nullptr;
+  report(ctx, dynamic_quantize_launch(p, stream_of(ctx), &detail), "dynamic_quantize", detail);
+  return std::make_tuple(r0, r1);
+}
+
+template <typename T, int N>
+MemRef<T, N> dequantize_call(ExecContext* ctx, void* stream_handle, MemRef<int8_t, N> q,
+                             MemRef<float, 0> scale, MemRef<int32_t, 0> zp, void* custom_attrs) {
+  const int64_t numel = memref_numel(q);
+  if (numel == 0) return make_memref<T, N>(nullptr, q.sizes);
+  T* y = static_cast<T*>(ctx->alloc(static_cast<size_t>(numel) * sizeof(T)));
+  auto result = make_memref<T, N>(y, q.sizes);
+  if (!y) return result;
+  DequantizeParams p;
+  p.q = q.data;
+  p.y = y;
+  p.numel = numel;
+  p.out_type = elem_type_of<T>();
+  p.scale = scale.data;
+  p.zero_point = zp.data;
+  p.channels = 1;
+  p.inner = 1;
+  const char* detail = nullptr;
+  report(ctx, dequantize_launch(p, stream_of(ctx), &detail), "dequantize", detail);
+  return result;
+}
+
+template <typename T, int N>
+NormParams norm_params(const MemRef<T, N>& x, const T* residual, const T* gamma, const T* beta,
+                       float eps, int rms) {
+  NormParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.x = x.data;
+  p.residual = residual;
+  p.gamma = gamma;
+  p.beta = beta;
+  p.cols = x.sizes[N - 1];
+  p.rows = p.cols > 0 ? memref_numel(x) / p.cols : 0;
+  p.eps = eps;
+  p.type = elem_type_of<T>();
+  p.rms = rms;
+  return p;
+}
+
+template <typename T, int N>
+MemRef<T, N> layernorm_call(ExecContext* ctx, void* stream_handle, MemRef<T, N> x,
+                            MemRef<T, 1> gamma, MemRef<T, 1> beta, void* custom_attrs) {
+  if (memref_numel(x) == 0) return make_memref<T, N>(nullptr, x.sizes);
+  const Attr* at = attrs_of(ctx, custom_attrs);
+  if (!at) return make_memref<T, N>(nullptr, x.sizes);
+  T* y = static_cast<T*>(ctx->alloc(static_cast<size_t>(memref_numel(x)) * sizeof(T)));
+  auto result = make_memref<T, N>(y, x.sizes);
+  if (!y) return result;
+  NormParams p = norm_params<T, N>(x, nullptr, gamma.data, beta.data,
+                                   static_cast<float>(at->get_float("eps", 1e-5)), 0);
+  p.y = y;
+  const char* detail = nullptr;
+  report(ctx, norm_launch(p, stream_of(ctx), &detail), "layernorm", detail);
+  return result;
+}
+
+template <typename T, int N>
+MemRef<T, N> add_layernorm_call(ExecContext* ctx, void* stream_handle, MemRef<T, N> x,
+                                MemRef<T, N> residual, MemRef<T, 1> gamma, MemRef<T, 1> beta,
+                                void* custom_attrs) {
+  if (memref_numel(x) == 0) return make_memref<T, N>(nullptr, x.sizes);
+  const Attr* at = attrs_of(ctx, custom_attrs);
+  if (!at) return make_memref<T, N>(nullptr, x.sizes);
+  if (memref_numel(residual) != memref_numel(x)) {
+    ctx->signal_error("disc_b200_add_layernorm: residual shape differs");
+    return make_memref<T, N>(nullptr, x.sizes);
+  }
+  T* y = static_cast<T*>(ctx->alloc(static_cast<size_t>(memref_numel(x)) * sizeof(T)));
+  auto result = make_memref<T, N>(y, x.sizes);
+  if (!y) return result;
+  NormParams p = norm_params<T, N>(x, residual.data, gamma.data, beta.data,
+                                   static_cast<float>(at->get_float("eps", 1e-5)), 0);
+  p.y = y;
+  const char* detail = nullptr;
+  report(ctx, norm_launch(p, stream_of(ctx), &detail), "add_layernorm", detail);
+  return result;
+}
+
+// LayerNorm(x + residual) with a second, int8 output at a static scale.
+template <typename T, int N>
+std::tuple<MemRef<T, N>, MemRef<int8_t, N>> add_layernorm_quant_call(
+    ExecContext* ctx, void* stream_handle, MemRef<T, N> x, MemRef<T, N> residual,
+    MemRef<T, 1> gamma, MemRef<T, 1> beta, MemRef<float, 0> q_scale, void* custom_attrs) {
+  auto empty = std::make_tuple(make_memref<T, N>(nullptr, x.sizes), make_memref<int8_t, N>(nullptr, x.sizes));
+  if (memref_numel(x) == 0) return empty;
+  const Attr* at = attrs_of(ctx, custom_attrs);
+  if (!at) return empty;
+  if (memref_numel(residual) != memref_numel(x)) {
+    ctx->signal_error("disc_b200_add_layernorm_quant: residual shape differs");
+    return empty;
+  }
+  const size_t numel = static_cast<size_t>(memref_numel(x));
+  T* y = static_cast<T*>(ctx->alloc(numel * sizeof(T)));
+  int8_t* q = static_cast<int8_t*>(ctx->alloc(numel));
+  auto result = std::make_tuple(make_memref<T, N>(y, x.sizes), make_memref<int8_t, N>(q, x.sizes));
+  if (!y || !q) return result;
+  NormParams p = norm_params<T, N>(x, residual.data, gamma.data, beta.data,
+                                   static_cast<float>(at->get_float("eps", 1e-5)), 0);
+  p.y = y;
+  p.q_out = q;
+  p.q_scale = q_scale.data;
+  const char* detail = nullptr;
+  report(ctx, norm_launch(p, stream_of(ctx), &detail), "add_layernorm_quant", detail);
+  return result;
+}
+
+template <typename T, int N>
+MemRef<T, N> rmsnorm_call(ExecContext* ctx, void* stream_handle, MemRef<T, N> x, MemRef<T, 1> gamma,
+                          void* custom_attrs) {
+  if (memref_numel(x) == 0) return make_memref<T, N>(nullptr, x.sizes);
+  const Attr* at = attrs_of(ctx, custom_attrs);
+  if (!at) return make_memref<T, N>(nullptr, x.sizes);
+  T* y = static_cast<T*>(ctx->alloc(static_cast<size_t>(memref_numel(x)) * sizeof(T)));
+  auto result = make_memref<T, N>(y, x.sizes);
+  if (!y) return result;
+  NormParams p = norm_params<T, N>(x, nullptr, gamma.data, nullptr,
+                                   static_cast<float>(at->get_float("eps", 1e-6)), 1);
+  p.y = y;
+  const char* detail = nullptr;
+  report(ctx, norm_launch(p, stream_of(ctx), &detail), "rmsnorm", detail);
+  return result;
+}
+
+template <typename T, int N>
+MemRef<T, N> softmax_impl(ExecContext* ctx, MemRef<T, N> x, const int32_t* lens, int64_t batches,
+                          void* custom_attrs) {
+  if (memref_numel(x) == 0) return make_memref<T, N>(nullptr, x.sizes);
+  const Attr* at = attrs_of(ctx, custom_attrs);
+  if (!at) return make_memref<T, N>(nullptr, x.sizes);
+  T* y = static_cast<T*>(ctx->alloc(static_cast<size_t>(memref_numel(x)) * sizeof(T)));
+  auto result = make_memref<T, N>(y, x.sizes);
+  if (!y) return result;
+  SoftmaxParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.x = x.data;
+  p.y = y;
+  p.cols = x.sizes[N - 1];
+  p.rows = memref_numel(x) / p.cols;
+  p.rows_per_batch = (lens && batches > 0) ? p.rows / batches : p.rows;
+  p.lens = lens;
+  p.scale = static_cast<float>(at->get_float("scale", 1.0));
+  p.type = elem_type_of<T>();
+  p.log_softmax = at->get_bool("log", false) ? 1 : 0;
+  const char* detail = nullptr;
+  report(ctx, softmax_launch(p, stream_of(ctx), &detail), "softmax", detail);
+  return result;
+}
+
+template <typename T, int N>
+MemRef<T, N> softmax_call(ExecContext* ctx, void* stream_handle, MemRef<T, N> x, void* custom_attrs) {
+  return softmax_impl<T, N>(ctx, x, nullptr, 0, custom_attrs);
+}
+
+// Rows of batch b (the leading axis) keep only their first lens[b] columns.
+template <typename T, int N>
+MemRef<T, N> masked_softmax_call(ExecContext* ctx, void* stream_handle, MemRef<T, N> x,
+                                 MemRef<int32_t, 1> lens, void* custom_attrs) {
+  if (lens.sizes[0] != x.sizes[0]) {
+    ctx->signal_error("disc_b200_masked_softmax: one length per leading index expected");
+    return make_memref<T, N>(nullptr, x.sizes);
+  }
+  return softmax_impl<T, N>(ctx, x, lens.data, x.sizes[0], custom_attrs);
+}
+
+#define DISC_B200_REGISTER_ROWOPS(T, N)                                                  \
+  DISC_B200_RAL_API("disc_b200_quantize", "gpu", quantize_call<T, N>);                   \
+  DISC_B200_RAL_API("disc_b200_dynamic_quantize", "gpu", dynamic_quantize_call<T, N>);   \
+  DISC_B200_RAL_API("disc_b200_dequantize", "gpu", dequantize_call<T, N>);               \
+  DISC_B200_RAL_API("disc_b200_layernorm", "gpu", layernorm_call<T, N>);                 \
+  DISC_B200_RAL_API("disc_b200_add_layernorm", "gpu", add_layernorm_call<T, N>);         \
+  DISC_B200_RAL_API("disc_b200_add_layernorm_quant", "gpu", add_layernorm_quant_call<T, N>); \
+  DISC_B200_RAL_API("disc_b200_rmsnorm", "gpu", rmsnorm_call<T, N>);                     \
+  DISC_B200_RAL_API("disc_b200_softmax", "gpu", softmax_call<T, N>)
+DISC_B200_REGISTER_ROWOPS(float, 2);
+DISC_B200_REGISTER_ROWOPS(float, 3);
+DISC_B200_REGISTER_ROWOPS(f16_t, 2);
+DISC_B200_REGISTER_ROWOPS(f16_t, 3);
+DISC_B200_RAL_API("disc_b200_softmax", "gpu", softmax_call<float, 4>);
+DISC_B200_RAL_API("disc_b200_softmax", "gpu", softmax_call<f16_t, 4>);
+DISC_B200_RAL_API("disc_b200_masked_softmax", "gpu", masked_softmax_call<float, 4>);
+DISC_B200_RAL_API("disc_b200_masked_softmax", "gpu", masked_softmax_call<f16_t, 4>);
+DISC_B200_RAL_API("disc_b200_masked_softmax", "gpu", masked_softmax_call<float, 3>);
+DISC_B200_RAL_API("disc_b200_masked_softmax", "gpu", masked_softmax_call<f16_t, 3>);
+
+}  // namespace
+}  // namespace ral
+}  // namespace disc_b200

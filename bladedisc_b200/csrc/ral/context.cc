@@ -1,0 +1,267 @@
+#include "context.h"
+
+#include <cstring>
+#include <map>
+
+#include "abi.h"
+
+namespace disc_b200 {
+namespace ral {
+
+// ---------------------------------------------------------------- registry
+namespace {
+struct RegistryState {
+  std::mutex mu;
+  std::unordered_map<std::string, ApiFn> table;
+  std::vector<std::string> full_names;  // mangled names only, in registration order
+};
+RegistryState& registry() {
+  static RegistryState* r = new RegistryState;  // never destroyed: used by static registrars
+  return *r;
+}
+}  // namespace
+
+bool registry_add(const std::string& mangled, const std::string& nickname, ApiFn fn) {
+  RegistryState& r = registry();
+  std::lock_guard<std::mutex> l(r.mu);
+  const bool fresh = r.table.emplace(mangled, fn).second;
+  if (fresh) r.full_names.push_back(mangled);
+  r.table.emplace(nickname, fn);  // first registration keeps the nickname
+  return fresh;
+}
+
+ApiFn registry_find(const std::string& name) {
+  RegistryState& r = registry();
+  std::lock_guard<std::mutex> l(r.mu);
+  auto it = r.table.find(name);
+  return it == r.table.end() ? nullptr : it->second;
+}
+
+int registry_size() {
+  RegistryState& r = registry();
+  std::lock_guard<std::mutex> l(r.mu);
+  return static_cast<int>(r.full_names.size());
+}
+
+const char* registry_name_at(int i) {
+  RegistryState& r = registry();
+  std::lock_guard<std::mutex> l(r.mu);
+  if (i < 0 || i >= static_cast<int>(r.full_names.size())) return nullptr;
+  return r.full_names[i].c_str();
+}
+
+// ----------------------------------------------------------------- context
+void* Context::raw_alloc(size_t bytes) {
+  if (bytes == 0) bytes = 1;  // as the reference: zero-byte requests still get a pointer
+  if (alloc_fn) return alloc_fn(alloc_user, bytes);
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) return nullptr;
+  return p;
+}
+
+void Context::raw_free(void* p) {
+  if (!p) return;
+  if (free_fn) {
+    free_fn(alloc_user, p);
+    return;
+  }
+  cudaFree(p);
+}
+
+void Context::signal_error(int32_t code, const std::string& msg) {
+  std::lock_guard<std::mutex> l(mu);
+  if (status != 0) return;  // keep the first error
+  status = code;
+  message = msg;
+}
+
+bool Context::ok() {
+  std::lock_guard<std::mutex> l(mu);
+  return status == 0;
+}
+
+void* Context::get_splitk_ws(int64_t bytes) {
+  std::lock_guard<std::mutex> l(mu);
+  if (bytes <= splitk_ws_bytes) return splitk_ws;
+  // Work queued on the stream may still use the old block.
+  cudaStreamSynchronize(stream);
+  if (splitk_ws) raw_free(splitk_ws);
+  int64_t want = bytes < (8 << 20) ? (8 << 20) : bytes;
+  splitk_ws = raw_alloc(static_cast<size_t>(want));
+  splitk_ws_bytes = splitk_ws ? want : 0;
+  if (splitk_ws) cudaMemsetAsync(splitk_ws, 0, static_cast<size_t>(want), stream);
+  return splitk_ws;
+}
+
+Context::~Context() {
+  for (void* p : persistent) raw_free(p);
+  if (splitk_ws) raw_free(splitk_ws);
+  magic = 0;
+}
+
+void* ExecContext::alloc(size_t bytes) {
+  void* p = ctx->raw_alloc(bytes);
+  if (!p) {
+    signal_error("device allocation of " + std::to_string(bytes) + " bytes failed");
+    return nullptr;
+  }
+  refcount[p] = 1;
+  return p;
+}
+
+void ExecContext::dealloc(void* p) {
+  if (!p) return;
+  {
+    std::lock_guard<std::mutex> l(ctx->mu);
+    if (ctx->persistent.count(p)) return;
+  }
+  auto it = refcount.find(p);
+  if (it == refcount.end()) return;  // not ours (an input, or another context's buffer)
+  if (--it->second == 0) {
+    refcount.erase(it);
+    ctx->raw_free(p);
+  }
+}
+
+Context* context_of(void* handle) {
+  if (!handle) return nullptr;
+  uint32_t magic;
+  std::memcpy(&magic, handle, sizeof(magic));
+  if (magic == kContextMagic) return static_cast<Context*>(handle);
+  if (magic == kExecMagic) return static_cast<ExecContext*>(handle)->ctx;
+  return nullptr;
+}
+
+}  // namespace ral
+}  // namespace disc_b200
+
+// ------------------------------------------------------------------- C ABI
+using disc_b200::ral::Context;
+using disc_b200::ral::ExecContext;
+
+extern "C" {
+
+const char* const kMlirLoweredEntry = "main";
+
+void tao_ral_call_impl(tao_ral_context_t handle, void* name, void** args) {
+  if (!handle) return;
+  uint32_t magic;
+  std::memcpy(&magic, handle, sizeof(magic));
+  if (magic != disc_b200::ral::kExecMagic) return;
+  ExecContext* exec = static_cast<ExecContext*>(handle);
+  if (!name || !args) {
+    exec->signal_error("tao_ral_call_impl: null name or args");
+    return;
+  }
+  // Once a call has failed the following ones are skipped, so that a compiled
+  // executable runs through to its end without touching half-made results.
+  if (!exec->ctx->ok()) return;
+  const char* api = static_cast<const char*>(name);
+  disc_b200::ral::ApiFn fn = disc_b200::ral::registry_find(api);
+  if (!fn) {
+    exec->signal_error(std::string("api_func ") + api + " not found");
+    return;
+  }
+  fn(args);
+}
+
+tao_ral_status_t tao_ral_last_error(tao_ral_context_t handle, const char** err_msg) {
+  Context* ctx = disc_b200::ral::context_of(handle);
+  if (!ctx) {
+    if (err_msg) *err_msg = "invalid context handle";
+    return 1;
+  }
+  std::lock_guard<std::mutex> l(ctx->mu);
+  if (err_msg) *err_msg = ctx->message.c_str();
+  return ctx->status;
+}
+
+void tao_ral_clear_error(tao_ral_context_t handle) {
+  Context* ctx = disc_b200::ral::context_of(handle);
+  if (!ctx) return;
+  std::lock_guard<std::mutex> l(ctx->mu);
+  ctx->status = 0;
+  ctx->message.clear();
+}
+
+disc_b200_context* disc_b200_context_create(const disc_b200_context_options* opts) {
+  Context* c = new Context;
+  if (opts) {
+    c->device = opts->device;
+    c->stream = static_cast<cudaStream_t>(opts->stream);
+    c->alloc_fn = opts->gpu_alloc;
+    c->free_fn = opts->gpu_free;
+    c->alloc_user = opts->alloc_user;
+    c->nccl_comm = opts->nccl_comm;
+    c->comm_stream = static_cast<cudaStream_t>(opts->comm_stream ? opts->comm_stream : opts->stream);
+  }
+  return reinterpret_cast<disc_b200_context*>(c);
+}
+
+void disc_b200_context_destroy(disc_b200_context* ctx) { delete reinterpret_cast<Context*>(ctx); }
+
+disc_b200_exec* disc_b200_exec_create(disc_b200_context* ctx) {
+  if (!ctx) return nullptr;
+  ExecContext* e = new ExecContext;
+  e->ctx = reinterpret_cast<Context*>(ctx);
+  return reinterpret_cast<disc_b200_exec*>(e);
+}
+
+void disc_b200_exec_destroy(disc_b200_exec* handle) {
+  ExecContext* e = reinterpret_cast<ExecContext*>(handle);
+  if (!e) return;
+  std::unordered_set<void*> handed_out;
+  for (auto& kv : e->outputs) handed_out.insert(kv.second.data);
+  for (auto& kv : e->refcount) {
+    if (!handed_out.count(kv.first)) e->ctx->raw_free(kv.first);
+  }
+  e->magic = 0;
+  delete e;
+}
+
+int32_t disc_b200_exec_bind_input(disc_b200_exec* handle, int32_t idx, const void* data,
+                                  int32_t rank, const int64_t* sizes) {
+  ExecContext* e = reinterpret_cast<ExecContext*>(handle);
+  if (!e || rank < 0 || (rank > 0 && !sizes)) return 1;
+  disc_b200::ral::BoundTensor t;
+  t.data = const_cast<void*>(data);
+  if (rank > 0) t.shape.assign(sizes, sizes + rank);
+  e->inputs[idx] = t;
+  e->input_ptrs.insert(t.data);
+  return 0;
+}
+
+int32_t disc_b200_exec_get_output(disc_b200_exec* handle, int32_t idx, void** data, int32_t* rank,
+                                  int64_t* sizes8, int32_t* owned) {
+  ExecContext* e = reinterpret_cast<ExecContext*>(handle);
+  if (!e) return 1;
+  auto it = e->outputs.find(idx);
+  if (it == e->outputs.end()) return 1;
+  if (data) *data = it->second.data;
+  if (rank) *rank = static_cast<int32_t>(it->second.shape.size());
+  if (sizes8) {
+    for (size_t i = 0; i < it->second.shape.size() && i < 8; ++i) sizes8[i] = it->second.shape[i];
+  }
+  if (owned) {
+    // An output that aliases an input, a persistent buffer, or a buffer that
+    // is also another output with a smaller index stays with its first owner.
+    bool mine = e->refcount.count(it->second.data) != 0;
+    for (auto& kv : e->outputs) {
+      if (kv.first < idx && kv.second.data == it->second.data) mine = false;
+    }
+    *owned = mine ? 1 : 0;
+  }
+  return 0;
+}
+
+void disc_b200_exec_free_output(disc_b200_context* ctx, void* data) {
+  if (ctx) reinterpret_cast<Context*>(ctx)->raw_free(data);
+}
+
+int32_t disc_b200_registry_size(void) { return disc_b200::ral::registry_size(); }
+const char* disc_b200_registry_name(int32_t i) { return disc_b200::ral::registry_name_at(i); }
+int32_t disc_b200_registry_has(const char* n) {
+  return n && disc_b200::ral::registry_find(n) != nullptr ? 1 : 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,78 @@
+// Runtime context of the custom calls: the state the reference spreads over
+// tao::ral::Context / ExecutionContext (tao_compiler/mlir/ral/ral_context.h:55-199)
+// and BaseCudaContextState / BaseCudaExecutionContext
+// (tao_compiler/mlir/ral/context/base/cuda/cuda_context_impl.cc:117-166,
+//  base_context.h), reduced to what the quantized path touches.
+//
+// Differences by design: an error is recorded (first one wins) and reported
+// through tao_ral_last_error instead of aborting the process
+// (tao_compiler/mlir/ral/ral_context.cc:185-191 logs FATAL); the api-name
+// lookup is one hash lookup on a string_view, no per-thread cache is needed.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <unordered_set>
+#include <vector>
+
+#include "../../../include/disc_b200_ral.h"
+
+namespace disc_b200 {
+namespace ral {
+
+constexpr uint32_t kContextMagic = 0xD15CB200u;
+constexpr uint32_t kExecMagic = 0xD15CE8ECu;
+
+struct Context {
+  uint32_t magic = kContextMagic;
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  disc_b200_alloc_fn alloc_fn = nullptr;
+  disc_b200_free_fn free_fn = nullptr;
+  void* alloc_user = nullptr;
+  void* nccl_comm = nullptr;
+  cudaStream_t comm_stream = nullptr;
+
+  std::mutex mu;
+  int32_t status = 0;
+  std::string message;
+  std::unordered_set<void*> persistent;  // survive executions, freed with the context
+  // Scratch of the small-M qgemm path (grown on demand, counters kept zero).
+  void* splitk_ws = nullptr;
+  int64_t splitk_ws_bytes = 0;
+
+  void* raw_alloc(size_t bytes);
+  void raw_free(void* p);
+  void signal_error(int32_t code, const std::string& msg);
+  bool ok();
+  // Returns scratch of at least `bytes`, zeroed when (re)allocated.
+  void* get_splitk_ws(int64_t bytes);
+  ~Context();
+};
+
+struct BoundTensor {
+  void* data = nullptr;
+  std::vector<int64_t> shape;
+};
+
+struct ExecContext {
+  uint32_t magic = kExecMagic;
+  Context* ctx = nullptr;
+  std::unordered_map<int64_t, BoundTensor> inputs;
+  std::unordered_map<int64_t, BoundTensor> outputs;
+  std::unordered_map<void*, int> refcount;  // buffers allocated during this execution
+  std::unordered_set<void*> input_ptrs;
+
+  void* alloc(size_t bytes);
+  void dealloc(void* p);
+  void signal_error(const std::string& msg) { ctx->signal_error(1, msg); }
+};
+
+// Either handle kind -> its Context (nullptr if the handle is neither).
+Context* context_of(void* handle);
+
+}  // namespace ral
+}  // namespace disc_b200

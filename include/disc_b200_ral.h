@@ -1,0 +1,220 @@
+/* C ABI of libdisc_b200_ral.so: a B200 (sm_100a) implementation of the
+ * quantized-inference custom calls of BladeDISC's RAL (runtime abstraction
+ * layer).  Plain C types only.  All device pointers refer to the CUDA device
+ * that is current on the calling thread; work is enqueued on the given
+ * stream and the calls do not synchronise unless they say so.
+ *
+ * Citations name files of the reference project (alibaba/BladeDISC).
+ */
+#ifndef DISC_B200_RAL_H_
+#define DISC_B200_RAL_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------
+ * 1. The RAL dispatcher.  A DISC-compiled executable receives
+ *    ctx_struct = { execution context, pointer to this function } and calls
+ *    every runtime service through it with a mangled name
+ *    "<api>___<device>___<arg types>___<ret type>" and type-erased arguments.
+ *    Replaces tao_compiler/mlir/ral/ral_api.h:59-67 (declared there without
+ *    these exact parameter names; the symbols and meaning are the same).
+ * ---------------------------------------------------------------------- */
+
+/* Entry symbol of a compiled executable (tao_compiler/mlir/ral/ral_api.cc:29). */
+extern const char* const kMlirLoweredEntry;
+
+typedef void* tao_ral_context_t;
+typedef int32_t tao_ral_status_t;
+
+/* `ctx` is an execution context made by disc_b200_exec_create.  `name` is a
+ * NUL-terminated mangled api name, `args[i]` points at the i-th flattened
+ * argument; a rank-N memref occupies 3 + 2N slots (base pointer, aligned
+ * pointer, offset, sizes, strides); the slot after the last argument points at
+ * storage for the returned value (tao_compiler/mlir/ral/ral_helper.h:160-236).
+ * Unknown names and kernel failures put the context into an error state that
+ * tao_ral_last_error reports; nothing aborts and nothing throws. */
+void tao_ral_call_impl(tao_ral_context_t ctx, void* name, void** args);
+
+/* 0 when healthy.  Accepts a context or an execution context handle.  The
+ * message pointer stays valid until the error is cleared. */
+tao_ral_status_t tao_ral_last_error(tao_ral_context_t ctx, const char** err_msg);
+void tao_ral_clear_error(tao_ral_context_t ctx);
+
+/* ------------------------------------------------------------------------
+ * 2. Contexts.  What torch_blade's RalContext builds with
+ *    MakeBaseCudaContext / MakeExecutionContext
+ *    (pytorch_blade/pytorch_blade/compiler/mlir/runtime/ral_context.cpp:243-321,
+ *    tao_compiler/mlir/ral/context/base/cuda/cuda_context_impl.h:50-58).
+ *    One context per (device, stream); one execution context per inference.
+ * ---------------------------------------------------------------------- */
+
+typedef void* (*disc_b200_alloc_fn)(void* user, size_t bytes);
+typedef void (*disc_b200_free_fn)(void* user, void* ptr);
+
+typedef struct disc_b200_context_options {
+  int32_t device;        /* CUDA device ordinal */
+  void* stream;          /* cudaStream_t all work of this context runs on */
+  disc_b200_alloc_fn gpu_alloc; /* device allocator; NULL = cudaMalloc / cudaFree */
+  disc_b200_free_fn gpu_free;
+  void* alloc_user;
+  void* nccl_comm;       /* ncclComm_t for ral_all_gather; NULL = collectives unavailable */
+  void* comm_stream;     /* cudaStream_t for asynchronous collectives; NULL = `stream` */
+} disc_b200_context_options;
+
+typedef struct disc_b200_context disc_b200_context;
+typedef struct disc_b200_exec disc_b200_exec;
+
+disc_b200_context* disc_b200_context_create(const disc_b200_context_options* opts);
+void disc_b200_context_destroy(disc_b200_context* ctx);
+
+disc_b200_exec* disc_b200_exec_create(disc_b200_context* ctx);
+/* Frees buffers of this execution that were neither deallocated nor handed
+ * out as outputs. */
+void disc_b200_exec_destroy(disc_b200_exec* exec);
+
+/* Input idx of the executable: a borrowed buffer and its shape
+ * (ExecutionContext::bindInput, tao_compiler/mlir/ral/ral_context.h:164-170). */
+int32_t disc_b200_exec_bind_input(disc_b200_exec* exec, int32_t idx, const void* data, int32_t rank,
+                                  const int64_t* sizes);
+/* Output idx after the executable ran.  *owned = 1 when the buffer was
+ * allocated by this execution and is now the caller's to free with
+ * disc_b200_exec_free_output (ExecutionContext::bindOutput). */
+int32_t disc_b200_exec_get_output(disc_b200_exec* exec, int32_t idx, void** data, int32_t* rank,
+                                  int64_t* sizes8, int32_t* owned);
+void disc_b200_exec_free_output(disc_b200_context* ctx, void* data);
+
+/* Registry inspection (the reference keeps its registry private:
+ * tao_compiler/mlir/ral/ral_helper.h:254-269). */
+int32_t disc_b200_registry_size(void);
+const char* disc_b200_registry_name(int32_t i);
+int32_t disc_b200_registry_has(const char* mangled_name);
+
+/* ------------------------------------------------------------------------
+ * 3. Kernels by direct call.  The custom calls above unpack their memrefs and
+ *    land here; a host that is not a DISC executable can call these itself.
+ *    Every function returns 0 on success or a non-zero code with a message
+ *    available from disc_b200_last_error_string (thread local).
+ * ---------------------------------------------------------------------- */
+
+enum { DISC_B200_OUT_I8 = 0, DISC_B200_OUT_F16 = 1, DISC_B200_OUT_F32 = 2, DISC_B200_OUT_I32 = 3 };
+enum { DISC_B200_ACT_NONE = 0, DISC_B200_ACT_GELU = 1, DISC_B200_ACT_SILU = 2 };
+enum { DISC_B200_BIAS_NONE = 0, DISC_B200_BIAS_F32 = 1, DISC_B200_BIAS_I8 = 2 };
+enum { DISC_B200_SCALE_NONE = 0, DISC_B200_SCALE_SCALAR = 1, DISC_B200_SCALE_PER_COL = 2,
+       DISC_B200_SCALE_PER_ROW = 3 };
+enum { DISC_B200_PATH_AUTO = 0, DISC_B200_PATH_TILED = 1, DISC_B200_PATH_SMALL_M = 2,
+       DISC_B200_PATH_SIMT = 3 };
+enum { DISC_B200_F32 = 0, DISC_B200_F16 = 1 };
+
+/* out[m, n] = epilogue(sum_k a[m, k] * w[n, k]); a int8 [M, K], w int8 [N, K],
+ * both row-major.  All scale / bias pointers are DEVICE pointers: nothing is
+ * copied to the host, unlike the reference which reads the three scales back
+ * on first use (tao_compiler/mlir/ral/context/quantized_gpu_kernel_impl.cc:356-386).
+ *
+ *   t  = float(acc) [* x_scale[m] if x_scale_kind == PER_ROW]
+ *   cs = x_scale(n) * w_scale(n)                 [x_scale left out if PER_ROW]
+ *   cs = cs / out_scale(n)                       if fold_out_scale
+ *   v  = fma(t, cs, bias[n]);  v = act(v)
+ *   v  = v / out_scale                           if div_out_scale
+ *   out = sat_s8(rne(v)) | f16(v) | f32(v) ; OUT_I32 stores acc itself.
+ *
+ * The reference's ral_pdll_qgemm (quantized_gpu_kernel_impl.cc:328-422) is
+ * { fold_out_scale = 1, act = NONE, out = I8, bias F32 or I8 }.
+ * splitk_ws: device scratch of at least disc_b200_qgemm_scratch_bytes(M, N, K)
+ * bytes, needed when M <= 128 takes the small-M path; only its first
+ * ceil(N / 128) int32 words must be zero before the first use and they are
+ * left zero; launches that share it must not overlap on the GPU. */
+typedef struct disc_b200_qgemm_args {
+  const int8_t* a;
+  const int8_t* w;
+  void* out;
+  int64_t M, N, K;
+  int64_t lda, ldw, ldo;
+  const float* x_scale;
+  const float* w_scale;
+  const float* out_scale;
+  const void* bias;
+  int32_t x_scale_kind, w_scale_kind, out_scale_kind, bias_kind;
+  int32_t fold_out_scale, div_out_scale;
+  int32_t act, out_dtype;
+  int32_t path, split_k;
+  void* splitk_ws;
+  int64_t splitk_ws_bytes;
+} disc_b200_qgemm_args;
+
+int32_t disc_b200_qgemm(const disc_b200_qgemm_args* args, void* stream);
+int64_t disc_b200_qgemm_scratch_bytes(int64_t M, int64_t N, int64_t K);
+/* Path (DISC_B200_PATH_*) the launch would take. */
+int32_t disc_b200_qgemm_path(const disc_b200_qgemm_args* args);
+
+/* q = clamp(rne(x / scale + zero_point), qmin, qmax): the arithmetic of
+ * QuantizeOpConverter with RoundHalfToEven
+ * (tao_compiler/mlir/disc/transforms/disc_lower_quantize_and_dequantize.cc:36-97).
+ * channels == 1: per-tensor; otherwise the tensor is viewed as
+ * [outer, channels, inner] and scale / zero_point have `channels` entries.
+ * zero_point may be NULL. */
+int32_t disc_b200_quantize(const void* x, int32_t in_type, int8_t* q, int64_t numel,
+                           const float* scale, const int32_t* zero_point, int64_t channels,
+                           int64_t inner, int32_t qmin, int32_t qmax, void* stream);
+
+/* y = float(q - zero_point) * scale: DequantizeOpConverter
+ * (disc_lower_quantize_and_dequantize.cc:99-139). */
+int32_t disc_b200_dequantize(const int8_t* q, void* y, int32_t out_type, int64_t numel,
+                             const float* scale, const int32_t* zero_point, int64_t channels,
+                             int64_t inner, void* stream);
+
+/* Per-row symmetric quantize, row_scale[r] = max(max|x[r, :]| / 127, FLT_EPSILON).
+ * No counterpart in the reference, whose quantize op rejects use_dynamic
+ * (disc_lower_quantize_and_dequantize.cc:41-43). */
+int32_t disc_b200_dynamic_quantize(const void* x, int32_t in_type, int8_t* q, float* row_scale,
+                                   int64_t rows, int64_t cols, void* stream);
+
+/* LayerNorm / RMSNorm over the last axis with optional fused residual add and
+ * optional int8 second output; stands in for the kStitch fusion DISC generates
+ * for aten.layer_norm (tao_compiler/mlir/disc/transforms/
+ * lhlo_legalize_roots_to_loops.cc:3091-3330).  Pointers may be NULL where the
+ * comment of the field in rowops.h says so: residual, beta, y, sum_out, q_out,
+ * q_scale, q_row_scale. */
+typedef struct disc_b200_norm_args {
+  const void* x;
+  const void* residual;
+  const void* gamma;
+  const void* beta;
+  void* y;
+  void* sum_out;
+  int8_t* q_out;
+  const float* q_scale;
+  float* q_row_scale;
+  int64_t rows, cols;
+  float eps;
+  int32_t type;
+  int32_t rms;
+} disc_b200_norm_args;
+int32_t disc_b200_norm(const disc_b200_norm_args* args, void* stream);
+
+/* softmax(x * scale + mask) over the last axis; lens / mask may be NULL
+ * (kStitch softmax; same reference files as above). */
+int32_t disc_b200_softmax(const void* x, void* y, int32_t type, int64_t rows, int64_t cols,
+                          int64_t rows_per_batch, const int32_t* lens, const void* mask,
+                          float scale, int32_t log_softmax, void* stream);
+
+/* ------------------------------------------------------------------------
+ * 4. Diagnostics.
+ * ---------------------------------------------------------------------- */
+
+/* Message of the last failing section-3 call on this thread ("" if none). */
+const char* disc_b200_last_error_string(void);
+/* Synchronises the device, returns and clears the status word kernels set when
+ * one of their bounded waits ran out (0 = none did). */
+int32_t disc_b200_kernel_status(void);
+const char* disc_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* DISC_B200_RAL_H_ */
