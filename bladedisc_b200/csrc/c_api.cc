@@ -1,12 +1,14 @@
 // Direct (non-dispatched) C entry points: plain pointers and sizes in, a
 // status code out.  The custom calls of ral/calls.cc land on the same launch
 // functions.
+#include <cstdio>
 #include <cstring>
 #include <string>
 
 #include "../../include/disc_b200_ral.h"
 #include "kernels/qgemm.h"
 #include "kernels/rowops.h"
+#include "ral/pdl_attr.h"
 
 namespace {
 
@@ -18,6 +20,54 @@ int32_t finish(cudaError_t st, const char* what, const char* detail) {
   }
   g_last_error = std::string(what) + ": " + (detail ? detail : cudaGetErrorString(st));
   return static_cast<int32_t>(st);
+}
+
+void render(const disc_b200::ral::Attr& a, std::string& o) {
+  using disc_b200::ral::Attr;
+  switch (a.kind) {
+    case Attr::kDict: {
+      o += "{";
+      bool first = true;
+      for (const auto& kv : a.dict) {
+        if (!first) o += ", ";
+        first = false;
+        o += kv.first + ": ";
+        render(*kv.second, o);
+      }
+      o += "}";
+      break;
+    }
+    case Attr::kStr: o += "\"" + a.str + "\""; break;
+    case Attr::kBool: o += a.b ? "true" : "false"; break;
+    case Attr::kInt: o += std::to_string(a.i); break;
+    case Attr::kFloat: {
+      char buf[64];
+      snprintf(buf, sizeof(buf), "%.17g", a.f);
+      o += buf;
+      break;
+    }
+    case Attr::kIntArray: {
+      o += "[";
+      for (size_t i = 0; i < a.ints.size(); ++i) o += (i ? ", " : "") + std::to_string(a.ints[i]);
+      o += "]";
+      break;
+    }
+    case Attr::kArray: {
+      o += "[";
+      for (size_t i = 0; i < a.array.size(); ++i) {
+        if (i) o += ", ";
+        render(*a.array[i], o);
+      }
+      o += "]";
+      break;
+    }
+    case Attr::kDense: {
+      o += "dense<" + a.elem_type + std::to_string(a.elem_bits) + "[";
+      for (size_t i = 0; i < a.shape.size(); ++i) o += (i ? "x" : "") + std::to_string(a.shape[i]);
+      o += "]:" + std::to_string(a.raw.size()) + "B>";
+      break;
+    }
+  }
 }
 
 disc_b200::QGemmParams to_params(const disc_b200_qgemm_args* a) {
@@ -172,5 +222,18 @@ const char* disc_b200_last_error_string(void) { return g_last_error.c_str(); }
 int32_t disc_b200_kernel_status(void) { return disc_b200::kernel_status_fetch_and_clear(); }
 
 const char* disc_b200_version(void) { return "disc-b200-ral 0.1 (sm_100a)"; }
+
+int32_t disc_b200_attrs_describe(const void* blob, char* out, int32_t capacity) {
+  if (!blob || !out || capacity <= 0) return -1;
+  const uint8_t* cur = static_cast<const uint8_t*>(blob);
+  auto a = disc_b200::ral::parse_attr(&cur);
+  if (!a) return -1;
+  std::string text;
+  render(*a, text);
+  const int32_t n = static_cast<int32_t>(text.size()) < capacity - 1 ? static_cast<int32_t>(text.size()) : capacity - 1;
+  std::memcpy(out, text.data(), n);
+  out[n] = 0;
+  return n;
+}
 
 }  // extern "C"

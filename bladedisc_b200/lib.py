@@ -1,0 +1,127 @@
+"""ctypes binding of libdisc_b200_ral.so (declared in include/disc_b200_ral.h).
+
+There is no fallback: if the shared library has not been built, importing the
+symbols raises.  Build it with ``python -m bladedisc_b200.build``.
+"""
+import ctypes
+import os
+from ctypes import (POINTER, Structure, c_char_p, c_float, c_int8, c_int32,
+                    c_int64, c_size_t, c_void_p)
+from pathlib import Path
+
+_LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libdisc_b200_ral.so"
+
+ALLOC_FN = ctypes.CFUNCTYPE(c_void_p, c_void_p, c_size_t)
+FREE_FN = ctypes.CFUNCTYPE(None, c_void_p, c_void_p)
+
+# enums of include/disc_b200_ral.h
+OUT_I8, OUT_F16, OUT_F32, OUT_I32 = 0, 1, 2, 3
+ACT_NONE, ACT_GELU, ACT_SILU = 0, 1, 2
+BIAS_NONE, BIAS_F32, BIAS_I8 = 0, 1, 2
+SCALE_NONE, SCALE_SCALAR, SCALE_PER_COL, SCALE_PER_ROW = 0, 1, 2, 3
+PATH_AUTO, PATH_TILED, PATH_SMALL_M, PATH_SIMT = 0, 1, 2, 3
+F32, F16 = 0, 1
+
+
+class ContextOptions(Structure):
+    _fields_ = [
+        ("device", c_int32),
+        ("stream", c_void_p),
+        ("gpu_alloc", ALLOC_FN),
+        ("gpu_free", FREE_FN),
+        ("alloc_user", c_void_p),
+        ("nccl_comm", c_void_p),
+        ("comm_stream", c_void_p),
+    ]
+
+
+class QGemmArgs(Structure):
+    _fields_ = [
+        ("a", c_void_p), ("w", c_void_p), ("out", c_void_p),
+        ("M", c_int64), ("N", c_int64), ("K", c_int64),
+        ("lda", c_int64), ("ldw", c_int64), ("ldo", c_int64),
+        ("x_scale", c_void_p), ("w_scale", c_void_p), ("out_scale", c_void_p),
+        ("bias", c_void_p),
+        ("x_scale_kind", c_int32), ("w_scale_kind", c_int32),
+        ("out_scale_kind", c_int32), ("bias_kind", c_int32),
+        ("fold_out_scale", c_int32), ("div_out_scale", c_int32),
+        ("act", c_int32), ("out_dtype", c_int32),
+        ("path", c_int32), ("split_k", c_int32),
+        ("splitk_ws", c_void_p), ("splitk_ws_bytes", c_int64),
+    ]
+
+
+class NormArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("residual", c_void_p), ("gamma", c_void_p), ("beta", c_void_p),
+        ("y", c_void_p), ("sum_out", c_void_p), ("q_out", c_void_p),
+        ("q_scale", c_void_p), ("q_row_scale", c_void_p),
+        ("rows", c_int64), ("cols", c_int64),
+        ("eps", c_float), ("type", c_int32), ("rms", c_int32),
+    ]
+
+
+# name -> (restype, argtypes): every function include/disc_b200_ral.h declares.
+SIGNATURES = {
+    "tao_ral_call_impl": (None, [c_void_p, c_void_p, POINTER(c_void_p)]),
+    "tao_ral_last_error": (c_int32, [c_void_p, POINTER(c_char_p)]),
+    "tao_ral_clear_error": (None, [c_void_p]),
+    "disc_b200_context_create": (c_void_p, [POINTER(ContextOptions)]),
+    "disc_b200_context_destroy": (None, [c_void_p]),
+    "disc_b200_exec_create": (c_void_p, [c_void_p]),
+    "disc_b200_exec_destroy": (None, [c_void_p]),
+    "disc_b200_exec_bind_input": (c_int32, [c_void_p, c_int32, c_void_p, c_int32, POINTER(c_int64)]),
+    "disc_b200_exec_get_output": (c_int32, [c_void_p, c_int32, POINTER(c_void_p), POINTER(c_int32),
+                                            POINTER(c_int64), POINTER(c_int32)]),
+    "disc_b200_exec_free_output": (None, [c_void_p, c_void_p]),
+    "disc_b200_registry_size": (c_int32, []),
+    "disc_b200_registry_name": (c_char_p, [c_int32]),
+    "disc_b200_registry_has": (c_int32, [c_char_p]),
+    "disc_b200_qgemm": (c_int32, [POINTER(QGemmArgs), c_void_p]),
+    "disc_b200_qgemm_scratch_bytes": (c_int64, [c_int64, c_int64, c_int64]),
+    "disc_b200_qgemm_path": (c_int32, [POINTER(QGemmArgs)]),
+    "disc_b200_quantize": (c_int32, [c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_void_p,
+                                     c_int64, c_int64, c_int32, c_int32, c_void_p]),
+    "disc_b200_dequantize": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_void_p, c_void_p,
+                                       c_int64, c_int64, c_void_p]),
+    "disc_b200_dynamic_quantize": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_int64, c_int64,
+                                             c_void_p]),
+    "disc_b200_norm": (c_int32, [POINTER(NormArgs), c_void_p]),
+    "disc_b200_softmax": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int64, c_void_p,
+                                    c_void_p, c_float, c_int32, c_void_p]),
+    "disc_b200_last_error_string": (c_char_p, []),
+    "disc_b200_kernel_status": (c_int32, []),
+    "disc_b200_version": (c_char_p, []),
+    "disc_b200_attrs_describe": (c_int32, [c_void_p, c_char_p, c_int32]),
+}
+
+_lib = None
+
+
+def library_path() -> Path:
+    return _LIB_PATH
+
+
+def load() -> ctypes.CDLL:
+    """Loads the shared library once and types every exported function."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB_PATH.exists():
+        raise RuntimeError(
+            f"{_LIB_PATH} is missing: the CUDA extension has not been built "
+            "(run `python -m bladedisc_b200.build`); there is no CPU fallback")
+    lib = ctypes.CDLL(os.fspath(_LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(code: int) -> None:
+    """Raises with the library's message when a section-3 call failed."""
+    if code != 0:
+        msg = load().disc_b200_last_error_string().decode()
+        raise RuntimeError(f"disc_b200 call failed ({code}): {msg}")

@@ -1,0 +1,295 @@
+"""Operators of the quantized path on torch CUDA tensors.
+
+Every function launches hand-written sm_100a kernels through the C ABI of
+libdisc_b200_ral.so on torch's current stream.  torch is used for device
+memory and streams only.  Nothing here computes on the CPU and nothing falls
+back to torch operators.
+"""
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import lib as _lib
+
+_ACT = {None: _lib.ACT_NONE, "none": _lib.ACT_NONE, "gelu": _lib.ACT_GELU, "silu": _lib.ACT_SILU}
+_OUT = {torch.int8: _lib.OUT_I8, torch.float16: _lib.OUT_F16, torch.float32: _lib.OUT_F32,
+        torch.int32: _lib.OUT_I32}
+_PATH = {None: _lib.PATH_AUTO, "auto": _lib.PATH_AUTO, "tiled": _lib.PATH_TILED,
+         "small_m": _lib.PATH_SMALL_M, "simt": _lib.PATH_SIMT}
+_scratch = {}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _cuda(t: torch.Tensor, name: str, dtype=None) -> torch.Tensor:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor: the quantized path has no CPU implementation")
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    return t.contiguous()
+
+
+def _etype(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _lib.F32
+    if t.dtype == torch.float16:
+        return _lib.F16
+    raise TypeError(f"float32 or float16 expected, got {t.dtype}")
+
+
+def qgemm_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Zero-initialised scratch of the small-M path, one per (device, stream)."""
+    key = (device.index, _stream())
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, 8 << 20), dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def _scale_kind(s: Optional[torch.Tensor], rows: int, cols: int, what: str, x_per_col: bool) -> int:
+    if s is None:
+        return _lib.SCALE_NONE
+    if s.numel() == 1:
+        return _lib.SCALE_SCALAR
+    if what == "x" and not x_per_col:
+        if s.numel() != rows:
+            raise ValueError(f"x_scale has {s.numel()} entries; expected 1 or one per row ({rows})")
+        return _lib.SCALE_PER_ROW
+    if s.numel() != cols:
+        raise ValueError(f"{what}_scale has {s.numel()} entries; expected 1 or one per channel ({cols})")
+    return _lib.SCALE_PER_COL
+
+
+def qgemm(a: torch.Tensor, w: torch.Tensor, *, x_scale: Optional[torch.Tensor] = None,
+          w_scale: Optional[torch.Tensor] = None, out_scale: Optional[torch.Tensor] = None,
+          bias: Optional[torch.Tensor] = None, act: Optional[str] = None,
+          out_dtype: torch.dtype = torch.int8, fold_out_scale: bool = False,
+          x_scale_per_col: bool = False, path: Optional[str] = None, split_k: int = 0,
+          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = epilogue(a[..., K] @ w[N, K]^T) with int8 operands and int32 accumulation.
+
+    ``fold_out_scale=True`` is the reference custom call ``ral_pdll_qgemm``:
+    ``sat_s8(rne(acc * (x_scale * w_scale / out_scale) + bias))``.  Otherwise
+    ``v = act(acc * x_scale * w_scale + bias)`` and int8 output divides ``v`` by
+    ``out_scale`` before rounding.  Scales and bias are device tensors.
+    """
+    a = _cuda(a, "a", torch.int8)
+    w = _cuda(w, "w", torch.int8)
+    if w.dim() != 2 or a.shape[-1] != w.shape[1]:
+        raise ValueError(f"shape mismatch: a {tuple(a.shape)} w {tuple(w.shape)}")
+    K = w.shape[1]
+    N = w.shape[0]
+    M = a.numel() // K if K else 0
+    out_shape = tuple(a.shape[:-1]) + (N,)
+    if out is None:
+        out = torch.empty(out_shape, dtype=out_dtype, device=a.device)
+    elif out.dtype != out_dtype or not out.is_contiguous() or out.numel() != M * N:
+        raise ValueError("out must be a contiguous tensor of the result's dtype and size")
+    if M == 0 or N == 0:
+        return out
+    args = _lib.QGemmArgs()
+    args.a, args.w, args.out = a.data_ptr(), w.data_ptr(), out.data_ptr()
+    args.M, args.N, args.K = M, N, K
+    args.lda, args.ldw, args.ldo = K, K, N
+    keep = []
+    for name, t in (("x", x_scale), ("w", w_scale), ("out", out_scale)):
+        if t is not None:
+            t = _cuda(t, f"{name}_scale", torch.float32)
+            keep.append(t)
+        kind = _scale_kind(t, M, N, name, x_scale_per_col)
+        setattr(args, f"{name}_scale", _p(t))
+        setattr(args, f"{name}_scale_kind", kind)
+    if bias is not None:
+        bias = _cuda(bias, "bias")
+        if bias.dtype == torch.float32:
+            args.bias_kind = _lib.BIAS_F32
+        elif bias.dtype == torch.int8:
+            args.bias_kind = _lib.BIAS_I8
+        else:
+            raise TypeError("bias must be float32 or int8")
+        if bias.numel() != N:
+            raise ValueError("bias must have one entry per output channel")
+        args.bias = bias.data_ptr()
+    args.fold_out_scale = 1 if fold_out_scale else 0
+    args.div_out_scale = 1 if (out_dtype == torch.int8 and out_scale is not None and not fold_out_scale) else 0
+    args.act = _ACT[act]
+    args.out_dtype = _OUT[out_dtype]
+    args.path = _PATH[path]
+    args.split_k = split_k
+    L = _lib.load()
+    if M <= 128:
+        need = L.disc_b200_qgemm_scratch_bytes(M, N, K)
+        ws = qgemm_scratch(a.device, need)
+        args.splitk_ws = ws.data_ptr()
+        args.splitk_ws_bytes = ws.numel()
+    _lib.check(L.disc_b200_qgemm(ctypes.byref(args), _stream()))
+    return out
+
+
+def qgemm_path(M: int, N: int, K: int) -> str:
+    """Which kernel path an aligned (M, N, K) problem takes."""
+    args = _lib.QGemmArgs()
+    args.a, args.w, args.out = 16, 16, 16
+    args.M, args.N, args.K, args.lda, args.ldw, args.ldo = M, N, K, K, K, N
+    code = _lib.load().disc_b200_qgemm_path(ctypes.byref(args))
+    return {1: "tiled", 2: "small_m", 3: "simt"}[code]
+
+
+def quantize(x: torch.Tensor, scale: torch.Tensor, zero_point: Optional[torch.Tensor] = None,
+             axis: Optional[int] = None, qmin: int = -128, qmax: int = 127) -> torch.Tensor:
+    """q = clamp(rne(x / scale + zero_point), qmin, qmax) as int8 (static scales)."""
+    x = _cuda(x, "x")
+    scale = _cuda(scale, "scale", torch.float32)
+    if zero_point is not None:
+        zero_point = _cuda(zero_point, "zero_point", torch.int32)
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    channels, inner = 1, 1
+    if axis is not None and scale.numel() > 1:
+        axis = axis % x.dim()
+        channels = x.shape[axis]
+        inner = 1
+        for d in x.shape[axis + 1:]:
+            inner *= d
+        if scale.numel() != channels:
+            raise ValueError("scale must have one entry per slice along axis")
+    _lib.check(_lib.load().disc_b200_quantize(x.data_ptr(), _etype(x), q.data_ptr(), x.numel(),
+                                              scale.data_ptr(), _p(zero_point), channels, inner,
+                                              qmin, qmax, _stream()))
+    return q
+
+
+def dequantize(q: torch.Tensor, scale: torch.Tensor, zero_point: Optional[torch.Tensor] = None,
+               axis: Optional[int] = None, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """y = (q - zero_point) * scale."""
+    q = _cuda(q, "q", torch.int8)
+    scale = _cuda(scale, "scale", torch.float32)
+    if zero_point is not None:
+        zero_point = _cuda(zero_point, "zero_point", torch.int32)
+    y = torch.empty(q.shape, dtype=dtype, device=q.device)
+    channels, inner = 1, 1
+    if axis is not None and scale.numel() > 1:
+        axis = axis % q.dim()
+        channels = q.shape[axis]
+        for d in q.shape[axis + 1:]:
+            inner *= d
+    _lib.check(_lib.load().disc_b200_dequantize(q.data_ptr(), y.data_ptr(), _etype(y), q.numel(),
+                                                scale.data_ptr(), _p(zero_point), channels, inner,
+                                                _stream()))
+    return y
+
+
+def dynamic_quantize(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row symmetric int8: returns (q, row_scale) with row_scale = max|row| / 127."""
+    x = _cuda(x, "x")
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    s = torch.empty(rows, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().disc_b200_dynamic_quantize(x.data_ptr(), _etype(x), q.data_ptr(),
+                                                      s.data_ptr(), rows, cols, _stream()))
+    return q, s
+
+
+def _norm(x, residual, gamma, beta, eps, rms, q_scale, want_y, want_sum, want_q, dynamic_q):
+    x = _cuda(x, "x")
+    gamma = _cuda(gamma, "gamma", x.dtype)
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    a = _lib.NormArgs()
+    a.x = x.data_ptr()
+    a.gamma = gamma.data_ptr()
+    keep = [x, gamma]
+    if residual is not None:
+        residual = _cuda(residual, "residual", x.dtype)
+        if residual.shape != x.shape:
+            raise ValueError("residual must have the shape of x")
+        a.residual = residual.data_ptr()
+        keep.append(residual)
+    if beta is not None:
+        beta = _cuda(beta, "beta", x.dtype)
+        a.beta = beta.data_ptr()
+        keep.append(beta)
+    y = s = q = rs = None
+    if want_y:
+        y = torch.empty_like(x)
+        a.y = y.data_ptr()
+    if want_sum:
+        s = torch.empty_like(x)
+        a.sum_out = s.data_ptr()
+    if want_q:
+        q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+        a.q_out = q.data_ptr()
+        if dynamic_q:
+            rs = torch.empty(rows, dtype=torch.float32, device=x.device)
+            a.q_row_scale = rs.data_ptr()
+        else:
+            q_scale = _cuda(q_scale, "q_scale", torch.float32)
+            a.q_scale = q_scale.data_ptr()
+            keep.append(q_scale)
+    a.rows, a.cols, a.eps, a.type, a.rms = rows, cols, eps, _etype(x), 1 if rms else 0
+    _lib.check(_lib.load().disc_b200_norm(ctypes.byref(a), _stream()))
+    return y, s, q, rs
+
+
+def layernorm(x, gamma, beta, eps: float = 1e-5, residual=None) -> torch.Tensor:
+    """LayerNorm(x [+ residual]) over the last axis."""
+    return _norm(x, residual, gamma, beta, eps, False, None, True, False, False, False)[0]
+
+
+def layernorm_quant(x, gamma, beta, q_scale, eps: float = 1e-5, residual=None):
+    """LayerNorm(x [+ residual]) and its int8 copy at a static scale: (y, q)."""
+    y, _, q, _ = _norm(x, residual, gamma, beta, eps, False, q_scale, True, False, True, False)
+    return y, q
+
+
+def rmsnorm(x, gamma, eps: float = 1e-6, residual=None, return_sum: bool = False):
+    """RMSNorm(x [+ residual]); with return_sum also x + residual."""
+    y, s, _, _ = _norm(x, residual, gamma, None, eps, True, None, True, return_sum, False, False)
+    return (y, s) if return_sum else y
+
+
+def rmsnorm_dynamic_quant(x, gamma, eps: float = 1e-6, residual=None):
+    """RMSNorm(x [+ residual]) quantized per row: (q, row_scale, x + residual or None)."""
+    _, s, q, rs = _norm(x, residual, gamma, None, eps, True, None, False, residual is not None, True, True)
+    return q, rs, s
+
+
+def softmax(x: torch.Tensor, scale: float = 1.0, lens: Optional[torch.Tensor] = None,
+            mask: Optional[torch.Tensor] = None, log: bool = False) -> torch.Tensor:
+    """softmax(x * scale + mask) over the last axis.
+
+    ``lens`` (int32, one per index of the leading axis) zeroes the columns at
+    and beyond the length; ``mask`` ([leading, cols], dtype of x) is added.
+    """
+    x = _cuda(x, "x")
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    y = torch.empty_like(x)
+    rpb = rows
+    if lens is not None:
+        lens = _cuda(lens, "lens", torch.int32)
+        if lens.numel() != x.shape[0]:
+            raise ValueError("one length per index of the leading axis expected")
+        rpb = rows // x.shape[0]
+    if mask is not None:
+        mask = _cuda(mask, "mask", x.dtype)
+        if mask.numel() != x.shape[0] * cols:
+            raise ValueError("mask must be [leading axis, cols]")
+        rpb = rows // x.shape[0]
+    _lib.check(_lib.load().disc_b200_softmax(x.data_ptr(), y.data_ptr(), _etype(x), rows, cols, rpb,
+                                             _p(lens), _p(mask), float(scale), 1 if log else 0,
+                                             _stream()))
+    return y
+
+
+def kernel_status() -> int:
+    """0 unless a kernel's bounded wait ran out since the last query (synchronises)."""
+    return _lib.load().disc_b200_kernel_status()

@@ -212,6 +212,11 @@ const char* disc_b200_last_error_string(void);
  * one of their bounded waits ran out (0 = none did). */
 int32_t disc_b200_kernel_status(void);
 const char* disc_b200_version(void);
+/* Parses a serialized custom_attrs blob (wire format of tao_compiler/mlir/ral/
+ * context/pdll_util.cc:20-170) and writes a canonical text rendering such as
+ * {a: true, b: 127, c: "s", d: [1, 2], e: dense<int64[2]>} into `out`.
+ * Returns the length written, or -1 if the blob does not parse. */
+int32_t disc_b200_attrs_describe(const void* blob, char* out, int32_t capacity);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,228 @@
+"""TEST INFRASTRUCTURE: ctypes wrapper of oracle/qpath_oracle.c (numpy in, numpy out).
+
+Each wrapper names the C function it calls; the C source cites the reference
+file:line that the function restates.
+"""
+import ctypes
+import subprocess
+from ctypes import POINTER, c_float, c_int, c_int8, c_int32, c_int64, c_void_p
+from pathlib import Path
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+_SO = _HERE / "_build" / "libqpath_oracle.so"
+_lib = None
+
+SCALE_NONE, SCALE_SCALAR, SCALE_PER_COL, SCALE_PER_ROW = 0, 1, 2, 3
+BIAS_NONE, BIAS_F32, BIAS_I8 = 0, 1, 2
+ACT = {None: 0, "none": 0, "gelu": 1, "silu": 2}
+
+
+def build() -> Path:
+    """Compiles the C restatement (gcc) if it is missing or stale."""
+    src = _HERE / "qpath_oracle.c"
+    if not _SO.exists() or _SO.stat().st_mtime < src.stat().st_mtime:
+        subprocess.run(["make", "-C", str(_HERE)], check=True, stdout=subprocess.DEVNULL)
+    return _SO
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(str(build()))
+    return _lib
+
+
+def _f32(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i32(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(c_void_p)
+
+
+def _axis_view(shape, axis):
+    if axis is None:
+        return 1, 1
+    axis = axis % len(shape)
+    inner = int(np.prod(shape[axis + 1:], dtype=np.int64))
+    return int(shape[axis]), inner
+
+
+def quantize(x, scale, zero_point=None, axis=None, qmin=-128, qmax=127):
+    """oracle_quantize_f32"""
+    x = _f32(x)
+    scale = _f32(np.atleast_1d(scale))
+    zp = _i32(np.atleast_1d(zero_point)) if zero_point is not None else None
+    ch, inner = _axis_view(x.shape, axis if scale.size > 1 else None)
+    q = np.empty(x.shape, dtype=np.int8)
+    lib().oracle_quantize_f32(_ptr(x), c_int64(x.size), _ptr(scale), _ptr(zp), c_int64(ch), c_int64(inner),
+                              c_int32(qmin), c_int32(qmax), _ptr(q))
+    return q
+
+
+def dequantize(q, scale, zero_point=None, axis=None):
+    """oracle_dequantize_f32"""
+    q = np.ascontiguousarray(q, dtype=np.int8)
+    scale = _f32(np.atleast_1d(scale))
+    zp = _i32(np.atleast_1d(zero_point)) if zero_point is not None else None
+    ch, inner = _axis_view(q.shape, axis if scale.size > 1 else None)
+    y = np.empty(q.shape, dtype=np.float32)
+    lib().oracle_dequantize_f32(_ptr(q), c_int64(q.size), _ptr(scale), _ptr(zp), c_int64(ch), c_int64(inner),
+                                _ptr(y))
+    return y
+
+
+def quantize_weight(w, scale, zero_point=None, per_channel=True, qmin=-128, qmax=127):
+    """oracle_quantize_weight_f64"""
+    w = _f32(w)
+    scale = _f32(np.atleast_1d(scale))
+    zp = _i32(np.atleast_1d(zero_point)) if zero_point is not None else None
+    q = np.empty(w.shape, dtype=np.int8)
+    lib().oracle_quantize_weight_f64(_ptr(w), c_int64(w.shape[0]), c_int64(w.shape[1]), _ptr(scale), _ptr(zp),
+                                     c_int(1 if per_channel else 0), c_int32(qmin), c_int32(qmax), _ptr(q))
+    return q
+
+
+def fake_quant(x, scale, zero_point=None, axis=None, qmin=-128, qmax=127):
+    """oracle_fake_quant_f32"""
+    x = _f32(x)
+    scale = _f32(np.atleast_1d(scale))
+    zp = _i32(np.atleast_1d(zero_point)) if zero_point is not None else None
+    ch, inner = _axis_view(x.shape, axis if scale.size > 1 else None)
+    y = np.empty(x.shape, dtype=np.float32)
+    lib().oracle_fake_quant_f32(_ptr(x), c_int64(x.size), _ptr(scale), _ptr(zp), c_int64(ch), c_int64(inner),
+                                c_int32(qmin), c_int32(qmax), _ptr(y))
+    return y
+
+
+def qgemm_acc(a, w):
+    """oracle_qgemm_acc: int32 a[M,K] . w[N,K]^T"""
+    a = np.ascontiguousarray(a, dtype=np.int8)
+    w = np.ascontiguousarray(w, dtype=np.int8)
+    K = w.shape[1]
+    a2 = a.reshape(-1, K)
+    acc = np.empty((a2.shape[0], w.shape[0]), dtype=np.int32)
+    lib().oracle_qgemm_acc(_ptr(a2), _ptr(w), c_int64(a2.shape[0]), c_int64(w.shape[0]), c_int64(K), _ptr(acc))
+    return acc.reshape(a.shape[:-1] + (w.shape[0],))
+
+
+def _kind(s, rows, cols, is_x, x_per_col=False):
+    if s is None:
+        return SCALE_NONE
+    if s.size == 1:
+        return SCALE_SCALAR
+    if is_x and not x_per_col:
+        assert s.size == rows
+        return SCALE_PER_ROW
+    assert s.size == cols
+    return SCALE_PER_COL
+
+
+def qgemm_epilogue(acc, x_scale=None, w_scale=None, out_scale=None, bias=None, fold_out=False,
+                   div_out=False, act=None, x_per_col=False):
+    """oracle_qgemm_epilogue: returns (float32 values, int8 values)."""
+    acc = np.ascontiguousarray(acc, dtype=np.int32)
+    N = acc.shape[-1]
+    acc2 = acc.reshape(-1, N)
+    M = acc2.shape[0]
+    xs = _f32(np.atleast_1d(x_scale)) if x_scale is not None else None
+    ws = _f32(np.atleast_1d(w_scale)) if w_scale is not None else None
+    os_ = _f32(np.atleast_1d(out_scale)) if out_scale is not None else None
+    bias_kind = BIAS_NONE
+    b = None
+    if bias is not None:
+        b = np.ascontiguousarray(bias)
+        if b.dtype == np.int8:
+            bias_kind = BIAS_I8
+        else:
+            b = _f32(b)
+            bias_kind = BIAS_F32
+    of = np.empty((M, N), dtype=np.float32)
+    oi = np.empty((M, N), dtype=np.int8)
+    lib().oracle_qgemm_epilogue(_ptr(acc2), c_int64(M), c_int64(N), _ptr(xs), c_int(_kind(xs, M, N, True, x_per_col)),
+                                _ptr(ws), c_int(_kind(ws, M, N, False)), _ptr(os_),
+                                c_int(_kind(os_, M, N, False)), _ptr(b), c_int(bias_kind),
+                                c_int(1 if fold_out else 0), c_int(1 if div_out else 0), c_int(ACT[act]),
+                                _ptr(of), _ptr(oi))
+    return of.reshape(acc.shape), oi.reshape(acc.shape)
+
+
+def qgemm_x86(acc, s_x, s_w, s_out, bias=None):
+    """oracle_qgemm_x86"""
+    acc = np.ascontiguousarray(acc, dtype=np.int32)
+    N = acc.shape[-1]
+    acc2 = acc.reshape(-1, N)
+    ws = _f32(np.atleast_1d(s_w))
+    b = _f32(bias) if bias is not None else None
+    out = np.empty(acc2.shape, dtype=np.int8)
+    lib().oracle_qgemm_x86(_ptr(acc2), c_int64(acc2.shape[0]), c_int64(N), c_float(s_x), _ptr(ws),
+                           c_int(1 if ws.size > 1 else 0), c_float(s_out), _ptr(b), _ptr(out))
+    return out.reshape(acc.shape)
+
+
+def qgemm_ral_i8(a, w, s_x, s_w, s_out, bias=None):
+    """oracle_qgemm_ral_i8 (product + ral_pdll_qgemm epilogue in one, OpenMP when built with it)."""
+    a = np.ascontiguousarray(a, dtype=np.int8)
+    w = np.ascontiguousarray(w, dtype=np.int8)
+    K = w.shape[1]
+    a2 = a.reshape(-1, K)
+    ws = _f32(np.atleast_1d(s_w))
+    b = _f32(bias) if bias is not None else None
+    out = np.empty((a2.shape[0], w.shape[0]), dtype=np.int8)
+    lib().oracle_qgemm_ral_i8(_ptr(a2), _ptr(w), c_int64(a2.shape[0]), c_int64(w.shape[0]), c_int64(K),
+                              c_float(s_x), _ptr(ws), c_int(1 if ws.size > 1 else 0), c_float(s_out),
+                              _ptr(b), _ptr(out))
+    return out.reshape(a.shape[:-1] + (w.shape[0],))
+
+
+def dynamic_quantize(x):
+    """oracle_dynamic_quantize_f32: returns (q, row_scale)."""
+    x = _f32(x)
+    cols = x.shape[-1]
+    x2 = x.reshape(-1, cols)
+    q = np.empty(x2.shape, dtype=np.int8)
+    s = np.empty(x2.shape[0], dtype=np.float32)
+    lib().oracle_dynamic_quantize_f32(_ptr(x2), c_int64(x2.shape[0]), c_int64(cols), _ptr(q), _ptr(s))
+    return q.reshape(x.shape), s
+
+
+def norm(x, gamma, beta=None, residual=None, eps=1e-5, rms=False):
+    """oracle_norm_f32: returns (y, x + residual)."""
+    x = _f32(x)
+    cols = x.shape[-1]
+    x2 = x.reshape(-1, cols)
+    r = _f32(residual).reshape(-1, cols) if residual is not None else None
+    g = _f32(gamma)
+    b = _f32(beta) if beta is not None else None
+    y = np.empty(x2.shape, dtype=np.float32)
+    s = np.empty(x2.shape, dtype=np.float32)
+    lib().oracle_norm_f32(_ptr(x2), _ptr(r), _ptr(g), _ptr(b), c_int64(x2.shape[0]), c_int64(cols), c_float(eps),
+                          c_int(1 if rms else 0), _ptr(y), _ptr(s))
+    return y.reshape(x.shape), s.reshape(x.shape)
+
+
+def softmax(x, scale=1.0, lens=None, mask=None, log=False):
+    """oracle_softmax_f32: lens / mask are per index of the leading axis."""
+    x = _f32(x)
+    cols = x.shape[-1]
+    x2 = x.reshape(-1, cols)
+    rows = x2.shape[0]
+    rpb = rows
+    ln = None
+    mk = None
+    if lens is not None:
+        ln = _i32(lens)
+        rpb = rows // x.shape[0]
+    if mask is not None:
+        mk = _f32(mask).reshape(-1, cols)
+        rpb = rows // x.shape[0]
+    y = np.empty(x2.shape, dtype=np.float32)
+    lib().oracle_softmax_f32(_ptr(x2), c_int64(rows), c_int64(cols), c_int64(rpb), _ptr(ln), _ptr(mk),
+                             c_float(scale), c_int(1 if log else 0), _ptr(y))
+    return y.reshape(x.shape)

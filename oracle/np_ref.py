@@ -1,0 +1,78 @@
+"""TEST INFRASTRUCTURE: numpy statement of the same formulas as qpath_oracle.c,
+written independently so that tests can cross-check the C restatement.
+All float arithmetic is float32 unless a formula says double."""
+import math
+
+import numpy as np
+
+f32 = np.float32
+
+
+def quantize(x, scale, zero_point=0, qmin=-128, qmax=127):
+    """clamp(rne(x / scale + zp)), per-tensor or broadcastable scale
+    (disc_lower_quantize_and_dequantize.cc:77-93 of the reference)."""
+    x = np.asarray(x, dtype=f32)
+    t = (x / np.asarray(scale, dtype=f32)).astype(f32) + np.asarray(zero_point, dtype=f32)
+    t = np.rint(t.astype(f32))
+    return np.clip(t, qmin, qmax).astype(np.int8)
+
+
+def dequantize(q, scale, zero_point=0):
+    """(q - zp) * scale (disc_lower_quantize_and_dequantize.cc:131-136)."""
+    return ((q.astype(np.int32) - np.asarray(zero_point, dtype=np.int32)).astype(f32)
+            * np.asarray(scale, dtype=f32)).astype(f32)
+
+
+def fake_quant(x, scale, zero_point=0, qmin=-128, qmax=127):
+    """torch.fake_quantize_*_affine: multiply by the reciprocal, nearbyint, clamp, scale back."""
+    x = np.asarray(x, dtype=f32)
+    s = np.asarray(scale, dtype=f32)
+    inv = (f32(1.0) / s).astype(f32)
+    t = np.rint((x * inv).astype(f32)) + np.asarray(zero_point, dtype=f32)
+    t = np.clip(t, qmin, qmax)
+    return ((t - np.asarray(zero_point, dtype=f32)).astype(f32) * s).astype(f32)
+
+
+def qgemm_acc(a, w):
+    """int32 a[M,K] . w[N,K]^T (exact in int64, then checked to fit int32)."""
+    acc = a.astype(np.int64) @ w.astype(np.int64).T
+    assert np.abs(acc).max() < 2 ** 31
+    return acc.astype(np.int32)
+
+
+def ral_epilogue(acc, s_x, s_w, s_out, bias=None):
+    """sat_s8(rne(fma(acc, (s_x * s_w) / s_out, bias))): quantized_gpu_kernel_impl.cc:382,418-420.
+    The fused multiply-add is done in double and rounded once, which equals fmaf
+    for these magnitudes (|acc| < 2^31, one rounding)."""
+    cs = ((np.asarray(s_x, dtype=f32) * np.asarray(s_w, dtype=f32)).astype(f32)
+          / np.asarray(s_out, dtype=f32)).astype(f32)
+    b = np.zeros(acc.shape[-1], dtype=f32) if bias is None else np.asarray(bias).astype(f32)
+    v = (acc.astype(np.float64) * cs.astype(np.float64) + b.astype(np.float64)).astype(f32)
+    return np.clip(np.rint(v), -128, 127).astype(np.int8)
+
+
+def gelu(v):
+    v = np.asarray(v, dtype=f32)
+    erf = np.vectorize(math.erf)
+    return (f32(0.5) * v * (f32(1.0) + erf((v * f32(0.70710678118654752440)).astype(np.float64)).astype(f32))).astype(f32)
+
+
+def dynamic_quantize(x):
+    x = np.asarray(x, dtype=f32)
+    m = np.abs(x).max(axis=-1, keepdims=True)
+    s = np.maximum((m / f32(127.0)).astype(f32), np.finfo(f32).eps).astype(f32)
+    q = np.clip(np.rint((x / s).astype(f32)), -128, 127).astype(np.int8)
+    return q, s.reshape(-1)
+
+
+def layernorm(x, gamma, beta, eps=1e-5):
+    x = np.asarray(x, dtype=np.float64)
+    mean = x.mean(axis=-1, keepdims=True)
+    var = ((x - mean) ** 2).mean(axis=-1, keepdims=True)
+    return ((x - mean) / np.sqrt(var + eps) * gamma + beta).astype(f32)
+
+
+def softmax(x, scale=1.0):
+    x = (np.asarray(x, dtype=f32) * f32(scale)).astype(np.float64)
+    e = np.exp(x - x.max(axis=-1, keepdims=True))
+    return (e / e.sum(axis=-1, keepdims=True)).astype(f32)

@@ -1,0 +1,315 @@
+/* TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+ *
+ * CPU restatement of the arithmetic of BladeDISC's quantized-inference path,
+ * used only as the checker in tests/, in __graft_entry__.smoke() and as the
+ * "port" CPU baseline of bench.py.  Nothing under bladedisc_b200/ may call it.
+ *
+ * Parity pins: checked in tests/test_oracle.py against the reference's own
+ * known-answer vectors (12.0 and 128.0 cases of its qgemm feature tests) and
+ * against fixtures under tests/golden/ generated here by torch's
+ * fake_quantize / layer_norm / softmax and by the reference's torch_quant
+ * observers (script: tests/golden/make_golden.py).
+ *
+ * Every function cites the reference file:line it restates (paths inside
+ * alibaba/BladeDISC).  Build: make -C oracle  (gcc -O2 -ffp-contract=off, so
+ * that a*b+c stays two roundings unless fmaf is written out).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define ORACLE_API __attribute__((visibility("default")))
+
+static inline float clampf(float v, float lo, float hi) { return v < lo ? lo : (v > hi ? hi : v); }
+
+/* q = convert(clamp(round_half_even(x / scale + zero_point), qmin, qmax)).
+ * tao_compiler/mlir/disc/transforms/disc_lower_quantize_and_dequantize.cc:77-93
+ * (divide, add, round per round_mode, clamp, convert); the torch front end
+ * selects RoundHalfToEven (pytorch_blade/pytorch_blade/torch-mlir/lib/Conversion/
+ * TorchToMhlo/DiscConvertTorchToDiscMhlo.cpp:115-117).
+ * The tensor is viewed as [outer, channels, inner]; channels == 1 is per-tensor. */
+ORACLE_API void oracle_quantize_f32(const float* x, int64_t numel, const float* scale,
+                                    const int32_t* zero_point, int64_t channels, int64_t inner,
+                                    int32_t qmin, int32_t qmax, int8_t* q) {
+  if (channels < 1) channels = 1;
+  if (inner < 1) inner = 1;
+  for (int64_t i = 0; i < numel; ++i) {
+    const int64_t c = channels == 1 ? 0 : (i / inner) % channels;
+    const float zp = zero_point ? (float)zero_point[c] : 0.f;
+    float t = x[i] / scale[c];
+    t = t + zp;
+    t = rintf(t); /* default rounding mode: to nearest, ties to even */
+    t = clampf(t, (float)qmin, (float)qmax);
+    q[i] = (int8_t)(int32_t)t;
+  }
+}
+
+/* y = float(q - zero_point) * scale.
+ * disc_lower_quantize_and_dequantize.cc:131-136. */
+ORACLE_API void oracle_dequantize_f32(const int8_t* q, int64_t numel, const float* scale,
+                                      const int32_t* zero_point, int64_t channels, int64_t inner,
+                                      float* y) {
+  if (channels < 1) channels = 1;
+  if (inner < 1) inner = 1;
+  for (int64_t i = 0; i < numel; ++i) {
+    const int64_t c = channels == 1 ? 0 : (i / inner) % channels;
+    const int32_t zp = zero_point ? zero_point[c] : 0;
+    y[i] = (float)((int32_t)q[i] - zp) * scale[c];
+  }
+}
+
+/* Offline constant (weight) quantisation, done by the compiler in double:
+ * q = clamp(round(double(w) / double(s[c]) + zp[c]), qmin, qmax), half-to-even.
+ * tao_compiler/mlir/disc/IR/hlo_disc_ops.cc:149-340 (QuantizeOp::fold). */
+ORACLE_API void oracle_quantize_weight_f64(const float* w, int64_t rows, int64_t cols,
+                                           const float* scale, const int32_t* zero_point,
+                                           int per_channel, int32_t qmin, int32_t qmax, int8_t* q) {
+  for (int64_t r = 0; r < rows; ++r) {
+    const int64_t c = per_channel ? r : 0;
+    const double s = (double)scale[c];
+    const double zp = zero_point ? (double)zero_point[c] : 0.0;
+    for (int64_t j = 0; j < cols; ++j) {
+      double t = rint((double)w[r * cols + j] / s + zp);
+      if (t < (double)qmin) t = (double)qmin;
+      if (t > (double)qmax) t = (double)qmax;
+      q[r * cols + j] = (int8_t)(int32_t)t;
+    }
+  }
+}
+
+/* The golden of the reference's own e2e tests: torch.fake_quantize_per_tensor_affine
+ * / per_channel_affine (pytorch_blade/tests/disc/pdl/test_e2e/test_quantization.py:357-460;
+ * tools/torch_quant/torch_quant/observer.py:181-208):
+ * fq(x) = (clamp(nearbyint(x * (1/s)) + zp, qmin, qmax) - zp) * s. */
+ORACLE_API void oracle_fake_quant_f32(const float* x, int64_t numel, const float* scale,
+                                      const int32_t* zero_point, int64_t channels, int64_t inner,
+                                      int32_t qmin, int32_t qmax, float* y) {
+  if (channels < 1) channels = 1;
+  if (inner < 1) inner = 1;
+  for (int64_t i = 0; i < numel; ++i) {
+    const int64_t c = channels == 1 ? 0 : (i / inner) % channels;
+    const int32_t zp = zero_point ? zero_point[c] : 0;
+    const float inv = 1.0f / scale[c];
+    float t = nearbyintf(x[i] * inv) + (float)zp;
+    t = clampf(t, (float)qmin, (float)qmax);
+    y[i] = (t - (float)zp) * scale[c];
+  }
+}
+
+/* acc[m, n] = sum_k a[m, k] * w[n, k] in int32: the COMPUTE_32I product the GPU
+ * path asks cuBLASLt for (tao_compiler/mlir/ral/context/
+ * quantized_gpu_kernel_impl.cc:57-100, 418-420; weight is [N, K], "n x k col major"
+ * at :323-327). */
+ORACLE_API void oracle_qgemm_acc(const int8_t* a, const int8_t* w, int64_t M, int64_t N, int64_t K,
+                                 int32_t* acc) {
+#ifdef _OPENMP
+#pragma omp parallel for schedule(static)
+#endif
+  for (int64_t m = 0; m < M; ++m) {
+    const int8_t* ar = a + m * K;
+    for (int64_t n = 0; n < N; ++n) {
+      const int8_t* wr = w + n * K;
+      int32_t s = 0;
+      for (int64_t k = 0; k < K; ++k) s += (int32_t)ar[k] * (int32_t)wr[k];
+      acc[m * N + n] = s;
+    }
+  }
+}
+
+static inline float act_apply(float v, int act) {
+  if (act == 1) return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f)); /* exact GELU */
+  if (act == 2) return v / (1.f + expf(-v));                                  /* SiLU */
+  return v;
+}
+
+static inline int8_t sat_s8(float v) {
+  float r = rintf(v);
+  r = clampf(r, -128.f, 127.f);
+  return (int8_t)(int32_t)r;
+}
+
+enum { SCALE_NONE = 0, SCALE_SCALAR = 1, SCALE_PER_COL = 2, SCALE_PER_ROW = 3 };
+enum { BIAS_NONE = 0, BIAS_F32 = 1, BIAS_I8 = 2 };
+enum { OUT_I8 = 0, OUT_F16 = 1, OUT_F32 = 2, OUT_I32 = 3 };
+
+/* General epilogue on an int32 accumulator matrix; produces float values
+ * (before the final store conversion) and, for OUT_I8, the int8 result.
+ *
+ *   cs = x_scale(n) * w_scale(n) [/ out_scale(n) when fold_out]
+ *   v  = fmaf(float(acc) [* x_scale[m]], cs, bias[n]); v = act(v); [v /= out_scale]
+ *
+ * With fold_out = 1, act = 0 and scalar scales this is ral_pdll_qgemm:
+ * kernel_scale = input_scale * weight_scale / result_scale computed in fp32 in
+ * that order (quantized_gpu_kernel_impl.cc:382), alpha * acc + bias, saturating
+ * round-to-nearest conversion to int8 (cuBLASLt epilogue, :130-159).  With
+ * per-column scales it is ral_pdll_qgemm_per_channel (:267-270).  With
+ * div_out it is dequantize -> bias -> activation -> quantize of the lowered
+ * graph (disc_lower_quantize_and_dequantize.cc:77-93,131-136). */
+ORACLE_API void oracle_qgemm_epilogue(const int32_t* acc, int64_t M, int64_t N, const float* x_scale,
+                                      int x_kind, const float* w_scale, int w_kind,
+                                      const float* out_scale, int o_kind, const void* bias,
+                                      int bias_kind, int fold_out, int div_out, int act,
+                                      float* out_f32, int8_t* out_i8) {
+  for (int64_t m = 0; m < M; ++m) {
+    for (int64_t n = 0; n < N; ++n) {
+      float sx = 1.f, sw = 1.f;
+      if (x_kind == SCALE_SCALAR) sx = x_scale[0];
+      else if (x_kind == SCALE_PER_COL) sx = x_scale[n];
+      if (w_kind == SCALE_SCALAR) sw = w_scale[0];
+      else if (w_kind == SCALE_PER_COL) sw = w_scale[n];
+      float cs = sx * sw;
+      if (fold_out) cs = cs / (o_kind == SCALE_PER_COL ? out_scale[n] : out_scale[0]);
+      float cb = 0.f;
+      if (bias_kind == BIAS_F32) cb = ((const float*)bias)[n];
+      else if (bias_kind == BIAS_I8) cb = (float)((const int8_t*)bias)[n];
+      float t = (float)acc[m * N + n];
+      if (x_kind == SCALE_PER_ROW) t = t * x_scale[m];
+      float v = fmaf(t, cs, cb);
+      v = act_apply(v, act);
+      if (div_out) v = v / out_scale[0];
+      if (out_f32) out_f32[m * N + n] = v;
+      if (out_i8) out_i8[m * N + n] = sat_s8(v);
+    }
+  }
+}
+
+/* x86 (oneDNN) form of the same custom call: the f32 bias is first rounded to
+ * s32 at the accumulator scale, then one per-channel output scale is applied:
+ *   bias_s32[n] = rne(bias[n] * (1 / (s_x * s_w[n])))
+ *   out = sat_s8(rne(float(acc + bias_s32[n]) * ((s_x * s_w[n]) / s_out)))
+ * tao_compiler/mlir/ral/context/mkldnn/ideep/ideep/operators/matmul.hpp:527-536
+ * (bias_scales, op_scales) and :556-565 (bias as s32); call site
+ * tao_compiler/mlir/ral/context/common_context_impl_quantization.cc:1268-1400. */
+ORACLE_API void oracle_qgemm_x86(const int32_t* acc, int64_t M, int64_t N, float s_x,
+                                 const float* s_w, int w_per_channel, float s_out,
+                                 const float* bias, int8_t* out) {
+  for (int64_t n = 0; n < N; ++n) {
+    const float sw = w_per_channel ? s_w[n] : s_w[0];
+    const float bias_scale = 1.0f / (s_x * sw);
+    const float op_scale = (s_x * sw) / s_out;
+    int32_t b32 = 0;
+    if (bias) {
+      float br = rintf(bias[n] * bias_scale);
+      if (br > 2147483520.f) br = 2147483520.f;
+      if (br < -2147483648.f) br = -2147483648.f;
+      b32 = (int32_t)br;
+    }
+    for (int64_t m = 0; m < M; ++m) {
+      const float v = (float)(acc[m * N + n] + b32) * op_scale;
+      out[m * N + n] = sat_s8(v);
+    }
+  }
+}
+
+/* Per-row symmetric quantisation of activations (an extension: the reference
+ * quantize op rejects use_dynamic, disc_lower_quantize_and_dequantize.cc:41-43):
+ * scale[r] = max(max|x[r,:]| / 127, FLT_EPSILON), q = quantize(x, scale[r]). */
+ORACLE_API void oracle_dynamic_quantize_f32(const float* x, int64_t rows, int64_t cols, int8_t* q,
+                                            float* row_scale) {
+  for (int64_t r = 0; r < rows; ++r) {
+    float m = 0.f;
+    for (int64_t c = 0; c < cols; ++c) {
+      const float a = fabsf(x[r * cols + c]);
+      if (a > m) m = a;
+    }
+    float s = m / 127.f;
+    if (s < 1.1920928955078125e-07f) s = 1.1920928955078125e-07f;
+    row_scale[r] = s;
+    for (int64_t c = 0; c < cols; ++c) {
+      float t = rintf(x[r * cols + c] / s);
+      t = clampf(t, -128.f, 127.f);
+      q[r * cols + c] = (int8_t)(int32_t)t;
+    }
+  }
+}
+
+/* LayerNorm / RMSNorm over the last axis, as eager PyTorch computes it (the
+ * golden of pytorch_blade/tests/disc/ops/test_layer_norm.py); statistics in
+ * double so that the restatement itself adds no error.
+ * y = (x + residual - mean) / sqrt(var + eps) * gamma + beta. */
+ORACLE_API void oracle_norm_f32(const float* x, const float* residual, const float* gamma,
+                                const float* beta, int64_t rows, int64_t cols, float eps, int rms,
+                                float* y, float* sum_out) {
+  double* buf = (double*)malloc(sizeof(double) * (size_t)cols);
+  for (int64_t r = 0; r < rows; ++r) {
+    double mean = 0.0;
+    for (int64_t c = 0; c < cols; ++c) {
+      float v = x[r * cols + c];
+      if (residual) v = v + residual[r * cols + c];
+      if (sum_out) sum_out[r * cols + c] = v;
+      buf[c] = (double)v;
+      mean += buf[c];
+    }
+    mean = rms ? 0.0 : mean / (double)cols;
+    double var = 0.0;
+    for (int64_t c = 0; c < cols; ++c) var += (buf[c] - mean) * (buf[c] - mean);
+    var /= (double)cols;
+    const double rstd = 1.0 / sqrt(var + (double)eps);
+    for (int64_t c = 0; c < cols; ++c) {
+      double v = (buf[c] - mean) * rstd * (double)gamma[c];
+      if (!rms && beta) v += (double)beta[c];
+      y[r * cols + c] = (float)v;
+    }
+  }
+  free(buf);
+}
+
+/* softmax(x * scale + mask) over the last axis with an optional valid length
+ * per batch (columns >= len get probability 0): eager PyTorch's softmax, the
+ * golden of pytorch_blade/tests/disc/ops/test_nn_ops.py:30-90. */
+ORACLE_API void oracle_softmax_f32(const float* x, int64_t rows, int64_t cols, int64_t rows_per_batch,
+                                   const int32_t* lens, const float* mask, float scale,
+                                   int log_softmax, float* y) {
+  if (rows_per_batch <= 0) rows_per_batch = rows;
+  for (int64_t r = 0; r < rows; ++r) {
+    const int64_t b = r / rows_per_batch;
+    int64_t len = lens ? lens[b] : cols;
+    if (len > cols) len = cols;
+    double mx = -INFINITY;
+    for (int64_t c = 0; c < len; ++c) {
+      double v = (double)(x[r * cols + c] * scale);
+      if (mask) v = (double)(x[r * cols + c] * scale + mask[b * cols + c]);
+      if (v > mx) mx = v;
+    }
+    double sum = 0.0;
+    for (int64_t c = 0; c < len; ++c) {
+      float v = x[r * cols + c] * scale;
+      if (mask) v = v + mask[b * cols + c];
+      sum += exp((double)v - mx);
+    }
+    for (int64_t c = 0; c < cols; ++c) {
+      if (c >= len) {
+        y[r * cols + c] = log_softmax ? -INFINITY : 0.f;
+        continue;
+      }
+      float v = x[r * cols + c] * scale;
+      if (mask) v = v + mask[b * cols + c];
+      const double d = (double)v - mx;
+      y[r * cols + c] = (float)(log_softmax ? d - log(sum) : exp(d) / sum);
+    }
+  }
+}
+
+/* Convenience for timing (bench.py "port" baseline): int32 product plus the
+ * ral_pdll_qgemm epilogue, blocked over rows so that OpenMP (if the file is
+ * built with -fopenmp) can spread it.  Same arithmetic as the two functions
+ * above. */
+ORACLE_API void oracle_qgemm_ral_i8(const int8_t* a, const int8_t* w, int64_t M, int64_t N, int64_t K,
+                                    float s_x, const float* s_w, int w_per_channel, float s_out,
+                                    const float* bias, int8_t* out) {
+#ifdef _OPENMP
+#pragma omp parallel for schedule(static)
+#endif
+  for (int64_t m = 0; m < M; ++m) {
+    const int8_t* ar = a + m * K;
+    for (int64_t n = 0; n < N; ++n) {
+      const int8_t* wr = w + n * K;
+      int32_t s = 0;
+      for (int64_t k = 0; k < K; ++k) s += (int32_t)ar[k] * (int32_t)wr[k];
+      const float sw = w_per_channel ? s_w[n] : s_w[0];
+      const float cs = (s_x * sw) / s_out;
+      out[m * N + n] = sat_s8(fmaf((float)s, cs, bias ? bias[n] : 0.f));
+    }
+  }
+}

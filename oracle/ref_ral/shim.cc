@@ -1,0 +1,209 @@
+// TEST INFRASTRUCTURE.  Linked together with the reference's own RAL core
+// (ral_api.cc, ral_context.cc, ral_helper.cc, ral_logging.cc, compiled from
+// the reference tree where it lies) into oracle/_ref/libref_ral.so.
+//
+// It registers recording stubs, with the reference's registration macro and
+// the reference's C++ signatures, for the custom calls our library implements
+// under reference names.  Tests then (1) compare the names the reference
+// mangles with the names our registry holds and (2) send one packed argument
+// array through the reference's tao_ral_call_impl and read back what its
+// unpacking produced, which pins the packing our own tests use.
+#include <cstdint>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "mlir/ral/ral_api.h"
+#include "mlir/ral/ral_context.h"
+#include "mlir/ral/ral_helper.h"
+
+using tao::ral::ExecutionContext;
+using tao::ral::MemRefType;
+
+namespace {
+
+std::vector<int64_t> g_record;
+std::vector<std::string> g_names;
+
+void rec(int64_t v) { g_record.push_back(v); }
+void rec_ptr(const void* p) { g_record.push_back(static_cast<int64_t>(reinterpret_cast<intptr_t>(p))); }
+template <typename T, int N>
+void rec_memref(const MemRefType<T, N>& m) {
+  rec_ptr(m.basePtr);
+  rec_ptr(m.data);
+  rec(m.offset);
+  for (int i = 0; i < N; ++i) rec(m.sizes[i]);
+  for (int i = 0; i < N; ++i) rec(m.strides[i]);
+}
+template <typename T>
+void rec_memref(const MemRefType<T, 0>& m) {
+  rec_ptr(m.basePtr);
+  rec_ptr(m.data);
+  rec(m.offset);
+}
+
+template <int N, typename BiasT>
+MemRefType<int8_t, N> stub_pdll_qgemm(ExecutionContext* ctx, void* stream, MemRefType<int8_t, N> input,
+                                      MemRefType<int8_t, 2> weight, MemRefType<BiasT, 1> bias,
+                                      MemRefType<float, 0> in_s, MemRefType<int32_t, 0> in_zp,
+                                      MemRefType<float, 0> w_s, MemRefType<int32_t, 0> w_zp,
+                                      MemRefType<float, 0> out_s, MemRefType<int32_t, 0> out_zp,
+                                      void* attrs) {
+  g_record.clear();
+  rec_ptr(ctx);
+  rec_ptr(stream);
+  rec_memref(input);
+  rec_memref(weight);
+  rec_memref(bias);
+  rec_memref(in_s);
+  rec_memref(in_zp);
+  rec_memref(w_s);
+  rec_memref(w_zp);
+  rec_memref(out_s);
+  rec_memref(out_zp);
+  rec_ptr(attrs);
+  MemRefType<int8_t, N> r;
+  r.basePtr = reinterpret_cast<int8_t*>(0x1000);
+  r.data = reinterpret_cast<int8_t*>(0x1040);
+  r.offset = 7;
+  for (int i = 0; i < N; ++i) {
+    r.sizes[i] = 100 + i;
+    r.strides[i] = 200 + i;
+  }
+  return r;
+}
+
+template <int N>
+MemRefType<int8_t, N> stub_pdll_qgemm_pc(ExecutionContext* ctx, void* stream, MemRefType<int8_t, N> input,
+                                         MemRefType<int8_t, 2> weight, MemRefType<int8_t, 1> bias,
+                                         MemRefType<float, 1> in_s, MemRefType<int32_t, 1> in_zp,
+                                         MemRefType<float, 1> w_s, MemRefType<int32_t, 1> w_zp,
+                                         MemRefType<float, 1> out_s, MemRefType<int32_t, 1> out_zp,
+                                         void* attrs) {
+  g_record.clear();
+  rec_ptr(ctx);
+  rec_ptr(stream);
+  rec_memref(input);
+  rec_memref(weight);
+  rec_memref(bias);
+  rec_memref(in_s);
+  rec_memref(in_zp);
+  rec_memref(w_s);
+  rec_memref(w_zp);
+  rec_memref(out_s);
+  rec_memref(out_zp);
+  rec_ptr(attrs);
+  MemRefType<int8_t, N> r;
+  std::memset(&r, 0, sizeof(r));
+  return r;
+}
+
+void stub_qgemm(ExecutionContext* ctx, void* stream, MemRefType<int8_t, 2> input,
+                MemRefType<int8_t, 2> weight, MemRefType<float, 0> in_s, MemRefType<int32_t, 0> in_zp,
+                MemRefType<float, 0> w_s, MemRefType<int32_t, 0> w_zp, MemRefType<float, 0> out_s,
+                MemRefType<int32_t, 0> out_zp, MemRefType<int8_t, 2> result, bool tp_a, bool tp_b,
+                bool weight_is_const) {
+  g_record.clear();
+  rec_ptr(ctx);
+  rec_ptr(stream);
+  rec_memref(input);
+  rec_memref(weight);
+  rec_memref(in_s);
+  rec_memref(in_zp);
+  rec_memref(w_s);
+  rec_memref(w_zp);
+  rec_memref(out_s);
+  rec_memref(out_zp);
+  rec_memref(result);
+  rec(tp_a);
+  rec(tp_b);
+  rec(weight_is_const);
+}
+
+// Driver-set signatures (tao_compiler/mlir/ral/context/base/cuda/cuda_context_impl.cc).
+void* stub_alloc(ExecutionContext* ctx, size_t bytes) {
+  g_record.clear();
+  rec_ptr(ctx);
+  rec(static_cast<int64_t>(bytes));
+  return reinterpret_cast<void*>(0x2000);
+}
+void stub_dealloc(ExecutionContext* ctx, void* p) {
+  g_record.clear();
+  rec_ptr(ctx);
+  rec_ptr(p);
+}
+void* stub_alloc_persistent(ExecutionContext*, size_t) { return nullptr; }
+void stub_memset(ExecutionContext*, void*, void*, int, size_t) {}
+void* stub_get_stream(ExecutionContext*, int32_t) { return nullptr; }
+void* stub_as_cu_stream(ExecutionContext*, void*) { return nullptr; }
+void stub_d2d(ExecutionContext*, void*, void*, void*, size_t) {}
+void stub_h2d(ExecutionContext*, void*, const void*, void*, size_t) {}
+void stub_d2h(ExecutionContext*, void*, void*, void*, size_t) {}
+void stub_sync_on_stream(ExecutionContext*, void*) {}
+void stub_sync_all(ExecutionContext*) {}
+void stub_launch(ExecutionContext*, void**, size_t, const char*, intptr_t, intptr_t, intptr_t, intptr_t,
+                 intptr_t, intptr_t, int32_t, void*, int32_t, void**) {}
+template <typename T, int N>
+MemRefType<T, N> stub_recv_input(ExecutionContext*, int64_t) {
+  MemRefType<T, N> m;
+  std::memset(&m, 0, sizeof(m));
+  return m;
+}
+template <typename T, int N>
+void stub_send_output(ExecutionContext*, int64_t, MemRefType<T, N>) {}
+
+template <typename F>
+void note(const char* api, const char* device, F f) {
+  g_names.push_back(
+      tao::ral::TaoRalApiFuncNameHelper<F>::Invoke(std::string(api) + "___" + std::string(device)));
+}
+
+}  // namespace
+
+#define REF_STUB2(api, device, line, ...)        \
+  TAO_RAL_API(api, device, __VA_ARGS__);         \
+  static bool disc_note_##line = (note(api, device, &__VA_ARGS__), true)
+#define REF_STUB1(api, device, line, ...) REF_STUB2(api, device, line, __VA_ARGS__)
+#define REF(api, device, ...) REF_STUB1(api, device, __COUNTER__, __VA_ARGS__)
+
+REF("ral_pdll_qgemm", "gpu", stub_pdll_qgemm<2, int8_t>);
+REF("ral_pdll_qgemm", "gpu", stub_pdll_qgemm<3, int8_t>);
+REF("ral_pdll_qgemm", "gpu", stub_pdll_qgemm<2, float>);
+REF("ral_pdll_qgemm", "gpu", stub_pdll_qgemm<3, float>);
+REF("ral_pdll_qgemm_per_channel", "gpu", stub_pdll_qgemm_pc<2>);
+REF("ral_pdll_qgemm_per_channel", "gpu", stub_pdll_qgemm_pc<3>);
+REF("ral_qgemm", "gpu", stub_qgemm);
+REF("alloc", "gpu", stub_alloc);
+REF("dealloc", "gpu", stub_dealloc);
+REF("ral_gpu_alloc_persistent", "gpu", stub_alloc_persistent);
+REF("ral_gpu_memset", "gpu", stub_memset);
+REF("ral_gpu_get_stream", "gpu", stub_get_stream);
+REF("ral_gpu_as_cu_stream", "gpu", stub_as_cu_stream);
+REF("d2d_", "gpu", stub_d2d);
+REF("h2d_", "gpu", stub_h2d);
+REF("d2h_", "gpu", stub_d2h);
+REF("sync_on_stream", "gpu", stub_sync_on_stream);
+REF("ral_gpu_sync_all", "gpu", stub_sync_all);
+REF("ral_kernel_launch", "gpu", stub_launch);
+REF("ral_recv_input", "cpu", stub_recv_input<float, 2>);
+REF("ral_recv_input", "cpu", stub_recv_input<int8_t, 3>);
+REF("ral_send_output", "cpu", stub_send_output<float, 2>);
+REF("ral_send_output", "cpu", stub_send_output<int8_t, 3>);
+
+extern "C" {
+
+int ref_num_names() { return static_cast<int>(g_names.size()); }
+const char* ref_name(int i) { return g_names[i].c_str(); }
+
+// Dispatches through the reference's own entry point with a reference
+// Context / ExecutionContext; returns the number of recorded values.
+int ref_dispatch(const char* name, void** args) {
+  static tao::ral::Context* ctx = new tao::ral::Context;
+  tao::ral::ExecutionContext exec(ctx);
+  // The generated stub overwrites the first argument with the real context.
+  *static_cast<void**>(args[0]) = &exec;
+  tao_ral_call_impl(&exec, const_cast<char*>(name), args);
+  return static_cast<int>(g_record.size());
+}
+int64_t ref_recorded(int i) { return g_record[i]; }
+}

@@ -1,0 +1,216 @@
+"""Parity of the sm_100a quantized linear against the CPU oracle (B200 only).
+
+int32 accumulators: bit-exact.  int8 outputs: bit-exact against the oracle's
+statement of the same epilogue and within 1 LSB of the reference's fake-quant
+golden.  fp16 / fp32 outputs: rtol 1e-2, atol 1e-3.
+"""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-2, 1e-3
+
+
+@pytest.fixture(scope="module")
+def ops():
+    assert torch.cuda.is_available()
+    from bladedisc_b200 import ops as o
+    yield o
+    assert o.kernel_status() == 0, "a kernel's bounded wait ran out"
+
+
+def _rand_i8(rng, shape):
+    return rng.integers(-127, 128, shape, dtype=np.int8)
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+# (M, K, N): every path, ragged edges, K not a multiple of the 128-byte tile,
+# N not a multiple of the vector width, one row, one tile exactly.
+ACC_SHAPES = [
+    (1, 768, 768), (7, 768, 3072), (64, 3072, 768), (33, 144, 80), (16, 128, 128), (64, 4096, 512),
+    (128, 256, 256), (129, 256, 384), (333, 768, 768), (200, 144, 72), (256, 128, 136), (1024, 768, 3072),
+    (1024, 3072, 768), (130, 2064, 264),
+]
+
+
+@pytest.mark.parametrize("M,K,N", ACC_SHAPES)
+def test_accumulators_bit_exact(ops, M, K, N):
+    from oracle import c
+    rng = np.random.default_rng(M * 131 + K * 7 + N)
+    a, w = _rand_i8(rng, (M, K)), _rand_i8(rng, (N, K))
+    want = c.qgemm_acc(a, w)
+    got = ops.qgemm(_dev(a), _dev(w), out_dtype=torch.int32).cpu().numpy()
+    assert got.shape == want.shape
+    assert (got == want).all(), f"path {ops.qgemm_path(M, N, K)}: {np.count_nonzero(got != want)} mismatches"
+
+
+@pytest.mark.parametrize("path,M", [("tiled", 96), ("tiled", 1), ("small_m", 128), ("small_m", 100),
+                                    ("simt", 70), ("small_m", 5)])
+def test_forced_paths_agree(ops, path, M):
+    from oracle import c
+    rng = np.random.default_rng(11)
+    a, w = _rand_i8(rng, (M, 640)), _rand_i8(rng, (392, 640))
+    got = ops.qgemm(_dev(a), _dev(w), out_dtype=torch.int32, path=path).cpu().numpy()
+    assert (got == c.qgemm_acc(a, w)).all()
+
+
+@pytest.mark.parametrize("split", [1, 2, 3, 5, 8])
+def test_small_m_split_k_is_exact_and_repeatable(ops, split):
+    from oracle import c
+    rng = np.random.default_rng(split)
+    a, w = _rand_i8(rng, (48, 1024)), _rand_i8(rng, (520, 1024))
+    want = c.qgemm_acc(a, w)
+    for _ in range(3):  # the scratch and its arrival counters are reused
+        got = ops.qgemm(_dev(a), _dev(w), out_dtype=torch.int32, path="small_m", split_k=split).cpu().numpy()
+        assert (got == want).all()
+
+
+def test_unaligned_shapes_take_the_simt_path(ops):
+    """K = 25 cannot be addressed by TMA (rows must be 16-byte multiples): the
+    reference's known-answer shape (x [4,25], w [71,25]) still has to work."""
+    from oracle import c
+    assert ops.qgemm_path(4, 71, 25) == "simt"
+    x = np.full((4, 25), -0.6, dtype=np.float32)
+    w = np.full((71, 25), -0.8, dtype=np.float32)
+    s_x, s_w, s_out = np.float32(8.333333e-3), np.float32(1.568627e-2), np.float32(1.0)
+    xq = ops.quantize(_dev(x), _dev(np.array([s_x])))
+    wq = ops.quantize(_dev(w), _dev(np.array([s_w])))
+    assert (xq.cpu().numpy() == c.quantize(x, s_x)).all()
+    q = ops.qgemm(xq, wq, x_scale=_dev(np.array([s_x])), w_scale=_dev(np.array([s_w])),
+                  out_scale=_dev(np.array([s_out])), fold_out_scale=True)
+    y = ops.dequantize(q, _dev(np.array([s_out])))
+    assert (y.cpu().numpy() == 12.0).all()  # tao_compiler/mlir/disc/tests/pdll/qgemm.cc:24-42
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 768, 768), (64, 768, 3072), (333, 3072, 768), (1024, 768, 768)])
+@pytest.mark.parametrize("bias_kind", ["f32", "i8", None])
+def test_reference_epilogue_int8(ops, M, K, N, bias_kind):
+    """ral_pdll_qgemm: sat(rne(acc * (s_x * s_w / s_out) + bias)) (config 1 scales)."""
+    from oracle import c
+    rng = np.random.default_rng(M + K + N)
+    a, w = _rand_i8(rng, (M, K)), _rand_i8(rng, (N, K))
+    s_x, s_w, s_out = np.float32(0.02), np.float32(0.004), np.float32(0.05)
+    bias = None
+    if bias_kind == "f32":
+        bias = (rng.standard_normal(N) * 20).astype(np.float32)
+    elif bias_kind == "i8":
+        bias = _rand_i8(rng, N)
+    _, want = c.qgemm_epilogue(c.qgemm_acc(a, w), x_scale=s_x, w_scale=s_w, out_scale=s_out, bias=bias,
+                               fold_out=True)
+    got = ops.qgemm(_dev(a), _dev(w), x_scale=_dev(np.array([s_x])), w_scale=_dev(np.array([s_w])),
+                    out_scale=_dev(np.array([s_out])), bias=None if bias is None else _dev(bias),
+                    fold_out_scale=True).cpu().numpy()
+    assert (got == want).all()
+    assert np.abs(got.astype(int)).max() > 100  # the case exercises saturation too
+
+
+@pytest.mark.parametrize("M", [7, 200])
+def test_per_channel_folded_form(ops, M):
+    """ral_pdll_qgemm_per_channel: every scale operand has N entries, int8 bias."""
+    from oracle import c
+    rng = np.random.default_rng(5)
+    K, N = 256, 192
+    a, w = _rand_i8(rng, (M, K)), _rand_i8(rng, (N, K))
+    sx = (rng.random(N) * 0.02 + 0.01).astype(np.float32)
+    sw = (rng.random(N) * 9e-3 + 1e-3).astype(np.float32)
+    so = (rng.random(N) * 0.05 + 0.02).astype(np.float32)
+    bias = _rand_i8(rng, N)
+    _, want = c.qgemm_epilogue(c.qgemm_acc(a, w), x_scale=sx, w_scale=sw, out_scale=so, bias=bias,
+                               fold_out=True, x_per_col=True)
+    got = ops.qgemm(_dev(a), _dev(w), x_scale=_dev(sx), w_scale=_dev(sw), out_scale=_dev(so), bias=_dev(bias),
+                    fold_out_scale=True, x_scale_per_col=True).cpu().numpy()
+    assert (got == want).all()
+
+
+@pytest.mark.parametrize("M,K,N", [(7, 768, 768), (64, 768, 3072), (333, 768, 3072), (1024, 3072, 768)])
+@pytest.mark.parametrize("act", [None, "gelu", "silu"])
+def test_fused_epilogue_fp16_and_requant(ops, M, K, N, act):
+    """Config 1: per-tensor s_x = 0.02, per-channel s_w in [1e-3, 1e-2], fp32 bias;
+    fp16 dequantized output and int8 requantized at 0.05."""
+    from oracle import c
+    rng = np.random.default_rng(M * 3 + N)
+    a, w = _rand_i8(rng, (M, K)), _rand_i8(rng, (N, K))
+    sw = (rng.random(N) * 9e-3 + 1e-3).astype(np.float32)
+    bias = (rng.standard_normal(N) * 0.01).astype(np.float32)
+    s_x, s_out = np.float32(0.02), np.float32(0.05)
+    acc = c.qgemm_acc(a, w)
+    f_want, _ = c.qgemm_epilogue(acc, x_scale=s_x, w_scale=sw, bias=bias, act=act)
+    _, q_want = c.qgemm_epilogue(acc, x_scale=s_x, w_scale=sw, out_scale=s_out, bias=bias, act=act, div_out=True)
+    kw = dict(x_scale=_dev(np.array([s_x])), w_scale=_dev(sw), bias=_dev(bias), act=act)
+    f16 = ops.qgemm(_dev(a), _dev(w), out_dtype=torch.float16, **kw).float().cpu().numpy()
+    f32 = ops.qgemm(_dev(a), _dev(w), out_dtype=torch.float32, **kw).cpu().numpy()
+    q = ops.qgemm(_dev(a), _dev(w), out_scale=_dev(np.array([s_out])), **kw).cpu().numpy()
+    assert np.allclose(f32, f_want, rtol=RTOL, atol=ATOL)
+    finite = np.abs(f_want) < 60000
+    assert np.allclose(f16[finite], f_want[finite], rtol=RTOL, atol=ATOL)
+    assert np.abs(q.astype(int) - q_want.astype(int)).max() <= 1  # libdevice erf / exp vs libm
+    if act is None:
+        assert (q == q_want).all() and (f32 == f_want).all()
+
+
+@pytest.mark.parametrize("M", [5, 150])
+def test_per_row_dynamic_scales(ops, M):
+    """Per-token activation scales (config 4): acc * s_x[m] * s_w[n] + bias."""
+    from oracle import c
+    rng = np.random.default_rng(M)
+    K, N = 512, 320
+    x = (rng.standard_normal((M, K)) * rng.random((M, 1)) * 4).astype(np.float32)
+    w = _rand_i8(rng, (N, K))
+    sw = (rng.random(N) * 9e-3 + 1e-3).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    xq, sx = ops.dynamic_quantize(_dev(x))
+    xq_want, sx_want = c.dynamic_quantize(x)
+    assert (xq.cpu().numpy() == xq_want).all() and (sx.cpu().numpy() == sx_want).all()
+    want, _ = c.qgemm_epilogue(c.qgemm_acc(xq_want, w), x_scale=sx_want, w_scale=sw, bias=bias)
+    got = ops.qgemm(xq, _dev(w), x_scale=sx, w_scale=_dev(sw), bias=_dev(bias), out_dtype=torch.float32)
+    assert (got.cpu().numpy() == want).all()
+
+
+def test_fake_quant_golden_within_one_lsb(ops, golden):
+    """The reference's e2e golden (eager fake-quant linear): atol = output scale
+    (pytorch_blade/tests/disc/pdl/test_e2e/test_quantization.py:408)."""
+    for tag in ("r2", "r3"):
+        x, w, b, s, y = [golden[f"fq_linear_{tag}_{k}"] for k in ("x", "w", "b", "scales", "y")]
+        sc = [_dev(np.array([v], dtype=np.float32)) for v in s]
+        xq = ops.quantize(_dev(x), sc[0])
+        wq = ops.quantize(_dev(w), sc[1])
+        q = ops.qgemm(xq, wq, x_scale=sc[0], w_scale=sc[1], out_scale=sc[2],
+                      bias=_dev((b / s[2]).astype(np.float32)), fold_out_scale=True)
+        got = ops.dequantize(q, sc[2]).cpu().numpy()
+        assert got.shape == y.shape
+        assert np.abs(got - y).max() <= s[2] * 1.0001
+
+
+def test_empty_and_degenerate(ops):
+    a = torch.zeros((0, 64), dtype=torch.int8, device="cuda")
+    w = torch.ones((32, 64), dtype=torch.int8, device="cuda")
+    assert ops.qgemm(a, w, out_dtype=torch.int32).shape == (0, 32)
+    # extreme values: -128 * -128 * K stays inside int32
+    a = torch.full((130, 4096), -128, dtype=torch.int8, device="cuda")
+    w = torch.full((144, 4096), -128, dtype=torch.int8, device="cuda")
+    assert (ops.qgemm(a, w, out_dtype=torch.int32) == 128 * 128 * 4096).all()
+    assert (ops.qgemm(a[:3], w, out_dtype=torch.int32) == 128 * 128 * 4096).all()
+
+
+@pytest.mark.parametrize("M,K,N", [(4096, 4096, 4096), (16384, 4096, 11008), (64, 4096, 11008)])
+def test_full_size_checksums(ops, M, K, N):
+    """At benchmark sizes the oracle is too slow; two size-independent identities
+    cover every output: row sums  sum_n acc[m, n] = a[m, :] . (sum_n w[n, :])  and
+    column sums  sum_m acc[m, n] = (sum_m a[m, :]) . w[n, :]  (exact in int64),
+    plus 32 full rows against the oracle."""
+    from oracle import c
+    rng = np.random.default_rng(M + N)
+    a, w = _rand_i8(rng, (M, K)), _rand_i8(rng, (N, K))
+    acc = ops.qgemm(_dev(a), _dev(w), out_dtype=torch.int32)
+    row_sum = acc.sum(dim=1, dtype=torch.int64).cpu().numpy()
+    col_sum = acc.sum(dim=0, dtype=torch.int64).cpu().numpy()
+    a64, w64 = a.astype(np.int64), w.astype(np.int64)
+    assert (row_sum == a64 @ w64.sum(axis=0)).all()
+    assert (col_sum == w64 @ a64.sum(axis=0)).all()
+    rows = rng.choice(M, size=min(32, M), replace=False)
+    assert (acc[torch.from_numpy(rows).cuda()].cpu().numpy() == c.qgemm_acc(a[rows], w)).all()
