@@ -41,6 +41,8 @@ def _args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=M_ROWS, help="activation rows per rank and step")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="for ncu captures: only warm-up and timed steps (no clock hold, e2e or CPU legs)")
     return ap.parse_args()
 
 
@@ -53,55 +55,81 @@ def _peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons through NVML (read-only) in a thread while the
+    GPU is under load; falls back to polling nvidia-smi."""
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, index: int):
         self.index = index
-        self.proc = None
-        self.lines = []
+        self.samples = []
+        self.mask = 0
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self.thread = None
+        self.how = None
+
+    def _nvml_loop(self, nv, h):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                self.mask |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def _smi_loop(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        bits = [0x8, 0x40, 0x20, 0x4]
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i",
+                                      str(self.index)], capture_output=True, text=True, timeout=10).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                self.samples.append(float(parts[0]))
+                self.max_mhz = float(parts[1])
+                for b, v in zip(bits, parts[2:6]):
+                    if v.lower().startswith("active"):
+                        self.mask |= b
+            except Exception:
+                time.sleep(0.05)
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            import pynvml as nv
+            nv.nvmlInit()
+            uuid = None
+            try:
+                import torch
+                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            except Exception:
+                pass
+            h = None
+            if uuid:
+                for i in range(nv.nvmlDeviceGetCount()):
+                    cand = nv.nvmlDeviceGetHandleByIndex(i)
+                    u = nv.nvmlDeviceGetUUID(cand)
+                    u = u.decode() if isinstance(u, bytes) else u
+                    if uuid in u:
+                        h = cand
+            if h is None:
+                h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            self.how = "nvml"
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, h), daemon=True)
+        except Exception:
+            self.how = "nvidia-smi"
+            self.thread = threading.Thread(target=self._smi_loop, daemon=True)
+        self.thread.start()
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx = float(parts[1])
-            except ValueError:
-                continue
-            for name, v in zip(names, parts[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        self._stop.set()
+        if self.thread:
+            self.thread.join(timeout=15)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(n for b, n in self.REASONS.items() if self.mask & b),
+                "samples": len(s), "how": self.how}
 
 
 def _make_problem(torch, rows, device, seed):
@@ -250,6 +278,15 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    # Untimed: keep the same kernel running for a moment so that clocks settle under load and
+    # the sampler (10 ms period) sees the loaded state even when K steps take only milliseconds.
+    t_hold = time.perf_counter()
+    j = 0
+    while not args.profile and time.perf_counter() - t_hold < 0.5:
+        for _ in range(20):
+            step(j)
+            j += 1
+        torch.cuda.synchronize()
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     barrier()
     evs[0].record()
@@ -263,6 +300,10 @@ def run_ours(args):
     status = ops.kernel_status()
     if status != 0:
         raise SystemExit(f"kernel status {status}: a bounded wait ran out; numbers would be meaningless")
+
+    if args.profile:
+        print(json.dumps({"profile_run": True, "ms_per_step": total_ms / args.steps, "rows": rows}), flush=True)
+        return
 
     # ---- end to end through the host-buffer API
     layer = HostQLinear(w, w_scale, x_scale, bias=bias, out_scale=out_scale, chunk_rows=2048)

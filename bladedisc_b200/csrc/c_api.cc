@@ -139,8 +139,8 @@ int32_t disc_b200_quantize(const void* x, int32_t in_type, int8_t* q, int64_t nu
   p.qmin = qmin;
   p.qmax = qmax;
   const char* detail = nullptr;
-  return finish(disc_b200::quantize_launch(p, static_cast<cudaStream_t>(stream), &detail), "quantize",
-                detail);
+  const cudaError_t st = disc_b200::quantize_launch(p, static_cast<cudaStream_t>(stream), &detail);
+  return finish(st, "quantize", detail);
 }
 
 int32_t disc_b200_dequantize(const int8_t* q, void* y, int32_t out_type, int64_t numel,
@@ -156,8 +156,8 @@ int32_t disc_b200_dequantize(const int8_t* q, void* y, int32_t out_type, int64_t
   p.channels = channels;
   p.inner = inner;
   const char* detail = nullptr;
-  return finish(disc_b200::dequantize_launch(p, static_cast<cudaStream_t>(stream), &detail),
-                "dequantize", detail);
+  const cudaError_t st = disc_b200::dequantize_launch(p, static_cast<cudaStream_t>(stream), &detail);
+  return finish(st, "dequantize", detail);
 }
 
 int32_t disc_b200_dynamic_quantize(const void* x, int32_t in_type, int8_t* q, float* row_scale,
@@ -170,8 +170,8 @@ int32_t disc_b200_dynamic_quantize(const void* x, int32_t in_type, int8_t* q, fl
   p.cols = cols;
   p.in_type = in_type;
   const char* detail = nullptr;
-  return finish(disc_b200::dynamic_quantize_launch(p, static_cast<cudaStream_t>(stream), &detail),
-                "dynamic_quantize", detail);
+  const cudaError_t st = disc_b200::dynamic_quantize_launch(p, static_cast<cudaStream_t>(stream), &detail);
+  return finish(st, "dynamic_quantize", detail);
 }
 
 int32_t disc_b200_norm(const disc_b200_norm_args* a, void* stream) {
@@ -195,7 +195,8 @@ int32_t disc_b200_norm(const disc_b200_norm_args* a, void* stream) {
   p.type = a->type;
   p.rms = a->rms;
   const char* detail = nullptr;
-  return finish(disc_b200::norm_launch(p, static_cast<cudaStream_t>(stream), &detail), "norm", detail);
+  const cudaError_t st = disc_b200::norm_launch(p, static_cast<cudaStream_t>(stream), &detail);
+  return finish(st, "norm", detail);
 }
 
 int32_t disc_b200_softmax(const void* x, void* y, int32_t type, int64_t rows, int64_t cols,
@@ -213,8 +214,8 @@ int32_t disc_b200_softmax(const void* x, void* y, int32_t type, int64_t rows, in
   p.type = type;
   p.log_softmax = log_softmax;
   const char* detail = nullptr;
-  return finish(disc_b200::softmax_launch(p, static_cast<cudaStream_t>(stream), &detail), "softmax",
-                detail);
+  const cudaError_t st = disc_b200::softmax_launch(p, static_cast<cudaStream_t>(stream), &detail);
+  return finish(st, "softmax", detail);
 }
 
 const char* disc_b200_last_error_string(void) { return g_last_error.c_str(); }

@@ -42,9 +42,9 @@ struct QGemmParams {
   int out_dtype;  // QGemmOut
   int path;       // QGemmPath (tests force a path; callers leave kPathAuto)
   int split_k;    // small-M path: 0 = choose
-  // Scratch for the small-M split-K reduction (zero on entry, left zero on
-  // exit): int32 partial sums followed by one int32 arrival counter per
-  // 128-channel block.  Needed only when the launch splits K.
+  // Scratch for the small-M split-K reduction: 4096 int32 arrival counters
+  // (zero on entry, left zero on exit), then int32 partial sums (need no
+  // clearing).  Needed only when the launch splits K.
   int32_t* splitk_ws;
   int64_t splitk_ws_bytes;
 };

@@ -368,6 +368,7 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 // ---------------------------------------------------------------- small M
 constexpr int kSmallMaxStages = 8;
+constexpr int kSplitCounterWords = 4096;  // int32 arrival counters at the front of the scratch
 constexpr int kSmallBarOffset = 200 * 1024;  // stages live below this offset
 constexpr int kSmallDynamic = kSmallBarOffset + 256 + 1024;
 
@@ -714,13 +715,15 @@ cudaError_t launch_smallm(const QGemmParams& p, cudaStream_t stream, const char*
   int32_t* counters = nullptr;
   if (split > 1) {
     const int64_t n_pad = static_cast<int64_t>(tiles_n) * kTileM;
-    const int64_t need = (static_cast<int64_t>(split) * p.M * n_pad + tiles_n) * 4;
-    if (!p.splitk_ws || p.splitk_ws_bytes < need) {
+    const int64_t need = (static_cast<int64_t>(split) * p.M * n_pad + kSplitCounterWords) * 4;
+    if (!p.splitk_ws || p.splitk_ws_bytes < need || tiles_n > kSplitCounterWords) {
       if (err) *err = "small-M qgemm: split-K scratch missing or too small";
       return cudaErrorInvalidValue;
     }
-    counters = p.splitk_ws;  // counters first so their place does not depend on the split
-    ws = p.splitk_ws + tiles_n;
+    // The arrival counters own a fixed region at the front (they must stay zero
+    // between launches); partial sums of any launch shape live behind it.
+    counters = p.splitk_ws;
+    ws = p.splitk_ws + kSplitCounterWords;
   }
   CUtensorMap tw, tx;
   if (!make_tmap(&tw, p.w, p.N, p.K, p.ldw, kTileM) || !make_tmap(&tx, p.a, p.M, p.K, p.lda, MT)) {
@@ -773,7 +776,7 @@ int64_t qgemm_splitk_ws_bytes(int64_t M, int64_t N, int64_t K) {
   const int64_t tiles_n = (N + kTileM - 1) / kTileM;
   const int64_t num_kb = (K + kTileKBytes - 1) / kTileKBytes;
   int64_t split = num_kb < 8 ? num_kb : 8;
-  return (split * M * tiles_n * kTileM + tiles_n) * 4;
+  return (split * M * tiles_n * kTileM + kSplitCounterWords) * 4;
 }
 
 cudaError_t qgemm_launch(const QGemmParams& p, cudaStream_t stream, const char** err) {

@@ -426,7 +426,8 @@ MemRef<int8_t, N> quantize_call(ExecContext* ctx, void* stream_handle, MemRef<T,
   p.qmin = static_cast<int>(at->get_int("quant_min", -128));
   p.qmax = static_cast<int>(at->get_int("quant_max", 127));
   const char* detail = nullptr;
-  report(ctx, quantize_launch(p, stream_of(ctx), &detail), "quantize", detail);
+  const cudaError_t launch_st = quantize_launch(p, stream_of(ctx), &detail);
+  report(ctx, launch_st, "quantize", detail);
   return result;
 }
 
@@ -455,7 +456,8 @@ std::tuple<MemRef<int8_t, N>, MemRef<float, 1>> dynamic_quantize_call(ExecContex
   p.cols = cols;
   p.in_type = elem_type_of<T>();
   const char* detail = nullptr;
-  report(ctx, dynamic_quantize_launch(p, stream_of(ctx), &detail), "dynamic_quantize", detail);
+  const cudaError_t launch_st = dynamic_quantize_launch(p, stream_of(ctx), &detail);
+  report(ctx, launch_st, "dynamic_quantize", detail);
   return std::make_tuple(r0, r1);
 }
 
@@ -477,7 +479,8 @@ MemRef<T, N> dequantize_call(ExecContext* ctx, void* stream_handle, MemRef<int8_
   p.channels = 1;
   p.inner = 1;
   const char* detail = nullptr;
-  report(ctx, dequantize_launch(p, stream_of(ctx), &detail), "dequantize", detail);
+  const cudaError_t launch_st = dequantize_launch(p, stream_of(ctx), &detail);
+  report(ctx, launch_st, "dequantize", detail);
   return result;
 }
 
@@ -511,7 +514,8 @@ MemRef<T, N> layernorm_call(ExecContext* ctx, void* stream_handle, MemRef<T, N> 
                                    static_cast<float>(at->get_float("eps", 1e-5)), 0);
   p.y = y;
   const char* detail = nullptr;
-  report(ctx, norm_launch(p, stream_of(ctx), &detail), "layernorm", detail);
+  const cudaError_t launch_st = norm_launch(p, stream_of(ctx), &detail);
+  report(ctx, launch_st, "layernorm", detail);
   return result;
 }
 
@@ -533,7 +537,8 @@ MemRef<T, N> add_layernorm_call(ExecContext* ctx, void* stream_handle, MemRef<T,
                                    static_cast<float>(at->get_float("eps", 1e-5)), 0);
   p.y = y;
   const char* detail = nullptr;
-  report(ctx, norm_launch(p, stream_of(ctx), &detail), "add_layernorm", detail);
+  const cudaError_t launch_st = norm_launch(p, stream_of(ctx), &detail);
+  report(ctx, launch_st, "add_layernorm", detail);
   return result;
 }
 
@@ -561,7 +566,8 @@ std::tuple<MemRef<T, N>, MemRef<int8_t, N>> add_layernorm_quant_call(
   p.q_out = q;
   p.q_scale = q_scale.data;
   const char* detail = nullptr;
-  report(ctx, norm_launch(p, stream_of(ctx), &detail), "add_layernorm_quant", detail);
+  const cudaError_t launch_st = norm_launch(p, stream_of(ctx), &detail);
+  report(ctx, launch_st, "add_layernorm_quant", detail);
   return result;
 }
 
@@ -578,7 +584,8 @@ MemRef<T, N> rmsnorm_call(ExecContext* ctx, void* stream_handle, MemRef<T, N> x,
                                    static_cast<float>(at->get_float("eps", 1e-6)), 1);
   p.y = y;
   const char* detail = nullptr;
-  report(ctx, norm_launch(p, stream_of(ctx), &detail), "rmsnorm", detail);
+  const cudaError_t launch_st = norm_launch(p, stream_of(ctx), &detail);
+  report(ctx, launch_st, "rmsnorm", detail);
   return result;
 }
 
@@ -603,7 +610,8 @@ MemRef<T, N> softmax_impl(ExecContext* ctx, MemRef<T, N> x, const int32_t* lens,
   p.type = elem_type_of<T>();
   p.log_softmax = at->get_bool("log", false) ? 1 : 0;
   const char* detail = nullptr;
-  report(ctx, softmax_launch(p, stream_of(ctx), &detail), "softmax", detail);
+  const cudaError_t launch_st = softmax_launch(p, stream_of(ctx), &detail);
+  report(ctx, launch_st, "softmax", detail);
   return result;
 }
 

@@ -125,9 +125,9 @@ enum { DISC_B200_F32 = 0, DISC_B200_F16 = 1 };
  * The reference's ral_pdll_qgemm (quantized_gpu_kernel_impl.cc:328-422) is
  * { fold_out_scale = 1, act = NONE, out = I8, bias F32 or I8 }.
  * splitk_ws: device scratch of at least disc_b200_qgemm_scratch_bytes(M, N, K)
- * bytes, needed when M <= 128 takes the small-M path; only its first
- * ceil(N / 128) int32 words must be zero before the first use and they are
- * left zero; launches that share it must not overlap on the GPU. */
+ * bytes, needed when M <= 128 takes the small-M path; its first 16 KiB (the
+ * arrival counters of the split-K reduction) must be zero before the first use
+ * and are left zero; launches that share it must not overlap on the GPU. */
 typedef struct disc_b200_qgemm_args {
   const int8_t* a;
   const int8_t* w;
