@@ -73,14 +73,53 @@ __device__ __forceinline__ float act_apply(float v, int act) {
   return v;
 }
 
+// Per-thread constants of the epilogue.
+struct EpiCtx {
+  float rs;      // row scale (per-token quantization) or 1
+  float so;      // output scale when the result is divided by it
+  float so_inv;  // correctly rounded 1 / so
+  int act;
+  bool has_rs;
+  bool div_out;
+  bool div_fast;  // so is in the range where the reciprocal sequence below is safe
+};
+
+__device__ __forceinline__ EpiCtx make_epi_ctx(const EpiParams& e) {
+  EpiCtx c;
+  c.rs = 1.f;
+  c.has_rs = e.x_kind == kScalePerRow;
+  c.act = e.act;
+  c.div_out = e.div_out != 0;
+  c.so = c.div_out ? __ldg(e.out_scale) : 1.f;
+  c.so_inv = __frcp_rn(c.so);
+  const float a = fabsf(c.so);
+  c.div_fast = a > 1e-15f && a < 1e15f;
+  return c;
+}
+
+// v / so, correctly rounded wherever it decides the int8 result.  One IEEE
+// division per output is the most expensive instruction sequence of the whole
+// epilogue, so the quotient is first formed from the (correctly rounded)
+// reciprocal with one residual correction: q0 = v * r, q = q0 + (v - q0 * so) * r.
+// That is within one ulp of the true quotient; only a quotient that close to a
+// rounding tie (k + 0.5) could round to a different integer, so those rare
+// values alone are recomputed with the IEEE division the reference uses.
+__device__ __forceinline__ float div_out_scale(float v, const EpiCtx& c) {
+  if (!c.div_fast) return __fdiv_rn(v, c.so);
+  const float q0 = v * c.so_inv;
+  float q = __fmaf_rn(__fmaf_rn(-q0, c.so, v), c.so_inv, q0);
+  const float frac = fabsf(q - rintf(q));
+  if (fabsf(frac - 0.5f) < 1e-3f && fabsf(q) < 256.f) q = __fdiv_rn(v, c.so);
+  return q;
+}
+
 // acc -> real value, shared by every path.
-__device__ __forceinline__ float epi_value(int32_t acc, float rs, bool has_rs, float cs, float cb,
-                                           int act, bool div_out, float so) {
+__device__ __forceinline__ float epi_value(int32_t acc, float cs, float cb, const EpiCtx& c) {
   float t = __int2float_rn(acc);
-  if (has_rs) t = __fmul_rn(t, rs);
+  if (c.has_rs) t = __fmul_rn(t, c.rs);
   float v = __fmaf_rn(t, cs, cb);
-  v = act_apply(v, act);
-  if (div_out) v = __fdiv_rn(v, so);
+  v = act_apply(v, c.act);
+  if (c.div_out) v = div_out_scale(v, c);
   return v;
 }
 
@@ -109,31 +148,29 @@ __device__ __forceinline__ void store_one<int32_t>(int32_t* p, float, int32_t ac
   *p = acc;
 }
 
-// Stores 32 consecutive outputs of one row with 16-byte stores.
+// Stores 16 consecutive outputs of one row with 16-byte stores.
 template <typename OutT>
-__device__ __forceinline__ void store_row32_vec(OutT* p, const float* v, const uint32_t* acc);
+__device__ __forceinline__ void store_row16_vec(OutT* p, const float* v, const uint32_t* acc);
 template <>
-__device__ __forceinline__ void store_row32_vec<int8_t>(int8_t* p, const float* v,
+__device__ __forceinline__ void store_row16_vec<int8_t>(int8_t* p, const float* v,
                                                         const uint32_t*) {
-  uint32_t w[8];
+  uint32_t w[4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < 4; ++i) {
     uint32_t b0 = static_cast<uint8_t>(to_s8(v[4 * i + 0]));
     uint32_t b1 = static_cast<uint8_t>(to_s8(v[4 * i + 1]));
     uint32_t b2 = static_cast<uint8_t>(to_s8(v[4 * i + 2]));
     uint32_t b3 = static_cast<uint8_t>(to_s8(v[4 * i + 3]));
     w[i] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
   }
-  uint4* q = reinterpret_cast<uint4*>(p);
-  q[0] = make_uint4(w[0], w[1], w[2], w[3]);
-  q[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 template <>
-__device__ __forceinline__ void store_row32_vec<__half>(__half* p, const float* v,
+__device__ __forceinline__ void store_row16_vec<__half>(__half* p, const float* v,
                                                         const uint32_t*) {
   uint4* q = reinterpret_cast<uint4*>(p);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < 2; ++i) {
     __half2 h0 = __floats2half2_rn(v[8 * i + 0], v[8 * i + 1]);
     __half2 h1 = __floats2half2_rn(v[8 * i + 2], v[8 * i + 3]);
     __half2 h2 = __floats2half2_rn(v[8 * i + 4], v[8 * i + 5]);
@@ -143,24 +180,32 @@ __device__ __forceinline__ void store_row32_vec<__half>(__half* p, const float* 
   }
 }
 template <>
-__device__ __forceinline__ void store_row32_vec<float>(float* p, const float* v, const uint32_t*) {
+__device__ __forceinline__ void store_row16_vec<float>(float* p, const float* v, const uint32_t*) {
   float4* q = reinterpret_cast<float4*>(p);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) q[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  for (int i = 0; i < 4; ++i) q[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
 }
 template <>
-__device__ __forceinline__ void store_row32_vec<int32_t>(int32_t* p, const float*,
+__device__ __forceinline__ void store_row16_vec<int32_t>(int32_t* p, const float*,
                                                          const uint32_t* acc) {
   uint4* q = reinterpret_cast<uint4*>(p);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) q[i] = make_uint4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+  for (int i = 0; i < 4; ++i) q[i] = make_uint4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
 }
 
 // ------------------------------------------------------------------ tiled
 constexpr int kTileM = 128;        // MMA M, rows of the 128-row operand tile
 constexpr int kTileKBytes = 128;   // one 128-byte swizzle row of int8 = 128 k
 constexpr int kMmaK = 32;          // k per tcgen05.mma kind::i8
-constexpr int kThreads = 192;      // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+// Tiled kernel: warps [0, 16) run the epilogue, four per TMEM lane quadrant
+// (a warp may only read the quadrant warp_id % 4), each owning a quarter of the
+// tile's columns; warp 16 issues TMA, warp 17 owns TMEM and issues the MMAs.
+// Four epilogue warps per scheduler hide the latency of the conversion /
+// activation / division chain, which one warp per scheduler could not.
+constexpr int kEpiWarps = 16;
+constexpr int kEpiGroups = kEpiWarps / 4;
+constexpr int kTiledThreads = (kEpiWarps + 2) * 32;
+constexpr int kThreads = 192;      // small-M kernel: warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
 
 template <int BN, int STAGES>
 struct TiledSmem {
@@ -171,12 +216,13 @@ struct TiledSmem {
   static constexpr int kNumBars = 2 * STAGES + 4;
   static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;  // tmem slot, abort flag
   static constexpr int kScaleOffset = kMiscOffset + 16;
-  static constexpr int kTotal = kScaleOffset + 4 * 2 * BN * 4;  // per epilogue warp: cs[BN], cb[BN]
+  static constexpr int kColsPerWarp = BN / kEpiGroups;
+  static constexpr int kTotal = kScaleOffset + kEpiWarps * 2 * kColsPerWarp * 4;  // per warp: cs[], cb[]
   static constexpr int kDynamic = kTotal + 1024;  // slack to align the base to 1024
 };
 
 template <int BN, int STAGES, typename OutT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kTiledThreads, 1)
 qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
                    const __grid_constant__ CUtensorMap tmap_w, EpiParams ep, int num_kb, int tiles_m,
                    int tiles_n, int vec_ok) {
@@ -192,13 +238,15 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 4);
-  float* s_scale = reinterpret_cast<float*>(smem + L::kScaleOffset);  // [4 warps][2][BN]
+  float* s_scale = reinterpret_cast<float*>(smem + L::kScaleOffset);  // [warp][2][kColsPerWarp]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   constexpr uint32_t kTmemCols = 2 * BN;  // 128, 256 or 512: a power of two >= 32
+  constexpr int kProducerWarp = kEpiWarps;
+  constexpr int kMmaWarp = kEpiWarps + 1;
 
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == kProducerWarp * 32) {
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_w);
     for (int s = 0; s < STAGES; ++s) {
@@ -207,12 +255,12 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 4);  // one arrival per epilogue warp
+      mbar_init(tempty_bar(b), kEpiWarps);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
     tmem_relinquish();
   }
@@ -223,7 +271,7 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const int num_tiles = tiles_m * tiles_n;
 
-  if (warp == 0) {
+  if (warp == kProducerWarp) {
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
@@ -246,7 +294,7 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == kMmaWarp) {
     if (lane == 0) {
       constexpr uint32_t idesc = make_i8_idesc(kTileM, BN);
       int stage = 0;
@@ -284,27 +332,26 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
   } else {
-    // Epilogue warps 2..5.  A warp may only touch the TMEM lane quadrant
-    // (warp id mod 4), which is also the 32-row slice of the tile it owns.
-    // Each warp keeps its own copy of the tile's column scale / bias so that
-    // the epilogue warps never wait on one another.
+    // Epilogue warp: TMEM lane quadrant q = 32-row slice of the tile, column
+    // group g = a quarter of the tile's columns.  Each warp keeps its own copy
+    // of its columns' scale / bias, so epilogue warps never wait on one another.
+    constexpr int CW = L::kColsPerWarp;
     const int q = warp & 3;
-    float* cs = s_scale + q * 2 * BN;
-    float* cb = cs + BN;
+    const int g = warp >> 2;
+    float* cs = s_scale + warp * 2 * CW;
+    float* cb = cs + CW;
     int acc_buf = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    const bool has_rs = ep.x_kind == kScalePerRow;
-    const bool div_out = ep.div_out != 0;
-    float so = 1.f;
-    if (div_out) so = __ldg(ep.out_scale);
+    EpiCtx ctx = make_epi_ctx(ep);
     OutT* out = reinterpret_cast<OutT*>(ep.out);
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int m_blk = tile / tiles_n;
       const int n_blk = tile % tiles_n;
+      const int64_t col0 = static_cast<int64_t>(n_blk) * BN + g * CW;  // first column of this warp
       __syncwarp();
-      for (int j = lane; j < BN; j += 32) {
-        const int64_t n = static_cast<int64_t>(n_blk) * BN + j;
+      for (int j = lane; j < CW; j += 32) {
+        const int64_t n = col0 + j;
         cs[j] = n < ep.N ? col_scale(ep, n) : 0.f;
         cb[j] = n < ep.N ? col_bias(ep, n) : 0.f;
       }
@@ -315,29 +362,28 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_after();
       const int64_t m = static_cast<int64_t>(m_blk) * kTileM + q * 32 + lane;
       const bool row_ok = m < ep.M;
-      float rs = 1.f;
-      if (has_rs && row_ok) rs = __ldg(ep.x_scale + m);
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc_buf * BN;
+      if (ctx.has_rs) ctx.rs = row_ok ? __ldg(ep.x_scale + m) : 1.f;
+      const uint32_t t_row =
+          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc_buf * BN + g * CW;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int64_t n0 = static_cast<int64_t>(n_blk) * BN + c * 32;
-        if (n0 >= ep.N) break;  // uniform across the CTA
-        uint32_t r[32];
-        tmem_ld_x32(t_row + c * 32, r);
+      for (int c = 0; c < CW / 16; ++c) {
+        const int64_t n0 = col0 + c * 16;
+        if (n0 >= ep.N) break;  // uniform across the warp
+        uint32_t r[16];
+        tmem_ld_x16(t_row + c * 16, r);
         tmem_ld_wait();
         if (row_ok) {
-          float v[32];
+          float v[16];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            v[j] = epi_value(static_cast<int32_t>(r[j]), rs, has_rs, cs[c * 32 + j], cb[c * 32 + j],
-                             ep.act, div_out, so);
+          for (int j = 0; j < 16; ++j) {
+            v[j] = epi_value(static_cast<int32_t>(r[j]), cs[c * 16 + j], cb[c * 16 + j], ctx);
           }
           OutT* dst = out + m * ep.ldo + n0;
-          if (vec_ok && n0 + 32 <= ep.N) {
-            store_row32_vec<OutT>(dst, v, r);
+          if (vec_ok && n0 + 16 <= ep.N) {
+            store_row16_vec<OutT>(dst, v, r);
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
+            for (int j = 0; j < 16; ++j) {
               if (n0 + j < ep.N) store_one<OutT>(dst + j, v[j], static_cast<int32_t>(r[j]));
             }
           }
@@ -360,7 +406,7 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -478,17 +524,15 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int64_t n = static_cast<int64_t>(n_blk) * kTileM + q * 32 + lane;  // this thread's channel
     const bool n_ok = n < ep.N;
     const int64_t n_pad = static_cast<int64_t>(gridDim.x) * kTileM;
-    const bool has_rs = ep.x_kind == kScalePerRow;
-    const bool div_out = ep.div_out != 0;
-    const float so = div_out ? __ldg(ep.out_scale) : 1.f;
+    EpiCtx ctx = make_epi_ctx(ep);
     const float cs = n_ok ? col_scale(ep, n) : 0.f;
     const float cb = n_ok ? col_bias(ep, n) : 0.f;
     OutT* out = reinterpret_cast<OutT*>(ep.out);
     const int Mrows = static_cast<int>(ep.M);
 
     auto emit = [&](int m, int32_t acc) {
-      const float rs = has_rs ? __ldg(ep.x_scale + m) : 1.f;
-      const float v = epi_value(acc, rs, has_rs, cs, cb, ep.act, div_out, so);
+      if (ctx.has_rs) ctx.rs = __ldg(ep.x_scale + m);
+      const float v = epi_value(acc, cs, cb, ctx);
       store_one<OutT>(out + static_cast<int64_t>(m) * ep.ldo + n, v, acc);
     };
 
@@ -577,11 +621,9 @@ __global__ void qgemm_simt_kernel(const int8_t* __restrict__ a, const int8_t* __
   const int8_t* wr = w + n * ldw;
   int32_t acc = 0;
   for (int64_t k = 0; k < K; ++k) acc += static_cast<int32_t>(ar[k]) * static_cast<int32_t>(wr[k]);
-  const bool has_rs = ep.x_kind == kScalePerRow;
-  const float rs = has_rs ? ep.x_scale[m] : 1.f;
-  const bool div_out = ep.div_out != 0;
-  const float so = div_out ? ep.out_scale[0] : 1.f;
-  const float v = epi_value(acc, rs, has_rs, col_scale(ep, n), col_bias(ep, n), ep.act, div_out, so);
+  EpiCtx ctx = make_epi_ctx(ep);
+  if (ctx.has_rs) ctx.rs = ep.x_scale[m];
+  const float v = epi_value(acc, col_scale(ep, n), col_bias(ep, n), ctx);
   store_one<OutT>(reinterpret_cast<OutT*>(ep.out) + m * ep.ldo + n, v, acc);
 }
 
@@ -691,7 +733,7 @@ cudaError_t launch_tiled_t(const QGemmParams& p, cudaStream_t stream, const char
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
   const int eb = out_elem_bytes(p.out_dtype);
   const int vec_ok = ((p.ldo * eb) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
-  kern<<<grid, kThreads, L::kDynamic, stream>>>(ta, tw, make_epi(p), num_kb, tiles_m, tiles_n, vec_ok);
+  kern<<<grid, kTiledThreads, L::kDynamic, stream>>>(ta, tw, make_epi(p), num_kb, tiles_m, tiles_n, vec_ok);
   return cudaGetLastError();
 }
 
