@@ -115,6 +115,19 @@ int32_t disc_b200_qgemm(const disc_b200_qgemm_args* args, void* stream) {
   return finish(st, "qgemm", detail);
 }
 
+int32_t disc_b200_qgemm_small_m_noalloc(const disc_b200_qgemm_args* args, void* stream) {
+  if (!args) {
+    g_last_error = "no-alloc small-M qgemm: null args";
+    return 1;
+  }
+  const char* detail = nullptr;
+  const cudaError_t st =
+      disc_b200::qgemm_small_m_noalloc_launch(to_params(args), static_cast<cudaStream_t>(stream), &detail);
+  return finish(st, "qgemm_small_m_noalloc", detail);
+}
+
+int64_t disc_b200_qgemm_small_m_noalloc_capacity(void) { return disc_b200::qgemm_small_m_noalloc_capacity(); }
+
 int64_t disc_b200_qgemm_scratch_bytes(int64_t M, int64_t N, int64_t K) {
   return disc_b200::qgemm_splitk_ws_bytes(M, N, K);
 }

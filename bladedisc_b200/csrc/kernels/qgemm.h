@@ -56,6 +56,13 @@ int64_t qgemm_splitk_ws_bytes(int64_t M, int64_t N, int64_t K);
 // null) receives a static description for argument errors.
 cudaError_t qgemm_launch(const QGemmParams& p, cudaStream_t stream, const char** err);
 
+// Small-M path with the split-K scratch taken from an array built into the
+// library instead of from the caller (p.splitk_ws is ignored).  Allocates
+// nothing; rejects M > 128, TMA-unfriendly shapes and problems whose partial
+// sums exceed qgemm_small_m_noalloc_capacity() bytes.
+cudaError_t qgemm_small_m_noalloc_launch(const QGemmParams& p, cudaStream_t stream, const char** err);
+int64_t qgemm_small_m_noalloc_capacity();
+
 // Which path kPathAuto resolves to (exposed for tests and the bench).
 int qgemm_choose_path(const QGemmParams& p);
 

@@ -852,6 +852,101 @@ cudaError_t qgemm_launch(const QGemmParams& p, cudaStream_t stream, const char**
   }
 }
 
+// ------------------------------------------------ small-M without allocation
+// Some hosts of this library cannot give the small-M path its split-K scratch:
+// code running while a CUDA graph is being captured, a serving loop that has
+// handed the whole device heap to its own pool, a callback on a thread where
+// cudaMalloc would serialise against the rest of the process.  For them the
+// scratch lives here, in the library's own image: every GPU that loads the
+// library carries these bytes until the process exits.
+constexpr int64_t kStaticScratchBytes = 8ll << 20;
+static __device__ __align__(256) unsigned char g_static_splitk_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxDevices] = {};
+
+// Device address of the array for the current device.  In host code the
+// array's name is only a handle for the runtime, never a device pointer, so the
+// address is asked for once per device (with that device current) and cached.
+cudaError_t static_scratch_address(void** out, const char** err) {
+  int dev = -1;
+  cudaError_t st = cudaGetDevice(&dev);
+  if (st != cudaSuccess) return st;
+  if (dev < 0 || dev >= kMaxDevices) {
+    if (err) *err = "no-alloc small-M qgemm: device ordinal out of range";
+    return cudaErrorInvalidDevice;
+  }
+  std::lock_guard<std::mutex> l(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    st = cudaGetSymbolAddress(&p, g_static_splitk_scratch);
+    if (st != cudaSuccess) {
+      if (err) *err = "no-alloc small-M qgemm: cudaGetSymbolAddress failed";
+      return st;
+    }
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return cudaSuccess;
+}
+}  // namespace
+
+int64_t qgemm_small_m_noalloc_capacity() { return kStaticScratchBytes; }
+
+cudaError_t qgemm_small_m_noalloc_launch(const QGemmParams& in, cudaStream_t stream, const char** err) {
+  if (err) *err = nullptr;
+  if (in.M <= 0 || in.N <= 0) return cudaSuccess;
+  if (in.K <= 0 || !in.a || !in.w || !in.out) {
+    if (err) *err = "no-alloc small-M qgemm: null operand or K <= 0";
+    return cudaErrorInvalidValue;
+  }
+  if (in.M > 128) {
+    if (err) *err = "no-alloc small-M qgemm: more than 128 activation rows";
+    return cudaErrorInvalidValue;
+  }
+  if (in.N > 0x7fffffff || in.K > 0x7fffffff) {
+    if (err) *err = "no-alloc small-M qgemm: extent exceeds 2^31-1";
+    return cudaErrorInvalidValue;
+  }
+  if (!tma_ok(in)) {
+    if (err) *err = "no-alloc small-M qgemm: K and the row strides must be multiples of 16, bases 16-byte aligned";
+    return cudaErrorInvalidValue;
+  }
+  if ((in.fold_out_scale || in.div_out_scale) && !in.out_scale) {
+    if (err) *err = "no-alloc small-M qgemm: out_scale required";
+    return cudaErrorInvalidValue;
+  }
+  QGemmParams p = in;
+  p.path = kPathSmallM;
+  const int split = small_split(p);
+  const int64_t tiles_n = (p.N + kTileM - 1) / kTileM;
+  const int64_t need = (static_cast<int64_t>(split) * p.M * tiles_n * kTileM + kSplitCounterWords) * 4;
+  if (split > 1 && (need > kStaticScratchBytes || tiles_n > kSplitCounterWords)) {
+    if (err) *err = "no-alloc small-M qgemm: problem needs more than the 8 MiB built-in scratch";
+    return cudaErrorInvalidValue;
+  }
+  void* scratch = nullptr;
+  cudaError_t st = static_scratch_address(&scratch, err);
+  if (st != cudaSuccess) return st;
+  // The arrival counters must start at zero; an earlier launch that was cut
+  // short could have left them otherwise.  Stream-ordered, no allocation.
+  st = cudaMemsetAsync(scratch, 0, kSplitCounterWords * sizeof(int32_t), stream);
+  if (st != cudaSuccess) return st;
+  p.splitk_ws = static_cast<int32_t*>(scratch);
+  p.splitk_ws_bytes = kStaticScratchBytes;
+  switch (p.out_dtype) {
+    case kOutI8: return launch_smallm<int8_t>(p, stream, err);
+    case kOutF16: return launch_smallm<__half>(p, stream, err);
+    case kOutF32: return launch_smallm<float>(p, stream, err);
+    case kOutI32: return launch_smallm<int32_t>(p, stream, err);
+    default:
+      if (err) *err = "no-alloc small-M qgemm: unknown out_dtype";
+      return cudaErrorInvalidValue;
+  }
+}
+
 int kernel_status_fetch_and_clear() {
   int h = 0;
   if (cudaDeviceSynchronize() != cudaSuccess) return -1;

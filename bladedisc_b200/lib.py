@@ -79,6 +79,8 @@ SIGNATURES = {
     "disc_b200_registry_has": (c_int32, [c_char_p]),
     "disc_b200_qgemm": (c_int32, [POINTER(QGemmArgs), c_void_p]),
     "disc_b200_qgemm_scratch_bytes": (c_int64, [c_int64, c_int64, c_int64]),
+    "disc_b200_qgemm_small_m_noalloc": (c_int32, [POINTER(QGemmArgs), c_void_p]),
+    "disc_b200_qgemm_small_m_noalloc_capacity": (c_int64, []),
     "disc_b200_qgemm_path": (c_int32, [POINTER(QGemmArgs)]),
     "disc_b200_quantize": (c_int32, [c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_void_p,
                                      c_int64, c_int64, c_int32, c_int32, c_void_p]),

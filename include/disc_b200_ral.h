@@ -151,6 +151,29 @@ int64_t disc_b200_qgemm_scratch_bytes(int64_t M, int64_t N, int64_t K);
 /* Path (DISC_B200_PATH_*) the launch would take. */
 int32_t disc_b200_qgemm_path(const disc_b200_qgemm_args* args);
 
+/* The small-M path (M <= 128) of disc_b200_qgemm for callers that cannot
+ * allocate device memory at the point of the call and so have no scratch to
+ * pass: code that runs while a stream is being captured, servers that gave
+ * the whole device heap to their own pool, threads on which a cudaMalloc
+ * would stall the rest of the process.  This entry point has no counterpart
+ * in the reference.  It allocates nothing (no cudaMalloc / cudaFree, no
+ * allocating library routine): the split-K scratch is an 8 MiB array built
+ * into the library, resident on every GPU that loads it until the process
+ * exits.  `splitk_ws` / `splitk_ws_bytes` / `path` of `args` are ignored; the
+ * caller still provides inputs and outputs.
+ *   - Limits: M <= 128, K and row strides multiples of 16 with 16-byte aligned
+ *     bases (the TMA rules), and split * M * round_up(N, 128) * 4 + 16 KiB must
+ *     fit the array (disc_b200_qgemm_small_m_noalloc_capacity() bytes);
+ *     anything else is refused with a message, never silently redirected.
+ *   - The first call on each device looks up the array's device address; make
+ *     that first call before starting any stream capture.
+ *   - All calls on a device share the one array, which keeps what the previous
+ *     call left; the part that must start at zero is cleared on the stream by
+ *     every call.  Two calls that overlap on the GPU (different streams, no
+ *     ordering between them) race on it: order them. */
+int32_t disc_b200_qgemm_small_m_noalloc(const disc_b200_qgemm_args* args, void* stream);
+int64_t disc_b200_qgemm_small_m_noalloc_capacity(void);
+
 /* q = clamp(rne(x / scale + zero_point), qmin, qmax): the arithmetic of
  * QuantizeOpConverter with RoundHalfToEven
  * (tao_compiler/mlir/disc/transforms/disc_lower_quantize_and_dequantize.cc:36-97).
