@@ -1,0 +1,296 @@
+// Included by qgemm_sm100.cu inside its anonymous namespace.
+//
+// qgemm_pair_kernel: the large-M path.  Two CTAs on neighbouring SMs (a
+// cluster of 2, tcgen05 cta_group::2) compute one 256 x 256 output tile: CTA r
+// of the pair owns rows [128 r, 128 r + 128) of the tile (its TMEM holds that
+// half of the accumulator) and supplies half of the weight rows, so each CTA
+// moves 32 KB per 128-byte K step for 128 x 256 x 128 multiply-adds, a third
+// less L2 traffic per operation than two independent 128 x 256 tiles.  The
+// leader CTA (rank 0) issues every MMA; mbarriers that both CTAs wait on are
+// completed in both by tcgen05.commit with a CTA mask.  Loads are plain TMA
+// tiles into the issuing CTA's own shared memory (no multicast).
+//
+// The epilogue leaves through shared memory: each epilogue warp stages a
+// 32-row x 64-byte piece of the output (swizzled, conflict-free) and one lane
+// hands it to a TMA store, which writes full 32-byte sectors and clips at the
+// tensor edge; per-lane scattered 16-byte stores, one row per lane, were the
+// bottleneck of the single-CTA kernel for short K.
+
+constexpr int kPairStages = 5;
+constexpr int kPairStageBytes = 2 * kTileM * kTileKBytes;  // A half + W half, 32 KB
+constexpr int kPairBN = 256;
+constexpr int kPairColsPerWarp = kPairBN / kEpiGroups;     // 64
+constexpr int kPairStagingBytes = 32 * 64;                 // per epilogue warp: 32 rows x 64 B
+
+struct PairSmem {
+  static constexpr int kBarOffset = kPairStages * kPairStageBytes;
+  static constexpr int kNumBars = 2 * kPairStages + 4;
+  static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
+  static constexpr int kScaleOffset = kMiscOffset + 16;
+  static constexpr int kStagingOffset = ((kScaleOffset + kEpiWarps * 2 * kPairColsPerWarp * 4) + 1023) & ~1023;
+  static constexpr int kTotal = kStagingOffset + kEpiWarps * kPairStagingBytes;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
+template <typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTiledThreads, 1)
+qgemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                  const __grid_constant__ CUtensorMap tmap_w,
+                  const __grid_constant__ CUtensorMap tmap_out, EpiParams ep, int num_kb, int tiles_m,
+                  int tiles_n, int use_tma_store, int vec_ok) {
+  using L = PairSmem;
+  constexpr int STAGES = kPairStages;
+  constexpr int BN = kPairBN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::kBarOffset;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 4);
+  float* s_scale = reinterpret_cast<float*>(smem + L::kScaleOffset);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  constexpr uint32_t kTmemCols = 2 * BN;
+  constexpr int kProducerWarp = kEpiWarps;
+  constexpr int kMmaWarp = kEpiWarps + 1;
+
+  if (threadIdx.x == kProducerWarp * 32) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_out);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);   // the leader's own arrive; bytes of both CTAs are counted on it
+      mbar_init(empty_bar(s), 1);  // one commit per use, delivered to both CTAs
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 2 * kEpiWarps);  // leader's copy is the one waited on: both CTAs' epilogue warps
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything is sent to them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = tiles_m * tiles_n;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  if (warp == kProducerWarp) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const int m_blk = tile / tiles_n;
+        const int n_blk = tile % tiles_n;
+        const int a_row = m_blk * 2 * kTileM + static_cast<int>(rank) * kTileM;
+        const int w_row = n_blk * BN + static_cast<int>(rank) * kTileM;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, &g_kernel_status,
+                         kStatusTimeoutEmpty);
+          if (!ok) break;
+          if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * kPairStageBytes);
+          const uint32_t a_dst = smem_base + stage * kPairStageBytes;
+          tma_load_2d_pair(a_dst, &tmap_a, full_bar(stage), kb * kTileKBytes, a_row);
+          tma_load_2d_pair(a_dst + kTileM * kTileKBytes, &tmap_w, full_bar(stage), kb * kTileKBytes,
+                           w_row);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_i8_idesc(2 * kTileM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc_buf = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        ok = mbar_wait(tempty_bar(acc_buf), acc_phase ^ 1, abort_flag, &g_kernel_status,
+                       kStatusTimeoutTmemEmpty);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc_buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(full_bar(stage), phase, abort_flag, &g_kernel_status, kStatusTimeoutFull);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * kPairStageBytes;
+          const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
+          const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + kTileM * kTileKBytes);
+#pragma unroll
+          for (int k = 0; k < kTileKBytes / kMmaK; ++k) {
+            umma_i8_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(empty_bar(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(tfull_bar(acc_buf));
+        acc_buf ^= 1;
+        if (acc_buf == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    constexpr int CW = kPairColsPerWarp;
+    constexpr int EB = static_cast<int>(sizeof(OutT));
+    constexpr int SUB_COLS = 64 / EB;     // columns in one 64-byte staging row
+    constexpr int SUBS = CW / SUB_COLS;   // staging rounds per tile and warp
+    constexpr int LOADS = SUB_COLS / 16;  // 16-column TMEM loads per round
+    const int q = warp & 3;
+    const int g = warp >> 2;
+    float* cs = s_scale + warp * 2 * CW;
+    float* cb = cs + CW;
+    uint8_t* stg = smem + L::kStagingOffset + warp * kPairStagingBytes;
+    const uint32_t stg_addr = smem_u32(stg);
+    const uint32_t tempty_leader0 = map_to_cta(tempty_bar(0), 0);
+    const uint32_t tempty_leader1 = map_to_cta(tempty_bar(1), 0);
+    int acc_buf = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    EpiCtx ctx = make_epi_ctx(ep);
+    OutT* out = reinterpret_cast<OutT*>(ep.out);
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      const int m_blk = tile / tiles_n;
+      const int n_blk = tile % tiles_n;
+      const int64_t col0 = static_cast<int64_t>(n_blk) * BN + g * CW;
+      __syncwarp();
+      for (int j = lane; j < CW; j += 32) {
+        const int64_t n = col0 + j;
+        cs[j] = n < ep.N ? col_scale(ep, n) : 0.f;
+        cb[j] = n < ep.N ? col_bias(ep, n) : 0.f;
+      }
+      __syncwarp();
+      ok = mbar_wait(tfull_bar(acc_buf), acc_phase, abort_flag, &g_kernel_status,
+                     kStatusTimeoutTmemFull);
+      if (!ok) break;
+      tc_fence_after();
+      const int64_t row0 = static_cast<int64_t>(m_blk) * 2 * kTileM + rank * kTileM + q * 32;
+      const int64_t m = row0 + lane;
+      const bool row_ok = m < ep.M;
+      if (ctx.has_rs) ctx.rs = row_ok ? __ldg(ep.x_scale + m) : 1.f;
+      const uint32_t t_row =
+          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc_buf * BN + g * CW;
+#pragma unroll 1
+      for (int sub = 0; sub < SUBS; ++sub) {
+        const int64_t n_sub = col0 + sub * SUB_COLS;
+        if (n_sub >= ep.N || row0 >= ep.M) break;  // uniform across the warp
+        if (use_tma_store) {
+          // the previous round's store must have read the staging buffer
+          if (lane == 0) tma_store_wait_read();
+          __syncwarp();
+        }
+#pragma unroll
+        for (int ld = 0; ld < LOADS; ++ld) {
+          uint32_t r[16];
+          tmem_ld_x16(t_row + sub * SUB_COLS + ld * 16, r);
+          tmem_ld_wait();
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int c = sub * SUB_COLS + ld * 16 + j;
+            v[j] = epi_value(static_cast<int32_t>(r[j]), cs[c], cb[c], ctx);
+          }
+          if (use_tma_store) {
+            // 16 values = 16 * EB bytes = EB chunks of 16 bytes; chunk index inside
+            // the 64-byte row is xor-ed with ((row >> 1) & 3): the 64-byte TMA swizzle.
+            uint32_t w[4 * EB];
+            if constexpr (EB == 1) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                w[i] = static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i]))) |
+                       (static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i + 1]))) << 8) |
+                       (static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i + 2]))) << 16) |
+                       (static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i + 3]))) << 24);
+              }
+            } else if constexpr (EB == 2) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<uint32_t*>(&h);
+              }
+            } else if constexpr (std::is_same_v<OutT, float>) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) w[i] = __float_as_uint(v[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) w[i] = r[i];
+            }
+#pragma unroll
+            for (int ch = 0; ch < EB; ++ch) {
+              const int chunk = ld * EB + ch;  // 0..3 inside the 64-byte row
+              const uint32_t off = lane * 64 + ((chunk ^ ((lane >> 1) & 3)) << 4);
+              *reinterpret_cast<uint4*>(stg + off) =
+                  make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
+            }
+          } else if (row_ok) {
+            const int64_t n0 = n_sub + ld * 16;
+            OutT* dst = out + m * ep.ldo + n0;
+            if (vec_ok && n0 + 16 <= ep.N) {
+              store_row16_vec<OutT>(dst, v, r);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (n0 + j < ep.N) store_one<OutT>(dst + j, v[j], static_cast<int32_t>(r[j]));
+              }
+            }
+          }
+        }
+        if (use_tma_store) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_out, stg_addr, static_cast<int>(n_sub * EB), static_cast<int>(row0));
+            tma_store_commit();
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(tempty_bar(acc_buf));
+        else mbar_arrive_remote(acc_buf == 0 ? tempty_leader0 : tempty_leader1);
+      }
+      acc_buf ^= 1;
+      if (acc_buf == 0) acc_phase ^= 1;
+    }
+    if (use_tma_store && lane == 0) tma_store_wait_all();
+  }
+
+  // Wind-down: nothing may leave while the other CTA can still touch its
+  // shared memory or barriers, so both CTAs meet before TMEM is released.
+  __syncwarp();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}

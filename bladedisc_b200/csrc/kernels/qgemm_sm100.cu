@@ -24,6 +24,7 @@
 #include <cuda_runtime.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "qgemm.h"
 #include "sm100_ptx.cuh"
@@ -412,6 +413,8 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
+#include "qgemm_pair.inl"
+
 // ---------------------------------------------------------------- small M
 constexpr int kSmallMaxStages = 8;
 constexpr int kSplitCounterWords = 4096;  // int32 arrival counters at the front of the scratch
@@ -744,6 +747,76 @@ cudaError_t launch_tiled(const QGemmParams& p, cudaStream_t stream, const char**
   return launch_tiled_t<OutT, 128, 6>(p, stream, err);
 }
 
+// Output described in bytes: [M rows, N * elem bytes], box = 32 rows x 64 bytes, 64-byte swizzle.
+bool make_out_tmap(CUtensorMap* tm, void* base, int64_t rows, int64_t row_bytes, int64_t ld_bytes) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_bytes)};
+  cuuint32_t box[2] = {64, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <typename OutT>
+int pair_max_clusters() {
+  static int n = 0;
+  if (n == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * 74);
+    cfg.blockDim = dim3(kTiledThreads);
+    cfg.dynamicSmemBytes = PairSmem::kDynamic;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int c = 0;
+    if (cudaOccupancyMaxActiveClusters(&c, qgemm_pair_kernel<OutT>, &cfg) != cudaSuccess || c <= 0) {
+      (void)cudaGetLastError();
+      c = sm_count() / 2;
+    }
+    n = c;
+  }
+  return n;
+}
+
+template <typename OutT>
+cudaError_t launch_pair(const QGemmParams& p, cudaStream_t stream, const char** err) {
+  CUtensorMap ta, tw, to;
+  if (!make_tmap(&ta, p.a, p.M, p.K, p.lda, kTileM) || !make_tmap(&tw, p.w, p.N, p.K, p.ldw, kTileM)) {
+    if (err) *err = "cuTensorMapEncodeTiled failed";
+    return cudaErrorInvalidValue;
+  }
+  const int eb = out_elem_bytes(p.out_dtype);
+  const bool out_aligned =
+      ((p.ldo * eb) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+  int use_tma_store = out_aligned ? 1 : 0;
+  if (!use_tma_store || !make_out_tmap(&to, p.out, p.M, p.N * eb, p.ldo * eb)) {
+    use_tma_store = 0;
+    to = ta;  // never dereferenced when stores are direct
+  }
+  auto kern = qgemm_pair_kernel<OutT>;
+  cudaError_t st =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kDynamic);
+  if (st != cudaSuccess) return st;
+  const int tiles_m = static_cast<int>((p.M + 2 * kTileM - 1) / (2 * kTileM));
+  const int tiles_n = static_cast<int>((p.N + kPairBN - 1) / kPairBN);
+  const int num_kb = static_cast<int>((p.K + kTileKBytes - 1) / kTileKBytes);
+  const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n;
+  const int max_clusters = pair_max_clusters<OutT>();
+  const int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
+  kern<<<2 * clusters, kTiledThreads, PairSmem::kDynamic, stream>>>(ta, tw, to, make_epi(p), num_kb,
+                                                                   tiles_m, tiles_n, use_tma_store,
+                                                                   out_aligned ? 1 : 0);
+  return cudaGetLastError();
+}
+
 template <typename OutT>
 cudaError_t launch_smallm(const QGemmParams& p, cudaStream_t stream, const char** err) {
   const int MT = small_mt(p.M);
@@ -799,6 +872,7 @@ cudaError_t dispatch(const QGemmParams& p, int path, cudaStream_t stream, const 
   switch (path) {
     case kPathTiled: return launch_tiled<OutT>(p, stream, err);
     case kPathSmallM: return launch_smallm<OutT>(p, stream, err);
+    case kPathPair: return launch_pair<OutT>(p, stream, err);
     default: return launch_simt<OutT>(p, stream, err);
   }
 }
@@ -810,7 +884,12 @@ int qgemm_choose_path(const QGemmParams& p) {
   if (p.path == kPathSimt) return kPathSimt;
   if (p.path == kPathSmallM && p.M <= 128) return kPathSmallM;
   if (p.path == kPathTiled) return kPathTiled;
-  return p.M <= 64 ? kPathSmallM : kPathTiled;
+  if (p.path == kPathPair) return kPathPair;
+  if (p.M <= 64) return kPathSmallM;
+  // CTA pairs compute 256 x 256 tiles: worth it once there are enough of them
+  // to occupy every pair of SMs.
+  const int64_t pair_tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
+  return pair_tiles >= sm_count() / 2 ? kPathPair : kPathTiled;
 }
 
 int64_t qgemm_splitk_ws_bytes(int64_t M, int64_t N, int64_t K) {

@@ -1,0 +1,192 @@
+"""Per-kernel sweep: every (M, K, N) point of the quantized-linear configuration
+and the bandwidth kernels, with achieved TOPS / GB/s and the roofline fraction.
+
+    python -m bladedisc_b200.kernel_bench [--quick] [--json out.json]
+
+Timing: CUDA events on the launching stream around `iters` back-to-back
+launches after 3 warm-ups.  Operand sets rotate through copies whose total
+footprint exceeds the 126 MB L2, so no launch finds its operands cached by
+the previous one.  Peaks come from MEASURED_PEAKS.json when it is present.
+"""
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+from . import ops
+
+ROOT = Path(__file__).resolve().parent.parent
+L2_BYTES = 126 << 20
+MS = [1, 7, 64, 333, 1024, 4096, 16384]
+KNS = [(768, 768), (768, 3072), (3072, 768), (4096, 4096), (4096, 11008)]
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"], 2.0 * d["bf16_tflops"], "measured"
+    return 6650.0, 2.0 * 1590.0, "fallback"
+
+
+def time_ms(fns, iters):
+    """Average ms per launch; `fns` is a list of closures over rotating operand sets.
+
+    The launches are captured into one CUDA graph and replayed, so that the
+    host's per-call overhead (tens of microseconds from Python) does not hide
+    kernels that run for a few microseconds; if capture fails the launches are
+    issued eagerly.
+    """
+    n = len(fns)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(min(3, n) + 2):
+            fns[i % n]()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    graph = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(iters):
+                fns[i % n]()
+        graph.replay()
+        torch.cuda.synchronize()
+    except Exception:
+        graph = None
+        torch.cuda.synchronize()
+    if graph is not None:
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+    e0.record()
+    for i in range(iters):
+        fns[i % n]()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def copies_for(nbytes):
+    return max(2, min(400, (2 * L2_BYTES + nbytes - 1) // max(nbytes, 1)))
+
+
+def bench_qgemm(M, K, N, out_dtype, hbm, tops_peak, iters):
+    dev = "cuda"
+    b_out = 1 if out_dtype == torch.int8 else 2
+    algo_bytes = M * K + N * K + M * N * b_out + 8 * N
+    n_sets = copies_for(algo_bytes)
+    g = torch.Generator(device=dev).manual_seed(M + K + N)
+    sets = []
+    for _ in range(n_sets):
+        a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev, generator=g)
+        w = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev, generator=g)
+        o = torch.empty((M, N), dtype=out_dtype, device=dev)
+        sets.append((a, w, o))
+    sw = torch.rand(N, device=dev, generator=g) * 9e-3 + 1e-3
+    bias = torch.randn(N, device=dev, generator=g) * 0.01
+    sx = torch.tensor([0.02], device=dev)
+    so = torch.tensor([0.05], device=dev) if out_dtype == torch.int8 else None
+    fns = [(lambda a=a, w=w, o=o: ops.qgemm(a, w, x_scale=sx, w_scale=sw, out_scale=so, bias=bias,
+                                            out_dtype=out_dtype, out=o)) for a, w, o in sets]
+    ms = time_ms(fns, iters)
+    tops = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+    gbs = algo_bytes / (ms * 1e-3) / 1e9
+    path = ops.qgemm_path(M, N, K)
+    # the bound that applies: time cannot beat max(ops / tensor peak, bytes / hbm peak)
+    t_tensor = 2.0 * M * N * K / (tops_peak * 1e12)
+    t_hbm = algo_bytes / (hbm * 1e9)
+    bound = "tensor" if t_tensor >= t_hbm else "hbm"
+    frac = max(t_tensor, t_hbm) / (ms * 1e-3)
+    return {"kernel": f"qgemm_{path}", "M": M, "K": K, "N": N, "out": str(out_dtype).split(".")[-1], "us": ms * 1e3,
+            "tops": tops, "gbs": gbs, "bound": bound, "frac": frac, "sets": n_sets}
+
+
+def bench_rows(name, rows, cols, dtype, hbm, iters):
+    dev = "cuda"
+    eb = 2 if dtype == torch.float16 else 4
+    E = rows * cols
+    g = torch.Generator(device=dev).manual_seed(rows + cols)
+    if name == "quantize":
+        algo = eb * E + E
+    elif name == "dynamic_quantize":
+        algo = eb * E + E + 4 * rows
+    elif name == "layernorm":
+        algo = 2 * eb * E + 2 * eb * cols
+    elif name == "add_layernorm_quant":
+        algo = 3 * eb * E + E + 2 * eb * cols
+    elif name == "rmsnorm_dynquant":
+        algo = eb * E + E + 4 * rows + eb * cols
+    elif name == "softmax":
+        algo = 2 * eb * E
+    else:
+        raise ValueError(name)
+    n_sets = copies_for(algo)
+    xs = [torch.randn((rows, cols), device=dev, generator=g).to(dtype) for _ in range(n_sets)]
+    rs = [torch.randn((rows, cols), device=dev, generator=g).to(dtype) for _ in range(n_sets)] \
+        if name == "add_layernorm_quant" else None
+    gamma = torch.ones(cols, dtype=dtype, device=dev)
+    beta = torch.zeros(cols, dtype=dtype, device=dev)
+    s = torch.tensor([0.03], device=dev)
+    if name == "quantize":
+        fns = [(lambda x=x: ops.quantize(x, s)) for x in xs]
+    elif name == "dynamic_quantize":
+        fns = [(lambda x=x: ops.dynamic_quantize(x)) for x in xs]
+    elif name == "layernorm":
+        fns = [(lambda x=x: ops.layernorm(x, gamma, beta)) for x in xs]
+    elif name == "add_layernorm_quant":
+        fns = [(lambda x=x, r=r: ops.layernorm_quant(x, gamma, beta, s, residual=r)) for x, r in zip(xs, rs)]
+    elif name == "rmsnorm_dynquant":
+        fns = [(lambda x=x: ops.rmsnorm_dynamic_quant(x, gamma)) for x in xs]
+    else:
+        fns = [(lambda x=x: ops.softmax(x, scale=0.125)) for x in xs]
+    ms = time_ms(fns, iters)
+    gbs = algo / (ms * 1e-3) / 1e9
+    return {"kernel": name, "rows": rows, "cols": cols, "dtype": str(dtype).split(".")[-1], "us": ms * 1e3,
+            "gbs": gbs, "bound": "hbm", "frac": gbs / hbm, "sets": n_sets,
+            "note": "timing includes torch's allocation of the outputs"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--quick", action="store_true", help="a few points only")
+    ap.add_argument("--json", default=None)
+    args = ap.parse_args()
+    hbm, tops_peak, src = peaks()
+    out = {"peaks": {"hbm_gbs": hbm, "int8_tops": tops_peak, "source": src}, "rows": []}
+    ms_list = [7, 64, 4096] if args.quick else MS
+    kns = [(768, 3072), (4096, 4096)] if args.quick else KNS
+    print(f"# peaks ({src}): HBM {hbm:.0f} GB/s, int8 tensor {tops_peak:.0f} TOPS (2 x bf16)")
+    print(f"{'kernel':<16}{'M':>6}{'K':>6}{'N':>7}{'out':>9}{'us':>10}{'TOPS':>9}{'GB/s':>9}{'bound':>8}{'frac':>7}")
+    for K, N in kns:
+        for M in ms_list:
+            for od in (torch.int8, torch.float16):
+                iters = 200 if M <= 1024 else 30
+                r = bench_qgemm(M, K, N, od, hbm, tops_peak, iters)
+                out["rows"].append(r)
+                print(f"{r['kernel']:<16}{M:>6}{K:>6}{N:>7}{r['out']:>9}{r['us']:>10.2f}{r['tops']:>9.1f}{r['gbs']:>9.0f}"
+                      f"{r['bound']:>8}{r['frac']:>7.2f}", flush=True)
+    row_cases = [("quantize", 16384, 768, torch.float32), ("quantize", 16384, 3072, torch.float16),
+                 ("dynamic_quantize", 16384, 4096, torch.float16), ("layernorm", 16384, 768, torch.float16),
+                 ("add_layernorm_quant", 16384, 768, torch.float16), ("add_layernorm_quant", 32768, 1024, torch.float16),
+                 ("rmsnorm_dynquant", 16384, 4096, torch.float16), ("softmax", 32 * 12 * 512, 512, torch.float16),
+                 ("softmax", 196608, 128, torch.float16)]
+    if args.quick:
+        row_cases = row_cases[:1] + row_cases[3:5] + row_cases[7:8]
+    print(f"{'kernel':<22}{'rows':>8}{'cols':>7}{'dtype':>9}{'us':>10}{'GB/s':>9}{'frac':>7}")
+    for name, rows, cols, dt in row_cases:
+        r = bench_rows(name, rows, cols, dt, hbm, 50)
+        out["rows"].append(r)
+        print(f"{name:<22}{rows:>8}{cols:>7}{r['dtype']:>9}{r['us']:>10.2f}{r['gbs']:>9.0f}{r['frac']:>7.2f}", flush=True)
+    st = ops.kernel_status()
+    print("kernel_status", st)
+    if args.json:
+        Path(args.json).write_text(json.dumps(out, indent=1))
+
+
+if __name__ == "__main__":
+    main()

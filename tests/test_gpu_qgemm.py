@@ -59,6 +59,42 @@ def test_forced_paths_agree(ops, path, M):
     assert (got == c.qgemm_acc(a, w)).all()
 
 
+@pytest.mark.parametrize("M,K,N", [(256, 128, 256), (1, 128, 16), (300, 640, 392), (512, 2064, 520), (1000, 768, 72),
+                                   (2048, 1024, 1024), (777, 144, 264)])
+@pytest.mark.parametrize("out_dtype", [torch.int32, torch.int8, torch.float16, torch.float32])
+def test_cta_pair_path(ops, M, K, N, out_dtype):
+    """The 2-CTA (256 x 256 tile, TMA-store epilogue) kernel, forced on shapes that
+    exercise ragged rows / columns / K tails and both store routes (N = 72 with
+    int8 output is not 16-byte aligned per row, so it leaves by direct stores)."""
+    from oracle import c
+    rng = np.random.default_rng(M + K + N)
+    a, w = _rand_i8(rng, (M, K)), _rand_i8(rng, (N, K))
+    acc = c.qgemm_acc(a, w)
+    if out_dtype == torch.int32:
+        got = ops.qgemm(_dev(a), _dev(w), out_dtype=torch.int32, path="pair").cpu().numpy()
+        assert (got == acc).all()
+        return
+    sw = (rng.random(N) * 9e-3 + 1e-3).astype(np.float32)
+    bias = (rng.standard_normal(N) * 0.5).astype(np.float32)
+    s_x, s_out = np.float32(0.02), np.float32(0.05)
+    kw = dict(x_scale=_dev(np.array([s_x])), w_scale=_dev(sw), bias=_dev(bias), path="pair")
+    if out_dtype == torch.int8:
+        _, want = c.qgemm_epilogue(acc, x_scale=s_x, w_scale=sw, out_scale=s_out, bias=bias, div_out=True)
+        # canary rows around the result: a store that runs past the tensor edge would touch them
+        buf = torch.full((M + 2, N), 99, dtype=torch.int8, device="cuda")
+        ops.qgemm(_dev(a), _dev(w), out_scale=_dev(np.array([s_out])), out=buf[1:M + 1], **kw)
+        assert (buf[1:M + 1].cpu().numpy() == want).all()
+        assert (buf[0] == 99).all() and (buf[M + 1] == 99).all()
+    else:
+        want, _ = c.qgemm_epilogue(acc, x_scale=s_x, w_scale=sw, bias=bias)
+        got = ops.qgemm(_dev(a), _dev(w), out_dtype=out_dtype, **kw).float().cpu().numpy()
+        if out_dtype == torch.float32:
+            assert (got == want).all()
+        else:
+            ok = np.abs(want) < 60000
+            assert np.allclose(got[ok], want[ok], rtol=RTOL, atol=ATOL)
+
+
 @pytest.mark.parametrize("split", [1, 2, 3, 5, 8])
 def test_small_m_split_k_is_exact_and_repeatable(ops, split):
     from oracle import c
