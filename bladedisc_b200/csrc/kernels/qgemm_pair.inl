@@ -32,6 +32,99 @@ struct PairSmem {
   static constexpr int kDynamic = kTotal + 1024;
 };
 
+// One epilogue warp's share of a pair tile: 64 columns of its 32 rows, handed
+// to TMA stores in pieces of 32 rows x 64 bytes (or stored directly when the
+// output rows are not 16-byte aligned).
+template <typename OutT, int ACT, bool DIV, bool RS>
+__device__ __forceinline__ void pair_epilogue_cols(uint32_t t_row, const float* cs, const float* cb,
+                                                   const EpiCtx& ctx, OutT* out, int64_t row0, int lane,
+                                                   int64_t col0, int64_t M, int64_t N, int64_t ldo,
+                                                   uint8_t* stg, uint32_t stg_addr,
+                                                   const CUtensorMap* tmap_out, int use_tma_store,
+                                                   int vec_ok) {
+  constexpr int CW = kPairColsPerWarp;
+  constexpr int EB = static_cast<int>(sizeof(OutT));
+  constexpr int SUB_COLS = 64 / EB;     // columns in one 64-byte staging row
+  constexpr int SUBS = CW / SUB_COLS;   // staging rounds per tile and warp
+  constexpr int LOADS = SUB_COLS / 16;  // 16-column TMEM loads per round
+  const int64_t m = row0 + lane;
+  const bool row_ok = m < M;
+#pragma unroll 1
+      for (int sub = 0; sub < SUBS; ++sub) {
+        const int64_t n_sub = col0 + sub * SUB_COLS;
+        if (n_sub >= N || row0 >= M) break;  // uniform across the warp
+        if (use_tma_store) {
+          // the previous round's store must have read the staging buffer
+          if (lane == 0) tma_store_wait_read();
+          __syncwarp();
+        }
+#pragma unroll 1
+        for (int ld = 0; ld < LOADS; ++ld) {
+          uint32_t r[16];
+          tmem_ld_x16(t_row + sub * SUB_COLS + ld * 16, r);
+          tmem_ld_wait();
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int c = sub * SUB_COLS + ld * 16 + j;
+            v[j] = epi_value_t<ACT, DIV, RS>(static_cast<int32_t>(r[j]), cs[c], cb[c], ctx);
+          }
+          if (use_tma_store) {
+            // 16 values = 16 * EB bytes = EB chunks of 16 bytes; chunk index inside
+            // the 64-byte row is xor-ed with ((row >> 1) & 3): the 64-byte TMA swizzle.
+            uint32_t w[4 * EB];
+            if constexpr (EB == 1) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                w[i] = static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i]))) |
+                       (static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i + 1]))) << 8) |
+                       (static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i + 2]))) << 16) |
+                       (static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i + 3]))) << 24);
+              }
+            } else if constexpr (EB == 2) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<uint32_t*>(&h);
+              }
+            } else if constexpr (std::is_same_v<OutT, float>) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) w[i] = __float_as_uint(v[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) w[i] = r[i];
+            }
+#pragma unroll
+            for (int ch = 0; ch < EB; ++ch) {
+              const int chunk = ld * EB + ch;  // 0..3 inside the 64-byte row
+              const uint32_t off = lane * 64 + ((chunk ^ ((lane >> 1) & 3)) << 4);
+              *reinterpret_cast<uint4*>(stg + off) =
+                  make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
+            }
+          } else if (row_ok) {
+            const int64_t n0 = n_sub + ld * 16;
+            OutT* dst = out + m * ldo + n0;
+            if (vec_ok && n0 + 16 <= N) {
+              store_row16_vec<OutT>(dst, v, r);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (n0 + j < N) store_one<OutT>(dst + j, v[j], static_cast<int32_t>(r[j]));
+              }
+            }
+          }
+        }
+        if (use_tma_store) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(tmap_out, stg_addr, static_cast<int>(n_sub * EB), static_cast<int>(row0));
+            tma_store_commit();
+          }
+        }
+      }
+}
+
 template <typename OutT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTiledThreads, 1)
 qgemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
@@ -155,10 +248,6 @@ qgemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else {
     constexpr int CW = kPairColsPerWarp;
-    constexpr int EB = static_cast<int>(sizeof(OutT));
-    constexpr int SUB_COLS = 64 / EB;     // columns in one 64-byte staging row
-    constexpr int SUBS = CW / SUB_COLS;   // staging rounds per tile and warp
-    constexpr int LOADS = SUB_COLS / 16;  // 16-column TMEM loads per round
     const int q = warp & 3;
     const int g = warp >> 2;
     float* cs = s_scale + warp * 2 * CW;
@@ -188,85 +277,13 @@ qgemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (!ok) break;
       tc_fence_after();
       const int64_t row0 = static_cast<int64_t>(m_blk) * 2 * kTileM + rank * kTileM + q * 32;
-      const int64_t m = row0 + lane;
-      const bool row_ok = m < ep.M;
-      if (ctx.has_rs) ctx.rs = row_ok ? __ldg(ep.x_scale + m) : 1.f;
+      if (ctx.has_rs) ctx.rs = (row0 + lane < ep.M) ? __ldg(ep.x_scale + row0 + lane) : 1.f;
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc_buf * BN + g * CW;
-#pragma unroll 1
-      for (int sub = 0; sub < SUBS; ++sub) {
-        const int64_t n_sub = col0 + sub * SUB_COLS;
-        if (n_sub >= ep.N || row0 >= ep.M) break;  // uniform across the warp
-        if (use_tma_store) {
-          // the previous round's store must have read the staging buffer
-          if (lane == 0) tma_store_wait_read();
-          __syncwarp();
-        }
-#pragma unroll
-        for (int ld = 0; ld < LOADS; ++ld) {
-          uint32_t r[16];
-          tmem_ld_x16(t_row + sub * SUB_COLS + ld * 16, r);
-          tmem_ld_wait();
-          float v[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int c = sub * SUB_COLS + ld * 16 + j;
-            v[j] = epi_value(static_cast<int32_t>(r[j]), cs[c], cb[c], ctx);
-          }
-          if (use_tma_store) {
-            // 16 values = 16 * EB bytes = EB chunks of 16 bytes; chunk index inside
-            // the 64-byte row is xor-ed with ((row >> 1) & 3): the 64-byte TMA swizzle.
-            uint32_t w[4 * EB];
-            if constexpr (EB == 1) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                w[i] = static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i]))) |
-                       (static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i + 1]))) << 8) |
-                       (static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i + 2]))) << 16) |
-                       (static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i + 3]))) << 24);
-              }
-            } else if constexpr (EB == 2) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-                w[i] = *reinterpret_cast<uint32_t*>(&h);
-              }
-            } else if constexpr (std::is_same_v<OutT, float>) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) w[i] = __float_as_uint(v[i]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) w[i] = r[i];
-            }
-#pragma unroll
-            for (int ch = 0; ch < EB; ++ch) {
-              const int chunk = ld * EB + ch;  // 0..3 inside the 64-byte row
-              const uint32_t off = lane * 64 + ((chunk ^ ((lane >> 1) & 3)) << 4);
-              *reinterpret_cast<uint4*>(stg + off) =
-                  make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
-            }
-          } else if (row_ok) {
-            const int64_t n0 = n_sub + ld * 16;
-            OutT* dst = out + m * ep.ldo + n0;
-            if (vec_ok && n0 + 16 <= ep.N) {
-              store_row16_vec<OutT>(dst, v, r);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (n0 + j < ep.N) store_one<OutT>(dst + j, v[j], static_cast<int32_t>(r[j]));
-              }
-            }
-          }
-        }
-        if (use_tma_store) {
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(&tmap_out, stg_addr, static_cast<int>(n_sub * EB), static_cast<int>(row0));
-            tma_store_commit();
-          }
-        }
-      }
+      const int mode = std::is_same_v<OutT, int32_t> ? 0 : epi_mode(ctx);
+      DISC_EPI_SWITCH(mode, (pair_epilogue_cols<OutT, ACT, DIV, RS>(t_row, cs, cb, ctx, out, row0, lane, col0,
+                                                                    ep.M, ep.N, ep.ldo, stg, stg_addr, &tmap_out,
+                                                                    use_tma_store, vec_ok)))
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {

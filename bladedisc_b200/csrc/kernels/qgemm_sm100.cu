@@ -124,6 +124,46 @@ __device__ __forceinline__ float epi_value(int32_t acc, float cs, float cb, cons
   return v;
 }
 
+// The same arithmetic with the mode fixed at compile time.  The tiled kernels
+// run the epilogue of a whole tile inside one case of a switch over the mode,
+// so the instructions a launch actually fetches are a short straight-line
+// loop instead of sixteen unrolled copies of every branch (erf, exp, the
+// division fix-up): with 18 warps in three roles the instruction cache was
+// the first thing to run out.
+template <int ACT, bool DIV, bool RS>
+__device__ __forceinline__ float epi_value_t(int32_t acc, float cs, float cb, const EpiCtx& c) {
+  float t = __int2float_rn(acc);
+  if (RS) t = __fmul_rn(t, c.rs);
+  float v = __fmaf_rn(t, cs, cb);
+  if (ACT == kActGelu) v = 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
+  if (ACT == kActSilu) v = v / (1.f + __expf(-v));
+  if (DIV) v = div_out_scale(v, c);
+  return v;
+}
+
+__device__ __forceinline__ int epi_mode(const EpiCtx& c) {
+  return c.act | (c.div_out ? 4 : 0) | (c.has_rs ? 8 : 0);
+}
+
+// Calls BODY with ACT / DIV / RS bound as compile-time constants for `mode`.
+#define DISC_EPI_CASE(A, D, R, BODY)                 \
+  case ((A) | ((D) ? 4 : 0) | ((R) ? 8 : 0)): {      \
+    constexpr int ACT = (A);                         \
+    constexpr bool DIV = (D);                        \
+    constexpr bool RS = (R);                         \
+    BODY;                                            \
+  } break;
+#define DISC_EPI_SWITCH(mode, BODY)                                                        \
+  switch (mode) {                                                                          \
+    DISC_EPI_CASE(0, false, false, BODY) DISC_EPI_CASE(1, false, false, BODY)              \
+    DISC_EPI_CASE(2, false, false, BODY) DISC_EPI_CASE(0, true, false, BODY)               \
+    DISC_EPI_CASE(1, true, false, BODY) DISC_EPI_CASE(2, true, false, BODY)                \
+    DISC_EPI_CASE(0, false, true, BODY) DISC_EPI_CASE(1, false, true, BODY)                \
+    DISC_EPI_CASE(2, false, true, BODY) DISC_EPI_CASE(0, true, true, BODY)                 \
+    DISC_EPI_CASE(1, true, true, BODY) DISC_EPI_CASE(2, true, true, BODY)                  \
+    default: break;                                                                        \
+  }
+
 __device__ __forceinline__ int8_t to_s8(float v) {
   int r = __float2int_rn(v);
   r = max(-128, min(127, r));
@@ -221,6 +261,39 @@ struct TiledSmem {
   static constexpr int kTotal = kScaleOffset + kEpiWarps * 2 * kColsPerWarp * 4;  // per warp: cs[], cb[]
   static constexpr int kDynamic = kTotal + 1024;  // slack to align the base to 1024
 };
+
+// One epilogue warp's share of a tile: CW columns of its 32 rows, 16 columns
+// per TMEM load, converted and stored straight from registers.
+template <typename OutT, int ACT, bool DIV, bool RS, int CW>
+__device__ __forceinline__ void tiled_epilogue_cols(uint32_t t_row, const float* cs, const float* cb,
+                                                    const EpiCtx& ctx, OutT* out, int64_t m,
+                                                    bool row_ok, int64_t col0, int64_t N,
+                                                    int64_t ldo, int vec_ok) {
+#pragma unroll 1
+  for (int c = 0; c < CW / 16; ++c) {
+    const int64_t n0 = col0 + c * 16;
+    if (n0 >= N) break;  // uniform across the warp
+    uint32_t r[16];
+    tmem_ld_x16(t_row + c * 16, r);
+    tmem_ld_wait();
+    if (row_ok) {
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        v[j] = epi_value_t<ACT, DIV, RS>(static_cast<int32_t>(r[j]), cs[c * 16 + j], cb[c * 16 + j], ctx);
+      }
+      OutT* dst = out + m * ldo + n0;
+      if (vec_ok && n0 + 16 <= N) {
+        store_row16_vec<OutT>(dst, v, r);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (n0 + j < N) store_one<OutT>(dst + j, v[j], static_cast<int32_t>(r[j]));
+        }
+      }
+    }
+  }
+}
 
 template <int BN, int STAGES, typename OutT>
 __global__ void __launch_bounds__(kTiledThreads, 1)
@@ -366,30 +439,9 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (ctx.has_rs) ctx.rs = row_ok ? __ldg(ep.x_scale + m) : 1.f;
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc_buf * BN + g * CW;
-#pragma unroll 1
-      for (int c = 0; c < CW / 16; ++c) {
-        const int64_t n0 = col0 + c * 16;
-        if (n0 >= ep.N) break;  // uniform across the warp
-        uint32_t r[16];
-        tmem_ld_x16(t_row + c * 16, r);
-        tmem_ld_wait();
-        if (row_ok) {
-          float v[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            v[j] = epi_value(static_cast<int32_t>(r[j]), cs[c * 16 + j], cb[c * 16 + j], ctx);
-          }
-          OutT* dst = out + m * ep.ldo + n0;
-          if (vec_ok && n0 + 16 <= ep.N) {
-            store_row16_vec<OutT>(dst, v, r);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (n0 + j < ep.N) store_one<OutT>(dst + j, v[j], static_cast<int32_t>(r[j]));
-            }
-          }
-        }
-      }
+      const int mode = std::is_same_v<OutT, int32_t> ? 0 : epi_mode(ctx);
+      DISC_EPI_SWITCH(mode, (tiled_epilogue_cols<OutT, ACT, DIV, RS, CW>(t_row, cs, cb, ctx, out, m, row_ok,
+                                                                         col0, ep.N, ep.ldo, vec_ok)))
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc_buf));
