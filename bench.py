@@ -50,8 +50,9 @@ def _peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
-        return {"hbm_gbs": d.get("hbm_gbs"), "bf16": d.get("bf16_tflops"), "source": "measured"}
-    return {"hbm_gbs": 6650.0, "bf16": 1590.0, "source": "fallback"}
+        return {"hbm_gbs": d.get("hbm_gbs"), "bf16": d.get("bf16_tflops"),
+                "bf16_sustained": d.get("bf16_tflops_sustained") or d.get("bf16_tflops"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
 
 
 class ClockSampler:
@@ -334,7 +335,13 @@ def run_ours(args):
         value = world * ops_per_step * args.steps / (total_ms * 1e-3) / 1e12
         e2e_value = world * ops_per_step * e2e_steps / (e2e_ms * 1e-3) / 1e12
         peaks = _peaks()
-        peak_i8 = 2.0 * peaks["bf16"]
+        # The timed steps follow half a second of the same kernel back to back, so the GPU runs
+        # under its power cap like the seconds-long GEMM loop behind the "sustained" peak; the
+        # burst peak applies only if the cap never engaged.
+        capped = bool(clocks and "sw_power_cap" in clocks.get("reasons", []))
+        peak_kind = "sustained" if capped else "burst"
+        peak_bf16 = peaks["bf16_sustained"] if capped else peaks["bf16"]
+        peak_i8 = 2.0 * peak_bf16
         launch_ms = total_ms / args.steps
         achieved = ops_per_step / (launch_ms * 1e-3) / 1e12
         algo_bytes = rows * K_DIM + N_DIM * K_DIM + rows * N_DIM + 8 * N_DIM
@@ -348,8 +355,9 @@ def run_ours(args):
                        "l2": f"{n_sets} rotating operand sets ({n_sets * (rows * K_DIM + rows * N_DIM) >> 20} MiB) > 126 MB L2"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_i8, "unit": "TOPS",
                          "frac": achieved / peak_i8, "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
-                         "peak_source": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16']} TF/s): int8 issues at "
-                                        "twice the bf16 rate; of measured",
+                         "peak_source": f"2 x {peaks['source']} cuBLAS bf16 {peak_kind} ({peak_bf16} TF/s): int8 issues "
+                                        f"at twice the bf16 rate; of {peaks['source']}",
+                         "frac_of_burst_peak": achieved / (2.0 * peaks["bf16"]),
                          "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS,
                          "algorithmic_bytes": algo_bytes, "algorithmic_ops": ops_per_step,
                          "launch_ms_median": per_launch_ms[len(per_launch_ms) // 2]},

@@ -75,12 +75,7 @@ __device__ __forceinline__ void pair_epilogue_cols(uint32_t t_row, const float* 
             uint32_t w[4 * EB];
             if constexpr (EB == 1) {
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                w[i] = static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i]))) |
-                       (static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i + 1]))) << 8) |
-                       (static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i + 2]))) << 16) |
-                       (static_cast<uint32_t>(static_cast<uint8_t>(to_s8(v[4 * i + 3]))) << 24);
-              }
+              for (int i = 0; i < 4; ++i) w[i] = pack4_s8(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
             } else if constexpr (EB == 2) {
 #pragma unroll
               for (int i = 0; i < 8; ++i) {

@@ -109,7 +109,9 @@ __device__ __forceinline__ float div_out_scale(float v, const EpiCtx& c) {
   if (!c.div_fast) return __fdiv_rn(v, c.so);
   const float q0 = v * c.so_inv;
   float q = __fmaf_rn(__fmaf_rn(-q0, c.so, v), c.so_inv, q0);
-  const float frac = fabsf(q - rintf(q));
+  // (q + 1.5 * 2^23) - 1.5 * 2^23 is q rounded half-to-even for |q| < 2^22: two
+  // additions instead of a conversion-rate round instruction.
+  const float frac = fabsf(q - ((q + 12582912.f) - 12582912.f));
   if (fabsf(frac - 0.5f) < 1e-3f && fabsf(q) < 256.f) q = __fdiv_rn(v, c.so);
   return q;
 }
@@ -170,6 +172,21 @@ __device__ __forceinline__ int8_t to_s8(float v) {
   return static_cast<int8_t>(r);
 }
 
+// Four saturated, round-half-to-even int8 values packed into one word without
+// float-to-int conversions: after clamping to [-128, 127], adding 1.5 * 2^23
+// leaves the rounded integer in the low mantissa bits (the add itself rounds
+// to nearest even), so the low byte of each sum is the two's-complement result.
+__device__ __forceinline__ uint32_t pack4_s8(float a, float b, float c, float d) {
+  const float kMagic = 12582912.f;
+  a = fminf(fmaxf(a, -128.f), 127.f) + kMagic;
+  b = fminf(fmaxf(b, -128.f), 127.f) + kMagic;
+  c = fminf(fmaxf(c, -128.f), 127.f) + kMagic;
+  d = fminf(fmaxf(d, -128.f), 127.f) + kMagic;
+  const uint32_t ab = __byte_perm(__float_as_uint(a), __float_as_uint(b), 0x0040);
+  const uint32_t cd = __byte_perm(__float_as_uint(c), __float_as_uint(d), 0x0040);
+  return __byte_perm(ab, cd, 0x5410);
+}
+
 template <typename OutT>
 __device__ __forceinline__ void store_one(OutT* p, float v, int32_t acc);
 template <>
@@ -197,13 +214,7 @@ __device__ __forceinline__ void store_row16_vec<int8_t>(int8_t* p, const float* 
                                                         const uint32_t*) {
   uint32_t w[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint32_t b0 = static_cast<uint8_t>(to_s8(v[4 * i + 0]));
-    uint32_t b1 = static_cast<uint8_t>(to_s8(v[4 * i + 1]));
-    uint32_t b2 = static_cast<uint8_t>(to_s8(v[4 * i + 2]));
-    uint32_t b3 = static_cast<uint8_t>(to_s8(v[4 * i + 3]));
-    w[i] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
-  }
+  for (int i = 0; i < 4; ++i) w[i] = pack4_s8(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
   *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 template <>
