@@ -30,7 +30,7 @@ S_X, S_OUT = 0.02, 0.05
 NOMINAL_INT8_TOPS = 4500.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one qgemm_tiled launch at the
 # bench shape, from the ncu capture summarised under profiles/ (None = not captured yet).
-NCU_DRAM_BYTES_PER_LAUNCH = None
+NCU_DRAM_BYTES_PER_LAUNCH = 1.04e8  # captured at rows=8192 (60.4 MB), reads and writes scaled by the row count
 
 
 def _args():
@@ -43,6 +43,8 @@ def _args():
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--profile", action="store_true",
                     help="for ncu captures: only warm-up and timed steps (no clock hold, e2e or CPU legs)")
+    ap.add_argument("--workload", default="qlinear", choices=["qlinear", "bert_base", "bert_large"],
+                    help="qlinear (default, configuration 1) or a W8A8 encoder forward (configurations 2 / 3)")
     return ap.parse_args()
 
 
@@ -374,10 +376,152 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_encoder(args):
+    """Configurations 2 / 3: one step = one forward of the W8A8 encoder over the global batch
+    (32 sequences of length U[16,512] for BERT-base, 64 of U[64,512] for BERT-large), the
+    sequences split over the ranks by length (no collective; total work fixed: "strong")."""
+    import torch
+    import torch.distributed as dist
+    from bladedisc_b200 import encoder as E
+    from bladedisc_b200 import ops
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the quantized path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if args.workload == "bert_base":
+        cfg, batch, lo = E.EncoderConfig.bert_base(), 32, 16
+    else:
+        cfg, batch, lo = E.EncoderConfig.bert_large(), 64, 64
+    enc, qenc, scales = E.build_quant_encoder(cfg, seed=1234, device=dev, min_len=lo)
+    del enc
+    ids_h, lens_h = E.synthetic_batch(cfg, batch, lo, 512, seed=4321, device="cpu")
+    my_ids_h, my_lens_h, assign = E.shard_batch(ids_h, lens_h, world, rank)
+    ids_pin, lens_pin = my_ids_h.pin_memory(), my_lens_h.pin_memory()
+    have_work = len(assign) > 0
+    ids_d = torch.empty_like(ids_pin, device=dev)
+    lens_d = torch.empty_like(lens_pin, device=dev)
+    cls_pin = torch.empty((max(len(assign), 1), cfg.hidden), dtype=torch.float16).pin_memory()
+
+    # The forward is a fixed sequence of ~100 short launches: capture it once per batch shape
+    # and replay it, so that launch latency does not dominate small per-GPU batches.
+    side = torch.cuda.Stream(dev)
+    graph, out_ref = None, [None]
+    if have_work:
+        ids_d.copy_(ids_pin)
+        lens_d.copy_(lens_pin)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                out_ref[0] = qenc.forward(ids_d, lens_d)
+        torch.cuda.synchronize()
+        launches_per_fwd = qenc.kernel_launches // 2
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                out_ref[0] = qenc.forward(ids_d, lens_d)
+        except Exception:
+            graph = None
+            torch.cuda.synchronize()
+    else:
+        launches_per_fwd = 0
+
+    def device_step():
+        if not have_work:
+            return
+        if graph is not None:
+            graph.replay()
+        else:
+            out_ref[0] = qenc.forward(ids_d, lens_d)
+
+    def e2e_step():
+        if not have_work:
+            return
+        ids_d.copy_(ids_pin, non_blocking=True)
+        lens_d.copy_(lens_pin, non_blocking=True)
+        device_step()
+        cls_pin[:len(assign)].copy_(out_ref[0][:, 0, :], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1)
+
+    for _ in range(max(3, args.warmup)):
+        device_step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    t_hold = time.perf_counter()
+    while not args.profile and time.perf_counter() - t_hold < 0.5:
+        device_step()
+        torch.cuda.synchronize()
+    dev_ms = timed(device_step, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "ms_per_step": dev_ms / args.steps, "workload": args.workload}))
+        return
+    for _ in range(3):
+        e2e_step()
+    e2e_steps = max(3, min(args.steps, 20))
+    e2e_ms = timed(e2e_step, e2e_steps)
+    if ops.kernel_status() != 0:
+        raise SystemExit("kernel status non-zero: a bounded wait ran out")
+    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
+    tokens = torch.tensor([float(my_ids_h.numel()), float(my_lens_h.sum())], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tokens, op=dist.ReduceOp.SUM)
+    dev_ms, e2e_ms = times.tolist()
+    if rank == 0:
+        name = args.workload
+        line = {
+            "metric": f"quant_{name}_seqs_per_s", "value": batch * args.steps / (dev_ms * 1e-3), "unit": "sequences/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": dev_ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
+            "config": {"workload": f"{name} W8A8 encoder forward, {cfg.layers} layers, hidden {cfg.hidden}, "
+                                   f"global batch {batch}, lengths U[{lo},512], padded-mask attention",
+                       "sharding": "sequences split by length over ranks, no collective",
+                       "padded_tokens_all_ranks": int(tokens[0]), "real_tokens": int(tokens[1]),
+                       "cuda_graph": graph is not None,
+                       "l2": "activations of a forward (> 126 MB for the full batch) are rewritten every step",
+                       "note": "the two attention batched GEMMs per layer run on cuBLAS (torch.matmul), as the "
+                               "reference runs them through ral_gemm; every other kernel is this library's"},
+            "e2e": {"value": batch * e2e_steps / (e2e_ms * 1e-3), "unit": "sequences/s",
+                    "h2d_bytes_per_step": int(ids_pin.numel() * 8 + lens_pin.numel() * 4),
+                    "d2h_bytes_per_step": int(len(assign) * cfg.hidden * 2), "steps": e2e_steps},
+            "gpu_launches": launches_per_fwd * args.steps, "launches_per_forward": launches_per_fwd,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     args = _args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "qlinear":
+        run_encoder(args)
     else:
         run_ours(args)
 

@@ -1,0 +1,105 @@
+"""End-to-end harnesses on the quantized path (B200 only): the 2-layer quantized
+MLP of configuration 0 and a small BERT-shaped W8A8 encoder, against the int8
+pipeline replayed on the CPU oracle and against the eager fake-quant model
+(the functional golden of the reference's own e2e tests)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def test_quantized_mlp_config0():
+    """x fp32 [8,128,768] ~ N(0,1); Linear 768->3072 -> GELU -> Linear 3072->768; weights N(0,0.02)
+    per-channel int8 (max|row| / 127), biases N(0,0.01), activations per-tensor (max|x| / 127 over
+    4 calibration batches).  Path: quantize -> qgemm(+bias+GELU+requant) -> qgemm(+bias) -> fp16."""
+    from bladedisc_b200 import ops, quant
+    from oracle import c, np_ref
+    g = torch.Generator().manual_seed(1234)
+    x = torch.randn(8, 128, 768, generator=g)
+    w1 = torch.randn(3072, 768, generator=g) * 0.02
+    b1 = torch.randn(3072, generator=g) * 0.01
+    w2 = torch.randn(768, 3072, generator=g) * 0.02
+    b2 = torch.randn(768, generator=g) * 0.01
+    calib = [torch.randn(8, 128, 768, generator=g) for _ in range(4)]
+    s_x = quant.calibrate_per_tensor(calib)
+    s_mid = quant.calibrate_per_tensor([torch.nn.functional.gelu(torch.nn.functional.linear(cb, w1, b1)) for cb in calib])
+    w1q, s_w1 = quant.quantize_linear(w1)
+    w2q, s_w2 = quant.quantize_linear(w2)
+    # offline weight quantisation equals the oracle's double-precision statement
+    assert (w1q.numpy() == c.quantize_weight(w1.numpy(), s_w1.numpy())).all()
+    # GPU path
+    xq = ops.quantize(x.cuda(), s_x.cuda())
+    midq = ops.qgemm(xq, w1q.cuda(), x_scale=s_x.cuda(), w_scale=s_w1.cuda(), bias=b1.cuda(), act="gelu",
+                     out_scale=s_mid.cuda())
+    y = ops.qgemm(midq, w2q.cuda(), x_scale=s_mid.cuda(), w_scale=s_w2.cuda(), bias=b2.cuda(), out_dtype=torch.float32)
+    assert y.shape == (8, 128, 768)
+    # the same int8 pipeline on the CPU oracle
+    xq_o = c.quantize(x.numpy(), s_x.numpy())
+    assert (xq.cpu().numpy() == xq_o).all()
+    _, midq_o = c.qgemm_epilogue(c.qgemm_acc(xq_o, w1q.numpy()), x_scale=s_x.numpy(), w_scale=s_w1.numpy(),
+                                 out_scale=s_mid.numpy(), bias=b1.numpy(), act="gelu", div_out=True)
+    d_mid = np.abs(midq.cpu().numpy().astype(int) - midq_o.astype(int))
+    assert d_mid.max() <= 1 and (d_mid > 0).mean() < 1e-3  # erf of libdevice vs libm
+    y_o, _ = c.qgemm_epilogue(c.qgemm_acc(midq_o, w2q.numpy()), x_scale=s_mid.numpy(), w_scale=s_w2.numpy(),
+                              bias=b2.numpy())
+    assert np.allclose(y.cpu().numpy(), y_o, rtol=1e-2, atol=1e-3)
+    # and the eager fake-quant model built the way the reference's tests build it
+    fq = torch.fake_quantize_per_tensor_affine
+    zp1, zp2 = torch.zeros(3072, dtype=torch.int32), torch.zeros(768, dtype=torch.int32)
+    w1f = torch.fake_quantize_per_channel_affine(w1, s_w1, zp1, 0, -128, 127)
+    w2f = torch.fake_quantize_per_channel_affine(w2, s_w2, zp2, 0, -128, 127)
+    mid = fq(torch.nn.functional.gelu(torch.nn.functional.linear(fq(x, float(s_x), 0, -128, 127), w1f, b1)),
+             float(s_mid), 0, -128, 127)
+    y_fq = torch.nn.functional.linear(mid, w2f, b2)
+    err = (y.cpu() - y_fq).abs()
+    assert float(err.max()) < 5e-3 and float(err.mean()) < 2e-4
+    del np_ref
+
+
+def test_small_encoder_matches_fake_quant_model():
+    from bladedisc_b200 import encoder as E
+    cfg = E.EncoderConfig(layers=3, hidden=256, heads=4, ffn=512, vocab=2000, max_len=96)
+    enc, qenc, scales = E.build_quant_encoder(cfg, seed=7, calib_batch=4, min_len=8, max_len=96)
+    ids, lens = E.synthetic_batch(cfg, 5, 8, 96, seed=99)
+    got = qenc.forward(ids, lens).float()
+    with torch.no_grad():
+        want = E.float_forward(enc, ids, lens, scales=scales)
+        ref_fp = E.float_forward(enc, ids, lens)
+    valid = (torch.arange(ids.shape[1], device=ids.device)[None, :] < lens[:, None])
+    d_q = (got - want)[valid].abs()
+    d_fp = (want - ref_fp)[valid].abs()
+    # the int8 path tracks the fake-quant model much more closely than quantisation
+    # itself moves the model away from fp32
+    assert float(d_q.mean()) < 0.02, float(d_q.mean())
+    assert float(d_q.max()) < 0.35, float(d_q.max())
+    assert float(d_q.mean()) < float(d_fp.mean()) * 1.5 + 0.01
+    assert torch.isfinite(got).all()
+    assert qenc.kernel_launches == 1 + 8 * cfg.layers
+
+
+def test_sharded_batches_cover_the_batch_and_agree():
+    """Splitting a batch over ranks (length-balanced) gives every sequence the result it has in the full batch."""
+    from bladedisc_b200 import encoder as E
+    cfg = E.EncoderConfig.tiny()
+    enc, qenc, scales = E.build_quant_encoder(cfg, seed=3, calib_batch=4, min_len=4, max_len=64)
+    ids, lens = E.synthetic_batch(cfg, 9, 4, 64, seed=5)
+    full = qenc.forward(ids, lens)
+    seen = []
+    for rank in range(4):
+        my_ids, my_lens, assign = E.shard_batch(ids, lens, 4, rank)
+        if not assign:
+            continue
+        out = qenc.forward(my_ids, my_lens)
+        for j, seq in enumerate(assign):
+            n = int(lens[seq])
+            # the attention products run on cuBLAS, which may order its sums differently for a
+            # different batch shape; everything else is bitwise independent of the batch
+            diff = (out[j, :n].float() - full[seq, :n].float()).abs()
+            assert float(diff.mean()) < 5e-3 and float(diff.max()) < 0.15, f"sequence {seq} differs when sharded"
+        seen += assign
+    assert sorted(seen) == list(range(9))
