@@ -54,7 +54,16 @@ def balance_sequences(lengths: Sequence[int], world: int) -> List[List[int]]:
             hi = mid
         else:
             lo = mid + 1
-    for r, run in enumerate(fill(lo)):
+    runs = fill(lo)
+    # Idle ranks help nobody: while some rank would get nothing, halve the most expensive
+    # run that can still be cut (this never raises the maximum).
+    while len(runs) < min(world, n):
+        k = max((i for i in range(len(runs)) if len(runs[i]) > 1),
+                key=lambda i: len(runs[i]) * lengths[runs[i][0]])
+        run = runs[k]
+        half = len(run) // 2
+        runs[k:k + 1] = [run[:half], run[half:]]
+    for r, run in enumerate(runs):
         out[r] = sorted(run)
     return out
 
