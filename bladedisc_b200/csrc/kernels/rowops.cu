@@ -7,8 +7,18 @@
 // of two schedules, one warp per row or one block per row
 // (tao_compiler/mlir/disc/transforms/lhlo_legalize_roots_to_loops.cc:1263-1289,
 // 1678-1716; choice at disc_specialize_fusion_with_speculation.cc:393-452).
-// Here the same two schedules exist, but a row is read once with 16-byte
-// loads, kept in registers across the reductions, and written once.
+//
+// Here a row is read once with 16-byte loads and written once.  What decides
+// the speed of such kernels on B200 is how many bytes each SM keeps in flight
+// (about 6.5 TB/s x 1 us / 148 SMs = 45 KB at the least), so:
+//   * rows stay in registers in their storage type (packed 16-byte vectors),
+//     converted to fp32 on the fly in each pass, which halves the registers a
+//     fp16 row needs and lets more warps be resident;
+//   * a group of G threads (8, 16 or 32 lanes of a warp, or a 256-thread
+//     block for long rows) works on R rows at once, so that R x NV loads per
+//     thread are issued before the first reduction starts;
+//   * per-column parameters (gamma, beta) are fetched per vector from L1/L2
+//     instead of being kept for the whole row.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <float.h>
@@ -19,6 +29,7 @@ namespace disc_b200 {
 namespace {
 
 constexpr int kBlock = 256;
+constexpr float kRoundMagic = 12582912.f;  // 1.5 * 2^23: (x + m) - m rounds half-to-even for |x| < 2^22
 
 int sm_count() {
   static int n = 0;
@@ -31,95 +42,199 @@ int sm_count() {
   return n;
 }
 
-__device__ __forceinline__ int8_t quant_one(float x, float s, float zp, float qmin, float qmax) {
-  // divide, add zero point, round half to even, clamp, convert: the order of the reference.
-  float t = __fadd_rn(__fdiv_rn(x, s), zp);
-  t = rintf(t);
-  t = fminf(fmaxf(t, qmin), qmax);
-  return static_cast<int8_t>(static_cast<int>(t));
+// x / s wherever the exact IEEE quotient decides the integer result.  The
+// product with the (correctly rounded) reciprocal is within 2 ulp of the true
+// quotient; only a quotient that close to a rounding tie (k + 0.5) can round to
+// a different integer, and anything beyond +-1024 saturates whatever its last
+// bits are.  So ties within 1e-3 (and small magnitudes only) take the real
+// division, kept out of line because it is rare and long: unrolled copies of
+// it were what overflowed the instruction cache.
+__device__ __noinline__ float slow_div(float x, float s) { return __fdiv_rn(x, s); }
+
+struct Divisor {
+  float s, inv;
+  bool fast;
+};
+__device__ __forceinline__ Divisor make_divisor(float s) {
+  Divisor d;
+  d.s = s;
+  d.inv = __frcp_rn(s);
+  const float a = fabsf(s);
+  d.fast = a > 1e-15f && a < 1e15f;
+  return d;
+}
+__device__ __forceinline__ float div_exact_for_rounding(float x, const Divisor& d) {
+  if (!d.fast) return slow_div(x, d.s);
+  float q = x * d.inv;
+  const float frac = fabsf(q - ((q + kRoundMagic) - kRoundMagic));
+  if (fabsf(frac - 0.5f) < 1e-3f && fabsf(q) < 1024.f) q = slow_div(x, d.s);
+  return q;
 }
 
-// 8 consecutive elements as floats.
+// divide, add zero point, round half to even, clamp: the order of the reference
+// (clamping to integer bounds before rounding gives the same result as after).
+// Returns the value still carrying the rounding constant: its low byte is the int8.
+__device__ __forceinline__ float quant_biased(float x, const Divisor& d, float zp, float qmin, float qmax) {
+  const float t = __fadd_rn(div_exact_for_rounding(x, d), zp);
+  return fminf(fmaxf(t, qmin), qmax) + kRoundMagic;
+}
+__device__ __forceinline__ int8_t quant_one(float x, const Divisor& d, float zp, float qmin, float qmax) {
+  return static_cast<int8_t>(__float_as_uint(quant_biased(x, d, zp, qmin, qmax)) & 0xffu);
+}
+// Four values from quant_biased -> packed bytes.
+__device__ __forceinline__ uint32_t pack4(float a, float b, float c, float d) {
+  const uint32_t ab = __byte_perm(__float_as_uint(a), __float_as_uint(b), 0x0040);
+  const uint32_t cd = __byte_perm(__float_as_uint(c), __float_as_uint(d), 0x0040);
+  return __byte_perm(ab, cd, 0x5410);
+}
+
+// ------------------------------------------------------------ 16-byte vectors
 template <typename T>
-struct Pack8;
+struct VecT;
 template <>
-struct Pack8<float> {
-  static __device__ __forceinline__ void load(const float* p, float* v) {
-    const float4 a = *reinterpret_cast<const float4*>(p);
-    const float4 b = *reinterpret_cast<const float4*>(p + 4);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+struct VecT<float> {
+  static constexpr int kElems = 4;
+  static __device__ __forceinline__ float get(const uint4& v, int j) {
+    return __uint_as_float(j == 0 ? v.x : (j == 1 ? v.y : (j == 2 ? v.z : v.w)));
   }
-  static __device__ __forceinline__ void store(float* p, const float* v) {
-    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  static __device__ __forceinline__ uint4 pack(const float* f) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
   }
-  static __device__ __forceinline__ float get(const float* p) { return *p; }
-  static __device__ __forceinline__ void put(float* p, float v) { *p = v; }
+  static __device__ __forceinline__ float load1(const float* p) { return *p; }
+  static __device__ __forceinline__ void store1(float* p, float v) { *p = v; }
+  static __device__ __forceinline__ float round_to_storage(float v) { return v; }
 };
 template <>
-struct Pack8<__half> {
-  static __device__ __forceinline__ void load(const __half* p, float* v) {
-    const uint4 u = *reinterpret_cast<const uint4*>(p);
-    const __half2* h = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = __half22float2(h[i]);
-      v[2 * i] = f.x;
-      v[2 * i + 1] = f.y;
-    }
+struct VecT<__half> {
+  static constexpr int kElems = 8;
+  static __device__ __forceinline__ float get(const uint4& v, int j) {
+    const uint32_t w = (j >> 1) == 0 ? v.x : ((j >> 1) == 1 ? v.y : ((j >> 1) == 2 ? v.z : v.w));
+    const __half2 h = *reinterpret_cast<const __half2*>(&w);
+    return (j & 1) ? __high2float(h) : __low2float(h);
   }
-  static __device__ __forceinline__ void store(__half* p, const float* v) {
+  static __device__ __forceinline__ uint4 pack(const float* f) {
     uint4 u;
-    __half2* h = reinterpret_cast<__half2*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-    *reinterpret_cast<uint4*>(p) = u;
+    __half2 h0 = __floats2half2_rn(f[0], f[1]), h1 = __floats2half2_rn(f[2], f[3]);
+    __half2 h2 = __floats2half2_rn(f[4], f[5]), h3 = __floats2half2_rn(f[6], f[7]);
+    u.x = *reinterpret_cast<uint32_t*>(&h0);
+    u.y = *reinterpret_cast<uint32_t*>(&h1);
+    u.z = *reinterpret_cast<uint32_t*>(&h2);
+    u.w = *reinterpret_cast<uint32_t*>(&h3);
+    return u;
   }
-  static __device__ __forceinline__ float get(const __half* p) { return __half2float(*p); }
-  static __device__ __forceinline__ void put(__half* p, float v) { *p = __float2half_rn(v); }
+  static __device__ __forceinline__ float load1(const __half* p) { return __half2float(*p); }
+  static __device__ __forceinline__ void store1(__half* p, float v) { *p = __float2half_rn(v); }
+  static __device__ __forceinline__ float round_to_storage(float v) { return __half2float(__float2half_rn(v)); }
 };
 
-__device__ __forceinline__ void store_q8(int8_t* p, const int8_t* q) {
-  uint2 u;
-  u.x = static_cast<uint8_t>(q[0]) | (static_cast<uint8_t>(q[1]) << 8) |
-        (static_cast<uint8_t>(q[2]) << 16) | (static_cast<uint32_t>(static_cast<uint8_t>(q[3])) << 24);
-  u.y = static_cast<uint8_t>(q[4]) | (static_cast<uint8_t>(q[5]) << 8) |
-        (static_cast<uint8_t>(q[6]) << 16) | (static_cast<uint32_t>(static_cast<uint8_t>(q[7])) << 24);
-  *reinterpret_cast<uint2*>(p) = u;
+// Vector `v` (16 bytes) of a row of `cols` elements; elements past the row read as `fill`.
+template <typename T>
+__device__ __forceinline__ uint4 load_vec(const T* row, int cols, int v, bool aligned, float fill) {
+  constexpr int E = VecT<T>::kElems;
+  const int base = v * E;
+  if (aligned) {
+    if (base < cols) return *reinterpret_cast<const uint4*>(row + base);
+    float f[E];
+#pragma unroll
+    for (int j = 0; j < E; ++j) f[j] = fill;
+    return VecT<T>::pack(f);
+  }
+  float f[E];
+#pragma unroll
+  for (int j = 0; j < E; ++j) f[j] = (base + j < cols) ? VecT<T>::load1(row + base + j) : fill;
+  return VecT<T>::pack(f);
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T* row, int cols, int v, bool aligned, const uint4& u) {
+  constexpr int E = VecT<T>::kElems;
+  const int base = v * E;
+  if (base >= cols) return;
+  if (aligned) {
+    *reinterpret_cast<uint4*>(row + base) = u;
+  } else {
+#pragma unroll
+    for (int j = 0; j < E; ++j)
+      if (base + j < cols) VecT<T>::store1(row + base + j, VecT<T>::get(u, j));
+  }
+}
+// E int8 values of vector v, as produced by quant_biased.
+template <int E>
+__device__ __forceinline__ void store_q(int8_t* row, int cols, int v, bool aligned, const float* q) {
+  const int base = v * E;
+  if (base >= cols) return;
+  if (aligned) {
+    if (E == 8) {
+      *reinterpret_cast<uint2*>(row + base) = make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
+    } else {
+      *reinterpret_cast<uint32_t*>(row + base) = pack4(q[0], q[1], q[2], q[3]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < E; ++j)
+      if (base + j < cols) row[base + j] = static_cast<int8_t>(__float_as_uint(q[j]) & 0xffu);
+  }
+}
+
+// ------------------------------------------------------ group reductions
+// G lanes of a warp (8, 16, 32) reduce with shuffles; G = 256 is a whole block
+// and goes through shared memory.  R values are reduced together.
+template <int G, int R, bool IS_MAX>
+__device__ __forceinline__ void group_reduce(float (&v)[R], float* red) {
+  constexpr int kLanes = G < 32 ? G : 32;
+#pragma unroll
+  for (int o = kLanes / 2; o > 0; o >>= 1) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[r], o);
+      v[r] = IS_MAX ? fmaxf(v[r], other) : v[r] + other;
+    }
+  }
+  if (G > 32) {
+    const int w = threadIdx.x >> 5;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) red[r * 8 + w] = v[r];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float a = red[r * 8];
+#pragma unroll
+      for (int i = 1; i < G / 32; ++i) a = IS_MAX ? fmaxf(a, red[r * 8 + i]) : a + red[r * 8 + i];
+      v[r] = a;
+    }
+  }
 }
 
 // ------------------------------------------------------ elementwise quantize
-// Per-tensor, 16 elements per thread per step: 16-byte int8 stores.
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
 quantize_tensor_kernel(const T* __restrict__ x, int8_t* __restrict__ q, int64_t numel,
                        const float* __restrict__ scale, const int32_t* __restrict__ zero_point,
                        float qmin, float qmax, int aligned) {
-  const float s = __ldg(scale);
+  constexpr int E = VecT<T>::kElems;
+  constexpr int NVEC = 16 / E;  // input vectors per 16 output bytes
+  const Divisor d = make_divisor(__ldg(scale));
   const float zp = zero_point ? static_cast<float>(__ldg(zero_point)) : 0.f;
-  const int64_t nvec = aligned ? numel / 16 : 0;
+  const int64_t nchunk = aligned ? numel / 16 : 0;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t v = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; v < nvec; v += stride) {
-    float f[16];
-    Pack8<T>::load(x + v * 16, f);
-    Pack8<T>::load(x + v * 16 + 8, f + 8);
-    int8_t o[16];
+  const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  for (int64_t c = tid; c < nchunk; c += stride) {
+    uint4 in[NVEC];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) o[i] = quant_one(f[i], s, zp, qmin, qmax);
-    uint4 u;
-    uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+    for (int i = 0; i < NVEC; ++i) in[i] = *reinterpret_cast<const uint4*>(x + c * 16 + i * E);
+    float o[16];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      w[i] = static_cast<uint8_t>(o[4 * i]) | (static_cast<uint8_t>(o[4 * i + 1]) << 8) |
-             (static_cast<uint8_t>(o[4 * i + 2]) << 16) |
-             (static_cast<uint32_t>(static_cast<uint8_t>(o[4 * i + 3])) << 24);
-    }
-    *reinterpret_cast<uint4*>(q + v * 16) = u;
+    for (int i = 0; i < NVEC; ++i)
+#pragma unroll
+      for (int j = 0; j < E; ++j) o[i * E + j] = quant_biased(VecT<T>::get(in[i], j), d, zp, qmin, qmax);
+    *reinterpret_cast<uint4*>(q + c * 16) =
+        make_uint4(pack4(o[0], o[1], o[2], o[3]), pack4(o[4], o[5], o[6], o[7]),
+                   pack4(o[8], o[9], o[10], o[11]), pack4(o[12], o[13], o[14], o[15]));
   }
-  for (int64_t i = nvec * 16 + blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < numel;
-       i += stride) {
-    q[i] = quant_one(Pack8<T>::get(x + i), s, zp, qmin, qmax);
+  for (int64_t i = nchunk * 16 + tid; i < numel; i += stride) {
+    q[i] = quant_one(VecT<T>::load1(x + i), d, zp, qmin, qmax);
   }
 }
 
@@ -133,7 +248,7 @@ quantize_axis_kernel(const T* __restrict__ x, int8_t* __restrict__ q, int64_t nu
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < numel; i += stride) {
     const int64_t c = (i / inner) % channels;
     const float zp = zero_point ? static_cast<float>(__ldg(zero_point + c)) : 0.f;
-    q[i] = quant_one(Pack8<T>::get(x + i), __ldg(scale + c), zp, qmin, qmax);
+    q[i] = quant_one(VecT<T>::load1(x + i), make_divisor(__ldg(scale + c)), zp, qmin, qmax);
   }
 }
 
@@ -142,297 +257,363 @@ __global__ void __launch_bounds__(kBlock)
 dequantize_kernel(const int8_t* __restrict__ q, T* __restrict__ y, int64_t numel,
                   const float* __restrict__ scale, const int32_t* __restrict__ zero_point,
                   int64_t channels, int64_t inner, int aligned) {
+  constexpr int E = VecT<T>::kElems;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   if (channels == 1) {
     const float s = __ldg(scale);
     const int zp = zero_point ? __ldg(zero_point) : 0;
-    const int64_t nvec = aligned ? numel / 16 : 0;
-    for (int64_t v = tid; v < nvec; v += stride) {
-      const uint4 u = *reinterpret_cast<const uint4*>(q + v * 16);
+    const int64_t nchunk = aligned ? numel / 16 : 0;
+    for (int64_t c = tid; c < nchunk; c += stride) {
+      const uint4 u = *reinterpret_cast<const uint4*>(q + c * 16);
       const int8_t* b = reinterpret_cast<const int8_t*>(&u);
       float f[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) f[i] = __fmul_rn(static_cast<float>(static_cast<int>(b[i]) - zp), s);
-      Pack8<T>::store(y + v * 16, f);
-      Pack8<T>::store(y + v * 16 + 8, f + 8);
+#pragma unroll
+      for (int i = 0; i < 16 / E; ++i) *reinterpret_cast<uint4*>(y + c * 16 + i * E) = VecT<T>::pack(f + i * E);
     }
-    for (int64_t i = nvec * 16 + tid; i < numel; i += stride) {
-      Pack8<T>::put(y + i, __fmul_rn(static_cast<float>(static_cast<int>(q[i]) - zp), s));
+    for (int64_t i = nchunk * 16 + tid; i < numel; i += stride) {
+      VecT<T>::store1(y + i, __fmul_rn(static_cast<float>(static_cast<int>(q[i]) - zp), s));
     }
   } else {
     for (int64_t i = tid; i < numel; i += stride) {
       const int64_t c = (i / inner) % channels;
       const int zp = zero_point ? __ldg(zero_point + c) : 0;
-      Pack8<T>::put(y + i, __fmul_rn(static_cast<float>(static_cast<int>(q[i]) - zp), __ldg(scale + c)));
+      VecT<T>::store1(y + i, __fmul_rn(static_cast<float>(static_cast<int>(q[i]) - zp), __ldg(scale + c)));
     }
   }
 }
 
 // ------------------------------------------------------------- row kernels
-// A row is shared by G threads (32 = one warp per row, 256 = one block per
-// row).  Thread t of the group owns 8-element vectors t, t+G, t+2G, ... up to
-// MAXV of them, all kept in registers.
-template <int G>
-__device__ __forceinline__ float group_sum(float v, float* red) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  if (G > 32) {
-    const int w = threadIdx.x >> 5;
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) red[w] = v;
-    __syncthreads();
-    v = red[0];
-#pragma unroll
-    for (int i = 1; i < G / 32; ++i) v += red[i];
-  }
-  return v;
-}
-template <int G>
-__device__ __forceinline__ float group_max(float v, float* red) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  if (G > 32) {
-    const int w = threadIdx.x >> 5;
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) red[w] = v;
-    __syncthreads();
-    v = red[0];
-#pragma unroll
-    for (int i = 1; i < G / 32; ++i) v = fmaxf(v, red[i]);
-  }
-  return v;
-}
-
-template <typename T, int G, int MAXV>
-__device__ __forceinline__ void row_load(const T* row, int cols, int t, bool aligned, float fill,
-                                         float (&x)[MAXV * 8]) {
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int base = (t + i * G) * 8;
-    if (aligned) {
-      if (base < cols) {
-        Pack8<T>::load(row + base, &x[i * 8]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) x[i * 8 + j] = fill;
-      }
+// Thread t of a group owns vectors t, t + G, ... (NV of them) of each of its R rows.
+template <int G, int R>
+struct RowIndex {
+  int t;
+  int64_t row0;  // first of the R rows of this group
+  __device__ __forceinline__ RowIndex() {
+    if (G >= 32 * 8) {
+      t = threadIdx.x;
+      row0 = static_cast<int64_t>(blockIdx.x) * R;
     } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) x[i * 8 + j] = (base + j < cols) ? Pack8<T>::get(row + base + j) : fill;
+      t = threadIdx.x % G;
+      row0 = (static_cast<int64_t>(blockIdx.x) * (kBlock / G) + threadIdx.x / G) * R;
     }
   }
-}
+};
 
-template <typename T, int G, int MAXV>
-__device__ __forceinline__ void row_store(T* row, int cols, int t, bool aligned,
-                                          const float (&x)[MAXV * 8]) {
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int base = (t + i * G) * 8;
-    if (aligned) {
-      if (base < cols) Pack8<T>::store(row + base, &x[i * 8]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (base + j < cols) Pack8<T>::put(row + base + j, x[i * 8 + j]);
-    }
-  }
-}
-
-template <int G, int MAXV>
-__device__ __forceinline__ void row_store_q8(int8_t* row, int cols, int t, bool aligned,
-                                             const int8_t (&q)[MAXV * 8]) {
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int base = (t + i * G) * 8;
-    if (aligned) {
-      if (base < cols) store_q8(row + base, &q[i * 8]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (base + j < cols) row[base + j] = q[i * 8 + j];
-    }
-  }
-}
-
-template <typename T, int G, int MAXV>
-__global__ void __launch_bounds__(kBlock)
+template <typename T, int G, int NV, int R>
+__global__ void __launch_bounds__(kBlock, (NV * R <= 4 ? 3 : (NV * R <= 8 ? 2 : 1)))
 norm_kernel(NormParams p, int aligned) {
-  __shared__ float red[8];
-  const int t = threadIdx.x % G;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * (kBlock / G) + threadIdx.x / G;
-  const bool active = row < p.rows;  // whole groups are active or not
-  if (G == 32 && !active) return;    // warp-per-row: no block-level sync is used
+  constexpr int E = VecT<T>::kElems;
+  __shared__ float red[R * 8];
+  const RowIndex<G, R> ix;
+  const int t = ix.t;
   const int cols = static_cast<int>(p.cols);
   const bool al = aligned != 0;
-  const int64_t off = (active ? row : 0) * p.cols;
-  float x[MAXV * 8];
-  row_load<T, G, MAXV>(reinterpret_cast<const T*>(p.x) + off, cols, t, al, 0.f, x);
-  if (p.residual) {
-    float r[MAXV * 8];
-    row_load<T, G, MAXV>(reinterpret_cast<const T*>(p.residual) + off, cols, t, al, 0.f, r);
+  const T* xb = reinterpret_cast<const T*>(p.x);
+  const T* rb = reinterpret_cast<const T*>(p.residual);
+  uint4 raw[R][NV];
+  bool live[R];
 #pragma unroll
-    for (int i = 0; i < MAXV * 8; ++i) x[i] += r[i];
-    if (p.sum_out) {
-      // Round the stream to its storage type once, and normalise what was stored.
+  for (int r = 0; r < R; ++r) {
+    live[r] = ix.row0 + r < p.rows;
+    const int64_t off = (live[r] ? ix.row0 + r : 0) * p.cols;
 #pragma unroll
-      for (int i = 0; i < MAXV * 8; ++i) {
-        if (sizeof(T) == 2) x[i] = __half2float(__float2half_rn(x[i]));
+    for (int i = 0; i < NV; ++i) raw[r][i] = load_vec<T>(xb + off, cols, t + i * G, al, 0.f);
+  }
+  if (rb) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int64_t off = (live[r] ? ix.row0 + r : 0) * p.cols;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const uint4 rv = load_vec<T>(rb + off, cols, t + i * G, al, 0.f);
+        float f[E];
+#pragma unroll
+        for (int j = 0; j < E; ++j) f[j] = VecT<T>::get(raw[r][i], j) + VecT<T>::get(rv, j);
+        raw[r][i] = VecT<T>::pack(f);  // the sum lives in the storage type, as a separate add would leave it
+        if (p.sum_out && live[r]) store_vec<T>(reinterpret_cast<T*>(p.sum_out) + off, cols, t + i * G, al, raw[r][i]);
       }
-      if (active) row_store<T, G, MAXV>(reinterpret_cast<T*>(p.sum_out) + off, cols, t, al, x);
     }
   }
   const float inv_n = 1.f / static_cast<float>(cols);
-  float mean = 0.f;
-  if (!p.rms) {
+  float mean[R], var[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float s = 0.f;
+    if (!p.rms) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int j = 0; j < E; ++j) s += VecT<T>::get(raw[r][i], j);
+    }
+    mean[r] = s;
+  }
+  if (!p.rms) group_reduce<G, R, false>(mean, red);
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    mean[r] *= inv_n;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const int c = (t + i * G) * E + j;
+        const float dlt = c < cols ? VecT<T>::get(raw[r][i], j) - mean[r] : 0.f;
+        ss += dlt * dlt;
+      }
+    var[r] = ss;
+  }
+  group_reduce<G, R, false>(var, red);
+  float rstd[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) rstd[r] = 1.f / sqrtf(var[r] * inv_n + p.eps);
+
+  const T* gb = reinterpret_cast<const T*>(p.gamma);
+  const T* bb = (!p.rms && p.beta) ? reinterpret_cast<const T*>(p.beta) : nullptr;
+  // y of one vector of one row, rounded to the storage type (what the next op reads).
+  auto normalized = [&](int r, int i, const uint4& gv, const uint4& bv, float* y) {
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+      float v = (VecT<T>::get(raw[r][i], j) - mean[r]) * rstd[r] * VecT<T>::get(gv, j);
+      if (bb) v += VecT<T>::get(bv, j);
+      y[j] = VecT<T>::round_to_storage(v);
+    }
+  };
+  float qs[R];
+  const bool dyn = p.q_out && !p.q_scale;
+  if (dyn) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) qs[r] = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const uint4 gv = load_vec<T>(gb, cols, t + i * G, al, 0.f);
+      const uint4 bv = bb ? load_vec<T>(bb, cols, t + i * G, al, 0.f) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float y[E];
+        normalized(r, i, gv, bv, y);
+#pragma unroll
+        for (int j = 0; j < E; ++j) qs[r] = fmaxf(qs[r], fabsf(y[j]));  // padding holds 0 (gamma fill)
+      }
+    }
+    group_reduce<G, R, true>(qs, red);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      qs[r] = fmaxf(__fdiv_rn(qs[r], 127.f), FLT_EPSILON);
+      if (t == 0 && live[r] && p.q_row_scale) p.q_row_scale[ix.row0 + r] = qs[r];
+    }
+  } else if (p.q_out) {
+    const float s = __ldg(p.q_scale);
+#pragma unroll
+    for (int r = 0; r < R; ++r) qs[r] = s;
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const uint4 gv = load_vec<T>(gb, cols, t + i * G, al, 0.f);
+    const uint4 bv = bb ? load_vec<T>(bb, cols, t + i * G, al, 0.f) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (!live[r]) continue;
+      const int64_t off = (ix.row0 + r) * p.cols;
+      float y[E];
+      normalized(r, i, gv, bv, y);
+      if (p.y) store_vec<T>(reinterpret_cast<T*>(p.y) + off, cols, t + i * G, al, VecT<T>::pack(y));
+      if (p.q_out) {
+        const Divisor d = make_divisor(qs[r]);
+        float q[E];
+#pragma unroll
+        for (int j = 0; j < E; ++j) q[j] = quant_biased(y[j], d, 0.f, -128.f, 127.f);
+        store_q<E>(p.q_out + off, cols, t + i * G, al, q);
+      }
+    }
+  }
+}
+
+template <typename T, int G, int NV, int R>
+__global__ void __launch_bounds__(kBlock, (NV * R <= 4 ? 3 : (NV * R <= 8 ? 2 : 1)))
+dynquant_kernel(DynQuantParams p, int aligned) {
+  constexpr int E = VecT<T>::kElems;
+  __shared__ float red[R * 8];
+  const RowIndex<G, R> ix;
+  const int t = ix.t;
+  const int cols = static_cast<int>(p.cols);
+  const bool al = aligned != 0;
+  const T* xb = reinterpret_cast<const T*>(p.x);
+  uint4 raw[R][NV];
+  bool live[R];
+  float m[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    live[r] = ix.row0 + r < p.rows;
+    const int64_t off = (live[r] ? ix.row0 + r : 0) * p.cols;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) raw[r][i] = load_vec<T>(xb + off, cols, t + i * G, al, 0.f);
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float a = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+      for (int j = 0; j < E; ++j) a = fmaxf(a, fabsf(VecT<T>::get(raw[r][i], j)));
+    m[r] = a;
+  }
+  group_reduce<G, R, true>(m, red);
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    if (!live[r]) continue;
+    const float s = fmaxf(__fdiv_rn(m[r], 127.f), FLT_EPSILON);
+    if (t == 0) p.row_scale[ix.row0 + r] = s;
+    const Divisor d = make_divisor(s);
+    const int64_t off = (ix.row0 + r) * p.cols;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float q[E];
+#pragma unroll
+      for (int j = 0; j < E; ++j) q[j] = quant_biased(VecT<T>::get(raw[r][i], j), d, 0.f, -128.f, 127.f);
+      store_q<E>(p.q + off, cols, t + i * G, al, q);
+    }
+  }
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// softmax over rows held in registers.  exp(x * scale - max) is evaluated as
+// ex2(x * k - max * k) with k = scale * log2(e): one fused multiply-add and one
+// special-function op per element and pass; the maximum is taken on the raw
+// values (a positive scale keeps the order; a negative one turns it into the
+// minimum).  Columns at and beyond the valid length are skipped by a
+// per-vector count instead of a per-element index.
+template <typename T, int G, int NV, int R>
+__global__ void __launch_bounds__(kBlock, (NV * R <= 4 ? 3 : (NV * R <= 8 ? 2 : 1)))
+softmax_kernel(SoftmaxParams p, int aligned) {
+  constexpr int E = VecT<T>::kElems;
+  constexpr float kLog2e = 1.4426950408889634f;
+  __shared__ float red[R * 8];
+  const RowIndex<G, R> ix;
+  const int t = ix.t;
+  const int cols = static_cast<int>(p.cols);
+  const bool al = aligned != 0;
+  const T* xb = reinterpret_cast<const T*>(p.x);
+  const T* mb = reinterpret_cast<const T*>(p.mask);
+  uint4 raw[R][NV];
+  bool live[R];
+  int len[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    live[r] = ix.row0 + r < p.rows;
+    const int64_t row = live[r] ? ix.row0 + r : 0;
+    const int64_t batch = row / p.rows_per_batch;
+    len[r] = p.lens ? min(cols, __ldg(p.lens + batch)) : cols;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) raw[r][i] = load_vec<T>(xb + row * p.cols, cols, t + i * G, al, 0.f);
+    if (mb) {
+      // fold the additive mask in once; the biased logits replace the raw values in the
+      // storage type (as an unfused add would leave them) and carry the scale already
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const uint4 mv = load_vec<T>(mb + batch * p.cols, cols, t + i * G, al, 0.f);
+        float f[E];
+#pragma unroll
+        for (int j = 0; j < E; ++j) f[j] = VecT<T>::get(raw[r][i], j) * p.scale + VecT<T>::get(mv, j);
+        raw[r][i] = VecT<T>::pack(f);
+      }
+    }
+  }
+  const float scale = mb ? 1.f : p.scale;
+  const float k = scale * kLog2e;
+  const bool neg = scale < 0.f;
+  float mx[R], sum[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float a = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int nvalid = len[r] - (t + i * G) * E;  // valid elements of this vector (may be <= 0 or >= E)
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const float v = VecT<T>::get(raw[r][i], j);
+        if (j < nvalid) a = fmaxf(a, neg ? -v : v);
+      }
+    }
+    mx[r] = a;
+  }
+  group_reduce<G, R, true>(mx, red);
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    // mx holds max(x) (or max(-x) for a negative scale); the largest logit is |scale| * mx
+    const float top = mx[r] == -INFINITY ? 0.f : mx[r] * fabsf(scale);
+    mx[r] = top;                  // largest logit (0 for an empty row: every probability 0)
+    const float bias = -top * kLog2e;
     float s = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAXV * 8; ++i) s += x[i];
-    mean = group_sum<G>(s, red) * inv_n;
+    for (int i = 0; i < NV; ++i) {
+      const int nvalid = len[r] - (t + i * G) * E;
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const float e = ex2_approx(__fmaf_rn(VecT<T>::get(raw[r][i], j), k, bias));
+        if (j < nvalid) s += e;
+      }
+    }
+    sum[r] = s;
   }
-  float ss = 0.f;
+  group_reduce<G, R, false>(sum, red);
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
+  for (int r = 0; r < R; ++r) {
+    if (!live[r]) continue;
+    const float inv = sum[r] > 0.f ? 1.f / sum[r] : 0.f;
+    const float lsum = logf(sum[r]);
+    const float bias = -mx[r] * kLog2e;
+    const int64_t off = (ix.row0 + r) * p.cols;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int c = (t + i * G) * 8 + j;
-      const float d = (c < cols) ? x[i * 8 + j] - mean : 0.f;
-      ss += d * d;
+    for (int i = 0; i < NV; ++i) {
+      const int nvalid = len[r] - (t + i * G) * E;
+      float y[E];
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const float x = VecT<T>::get(raw[r][i], j);
+        if (p.log_softmax) {
+          y[j] = j < nvalid ? __fmaf_rn(x, scale, -mx[r]) - lsum : -INFINITY;
+        } else {
+          y[j] = j < nvalid ? ex2_approx(__fmaf_rn(x, k, bias)) * inv : 0.f;
+        }
+      }
+      store_vec<T>(reinterpret_cast<T*>(p.y) + off, cols, t + i * G, al, VecT<T>::pack(y));
     }
   }
-  const float var = group_sum<G>(ss, red) * inv_n;
-  const float rstd = 1.f / sqrtf(var + p.eps);
-  float g[MAXV * 8];
-  row_load<T, G, MAXV>(reinterpret_cast<const T*>(p.gamma), cols, t, al, 0.f, g);
-#pragma unroll
-  for (int i = 0; i < MAXV * 8; ++i) x[i] = (x[i] - mean) * rstd * g[i];
-  if (!p.rms && p.beta) {
-    row_load<T, G, MAXV>(reinterpret_cast<const T*>(p.beta), cols, t, al, 0.f, g);
-#pragma unroll
-    for (int i = 0; i < MAXV * 8; ++i) x[i] += g[i];
-  }
-  if (sizeof(T) == 2) {
-    // What the next op sees is the stored half value; quantize that one.
-#pragma unroll
-    for (int i = 0; i < MAXV * 8; ++i) x[i] = __half2float(__float2half_rn(x[i]));
-  }
-  if (p.y && active) row_store<T, G, MAXV>(reinterpret_cast<T*>(p.y) + off, cols, t, al, x);
-  if (p.q_out) {
-    float s;
-    if (p.q_scale) {
-      s = __ldg(p.q_scale);
-    } else {
-      float m = 0.f;
-#pragma unroll
-      for (int i = 0; i < MAXV * 8; ++i) m = fmaxf(m, fabsf(x[i]));  // padding holds 0
-      m = group_max<G>(m, red);
-      s = fmaxf(__fdiv_rn(m, 127.f), FLT_EPSILON);
-      if (t == 0 && active && p.q_row_scale) p.q_row_scale[row] = s;
-    }
-    int8_t q[MAXV * 8];
-#pragma unroll
-    for (int i = 0; i < MAXV * 8; ++i) q[i] = quant_one(x[i], s, 0.f, -128.f, 127.f);
-    if (active) row_store_q8<G, MAXV>(p.q_out + off, cols, t, al, q);
-  }
-}
-
-template <typename T, int G, int MAXV>
-__global__ void __launch_bounds__(kBlock)
-dynquant_kernel(DynQuantParams p, int aligned) {
-  __shared__ float red[8];
-  const int t = threadIdx.x % G;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * (kBlock / G) + threadIdx.x / G;
-  const bool active = row < p.rows;
-  if (G == 32 && !active) return;
-  const int cols = static_cast<int>(p.cols);
-  const bool al = aligned != 0;
-  const int64_t off = (active ? row : 0) * p.cols;
-  float x[MAXV * 8];
-  row_load<T, G, MAXV>(reinterpret_cast<const T*>(p.x) + off, cols, t, al, 0.f, x);
-  float m = 0.f;
-#pragma unroll
-  for (int i = 0; i < MAXV * 8; ++i) m = fmaxf(m, fabsf(x[i]));
-  m = group_max<G>(m, red);
-  const float s = fmaxf(__fdiv_rn(m, 127.f), FLT_EPSILON);
-  if (t == 0 && active) p.row_scale[row] = s;
-  int8_t q[MAXV * 8];
-#pragma unroll
-  for (int i = 0; i < MAXV * 8; ++i) q[i] = quant_one(x[i], s, 0.f, -128.f, 127.f);
-  if (active) row_store_q8<G, MAXV>(p.q + off, cols, t, al, q);
-}
-
-template <typename T, int G, int MAXV>
-__global__ void __launch_bounds__(kBlock)
-softmax_kernel(SoftmaxParams p, int aligned) {
-  __shared__ float red[8];
-  const int t = threadIdx.x % G;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * (kBlock / G) + threadIdx.x / G;
-  const bool active = row < p.rows;
-  if (G == 32 && !active) return;
-  const int cols = static_cast<int>(p.cols);
-  const bool al = aligned != 0;
-  const int64_t r = active ? row : 0;
-  const int64_t batch = r / p.rows_per_batch;
-  const int len = p.lens ? min(cols, __ldg(p.lens + batch)) : cols;
-  float x[MAXV * 8];
-  row_load<T, G, MAXV>(reinterpret_cast<const T*>(p.x) + r * p.cols, cols, t, al, 0.f, x);
-#pragma unroll
-  for (int i = 0; i < MAXV * 8; ++i) x[i] *= p.scale;
-  if (p.mask) {
-    float mk[MAXV * 8];
-    row_load<T, G, MAXV>(reinterpret_cast<const T*>(p.mask) + batch * p.cols, cols, t, al, 0.f, mk);
-#pragma unroll
-    for (int i = 0; i < MAXV * 8; ++i) x[i] += mk[i];
-  }
-  float mx = -INFINITY;
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int c = (t + i * G) * 8 + j;
-      if (c >= len) x[i * 8 + j] = -INFINITY;
-      mx = fmaxf(mx, x[i * 8 + j]);
-    }
-  }
-  mx = group_max<G>(mx, red);
-  if (mx == -INFINITY) mx = 0.f;  // empty row: all probabilities 0
-  float sum = 0.f;
-#pragma unroll
-  for (int i = 0; i < MAXV * 8; ++i) {
-    const float d = x[i] - mx;
-    const float e = expf(d);  // exp(-inf) = 0 for masked columns
-    sum += e;
-    x[i] = p.log_softmax ? d : e;
-  }
-  sum = group_sum<G>(sum, red);
-  if (p.log_softmax) {
-    const float l = logf(sum);
-#pragma unroll
-    for (int i = 0; i < MAXV * 8; ++i) x[i] -= l;
-  } else {
-    const float inv = sum > 0.f ? 1.f / sum : 0.f;
-#pragma unroll
-    for (int i = 0; i < MAXV * 8; ++i) x[i] *= inv;
-  }
-  if (active) row_store<T, G, MAXV>(reinterpret_cast<T*>(p.y) + r * p.cols, cols, t, al, x);
 }
 
 bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-// Picks (G, MAXV) for a row length: one warp per row up to 1024 columns, one
-// block per row up to 16384.
-#define DISC_ROW_DISPATCH(KERNEL, T, cols, rows, stream, ...)                              \
-  do {                                                                                     \
-    if ((cols) <= 512) {                                                                   \
-      KERNEL<T, 32, 2><<<static_cast<unsigned>(((rows) + 7) / 8), kBlock, 0, stream>>>(__VA_ARGS__); \
-    } else if ((cols) <= 1024) {                                                           \
-      KERNEL<T, 32, 4><<<static_cast<unsigned>(((rows) + 7) / 8), kBlock, 0, stream>>>(__VA_ARGS__); \
-    } else if ((cols) <= 4096) {                                                           \
-      KERNEL<T, 256, 2><<<static_cast<unsigned>(rows), kBlock, 0, stream>>>(__VA_ARGS__);  \
-    } else {                                                                               \
-      KERNEL<T, 256, 8><<<static_cast<unsigned>(rows), kBlock, 0, stream>>>(__VA_ARGS__);  \
-    }                                                                                      \
+// (G, NV, R) for a row of `nvec` 16-byte vectors: sub-warp groups for short
+// rows, one warp up to 8 vectors per lane, one block above; R chosen so that a
+// thread has 4 to 8 loads in flight.
+#define DISC_ROW_LAUNCH(KERNEL, T, G, NV, R, rows, stream, ...)                                        \
+  do {                                                                                                 \
+    const int64_t groups_per_block = (G) >= 256 ? 1 : kBlock / (G);                                    \
+    const int64_t rows_per_block = groups_per_block * (R);                                             \
+    const unsigned grid = static_cast<unsigned>(((rows) + rows_per_block - 1) / rows_per_block);       \
+    KERNEL<T, G, NV, R><<<grid, kBlock, 0, stream>>>(__VA_ARGS__);                                     \
+  } while (0)
+
+#define DISC_ROW_DISPATCH(KERNEL, T, nvec, rows, stream, ...)                                          \
+  do {                                                                                                 \
+    if ((nvec) <= 8) DISC_ROW_LAUNCH(KERNEL, T, 8, 1, 4, rows, stream, __VA_ARGS__);                   \
+    else if ((nvec) <= 16) DISC_ROW_LAUNCH(KERNEL, T, 8, 2, 2, rows, stream, __VA_ARGS__);             \
+    else if ((nvec) <= 32) DISC_ROW_LAUNCH(KERNEL, T, 16, 2, 2, rows, stream, __VA_ARGS__);            \
+    else if ((nvec) <= 64) DISC_ROW_LAUNCH(KERNEL, T, 32, 2, 2, rows, stream, __VA_ARGS__);            \
+    else if ((nvec) <= 128) DISC_ROW_LAUNCH(KERNEL, T, 32, 4, 1, rows, stream, __VA_ARGS__);           \
+    else if ((nvec) <= 256) DISC_ROW_LAUNCH(KERNEL, T, 32, 8, 1, rows, stream, __VA_ARGS__);           \
+    else if ((nvec) <= 512) DISC_ROW_LAUNCH(KERNEL, T, 256, 2, 1, rows, stream, __VA_ARGS__);          \
+    else if ((nvec) <= 1024) DISC_ROW_LAUNCH(KERNEL, T, 256, 4, 1, rows, stream, __VA_ARGS__);         \
+    else if ((nvec) <= 2048) DISC_ROW_LAUNCH(KERNEL, T, 256, 8, 1, rows, stream, __VA_ARGS__);         \
+    else DISC_ROW_LAUNCH(KERNEL, T, 256, 16, 1, rows, stream, __VA_ARGS__);                            \
   } while (0)
 
 bool row_shape_ok(int64_t rows, int64_t cols, const char** err) {
@@ -453,6 +634,11 @@ int elem_grid(int64_t work_items) {
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   return static_cast<int>(blocks);
+}
+
+template <typename T>
+int64_t vectors_per_row(int64_t cols) {
+  return (cols + VecT<T>::kElems - 1) / VecT<T>::kElems;
 }
 
 }  // namespace
@@ -519,11 +705,13 @@ cudaError_t dynamic_quantize_launch(const DynQuantParams& p, cudaStream_t s, con
     return cudaErrorInvalidValue;
   }
   if (!row_shape_ok(p.rows, p.cols, err)) return cudaErrorInvalidValue;
-  const int aligned = (p.cols % 8 == 0) && is_aligned16(p.x) && ((reinterpret_cast<uintptr_t>(p.q) & 7) == 0);
-  if (p.in_type == kF32)
-    DISC_ROW_DISPATCH(dynquant_kernel, float, p.cols, p.rows, s, p, aligned);
-  else
-    DISC_ROW_DISPATCH(dynquant_kernel, __half, p.cols, p.rows, s, p, aligned);
+  if (p.in_type == kF32) {
+    const int aligned = (p.cols % 4 == 0) && is_aligned16(p.x) && ((reinterpret_cast<uintptr_t>(p.q) & 3) == 0);
+    DISC_ROW_DISPATCH(dynquant_kernel, float, vectors_per_row<float>(p.cols), p.rows, s, p, aligned);
+  } else {
+    const int aligned = (p.cols % 8 == 0) && is_aligned16(p.x) && ((reinterpret_cast<uintptr_t>(p.q) & 7) == 0);
+    DISC_ROW_DISPATCH(dynquant_kernel, __half, vectors_per_row<__half>(p.cols), p.rows, s, p, aligned);
+  }
   return cudaGetLastError();
 }
 
@@ -539,14 +727,15 @@ cudaError_t norm_launch(const NormParams& p, cudaStream_t s, const char** err) {
     return cudaErrorInvalidValue;
   }
   if (!row_shape_ok(p.rows, p.cols, err)) return cudaErrorInvalidValue;
-  const int aligned = (p.cols % 8 == 0) && is_aligned16(p.x) && is_aligned16(p.gamma) &&
+  const int epv = p.type == kF32 ? 4 : 8;
+  const int aligned = (p.cols % epv == 0) && is_aligned16(p.x) && is_aligned16(p.gamma) &&
                       (!p.residual || is_aligned16(p.residual)) && (!p.beta || is_aligned16(p.beta)) &&
                       (!p.y || is_aligned16(p.y)) && (!p.sum_out || is_aligned16(p.sum_out)) &&
-                      (!p.q_out || (reinterpret_cast<uintptr_t>(p.q_out) & 7) == 0);
+                      (!p.q_out || (reinterpret_cast<uintptr_t>(p.q_out) & (epv - 1)) == 0);
   if (p.type == kF32)
-    DISC_ROW_DISPATCH(norm_kernel, float, p.cols, p.rows, s, p, aligned);
+    DISC_ROW_DISPATCH(norm_kernel, float, vectors_per_row<float>(p.cols), p.rows, s, p, aligned);
   else
-    DISC_ROW_DISPATCH(norm_kernel, __half, p.cols, p.rows, s, p, aligned);
+    DISC_ROW_DISPATCH(norm_kernel, __half, vectors_per_row<__half>(p.cols), p.rows, s, p, aligned);
   return cudaGetLastError();
 }
 
@@ -560,12 +749,13 @@ cudaError_t softmax_launch(const SoftmaxParams& p, cudaStream_t s, const char** 
   if (!row_shape_ok(p.rows, p.cols, err)) return cudaErrorInvalidValue;
   SoftmaxParams q = p;
   if (q.rows_per_batch <= 0) q.rows_per_batch = q.rows;
-  const int aligned = (p.cols % 8 == 0) && is_aligned16(p.x) && is_aligned16(p.y) &&
+  const int epv = p.type == kF32 ? 4 : 8;
+  const int aligned = (p.cols % epv == 0) && is_aligned16(p.x) && is_aligned16(p.y) &&
                       (!p.mask || is_aligned16(p.mask));
   if (p.type == kF32)
-    DISC_ROW_DISPATCH(softmax_kernel, float, q.cols, q.rows, s, q, aligned);
+    DISC_ROW_DISPATCH(softmax_kernel, float, vectors_per_row<float>(q.cols), q.rows, s, q, aligned);
   else
-    DISC_ROW_DISPATCH(softmax_kernel, __half, q.cols, q.rows, s, q, aligned);
+    DISC_ROW_DISPATCH(softmax_kernel, __half, vectors_per_row<__half>(q.cols), q.rows, s, q, aligned);
   return cudaGetLastError();
 }
 

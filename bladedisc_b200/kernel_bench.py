@@ -30,6 +30,9 @@ def peaks():
     return 6650.0, 2.0 * 1590.0, "fallback"
 
 
+EAGER = False
+
+
 def time_ms(fns, iters):
     """Average ms per launch; `fns` is a list of closures over rotating operand sets.
 
@@ -48,6 +51,8 @@ def time_ms(fns, iters):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     graph = None
     try:
+        if EAGER:
+            raise RuntimeError("eager timing requested")
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=side):
             for i in range(iters):
@@ -155,7 +160,12 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true", help="a few points only")
     ap.add_argument("--json", default=None)
+    ap.add_argument("--only", default=None, help="comma-separated substrings: run only the cases whose kernel name contains one (qgemm, quantize, norm, softmax ...)")
+    ap.add_argument("--eager", action="store_true", help="no CUDA graph (for ncu captures); few iterations")
     args = ap.parse_args()
+    global EAGER
+    EAGER = args.eager
+    only = [o for o in (args.only or "").split(",") if o]
     hbm, tops_peak, src = peaks()
     out = {"peaks": {"hbm_gbs": hbm, "int8_tops": tops_peak, "source": src}, "rows": []}
     ms_list = [7, 64, 4096] if args.quick else MS
@@ -165,7 +175,11 @@ def main():
     for K, N in kns:
         for M in ms_list:
             for od in (torch.int8, torch.float16):
+                if only and "qgemm" not in only:
+                    continue
                 iters = 200 if M <= 1024 else 30
+                if args.eager:
+                    iters = 3
                 r = bench_qgemm(M, K, N, od, hbm, tops_peak, iters)
                 out["rows"].append(r)
                 print(f"{r['kernel']:<16}{M:>6}{K:>6}{N:>7}{r['out']:>9}{r['us']:>10.2f}{r['tops']:>9.1f}{r['gbs']:>9.0f}"
@@ -179,7 +193,9 @@ def main():
         row_cases = row_cases[:1] + row_cases[3:5] + row_cases[7:8]
     print(f"{'kernel':<22}{'rows':>8}{'cols':>7}{'dtype':>9}{'us':>10}{'GB/s':>9}{'frac':>7}")
     for name, rows, cols, dt in row_cases:
-        r = bench_rows(name, rows, cols, dt, hbm, 50)
+        if only and not any(o in name for o in only):
+            continue
+        r = bench_rows(name, rows, cols, dt, hbm, 3 if args.eager else 50)
         out["rows"].append(r)
         print(f"{name:<22}{rows:>8}{cols:>7}{r['dtype']:>9}{r['us']:>10.2f}{r['gbs']:>9.0f}{r['frac']:>7.2f}", flush=True)
     st = ops.kernel_status()
