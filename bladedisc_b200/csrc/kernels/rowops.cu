@@ -190,7 +190,11 @@ __device__ __forceinline__ void group_reduce(float (&v)[R], float* red) {
     }
   }
   if (G > 32) {
+    // groups of 2, 4 or 8 warps: partials meet in shared memory; every group of the
+    // block runs the same sequence, so block-wide barriers serve all of them
+    constexpr int kWarps = G / 32;
     const int w = threadIdx.x >> 5;
+    const int grp = w / kWarps;
     __syncthreads();
     if ((threadIdx.x & 31) == 0) {
 #pragma unroll
@@ -199,9 +203,10 @@ __device__ __forceinline__ void group_reduce(float (&v)[R], float* red) {
     __syncthreads();
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      float a = red[r * 8];
+      float a = red[r * 8 + grp * kWarps];
 #pragma unroll
-      for (int i = 1; i < G / 32; ++i) a = IS_MAX ? fmaxf(a, red[r * 8 + i]) : a + red[r * 8 + i];
+      for (int i = 1; i < kWarps; ++i)
+        a = IS_MAX ? fmaxf(a, red[r * 8 + grp * kWarps + i]) : a + red[r * 8 + grp * kWarps + i];
       v[r] = a;
     }
   }
@@ -292,77 +297,105 @@ struct RowIndex {
   int t;
   int64_t row0;  // first of the R rows of this group
   __device__ __forceinline__ RowIndex() {
-    if (G >= 32 * 8) {
-      t = threadIdx.x;
-      row0 = static_cast<int64_t>(blockIdx.x) * R;
-    } else {
-      t = threadIdx.x % G;
-      row0 = (static_cast<int64_t>(blockIdx.x) * (kBlock / G) + threadIdx.x / G) * R;
-    }
+    t = threadIdx.x % G;
+    row0 = (static_cast<int64_t>(blockIdx.x) * (kBlock / G) + threadIdx.x / G) * R;
   }
 };
 
-template <typename T, int G, int NV, int R>
+// E values of one vector quantized at `d` (zero point 0, int8 range) into biased
+// floats for store_q.  The rounding constant is added first, the clamp works on
+// the biased value, and the tie test that decides whether the reciprocal
+// product may stand in for the division is taken once per vector.
+template <int E>
+__device__ __forceinline__ void quant_vec(const float* y, const Divisor& d, float* q) {
+  float worst = 0.f;
+#pragma unroll
+  for (int j = 0; j < E; ++j) {
+    const float t = y[j] * d.inv;
+    const float r = t + kRoundMagic;
+    worst = fmaxf(worst, fabsf(t - (r - kRoundMagic)));
+    q[j] = fminf(fmaxf(r, kRoundMagic - 128.f), kRoundMagic + 127.f);
+  }
+  if (worst > 0.499f || !d.fast) {  // some quotient sits on a rounding tie: divide for real
+#pragma unroll
+    for (int j = 0; j < E; ++j) q[j] = quant_biased(y[j], d, 0.f, -128.f, 127.f);
+  }
+}
+
+// LayerNorm / RMSNorm over rows held in registers, with optional residual add,
+// sum output and int8 second output.  ALIGNED rows (16-byte aligned, length a
+// multiple of the vector) need no per-element bounds: a vector is either inside
+// the row or entirely outside it.
+template <typename T, int G, int NV, int R, bool ALIGNED>
 __global__ void __launch_bounds__(kBlock, (NV * R <= 4 ? 3 : (NV * R <= 8 ? 2 : 1)))
-norm_kernel(NormParams p, int aligned) {
+norm_kernel(NormParams p) {
   constexpr int E = VecT<T>::kElems;
   __shared__ float red[R * 8];
   const RowIndex<G, R> ix;
   const int t = ix.t;
   const int cols = static_cast<int>(p.cols);
-  const bool al = aligned != 0;
   const T* xb = reinterpret_cast<const T*>(p.x);
   const T* rb = reinterpret_cast<const T*>(p.residual);
   uint4 raw[R][NV];
   bool live[R];
+  float mean[R], var[R];
+  // number of valid elements of vector i of this thread: E, 0, or (unaligned rows) in between
+  auto nvalid = [&](int i) {
+    const int n = cols - (t + i * G) * E;
+    return ALIGNED ? (n > 0 ? E : 0) : n;
+  };
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     live[r] = ix.row0 + r < p.rows;
     const int64_t off = (live[r] ? ix.row0 + r : 0) * p.cols;
 #pragma unroll
-    for (int i = 0; i < NV; ++i) raw[r][i] = load_vec<T>(xb + off, cols, t + i * G, al, 0.f);
+    for (int i = 0; i < NV; ++i) raw[r][i] = load_vec<T>(xb + off, cols, t + i * G, ALIGNED, 0.f);
   }
-  if (rb) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int64_t off = (live[r] ? ix.row0 + r : 0) * p.cols;
+  for (int r = 0; r < R; ++r) {
+    const int64_t off = (live[r] ? ix.row0 + r : 0) * p.cols;
+    float s = 0.f;
 #pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const uint4 rv = load_vec<T>(rb + off, cols, t + i * G, al, 0.f);
-        float f[E];
+    for (int i = 0; i < NV; ++i) {
+      float f[E];
+      if (rb) {
+        const uint4 rv = load_vec<T>(rb + off, cols, t + i * G, ALIGNED, 0.f);
 #pragma unroll
         for (int j = 0; j < E; ++j) f[j] = VecT<T>::get(raw[r][i], j) + VecT<T>::get(rv, j);
         raw[r][i] = VecT<T>::pack(f);  // the sum lives in the storage type, as a separate add would leave it
-        if (p.sum_out && live[r]) store_vec<T>(reinterpret_cast<T*>(p.sum_out) + off, cols, t + i * G, al, raw[r][i]);
+        if (p.sum_out && live[r])
+          store_vec<T>(reinterpret_cast<T*>(p.sum_out) + off, cols, t + i * G, ALIGNED, raw[r][i]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < E; ++j) f[j] = VecT<T>::get(raw[r][i], j);
       }
-    }
-  }
-  const float inv_n = 1.f / static_cast<float>(cols);
-  float mean[R], var[R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    float s = 0.f;
-    if (!p.rms) {
-#pragma unroll
-      for (int i = 0; i < NV; ++i)
-#pragma unroll
-        for (int j = 0; j < E; ++j) s += VecT<T>::get(raw[r][i], j);
+      for (int j = 0; j < E; ++j) s += f[j];  // padding holds 0
     }
     mean[r] = s;
   }
-  if (!p.rms) group_reduce<G, R, false>(mean, red);
+  const float inv_n = 1.f / static_cast<float>(cols);
+  if (!p.rms) {
+    group_reduce<G, R, false>(mean, red);
+#pragma unroll
+    for (int r = 0; r < R; ++r) mean[r] *= inv_n;
+  } else {
+#pragma unroll
+    for (int r = 0; r < R; ++r) mean[r] = 0.f;
+  }
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    mean[r] *= inv_n;
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < NV; ++i)
+    for (int i = 0; i < NV; ++i) {
+      const int nv = nvalid(i);
+      if (ALIGNED && nv == 0) continue;
 #pragma unroll
       for (int j = 0; j < E; ++j) {
-        const int c = (t + i * G) * E + j;
-        const float dlt = c < cols ? VecT<T>::get(raw[r][i], j) - mean[r] : 0.f;
-        ss += dlt * dlt;
+        const float dlt = VecT<T>::get(raw[r][i], j) - mean[r];
+        if (ALIGNED || j < nv) ss = __fmaf_rn(dlt, dlt, ss);
       }
+    }
     var[r] = ss;
   }
   group_reduce<G, R, false>(var, red);
@@ -372,61 +405,57 @@ norm_kernel(NormParams p, int aligned) {
 
   const T* gb = reinterpret_cast<const T*>(p.gamma);
   const T* bb = (!p.rms && p.beta) ? reinterpret_cast<const T*>(p.beta) : nullptr;
-  // y of one vector of one row, rounded to the storage type (what the next op reads).
-  auto normalized = [&](int r, int i, const uint4& gv, const uint4& bv, float* y) {
-#pragma unroll
-    for (int j = 0; j < E; ++j) {
-      float v = (VecT<T>::get(raw[r][i], j) - mean[r]) * rstd[r] * VecT<T>::get(gv, j);
-      if (bb) v += VecT<T>::get(bv, j);
-      y[j] = VecT<T>::round_to_storage(v);
-    }
-  };
-  float qs[R];
   const bool dyn = p.q_out && !p.q_scale;
-  if (dyn) {
+  // normalise in place: raw becomes y in the storage type (what the next op reads)
+  float qs[R];
 #pragma unroll
-    for (int r = 0; r < R; ++r) qs[r] = 0.f;
+  for (int r = 0; r < R; ++r) qs[r] = 0.f;
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const uint4 gv = load_vec<T>(gb, cols, t + i * G, al, 0.f);
-      const uint4 bv = bb ? load_vec<T>(bb, cols, t + i * G, al, 0.f) : make_uint4(0, 0, 0, 0);
+  for (int i = 0; i < NV; ++i) {
+    const uint4 gv = load_vec<T>(gb, cols, t + i * G, ALIGNED, 0.f);
+    const uint4 bv = bb ? load_vec<T>(bb, cols, t + i * G, ALIGNED, 0.f) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        float y[E];
-        normalized(r, i, gv, bv, y);
+    for (int r = 0; r < R; ++r) {
+      float y[E];
 #pragma unroll
-        for (int j = 0; j < E; ++j) qs[r] = fmaxf(qs[r], fabsf(y[j]));  // padding holds 0 (gamma fill)
+      for (int j = 0; j < E; ++j) {
+        y[j] = (VecT<T>::get(raw[r][i], j) - mean[r]) * rstd[r] * VecT<T>::get(gv, j);
+        if (bb) y[j] += VecT<T>::get(bv, j);
+      }
+      raw[r][i] = VecT<T>::pack(y);
+      if (p.y && live[r])
+        store_vec<T>(reinterpret_cast<T*>(p.y) + (ix.row0 + r) * p.cols, cols, t + i * G, ALIGNED, raw[r][i]);
+      if (dyn) {
+#pragma unroll
+        for (int j = 0; j < E; ++j) qs[r] = fmaxf(qs[r], fabsf(VecT<T>::get(raw[r][i], j)));  // padding: gamma fill 0
       }
     }
+  }
+  if (!p.q_out) return;
+  if (dyn) {
     group_reduce<G, R, true>(qs, red);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       qs[r] = fmaxf(__fdiv_rn(qs[r], 127.f), FLT_EPSILON);
       if (t == 0 && live[r] && p.q_row_scale) p.q_row_scale[ix.row0 + r] = qs[r];
     }
-  } else if (p.q_out) {
+  } else {
     const float s = __ldg(p.q_scale);
 #pragma unroll
     for (int r = 0; r < R; ++r) qs[r] = s;
   }
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const uint4 gv = load_vec<T>(gb, cols, t + i * G, al, 0.f);
-    const uint4 bv = bb ? load_vec<T>(bb, cols, t + i * G, al, 0.f) : make_uint4(0, 0, 0, 0);
+  for (int r = 0; r < R; ++r) {
+    if (!live[r]) continue;
+    const Divisor d = make_divisor(qs[r]);
+    const int64_t off = (ix.row0 + r) * p.cols;
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      if (!live[r]) continue;
-      const int64_t off = (ix.row0 + r) * p.cols;
-      float y[E];
-      normalized(r, i, gv, bv, y);
-      if (p.y) store_vec<T>(reinterpret_cast<T*>(p.y) + off, cols, t + i * G, al, VecT<T>::pack(y));
-      if (p.q_out) {
-        const Divisor d = make_divisor(qs[r]);
-        float q[E];
+    for (int i = 0; i < NV; ++i) {
+      float y[E], q[E];
 #pragma unroll
-        for (int j = 0; j < E; ++j) q[j] = quant_biased(y[j], d, 0.f, -128.f, 127.f);
-        store_q<E>(p.q_out + off, cols, t + i * G, al, q);
-      }
+      for (int j = 0; j < E; ++j) y[j] = VecT<T>::get(raw[r][i], j);
+      quant_vec<E>(y, d, q);
+      store_q<E>(p.q_out + off, cols, t + i * G, ALIGNED, q);
     }
   }
 }
@@ -596,7 +625,7 @@ bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) 
 // thread has 4 to 8 loads in flight.
 #define DISC_ROW_LAUNCH(KERNEL, T, G, NV, R, rows, stream, ...)                                        \
   do {                                                                                                 \
-    const int64_t groups_per_block = (G) >= 256 ? 1 : kBlock / (G);                                    \
+    const int64_t groups_per_block = kBlock / (G);                                                     \
     const int64_t rows_per_block = groups_per_block * (R);                                             \
     const unsigned grid = static_cast<unsigned>(((rows) + rows_per_block - 1) / rows_per_block);       \
     KERNEL<T, G, NV, R><<<grid, kBlock, 0, stream>>>(__VA_ARGS__);                                     \
@@ -615,6 +644,11 @@ bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) 
     else if ((nvec) <= 2048) DISC_ROW_LAUNCH(KERNEL, T, 256, 8, 1, rows, stream, __VA_ARGS__);         \
     else DISC_ROW_LAUNCH(KERNEL, T, 256, 16, 1, rows, stream, __VA_ARGS__);                            \
   } while (0)
+
+template <typename T, int G, int NV, int R>
+constexpr auto NORM_ALIGNED = norm_kernel<T, G, NV, R, true>;
+template <typename T, int G, int NV, int R>
+constexpr auto NORM_RAGGED = norm_kernel<T, G, NV, R, false>;
 
 bool row_shape_ok(int64_t rows, int64_t cols, const char** err) {
   if (cols > 16384) {
@@ -732,10 +766,13 @@ cudaError_t norm_launch(const NormParams& p, cudaStream_t s, const char** err) {
                       (!p.residual || is_aligned16(p.residual)) && (!p.beta || is_aligned16(p.beta)) &&
                       (!p.y || is_aligned16(p.y)) && (!p.sum_out || is_aligned16(p.sum_out)) &&
                       (!p.q_out || (reinterpret_cast<uintptr_t>(p.q_out) & (epv - 1)) == 0);
-  if (p.type == kF32)
-    DISC_ROW_DISPATCH(norm_kernel, float, vectors_per_row<float>(p.cols), p.rows, s, p, aligned);
-  else
-    DISC_ROW_DISPATCH(norm_kernel, __half, vectors_per_row<__half>(p.cols), p.rows, s, p, aligned);
+  if (p.type == kF32) {
+    if (aligned) DISC_ROW_DISPATCH(NORM_ALIGNED, float, vectors_per_row<float>(p.cols), p.rows, s, p);
+    else DISC_ROW_DISPATCH(NORM_RAGGED, float, vectors_per_row<float>(p.cols), p.rows, s, p);
+  } else {
+    if (aligned) DISC_ROW_DISPATCH(NORM_ALIGNED, __half, vectors_per_row<__half>(p.cols), p.rows, s, p);
+    else DISC_ROW_DISPATCH(NORM_RAGGED, __half, vectors_per_row<__half>(p.cols), p.rows, s, p);
+  }
   return cudaGetLastError();
 }
 
