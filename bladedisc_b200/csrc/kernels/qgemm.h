@@ -10,7 +10,14 @@ enum QGemmOut : int { kOutI8 = 0, kOutF16 = 1, kOutF32 = 2, kOutI32 = 3 };
 enum QGemmAct : int { kActNone = 0, kActGelu = 1, kActSilu = 2 };
 enum QGemmBias : int { kBiasNone = 0, kBiasF32 = 1, kBiasI8 = 2 };
 enum ScaleKind : int { kScaleNone = 0, kScaleScalar = 1, kScalePerCol = 2, kScalePerRow = 3 };
-enum QGemmPath : int { kPathAuto = 0, kPathTiled = 1, kPathSmallM = 2, kPathSimt = 3, kPathPair = 4 };
+enum QGemmPath : int {
+  kPathAuto = 0,
+  kPathTiled = 1,   // one CTA per 128 x BN tile
+  kPathSmallM = 2,  // operands swapped, optional split-K (M <= 128)
+  kPathSimt = 3,    // shapes TMA cannot address
+  kPathPair = 4,    // CTA pairs, 256 x 256 tiles
+  kPathGemv = 5     // M <= 8: dp4a matrix-vector stream
+};
 
 // out[m, n] = epilogue( sum_k a[m, k] * w[n, k] ), a and w int8, K-contiguous.
 //

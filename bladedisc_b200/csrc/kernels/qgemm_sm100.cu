@@ -650,12 +650,20 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         ok = mbar_wait(counted_bar, 0, abort_flag, &g_kernel_status, kStatusTimeoutSplitK);
         if (ok && *last_flag) {
           __threadfence();
-          for (int m = 0; m < Mrows; ++m) {
-            int32_t acc = 0;
+          // eight rows at a time so that the loads of a round are independent
+          for (int m0 = 0; m0 < Mrows; m0 += 8) {
+            int32_t acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             for (int s = 0; s < split; ++s) {
-              acc += __ldcg(ws + (static_cast<int64_t>(s) * Mrows + m) * n_pad + n_ws);
+              const int32_t* part = ws + static_cast<int64_t>(s) * Mrows * n_pad + n_ws;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (m0 + j < Mrows) acc[j] += __ldcg(part + static_cast<int64_t>(m0 + j) * n_pad);
+              }
             }
-            if (n_ok) emit(m, acc);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (m0 + j < Mrows && n_ok) emit(m0 + j, acc[j]);
+            }
           }
           if (et == 0) counters[n_blk] = 0;  // ready for the next launch
         }
@@ -930,9 +938,12 @@ cudaError_t launch_simt(const QGemmParams& p, cudaStream_t stream, const char** 
   return cudaGetLastError();
 }
 
+#include "qgemm_gemv.inl"
+
 template <typename OutT>
 cudaError_t dispatch(const QGemmParams& p, int path, cudaStream_t stream, const char** err) {
   switch (path) {
+    case kPathGemv: return launch_gemv<OutT>(p, stream, err);
     case kPathTiled: return launch_tiled<OutT>(p, stream, err);
     case kPathSmallM: return launch_smallm<OutT>(p, stream, err);
     case kPathPair: return launch_pair<OutT>(p, stream, err);
@@ -948,6 +959,8 @@ int qgemm_choose_path(const QGemmParams& p) {
   if (p.path == kPathSmallM && p.M <= 128) return kPathSmallM;
   if (p.path == kPathTiled) return kPathTiled;
   if (p.path == kPathPair) return kPathPair;
+  if (p.path == kPathGemv && p.M <= 8 && p.K <= kGemvMaxK) return kPathGemv;
+  if (p.path == kPathAuto && p.M <= 8 && p.K <= kGemvMaxK) return kPathGemv;
   if (p.M <= 64) return kPathSmallM;
   // CTA pairs compute 256 x 256 tiles: worth it once there are enough of them
   // to occupy every pair of SMs.

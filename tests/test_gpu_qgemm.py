@@ -95,6 +95,30 @@ def test_cta_pair_path(ops, M, K, N, out_dtype):
             assert np.allclose(got[ok], want[ok], rtol=RTOL, atol=ATOL)
 
 
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 8])
+@pytest.mark.parametrize("K,N", [(768, 768), (4096, 1000), (16, 5), (2064, 77), (16384, 130)])
+def test_gemv_path(ops, M, K, N):
+    """M <= 8 takes the dp4a matrix-vector kernel: exact sums, same epilogue, odd N and K tails."""
+    from oracle import c
+    assert ops.qgemm_path(M, N, K) == "gemv"
+    rng = np.random.default_rng(M * 1000 + K + N)
+    a, w = _rand_i8(rng, (M, K)), _rand_i8(rng, (N, K))
+    acc = c.qgemm_acc(a, w)
+    assert (ops.qgemm(_dev(a), _dev(w), out_dtype=torch.int32).cpu().numpy() == acc).all()
+    sw = (rng.random(N) * 9e-3 + 1e-3).astype(np.float32)
+    bias = (rng.standard_normal(N) * 0.5).astype(np.float32)
+    sx = (rng.random(M) * 0.03 + 0.01).astype(np.float32)  # per-row (dynamic) activation scales
+    s_out = np.float32(0.05)
+    _, want = c.qgemm_epilogue(acc, x_scale=sx if M > 1 else sx[:1], w_scale=sw, out_scale=s_out, bias=bias, div_out=True)
+    got = ops.qgemm(_dev(a), _dev(w), x_scale=_dev(sx), w_scale=_dev(sw), out_scale=_dev(np.array([s_out])),
+                    bias=_dev(bias)).cpu().numpy()
+    assert (got == want).all()
+    # the tensor-core small-M path computes the same thing
+    alt = ops.qgemm(_dev(a), _dev(w), x_scale=_dev(sx), w_scale=_dev(sw), out_scale=_dev(np.array([s_out])),
+                    bias=_dev(bias), path="small_m").cpu().numpy()
+    assert (alt == want).all()
+
+
 @pytest.mark.parametrize("split", [1, 2, 3, 5, 8])
 def test_small_m_split_k_is_exact_and_repeatable(ops, split):
     from oracle import c
