@@ -192,7 +192,7 @@ __device__ __forceinline__ void group_reduce(float (&v)[R], float* red) {
   if (G > 32) {
     // groups of 2, 4 or 8 warps: partials meet in shared memory; every group of the
     // block runs the same sequence, so block-wide barriers serve all of them
-    constexpr int kWarps = G / 32;
+    constexpr int kWarps = G > 32 ? G / 32 : 1;
     const int w = threadIdx.x >> 5;
     const int grp = w / kWarps;
     __syncthreads();
