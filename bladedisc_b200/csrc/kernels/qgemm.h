@@ -16,7 +16,8 @@ enum QGemmPath : int {
   kPathSmallM = 2,  // operands swapped, optional split-K (M <= 128)
   kPathSimt = 3,    // shapes TMA cannot address
   kPathPair = 4,    // CTA pairs, 256 x 256 tiles
-  kPathGemv = 5     // M <= 8: dp4a matrix-vector stream
+  kPathGemv = 5,    // M <= 8: dp4a matrix-vector stream
+  kPathSkinny = 6   // few rows: BN = 16..128 channels per CTA, full K, no split
 };
 
 // out[m, n] = epilogue( sum_k a[m, k] * w[n, k] ), a and w int8, K-contiguous.

@@ -1,0 +1,220 @@
+// Few-row path of the int8 quantized linear (included by qgemm_sm100.cu).
+//
+// For a handful up to a few hundred activation rows the weight is the whole
+// traffic, so the job is to keep every SM streaming its share of W and to keep
+// the latency chain around that stream short.  Instead of splitting K (partial
+// sums through global scratch, a fence, an atomic and a second pass) the
+// output channels are cut finer: a CTA owns BN channels, BN any multiple of 16
+// chosen so that one wave of CTAs covers N, and walks the full K itself.
+//
+//   A operand (MMA M = 128): activation rows.  Only MT = 16/32/64/128 rows are
+//     fetched per K block; the rows of the 128-row operand above MT are whatever
+//     follows in shared memory.  They only feed accumulator rows nobody reads.
+//   B operand (MMA N = BN): BN weight rows.
+//   grid = (ceil(N / BN), ceil(M / 128)); CTAs of different row tiles read the
+//     same weight slab at about the same time, so it crosses HBM once.
+//
+// Warp roles as in the small-M kernel: warp 0 TMA, warp 1 TMEM + MMA, warps
+// 2..17 epilogue (TMEM lane quadrant = warp & 3 = 32 rows; the four warps of a
+// quadrant interleave 16-column chunks).
+
+constexpr int kSkinnyStageRegion = 184 * 1024;  // a short activation tile is read up to 16 KB past its end
+constexpr int kSkinnyBarOffset = 200 * 1024;
+constexpr int kSkinnyScaleOffset = kSkinnyBarOffset + 256;
+constexpr int kSkinnyDynamic = kSkinnyScaleOffset + 2 * 128 * 4 + 1024;
+constexpr int kSkinnyMaxBN = 128;
+
+template <typename OutT, int ACT, bool DIV, bool RS>
+__device__ __forceinline__ void skinny_epilogue_cols(uint32_t t_row, const float* cs, const float* cb,
+                                                     const EpiCtx& ctx, OutT* out, int64_t m,
+                                                     bool row_ok, int64_t col0, int64_t N,
+                                                     int64_t ldo, int vec_ok, int g, int BN) {
+#pragma unroll 1
+  for (int c = g; c < BN / 16; c += 4) {
+    const int64_t n0 = col0 + c * 16;
+    if (n0 >= N) break;  // uniform across the warp
+    uint32_t r[16];
+    tmem_ld_x16(t_row + c * 16, r);
+    tmem_ld_wait();
+    if (row_ok) {
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        v[j] = epi_value_t<ACT, DIV, RS>(static_cast<int32_t>(r[j]), cs[c * 16 + j], cb[c * 16 + j], ctx);
+      }
+      OutT* dst = out + m * ldo + n0;
+      if (vec_ok && n0 + 16 <= N) {
+        store_row16_vec<OutT>(dst, v, r);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (n0 + j < N) store_one<OutT>(dst + j, v[j], static_cast<int32_t>(r[j]));
+        }
+      }
+    }
+  }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                    const __grid_constant__ CUtensorMap tmap_w, EpiParams ep, int MT, int BN,
+                    int stages, int kbs, int num_kb, int vec_ok, int k3d) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + kSkinnyBarOffset;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kSmallMaxStages + s); };
+  const uint32_t tfull_bar = bar_base + 8u * (2 * kSmallMaxStages);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSkinnyBarOffset + 8 * (2 * kSmallMaxStages + 1));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* s_cs = reinterpret_cast<float*>(smem + kSkinnyScaleOffset);
+  float* s_cb = s_cs + kSkinnyMaxBN;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int64_t n0 = static_cast<int64_t>(blockIdx.x) * BN;
+  const int64_t m0 = static_cast<int64_t>(blockIdx.y) * kTileM;
+  const uint32_t w_bytes = static_cast<uint32_t>(BN) * kTileKBytes;
+  const uint32_t x_bytes = static_cast<uint32_t>(MT) * kTileKBytes;
+  const uint32_t stage_bytes = kbs * (w_bytes + x_bytes);  // multiples of 1024
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < static_cast<uint32_t>(BN)) tmem_cols <<= 1;
+
+  // Issues the loads of one stage (K blocks kb0 .. kb0 + nk - 1).
+  auto issue_stage = [&](int stage, int kb0) {
+    const uint32_t w_dst = smem_base + stage * stage_bytes;
+    const uint32_t x_dst = w_dst + kbs * w_bytes;
+    if (k3d) {
+      // K blocks past the end of K read as zero and still count their bytes
+      mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
+      tma_load_3d(w_dst, &tmap_w, full_bar(stage), 0, static_cast<int>(n0), kb0);
+      tma_load_3d(x_dst, &tmap_x, full_bar(stage), 0, static_cast<int>(m0), kb0);
+      return;
+    }
+    const int nk = num_kb - kb0 < kbs ? num_kb - kb0 : kbs;
+    mbar_arrive_expect_tx(full_bar(stage), nk * (w_bytes + x_bytes));
+    for (int c = 0; c < nk; ++c) {
+      tma_load_2d(w_dst + c * w_bytes, &tmap_w, full_bar(stage), (kb0 + c) * kTileKBytes,
+                  static_cast<int>(n0));
+    }
+    for (int c = 0; c < nk; ++c) {
+      tma_load_2d(x_dst + c * x_bytes, &tmap_x, full_bar(stage), (kb0 + c) * kTileKBytes,
+                  static_cast<int>(m0));
+    }
+  };
+
+  // The producer needs nothing but its own barriers, so the first ring of
+  // stages is on its way before the accumulator columns are allocated and the
+  // CTA meets at the barrier below.
+  int first_kb = 0;
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_w);
+      tma_prefetch_desc(&tmap_x);
+      for (int s = 0; s < stages; ++s) {
+        mbar_init(full_bar(s), 1);
+        mbar_init(empty_bar(s), 1);
+      }
+      mbar_init(tfull_bar, 1);
+      *abort_flag = 0;
+      fence_mbar_init();
+      for (int s = 0; s < stages && first_kb < num_kb; ++s, first_kb += kbs) issue_stage(s, first_kb);
+    }
+  } else if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // If anything is left the ring has been filled exactly once: stage 0 is
+      // next, one phase later.
+      int stage = 0;
+      uint32_t phase = 1;
+      for (int kb0 = first_kb; kb0 < num_kb; kb0 += kbs) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, &g_kernel_status,
+                       kStatusTimeoutEmpty))
+          break;
+        issue_stage(stage, kb0);
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_i8_idesc(kTileM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb0 = 0; kb0 < num_kb; kb0 += kbs) {
+        const int nk = num_kb - kb0 < kbs ? num_kb - kb0 : kbs;
+        ok = mbar_wait(full_bar(stage), phase, abort_flag, &g_kernel_status, kStatusTimeoutFull);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t w_addr = smem_base + stage * stage_bytes;
+        const uint32_t x_addr = w_addr + kbs * w_bytes;
+        for (int c = 0; c < nk; ++c) {
+          const uint64_t a_desc = make_kmajor_sw128_desc(x_addr + c * x_bytes);
+          const uint64_t b_desc = make_kmajor_sw128_desc(w_addr + c * w_bytes);
+#pragma unroll
+          for (int k = 0; k < kTileKBytes / kMmaK; ++k) {
+            umma_i8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb0 + c != 0 || k != 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(empty_bar(stage));
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok) umma_commit(tfull_bar);
+    }
+  } else {
+    const int q = warp & 3;
+    const int g = (warp - 2) >> 2;
+    const int et = threadIdx.x - 64;
+    // Column constants while the weight streams.
+    for (int i = et; i < BN; i += kThreads - 64) {
+      const int64_t n = n0 + i;
+      const bool n_ok = n < ep.N;
+      s_cs[i] = n_ok ? col_scale(ep, n) : 0.f;
+      s_cb[i] = n_ok ? col_bias(ep, n) : 0.f;
+    }
+    EpiCtx ctx = make_epi_ctx(ep);
+    const int64_t m = m0 + q * 32 + lane;
+    const bool row_ok = m < ep.M;
+    if (ctx.has_rs && row_ok) ctx.rs = __ldg(ep.x_scale + m);
+    asm volatile("bar.sync 1, %0;" ::"r"(kThreads - 64) : "memory");
+
+    const bool ok = mbar_wait(tfull_bar, 0, abort_flag, &g_kernel_status, kStatusTimeoutTmemFull);
+    if (ok && m0 + q * 32 < ep.M) {  // a quadrant without rows has nothing to read
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+      OutT* out = reinterpret_cast<OutT*>(ep.out);
+      const int mode = epi_mode(ctx);
+      DISC_EPI_SWITCH(mode, (skinny_epilogue_cols<OutT, ACT, DIV, RS>(
+                                t_row, s_cs, s_cb, ctx, out, m, row_ok, n0, ep.N, ep.ldo, vec_ok, g, BN)));
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}

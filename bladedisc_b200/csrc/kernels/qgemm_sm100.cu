@@ -105,14 +105,19 @@ __device__ __forceinline__ EpiCtx make_epi_ctx(const EpiParams& e) {
 // That is within one ulp of the true quotient; only a quotient that close to a
 // rounding tie (k + 0.5) could round to a different integer, so those rare
 // values alone are recomputed with the IEEE division the reference uses.
+// The IEEE division is kept out of line: it runs for a few outputs in a
+// thousand, and inlined into every unrolled epilogue slot it multiplies the
+// code a CTA has to fetch.
+__device__ __noinline__ float ieee_div(float v, float so) { return __fdiv_rn(v, so); }
+
 __device__ __forceinline__ float div_out_scale(float v, const EpiCtx& c) {
-  if (!c.div_fast) return __fdiv_rn(v, c.so);
+  if (!c.div_fast) return ieee_div(v, c.so);
   const float q0 = v * c.so_inv;
   float q = __fmaf_rn(__fmaf_rn(-q0, c.so, v), c.so_inv, q0);
   // (q + 1.5 * 2^23) - 1.5 * 2^23 is q rounded half-to-even for |q| < 2^22: two
   // additions instead of a conversion-rate round instruction.
   const float frac = fabsf(q - ((q + 12582912.f) - 12582912.f));
-  if (fabsf(frac - 0.5f) < 1e-3f && fabsf(q) < 256.f) q = __fdiv_rn(v, c.so);
+  if (fabsf(frac - 0.5f) < 1e-3f && fabsf(q) < 256.f) q = ieee_div(v, c.so);
   return q;
 }
 
@@ -257,7 +262,7 @@ constexpr int kMmaK = 32;          // k per tcgen05.mma kind::i8
 constexpr int kEpiWarps = 16;
 constexpr int kEpiGroups = kEpiWarps / 4;
 constexpr int kTiledThreads = (kEpiWarps + 2) * 32;
-constexpr int kThreads = 192;      // small-M kernel: warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int kThreads = 576;      // small-M kernel: warp 0 TMA, warp 1 MMA, warps 2-17 epilogue
 
 template <int BN, int STAGES>
 struct TiledSmem {
@@ -480,6 +485,7 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 // ---------------------------------------------------------------- small M
 constexpr int kSmallMaxStages = 8;
+constexpr int kSmallMaxSplit = 8;   // K splits per channel block
 constexpr int kSplitCounterWords = 4096;  // int32 arrival counters at the front of the scratch
 constexpr int kSmallBarOffset = 200 * 1024;  // stages live below this offset
 constexpr int kSmallDynamic = kSmallBarOffset + 256 + 1024;
@@ -490,7 +496,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     const __grid_constant__ CUtensorMap tmap_x, EpiParams ep, int MT, int stages,
-                    int num_kb, int32_t* ws, int32_t* counters) {
+                    int num_kb, int32_t* ws, int32_t* counters, int kbs, int box_rows) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -499,7 +505,7 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kSmallMaxStages + s); };
   const uint32_t tfull_bar = bar_base + 8u * (2 * kSmallMaxStages);
-  const uint32_t stored_bar = bar_base + 8u * (2 * kSmallMaxStages + 1);   // 4 warps stored partials
+  const uint32_t stored_bar = bar_base + 8u * (2 * kSmallMaxStages + 1);   // 16 warps stored partials
   const uint32_t counted_bar = bar_base + 8u * (2 * kSmallMaxStages + 2);  // arrival count taken
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kSmallBarOffset + 8 * (2 * kSmallMaxStages + 3));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -514,7 +520,7 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   const int kb_end = static_cast<int>((static_cast<int64_t>(ks + 1) * num_kb) / split);
   const uint32_t w_bytes = kTileM * kTileKBytes;
   const uint32_t x_bytes = static_cast<uint32_t>(MT) * kTileKBytes;
-  const uint32_t stage_bytes = w_bytes + x_bytes;  // multiples of 1024 (MT >= 16)
+  const uint32_t stage_bytes = kbs * (w_bytes + x_bytes);  // multiples of 1024 (MT >= 16)
   const uint32_t tmem_cols = MT < 32 ? 32u : static_cast<uint32_t>(MT);
 
   if (threadIdx.x == 0) {
@@ -525,7 +531,7 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(tfull_bar, 1);
-    mbar_init(stored_bar, 4);
+    mbar_init(stored_bar, 16);
     mbar_init(counted_bar, 1);
     *abort_flag = 0;
     *last_flag = 0;
@@ -544,14 +550,27 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
+      // A stage holds `kbs` consecutive K blocks.  The weight boxes are issued
+      // row group by row group, the K blocks of a group back to back, so that
+      // requests for neighbouring 128-byte pieces of one weight row (one DRAM
+      // page) leave the SM close together.
+      for (int kb0 = kb_begin; kb0 < kb_end; kb0 += kbs) {
+        const int nk = kb_end - kb0 < kbs ? kb_end - kb0 : kbs;
         if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, &g_kernel_status,
                        kStatusTimeoutEmpty))
           break;
-        mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
+        mbar_arrive_expect_tx(full_bar(stage), nk * (w_bytes + x_bytes));
         const uint32_t w_dst = smem_base + stage * stage_bytes;
-        tma_load_2d(w_dst, &tmap_w, full_bar(stage), kb * kTileKBytes, n_blk * kTileM);
-        tma_load_2d(w_dst + w_bytes, &tmap_x, full_bar(stage), kb * kTileKBytes, 0);
+        const uint32_t x_dst = w_dst + kbs * w_bytes;
+        for (int r0 = 0; r0 < kTileM; r0 += box_rows) {
+          for (int c = 0; c < nk; ++c) {
+            tma_load_2d(w_dst + c * w_bytes + r0 * kTileKBytes, &tmap_w, full_bar(stage),
+                        (kb0 + c) * kTileKBytes, n_blk * kTileM + r0);
+          }
+        }
+        for (int c = 0; c < nk; ++c) {
+          tma_load_2d(x_dst + c * x_bytes, &tmap_x, full_bar(stage), (kb0 + c) * kTileKBytes, 0);
+        }
         if (++stage == stages) {
           stage = 0;
           phase ^= 1;
@@ -564,17 +583,21 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
+      for (int kb0 = kb_begin; kb0 < kb_end; kb0 += kbs) {
+        const int nk = kb_end - kb0 < kbs ? kb_end - kb0 : kbs;
         ok = mbar_wait(full_bar(stage), phase, abort_flag, &g_kernel_status, kStatusTimeoutFull);
         if (!ok) break;
         tc_fence_after();
         const uint32_t w_addr = smem_base + stage * stage_bytes;
-        const uint64_t a_desc = make_kmajor_sw128_desc(w_addr);
-        const uint64_t b_desc = make_kmajor_sw128_desc(w_addr + w_bytes);
+        const uint32_t x_addr = w_addr + kbs * w_bytes;
+        for (int c = 0; c < nk; ++c) {
+          const uint64_t a_desc = make_kmajor_sw128_desc(w_addr + c * w_bytes);
+          const uint64_t b_desc = make_kmajor_sw128_desc(x_addr + c * x_bytes);
 #pragma unroll
-        for (int k = 0; k < kTileKBytes / kMmaK; ++k) {
-          umma_i8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc,
-                  (kb != kb_begin || k != 0) ? 1u : 0u);
+          for (int k = 0; k < kTileKBytes / kMmaK; ++k) {
+            umma_i8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc,
+                    (kb0 + c != kb_begin || k != 0) ? 1u : 0u);
+          }
         }
         umma_commit(empty_bar(stage));
         if (++stage == stages) {
@@ -585,22 +608,38 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       if (ok) umma_commit(tfull_bar);
     }
   } else {
+    // Sixteen epilogue warps: warp w reads TMEM lane quadrant w & 3 (its 32
+    // channels) and activation rows 16 * g + [0, 16) (+64 when MT is 128),
+    // g = (w - 2) >> 2.  One warp per quadrant would walk all MT rows alone
+    // and, with nothing else resident to hide its latencies, cost more than
+    // the whole weight stream.
     const int q = warp & 3;
+    const int ew = warp - 2;  // 0..15
+    const int g = ew >> 2;
     const int et = threadIdx.x - 64;
     const int64_t n = static_cast<int64_t>(n_blk) * kTileM + q * 32 + lane;  // this thread's channel
     const bool n_ok = n < ep.N;
     const int64_t n_pad = static_cast<int64_t>(gridDim.x) * kTileM;
     EpiCtx ctx = make_epi_ctx(ep);
-    const float cs = n_ok ? col_scale(ep, n) : 0.f;
-    const float cb = n_ok ? col_bias(ep, n) : 0.f;
     OutT* out = reinterpret_cast<OutT*>(ep.out);
     const int Mrows = static_cast<int>(ep.M);
 
-    auto emit = [&](int m, int32_t acc) {
-      if (ctx.has_rs) ctx.rs = __ldg(ep.x_scale + m);
-      const float v = epi_value(acc, cs, cb, ctx);
-      store_one<OutT>(out + static_cast<int64_t>(m) * ep.ldo + n, v, acc);
-    };
+    // Column constants are fetched while the weight still streams.  With one
+    // split a thread finishes channel n; after a split-K sum it finishes the
+    // four channels n4 .. n4 + 3.
+    const int64_t n4 = static_cast<int64_t>(n_blk) * kTileM + lane * 4;
+    float cs = 0.f, cb = 0.f, cs4[4], cb4[4];
+    if (split == 1) {
+      cs = n_ok ? col_scale(ep, n) : 0.f;
+      cb = n_ok ? col_bias(ep, n) : 0.f;
+    } else {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const bool c_ok = n4 + c < ep.N;
+        cs4[c] = c_ok ? col_scale(ep, n4 + c) : 0.f;
+        cb4[c] = c_ok ? col_bias(ep, n4 + c) : 0.f;
+      }
+    }
 
     bool ok = mbar_wait(tfull_bar, 0, abort_flag, &g_kernel_status, kStatusTimeoutTmemFull);
     if (ok) {
@@ -608,7 +647,7 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
       if (split == 1) {
 #pragma unroll 1
-        for (int c = 0; c < MT / 16; ++c) {
+        for (int c = g; c < MT / 16; c += 4) {
           if (c * 16 >= Mrows) break;
           uint32_t r[16];
           tmem_ld_x16(t_row + c * 16, r);
@@ -616,7 +655,11 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int m = c * 16 + j;
-            if (m < Mrows && n_ok) emit(m, static_cast<int32_t>(r[j]));
+            if (m < Mrows && n_ok) {
+              if (ctx.has_rs) ctx.rs = __ldg(ep.x_scale + m);
+              const int32_t acc = static_cast<int32_t>(r[j]);
+              store_one<OutT>(out + static_cast<int64_t>(m) * ep.ldo + n, epi_value(acc, cs, cb, ctx), acc);
+            }
           }
         }
       } else {
@@ -625,7 +668,7 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         int32_t* my_ws = ws + static_cast<int64_t>(ks) * Mrows * n_pad;
         const int64_t n_ws = static_cast<int64_t>(n_blk) * kTileM + q * 32 + lane;
 #pragma unroll 1
-        for (int c = 0; c < MT / 16; ++c) {
+        for (int c = g; c < MT / 16; c += 4) {
           if (c * 16 >= Mrows) break;
           uint32_t r[16];
           tmem_ld_x16(t_row + c * 16, r);
@@ -650,19 +693,44 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         ok = mbar_wait(counted_bar, 0, abort_flag, &g_kernel_status, kStatusTimeoutSplitK);
         if (ok && *last_flag) {
           __threadfence();
-          // eight rows at a time so that the loads of a round are independent
-          for (int m0 = 0; m0 < Mrows; m0 += 8) {
-            int32_t acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (int s = 0; s < split; ++s) {
-              const int32_t* part = ws + static_cast<int64_t>(s) * Mrows * n_pad + n_ws;
+          // The sum is latency bound (the partials sit in L2), so every thread
+          // keeps many independent 16-byte loads in flight: it owns four
+          // consecutive channels, the sixteen warps interleave rows, and all
+          // splits of a row are read at once.
+          const int64_t slab = static_cast<int64_t>(Mrows) * n_pad;
+          for (int m0 = ew; m0 < Mrows; m0 += 32) {
+            int4 acc[2];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                if (m0 + j < Mrows) acc[j] += __ldcg(part + static_cast<int64_t>(m0 + j) * n_pad);
+            for (int r = 0; r < 2; ++r) acc[r] = make_int4(0, 0, 0, 0);
+#pragma unroll
+            for (int s = 0; s < kSmallMaxSplit; ++s) {
+              if (s < split) {
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                  const int m = m0 + 16 * r;
+                  if (m < Mrows) {
+                    const int4 v = __ldcg(reinterpret_cast<const int4*>(
+                        ws + s * slab + static_cast<int64_t>(m) * n_pad + n4));
+                    acc[r].x += v.x;
+                    acc[r].y += v.y;
+                    acc[r].z += v.z;
+                    acc[r].w += v.w;
+                  }
+                }
               }
             }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (m0 + j < Mrows && n_ok) emit(m0 + j, acc[j]);
+            for (int r = 0; r < 2; ++r) {
+              const int m = m0 + 16 * r;
+              if (m < Mrows) {
+                if (ctx.has_rs) ctx.rs = __ldg(ep.x_scale + m);
+                const int32_t a4[4] = {acc[r].x, acc[r].y, acc[r].z, acc[r].w};
+                OutT* orow = out + static_cast<int64_t>(m) * ep.ldo + n4;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                  if (n4 + c < ep.N) store_one<OutT>(orow + c, epi_value(a4[c], cs4[c], cb4[c], ctx), a4[c]);
+                }
+              }
             }
           }
           if (et == 0) counters[n_blk] = 0;  // ready for the next launch
@@ -775,15 +843,37 @@ bool tma_ok(const QGemmParams& p) {
          (reinterpret_cast<uintptr_t>(p.a) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.w) & 15) == 0;
 }
 
+// The same int8 [rows, K] operand seen as [K / 128 blocks][rows][128 bytes] (K a
+// multiple of 128): one box = `box_kb` consecutive K blocks of `box_rows` rows,
+// which land in shared memory as `box_kb` consecutive 128B-swizzled tiles.
+bool make_tmap_kblocks(CUtensorMap* tm, const int8_t* base, int64_t rows, int64_t K, int64_t ld,
+                       int box_rows, int box_kb) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn || K % kTileKBytes != 0) return false;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(kTileKBytes), static_cast<cuuint64_t>(rows),
+                        static_cast<cuuint64_t>(K / kTileKBytes)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld), static_cast<cuuint64_t>(kTileKBytes)};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(kTileKBytes), static_cast<cuuint32_t>(box_rows),
+                       static_cast<cuuint32_t>(box_kb)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 int small_mt(int64_t M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
 
 int small_split(const QGemmParams& p) {
   const int num_kb = static_cast<int>((p.K + kTileKBytes - 1) / kTileKBytes);
-  if (p.split_k > 0) return p.split_k < num_kb ? p.split_k : num_kb;
+  if (p.split_k > 0) {
+    const int want = p.split_k < kSmallMaxSplit ? p.split_k : kSmallMaxSplit;
+    return want < num_kb ? want : num_kb;
+  }
   const int tiles_n = static_cast<int>((p.N + kTileM - 1) / kTileM);
   int s = sm_count() / tiles_n;
   if (s < 1) s = 1;
-  if (s > 8) s = 8;
+  if (s > kSmallMaxSplit) s = kSmallMaxSplit;
   if (s > num_kb) s = num_kb;
   return s;
 }
@@ -894,7 +984,9 @@ cudaError_t launch_smallm(const QGemmParams& p, cudaStream_t stream, const char*
   const int split = small_split(p);
   const int tiles_n = static_cast<int>((p.N + kTileM - 1) / kTileM);
   const int num_kb = static_cast<int>((p.K + kTileKBytes - 1) / kTileKBytes);
-  const int stage_bytes = (kTileM + MT) * kTileKBytes;
+  const int kbs = 4;            // K blocks per pipeline stage
+  const int box_rows = kTileM;  // weight rows per TMA box
+  const int stage_bytes = kbs * (kTileM + MT) * kTileKBytes;
   int stages = kSmallBarOffset / stage_bytes;
   if (stages > kSmallMaxStages) stages = kSmallMaxStages;
   int32_t* ws = nullptr;
@@ -912,7 +1004,7 @@ cudaError_t launch_smallm(const QGemmParams& p, cudaStream_t stream, const char*
     ws = p.splitk_ws + kSplitCounterWords;
   }
   CUtensorMap tw, tx;
-  if (!make_tmap(&tw, p.w, p.N, p.K, p.ldw, kTileM) || !make_tmap(&tx, p.a, p.M, p.K, p.lda, MT)) {
+  if (!make_tmap(&tw, p.w, p.N, p.K, p.ldw, box_rows) || !make_tmap(&tx, p.a, p.M, p.K, p.lda, MT)) {
     if (err) *err = "cuTensorMapEncodeTiled failed";
     return cudaErrorInvalidValue;
   }
@@ -922,7 +1014,7 @@ cudaError_t launch_smallm(const QGemmParams& p, cudaStream_t stream, const char*
   if (st != cudaSuccess) return st;
   dim3 grid(tiles_n, split);
   kern<<<grid, kThreads, kSmallDynamic, stream>>>(tw, tx, make_epi(p), MT, stages, num_kb, ws,
-                                                  counters);
+                                                  counters, kbs, box_rows);
   return cudaGetLastError();
 }
 
@@ -939,11 +1031,58 @@ cudaError_t launch_simt(const QGemmParams& p, cudaStream_t stream, const char** 
 }
 
 #include "qgemm_gemv.inl"
+#include "qgemm_skinny.inl"
+
+// Channels per CTA of the few-row path: one wave of CTAs over N (per row tile).
+int skinny_bn(const QGemmParams& p) {
+  const int64_t tiles_m = (p.M + kTileM - 1) / kTileM;
+  int64_t ctas = sm_count() / tiles_m;
+  if (ctas < 1) ctas = 1;
+  int64_t bn = (p.N + ctas - 1) / ctas;
+  bn = (bn + 15) / 16 * 16;
+  if (bn < 16) bn = 16;
+  if (bn > kSkinnyMaxBN) bn = kSkinnyMaxBN;
+  return static_cast<int>(bn);
+}
+
+template <typename OutT>
+cudaError_t launch_skinny(const QGemmParams& p, cudaStream_t stream, const char** err) {
+  const int MT = p.M > 64 ? kTileM : small_mt(p.M);
+  const int BN = skinny_bn(p);
+  // K blocks per stage: as many as leave at least three stages in flight.
+  int kbs = 4;
+  while (kbs > 1 && 3 * kbs * (BN + MT) * kTileKBytes > kSkinnyStageRegion) kbs >>= 1;
+  int stages = kSkinnyStageRegion / (kbs * (BN + MT) * kTileKBytes);
+  if (stages > 4) stages = 4;  // 100+ KB in flight per SM is plenty; more only delays the start
+  CUtensorMap tx, tw;
+  // One box per operand and stage when K is a whole number of 128-byte blocks.
+  const int k3d = (p.K % kTileKBytes == 0) ? 1 : 0;
+  const bool maps_ok =
+      k3d ? (make_tmap_kblocks(&tx, p.a, p.M, p.K, p.lda, MT, kbs) &&
+             make_tmap_kblocks(&tw, p.w, p.N, p.K, p.ldw, BN, kbs))
+          : (make_tmap(&tx, p.a, p.M, p.K, p.lda, MT) && make_tmap(&tw, p.w, p.N, p.K, p.ldw, BN));
+  if (!maps_ok) {
+    if (err) *err = "cuTensorMapEncodeTiled failed";
+    return cudaErrorInvalidValue;
+  }
+  auto kern = qgemm_skinny_kernel<OutT>;
+  cudaError_t st =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkinnyDynamic);
+  if (st != cudaSuccess) return st;
+  const int num_kb = static_cast<int>((p.K + kTileKBytes - 1) / kTileKBytes);
+  const int eb = out_elem_bytes(p.out_dtype);
+  const int vec_ok = ((p.ldo * eb) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+  dim3 grid(static_cast<unsigned>((p.N + BN - 1) / BN), static_cast<unsigned>((p.M + kTileM - 1) / kTileM));
+  kern<<<grid, kThreads, kSkinnyDynamic, stream>>>(tx, tw, make_epi(p), MT, BN, stages, kbs, num_kb,
+                                                   vec_ok, k3d);
+  return cudaGetLastError();
+}
 
 template <typename OutT>
 cudaError_t dispatch(const QGemmParams& p, int path, cudaStream_t stream, const char** err) {
   switch (path) {
     case kPathGemv: return launch_gemv<OutT>(p, stream, err);
+    case kPathSkinny: return launch_skinny<OutT>(p, stream, err);
     case kPathTiled: return launch_tiled<OutT>(p, stream, err);
     case kPathSmallM: return launch_smallm<OutT>(p, stream, err);
     case kPathPair: return launch_pair<OutT>(p, stream, err);
@@ -959,9 +1098,15 @@ int qgemm_choose_path(const QGemmParams& p) {
   if (p.path == kPathSmallM && p.M <= 128) return kPathSmallM;
   if (p.path == kPathTiled) return kPathTiled;
   if (p.path == kPathPair) return kPathPair;
+  if (p.path == kPathSkinny && p.M <= 65535 * kTileM) return kPathSkinny;
   if (p.path == kPathGemv && p.M <= 8 && p.K <= kGemvMaxK) return kPathGemv;
-  if (p.path == kPathAuto && p.M <= 8 && p.K <= kGemvMaxK) return kPathGemv;
-  if (p.M <= 64) return kPathSmallM;
+  // One to a few rows: the dp4a stream; from five rows on a large weight is
+  // cheaper through the tensor cores.
+  if (p.M <= 8 && p.K <= kGemvMaxK && (p.M <= 4 || p.N * p.K < (int64_t{1} << 25))) return kPathGemv;
+  // Few rows: fine channel blocks over the full K, as long as one wave of CTAs
+  // covers the output.
+  const int64_t skinny_ctas = ((p.N + skinny_bn(p) - 1) / skinny_bn(p)) * ((p.M + kTileM - 1) / kTileM);
+  if (p.M <= 128 || (p.M <= 512 && skinny_ctas <= sm_count())) return kPathSkinny;
   // CTA pairs compute 256 x 256 tiles: worth it once there are enough of them
   // to occupy every pair of SMs.
   const int64_t pair_tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);

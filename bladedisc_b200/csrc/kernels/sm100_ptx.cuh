@@ -192,6 +192,16 @@ __device__ __forceinline__ void cluster_sync_all() {
 // In a shared::cluster address bit 24 selects the odd CTA of a pair; clearing
 // it names the same offset in the even (leader) CTA.
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
+// 3-D tiled load, no multicast (coordinates innermost first).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x,
+                                            int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 // Tiled load issued by either CTA of a pair: the box lands in the issuing CTA's
 // shared memory, the bytes are counted on the LEADER's mbarrier.  No multicast.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m,

@@ -19,7 +19,7 @@ OUT_I8, OUT_F16, OUT_F32, OUT_I32 = 0, 1, 2, 3
 ACT_NONE, ACT_GELU, ACT_SILU = 0, 1, 2
 BIAS_NONE, BIAS_F32, BIAS_I8 = 0, 1, 2
 SCALE_NONE, SCALE_SCALAR, SCALE_PER_COL, SCALE_PER_ROW = 0, 1, 2, 3
-PATH_AUTO, PATH_TILED, PATH_SMALL_M, PATH_SIMT, PATH_PAIR, PATH_GEMV = 0, 1, 2, 3, 4, 5
+PATH_AUTO, PATH_TILED, PATH_SMALL_M, PATH_SIMT, PATH_PAIR, PATH_GEMV, PATH_SKINNY = 0, 1, 2, 3, 4, 5, 6
 F32, F16 = 0, 1
 
 

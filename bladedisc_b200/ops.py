@@ -17,7 +17,7 @@ _OUT = {torch.int8: _lib.OUT_I8, torch.float16: _lib.OUT_F16, torch.float32: _li
         torch.int32: _lib.OUT_I32}
 _PATH = {None: _lib.PATH_AUTO, "auto": _lib.PATH_AUTO, "tiled": _lib.PATH_TILED,
          "small_m": _lib.PATH_SMALL_M, "simt": _lib.PATH_SIMT, "pair": _lib.PATH_PAIR,
-         "gemv": _lib.PATH_GEMV}
+         "gemv": _lib.PATH_GEMV, "skinny": _lib.PATH_SKINNY}
 _scratch = {}
 
 
@@ -141,7 +141,7 @@ def qgemm_path(M: int, N: int, K: int) -> str:
     args.a, args.w, args.out = 16, 16, 16
     args.M, args.N, args.K, args.lda, args.ldw, args.ldo = M, N, K, K, K, N
     code = _lib.load().disc_b200_qgemm_path(ctypes.byref(args))
-    return {1: "tiled", 2: "small_m", 3: "simt", 4: "pair", 5: "gemv"}[code]
+    return {1: "tiled", 2: "small_m", 3: "simt", 4: "pair", 5: "gemv", 6: "skinny"}[code]
 
 
 def quantize(x: torch.Tensor, scale: torch.Tensor, zero_point: Optional[torch.Tensor] = None,

@@ -107,7 +107,8 @@ enum { DISC_B200_BIAS_NONE = 0, DISC_B200_BIAS_F32 = 1, DISC_B200_BIAS_I8 = 2 };
 enum { DISC_B200_SCALE_NONE = 0, DISC_B200_SCALE_SCALAR = 1, DISC_B200_SCALE_PER_COL = 2,
        DISC_B200_SCALE_PER_ROW = 3 };
 enum { DISC_B200_PATH_AUTO = 0, DISC_B200_PATH_TILED = 1, DISC_B200_PATH_SMALL_M = 2,
-       DISC_B200_PATH_SIMT = 3, DISC_B200_PATH_PAIR = 4, DISC_B200_PATH_GEMV = 5 };
+       DISC_B200_PATH_SIMT = 3, DISC_B200_PATH_PAIR = 4, DISC_B200_PATH_GEMV = 5,
+       DISC_B200_PATH_SKINNY = 6 };
 enum { DISC_B200_F32 = 0, DISC_B200_F16 = 1 };
 
 /* out[m, n] = epilogue(sum_k a[m, k] * w[n, k]); a int8 [M, K], w int8 [N, K],

@@ -50,7 +50,8 @@ def test_accumulators_bit_exact(ops, M, K, N):
 
 
 @pytest.mark.parametrize("path,M", [("tiled", 96), ("tiled", 1), ("small_m", 128), ("small_m", 100),
-                                    ("simt", 70), ("small_m", 5)])
+                                    ("simt", 70), ("small_m", 5), ("skinny", 1), ("skinny", 70),
+                                    ("skinny", 128), ("skinny", 300)])
 def test_forced_paths_agree(ops, path, M):
     from oracle import c
     rng = np.random.default_rng(11)
@@ -93,6 +94,54 @@ def test_cta_pair_path(ops, M, K, N, out_dtype):
         else:
             ok = np.abs(want) < 60000
             assert np.allclose(got[ok], want[ok], rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("M,K,N", [(9, 768, 768), (16, 128, 16), (33, 144, 80), (64, 4096, 520), (100, 640, 392),
+                                   (128, 2064, 264), (129, 256, 384), (300, 640, 1000), (333, 768, 3072),
+                                   (48, 3072, 72), (600, 1024, 777)])
+@pytest.mark.parametrize("out_dtype", [torch.int32, torch.int8, torch.float16, torch.float32])
+def test_skinny_path(ops, M, K, N, out_dtype):
+    """The few-row kernel (fine channel blocks over the full K, one box per
+    operand and stage when K is a multiple of 128, per-block boxes otherwise),
+    forced on ragged rows / columns / K tails, several row tiles, and both
+    store routes (N = 72 or 777 with int8 output leaves by scalar stores)."""
+    from oracle import c
+    rng = np.random.default_rng(M * 3 + K + N)
+    a, w = _rand_i8(rng, (M, K)), _rand_i8(rng, (N, K))
+    acc = c.qgemm_acc(a, w)
+    if out_dtype == torch.int32:
+        got = ops.qgemm(_dev(a), _dev(w), out_dtype=torch.int32, path="skinny").cpu().numpy()
+        assert (got == acc).all()
+        return
+    sw = (rng.random(N) * 9e-3 + 1e-3).astype(np.float32)
+    bias = (rng.standard_normal(N) * 0.5).astype(np.float32)
+    sx = (rng.random(M) * 0.03 + 0.01).astype(np.float32)  # per-row (dynamic) activation scales
+    s_out = np.float32(0.05)
+    kw = dict(x_scale=_dev(sx), w_scale=_dev(sw), bias=_dev(bias), path="skinny")
+    if out_dtype == torch.int8:
+        _, want = c.qgemm_epilogue(acc, x_scale=sx, w_scale=sw, out_scale=s_out, bias=bias, div_out=True)
+        buf = torch.full((M + 2, N), 99, dtype=torch.int8, device="cuda")
+        ops.qgemm(_dev(a), _dev(w), out_scale=_dev(np.array([s_out])), out=buf[1:M + 1], **kw)
+        assert (buf[1:M + 1].cpu().numpy() == want).all()
+        assert (buf[0] == 99).all() and (buf[M + 1] == 99).all()
+    else:
+        want, _ = c.qgemm_epilogue(acc, x_scale=sx, w_scale=sw, bias=bias)
+        got = ops.qgemm(_dev(a), _dev(w), out_dtype=out_dtype, **kw).float().cpu().numpy()
+        if out_dtype == torch.float32:
+            assert (got == want).all()
+        else:
+            ok = np.abs(want) < 60000
+            assert np.allclose(got[ok], want[ok], rtol=RTOL, atol=ATOL)
+
+
+def test_auto_path_by_rows(ops):
+    assert ops.qgemm_path(1, 4096, 4096) == "gemv"
+    assert ops.qgemm_path(7, 11008, 4096) == "skinny"
+    assert ops.qgemm_path(64, 4096, 4096) == "skinny"
+    assert ops.qgemm_path(128, 768, 3072) == "skinny"
+    assert ops.qgemm_path(333, 4096, 4096) == "skinny"
+    assert ops.qgemm_path(1024, 4096, 4096) in ("tiled", "pair")
+    assert ops.qgemm_path(16384, 4096, 4096) == "pair"
 
 
 @pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 8])
