@@ -98,6 +98,9 @@ disc_b200::QGemmParams to_params(const disc_b200_qgemm_args* a) {
   p.split_k = a->split_k;
   p.splitk_ws = static_cast<int32_t*>(a->splitk_ws);
   p.splitk_ws_bytes = a->splitk_ws_bytes;
+  p.a_slabs = a->a_slabs;
+  p.a_slab_cols = a->a_slab_cols;
+  p.a_slab_stride = a->a_slab_stride;
   return p;
 }
 

@@ -55,6 +55,14 @@ struct QGemmParams {
   // clearing).  Needed only when the launch splits K.
   int32_t* splitk_ws;
   int64_t splitk_ws_bytes;
+  // Activation operand stored as `a_slabs` column slabs, the layout an
+  // all-gather of column-parallel outputs leaves behind: element (m, k) lives at
+  // a[(k / a_slab_cols) * a_slab_stride + m * lda + k % a_slab_cols], with
+  // K = a_slabs * a_slab_cols.  a_slabs <= 1 means plain row-major.  Slabs need
+  // a_slab_cols and lda multiples of 16 and a_slab_stride a multiple of lda.
+  int a_slabs;
+  int64_t a_slab_cols;
+  int64_t a_slab_stride;
 };
 
 // Bytes of zeroed scratch the small-M path may need for a given problem.

@@ -125,7 +125,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTiledThreads, 1)
 qgemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_w,
                   const __grid_constant__ CUtensorMap tmap_out, EpiParams ep, int num_kb, int tiles_m,
-                  int tiles_n, int use_tma_store, int vec_ok) {
+                  int tiles_n, int use_tma_store, int vec_ok, SlabA slab) {
   using L = PairSmem;
   constexpr int STAGES = kPairStages;
   constexpr int BN = kPairBN;
@@ -194,9 +194,9 @@ qgemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (!ok) break;
           if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * kPairStageBytes);
           const uint32_t a_dst = smem_base + stage * kPairStageBytes;
-          tma_load_2d_pair(a_dst, &tmap_a, full_bar(stage), kb * kTileKBytes, a_row);
-          tma_load_2d_pair(a_dst + kTileM * kTileKBytes, &tmap_w, full_bar(stage), kb * kTileKBytes,
-                           w_row);
+          const KCoord kc = k_coord(slab, kb);
+          tma_load_2d_pair(a_dst, &tmap_a, full_bar(stage), kc.ax, kc.ay + a_row);
+          tma_load_2d_pair(a_dst + kTileM * kTileKBytes, &tmap_w, full_bar(stage), kc.wx, w_row);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;

@@ -59,7 +59,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
                     const __grid_constant__ CUtensorMap tmap_w, EpiParams ep, int MT, int BN,
-                    int stages, int kbs, int num_kb, int vec_ok, int k3d) {
+                    int stages, int kbs, int num_kb, int vec_ok, int k3d, SlabA slab) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -97,12 +97,9 @@ qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const int nk = num_kb - kb0 < kbs ? num_kb - kb0 : kbs;
     mbar_arrive_expect_tx(full_bar(stage), nk * (w_bytes + x_bytes));
     for (int c = 0; c < nk; ++c) {
-      tma_load_2d(w_dst + c * w_bytes, &tmap_w, full_bar(stage), (kb0 + c) * kTileKBytes,
-                  static_cast<int>(n0));
-    }
-    for (int c = 0; c < nk; ++c) {
-      tma_load_2d(x_dst + c * x_bytes, &tmap_x, full_bar(stage), (kb0 + c) * kTileKBytes,
-                  static_cast<int>(m0));
+      const KCoord kc = k_coord(slab, kb0 + c);
+      tma_load_2d(w_dst + c * w_bytes, &tmap_w, full_bar(stage), kc.wx, static_cast<int>(n0));
+      tma_load_2d(x_dst + c * x_bytes, &tmap_x, full_bar(stage), kc.ax, kc.ay + static_cast<int>(m0));
     }
   };
 

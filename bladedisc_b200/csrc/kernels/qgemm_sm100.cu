@@ -46,6 +46,31 @@ struct EpiParams {
   int x_kind, w_kind, o_kind, bias_kind, fold_out, div_out, act;
 };
 
+// Where K block `kb` of the two operands starts when the activation is stored
+// as column slabs (kb_per_slab == 0: plain row-major, x = 128 * kb for both).
+struct SlabA {
+  int kb_per_slab;  // K blocks per slab = ceil(slab_cols / 128)
+  int slab_rows;    // rows of the activation tensor map between two slabs
+  int slab_cols;    // K extent of one slab
+};
+struct KCoord {
+  int ax, ay, wx;  // activation x, activation row offset, weight x
+};
+__device__ __forceinline__ KCoord k_coord(const SlabA& s, int kb) {
+  KCoord c;
+  if (s.kb_per_slab == 0) {
+    c.ax = c.wx = kb * 128;
+    c.ay = 0;
+  } else {
+    const int slab = kb / s.kb_per_slab;
+    const int kin = kb - slab * s.kb_per_slab;
+    c.ax = kin * 128;
+    c.ay = slab * s.slab_rows;
+    c.wx = slab * s.slab_cols + kin * 128;  // the tail of a ragged slab meets zeros of the activation
+  }
+  return c;
+}
+
 __device__ __forceinline__ float col_scale(const EpiParams& e, int64_t n) {
   float sx = 1.f;
   if (e.x_kind == kScaleScalar) sx = __ldg(e.x_scale);
@@ -315,7 +340,7 @@ template <int BN, int STAGES, typename OutT>
 __global__ void __launch_bounds__(kTiledThreads, 1)
 qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
                    const __grid_constant__ CUtensorMap tmap_w, EpiParams ep, int num_kb, int tiles_m,
-                   int tiles_n, int vec_ok) {
+                   int tiles_n, int vec_ok, SlabA slab) {
   using L = TiledSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -375,8 +400,9 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (!ok) break;
           mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
           const uint32_t a_dst = smem_base + stage * L::kStageBytes;
-          tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * kTileKBytes, m_blk * kTileM);
-          tma_load_2d(a_dst + L::kABytes, &tmap_w, full_bar(stage), kb * kTileKBytes, n_blk * BN);
+          const KCoord kc = k_coord(slab, kb);
+          tma_load_2d(a_dst, &tmap_a, full_bar(stage), kc.ax, kc.ay + m_blk * kTileM);
+          tma_load_2d(a_dst + L::kABytes, &tmap_w, full_bar(stage), kc.wx, n_blk * BN);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -755,14 +781,22 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
 // -------------------------------------------------------------------- simt
 template <typename OutT>
 __global__ void qgemm_simt_kernel(const int8_t* __restrict__ a, const int8_t* __restrict__ w,
-                                  int64_t K, int64_t lda, int64_t ldw, EpiParams ep) {
+                                  int64_t K, int64_t lda, int64_t ldw, EpiParams ep,
+                                  int64_t slab_cols, int64_t slab_stride) {
   const int64_t n = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   const int64_t m = blockIdx.y;
   if (n >= ep.N || m >= ep.M) return;
   const int8_t* ar = a + m * lda;
   const int8_t* wr = w + n * ldw;
   int32_t acc = 0;
-  for (int64_t k = 0; k < K; ++k) acc += static_cast<int32_t>(ar[k]) * static_cast<int32_t>(wr[k]);
+  if (slab_cols > 0) {
+    for (int64_t k = 0; k < K; ++k) {
+      const int64_t s = k / slab_cols;
+      acc += static_cast<int32_t>(ar[s * slab_stride + (k - s * slab_cols)]) * static_cast<int32_t>(wr[k]);
+    }
+  } else {
+    for (int64_t k = 0; k < K; ++k) acc += static_cast<int32_t>(ar[k]) * static_cast<int32_t>(wr[k]);
+  }
   EpiCtx ctx = make_epi_ctx(ep);
   if (ctx.has_rs) ctx.rs = ep.x_scale[m];
   const float v = epi_value(acc, col_scale(ep, n), col_bias(ep, n), ctx);
@@ -839,6 +873,7 @@ EpiParams make_epi(const QGemmParams& p) {
 int out_elem_bytes(int dt) { return dt == kOutI8 ? 1 : (dt == kOutF16 ? 2 : 4); }
 
 bool tma_ok(const QGemmParams& p) {
+  if (p.a_slabs > 1 && (p.a_slab_cols % 16 != 0 || p.a_slab_stride % p.lda != 0)) return false;
   return p.K % 16 == 0 && p.lda % 16 == 0 && p.ldw % 16 == 0 &&
          (reinterpret_cast<uintptr_t>(p.a) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.w) & 15) == 0;
 }
@@ -862,6 +897,30 @@ bool make_tmap_kblocks(CUtensorMap* tm, const int8_t* base, int64_t rows, int64_
   return r == CUDA_SUCCESS;
 }
 
+// Host view of the slab layout of the activation operand.
+bool has_slabs(const QGemmParams& p) { return p.a_slabs > 1; }
+SlabA slab_of(const QGemmParams& p) {
+  SlabA s = {0, 0, 0};
+  if (has_slabs(p)) {
+    s.kb_per_slab = static_cast<int>((p.a_slab_cols + kTileKBytes - 1) / kTileKBytes);
+    s.slab_rows = static_cast<int>(p.a_slab_stride / p.lda);
+    s.slab_cols = static_cast<int>(p.a_slab_cols);
+  }
+  return s;
+}
+int num_k_blocks(const QGemmParams& p) {
+  if (has_slabs(p)) return p.a_slabs * slab_of(p).kb_per_slab;
+  return static_cast<int>((p.K + kTileKBytes - 1) / kTileKBytes);
+}
+// Activation tensor map: plain [M, K], or all slabs stacked along the rows,
+// [(a_slabs - 1) * slab_rows + M, a_slab_cols] (rows past M of a slab are the
+// next slab's; they only reach accumulator rows that are never stored).
+bool make_a_tmap(CUtensorMap* tm, const QGemmParams& p, int box_rows) {
+  if (!has_slabs(p)) return make_tmap(tm, p.a, p.M, p.K, p.lda, box_rows);
+  const int64_t rows = (p.a_slabs - 1) * (p.a_slab_stride / p.lda) + p.M;
+  return make_tmap(tm, p.a, rows, p.a_slab_cols, p.lda, box_rows);
+}
+
 int small_mt(int64_t M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
 
 int small_split(const QGemmParams& p) {
@@ -882,7 +941,7 @@ template <typename OutT, int BN, int STAGES>
 cudaError_t launch_tiled_t(const QGemmParams& p, cudaStream_t stream, const char** err) {
   using L = TiledSmem<BN, STAGES>;
   CUtensorMap ta, tw;
-  if (!make_tmap(&ta, p.a, p.M, p.K, p.lda, kTileM) || !make_tmap(&tw, p.w, p.N, p.K, p.ldw, BN)) {
+  if (!make_a_tmap(&ta, p, kTileM) || !make_tmap(&tw, p.w, p.N, p.K, p.ldw, BN)) {
     if (err) *err = "cuTensorMapEncodeTiled failed";
     return cudaErrorInvalidValue;
   }
@@ -892,12 +951,13 @@ cudaError_t launch_tiled_t(const QGemmParams& p, cudaStream_t stream, const char
   if (st != cudaSuccess) return st;
   const int tiles_m = static_cast<int>((p.M + kTileM - 1) / kTileM);
   const int tiles_n = static_cast<int>((p.N + BN - 1) / BN);
-  const int num_kb = static_cast<int>((p.K + kTileKBytes - 1) / kTileKBytes);
+  const int num_kb = num_k_blocks(p);
   const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
   const int eb = out_elem_bytes(p.out_dtype);
   const int vec_ok = ((p.ldo * eb) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
-  kern<<<grid, kTiledThreads, L::kDynamic, stream>>>(ta, tw, make_epi(p), num_kb, tiles_m, tiles_n, vec_ok);
+  kern<<<grid, kTiledThreads, L::kDynamic, stream>>>(ta, tw, make_epi(p), num_kb, tiles_m, tiles_n, vec_ok,
+                                                   slab_of(p));
   return cudaGetLastError();
 }
 
@@ -950,7 +1010,7 @@ int pair_max_clusters() {
 template <typename OutT>
 cudaError_t launch_pair(const QGemmParams& p, cudaStream_t stream, const char** err) {
   CUtensorMap ta, tw, to;
-  if (!make_tmap(&ta, p.a, p.M, p.K, p.lda, kTileM) || !make_tmap(&tw, p.w, p.N, p.K, p.ldw, kTileM)) {
+  if (!make_a_tmap(&ta, p, kTileM) || !make_tmap(&tw, p.w, p.N, p.K, p.ldw, kTileM)) {
     if (err) *err = "cuTensorMapEncodeTiled failed";
     return cudaErrorInvalidValue;
   }
@@ -968,13 +1028,13 @@ cudaError_t launch_pair(const QGemmParams& p, cudaStream_t stream, const char** 
   if (st != cudaSuccess) return st;
   const int tiles_m = static_cast<int>((p.M + 2 * kTileM - 1) / (2 * kTileM));
   const int tiles_n = static_cast<int>((p.N + kPairBN - 1) / kPairBN);
-  const int num_kb = static_cast<int>((p.K + kTileKBytes - 1) / kTileKBytes);
+  const int num_kb = num_k_blocks(p);
   const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n;
   const int max_clusters = pair_max_clusters<OutT>();
   const int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   kern<<<2 * clusters, kTiledThreads, PairSmem::kDynamic, stream>>>(ta, tw, to, make_epi(p), num_kb,
                                                                    tiles_m, tiles_n, use_tma_store,
-                                                                   out_aligned ? 1 : 0);
+                                                                   out_aligned ? 1 : 0, slab_of(p));
   return cudaGetLastError();
 }
 
@@ -1026,7 +1086,8 @@ cudaError_t launch_simt(const QGemmParams& p, cudaStream_t stream, const char** 
   }
   dim3 block(128);
   dim3 grid(static_cast<unsigned>((p.N + 127) / 128), static_cast<unsigned>(p.M));
-  qgemm_simt_kernel<OutT><<<grid, block, 0, stream>>>(p.a, p.w, p.K, p.lda, p.ldw, make_epi(p));
+  qgemm_simt_kernel<OutT><<<grid, block, 0, stream>>>(p.a, p.w, p.K, p.lda, p.ldw, make_epi(p),
+                                                      p.a_slabs > 1 ? p.a_slab_cols : 0, p.a_slab_stride);
   return cudaGetLastError();
 }
 
@@ -1056,11 +1117,11 @@ cudaError_t launch_skinny(const QGemmParams& p, cudaStream_t stream, const char*
   if (stages > 4) stages = 4;  // 100+ KB in flight per SM is plenty; more only delays the start
   CUtensorMap tx, tw;
   // One box per operand and stage when K is a whole number of 128-byte blocks.
-  const int k3d = (p.K % kTileKBytes == 0) ? 1 : 0;
+  const int k3d = (p.K % kTileKBytes == 0 && !has_slabs(p)) ? 1 : 0;
   const bool maps_ok =
       k3d ? (make_tmap_kblocks(&tx, p.a, p.M, p.K, p.lda, MT, kbs) &&
              make_tmap_kblocks(&tw, p.w, p.N, p.K, p.ldw, BN, kbs))
-          : (make_tmap(&tx, p.a, p.M, p.K, p.lda, MT) && make_tmap(&tw, p.w, p.N, p.K, p.ldw, BN));
+          : (make_a_tmap(&tx, p, MT) && make_tmap(&tw, p.w, p.N, p.K, p.ldw, BN));
   if (!maps_ok) {
     if (err) *err = "cuTensorMapEncodeTiled failed";
     return cudaErrorInvalidValue;
@@ -1069,12 +1130,12 @@ cudaError_t launch_skinny(const QGemmParams& p, cudaStream_t stream, const char*
   cudaError_t st =
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkinnyDynamic);
   if (st != cudaSuccess) return st;
-  const int num_kb = static_cast<int>((p.K + kTileKBytes - 1) / kTileKBytes);
+  const int num_kb = num_k_blocks(p);
   const int eb = out_elem_bytes(p.out_dtype);
   const int vec_ok = ((p.ldo * eb) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
   dim3 grid(static_cast<unsigned>((p.N + BN - 1) / BN), static_cast<unsigned>((p.M + kTileM - 1) / kTileM));
   kern<<<grid, kThreads, kSkinnyDynamic, stream>>>(tx, tw, make_epi(p), MT, BN, stages, kbs, num_kb,
-                                                   vec_ok, k3d);
+                                                   vec_ok, k3d, slab_of(p));
   return cudaGetLastError();
 }
 
@@ -1095,14 +1156,16 @@ cudaError_t dispatch(const QGemmParams& p, int path, cudaStream_t stream, const 
 int qgemm_choose_path(const QGemmParams& p) {
   if (!tma_ok(p)) return kPathSimt;
   if (p.path == kPathSimt) return kPathSimt;
-  if (p.path == kPathSmallM && p.M <= 128) return kPathSmallM;
+  if (p.path == kPathSmallM && p.M <= 128 && p.a_slabs <= 1) return kPathSmallM;
   if (p.path == kPathTiled) return kPathTiled;
   if (p.path == kPathPair) return kPathPair;
   if (p.path == kPathSkinny && p.M <= 65535 * kTileM) return kPathSkinny;
-  if (p.path == kPathGemv && p.M <= 8 && p.K <= kGemvMaxK) return kPathGemv;
+  if (p.path == kPathGemv && p.M <= 8 && p.K <= kGemvMaxK && p.a_slabs <= 1) return kPathGemv;
   // One to a few rows: the dp4a stream; from five rows on a large weight is
   // cheaper through the tensor cores.
-  if (p.M <= 8 && p.K <= kGemvMaxK && (p.M <= 4 || p.N * p.K < (int64_t{1} << 25))) return kPathGemv;
+  const bool slabs = p.a_slabs > 1;  // read by the TMA paths (and the fallback) only
+  if (!slabs && p.M <= 8 && p.K <= kGemvMaxK && (p.M <= 4 || p.N * p.K < (int64_t{1} << 25)))
+    return kPathGemv;
   // Few rows: fine channel blocks over the full K, as long as one wave of CTAs
   // covers the output.
   const int64_t skinny_ctas = ((p.N + skinny_bn(p) - 1) / skinny_bn(p)) * ((p.M + kTileM - 1) / kTileM);
@@ -1138,6 +1201,11 @@ cudaError_t qgemm_launch(const QGemmParams& p, cudaStream_t stream, const char**
   }
   if (p.div_out_scale && p.out_scale_kind == kScalePerCol) {
     if (err) *err = "qgemm: per-channel out_scale only in folded form";
+    return cudaErrorInvalidValue;
+  }
+  if (p.a_slabs > 1 && (p.a_slab_cols <= 0 || p.lda <= 0 || p.a_slab_cols > p.lda ||
+                        p.a_slabs * p.a_slab_cols != p.K)) {
+    if (err) *err = "qgemm: K must equal a_slabs * a_slab_cols (and a_slab_cols <= lda)";
     return cudaErrorInvalidValue;
   }
   const int path = qgemm_choose_path(p);

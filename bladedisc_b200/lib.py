@@ -48,6 +48,7 @@ class QGemmArgs(Structure):
         ("act", c_int32), ("out_dtype", c_int32),
         ("path", c_int32), ("split_k", c_int32),
         ("splitk_ws", c_void_p), ("splitk_ws_bytes", c_int64),
+        ("a_slabs", c_int32), ("a_slab_cols", c_int64), ("a_slab_stride", c_int64),
     ]
 
 

@@ -74,22 +74,29 @@ def qgemm(a: torch.Tensor, w: torch.Tensor, *, x_scale: Optional[torch.Tensor] =
           bias: Optional[torch.Tensor] = None, act: Optional[str] = None,
           out_dtype: torch.dtype = torch.int8, fold_out_scale: bool = False,
           x_scale_per_col: bool = False, path: Optional[str] = None, split_k: int = 0,
-          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+          out: Optional[torch.Tensor] = None, a_gathered: bool = False) -> torch.Tensor:
     """out = epilogue(a[..., K] @ w[N, K]^T) with int8 operands and int32 accumulation.
 
     ``fold_out_scale=True`` is the reference custom call ``ral_pdll_qgemm``:
     ``sat_s8(rne(acc * (x_scale * w_scale / out_scale) + bias))``.  Otherwise
     ``v = act(acc * x_scale * w_scale + bias)`` and int8 output divides ``v`` by
     ``out_scale`` before rounding.  Scales and bias are device tensors.
+
+    ``a_gathered=True``: ``a`` is ``[g, M, K / g]``, the buffer an all-gather of
+    column-parallel outputs leaves (slab ``r`` holds columns ``r * K / g ...``);
+    it is consumed in place, the result is ``[M, N]``.
     """
     a = _cuda(a, "a", torch.int8)
     w = _cuda(w, "w", torch.int8)
-    if w.dim() != 2 or a.shape[-1] != w.shape[1]:
+    if a_gathered:
+        if a.dim() != 3 or w.dim() != 2 or a.shape[0] * a.shape[2] != w.shape[1]:
+            raise ValueError(f"shape mismatch: gathered a {tuple(a.shape)} w {tuple(w.shape)}")
+    elif w.dim() != 2 or a.shape[-1] != w.shape[1]:
         raise ValueError(f"shape mismatch: a {tuple(a.shape)} w {tuple(w.shape)}")
     K = w.shape[1]
     N = w.shape[0]
     M = a.numel() // K if K else 0
-    out_shape = tuple(a.shape[:-1]) + (N,)
+    out_shape = ((a.shape[1],) if a_gathered else tuple(a.shape[:-1])) + (N,)
     if out is None:
         out = torch.empty(out_shape, dtype=out_dtype, device=a.device)
     elif out.dtype != out_dtype or not out.is_contiguous() or out.numel() != M * N:
@@ -100,6 +107,9 @@ def qgemm(a: torch.Tensor, w: torch.Tensor, *, x_scale: Optional[torch.Tensor] =
     args.a, args.w, args.out = a.data_ptr(), w.data_ptr(), out.data_ptr()
     args.M, args.N, args.K = M, N, K
     args.lda, args.ldw, args.ldo = K, K, N
+    if a_gathered:
+        args.a_slabs, args.a_slab_cols, args.a_slab_stride = a.shape[0], a.shape[2], a.shape[1] * a.shape[2]
+        args.lda = a.shape[2]
     keep = []
     for name, t in (("x", x_scale), ("w", w_scale), ("out", out_scale)):
         if t is not None:

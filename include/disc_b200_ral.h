@@ -145,6 +145,13 @@ typedef struct disc_b200_qgemm_args {
   int32_t path, split_k;
   void* splitk_ws;
   int64_t splitk_ws_bytes;
+  /* Activation stored as a_slabs column slabs (what an all-gather of
+   * column-parallel outputs leaves, see disc_b200_qgemm_all_gather): element
+   * (m, k) is a[(k / a_slab_cols) * a_slab_stride + m * lda + k % a_slab_cols],
+   * K = a_slabs * a_slab_cols.  0 or 1 = plain row-major. */
+  int32_t a_slabs;
+  int64_t a_slab_cols;
+  int64_t a_slab_stride;
 } disc_b200_qgemm_args;
 
 int32_t disc_b200_qgemm(const disc_b200_qgemm_args* args, void* stream);

@@ -323,3 +323,32 @@ def test_full_size_checksums(ops, M, K, N):
     assert (col_sum == w64 @ a64.sum(axis=0)).all()
     rows = rng.choice(M, size=min(32, M), replace=False)
     assert (acc[torch.from_numpy(rows).cuda()].cpu().numpy() == c.qgemm_acc(a[rows], w)).all()
+
+
+@pytest.mark.parametrize("M,g,slab,N", [(64, 2, 2048, 520), (7, 4, 1376, 264), (300, 4, 512, 392), (1024, 2, 5504, 256),
+                                        (2048, 8, 128, 1024), (130, 3, 272, 72), (4, 2, 24, 10)])
+@pytest.mark.parametrize("path", [None, "tiled", "pair", "skinny", "simt"])
+def test_gathered_activation_layout(ops, M, g, slab, N, path):
+    """The activation given as [g, M, K / g] column slabs (what an all-gather of
+    column-parallel outputs leaves) multiplies exactly like the row-major
+    matrix, on every path that accepts it, slab widths that are not multiples
+    of the 128-byte K block included."""
+    from oracle import c
+    K = g * slab
+    if path in ("tiled", "pair", "skinny") and slab % 16:
+        pytest.skip("TMA paths need 16-byte multiples")
+    rng = np.random.default_rng(M + g + slab + N)
+    a, w = _rand_i8(rng, (M, K)), _rand_i8(rng, (N, K))
+    gathered = np.ascontiguousarray(a.reshape(M, g, slab).transpose(1, 0, 2))
+    want = c.qgemm_acc(a, w)
+    got = ops.qgemm(_dev(gathered), _dev(w), out_dtype=torch.int32, path=path, a_gathered=True).cpu().numpy()
+    assert got.shape == (M, N)
+    assert (got == want).all()
+    sw = (rng.random(N) * 9e-3 + 1e-3).astype(np.float32)
+    bias = (rng.standard_normal(N) * 0.5).astype(np.float32)
+    sx = (rng.random(M) * 0.03 + 0.01).astype(np.float32)
+    s_out = np.float32(0.05)
+    _, want8 = c.qgemm_epilogue(want, x_scale=sx, w_scale=sw, out_scale=s_out, bias=bias, div_out=True)
+    got8 = ops.qgemm(_dev(gathered), _dev(w), x_scale=_dev(sx), w_scale=_dev(sw), bias=_dev(bias),
+                     out_scale=_dev(np.array([s_out])), path=path, a_gathered=True).cpu().numpy()
+    assert (got8 == want8).all()
