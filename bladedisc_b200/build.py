@@ -26,12 +26,14 @@ SOURCES = [
     "kernels/rowops.cu",
     "ral/context.cc",
     "ral/pdl_attr.cc",
+    "ral/nccl_dyn.cc",
     "ral/calls.cc",
     "c_api.cc",
 ]
 HEADERS = [
     "kernels/qgemm.h", "kernels/rowops.h", "kernels/sm100_ptx.cuh",
-    "ral/abi.h", "ral/context.h", "ral/pdl_attr.h",
+    "kernels/qgemm_pair.inl", "kernels/qgemm_gemv.inl", "kernels/qgemm_skinny.inl",
+    "ral/abi.h", "ral/context.h", "ral/pdl_attr.h", "ral/nccl_dyn.h",
     "../../include/disc_b200_ral.h",
 ]
 
@@ -74,7 +76,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         subprocess.run(cmd, check=True)
         rebuilt = True
     if rebuilt or not LIB.exists() or force:
-        cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB), *map(str, objs)]
+        cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB), *map(str, objs), "-ldl"]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)

@@ -5,6 +5,7 @@
 #include <cstring>
 #include <string>
 
+#include "ral/nccl_dyn.h"
 #include "../../include/disc_b200_ral.h"
 #include "kernels/qgemm.h"
 #include "kernels/rowops.h"
@@ -210,6 +211,8 @@ int32_t disc_b200_norm(const disc_b200_norm_args* a, void* stream) {
   p.eps = a->eps;
   p.type = a->type;
   p.rms = a->rms;
+  p.x_slab_cols = a->x_slab_cols;
+  p.x_slab_stride = a->x_slab_stride;
   const char* detail = nullptr;
   const cudaError_t st = disc_b200::norm_launch(p, static_cast<cudaStream_t>(stream), &detail);
   return finish(st, "norm", detail);
@@ -232,6 +235,91 @@ int32_t disc_b200_softmax(const void* x, void* y, int32_t type, int64_t rows, in
   const char* detail = nullptr;
   const cudaError_t st = disc_b200::softmax_launch(p, static_cast<cudaStream_t>(stream), &detail);
   return finish(st, "softmax", detail);
+}
+
+int32_t disc_b200_gated_quantize(const disc_b200_gated_quantize_args* a, void* stream) {
+  if (!a) {
+    g_last_error = "gated quantize: null args";
+    return 1;
+  }
+  disc_b200::GatedQuantParams p;
+  p.gate = a->gate;
+  p.up = a->up;
+  p.ld = a->ld;
+  p.q = a->q;
+  p.ldq = a->ldq;
+  p.row_scale = a->row_scale;
+  p.rows = a->rows;
+  p.cols = a->cols;
+  p.type = a->type;
+  p.pass = a->pass;
+  const char* detail = nullptr;
+  const cudaError_t st = disc_b200::gated_quantize_launch(p, static_cast<cudaStream_t>(stream), &detail);
+  return finish(st, "gated_quantize", detail);
+}
+
+// ---- collectives of the column-parallel configuration
+static int32_t nccl_fail(const char* what, int result) {
+  const auto& api = disc_b200::ral::nccl_api();
+  g_last_error = std::string(what) + ": " + (api.ok ? api.describe(result) : api.error);
+  return 1;
+}
+
+int32_t disc_b200_nccl_available(void) {
+  const auto& api = disc_b200::ral::nccl_api();
+  if (!api.ok) g_last_error = "NCCL unavailable: " + api.error;
+  return api.ok ? api.version : 0;
+}
+
+int32_t disc_b200_nccl_unique_id(void* id128) {
+  const auto& api = disc_b200::ral::nccl_api();
+  if (!api.ok || !id128) return nccl_fail("ncclGetUniqueId", 0);
+  disc_b200::ral::NcclUniqueId id;
+  const int st = api.GetUniqueId(&id);
+  if (st != 0) return nccl_fail("ncclGetUniqueId", st);
+  std::memcpy(id128, id.internal, sizeof(id.internal));
+  return 0;
+}
+
+int32_t disc_b200_nccl_comm_create(const void* id128, int32_t nranks, int32_t rank, void** comm) {
+  const auto& api = disc_b200::ral::nccl_api();
+  if (!api.ok || !id128 || !comm || nranks <= 0 || rank < 0 || rank >= nranks) {
+    return nccl_fail("ncclCommInitRank (arguments)", 0);
+  }
+  disc_b200::ral::NcclUniqueId id;
+  std::memcpy(id.internal, id128, sizeof(id.internal));
+  *comm = nullptr;
+  const int st = api.CommInitRank(comm, nranks, id, rank);
+  if (st != 0) return nccl_fail("ncclCommInitRank", st);
+  return 0;
+}
+
+int32_t disc_b200_nccl_comm_destroy(void* comm) {
+  const auto& api = disc_b200::ral::nccl_api();
+  if (!api.ok || !comm) return 0;
+  const int st = api.CommDestroy(comm);
+  return st == 0 ? 0 : nccl_fail("ncclCommDestroy", st);
+}
+
+int32_t disc_b200_all_gather(void* comm, const void* send, void* recv, int64_t bytes_per_rank,
+                             void* stream) {
+  const auto& api = disc_b200::ral::nccl_api();
+  if (!api.ok || !comm) return nccl_fail("ncclAllGather (no communicator)", 0);
+  if (bytes_per_rank <= 0) return 0;
+  const int st = api.AllGather(send, recv, static_cast<size_t>(bytes_per_rank), disc_b200::ral::kNcclInt8,
+                               comm, static_cast<cudaStream_t>(stream));
+  return st == 0 ? 0 : nccl_fail("ncclAllGather", st);
+}
+
+int32_t disc_b200_all_reduce_f32(void* comm, const float* send, float* recv, int64_t count,
+                                 int32_t op, void* stream) {
+  const auto& api = disc_b200::ral::nccl_api();
+  if (!api.ok || !comm) return nccl_fail("ncclAllReduce (no communicator)", 0);
+  if (count <= 0) return 0;
+  if (op < 0 || op > 3) return nccl_fail("ncclAllReduce (op)", 0);
+  const int st = api.AllReduce(send, recv, static_cast<size_t>(count), disc_b200::ral::kNcclFloat32, op,
+                               comm, static_cast<cudaStream_t>(stream));
+  return st == 0 ? 0 : nccl_fail("ncclAllReduce", st);
 }
 
 const char* disc_b200_last_error_string(void) { return g_last_error.c_str(); }

@@ -347,9 +347,21 @@ norm_kernel(NormParams p) {
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     live[r] = ix.row0 + r < p.rows;
-    const int64_t off = (live[r] ? ix.row0 + r : 0) * p.cols;
+    const int64_t row = live[r] ? ix.row0 + r : 0;
+    if (ALIGNED && p.x_slab_cols > 0) {
+      // column slabs: vector v starts at column v * E of the logical row
+      const int sc = static_cast<int>(p.x_slab_cols);
 #pragma unroll
-    for (int i = 0; i < NV; ++i) raw[r][i] = load_vec<T>(xb + off, cols, t + i * G, ALIGNED, 0.f);
+      for (int i = 0; i < NV; ++i) {
+        const int c = (t + i * G) * E;
+        const int slab = c / sc;
+        raw[r][i] = load_vec<T>(xb + slab * p.x_slab_stride + row * sc - static_cast<int64_t>(slab) * sc, cols,
+                                t + i * G, true, 0.f);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) raw[r][i] = load_vec<T>(xb + row * p.cols, cols, t + i * G, ALIGNED, 0.f);
+    }
   }
 #pragma unroll
   for (int r = 0; r < R; ++r) {
@@ -507,6 +519,75 @@ dynquant_kernel(DynQuantParams p, int aligned) {
   }
 }
 
+// h of the two-pass gated quantization; one definition for both passes.
+__device__ __forceinline__ float gated_value(float g, float u, bool has_up) {
+  return has_up ? (g / (1.f + __expf(-g))) * u : g;
+}
+
+// PASS 0: local row scale.  PASS 1: quantize with the (agreed) row scale.
+template <typename T, int G, int NV, int R, int PASS>
+__global__ void __launch_bounds__(kBlock, (NV * R <= 4 ? 3 : (NV * R <= 8 ? 2 : 1)))
+gated_quant_kernel(GatedQuantParams p, int aligned) {
+  constexpr int E = VecT<T>::kElems;
+  __shared__ float red[R * 8];
+  const RowIndex<G, R> ix;
+  const int t = ix.t;
+  const int cols = static_cast<int>(p.cols);
+  const bool al = aligned != 0;
+  const bool has_up = p.up != nullptr;
+  const T* gb = reinterpret_cast<const T*>(p.gate);
+  const T* ub = reinterpret_cast<const T*>(p.up);
+  uint4 graw[R][NV], uraw[R][NV];
+  bool live[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    live[r] = ix.row0 + r < p.rows;
+    const int64_t off = (live[r] ? ix.row0 + r : 0) * p.ld;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      graw[r][i] = load_vec<T>(gb + off, cols, t + i * G, al, 0.f);
+      if (has_up) uraw[r][i] = load_vec<T>(ub + off, cols, t + i * G, al, 0.f);
+    }
+  }
+  if (PASS == 0) {
+    float m[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float a = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int j = 0; j < E; ++j) {
+          const float u = has_up ? VecT<T>::get(uraw[r][i], j) : 0.f;
+          a = fmaxf(a, fabsf(gated_value(VecT<T>::get(graw[r][i], j), u, has_up)));  // padding: h(0, 0) = 0
+        }
+      m[r] = a;
+    }
+    group_reduce<G, R, true>(m, red);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (live[r] && t == 0) p.row_scale[ix.row0 + r] = fmaxf(__fdiv_rn(m[r], 127.f), FLT_EPSILON);
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (!live[r]) continue;
+      const Divisor d = make_divisor(__ldg(p.row_scale + ix.row0 + r));
+      const int64_t off = (ix.row0 + r) * p.ldq;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        float q[E];
+#pragma unroll
+        for (int j = 0; j < E; ++j) {
+          const float u = has_up ? VecT<T>::get(uraw[r][i], j) : 0.f;
+          q[j] = quant_biased(gated_value(VecT<T>::get(graw[r][i], j), u, has_up), d, 0.f, -128.f, 127.f);
+        }
+        store_q<E>(p.q + off, cols, t + i * G, al, q);
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -650,6 +731,11 @@ constexpr auto NORM_ALIGNED = norm_kernel<T, G, NV, R, true>;
 template <typename T, int G, int NV, int R>
 constexpr auto NORM_RAGGED = norm_kernel<T, G, NV, R, false>;
 
+template <typename T, int G, int NV, int R>
+constexpr auto GATED_SCALE = gated_quant_kernel<T, G, NV, R, 0>;
+template <typename T, int G, int NV, int R>
+constexpr auto GATED_QUANT = gated_quant_kernel<T, G, NV, R, 1>;
+
 bool row_shape_ok(int64_t rows, int64_t cols, const char** err) {
   if (cols > 16384) {
     if (err) *err = "row kernel: more than 16384 columns is not supported";
@@ -749,6 +835,32 @@ cudaError_t dynamic_quantize_launch(const DynQuantParams& p, cudaStream_t s, con
   return cudaGetLastError();
 }
 
+cudaError_t gated_quantize_launch(const GatedQuantParams& p, cudaStream_t s, const char** err) {
+  if (err) *err = nullptr;
+  if (p.rows <= 0 || p.cols <= 0) return cudaSuccess;
+  if (!p.gate || !p.row_scale || (p.pass != 0 && !p.q) || (p.pass != 0 && p.pass != 1)) {
+    if (err) *err = "gated quantize: null operand or unknown pass";
+    return cudaErrorInvalidValue;
+  }
+  if (p.ld < p.cols || (p.pass == 1 && p.ldq < p.cols)) {
+    if (err) *err = "gated quantize: row stride smaller than the row";
+    return cudaErrorInvalidValue;
+  }
+  if (!row_shape_ok(p.rows, p.cols, err)) return cudaErrorInvalidValue;
+  const int epv = p.type == kF32 ? 4 : 8;
+  const int aligned = (p.cols % epv == 0) && (p.ld % epv == 0) && is_aligned16(p.gate) &&
+                      (!p.up || is_aligned16(p.up)) &&
+                      (p.pass == 0 || ((p.ldq % epv == 0) && (reinterpret_cast<uintptr_t>(p.q) & (epv - 1)) == 0));
+  if (p.type == kF32) {
+    if (p.pass == 0) DISC_ROW_DISPATCH(GATED_SCALE, float, vectors_per_row<float>(p.cols), p.rows, s, p, aligned);
+    else DISC_ROW_DISPATCH(GATED_QUANT, float, vectors_per_row<float>(p.cols), p.rows, s, p, aligned);
+  } else {
+    if (p.pass == 0) DISC_ROW_DISPATCH(GATED_SCALE, __half, vectors_per_row<__half>(p.cols), p.rows, s, p, aligned);
+    else DISC_ROW_DISPATCH(GATED_QUANT, __half, vectors_per_row<__half>(p.cols), p.rows, s, p, aligned);
+  }
+  return cudaGetLastError();
+}
+
 cudaError_t norm_launch(const NormParams& p, cudaStream_t s, const char** err) {
   if (err) *err = nullptr;
   if (p.rows <= 0 || p.cols <= 0) return cudaSuccess;
@@ -762,6 +874,12 @@ cudaError_t norm_launch(const NormParams& p, cudaStream_t s, const char** err) {
   }
   if (!row_shape_ok(p.rows, p.cols, err)) return cudaErrorInvalidValue;
   const int epv = p.type == kF32 ? 4 : 8;
+  if (p.x_slab_cols > 0 &&
+      (p.x_slab_cols % epv != 0 || p.cols % p.x_slab_cols != 0 || p.x_slab_stride % epv != 0 ||
+       p.cols % epv != 0 || !is_aligned16(p.x))) {
+    if (err) *err = "norm: slabbed x needs 16-byte aligned slabs whose width divides the row";
+    return cudaErrorInvalidValue;
+  }
   const int aligned = (p.cols % epv == 0) && is_aligned16(p.x) && is_aligned16(p.gamma) &&
                       (!p.residual || is_aligned16(p.residual)) && (!p.beta || is_aligned16(p.beta)) &&
                       (!p.y || is_aligned16(p.y)) && (!p.sum_out || is_aligned16(p.sum_out)) &&

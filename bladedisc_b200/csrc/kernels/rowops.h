@@ -70,8 +70,35 @@ struct NormParams {
   float eps;
   int type;  // ElemType of x / residual / gamma / beta / y
   int rms;
+  // x stored as column slabs, the layout an all-gather of column-parallel
+  // outputs leaves: element (r, c) at x[(c / x_slab_cols) * x_slab_stride +
+  // r * x_slab_cols + c % x_slab_cols].  0 = plain row-major.  Needs 16-byte
+  // aligned rows and x_slab_cols a multiple of the 16-byte vector.
+  int64_t x_slab_cols;
+  int64_t x_slab_stride;
 };
 cudaError_t norm_launch(const NormParams& p, cudaStream_t s, const char** err);
+
+// Per-row symmetric quantization of h = up ? silu(gate) * up : gate in two
+// passes, for rows whose columns are spread over several GPUs: pass 0 writes
+// row_scale[r] = max(max|h[r, :]| / 127, eps) of the local columns, the caller
+// takes the maximum over the GPUs, pass 1 writes q = sat(rne(h / row_scale[r])).
+// Both passes compute h with the same instructions, so the scale always covers
+// the values that are quantized.  gate / up are [rows, cols] with row stride ld
+// (two column halves of one buffer when a merged gate-up linear produced them),
+// q has row stride ldq.
+struct GatedQuantParams {
+  const void* gate;
+  const void* up;  // may be null
+  int64_t ld;
+  int8_t* q;  // pass 1
+  int64_t ldq;
+  float* row_scale;
+  int64_t rows, cols;
+  int type;  // ElemType of gate / up
+  int pass;
+};
+cudaError_t gated_quantize_launch(const GatedQuantParams& p, cudaStream_t s, const char** err);
 
 // y = softmax(x * scale + mask) over the last axis.  Row r belongs to batch
 // r / rows_per_batch; `lens` (optional) gives the valid length per batch

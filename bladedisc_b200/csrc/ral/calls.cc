@@ -18,6 +18,7 @@
 #include "../kernels/rowops.h"
 #include "abi.h"
 #include "context.h"
+#include "nccl_dyn.h"
 #include "pdl_attr.h"
 
 namespace disc_b200 {
@@ -650,6 +651,303 @@ DISC_B200_RAL_API("disc_b200_masked_softmax", "gpu", masked_softmax_call<float, 
 DISC_B200_RAL_API("disc_b200_masked_softmax", "gpu", masked_softmax_call<f16_t, 4>);
 DISC_B200_RAL_API("disc_b200_masked_softmax", "gpu", masked_softmax_call<float, 3>);
 DISC_B200_RAL_API("disc_b200_masked_softmax", "gpu", masked_softmax_call<f16_t, 3>);
+
+
+// ------------------------------------------------------- 4. collectives
+// The column-parallel split of a linear over the GPUs of one box ends in an
+// all-gather.  ral_all_gather / ral_all_reduce / ral_async_collective_done keep
+// the reference's names, attributes and result ownership
+// (tao_compiler/mlir/ral/collective.cu.cc:60-309,398-440, registered :444-504).
+// Differences: a failure is recorded instead of ignored, a call that is not
+// asynchronous runs on the compute stream (the reference issues it on the
+// communication stream without ordering it behind the producer), bf16 is sent
+// as bf16 (the reference maps it to ncclHalf, harmless for a gather and wrong
+// for a sum).
+template <typename T>
+constexpr int nccl_type_of() {
+  if constexpr (std::is_same_v<T, float>) return kNcclFloat32;
+  if constexpr (std::is_same_v<T, f16_t>) return kNcclFloat16;
+  if constexpr (std::is_same_v<T, bf16_t>) return kNcclBfloat16;
+  if constexpr (std::is_same_v<T, int32_t>) return kNcclInt32;
+  return kNcclInt8;
+}
+
+struct CollectiveEnv {
+  const NcclApi* api = nullptr;
+  void* comm = nullptr;
+  cudaStream_t compute = nullptr;
+  cudaStream_t comm_stream = nullptr;
+  int size = 0;
+  int rank = 0;
+};
+
+bool collective_env(ExecContext* ctx, CollectiveEnv* env) {
+  int size = 0, rank = 0;
+  if (!ctx->ctx->comm_info(&size, &rank)) return false;
+  env->api = &nccl_api();
+  env->comm = ctx->ctx->nccl_comm;
+  env->compute = stream_of(ctx);
+  env->comm_stream = ctx->ctx->comm_stream ? ctx->ctx->comm_stream : env->compute;
+  env->size = size;
+  env->rank = rank;
+  return true;
+}
+
+// Makes `later` wait for everything queued on `earlier` so far.
+bool order_streams(ExecContext* ctx, cudaStream_t earlier, cudaStream_t later) {
+  if (earlier == later) return true;
+  cudaEvent_t ev = nullptr;
+  cudaError_t st = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+  const bool created = st == cudaSuccess;
+  if (st == cudaSuccess) st = cudaEventRecord(ev, earlier);
+  if (st == cudaSuccess) st = cudaStreamWaitEvent(later, ev, 0);
+  if (created) cudaEventDestroy(ev);  // the queued wait keeps what it needs
+  if (st != cudaSuccess) {
+    report(ctx, st, "stream ordering for a collective", nullptr);
+    return false;
+  }
+  return true;
+}
+
+// Leaves an event on the communication stream under `key`;
+// ral_async_collective_done makes the compute stream wait for it.
+bool leave_token(ExecContext* ctx, const CollectiveEnv& env, int64_t key) {
+  cudaEvent_t ev;
+  cudaError_t st = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+  if (st == cudaSuccess) st = cudaEventRecord(ev, env.comm_stream);
+  if (st != cudaSuccess) {
+    report(ctx, st, "completion event of a collective", nullptr);
+    return false;
+  }
+  auto it = ctx->async_tokens.find(key);
+  if (it != ctx->async_tokens.end()) cudaEventDestroy(it->second);
+  ctx->async_tokens[key] = ev;
+  return true;
+}
+
+// Group size named by the replica_groups attribute ([groups, ranks per group]);
+// the communicator's size when the attribute is absent.
+int64_t group_size_of(const Attr* at, int comm_size) {
+  const Attr* rg = at->find("replica_groups");
+  if (rg && rg->kind == Attr::kDense && rg->shape.size() == 2) return rg->shape[1];
+  return comm_size;
+}
+
+// in-place capable gather of `count` elements per rank on the stream the
+// attributes select; returns false after recording the error.
+bool run_all_gather(ExecContext* ctx, const CollectiveEnv& env, const Attr* at, const void* send,
+                    void* recv, size_t count, int dtype) {
+  const bool is_async = at->get_bool("is_async", false);
+  cudaStream_t s = env.compute;
+  if (is_async) {
+    if (!order_streams(ctx, env.compute, env.comm_stream)) return false;
+    s = env.comm_stream;
+  }
+  const int st = env.api->AllGather(send, recv, count, dtype, env.comm, s);
+  if (st != 0) {
+    ctx->signal_error("ncclAllGather failed: " + env.api->describe(st));
+    return false;
+  }
+  if (is_async) return leave_token(ctx, env, at->get_int("async_token_key", 0));
+  return true;
+}
+
+template <typename T, int N>
+MemRef<T, N> ral_all_gather(ExecContext* ctx, void* stream_handle, MemRef<T, N> input,
+                            void* custom_attrs) {
+  int64_t sizes[N];
+  for (int i = 0; i < N; ++i) sizes[i] = input.sizes[i];
+  MemRef<T, N> none = make_memref<T, N>(nullptr, sizes);
+  if (!check_stream_handle(ctx, stream_handle)) return none;
+  const Attr* at = attrs_of(ctx, custom_attrs);
+  CollectiveEnv env;
+  if (!at || !collective_env(ctx, &env)) return none;
+  const int64_t dim = at->get_int("all_gather_dim", 0);
+  const int64_t group = group_size_of(at, env.size);
+  if (dim < 0 || dim >= N) {
+    ctx->signal_error("ral_all_gather: all_gather_dim out of range");
+    return none;
+  }
+  if (group != env.size) {
+    ctx->signal_error("ral_all_gather: replica group of " + std::to_string(group) +
+                      " ranks but the communicator has " + std::to_string(env.size));
+    return none;
+  }
+  // As in the reference the data arrives rank-major whatever the dimension:
+  // the result holds rank 0's buffer, then rank 1's, ...
+  sizes[dim] *= group;
+  const int64_t count = memref_numel(input);
+  if (count == 0) return make_memref<T, N>(nullptr, sizes);
+  T* out = static_cast<T*>(ctx->alloc(static_cast<size_t>(count * group) * sizeof(T)));
+  MemRef<T, N> result = make_memref<T, N>(out, sizes);
+  if (!out) return result;
+  run_all_gather(ctx, env, at, input.data, out, static_cast<size_t>(count), nccl_type_of<T>());
+  return result;
+}
+
+int nccl_op_of(const std::string& kind) {
+  if (kind == "prod") return kNcclProd;
+  if (kind == "min") return kNcclMin;
+  if (kind == "max") return kNcclMax;
+  return kNcclSum;  // the reference's default for anything else (collective.cu.cc:52-58)
+}
+
+template <typename T, int N>
+MemRef<T, N> ral_all_reduce(ExecContext* ctx, void* stream_handle, MemRef<T, N> input,
+                            void* custom_attrs) {
+  MemRef<T, N> result = input;
+  result.base = result.data = nullptr;
+  if (!check_stream_handle(ctx, stream_handle)) return result;
+  const Attr* at = attrs_of(ctx, custom_attrs);
+  CollectiveEnv env;
+  if (!at || !collective_env(ctx, &env)) return result;
+  const int64_t count = memref_numel(input);
+  if (count == 0) return result;
+  T* out = static_cast<T*>(ctx->alloc(static_cast<size_t>(count) * sizeof(T)));
+  if (!out) return result;
+  result.base = result.data = out;
+  result.offset = 0;
+  if constexpr (N > 0) {
+    int64_t stride = 1;
+    for (int i = N - 1; i >= 0; --i) {
+      result.strides[i] = stride;
+      stride *= result.sizes[i];
+    }
+  }
+  const bool is_async = at->get_bool("is_async", false);
+  cudaStream_t s = env.compute;
+  if (is_async) {
+    if (!order_streams(ctx, env.compute, env.comm_stream)) return result;
+    s = env.comm_stream;
+  }
+  const int st = env.api->AllReduce(input.data, out, static_cast<size_t>(count), nccl_type_of<T>(),
+                                    nccl_op_of(at->get_str("reduction_kind", "sum")), env.comm, s);
+  if (st != 0) {
+    ctx->signal_error("ncclAllReduce failed: " + env.api->describe(st));
+    return result;
+  }
+  if (is_async) leave_token(ctx, env, at->get_int("async_token_key", 0));
+  return result;
+}
+
+// The consumer side of an asynchronous collective: the compute stream waits for
+// the event the collective left; the buffer passes through with one more
+// reference, as in the reference (collective.cu.cc:411-416), so that the
+// dealloc of the collective's own result does not free what this call returns.
+template <typename T, int N>
+MemRef<T, N> ral_async_collective_done(ExecContext* ctx, void* stream_handle, MemRef<T, N> input,
+                                       void* custom_attrs) {
+  if (!check_stream_handle(ctx, stream_handle)) return input;
+  const Attr* at = attrs_of(ctx, custom_attrs);
+  if (!at) return input;
+  auto rc = ctx->refcount.find(input.data);
+  if (rc != ctx->refcount.end()) ++rc->second;
+  if (!at->get_bool("is_async", false)) return input;
+  const int64_t key = at->get_int("async_token_key", 0);
+  auto it = ctx->async_tokens.find(key);
+  if (it == ctx->async_tokens.end()) {
+    ctx->signal_error("ral_async_collective_done: no collective in flight under token " +
+                      std::to_string(key));
+    return input;
+  }
+  report(ctx, cudaStreamWaitEvent(stream_of(ctx), it->second, 0), "wait for a collective", nullptr);
+  cudaEventDestroy(it->second);
+  ctx->async_tokens.erase(it);
+  return input;
+}
+
+#define DISC_B200_REGISTER_COLLECTIVES(T)                                              \
+  DISC_B200_RAL_API("ral_all_reduce", "gpu", ral_all_reduce<T, 0>);                    \
+  DISC_B200_RAL_API("ral_all_reduce", "gpu", ral_all_reduce<T, 1>);                    \
+  DISC_B200_RAL_API("ral_all_reduce", "gpu", ral_all_reduce<T, 2>);                    \
+  DISC_B200_RAL_API("ral_all_reduce", "gpu", ral_all_reduce<T, 3>);                    \
+  DISC_B200_RAL_API("ral_all_reduce", "gpu", ral_all_reduce<T, 4>);                    \
+  DISC_B200_RAL_API("ral_all_gather", "gpu", ral_all_gather<T, 1>);                    \
+  DISC_B200_RAL_API("ral_all_gather", "gpu", ral_all_gather<T, 2>);                    \
+  DISC_B200_RAL_API("ral_all_gather", "gpu", ral_all_gather<T, 3>);                    \
+  DISC_B200_RAL_API("ral_all_gather", "gpu", ral_all_gather<T, 4>);                    \
+  DISC_B200_RAL_API("ral_async_collective_done", "gpu", ral_async_collective_done<T, 0>); \
+  DISC_B200_RAL_API("ral_async_collective_done", "gpu", ral_async_collective_done<T, 1>); \
+  DISC_B200_RAL_API("ral_async_collective_done", "gpu", ral_async_collective_done<T, 2>); \
+  DISC_B200_RAL_API("ral_async_collective_done", "gpu", ral_async_collective_done<T, 3>); \
+  DISC_B200_RAL_API("ral_async_collective_done", "gpu", ral_async_collective_done<T, 4>)
+DISC_B200_REGISTER_COLLECTIVES(float);
+DISC_B200_REGISTER_COLLECTIVES(f16_t);
+DISC_B200_REGISTER_COLLECTIVES(bf16_t);
+// int8 results of the fused call below travel through the same "done" call.
+DISC_B200_RAL_API("ral_async_collective_done", "gpu", ral_async_collective_done<int8_t, 3>);
+
+// One column-parallel shard of a quantized linear and its all-gather in one
+// call.  Rank r holds rows [r * N/g, (r + 1) * N/g) of the weight with their
+// scales and bias; its GEMM epilogue writes straight into slot r of the result
+// [g, M, N/g] and NCCL gathers in place (send buffer = slot r of the receive
+// buffer), so no copy sits between the kernel and the collective.  The result
+// keeps the rank-major layout the gather produces; the next linear reads it as
+// its activation without a re-layout (input rank 3 here = such a buffer).
+// Attributes: activation, and is_async / async_token_key as for ral_all_gather
+// (asynchronous: the gather runs on the communication stream and overlaps the
+// caller's next independent kernels until ral_async_collective_done).
+template <int NIN, typename OutT, typename XS>
+MemRef<OutT, 3> qgemm_all_gather(ExecContext* ctx, void* stream_handle, MemRef<int8_t, NIN> input,
+                                 MemRef<int8_t, 2> weight, MemRef<float, 1> bias, XS x_scale,
+                                 MemRef<float, 1> w_scale, MemRef<float, 0> out_scale,
+                                 void* custom_attrs) {
+  static_assert(NIN == 2 || NIN == 3, "row-major [M, K] or gathered [g, M, K / g]");
+  const int64_t k = weight.sizes[1];
+  const int64_t n_local = weight.sizes[0];
+  const int64_t m = input.sizes[NIN - 2];
+  int64_t rs[3] = {0, m, n_local};
+  if (!check_stream_handle(ctx, stream_handle)) return make_memref<OutT, 3>(nullptr, rs);
+  const Attr* at = attrs_of(ctx, custom_attrs);
+  CollectiveEnv env;
+  if (!at || !collective_env(ctx, &env)) return make_memref<OutT, 3>(nullptr, rs);
+  rs[0] = env.size;
+  const int64_t k_in = NIN == 2 ? input.sizes[1] : input.sizes[0] * input.sizes[2];
+  if (k_in != k || w_scale.sizes[0] != n_local) {
+    ctx->signal_error("disc_b200_qgemm_all_gather: operand extents disagree");
+    return make_memref<OutT, 3>(nullptr, rs);
+  }
+  if (m == 0 || n_local == 0 || k == 0) return make_memref<OutT, 3>(nullptr, rs);
+  const int64_t slot = m * n_local;
+  OutT* out = static_cast<OutT*>(ctx->alloc(static_cast<size_t>(slot * env.size) * sizeof(OutT)));
+  auto result = make_memref<OutT, 3>(out, rs);
+  if (!out) return result;
+  OutT* mine = out + slot * env.rank;
+  QGemmParams p = base_params(input.data, weight.data, mine, m, n_local, k);
+  if constexpr (NIN == 3) {
+    p.a_slabs = static_cast<int>(input.sizes[0]);
+    p.a_slab_cols = input.sizes[2];
+    p.a_slab_stride = input.sizes[1] * input.sizes[2];
+    p.lda = input.sizes[2];
+  }
+  p.x_scale = x_scale.data;
+  p.x_scale_kind = std::is_same_v<XS, MemRef<float, 0>> ? kScaleScalar : kScalePerRow;
+  p.w_scale = w_scale.data;
+  p.w_scale_kind = kScalePerCol;
+  p.bias = memref_numel(bias) == n_local ? bias.data : nullptr;
+  p.bias_kind = p.bias ? kBiasF32 : kBiasNone;
+  p.act = act_from(at);
+  if constexpr (std::is_same_v<OutT, int8_t>) {
+    p.out_scale = out_scale.data;
+    p.out_scale_kind = kScaleScalar;
+    p.div_out_scale = 1;
+    p.out_dtype = kOutI8;
+  } else {
+    p.out_dtype = kOutF16;
+  }
+  if (!run_qgemm(ctx, p)) return result;
+  // bytes, so that int8 and f16 results share one code path
+  run_all_gather(ctx, env, at, mine, out, static_cast<size_t>(slot) * sizeof(OutT), kNcclInt8);
+  return result;
+}
+
+#define DISC_B200_REGISTER_QGEMM_AG(NIN)                                                        \
+  DISC_B200_RAL_API("disc_b200_qgemm_all_gather", "gpu", qgemm_all_gather<NIN, f16_t, MemRef<float, 0>>);  \
+  DISC_B200_RAL_API("disc_b200_qgemm_all_gather", "gpu", qgemm_all_gather<NIN, f16_t, MemRef<float, 1>>);  \
+  DISC_B200_RAL_API("disc_b200_qgemm_all_gather", "gpu", qgemm_all_gather<NIN, int8_t, MemRef<float, 0>>); \
+  DISC_B200_RAL_API("disc_b200_qgemm_all_gather", "gpu", qgemm_all_gather<NIN, int8_t, MemRef<float, 1>>)
+DISC_B200_REGISTER_QGEMM_AG(2);
+DISC_B200_REGISTER_QGEMM_AG(3);
 
 }  // namespace
 }  // namespace ral

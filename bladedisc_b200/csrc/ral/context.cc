@@ -1,4 +1,5 @@
 #include "context.h"
+#include "nccl_dyn.h"
 
 #include <cstring>
 #include <map>
@@ -91,6 +92,33 @@ void* Context::get_splitk_ws(int64_t bytes) {
   splitk_ws_bytes = splitk_ws ? want : 0;
   if (splitk_ws) cudaMemsetAsync(splitk_ws, 0, static_cast<size_t>(want), stream);
   return splitk_ws;
+}
+
+bool Context::comm_info(int* size, int* rank) {
+  if (!nccl_comm) {
+    signal_error(1, "no NCCL communicator in this context (disc_b200_context_options.nccl_comm)");
+    return false;
+  }
+  if (comm_size == 0) {
+    const NcclApi& api = nccl_api();
+    if (!api.ok) {
+      signal_error(1, "NCCL unavailable: " + api.error);
+      return false;
+    }
+    int n = 0, r = 0;
+    int st = api.CommCount(nccl_comm, &n);
+    if (st == 0) st = api.CommUserRank(nccl_comm, &r);
+    if (st != 0 || n <= 0) {
+      signal_error(1, "ncclCommCount / ncclCommUserRank failed: " + api.describe(st));
+      return false;
+    }
+    std::lock_guard<std::mutex> l(mu);
+    comm_size = n;
+    comm_rank = r;
+  }
+  *size = comm_size;
+  *rank = comm_rank;
+  return true;
 }
 
 Context::~Context() {
@@ -215,6 +243,7 @@ void disc_b200_exec_destroy(disc_b200_exec* handle) {
   for (auto& kv : e->refcount) {
     if (!handed_out.count(kv.first)) e->ctx->raw_free(kv.first);
   }
+  for (auto& kv : e->async_tokens) cudaEventDestroy(kv.second);
   e->magic = 0;
   delete e;
 }

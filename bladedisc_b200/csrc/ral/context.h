@@ -35,6 +35,8 @@ struct Context {
   void* alloc_user = nullptr;
   void* nccl_comm = nullptr;
   cudaStream_t comm_stream = nullptr;
+  int comm_size = 0;  // ranks of nccl_comm, 0 until first asked
+  int comm_rank = 0;
 
   std::mutex mu;
   int32_t status = 0;
@@ -50,6 +52,9 @@ struct Context {
   bool ok();
   // Returns scratch of at least `bytes`, zeroed when (re)allocated.
   void* get_splitk_ws(int64_t bytes);
+  // Size and rank of nccl_comm (queried once); false, with an error signalled,
+  // when there is no communicator or NCCL cannot be reached.
+  bool comm_info(int* size, int* rank);
   ~Context();
 };
 
@@ -65,6 +70,9 @@ struct ExecContext {
   std::unordered_map<int64_t, BoundTensor> outputs;
   std::unordered_map<void*, int> refcount;  // buffers allocated during this execution
   std::unordered_set<void*> input_ptrs;
+  // Completion events of asynchronous collectives, by async_token_key
+  // (reference: async_pair_tokens, tao_compiler/mlir/ral/collective.cu.cc:134,431).
+  std::unordered_map<int64_t, cudaEvent_t> async_tokens;
 
   void* alloc(size_t bytes);
   void dealloc(void* p);

@@ -59,6 +59,15 @@ class NormArgs(Structure):
         ("q_scale", c_void_p), ("q_row_scale", c_void_p),
         ("rows", c_int64), ("cols", c_int64),
         ("eps", c_float), ("type", c_int32), ("rms", c_int32),
+        ("x_slab_cols", c_int64), ("x_slab_stride", c_int64),
+    ]
+
+
+class GatedQuantArgs(Structure):
+    _fields_ = [
+        ("gate", c_void_p), ("up", c_void_p), ("ld", c_int64),
+        ("q", c_void_p), ("ldq", c_int64), ("row_scale", c_void_p),
+        ("rows", c_int64), ("cols", c_int64), ("type", c_int32), ("pass_", c_int32),
     ]
 
 
@@ -90,8 +99,15 @@ SIGNATURES = {
     "disc_b200_dynamic_quantize": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_int64, c_int64,
                                              c_void_p]),
     "disc_b200_norm": (c_int32, [POINTER(NormArgs), c_void_p]),
+    "disc_b200_gated_quantize": (c_int32, [POINTER(GatedQuantArgs), c_void_p]),
     "disc_b200_softmax": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int64, c_void_p,
                                     c_void_p, c_float, c_int32, c_void_p]),
+    "disc_b200_nccl_available": (c_int32, []),
+    "disc_b200_nccl_unique_id": (c_int32, [c_void_p]),
+    "disc_b200_nccl_comm_create": (c_int32, [c_void_p, c_int32, c_int32, POINTER(c_void_p)]),
+    "disc_b200_nccl_comm_destroy": (c_int32, [c_void_p]),
+    "disc_b200_all_gather": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "disc_b200_all_reduce_f32": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
     "disc_b200_last_error_string": (c_char_p, []),
     "disc_b200_kernel_status": (c_int32, []),
     "disc_b200_version": (c_char_p, []),

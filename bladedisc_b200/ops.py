@@ -209,18 +209,27 @@ def dynamic_quantize(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return q, s
 
 
-def _norm(x, residual, gamma, beta, eps, rms, q_scale, want_y, want_sum, want_q, dynamic_q):
+def _norm(x, residual, gamma, beta, eps, rms, q_scale, want_y, want_sum, want_q, dynamic_q,
+          x_gathered=False):
     x = _cuda(x, "x")
     gamma = _cuda(gamma, "gamma", x.dtype)
-    cols = x.shape[-1]
-    rows = x.numel() // cols if cols else 0
     a = _lib.NormArgs()
+    if x_gathered:  # [g, rows, cols / g] column slabs
+        if x.dim() != 3:
+            raise ValueError("a gathered x is [g, rows, cols / g]")
+        rows, cols = x.shape[1], x.shape[0] * x.shape[2]
+        a.x_slab_cols, a.x_slab_stride = x.shape[2], x.shape[1] * x.shape[2]
+        shape = (rows, cols)
+    else:
+        cols = x.shape[-1]
+        rows = x.numel() // cols if cols else 0
+        shape = tuple(x.shape)
     a.x = x.data_ptr()
     a.gamma = gamma.data_ptr()
     keep = [x, gamma]
     if residual is not None:
         residual = _cuda(residual, "residual", x.dtype)
-        if residual.shape != x.shape:
+        if tuple(residual.shape) != shape:
             raise ValueError("residual must have the shape of x")
         a.residual = residual.data_ptr()
         keep.append(residual)
@@ -230,13 +239,13 @@ def _norm(x, residual, gamma, beta, eps, rms, q_scale, want_y, want_sum, want_q,
         keep.append(beta)
     y = s = q = rs = None
     if want_y:
-        y = torch.empty_like(x)
+        y = torch.empty(shape, dtype=x.dtype, device=x.device)
         a.y = y.data_ptr()
     if want_sum:
-        s = torch.empty_like(x)
+        s = torch.empty(shape, dtype=x.dtype, device=x.device)
         a.sum_out = s.data_ptr()
     if want_q:
-        q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+        q = torch.empty(shape, dtype=torch.int8, device=x.device)
         a.q_out = q.data_ptr()
         if dynamic_q:
             rs = torch.empty(rows, dtype=torch.float32, device=x.device)
@@ -261,16 +270,66 @@ def layernorm_quant(x, gamma, beta, q_scale, eps: float = 1e-5, residual=None):
     return y, q
 
 
-def rmsnorm(x, gamma, eps: float = 1e-6, residual=None, return_sum: bool = False):
+def rmsnorm(x, gamma, eps: float = 1e-6, residual=None, return_sum: bool = False, x_gathered: bool = False):
     """RMSNorm(x [+ residual]); with return_sum also x + residual."""
-    y, s, _, _ = _norm(x, residual, gamma, None, eps, True, None, True, return_sum, False, False)
+    y, s, _, _ = _norm(x, residual, gamma, None, eps, True, None, True, return_sum, False, False,
+                       x_gathered=x_gathered)
     return (y, s) if return_sum else y
 
 
-def rmsnorm_dynamic_quant(x, gamma, eps: float = 1e-6, residual=None):
-    """RMSNorm(x [+ residual]) quantized per row: (q, row_scale, x + residual or None)."""
-    _, s, q, rs = _norm(x, residual, gamma, None, eps, True, None, False, residual is not None, True, True)
+def rmsnorm_dynamic_quant(x, gamma, eps: float = 1e-6, residual=None, x_gathered: bool = False):
+    """RMSNorm(x [+ residual]) quantized per row: (q, row_scale, x + residual or None).
+
+    ``x_gathered``: x is ``[g, rows, cols / g]``, the buffer an all-gather of
+    column-parallel outputs leaves; it is read in place."""
+    _, s, q, rs = _norm(x, residual, gamma, None, eps, True, None, False, residual is not None, True, True,
+                        x_gathered=x_gathered)
     return q, rs, s
+
+
+def _gated(gate, up, q, row_scale, pass_):
+    gate = _cuda_strided(gate, "gate")
+    a = _lib.GatedQuantArgs()
+    a.gate, a.ld = gate.data_ptr(), gate.stride(0)
+    a.rows, a.cols, a.type, a.pass_ = gate.shape[0], gate.shape[1], _etype(gate), pass_
+    if up is not None:
+        up = _cuda_strided(up, "up")
+        if up.shape != gate.shape or up.stride(0) != gate.stride(0) or up.dtype != gate.dtype:
+            raise ValueError("up must match gate in shape, row stride and dtype")
+        a.up = up.data_ptr()
+    a.row_scale = row_scale.data_ptr()
+    if q is not None:
+        a.q, a.ldq = q.data_ptr(), q.stride(0)
+    _lib.check(_lib.load().disc_b200_gated_quantize(ctypes.byref(a), _stream()))
+
+
+def _cuda_strided(t: torch.Tensor, name: str) -> torch.Tensor:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: this library has no CPU path")
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be 2-D with unit column stride")
+    return t
+
+
+def row_scale_local(gate: torch.Tensor, up: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """First pass of the two-pass per-row quantization of ``h = silu(gate) * up``
+    (``h = gate`` without ``up``): ``max(max|h[r, :]| / 127, eps)`` over the
+    columns this GPU holds.  Rows may be strided views (column halves of one buffer)."""
+    s = torch.empty(gate.shape[0], dtype=torch.float32, device=gate.device)
+    _gated(gate, up, None, s, 0)
+    return s
+
+
+def quantize_rows(gate: torch.Tensor, row_scale: torch.Tensor, up: Optional[torch.Tensor] = None,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Second pass: ``sat(rne(h / row_scale[r]))`` into ``out`` (int8, may be a strided view)."""
+    row_scale = _cuda(row_scale, "row_scale", torch.float32)
+    if out is None:
+        out = torch.empty(gate.shape, dtype=torch.int8, device=gate.device)
+    elif out.dtype != torch.int8 or tuple(out.shape) != tuple(gate.shape) or out.stride(1) != 1:
+        raise ValueError("out must be int8 of gate's shape with unit column stride")
+    _gated(gate, up, out, row_scale, 1)
+    return out
 
 
 def softmax(x: torch.Tensor, scale: float = 1.0, lens: Optional[torch.Tensor] = None,

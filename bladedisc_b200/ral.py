@@ -93,6 +93,12 @@ def pack_attrs(attrs: Optional[dict]) -> bytes:
             return s("array") + struct.pack("<q", len(v)) + b"".join(value(i) for i in v)
         if isinstance(v, dict):
             return s("dict") + struct.pack("<q", len(v)) + b"".join(s(k) + value(x) for k, x in v.items())
+        if hasattr(v, "dtype") and hasattr(v, "tobytes"):  # numpy array -> denseElementsAttr
+            kind = {"i": "int", "u": "uint", "f": "float"}[v.dtype.kind]
+            raw = v.tobytes()
+            return (s("denseElementsAttr") + s(kind) + struct.pack("<I", v.dtype.itemsize * 8) +
+                    struct.pack("<q", v.ndim) + b"".join(struct.pack("<q", d) for d in v.shape) +
+                    struct.pack("<B", 0) + struct.pack("<q", len(raw)) + raw)
         raise TypeError(f"cannot serialize attribute of type {type(v)}")
 
     return value(dict(attrs or {}))
@@ -105,7 +111,8 @@ class RalError(RuntimeError):
 class RalContext:
     """One RAL context on the current device and stream."""
 
-    def __init__(self, device: Optional[int] = None, use_torch_allocator: bool = True):
+    def __init__(self, device: Optional[int] = None, use_torch_allocator: bool = True,
+                 nccl_comm: Optional[int] = None, comm_stream: Optional[int] = None):
         self._L = _lib.load()
         if not torch.cuda.is_available():
             raise RuntimeError("RalContext needs a CUDA device: there is no CPU implementation")
@@ -130,6 +137,9 @@ class RalContext:
             self._free_cb = _lib.FREE_FN(_free)
             opts.gpu_alloc = self._alloc_cb
             opts.gpu_free = self._free_cb
+        # communicator (tp.Communicator.handle) and stream for the collective calls
+        opts.nccl_comm = nccl_comm
+        opts.comm_stream = comm_stream
         self._opts = opts
         self.handle = self._L.disc_b200_context_create(ctypes.byref(opts))
         self.exec_handle = None

@@ -1,0 +1,167 @@
+"""Column-parallel (N-split) linears over the GPUs of one box.
+
+Rank ``r`` of ``g`` holds rows ``[r * N / g, (r + 1) * N / g)`` of a weight
+``[N, K]`` with their scales and bias and computes ``Y_r = X W_r^T`` of shape
+``[M, N / g]``; one all-gather makes ``[g, M, N / g]`` on every rank.  That is
+the pattern of the reference's ``ral_all_gather`` custom call
+(tao_compiler/mlir/ral/collective.cu.cc:226-309): NCCL concatenates rank-major,
+so the gathered buffer is *not* the row-major ``[M, N]`` matrix.  Here it never
+has to become one: the GEMM epilogue writes slot ``r`` of the gather buffer
+directly, NCCL gathers in place, and the next linear (``ops.qgemm(...,
+a_gathered=True)``) and the next norm (``x_gathered=True``) read the slabs where
+they lie.
+
+One process per GPU.  The communicator is made by this library's own NCCL
+binding; the 128-byte id travels over whatever ``torch.distributed`` group the
+processes already share (gloo is enough).
+"""
+import ctypes
+from typing import List, Optional, Tuple
+
+import torch
+
+from . import lib as _lib
+
+
+def column_share(n: int, world: int, rank: int, multiple: int = 16) -> Tuple[int, int]:
+    """Rows ``[begin, end)`` of an ``[N, K]`` weight that ``rank`` owns.
+
+    Every rank gets the same count (the all-gather needs equal shares), a
+    multiple of ``multiple`` (16: the TMA alignment of a slab of the gathered
+    activation).  ``n`` must split that way."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError("rank must be in [0, world)")
+    if n % (world * multiple) != 0:
+        raise ValueError(f"{n} output channels do not split into {world} shares that are multiples of {multiple}")
+    share = n // world
+    return rank * share, (rank + 1) * share
+
+
+def gathered_to_rowmajor(buf: torch.Tensor) -> torch.Tensor:
+    """``[g, M, C]`` rank-major slabs -> the ``[M, g * C]`` matrix they stand for
+    (a copy; the kernels never need it, tests and hosts at the end of a model do)."""
+    g, m, c = buf.shape
+    return buf.permute(1, 0, 2).reshape(m, g * c)
+
+
+def rowmajor_to_gathered(x: torch.Tensor, world: int) -> torch.Tensor:
+    """Inverse of :func:`gathered_to_rowmajor`."""
+    m, n = x.shape
+    if n % world:
+        raise ValueError("columns do not split evenly")
+    return x.reshape(m, world, n // world).permute(1, 0, 2).contiguous()
+
+
+class Communicator:
+    """An NCCL communicator of this library (``disc_b200_nccl_comm_create``)."""
+
+    def __init__(self, rank: int, world: int, unique_id: bytes):
+        if len(unique_id) != 128:
+            raise ValueError("an NCCL unique id has 128 bytes")
+        self.rank, self.world = rank, world
+        self._lib = _lib.load()
+        handle = ctypes.c_void_p()
+        buf = ctypes.create_string_buffer(unique_id, 128)
+        _lib.check(self._lib.disc_b200_nccl_comm_create(buf, world, rank, ctypes.byref(handle)))
+        self.handle = handle.value
+
+    @staticmethod
+    def new_unique_id() -> bytes:
+        buf = ctypes.create_string_buffer(128)
+        _lib.check(_lib.load().disc_b200_nccl_unique_id(buf))
+        return buf.raw
+
+    @classmethod
+    def from_torch_distributed(cls, device: torch.device, group=None) -> "Communicator":
+        """Rank 0 makes the id; it reaches the others through ``torch.distributed``."""
+        import torch.distributed as dist
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        torch.cuda.set_device(device)
+        box: List[Optional[bytes]] = [cls.new_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        return cls(rank, world, box[0])
+
+    @classmethod
+    def single(cls) -> "Communicator":
+        """A one-rank communicator (the same code path on one GPU)."""
+        return cls(0, 1, cls.new_unique_id())
+
+    def all_gather_(self, buf: torch.Tensor) -> torch.Tensor:
+        """In place: ``buf`` is ``[world, ...]`` and slot ``rank`` holds this rank's share."""
+        if buf.shape[0] != self.world or not buf.is_contiguous():
+            raise ValueError("gather buffer must be contiguous [world, ...]")
+        share = buf[self.rank]
+        nbytes = share.numel() * share.element_size()
+        stream = torch.cuda.current_stream(buf.device).cuda_stream
+        _lib.check(self._lib.disc_b200_all_gather(self.handle, share.data_ptr(), buf.data_ptr(), nbytes, stream))
+        return buf
+
+    def all_reduce_max_(self, t: torch.Tensor) -> torch.Tensor:
+        """In place elementwise maximum over the ranks (float32)."""
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise ValueError("all_reduce_max_ takes a contiguous float32 tensor")
+        stream = torch.cuda.current_stream(t.device).cuda_stream
+        _lib.check(self._lib.disc_b200_all_reduce_f32(self.handle, t.data_ptr(), t.data_ptr(), t.numel(), 2, stream))
+        return t
+
+    def close(self) -> None:
+        if self.handle:
+            self._lib.disc_b200_nccl_comm_destroy(self.handle)
+            self.handle = None
+
+
+class ColumnParallelQLinear:
+    """One rank's shard of a W8A8 linear with per-channel weight scales.
+
+    ``forward`` takes the int8 activation (row-major ``[M, K]`` or gathered
+    ``[g, M, K / g]``) with its per-row scales and returns the gathered fp16
+    output ``[g, M, N / g]`` (``gather=True``) or just the local ``[M, N / g]``
+    (``gather=False``: the consumer works on the local columns, e.g. attention
+    heads or the SwiGLU product)."""
+
+    def __init__(self, wq: torch.Tensor, w_scale: torch.Tensor, bias: Optional[torch.Tensor],
+                 comm: Optional[Communicator], rows: Optional[Tuple[int, int]] = None):
+        world = comm.world if comm else 1
+        rank = comm.rank if comm else 0
+        if rows is None:
+            rows = column_share(wq.shape[0], world, rank)
+        b, e = rows
+        self.comm = comm
+        self.world, self.rank = world, rank
+        self.wq = wq[b:e].contiguous()
+        self.w_scale = w_scale[b:e].contiguous()
+        self.bias = bias[b:e].contiguous() if bias is not None else None
+        self.n_local = e - b
+
+    def forward(self, xq: torch.Tensor, x_scale: torch.Tensor, *, a_gathered: bool = False, gather: bool = True,
+                act: Optional[str] = None) -> torch.Tensor:
+        from . import ops
+        m = xq.shape[1] if a_gathered else xq.shape[0]
+        if not gather:
+            return ops.qgemm(xq, self.wq, x_scale=x_scale, w_scale=self.w_scale, bias=self.bias, act=act,
+                             out_dtype=torch.float16, a_gathered=a_gathered)
+        buf = torch.empty((self.world, m, self.n_local), dtype=torch.float16, device=xq.device)
+        ops.qgemm(xq, self.wq, x_scale=x_scale, w_scale=self.w_scale, bias=self.bias, act=act,
+                  out_dtype=torch.float16, out=buf[self.rank], a_gathered=a_gathered)
+        if self.world > 1:
+            self.comm.all_gather_(buf)
+        return buf
+
+
+def quantize_rows_gathered(comm: Optional[Communicator], gate: torch.Tensor, up: Optional[torch.Tensor] = None):
+    """Per-row dynamic int8 quantization of ``h = silu(gate) * up`` (``h = gate``
+    without ``up``) whose columns are spread over the ranks: local row maxima,
+    maximum over the ranks, quantize into this rank's slot, all-gather.
+    Returns ``(q [g, M, C] int8, row_scale [M])``."""
+    from . import ops
+    world = comm.world if comm else 1
+    rank = comm.rank if comm else 0
+    m, c = gate.shape
+    scale = ops.row_scale_local(gate, up)
+    if world > 1:
+        comm.all_reduce_max_(scale)
+    buf = torch.empty((world, m, c), dtype=torch.int8, device=gate.device)
+    ops.quantize_rows(gate, scale, up, out=buf[rank])
+    if world > 1:
+        comm.all_gather_(buf)
+    return buf, scale

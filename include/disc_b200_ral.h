@@ -224,14 +224,66 @@ typedef struct disc_b200_norm_args {
   float eps;
   int32_t type;
   int32_t rms;
+  /* x stored as column slabs (the buffer disc_b200_qgemm_all_gather returns):
+   * element (r, c) at x[(c / x_slab_cols) * x_slab_stride + r * x_slab_cols +
+   * c % x_slab_cols]; 0 = plain row-major. */
+  int64_t x_slab_cols;
+  int64_t x_slab_stride;
 } disc_b200_norm_args;
 int32_t disc_b200_norm(const disc_b200_norm_args* args, void* stream);
+
+/* Per-row symmetric int8 quantization of h = up ? silu(gate) * up : gate in
+ * two passes, for rows whose columns are spread over the GPUs of a
+ * column-parallel split: pass 0 writes row_scale[r] = max(max|h[r, :]| / 127,
+ * FLT_EPSILON) over the local columns; the caller takes the maximum over the
+ * ranks (disc_b200_all_reduce_f32, op 2); pass 1 writes
+ * q = sat(rne(h / row_scale[r])).  gate / up have row stride ld, q row stride
+ * ldq (elements).  No counterpart in the reference (dynamic quantization is
+ * rejected there, disc_lower_quantize_and_dequantize.cc:41-43). */
+typedef struct disc_b200_gated_quantize_args {
+  const void* gate;
+  const void* up; /* may be NULL */
+  int64_t ld;
+  int8_t* q; /* pass 1 */
+  int64_t ldq;
+  float* row_scale;
+  int64_t rows, cols;
+  int32_t type;
+  int32_t pass;
+} disc_b200_gated_quantize_args;
+int32_t disc_b200_gated_quantize(const disc_b200_gated_quantize_args* args, void* stream);
 
 /* softmax(x * scale + mask) over the last axis; lens / mask may be NULL
  * (kStitch softmax; same reference files as above). */
 int32_t disc_b200_softmax(const void* x, void* y, int32_t type, int64_t rows, int64_t cols,
                           int64_t rows_per_batch, const int32_t* lens, const void* mask,
                           float scale, int32_t log_softmax, void* stream);
+
+/* ---- Collectives of the column-parallel (N-split) configuration.
+ * One process per GPU.  NCCL is reached through dlopen (the copy already
+ * mapped into the process, else the system's libnccl.so.2), so the library
+ * loads without it.  The communicator made here (or any ncclComm_t of the same
+ * NCCL) goes into disc_b200_context_options.nccl_comm for the custom calls
+ * ral_all_gather / ral_all_reduce / ral_async_collective_done
+ * (tao_compiler/mlir/ral/collective.cu.cc:60-309,398-504 in the reference, which
+ * takes its communicator from the execution context the same way) and
+ * disc_b200_qgemm_all_gather. */
+
+/* NCCL version code (e.g. 22809) when NCCL could be bound, 0 otherwise. */
+int32_t disc_b200_nccl_available(void);
+/* Rank 0 makes the 128-byte id and hands it to the other ranks (any host
+ * channel); every rank then creates its communicator with it. */
+int32_t disc_b200_nccl_unique_id(void* id128);
+int32_t disc_b200_nccl_comm_create(const void* id128, int32_t nranks, int32_t rank, void** comm);
+int32_t disc_b200_nccl_comm_destroy(void* comm);
+/* recv[r * bytes_per_rank ...] = rank r's send buffer; in place when
+ * send == recv + rank * bytes_per_rank. */
+int32_t disc_b200_all_gather(void* comm, const void* send, void* recv, int64_t bytes_per_rank,
+                             void* stream);
+/* op: 0 sum, 1 prod, 2 max, 3 min (per-token activation scales of a row that
+ * is spread over the ranks are agreed on with max). */
+int32_t disc_b200_all_reduce_f32(void* comm, const float* send, float* recv, int64_t count,
+                                 int32_t op, void* stream);
 
 /* ------------------------------------------------------------------------
  * 4. Diagnostics.
