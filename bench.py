@@ -41,9 +41,10 @@ def _args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=M_ROWS, help="activation rows per rank and step")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=32, help="decoder layers of the llama7b workload")
     ap.add_argument("--profile", action="store_true",
                     help="for ncu captures: only warm-up and timed steps (no clock hold, e2e or CPU legs)")
-    ap.add_argument("--workload", default="qlinear", choices=["qlinear", "bert_base", "bert_large"],
+    ap.add_argument("--workload", default="qlinear", choices=["qlinear", "bert_base", "bert_large", "llama7b"],
                     help="qlinear (default, configuration 1) or a W8A8 encoder forward (configurations 2 / 3)")
     return ap.parse_args()
 
@@ -516,10 +517,153 @@ def run_encoder(args):
         dist.destroy_process_group()
 
 
+def run_decoder(args):
+    """Configuration 4: Llama-7B-shaped W8A8 decoder, every linear split by output channels over
+    the ranks and followed by an NCCL all-gather.  One step = prefill of 8 x 2048 tokens through
+    all layers; decode steps (one token per sequence) are timed beside it.  Total work is fixed
+    as ranks are added ("strong")."""
+    import torch
+    import torch.distributed as dist
+    from bladedisc_b200 import ops, tp
+    from bladedisc_b200.decoder import DecoderConfig, QuantDecoder
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the quantized path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    comm = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        comm = tp.Communicator.from_torch_distributed(dev)
+    cfg = DecoderConfig.llama7b(layers=args.layers)
+    dec = QuantDecoder(cfg, comm, seed=1238, device=dev)
+    batch, seq = 8, 2048
+    gen = torch.Generator().manual_seed(4324)
+    ids_pin = torch.randint(0, cfg.vocab, (batch, seq), generator=gen).pin_memory()
+    ids_d = ids_pin.to(dev)
+    last_pin = torch.empty((batch, cfg.hidden), dtype=torch.float16).pin_memory()
+    dec.start(batch, seq + 8)
+    out = [None]
+
+    def device_step():
+        dec.pos = 0
+        out[0] = dec.forward(ids_d)
+
+    def e2e_step():
+        ids_d.copy_(ids_pin, non_blocking=True)
+        device_step()
+        last_pin.copy_(out[0].view(batch, seq, cfg.hidden)[:, -1, :], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1)
+
+    steps = min(args.steps, 10)
+    for _ in range(3):
+        device_step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    dev_ms = timed(device_step, steps)
+    clocks = sampler.stop() if rank == 0 else None
+    e2e_step()
+    e2e_steps = min(steps, 5)
+    e2e_ms = timed(e2e_step, e2e_steps)
+    # decode: context of 128 tokens, then one token per sequence and step
+    decode = {}
+    for b in (1, 8, 64):
+        dec.start(b, 128 + 40)
+        ctx_ids = torch.randint(0, cfg.vocab, (b, 128), generator=gen).to(dev)
+        nxt = torch.randint(0, cfg.vocab, (b, 1), generator=gen).to(dev)
+        dec.forward(ctx_ids)
+        for _ in range(3):
+            dec.forward(nxt)
+        # A decode step is ~40 short launches per layer.  On one GPU it is replayed from a CUDA
+        # graph (captured at one cache position, so every replay does the work of that position).
+        # With several ranks it runs eagerly: collectives are kept out of graph capture here, a
+        # capture that fails on one rank only would leave the ranks in different collectives.
+        step, graph = (lambda: dec.forward(nxt)), None
+        if world == 1:
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream())
+            try:
+                with torch.cuda.stream(side):
+                    dec.forward(nxt)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    dec.forward(nxt)
+                step = graph.replay
+            except Exception:
+                graph = None
+                torch.cuda.synchronize()
+        decode_graph = graph is not None
+        for _ in range(3):
+            step()
+        ms = timed(step, 32)
+        decode[b] = ms / 32
+        del graph
+    if ops.kernel_status() != 0:
+        raise SystemExit("kernel status non-zero: a bounded wait ran out")
+    vals = [dev_ms, e2e_ms] + [decode[b] for b in (1, 8, 64)]
+    times = torch.tensor(vals, dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms, d1, d8, d64 = times.tolist()
+    if rank == 0:
+        tokens = batch * seq
+        linear_ops = 2.0 * tokens * cfg.layers * (4 * cfg.hidden * cfg.hidden + 3 * cfg.hidden * cfg.ffn)
+        weight_bytes = cfg.layers * (4 * cfg.hidden * cfg.hidden + 3 * cfg.hidden * cfg.ffn)
+        line = {
+            "metric": "quant_llama7b_prefill_tokens_per_s", "value": tokens * steps / (dev_ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": dev_ms / steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
+            "config": {"workload": f"llama-7b-shaped W8A8 decoder, {cfg.layers} layers, hidden {cfg.hidden}, ffn {cfg.ffn}, "
+                                   f"prefill {batch} x {seq} tokens, per-token dynamic int8 activations",
+                       "parallelism": f"column-parallel N-split over {world} rank(s), NCCL all-gather after every "
+                                      "gathered linear (4 per layer), all-reduce(max) of row scales (2 per layer)",
+                       "l2": "activations of a step (hundreds of MB) are rewritten every step",
+                       "note": "attention (SDPA) and RoPE run in torch, a library call as the reference's ral_gemm; "
+                               "every linear, norm and quantize is this library's kernel",
+                       "linear_int8_tops": linear_ops * steps / (dev_ms * 1e-3) / 1e12,
+                       "decode_ms_per_step": {"batch1": d1, "batch8": d8, "batch64": d64, "context": 128,
+                                              "cuda_graph": decode_graph},
+                       "decode_weight_stream_gbs_batch1": weight_bytes / world / (d1 * 1e-3) / 1e9},
+            "e2e": {"value": tokens * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": int(ids_pin.numel() * 8), "d2h_bytes_per_step": int(last_pin.numel() * 2),
+                    "steps": e2e_steps},
+            "gpu_launches": dec.launches_per_layer() * cfg.layers * steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if comm is not None:
+        comm.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     args = _args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "llama7b":
+        run_decoder(args)
     elif args.workload != "qlinear":
         run_encoder(args)
     else:

@@ -31,6 +31,7 @@ from typing import List, Optional, Tuple
 
 import torch
 import torch.nn.functional as F
+from torch.nn.attention import SDPBackend, sdpa_kernel
 
 from . import ops
 from .tp import ColumnParallelQLinear, Communicator, column_share, quantize_rows_gathered
@@ -65,6 +66,9 @@ def _quantize_weight(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     scale = (w.abs().amax(dim=1) / 127.0).clamp_min(torch.finfo(torch.float32).eps)
     q = torch.round(w.double() / scale.double()[:, None]).clamp_(-128, 127).to(torch.int8)
     return q, scale.float()
+
+
+_SDPA_BACKENDS = [SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION, SDPBackend.MATH]
 
 
 class _Layer:
@@ -109,18 +113,26 @@ class QuantDecoder:
         self.g_final = (1.0 + rnd(H, std=0.1)).half()
         self.kv: Optional[List[Tuple[torch.Tensor, torch.Tensor]]] = None
         self.pos = 0
+        self._cos = self._sin = None
 
     def _linear(self, wq: torch.Tensor, scale: torch.Tensor) -> ColumnParallelQLinear:
         return ColumnParallelQLinear(wq, scale, None, self.comm, rows=(0, wq.shape[0]))
 
     # ------------------------------------------------------------------ pieces
+    def _rope_tables(self, upto: int) -> None:
+        half = self.cfg.head_dim // 2
+        inv = self.cfg.rope_theta ** (-torch.arange(half, device=self.device, dtype=torch.float32) / half)
+        ang = torch.arange(upto, device=self.device, dtype=torch.float32)[:, None] * inv[None, :]
+        self._cos, self._sin = ang.cos(), ang.sin()
+
     def _rope(self, x: torch.Tensor, pos0: int) -> torch.Tensor:
         """x [B, S, h, d]; rotates pairs (i, i + d/2) by position * theta^(-2i/d)."""
         b, s, h, d = x.shape
         half = d // 2
-        inv = self.cfg.rope_theta ** (-torch.arange(half, device=x.device, dtype=torch.float32) / half)
-        ang = (torch.arange(pos0, pos0 + s, device=x.device, dtype=torch.float32)[:, None] * inv[None, :])
-        cos, sin = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
+        if getattr(self, "_cos", None) is None or self._cos.shape[0] < pos0 + s:
+            self._rope_tables(max(pos0 + s, 256))
+        cos = self._cos[pos0:pos0 + s][None, :, None, :]
+        sin = self._sin[pos0:pos0 + s][None, :, None, :]
         xf = x.float()
         x1, x2 = xf[..., :half], xf[..., half:]
         return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).half()
@@ -134,10 +146,13 @@ class QuantDecoder:
         kc[:, :, self.pos:self.pos + seq] = k.transpose(1, 2)
         vc[:, :, self.pos:self.pos + seq] = v.transpose(1, 2)
         end = self.pos + seq
-        if self.pos == 0:
-            o = F.scaled_dot_product_attention(q.transpose(1, 2), kc[:, :, :end], vc[:, :, :end], is_causal=True)
-        else:  # decode: the new tokens see the whole cache
-            o = F.scaled_dot_product_attention(q.transpose(1, 2), kc[:, :, :end], vc[:, :, :end])
+        # Library attention, without the backend that builds a new plan for every
+        # cache length (tens of milliseconds on the host per decode step).
+        with sdpa_kernel(_SDPA_BACKENDS):
+            if self.pos == 0:
+                o = F.scaled_dot_product_attention(q.transpose(1, 2), kc[:, :, :end], vc[:, :, :end], is_causal=True)
+            else:  # decode: the new tokens see the whole cache
+                o = F.scaled_dot_product_attention(q.transpose(1, 2), kc[:, :, :end], vc[:, :, :end])
         return o.transpose(1, 2).reshape(batch * seq, hl * d)
 
     def start(self, batch: int, max_seq: int) -> None:
@@ -147,6 +162,7 @@ class QuantDecoder:
                     torch.zeros(batch, hl, max_seq, d, dtype=torch.float16, device=self.device))
                    for _ in range(cfg.layers)]
         self.pos = 0
+        self._rope_tables(max_seq)
 
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
         """ids [B, S] (prefill when the cache is empty, else S new tokens per
@@ -216,8 +232,9 @@ def reference_forward(dec: QuantDecoder, ids: torch.Tensor) -> torch.Tensor:
         q, k = dec._rope(q, 0), dec._rope(k, 0)
         dec.pos = save
         # the same library call as the kernel path: attention is not one of the kernels under test
-        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2).contiguous(),
-                                           v.transpose(1, 2).contiguous(), is_causal=True)
+        with sdpa_kernel(_SDPA_BACKENDS):
+            o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2).contiguous(),
+                                               v.transpose(1, 2).contiguous(), is_causal=True)
         att = o.transpose(1, 2).reshape(batch * seq, hl * d).float()
         o = lin(L.o, fq_rows(att))
         h = (h.float() + o).half()

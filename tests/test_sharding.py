@@ -86,3 +86,75 @@ def test_two_rank_gloo_sharding():
         assert work == [32.0, float(sum(lens))]        # every sequence counted once
         assert sorted(sum(gathered, [])) == list(range(32))
         assert rows == 1000.0
+
+
+# ------------------------------------------------ column-parallel (N-split) host logic
+def test_column_share_and_gathered_layout():
+    from bladedisc_b200 import tp
+    for world in (1, 2, 4, 8):
+        spans = [tp.column_share(11008, world, r) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == 11008
+        assert len({e - b for b, e in spans}) == 1 and all((e - b) % 16 == 0 for b, e in spans)
+    with pytest.raises(ValueError):
+        tp.column_share(11008, 3, 0)      # not an even split
+    with pytest.raises(ValueError):
+        tp.column_share(4096, 8, 8)
+    x = torch.arange(6 * 8).reshape(6, 8)
+    g = tp.rowmajor_to_gathered(x, 4)
+    assert g.shape == (4, 6, 2) and torch.equal(g[1, :, 0], x[:, 2])
+    assert torch.equal(tp.gathered_to_rowmajor(g), x)
+
+
+def _tp_worker(rank, world, port, q):
+    """Each rank computes its shard of a quantized linear with the CPU oracle; the
+    shards meet through a real all-gather (gloo) in the rank-major layout the GPU
+    path produces, and the next linear reads that layout slab by slab."""
+    import numpy as np
+    from oracle import c
+    from bladedisc_b200 import tp
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(5)  # same data on every rank
+        M, K, N, N2 = 9, 64, 32 * world, 16
+        a = rng.integers(-127, 128, (M, K), dtype=np.int8)
+        w = rng.integers(-127, 128, (N, K), dtype=np.int8)
+        w2 = rng.integers(-127, 128, (N2, N), dtype=np.int8)
+        sw = (rng.random(N) * 9e-3 + 1e-3).astype(np.float32)
+        b, e = tp.column_share(N, world, rank)
+        _, mine = c.qgemm_epilogue(c.qgemm_acc(a, w[b:e]), x_scale=np.float32(0.02), w_scale=sw[b:e],
+                                   out_scale=np.float32(0.05), div_out=True)
+        slots = [torch.empty((M, e - b), dtype=torch.int8) for _ in range(world)]
+        dist.all_gather(slots, torch.from_numpy(mine))
+        gathered = torch.stack(slots)                      # [g, M, N / g]
+        _, full = c.qgemm_epilogue(c.qgemm_acc(a, w), x_scale=np.float32(0.02), w_scale=sw,
+                                   out_scale=np.float32(0.05), div_out=True)
+        ok_layout = bool((tp.gathered_to_rowmajor(gathered).numpy() == full).all())
+        # K of the next linear walked slab by slab equals the row-major product
+        acc = np.zeros((M, N2), dtype=np.int32)
+        share = e - b
+        for s in range(world):
+            acc += c.qgemm_acc(np.ascontiguousarray(gathered[s].numpy()), np.ascontiguousarray(w2[:, s * share:(s + 1) * share]))
+        ok_chain = bool((acc == c.qgemm_acc(full, w2)).all())
+        # per-row scale of a row spread over the ranks = max of the local scales
+        local = torch.tensor(np.abs(mine).max(axis=1) / 127.0)
+        dist.all_reduce(local, op=dist.ReduceOp.MAX)
+        ok_scale = bool(np.allclose(local.numpy(), np.abs(full).max(axis=1) / 127.0))
+        q.put((rank, ok_layout, ok_chain, ok_scale))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_column_parallel_on_cpu(golden):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29650 + random.randint(0, 200)
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got == [(0, True, True, True), (1, True, True, True)]
