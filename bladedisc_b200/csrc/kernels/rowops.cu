@@ -100,6 +100,12 @@ struct VecT<float> {
   static __device__ __forceinline__ uint4 pack(const float* f) {
     return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
   }
+  static __device__ __forceinline__ void unpack(const uint4& v, float* f) {
+    f[0] = __uint_as_float(v.x);
+    f[1] = __uint_as_float(v.y);
+    f[2] = __uint_as_float(v.z);
+    f[3] = __uint_as_float(v.w);
+  }
   static __device__ __forceinline__ float load1(const float* p) { return *p; }
   static __device__ __forceinline__ void store1(float* p, float v) { *p = v; }
   static __device__ __forceinline__ float round_to_storage(float v) { return v; }
@@ -121,6 +127,15 @@ struct VecT<__half> {
     u.z = *reinterpret_cast<uint32_t*>(&h2);
     u.w = *reinterpret_cast<uint32_t*>(&h3);
     return u;
+  }
+  static __device__ __forceinline__ void unpack(const uint4& v, float* f) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      f[2 * i] = p.x;
+      f[2 * i + 1] = p.y;
+    }
   }
   static __device__ __forceinline__ float load1(const __half* p) { return __half2float(*p); }
   static __device__ __forceinline__ void store1(__half* p, float v) { *p = __float2half_rn(v); }
@@ -296,11 +311,21 @@ template <int G, int R>
 struct RowIndex {
   int t;
   int64_t row0;  // first of the R rows of this group
-  __device__ __forceinline__ RowIndex() {
+  __device__ __forceinline__ RowIndex() : RowIndex(blockIdx.x) {}
+  __device__ __forceinline__ explicit RowIndex(int64_t blk) {
     t = threadIdx.x % G;
-    row0 = (static_cast<int64_t>(blockIdx.x) * (kBlock / G) + threadIdx.x / G) * R;
+    row0 = (blk * (kBlock / G) + threadIdx.x / G) * R;
   }
 };
+// Blocks of work for `rows` rows: the row kernels walk them with a stride of
+// gridDim.x (a grid sized to what the GPU holds at once) and fetch the next
+// block's rows into registers before they work on the current one, so that
+// loads stay in flight while a warp computes.
+template <int G, int R>
+__device__ __forceinline__ int64_t row_blocks(int64_t rows) {
+  constexpr int64_t kRowsPerBlock = static_cast<int64_t>(kBlock / G) * R;
+  return (rows + kRowsPerBlock - 1) / kRowsPerBlock;
+}
 
 // E values of one vector quantized at `d` (zero point 0, int8 range) into biased
 // floats for store_q.  The rounding constant is added first, the clamp works on
@@ -603,42 +628,68 @@ __device__ __forceinline__ float ex2_approx(float x) {
 template <typename T, int G, int NV, int R>
 __global__ void __launch_bounds__(kBlock, (NV * R <= 4 ? 3 : (NV * R <= 8 ? 2 : 1)))
 softmax_kernel(SoftmaxParams p, int aligned) {
+  // Issue bound unless lean: the logits are unpacked once, the exponentials are
+  // kept (one special-function op per element, not one per pass), whole vectors
+  // inside the valid length take a path without per-element predicates.
   constexpr int E = VecT<T>::kElems;
   constexpr float kLog2e = 1.4426950408889634f;
   __shared__ float red[R * 8];
-  const RowIndex<G, R> ix;
-  const int t = ix.t;
   const int cols = static_cast<int>(p.cols);
   const bool al = aligned != 0;
   const T* xb = reinterpret_cast<const T*>(p.x);
   const T* mb = reinterpret_cast<const T*>(p.mask);
-  uint4 raw[R][NV];
+  const int64_t nblk = row_blocks<G, R>(p.rows);
+  uint4 nxt[R][NV];
+  auto fetch = [&](int64_t blk) {
+    const RowIndex<G, R> fx(blk);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int64_t row = fx.row0 + r < p.rows ? fx.row0 + r : 0;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) nxt[r][i] = load_vec<T>(xb + row * p.cols, cols, fx.t + i * G, al, 0.f);
+    }
+  };
+  if (blockIdx.x < nblk) fetch(blockIdx.x);
+  for (int64_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
+  const RowIndex<G, R> ix(blk);
+  const int t = ix.t;
+  float f[R][NV][E];
   bool live[R];
   int len[R];
+  {
+    uint4 raw[R][NV];
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    live[r] = ix.row0 + r < p.rows;
-    const int64_t row = live[r] ? ix.row0 + r : 0;
-    const int64_t batch = row / p.rows_per_batch;
-    len[r] = p.lens ? min(cols, __ldg(p.lens + batch)) : cols;
+    for (int r = 0; r < R; ++r)
 #pragma unroll
-    for (int i = 0; i < NV; ++i) raw[r][i] = load_vec<T>(xb + row * p.cols, cols, t + i * G, al, 0.f);
-    if (mb) {
-      // fold the additive mask in once; the biased logits replace the raw values in the
-      // storage type (as an unfused add would leave them) and carry the scale already
+      for (int i = 0; i < NV; ++i) raw[r][i] = nxt[r][i];
+    if (blk + gridDim.x < nblk) fetch(blk + gridDim.x);
 #pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const uint4 mv = load_vec<T>(mb + batch * p.cols, cols, t + i * G, al, 0.f);
-        float f[E];
+    for (int r = 0; r < R; ++r) {
+      live[r] = ix.row0 + r < p.rows;
+      const int64_t row = live[r] ? ix.row0 + r : 0;
+      const int64_t batch = row / p.rows_per_batch;
+      len[r] = p.lens ? min(cols, __ldg(p.lens + batch)) : cols;
+      if (mb) {
+        // fold the additive mask in once; the biased logits replace the raw values in the
+        // storage type (as an unfused add would leave them) and carry the scale already
 #pragma unroll
-        for (int j = 0; j < E; ++j) f[j] = VecT<T>::get(raw[r][i], j) * p.scale + VecT<T>::get(mv, j);
-        raw[r][i] = VecT<T>::pack(f);
+        for (int i = 0; i < NV; ++i) {
+          const uint4 mv = load_vec<T>(mb + batch * p.cols, cols, t + i * G, al, 0.f);
+          float a[E], b[E];
+          VecT<T>::unpack(raw[r][i], a);
+          VecT<T>::unpack(mv, b);
+#pragma unroll
+          for (int j = 0; j < E; ++j) a[j] = a[j] * p.scale + b[j];
+          raw[r][i] = VecT<T>::pack(a);
+        }
       }
+#pragma unroll
+      for (int i = 0; i < NV; ++i) VecT<T>::unpack(raw[r][i], f[r][i]);
     }
   }
   const float scale = mb ? 1.f : p.scale;
   const float k = scale * kLog2e;
-  const bool neg = scale < 0.f;
+  const float sgn = scale < 0.f ? -1.f : 1.f;  // a negative scale turns the maximum into the minimum
   float mx[R], sum[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
@@ -646,15 +697,24 @@ softmax_kernel(SoftmaxParams p, int aligned) {
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int nvalid = len[r] - (t + i * G) * E;  // valid elements of this vector (may be <= 0 or >= E)
+      if (nvalid >= E) {
+        if (sgn > 0.f) {
 #pragma unroll
-      for (int j = 0; j < E; ++j) {
-        const float v = VecT<T>::get(raw[r][i], j);
-        if (j < nvalid) a = fmaxf(a, neg ? -v : v);
+          for (int j = 0; j < E; ++j) a = fmaxf(a, f[r][i][j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < E; ++j) a = fmaxf(a, -f[r][i][j]);
+        }
+      } else if (nvalid > 0) {
+#pragma unroll
+        for (int j = 0; j < E; ++j)
+          if (j < nvalid) a = fmaxf(a, sgn * f[r][i][j]);
       }
     }
     mx[r] = a;
   }
   group_reduce<G, R, true>(mx, red);
+  const bool want_log = p.log_softmax != 0;
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     // mx holds max(x) (or max(-x) for a negative scale); the largest logit is |scale| * mx
@@ -665,10 +725,20 @@ softmax_kernel(SoftmaxParams p, int aligned) {
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int nvalid = len[r] - (t + i * G) * E;
+      if (nvalid >= E) {
 #pragma unroll
-      for (int j = 0; j < E; ++j) {
-        const float e = ex2_approx(__fmaf_rn(VecT<T>::get(raw[r][i], j), k, bias));
-        if (j < nvalid) s += e;
+        for (int j = 0; j < E; ++j) {
+          const float e = ex2_approx(__fmaf_rn(f[r][i][j], k, bias));
+          s += e;
+          if (!want_log) f[r][i][j] = e;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < E; ++j) {
+          const float e = j < nvalid ? ex2_approx(__fmaf_rn(f[r][i][j], k, bias)) : 0.f;
+          s += e;
+          if (!want_log) f[r][i][j] = e;
+        }
       }
     }
     sum[r] = s;
@@ -678,25 +748,28 @@ softmax_kernel(SoftmaxParams p, int aligned) {
   for (int r = 0; r < R; ++r) {
     if (!live[r]) continue;
     const float inv = sum[r] > 0.f ? 1.f / sum[r] : 0.f;
-    const float lsum = logf(sum[r]);
-    const float bias = -mx[r] * kLog2e;
     const int64_t off = (ix.row0 + r) * p.cols;
+    if (!want_log) {
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int nvalid = len[r] - (t + i * G) * E;
-      float y[E];
+      for (int i = 0; i < NV; ++i) {
+        float y[E];
 #pragma unroll
-      for (int j = 0; j < E; ++j) {
-        const float x = VecT<T>::get(raw[r][i], j);
-        if (p.log_softmax) {
-          y[j] = j < nvalid ? __fmaf_rn(x, scale, -mx[r]) - lsum : -INFINITY;
-        } else {
-          y[j] = j < nvalid ? ex2_approx(__fmaf_rn(x, k, bias)) * inv : 0.f;
-        }
+        for (int j = 0; j < E; ++j) y[j] = f[r][i][j] * inv;  // masked columns hold 0
+        store_vec<T>(reinterpret_cast<T*>(p.y) + off, cols, t + i * G, al, VecT<T>::pack(y));
       }
-      store_vec<T>(reinterpret_cast<T*>(p.y) + off, cols, t + i * G, al, VecT<T>::pack(y));
+    } else {
+      const float lsum = logf(sum[r]);
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int nvalid = len[r] - (t + i * G) * E;
+        float y[E];
+#pragma unroll
+        for (int j = 0; j < E; ++j) y[j] = j < nvalid ? __fmaf_rn(f[r][i][j], scale, -mx[r]) - lsum : -INFINITY;
+        store_vec<T>(reinterpret_cast<T*>(p.y) + off, cols, t + i * G, al, VecT<T>::pack(y));
+      }
     }
   }
+  }  // block loop
 }
 
 bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -724,6 +797,39 @@ bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) 
     else if ((nvec) <= 1024) DISC_ROW_LAUNCH(KERNEL, T, 256, 4, 1, rows, stream, __VA_ARGS__);         \
     else if ((nvec) <= 2048) DISC_ROW_LAUNCH(KERNEL, T, 256, 8, 1, rows, stream, __VA_ARGS__);         \
     else DISC_ROW_LAUNCH(KERNEL, T, 256, 16, 1, rows, stream, __VA_ARGS__);                            \
+  } while (0)
+
+// The same for kernels that walk row blocks with a stride of gridDim.x and
+// prefetch: the grid is what the GPU holds at once.
+#define DISC_ROW_LAUNCH_P(KERNEL, T, G, NV, R, rows, stream, ...)                                      \
+  do {                                                                                                 \
+    const int64_t groups_per_block = kBlock / (G);                                                     \
+    const int64_t rows_per_block = groups_per_block * (R);                                             \
+    int64_t grid = ((rows) + rows_per_block - 1) / rows_per_block;                                     \
+    static int resident = 0; /* blocks of this instantiation one SM holds */                          \
+    if (resident == 0) {                                                                               \
+      int n = 0;                                                                                       \
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, KERNEL<T, G, NV, R>, kBlock, 0) != cudaSuccess || n < 1) \
+        n = 1;                                                                                         \
+      resident = n;                                                                                    \
+    }                                                                                                  \
+    const int64_t cap = static_cast<int64_t>(sm_count()) * resident;                                   \
+    if (grid > cap) grid = cap;                                                                        \
+    KERNEL<T, G, NV, R><<<static_cast<unsigned>(grid), kBlock, 0, stream>>>(__VA_ARGS__);              \
+  } while (0)
+
+#define DISC_ROW_DISPATCH_P(KERNEL, T, nvec, rows, stream, ...)                                        \
+  do {                                                                                                 \
+    if ((nvec) <= 8) DISC_ROW_LAUNCH_P(KERNEL, T, 8, 1, 4, rows, stream, __VA_ARGS__);                 \
+    else if ((nvec) <= 16) DISC_ROW_LAUNCH_P(KERNEL, T, 8, 2, 2, rows, stream, __VA_ARGS__);           \
+    else if ((nvec) <= 32) DISC_ROW_LAUNCH_P(KERNEL, T, 16, 2, 2, rows, stream, __VA_ARGS__);          \
+    else if ((nvec) <= 64) DISC_ROW_LAUNCH_P(KERNEL, T, 32, 2, 2, rows, stream, __VA_ARGS__);          \
+    else if ((nvec) <= 128) DISC_ROW_LAUNCH_P(KERNEL, T, 32, 4, 1, rows, stream, __VA_ARGS__);         \
+    else if ((nvec) <= 256) DISC_ROW_LAUNCH_P(KERNEL, T, 32, 8, 1, rows, stream, __VA_ARGS__);         \
+    else if ((nvec) <= 512) DISC_ROW_LAUNCH_P(KERNEL, T, 256, 2, 1, rows, stream, __VA_ARGS__);        \
+    else if ((nvec) <= 1024) DISC_ROW_LAUNCH_P(KERNEL, T, 256, 4, 1, rows, stream, __VA_ARGS__);       \
+    else if ((nvec) <= 2048) DISC_ROW_LAUNCH_P(KERNEL, T, 256, 8, 1, rows, stream, __VA_ARGS__);       \
+    else DISC_ROW_LAUNCH_P(KERNEL, T, 256, 16, 1, rows, stream, __VA_ARGS__);                          \
   } while (0)
 
 template <typename T, int G, int NV, int R>
@@ -908,9 +1014,9 @@ cudaError_t softmax_launch(const SoftmaxParams& p, cudaStream_t s, const char** 
   const int aligned = (p.cols % epv == 0) && is_aligned16(p.x) && is_aligned16(p.y) &&
                       (!p.mask || is_aligned16(p.mask));
   if (p.type == kF32)
-    DISC_ROW_DISPATCH(softmax_kernel, float, vectors_per_row<float>(q.cols), q.rows, s, q, aligned);
+    DISC_ROW_DISPATCH_P(softmax_kernel, float, vectors_per_row<float>(q.cols), q.rows, s, q, aligned);
   else
-    DISC_ROW_DISPATCH(softmax_kernel, __half, vectors_per_row<__half>(q.cols), q.rows, s, q, aligned);
+    DISC_ROW_DISPATCH_P(softmax_kernel, __half, vectors_per_row<__half>(q.cols), q.rows, s, q, aligned);
   return cudaGetLastError();
 }
 

@@ -1,7 +1,7 @@
 """Per-kernel sweep: every (M, K, N) point of the quantized-linear configuration
 and the bandwidth kernels, with achieved TOPS / GB/s and the roofline fraction.
 
-    python -m bladedisc_b200.kernel_bench [--quick] [--json out.json]
+    python -m bladedisc_b200.kernel_bench [--quick] [--json out.json] [--only a,b] [--shape M,K,N] [--eager]
 
 Timing: CUDA events on the launching stream around `iters` back-to-back
 launches after 3 warm-ups.  Operand sets rotate through copies whose total
@@ -162,6 +162,7 @@ def main():
     ap.add_argument("--json", default=None)
     ap.add_argument("--only", default=None, help="comma-separated substrings: run only the cases whose kernel name contains one (qgemm, quantize, norm, softmax ...)")
     ap.add_argument("--eager", action="store_true", help="no CUDA graph (for ncu captures); few iterations")
+    ap.add_argument("--shape", default=None, help="M,K,N: only this quantized-linear point (with --only qgemm)")
     args = ap.parse_args()
     global EAGER
     EAGER = args.eager
@@ -170,6 +171,9 @@ def main():
     out = {"peaks": {"hbm_gbs": hbm, "int8_tops": tops_peak, "source": src}, "rows": []}
     ms_list = [7, 64, 4096] if args.quick else MS
     kns = [(768, 3072), (4096, 4096)] if args.quick else KNS
+    if args.shape:
+        m, k, n = (int(v) for v in args.shape.split(","))
+        ms_list, kns = [m], [(k, n)]
     print(f"# peaks ({src}): HBM {hbm:.0f} GB/s, int8 tensor {tops_peak:.0f} TOPS (2 x bf16)")
     print(f"{'kernel':<16}{'M':>6}{'K':>6}{'N':>7}{'out':>9}{'us':>10}{'TOPS':>9}{'GB/s':>9}{'bound':>8}{'frac':>7}")
     for K, N in kns:
