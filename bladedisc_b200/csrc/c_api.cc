@@ -102,6 +102,7 @@ disc_b200::QGemmParams to_params(const disc_b200_qgemm_args* a) {
   p.a_slabs = a->a_slabs;
   p.a_slab_cols = a->a_slab_cols;
   p.a_slab_stride = a->a_slab_stride;
+  p.weights_static = a->weights_static;
   return p;
 }
 

@@ -63,6 +63,12 @@ struct QGemmParams {
   int a_slabs;
   int64_t a_slab_cols;
   int64_t a_slab_stride;
+  // The weight (and nothing else) was final before the previous kernel on the
+  // stream was launched, as inference weights are: the few-row paths then
+  // start fetching it while that kernel still runs (programmatic dependent
+  // launch) and wait for it only before they touch activations, scales or the
+  // output.  0 = assume nothing.
+  int weights_static;
 };
 
 // Bytes of zeroed scratch the small-M path may need for a given problem.

@@ -21,6 +21,8 @@ qgemm_gemv_kernel(const int8_t* __restrict__ a, const int8_t* __restrict__ w, in
                   int64_t ldw, EpiParams ep) {
   extern __shared__ uint4 xs[];  // [MR][K / 16]
   const int kv = K >> 4;         // 16-byte vectors per row
+  grid_dep_launch();  // the next kernel on the stream may start its prologue
+  grid_dep_wait();    // everything read below may come from the kernel before this one
   const int M = static_cast<int>(ep.M);
   for (int i = threadIdx.x; i < MR * kv; i += kGemvThreads) {
     const int m = i / kv, v = i - m * kv;
@@ -109,9 +111,8 @@ cudaError_t launch_gemv_t(const QGemmParams& p, cudaStream_t stream) {
   int64_t blocks = (groups + kGemvThreads / 32 - 1) / (kGemvThreads / 32);
   const int64_t cap = 2 * static_cast<int64_t>(sm_count());
   if (blocks > cap) blocks = cap;
-  kern<<<static_cast<unsigned>(blocks), kGemvThreads, smem, stream>>>(p.a, p.w, static_cast<int>(p.K), p.lda, p.ldw,
-                                                                   make_epi(p));
-  return cudaGetLastError();
+  return launch_dependent(kern, dim3(static_cast<unsigned>(blocks)), dim3(kGemvThreads), smem, stream, p.a, p.w,
+                          static_cast<int>(p.K), p.lda, p.ldw, make_epi(p));
 }
 
 template <typename OutT>

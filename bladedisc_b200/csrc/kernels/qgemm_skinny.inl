@@ -59,7 +59,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
                     const __grid_constant__ CUtensorMap tmap_w, EpiParams ep, int MT, int BN,
-                    int stages, int kbs, int num_kb, int vec_ok, int k3d, SlabA slab) {
+                    int stages, int kbs, int num_kb, int vec_ok, int k3d, SlabA slab, int early_w) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -83,23 +83,27 @@ qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
   uint32_t tmem_cols = 32;
   while (tmem_cols < static_cast<uint32_t>(BN)) tmem_cols <<= 1;
 
-  // Issues the loads of one stage (K blocks kb0 .. kb0 + nk - 1).
-  auto issue_stage = [&](int stage, int kb0) {
+  // Loads of one stage (K blocks kb0 .. kb0 + nk - 1).  which: 1 = weight, 2 =
+  // activation, 3 = both; the call that brings the weight arms the barrier.
+  auto issue_stage = [&](int stage, int kb0, int which) {
     const uint32_t w_dst = smem_base + stage * stage_bytes;
     const uint32_t x_dst = w_dst + kbs * w_bytes;
     if (k3d) {
       // K blocks past the end of K read as zero and still count their bytes
-      mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
-      tma_load_3d(w_dst, &tmap_w, full_bar(stage), 0, static_cast<int>(n0), kb0);
-      tma_load_3d(x_dst, &tmap_x, full_bar(stage), 0, static_cast<int>(m0), kb0);
+      if (which & 1) {
+        mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
+        tma_load_3d(w_dst, &tmap_w, full_bar(stage), 0, static_cast<int>(n0), kb0);
+      }
+      if (which & 2) tma_load_3d(x_dst, &tmap_x, full_bar(stage), 0, static_cast<int>(m0), kb0);
       return;
     }
     const int nk = num_kb - kb0 < kbs ? num_kb - kb0 : kbs;
-    mbar_arrive_expect_tx(full_bar(stage), nk * (w_bytes + x_bytes));
+    if (which & 1) mbar_arrive_expect_tx(full_bar(stage), nk * (w_bytes + x_bytes));
     for (int c = 0; c < nk; ++c) {
       const KCoord kc = k_coord(slab, kb0 + c);
-      tma_load_2d(w_dst + c * w_bytes, &tmap_w, full_bar(stage), kc.wx, static_cast<int>(n0));
-      tma_load_2d(x_dst + c * x_bytes, &tmap_x, full_bar(stage), kc.ax, kc.ay + static_cast<int>(m0));
+      if (which & 1) tma_load_2d(w_dst + c * w_bytes, &tmap_w, full_bar(stage), kc.wx, static_cast<int>(n0));
+      if (which & 2)
+        tma_load_2d(x_dst + c * x_bytes, &tmap_x, full_bar(stage), kc.ax, kc.ay + static_cast<int>(m0));
     }
   };
 
@@ -118,7 +122,18 @@ qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
       mbar_init(tfull_bar, 1);
       *abort_flag = 0;
       fence_mbar_init();
-      for (int s = 0; s < stages && first_kb < num_kb; ++s, first_kb += kbs) issue_stage(s, first_kb);
+      grid_dep_launch();  // the next kernel on the stream may begin its own prologue
+      if (early_w) {
+        // The weight does not depend on the kernel before this one: its first
+        // ring of stages is requested while that kernel may still be running.
+        int kb = 0;
+        for (int s = 0; s < stages && kb < num_kb; ++s, kb += kbs) issue_stage(s, kb, 1);
+        grid_dep_wait();
+        for (int s = 0; s < stages && first_kb < num_kb; ++s, first_kb += kbs) issue_stage(s, first_kb, 2);
+      } else {
+        grid_dep_wait();
+        for (int s = 0; s < stages && first_kb < num_kb; ++s, first_kb += kbs) issue_stage(s, first_kb, 3);
+      }
     }
   } else if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), tmem_cols);
@@ -139,7 +154,7 @@ qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, &g_kernel_status,
                        kStatusTimeoutEmpty))
           break;
-        issue_stage(stage, kb0);
+        issue_stage(stage, kb0, 3);
         if (++stage == stages) {
           stage = 0;
           phase ^= 1;
@@ -179,6 +194,7 @@ qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const int q = warp & 3;
     const int g = (warp - 2) >> 2;
     const int et = threadIdx.x - 64;
+    grid_dep_wait();  // scales may come from the kernel before this one; the output may still be read by it
     // Column constants while the weight streams.
     for (int i = et; i < BN; i += kThreads - 64) {
       const int64_t n = n0 + i;

@@ -921,6 +921,24 @@ bool make_a_tmap(CUtensorMap* tm, const QGemmParams& p, int box_rows) {
   return make_tmap(tm, p.a, rows, p.a_slab_cols, p.lda, box_rows);
 }
 
+// Launch that may overlap the tail of the kernel before it on the stream
+// (programmatic dependent launch); the kernel orders itself with grid_dep_wait().
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 int small_mt(int64_t M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
 
 int small_split(const QGemmParams& p) {
@@ -1134,9 +1152,8 @@ cudaError_t launch_skinny(const QGemmParams& p, cudaStream_t stream, const char*
   const int eb = out_elem_bytes(p.out_dtype);
   const int vec_ok = ((p.ldo * eb) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
   dim3 grid(static_cast<unsigned>((p.N + BN - 1) / BN), static_cast<unsigned>((p.M + kTileM - 1) / kTileM));
-  kern<<<grid, kThreads, kSkinnyDynamic, stream>>>(tx, tw, make_epi(p), MT, BN, stages, kbs, num_kb,
-                                                   vec_ok, k3d, slab_of(p));
-  return cudaGetLastError();
+  return launch_dependent(kern, grid, dim3(kThreads), kSkinnyDynamic, stream, tx, tw, make_epi(p), MT, BN, stages,
+                          kbs, num_kb, vec_ok, k3d, slab_of(p), p.weights_static ? 1 : 0);
 }
 
 template <typename OutT>

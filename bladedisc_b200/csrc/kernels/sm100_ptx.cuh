@@ -192,6 +192,14 @@ __device__ __forceinline__ void cluster_sync_all() {
 // In a shared::cluster address bit 24 selects the odd CTA of a pair; clearing
 // it names the same offset in the even (leader) CTA.
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
+// Programmatic dependent launch.  A kernel launched with the programmatic
+// stream serialization attribute may start while the kernel before it on the
+// stream still runs: grid_dep_wait() blocks until that kernel has completed and
+// its writes are visible (it returns at once without the attribute), and
+// grid_dep_launch() lets the kernel after this one start its own prologue.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // 3-D tiled load, no multicast (coordinates innermost first).
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x,
                                             int y, int z) {

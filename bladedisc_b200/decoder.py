@@ -111,6 +111,10 @@ class QuantDecoder:
             self.layers.append(L)
             del wq, wk, wv, wo, wg, wu, wd
         self.g_final = (1.0 + rnd(H, std=0.1)).half()
+        torch.cuda.synchronize(self.device)  # the weights are final: linears may fetch them early
+        for L in self.layers:
+            for lin in (L.qkv, L.o, L.gate_up, L.down):
+                lin.weights_static = True
         self.kv: Optional[List[Tuple[torch.Tensor, torch.Tensor]]] = None
         self.pos = 0
         self._cos = self._sin = None

@@ -74,7 +74,8 @@ def qgemm(a: torch.Tensor, w: torch.Tensor, *, x_scale: Optional[torch.Tensor] =
           bias: Optional[torch.Tensor] = None, act: Optional[str] = None,
           out_dtype: torch.dtype = torch.int8, fold_out_scale: bool = False,
           x_scale_per_col: bool = False, path: Optional[str] = None, split_k: int = 0,
-          out: Optional[torch.Tensor] = None, a_gathered: bool = False) -> torch.Tensor:
+          out: Optional[torch.Tensor] = None, a_gathered: bool = False,
+          weights_static: bool = False) -> torch.Tensor:
     """out = epilogue(a[..., K] @ w[N, K]^T) with int8 operands and int32 accumulation.
 
     ``fold_out_scale=True`` is the reference custom call ``ral_pdll_qgemm``:
@@ -85,6 +86,10 @@ def qgemm(a: torch.Tensor, w: torch.Tensor, *, x_scale: Optional[torch.Tensor] =
     ``a_gathered=True``: ``a`` is ``[g, M, K / g]``, the buffer an all-gather of
     column-parallel outputs leaves (slab ``r`` holds columns ``r * K / g ...``);
     it is consumed in place, the result is ``[M, N]``.
+
+    ``weights_static=True`` promises that ``w`` was final before the previous
+    kernel on the stream was launched (inference weights): the few-row paths
+    then fetch it while that kernel still runs.
     """
     a = _cuda(a, "a", torch.int8)
     w = _cuda(w, "w", torch.int8)
@@ -110,6 +115,7 @@ def qgemm(a: torch.Tensor, w: torch.Tensor, *, x_scale: Optional[torch.Tensor] =
     if a_gathered:
         args.a_slabs, args.a_slab_cols, args.a_slab_stride = a.shape[0], a.shape[2], a.shape[1] * a.shape[2]
         args.lda = a.shape[2]
+    args.weights_static = 1 if weights_static else 0
     keep = []
     for name, t in (("x", x_scale), ("w", w_scale), ("out", out_scale)):
         if t is not None:

@@ -132,6 +132,9 @@ class ColumnParallelQLinear:
         self.w_scale = w_scale[b:e].contiguous()
         self.bias = bias[b:e].contiguous() if bias is not None else None
         self.n_local = e - b
+        # set once the weights are final and the stream that made them has been synchronised:
+        # the few-row kernels then fetch them while the kernel before them still runs
+        self.weights_static = False
 
     def forward(self, xq: torch.Tensor, x_scale: torch.Tensor, *, a_gathered: bool = False, gather: bool = True,
                 act: Optional[str] = None) -> torch.Tensor:
@@ -139,10 +142,11 @@ class ColumnParallelQLinear:
         m = xq.shape[1] if a_gathered else xq.shape[0]
         if not gather:
             return ops.qgemm(xq, self.wq, x_scale=x_scale, w_scale=self.w_scale, bias=self.bias, act=act,
-                             out_dtype=torch.float16, a_gathered=a_gathered)
+                             out_dtype=torch.float16, a_gathered=a_gathered, weights_static=self.weights_static)
         buf = torch.empty((self.world, m, self.n_local), dtype=torch.float16, device=xq.device)
         ops.qgemm(xq, self.wq, x_scale=x_scale, w_scale=self.w_scale, bias=self.bias, act=act,
-                  out_dtype=torch.float16, out=buf[self.rank], a_gathered=a_gathered)
+                  out_dtype=torch.float16, out=buf[self.rank], a_gathered=a_gathered,
+                  weights_static=self.weights_static)
         if self.world > 1:
             self.comm.all_gather_(buf)
         return buf

@@ -152,6 +152,12 @@ typedef struct disc_b200_qgemm_args {
   int32_t a_slabs;
   int64_t a_slab_cols;
   int64_t a_slab_stride;
+  /* Non-zero: `w` was final before the previous kernel on the stream was
+   * launched (inference weights).  The few-row paths then fetch it while that
+   * kernel still runs and wait for it only before touching anything else
+   * (the reference's ral_qgemm carries the same promise as weight_is_const,
+   * stream_executor_based_impl.cc:427-433). */
+  int32_t weights_static;
 } disc_b200_qgemm_args;
 
 int32_t disc_b200_qgemm(const disc_b200_qgemm_args* args, void* stream);

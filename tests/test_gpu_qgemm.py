@@ -352,3 +352,51 @@ def test_gathered_activation_layout(ops, M, g, slab, N, path):
     got8 = ops.qgemm(_dev(gathered), _dev(w), x_scale=_dev(sx), w_scale=_dev(sw), bias=_dev(bias),
                      out_scale=_dev(np.array([s_out])), path=path, a_gathered=True).cpu().numpy()
     assert (got8 == want8).all()
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 1024, 520), (7, 4096, 1000), (24, 2048, 392), (100, 768, 3072)])
+def test_early_weight_fetch_orders_itself(ops, M, K, N):
+    """weights_static lets the few-row kernels request the weight before the
+    kernel in front of them has finished; activations, scales and the output
+    are only touched after it has.  A chain in which each linear's activation
+    is written by the kernel right before it, repeated back to back, must give
+    the same bytes as the same chain with a synchronize between the steps."""
+    gen = torch.Generator(device="cuda").manual_seed(M + N)
+    w1 = torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda", generator=gen)
+    w2 = torch.randint(-127, 128, (K, N), dtype=torch.int8, device="cuda", generator=gen)
+    sw1 = torch.rand(N, device="cuda", generator=gen) * 9e-3 + 1e-3
+    sw2 = torch.rand(K, device="cuda", generator=gen) * 9e-3 + 1e-3
+    x0 = torch.randn(M, K, device="cuda", generator=gen).half()
+    torch.cuda.synchronize()
+
+    def chain(sync):
+        x = x0
+        outs = []
+        for _ in range(6):
+            q, s = ops.dynamic_quantize(x)                       # writes the activation and its scales
+            h = ops.qgemm(q, w1, x_scale=s, w_scale=sw1, out_dtype=torch.float16, weights_static=True)
+            if sync:
+                torch.cuda.synchronize()
+            q2, s2 = ops.dynamic_quantize(h)
+            x = ops.qgemm(q2, w2, x_scale=s2, w_scale=sw2, out_dtype=torch.float16, weights_static=True)
+            x = (x.float() / x.float().abs().amax().clamp_min(1e-3)).half()  # keep the chain in range
+            if sync:
+                torch.cuda.synchronize()
+            outs.append(x)
+        torch.cuda.synchronize()
+        return outs
+
+    want = chain(True)
+    for _ in range(3):
+        got = chain(False)
+        assert all(torch.equal(a.view(torch.int16), b.view(torch.int16)) for a, b in zip(got, want))
+        assert all(torch.isfinite(a).all() for a in got)
+    # without the promise a weight written by the previous kernel is still read correctly
+    w_late = torch.empty_like(w1)
+    for _ in range(3):
+        w_late.copy_(w1)  # a device-side copy kernel right in front of the linear
+        q, s = ops.dynamic_quantize(x0)
+        a = ops.qgemm(q, w_late, x_scale=s, w_scale=sw1, out_dtype=torch.float16)
+        w_late.zero_()
+        b = ops.qgemm(q, w1, x_scale=s, w_scale=sw1, out_dtype=torch.float16)
+        assert torch.equal(a, b)
