@@ -33,6 +33,7 @@ SOURCES = [
 HEADERS = [
     "kernels/qgemm.h", "kernels/rowops.h", "kernels/sm100_ptx.cuh",
     "kernels/qgemm_pair.inl", "kernels/qgemm_gemv.inl", "kernels/qgemm_skinny.inl",
+    "kernels/rownorm_staged.inl",
     "ral/abi.h", "ral/context.h", "ral/pdl_attr.h", "ral/nccl_dyn.h",
     "../../include/disc_b200_ral.h",
 ]

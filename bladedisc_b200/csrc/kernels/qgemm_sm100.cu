@@ -27,6 +27,7 @@
 #include <type_traits>
 
 #include "qgemm.h"
+#include "rowops.h"
 #include "sm100_ptx.cuh"
 
 namespace disc_b200 {
@@ -1340,7 +1341,8 @@ int kernel_status_fetch_and_clear() {
     int z = 0;
     cudaMemcpyToSymbol(g_kernel_status, &z, sizeof(int));
   }
-  return h;
+  const int r = rowops_status_fetch_and_clear();
+  return h != 0 ? h : r;
 }
 
 }  // namespace disc_b200

@@ -24,6 +24,7 @@
 #include <float.h>
 
 #include "rowops.h"
+#include "sm100_ptx.cuh"
 
 namespace disc_b200 {
 namespace {
@@ -774,6 +775,8 @@ softmax_kernel(SoftmaxParams p, int aligned) {
 
 bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+#include "rownorm_staged.inl"
+
 // (G, NV, R) for a row of `nvec` 16-byte vectors: sub-warp groups for short
 // rows, one warp up to 8 vectors per lane, one block above; R chosen so that a
 // thread has 4 to 8 loads in flight.
@@ -868,6 +871,16 @@ int64_t vectors_per_row(int64_t cols) {
 }
 
 }  // namespace
+
+int rowops_status_fetch_and_clear() {
+  int h = 0;
+  if (cudaMemcpyFromSymbol(&h, g_rowops_status, sizeof(int)) != cudaSuccess) return -1;
+  if (h != 0) {
+    int z = 0;
+    cudaMemcpyToSymbol(g_rowops_status, &z, sizeof(int));
+  }
+  return h;
+}
 
 cudaError_t quantize_launch(const QuantizeParams& p, cudaStream_t s, const char** err) {
   if (err) *err = nullptr;
@@ -990,6 +1003,22 @@ cudaError_t norm_launch(const NormParams& p, cudaStream_t s, const char** err) {
                       (!p.residual || is_aligned16(p.residual)) && (!p.beta || is_aligned16(p.beta)) &&
                       (!p.y || is_aligned16(p.y)) && (!p.sum_out || is_aligned16(p.sum_out)) &&
                       (!p.q_out || (reinterpret_cast<uintptr_t>(p.q_out) & (epv - 1)) == 0);
+  // long fp16 rows: a warp per row over a copy of the row in shared memory
+  if (p.type == kF16 && aligned && p.cols >= 2048 && p.cols <= 8192) {
+    const size_t row_bytes = static_cast<size_t>(p.cols) * 2;
+    const size_t smem = 2 * row_bytes + kStagedWarps * (p.residual ? 2 : 1) * row_bytes + kStagedWarps * 8 + 16;
+    auto kern = p.rms ? norm_staged_f16_kernel<true> : norm_staged_f16_kernel<false>;
+    cudaError_t st = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (st != cudaSuccess) return st;
+    int64_t per_sm = static_cast<int64_t>((227 * 1024) / (smem + 1024));
+    if (per_sm > 12) per_sm = 12;
+    if (per_sm < 1) per_sm = 1;
+    int64_t grid = (p.rows + kStagedWarps - 1) / kStagedWarps;
+    const int64_t cap = per_sm * sm_count();
+    if (grid > cap) grid = cap;
+    kern<<<static_cast<unsigned>(grid), kStagedWarps * 32, smem, s>>>(p);
+    return cudaGetLastError();
+  }
   if (p.type == kF32) {
     if (aligned) DISC_ROW_DISPATCH(NORM_ALIGNED, float, vectors_per_row<float>(p.cols), p.rows, s, p);
     else DISC_ROW_DISPATCH(NORM_RAGGED, float, vectors_per_row<float>(p.cols), p.rows, s, p);

@@ -117,4 +117,8 @@ struct SoftmaxParams {
 };
 cudaError_t softmax_launch(const SoftmaxParams& p, cudaStream_t s, const char** err);
 
+// Status word of the row kernels' bounded waits (0 = none ran out); cleared by
+// the read.  The caller has synchronised the device.
+int rowops_status_fetch_and_clear();
+
 }  // namespace disc_b200
