@@ -42,6 +42,9 @@ def _args():
     ap.add_argument("--rows", type=int, default=M_ROWS, help="activation rows per rank and step")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the llama7b workload")
+    ap.add_argument("--tp-row-blocks", type=int, default=None,
+                    help="llama7b workload: row blocks per column-parallel linear (gather of one block overlaps "
+                         "the next block's GEMM); default: the library's")
     ap.add_argument("--profile", action="store_true",
                     help="for ncu captures: only warm-up and timed steps (no clock hold, e2e or CPU legs)")
     ap.add_argument("--workload", default="qlinear", choices=["qlinear", "bert_base", "bert_large", "llama7b"],
@@ -538,6 +541,8 @@ def run_decoder(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         comm = tp.Communicator.from_torch_distributed(dev)
+    if args.tp_row_blocks is not None:
+        tp.MAX_ROW_BLOCKS = args.tp_row_blocks
     cfg = DecoderConfig.llama7b(layers=args.layers)
     dec = QuantDecoder(cfg, comm, seed=1238, device=dev)
     batch, seq = 8, 2048
@@ -636,7 +641,8 @@ def run_decoder(args):
             "config": {"workload": f"llama-7b-shaped W8A8 decoder, {cfg.layers} layers, hidden {cfg.hidden}, ffn {cfg.ffn}, "
                                    f"prefill {batch} x {seq} tokens, per-token dynamic int8 activations",
                        "parallelism": f"column-parallel N-split over {world} rank(s), NCCL all-gather after every "
-                                      "gathered linear (4 per layer), all-reduce(max) of row scales (2 per layer)",
+                                      "gathered linear (4 per layer), all-reduce(max) of row scales (2 per layer); "
+                                      f"up to {tp.MAX_ROW_BLOCKS} row block(s) per linear, gathers on a side stream",
                        "l2": "activations of a step (hundreds of MB) are rewritten every step",
                        "note": "attention (SDPA) and RoPE run in torch, a library call as the reference's ral_gemm; "
                                "every linear, norm and quantize is this library's kernel",

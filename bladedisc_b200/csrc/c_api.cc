@@ -312,6 +312,24 @@ int32_t disc_b200_all_gather(void* comm, const void* send, void* recv, int64_t b
   return st == 0 ? 0 : nccl_fail("ncclAllGather", st);
 }
 
+int32_t disc_b200_all_gather_rows(void* comm, void* buf, int32_t nranks, int64_t slot_bytes,
+                                  int64_t offset_bytes, int64_t bytes, void* stream) {
+  const auto& api = disc_b200::ral::nccl_api();
+  if (!api.ok || !comm) return nccl_fail("ncclBroadcast (no communicator)", 0);
+  if (bytes <= 0 || nranks <= 1) return 0;
+  if (!buf || offset_bytes < 0 || offset_bytes + bytes > slot_bytes) return nccl_fail("all_gather_rows (range)", 0);
+  // one broadcast per slot, root = the slot's rank, grouped so that they run as one operation
+  int st = api.GroupStart();
+  for (int r = 0; r < nranks && st == 0; ++r) {
+    char* p = static_cast<char*>(buf) + static_cast<int64_t>(r) * slot_bytes + offset_bytes;
+    st = api.Broadcast(p, p, static_cast<size_t>(bytes), disc_b200::ral::kNcclInt8, r, comm,
+                       static_cast<cudaStream_t>(stream));
+  }
+  const int end = api.GroupEnd();
+  if (st == 0) st = end;
+  return st == 0 ? 0 : nccl_fail("ncclBroadcast (grouped gather of a row range)", st);
+}
+
 int32_t disc_b200_all_reduce_f32(void* comm, const float* send, float* recv, int64_t count,
                                  int32_t op, void* stream) {
   const auto& api = disc_b200::ral::nccl_api();

@@ -38,6 +38,9 @@ NcclApi load() {
       !bind(lib, "ncclCommUserRank", &api.CommUserRank, &api.error) ||
       !bind(lib, "ncclAllGather", &api.AllGather, &api.error) ||
       !bind(lib, "ncclAllReduce", &api.AllReduce, &api.error) ||
+      !bind(lib, "ncclBroadcast", &api.Broadcast, &api.error) ||
+      !bind(lib, "ncclGroupStart", &api.GroupStart, &api.error) ||
+      !bind(lib, "ncclGroupEnd", &api.GroupEnd, &api.error) ||
       !bind(lib, "ncclGetErrorString", &api.GetErrorString, &api.error) ||
       !bind(lib, "ncclGetVersion", &get_version, &api.error)) {
     return api;

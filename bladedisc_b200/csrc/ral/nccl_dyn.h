@@ -39,6 +39,10 @@ struct NcclApi {
                    cudaStream_t stream) = nullptr;
   int (*AllReduce)(const void* send, void* recv, size_t count, int dtype, int op, void* comm,
                    cudaStream_t stream) = nullptr;
+  int (*Broadcast)(const void* send, void* recv, size_t count, int dtype, int root, void* comm,
+                   cudaStream_t stream) = nullptr;
+  int (*GroupStart)() = nullptr;
+  int (*GroupEnd)() = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
 
   std::string describe(int result) const;

@@ -108,6 +108,7 @@ SIGNATURES = {
     "disc_b200_nccl_comm_create": (c_int32, [c_void_p, c_int32, c_int32, POINTER(c_void_p)]),
     "disc_b200_nccl_comm_destroy": (c_int32, [c_void_p]),
     "disc_b200_all_gather": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "disc_b200_all_gather_rows": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int64, c_void_p]),
     "disc_b200_all_reduce_f32": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
     "disc_b200_last_error_string": (c_char_p, []),
     "disc_b200_kernel_status": (c_int32, []),

@@ -91,7 +91,14 @@ def qgemm(a: torch.Tensor, w: torch.Tensor, *, x_scale: Optional[torch.Tensor] =
     kernel on the stream was launched (inference weights): the few-row paths
     then fetch it while that kernel still runs.
     """
-    a = _cuda(a, "a", torch.int8)
+    if a_gathered:
+        # a block of rows of a gathered buffer ([:, m0:m1, :]) is accepted as it is
+        if not a.is_cuda or a.dtype != torch.int8:
+            raise TypeError("a must be a CUDA int8 tensor")
+        if a.dim() == 3 and (a.stride(2) != 1 or a.stride(1) != a.shape[2]):
+            a = a.contiguous()
+    else:
+        a = _cuda(a, "a", torch.int8)
     w = _cuda(w, "w", torch.int8)
     if a_gathered:
         if a.dim() != 3 or w.dim() != 2 or a.shape[0] * a.shape[2] != w.shape[1]:
@@ -113,7 +120,7 @@ def qgemm(a: torch.Tensor, w: torch.Tensor, *, x_scale: Optional[torch.Tensor] =
     args.M, args.N, args.K = M, N, K
     args.lda, args.ldw, args.ldo = K, K, N
     if a_gathered:
-        args.a_slabs, args.a_slab_cols, args.a_slab_stride = a.shape[0], a.shape[2], a.shape[1] * a.shape[2]
+        args.a_slabs, args.a_slab_cols, args.a_slab_stride = a.shape[0], a.shape[2], a.stride(0)
         args.lda = a.shape[2]
     args.weights_static = 1 if weights_static else 0
     keep = []

@@ -286,6 +286,13 @@ int32_t disc_b200_nccl_comm_destroy(void* comm);
  * send == recv + rank * bytes_per_rank. */
 int32_t disc_b200_all_gather(void* comm, const void* send, void* recv, int64_t bytes_per_rank,
                              void* stream);
+/* The same for a byte range of every slot of a [nranks][slot_bytes] buffer:
+ * bytes [offset_bytes, offset_bytes + bytes) of slot r come from rank r.  Lets a
+ * host gather a block of rows while the kernel computing the next block of
+ * rows still runs (the slots of a column-parallel result are row-major, so a
+ * block of rows is one contiguous range per slot). */
+int32_t disc_b200_all_gather_rows(void* comm, void* buf, int32_t nranks, int64_t slot_bytes,
+                                  int64_t offset_bytes, int64_t bytes, void* stream);
 /* op: 0 sum, 1 prod, 2 max, 3 min (per-token activation scales of a row that
  * is spread over the ranks are agreed on with max). */
 int32_t disc_b200_all_reduce_f32(void* comm, const float* send, float* recv, int64_t count,

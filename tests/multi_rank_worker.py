@@ -8,6 +8,32 @@ import torch
 import torch.distributed as dist
 
 
+def _linear_case(ops, tp, comm, rank, world, gen, M):
+    K, N, N2 = 1024, 256 * world, 128 * world
+    a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device="cuda", generator=gen)
+    w = torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda", generator=gen)
+    w2 = torch.randint(-127, 128, (N2, N), dtype=torch.int8, device="cuda", generator=gen)
+    sw = torch.rand(N, device="cuda", generator=gen) * 9e-3 + 1e-3
+    sw2 = torch.rand(N2, device="cuda", generator=gen) * 9e-3 + 1e-3
+    sx = torch.rand(M, device="cuda", generator=gen) * 0.03 + 0.01
+    # unsplit on this GPU
+    y_full = ops.qgemm(a, w, x_scale=sx, w_scale=sw, out_dtype=torch.float16)
+    s_full = ops.row_scale_local(y_full)
+    q_full = ops.quantize_rows(y_full, s_full)
+    z_full = ops.qgemm(q_full, w2, x_scale=s_full, w_scale=sw2, out_dtype=torch.float16)
+    # split: shard -> gather fp16; local scales -> max over ranks -> int8 gather -> next shard reads slabs
+    lin1 = tp.ColumnParallelQLinear(w, sw, None, comm)
+    lin2 = tp.ColumnParallelQLinear(w2, sw2, None, comm)
+    y_g = lin1.forward(a, sx)
+    q_g, s_g = tp.quantize_rows_gathered(comm, y_g[rank])
+    z_g = lin2.forward(q_g, s_g, a_gathered=True)
+    torch.cuda.synchronize()
+    acc = bool(torch.equal(tp.gathered_to_rowmajor(y_g), y_full))
+    scale = bool(torch.equal(s_g, s_full)) and bool(torch.equal(tp.gathered_to_rowmajor(q_g), q_full))
+    chain = bool(torch.equal(tp.gathered_to_rowmajor(z_g), z_full))
+    return acc, scale, chain
+
+
 def main():
     what, out_path = sys.argv[1], sys.argv[2]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -19,29 +45,13 @@ def main():
     gen = torch.Generator(device="cuda").manual_seed(11)
     result = {}
     if what == "linear":
-        M, K, N, N2 = 96, 1024, 256 * world, 128 * world
-        a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device="cuda", generator=gen)
-        w = torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda", generator=gen)
-        w2 = torch.randint(-127, 128, (N2, N), dtype=torch.int8, device="cuda", generator=gen)
-        sw = torch.rand(N, device="cuda", generator=gen) * 9e-3 + 1e-3
-        sw2 = torch.rand(N2, device="cuda", generator=gen) * 9e-3 + 1e-3
-        sx = torch.rand(M, device="cuda", generator=gen) * 0.03 + 0.01
-        # unsplit on this GPU
-        y_full = ops.qgemm(a, w, x_scale=sx, w_scale=sw, out_dtype=torch.float16)
-        s_full = ops.row_scale_local(y_full)
-        q_full = ops.quantize_rows(y_full, s_full)
-        z_full = ops.qgemm(q_full, w2, x_scale=s_full, w_scale=sw2, out_dtype=torch.float16)
-        # split: shard -> gather fp16; local scales -> max over ranks -> int8 gather -> next shard reads slabs
-        lin1 = tp.ColumnParallelQLinear(w, sw, None, comm)
-        lin2 = tp.ColumnParallelQLinear(w2, sw2, None, comm)
-        y_g = lin1.forward(a, sx)
-        y_local = y_g[rank]
-        q_g, s_g = tp.quantize_rows_gathered(comm, y_local)
-        z_g = lin2.forward(q_g, s_g, a_gathered=True)
-        torch.cuda.synchronize()
-        result["acc_equal"] = bool(torch.equal(tp.gathered_to_rowmajor(y_g), y_full))
-        result["scale_equal"] = bool(torch.equal(s_g, s_full)) and bool(torch.equal(tp.gathered_to_rowmajor(q_g), q_full))
-        result["chain_equal"] = bool(torch.equal(tp.gathered_to_rowmajor(z_g), z_full))
+        result = {"acc_equal": True, "scale_equal": True, "chain_equal": True}
+        for M, blocks in ((96, 1), (4608, 1), (4608, 2)):  # last: computed and gathered block of rows by block of rows
+            tp.MAX_ROW_BLOCKS = blocks
+            acc, scale, chain = _linear_case(ops, tp, comm, rank, world, gen, M)
+            result["acc_equal"] &= acc
+            result["scale_equal"] &= scale
+            result["chain_equal"] &= chain
     else:
         cfg = DecoderConfig.tiny()
         cfg.heads = 8

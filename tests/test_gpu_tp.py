@@ -192,3 +192,25 @@ def test_decoder_decode_steps_extend_prefill(ops):
     step = dec.forward(ids[:, 16:17]).view(2, 1, -1)
     err = (full[:, 16:17].float() - step.float()).abs()
     assert (err <= 2e-3 + 2e-2 * full[:, 16:17].float().abs()).float().mean() > 0.97
+
+
+def test_row_blocks_and_strided_gathered_operand(ops):
+    """Long inputs of a column-parallel linear are computed and gathered block of
+    rows by block of rows; a block of rows of a gathered activation is a strided
+    view that the linear reads in place."""
+    from bladedisc_b200 import tp
+    from oracle import c
+    assert tp._row_blocks(16384, 4, max_blocks=4) == [(0, 4096), (4096, 8192), (8192, 12288), (12288, 16384)]
+    assert tp._row_blocks(16384, 1, max_blocks=4) == [(0, 16384)] and tp._row_blocks(100, 8, max_blocks=4) == [(0, 100)]
+    assert tp._row_blocks(16384, 4) == [(0, 16384)]  # off unless asked for
+    blocks = tp._row_blocks(5000, 2, max_blocks=4)
+    assert blocks[0][0] == 0 and blocks[-1][1] == 5000 and all(b[0] % 128 == 0 for b in blocks)
+    rng = np.random.default_rng(9)
+    g, M, slab, N = 2, 300, 256, 72
+    a = rng.integers(-127, 128, (M, g * slab), dtype=np.int8)
+    w = rng.integers(-127, 128, (N, g * slab), dtype=np.int8)
+    gathered = torch.from_numpy(np.ascontiguousarray(a.reshape(M, g, slab).transpose(1, 0, 2))).cuda()
+    want = c.qgemm_acc(a, w)
+    for m0, m1 in ((0, 128), (128, 300), (37, 41)):
+        got = ops.qgemm(gathered[:, m0:m1, :], torch.from_numpy(w).cuda(), out_dtype=torch.int32, a_gathered=True)
+        assert (got.cpu().numpy() == want[m0:m1]).all()
