@@ -259,6 +259,26 @@ int32_t disc_b200_gated_quantize(const disc_b200_gated_quantize_args* a, void* s
   return finish(st, "gated_quantize", detail);
 }
 
+int32_t disc_b200_rope_kv_append(void* qkv, void* k_cache, void* v_cache, const float* cos_table,
+                                 const float* sin_table, int64_t batch, int64_t seq, int64_t heads, int64_t dim,
+                                 int64_t pos0, int64_t cache_len, void* stream) {
+  disc_b200::RopeParams p;
+  p.qkv = qkv;
+  p.k_cache = k_cache;
+  p.v_cache = v_cache;
+  p.cos = cos_table;
+  p.sin = sin_table;
+  p.batch = batch;
+  p.seq = seq;
+  p.heads = heads;
+  p.dim = dim;
+  p.pos0 = pos0;
+  p.cache_len = cache_len;
+  const char* detail = nullptr;
+  const cudaError_t st = disc_b200::rope_kv_append_launch(p, static_cast<cudaStream_t>(stream), &detail);
+  return finish(st, "rope_kv_append", detail);
+}
+
 // ---- collectives of the column-parallel configuration
 static int32_t nccl_fail(const char* what, int result) {
   const auto& api = disc_b200::ral::nccl_api();

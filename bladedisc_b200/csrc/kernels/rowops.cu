@@ -775,6 +775,54 @@ softmax_kernel(SoftmaxParams p, int aligned) {
 
 bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// ------------------------------------------------------------ rope + kv append
+// One thread rotates eight pairs (i, i + dim/2) of one (token, head) of q and of
+// k, and moves the matching sixteen values of v.
+__global__ void __launch_bounds__(kBlock) rope_kv_kernel(RopeParams p) {
+  const int half = static_cast<int>(p.dim / 2);
+  const int chunks = half / 8;  // threads per (token, head)
+  const int64_t total = p.batch * p.seq * p.heads * chunks;
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(kBlock) + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * kBlock) {
+    const int c = static_cast<int>(idx % chunks);
+    const int64_t th = idx / chunks;
+    const int h = static_cast<int>(th % p.heads);
+    const int64_t tok = th / p.heads;
+    const int64_t b = tok / p.seq, s = tok % p.seq;
+    const int64_t pos = p.pos0 + s;
+    __half* q = reinterpret_cast<__half*>(p.qkv) + ((tok * 3 + 0) * p.heads + h) * p.dim + c * 8;
+    __half* k = reinterpret_cast<__half*>(p.qkv) + ((tok * 3 + 1) * p.heads + h) * p.dim + c * 8;
+    const __half* v = reinterpret_cast<const __half*>(p.qkv) + ((tok * 3 + 2) * p.heads + h) * p.dim + c * 8;
+    const int64_t coff = ((b * p.heads + h) * p.cache_len + pos) * p.dim + c * 8;
+    __half* kc = reinterpret_cast<__half*>(p.k_cache) + coff;
+    __half* vc = reinterpret_cast<__half*>(p.v_cache) + coff;
+    float cs[8], sn[8];
+    {
+      const float4* cp = reinterpret_cast<const float4*>(p.cos + pos * half + c * 8);
+      const float4* sp = reinterpret_cast<const float4*>(p.sin + pos * half + c * 8);
+      const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+      cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+      sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    }
+    auto rotate = [&](const __half* src, __half* dst_lo, __half* dst_hi) {
+      float x1[8], x2[8], o1[8], o2[8];
+      VecT<__half>::unpack(*reinterpret_cast<const uint4*>(src), x1);
+      VecT<__half>::unpack(*reinterpret_cast<const uint4*>(src + half), x2);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o1[j] = __fsub_rn(__fmul_rn(x1[j], cs[j]), __fmul_rn(x2[j], sn[j]));
+        o2[j] = __fadd_rn(__fmul_rn(x2[j], cs[j]), __fmul_rn(x1[j], sn[j]));
+      }
+      *reinterpret_cast<uint4*>(dst_lo) = VecT<__half>::pack(o1);
+      *reinterpret_cast<uint4*>(dst_hi) = VecT<__half>::pack(o2);
+    };
+    rotate(q, q, q + half);
+    rotate(k, kc, kc + half);
+    *reinterpret_cast<uint4*>(vc) = *reinterpret_cast<const uint4*>(v);
+    *reinterpret_cast<uint4*>(vc + half) = *reinterpret_cast<const uint4*>(v + half);
+  }
+}
+
 #include "rownorm_staged.inl"
 
 // (G, NV, R) for a row of `nvec` 16-byte vectors: sub-warp groups for short
@@ -871,6 +919,27 @@ int64_t vectors_per_row(int64_t cols) {
 }
 
 }  // namespace
+
+cudaError_t rope_kv_append_launch(const RopeParams& p, cudaStream_t s, const char** err) {
+  if (err) *err = nullptr;
+  if (p.batch <= 0 || p.seq <= 0 || p.heads <= 0) return cudaSuccess;
+  if (!p.qkv || !p.k_cache || !p.v_cache || !p.cos || !p.sin) {
+    if (err) *err = "rope: null operand";
+    return cudaErrorInvalidValue;
+  }
+  if (p.dim <= 0 || p.dim % 16 != 0 || p.pos0 < 0 || p.pos0 + p.seq > p.cache_len) {
+    if (err) *err = "rope: head dim must be a multiple of 16 and the positions must fit the cache";
+    return cudaErrorInvalidValue;
+  }
+  if (!is_aligned16(p.qkv) || !is_aligned16(p.k_cache) || !is_aligned16(p.v_cache) || !is_aligned16(p.cos) ||
+      !is_aligned16(p.sin)) {
+    if (err) *err = "rope: operands must be 16-byte aligned";
+    return cudaErrorInvalidValue;
+  }
+  const int64_t total = p.batch * p.seq * p.heads * (p.dim / 16);
+  rope_kv_kernel<<<elem_grid(total), kBlock, 0, s>>>(p);
+  return cudaGetLastError();
+}
 
 int rowops_status_fetch_and_clear() {
   int h = 0;

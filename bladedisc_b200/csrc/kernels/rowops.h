@@ -117,6 +117,26 @@ struct SoftmaxParams {
 };
 cudaError_t softmax_launch(const SoftmaxParams& p, cudaStream_t s, const char** err);
 
+// Rotary position embedding of q and k inside the fused QKV output, and the
+// append of k and v to the cache, in one pass (decoder glue around the
+// quantized linears; elementwise, one read and one write per element).
+//   qkv      fp16 [batch * seq, 3, heads, dim]: q is rotated in place
+//   k_cache, v_cache fp16 [batch, heads, cache_len, dim]: positions pos0 .. pos0 + seq - 1 are written
+//   cos, sin fp32 [>= pos0 + seq, dim / 2]
+// Pairs (i, i + dim / 2) are rotated: out1 = x1 * cos - x2 * sin, out2 = x2 * cos + x1 * sin,
+// every product and sum rounded to fp32 separately (as an unfused elementwise graph computes them).
+// dim must be a multiple of 16.
+struct RopeParams {
+  void* qkv;
+  void* k_cache;
+  void* v_cache;
+  const float* cos;
+  const float* sin;
+  int64_t batch, seq, heads, dim;
+  int64_t pos0, cache_len;
+};
+cudaError_t rope_kv_append_launch(const RopeParams& p, cudaStream_t s, const char** err);
+
 // Status word of the row kernels' bounded waits (0 = none ran out); cleared by
 // the read.  The caller has synchronised the device.
 int rowops_status_fetch_and_clear();

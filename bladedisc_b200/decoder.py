@@ -144,11 +144,10 @@ class QuantDecoder:
     def _attention(self, L: _Layer, idx: int, qkv: torch.Tensor, batch: int, seq: int) -> torch.Tensor:
         cfg = self.cfg
         hl, d = cfg.heads // self.world, cfg.head_dim
-        q, k, v = qkv.view(batch, seq, 3, hl, d).unbind(dim=2)
-        q, k = self._rope(q, self.pos), self._rope(k, self.pos)
         kc, vc = self.kv[idx]
-        kc[:, :, self.pos:self.pos + seq] = k.transpose(1, 2)
-        vc[:, :, self.pos:self.pos + seq] = v.transpose(1, 2)
+        # q and k rotated, k and v appended to the cache: one pass over the QKV output
+        ops.rope_kv_append(qkv, kc, vc, self._cos, self._sin, batch, seq, self.pos)
+        q = qkv.view(batch, seq, 3, hl, d)[:, :, 0]
         end = self.pos + seq
         # Library attention, without the backend that builds a new plan for every
         # cache length (tens of milliseconds on the host per decode step).

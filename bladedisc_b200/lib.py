@@ -101,6 +101,8 @@ SIGNATURES = {
                                              c_void_p]),
     "disc_b200_norm": (c_int32, [POINTER(NormArgs), c_void_p]),
     "disc_b200_gated_quantize": (c_int32, [POINTER(GatedQuantArgs), c_void_p]),
+    "disc_b200_rope_kv_append": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                           c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "disc_b200_softmax": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int64, c_void_p,
                                     c_void_p, c_float, c_int32, c_void_p]),
     "disc_b200_nccl_available": (c_int32, []),

@@ -373,6 +373,24 @@ def softmax(x: torch.Tensor, scale: float = 1.0, lens: Optional[torch.Tensor] = 
     return y
 
 
+def rope_kv_append(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cos: torch.Tensor,
+                   sin: torch.Tensor, batch: int, seq: int, pos0: int) -> None:
+    """Rotates q and k inside ``qkv`` (fp16 ``[batch * seq, 3 * heads * dim]``, q in place) and
+    appends the rotated k and v to the caches ``[batch, heads, cache_len, dim]`` at ``pos0``."""
+    for t, n in ((qkv, "qkv"), (k_cache, "k_cache"), (v_cache, "v_cache")):
+        if not t.is_cuda or t.dtype != torch.float16 or not t.is_contiguous():
+            raise ValueError(f"{n} must be a contiguous CUDA fp16 tensor")
+    heads, cache_len, dim = k_cache.shape[1], k_cache.shape[2], k_cache.shape[3]
+    if qkv.numel() != batch * seq * 3 * heads * dim or k_cache.shape[0] != batch or v_cache.shape != k_cache.shape:
+        raise ValueError("qkv / cache shapes disagree")
+    cos, sin = _cuda(cos, "cos", torch.float32), _cuda(sin, "sin", torch.float32)
+    if cos.shape[0] < pos0 + seq or cos.shape[1] != dim // 2 or sin.shape != cos.shape:
+        raise ValueError("cos / sin tables must be [>= pos0 + seq, dim / 2]")
+    _lib.check(_lib.load().disc_b200_rope_kv_append(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                                    cos.data_ptr(), sin.data_ptr(), batch, seq, heads, dim, pos0,
+                                                    cache_len, _stream()))
+
+
 def kernel_status() -> int:
     """0 unless a kernel's bounded wait ran out since the last query (synchronises)."""
     return _lib.load().disc_b200_kernel_status()

@@ -259,6 +259,16 @@ typedef struct disc_b200_gated_quantize_args {
 } disc_b200_gated_quantize_args;
 int32_t disc_b200_gated_quantize(const disc_b200_gated_quantize_args* args, void* stream);
 
+/* Rotary position embedding of q and k inside a fused QKV output
+ * fp16 [batch * seq, 3, heads, dim] (q in place) and the append of the rotated
+ * k and of v to the caches fp16 [batch, heads, cache_len, dim] at positions
+ * pos0 .. pos0 + seq - 1; cos / sin are fp32 [>= pos0 + seq, dim / 2]; pairs
+ * (i, i + dim / 2).  Decoder glue around the quantized linears of the 7B-shaped
+ * configuration; the reference compiles this as generated elementwise kernels. */
+int32_t disc_b200_rope_kv_append(void* qkv, void* k_cache, void* v_cache, const float* cos_table,
+                                 const float* sin_table, int64_t batch, int64_t seq, int64_t heads, int64_t dim,
+                                 int64_t pos0, int64_t cache_len, void* stream);
+
 /* softmax(x * scale + mask) over the last axis; lens / mask may be NULL
  * (kStitch softmax; same reference files as above). */
 int32_t disc_b200_softmax(const void* x, void* y, int32_t type, int64_t rows, int64_t cols,

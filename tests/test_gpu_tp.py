@@ -214,3 +214,31 @@ def test_row_blocks_and_strided_gathered_operand(ops):
     for m0, m1 in ((0, 128), (128, 300), (37, 41)):
         got = ops.qgemm(gathered[:, m0:m1, :], torch.from_numpy(w).cuda(), out_dtype=torch.int32, a_gathered=True)
         assert (got.cpu().numpy() == want[m0:m1]).all()
+
+
+@pytest.mark.parametrize("batch,seq,heads,dim,pos0", [(2, 5, 3, 64, 0), (1, 1, 4, 128, 17), (3, 40, 2, 32, 8)])
+def test_rope_and_cache_append_match_the_elementwise_form(ops, batch, seq, heads, dim, pos0):
+    from bladedisc_b200.decoder import DecoderConfig, QuantDecoder
+    dec = QuantDecoder.__new__(QuantDecoder)  # only the table / rotation helpers are used
+    dec.cfg = DecoderConfig(hidden=heads * dim, heads=heads)
+    dec.device = torch.device("cuda")
+    dec._cos = dec._sin = None
+    cache_len = pos0 + seq + 3
+    dec._rope_tables(cache_len)
+    gen = torch.Generator(device="cuda").manual_seed(batch + seq)
+    qkv = torch.randn(batch * seq, 3 * heads * dim, generator=gen, device="cuda").half()
+    q, k, v = qkv.view(batch, seq, 3, heads, dim).unbind(dim=2)
+    want_q, want_k = dec._rope(q, pos0), dec._rope(k, pos0)
+    kc = torch.full((batch, heads, cache_len, dim), 7.0, dtype=torch.float16, device="cuda")
+    vc = torch.full_like(kc, 7.0)
+    work = qkv.clone()
+    ops.rope_kv_append(work, kc, vc, dec._cos, dec._sin, batch, seq, pos0)
+    got = work.view(batch, seq, 3, heads, dim)
+    assert torch.equal(got[:, :, 0], want_q)
+    assert torch.equal(got[:, :, 1], k) and torch.equal(got[:, :, 2], v)          # k, v of the input stay as they were
+    assert torch.equal(kc[:, :, pos0:pos0 + seq], want_k.transpose(1, 2))
+    assert torch.equal(vc[:, :, pos0:pos0 + seq], v.transpose(1, 2))
+    assert (kc[:, :, :pos0] == 7).all() and (kc[:, :, pos0 + seq:] == 7).all() and (vc[:, :, pos0 + seq:] == 7).all()
+    dec._rope_tables(2 * cache_len)
+    with pytest.raises(RuntimeError, match="fit the cache"):  # positions past the end of the cache are refused
+        ops.rope_kv_append(work, kc, vc, dec._cos, dec._sin, batch, seq, cache_len)
