@@ -129,9 +129,26 @@ def bench_rows(name, rows, cols, dtype, hbm, iters):
         algo = eb * E + E + 4 * rows + eb * cols
     elif name == "softmax":
         algo = 2 * eb * E
+    elif name == "swiglu_rowscale":      # pass 0 of the two-pass quantization of silu(gate) * up
+        algo = 2 * eb * E + 4 * rows
+    elif name == "swiglu_quantize":      # pass 1
+        algo = 2 * eb * E + E + 4 * rows
     else:
         raise ValueError(name)
     n_sets = copies_for(algo)
+    if name.startswith("swiglu"):
+        bufs = [torch.randn((rows, 2 * cols), device=dev, generator=g).to(dtype) for _ in range(n_sets)]
+        scales = [ops.row_scale_local(b[:, :cols], b[:, cols:]) for b in bufs]
+        outs = [torch.empty((rows, cols), dtype=torch.int8, device=dev) for _ in bufs]
+        if name == "swiglu_rowscale":
+            fns = [(lambda b=b: ops.row_scale_local(b[:, :cols], b[:, cols:])) for b in bufs]
+        else:
+            fns = [(lambda b=b, s=s, o=o: ops.quantize_rows(b[:, :cols], s, b[:, cols:], out=o))
+                   for b, s, o in zip(bufs, scales, outs)]
+        ms = time_ms(fns, iters)
+        gbs = algo / (ms * 1e-3) / 1e9
+        return {"kernel": name, "rows": rows, "cols": cols, "dtype": str(dtype).split(".")[-1], "us": ms * 1e3,
+                "gbs": gbs, "bound": "hbm", "frac": gbs / hbm, "sets": n_sets}
     xs = [torch.randn((rows, cols), device=dev, generator=g).to(dtype) for _ in range(n_sets)]
     rs = [torch.randn((rows, cols), device=dev, generator=g).to(dtype) for _ in range(n_sets)] \
         if name == "add_layernorm_quant" else None
@@ -193,7 +210,8 @@ def main():
                  ("dynamic_quantize", 16384, 4096, torch.float16), ("layernorm", 16384, 768, torch.float16),
                  ("add_layernorm_quant", 16384, 768, torch.float16), ("add_layernorm_quant", 32768, 1024, torch.float16),
                  ("rmsnorm_dynquant", 16384, 4096, torch.float16), ("softmax", 32 * 12 * 512, 512, torch.float16),
-                 ("softmax", 196608, 128, torch.float16)]
+                 ("softmax", 196608, 128, torch.float16),
+                 ("swiglu_rowscale", 16384, 11008, torch.float16), ("swiglu_quantize", 16384, 11008, torch.float16)]
     if args.quick:
         row_cases = row_cases[:1] + row_cases[3:5] + row_cases[7:8]
     print(f"{'kernel':<22}{'rows':>8}{'cols':>7}{'dtype':>9}{'us':>10}{'GB/s':>9}{'frac':>7}")
