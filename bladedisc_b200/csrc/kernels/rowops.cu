@@ -568,6 +568,7 @@ __device__ __forceinline__ float swiglu_value(float g, float u) {
 }
 
 // PASS 0: local row scale.  PASS 1: quantize with the (agreed) row scale.
+// PASS 2: both in one go, for rows that are whole on this GPU.
 template <typename T, int G, int NV, int R, int PASS>
 __global__ void __launch_bounds__(kBlock, (NV * R <= 4 ? 3 : (NV * R <= 8 ? 2 : 1)))
 gated_quant_kernel(GatedQuantParams p, int aligned) {
@@ -602,8 +603,8 @@ gated_quant_kernel(GatedQuantParams p, int aligned) {
       for (int j = 0; j < E; ++j) h[j] = swiglu_value(h[j], u[j]);
     }
   };
-  if (PASS == 0) {
-    float m[R];
+  float m[R];
+  if (PASS != 1) {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       float a = 0.f;
@@ -619,13 +620,15 @@ gated_quant_kernel(GatedQuantParams p, int aligned) {
     group_reduce<G, R, true>(m, red);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      if (live[r] && t == 0) p.row_scale[ix.row0 + r] = fmaxf(__fdiv_rn(m[r], 127.f), FLT_EPSILON);
+      m[r] = fmaxf(__fdiv_rn(m[r], 127.f), FLT_EPSILON);
+      if (live[r] && t == 0) p.row_scale[ix.row0 + r] = m[r];
     }
-  } else {
+  }
+  if (PASS != 0) {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       if (!live[r]) continue;
-      const Divisor d = make_divisor(__ldg(p.row_scale + ix.row0 + r));
+      const Divisor d = make_divisor(PASS == 1 ? __ldg(p.row_scale + ix.row0 + r) : m[r]);
       const int64_t off = (ix.row0 + r) * p.ldq;
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
@@ -917,6 +920,8 @@ template <typename T, int G, int NV, int R>
 constexpr auto GATED_SCALE = gated_quant_kernel<T, G, NV, R, 0>;
 template <typename T, int G, int NV, int R>
 constexpr auto GATED_QUANT = gated_quant_kernel<T, G, NV, R, 1>;
+template <typename T, int G, int NV, int R>
+constexpr auto GATED_BOTH = gated_quant_kernel<T, G, NV, R, 2>;
 
 bool row_shape_ok(int64_t rows, int64_t cols, const char** err) {
   if (cols > 16384) {
@@ -1051,11 +1056,11 @@ cudaError_t dynamic_quantize_launch(const DynQuantParams& p, cudaStream_t s, con
 cudaError_t gated_quantize_launch(const GatedQuantParams& p, cudaStream_t s, const char** err) {
   if (err) *err = nullptr;
   if (p.rows <= 0 || p.cols <= 0) return cudaSuccess;
-  if (!p.gate || !p.row_scale || (p.pass != 0 && !p.q) || (p.pass != 0 && p.pass != 1)) {
+  if (!p.gate || !p.row_scale || (p.pass != 0 && !p.q) || p.pass < 0 || p.pass > 2) {
     if (err) *err = "gated quantize: null operand or unknown pass";
     return cudaErrorInvalidValue;
   }
-  if (p.ld < p.cols || (p.pass == 1 && p.ldq < p.cols)) {
+  if (p.ld < p.cols || (p.pass != 0 && p.ldq < p.cols)) {
     if (err) *err = "gated quantize: row stride smaller than the row";
     return cudaErrorInvalidValue;
   }
@@ -1064,12 +1069,15 @@ cudaError_t gated_quantize_launch(const GatedQuantParams& p, cudaStream_t s, con
   const int aligned = (p.cols % epv == 0) && (p.ld % epv == 0) && is_aligned16(p.gate) &&
                       (!p.up || is_aligned16(p.up)) &&
                       (p.pass == 0 || ((p.ldq % epv == 0) && (reinterpret_cast<uintptr_t>(p.q) & (epv - 1)) == 0));
+  // pass 2 = pass 0 and pass 1 in one kernel (row scale written and used at once)
   if (p.type == kF32) {
     if (p.pass == 0) DISC_ROW_DISPATCH(GATED_SCALE, float, vectors_per_row<float>(p.cols), p.rows, s, p, aligned);
-    else DISC_ROW_DISPATCH(GATED_QUANT, float, vectors_per_row<float>(p.cols), p.rows, s, p, aligned);
+    else if (p.pass == 1) DISC_ROW_DISPATCH(GATED_QUANT, float, vectors_per_row<float>(p.cols), p.rows, s, p, aligned);
+    else DISC_ROW_DISPATCH(GATED_BOTH, float, vectors_per_row<float>(p.cols), p.rows, s, p, aligned);
   } else {
     if (p.pass == 0) DISC_ROW_DISPATCH(GATED_SCALE, __half, vectors_per_row<__half>(p.cols), p.rows, s, p, aligned);
-    else DISC_ROW_DISPATCH(GATED_QUANT, __half, vectors_per_row<__half>(p.cols), p.rows, s, p, aligned);
+    else if (p.pass == 1) DISC_ROW_DISPATCH(GATED_QUANT, __half, vectors_per_row<__half>(p.cols), p.rows, s, p, aligned);
+    else DISC_ROW_DISPATCH(GATED_BOTH, __half, vectors_per_row<__half>(p.cols), p.rows, s, p, aligned);
   }
   return cudaGetLastError();
 }

@@ -96,7 +96,7 @@ struct GatedQuantParams {
   float* row_scale;
   int64_t rows, cols;
   int type;  // ElemType of gate / up
-  int pass;
+  int pass;  // 0, 1, or 2 = both at once (rows that are whole on this GPU)
 };
 cudaError_t gated_quantize_launch(const GatedQuantParams& p, cudaStream_t s, const char** err);
 

@@ -324,6 +324,18 @@ def _cuda_strided(t: torch.Tensor, name: str) -> torch.Tensor:
     return t
 
 
+def quantize_rows_whole(gate: torch.Tensor, up: Optional[torch.Tensor] = None,
+                        out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Both passes in one kernel for rows that are whole on this GPU: ``(q, row_scale)``."""
+    s = torch.empty(gate.shape[0], dtype=torch.float32, device=gate.device)
+    if out is None:
+        out = torch.empty(gate.shape, dtype=torch.int8, device=gate.device)
+    elif out.dtype != torch.int8 or tuple(out.shape) != tuple(gate.shape) or out.stride(1) != 1:
+        raise ValueError("out must be int8 of gate's shape with unit column stride")
+    _gated(gate, up, out, s, 2)
+    return out, s
+
+
 def row_scale_local(gate: torch.Tensor, up: Optional[torch.Tensor] = None) -> torch.Tensor:
     """First pass of the two-pass per-row quantization of ``h = silu(gate) * up``
     (``h = gate`` without ``up``): ``max(max|h[r, :]| / 127, eps)`` over the

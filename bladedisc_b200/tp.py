@@ -229,6 +229,10 @@ def quantize_rows_gathered(comm: Optional[Communicator], gate: torch.Tensor, up:
     world = comm.world if comm else 1
     rank = comm.rank if comm else 0
     m, c = gate.shape
+    if world == 1:  # the rows are whole here: scale and quantize in one kernel
+        buf = torch.empty((1, m, c), dtype=torch.int8, device=gate.device)
+        _, scale = ops.quantize_rows_whole(gate, up, out=buf[0])
+        return buf, scale
     scale = ops.row_scale_local(gate, up)
     if world > 1:
         comm.all_reduce_max_(scale)

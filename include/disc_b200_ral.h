@@ -243,7 +243,8 @@ int32_t disc_b200_norm(const disc_b200_norm_args* args, void* stream);
  * column-parallel split: pass 0 writes row_scale[r] = max(max|h[r, :]| / 127,
  * FLT_EPSILON) over the local columns; the caller takes the maximum over the
  * ranks (disc_b200_all_reduce_f32, op 2); pass 1 writes
- * q = sat(rne(h / row_scale[r])).  gate / up have row stride ld, q row stride
+ * q = sat(rne(h / row_scale[r])); pass 2 does both at once for rows that are
+ * whole on this GPU.  gate / up have row stride ld, q row stride
  * ldq (elements).  No counterpart in the reference (dynamic quantization is
  * rejected there, disc_lower_quantize_and_dequantize.cc:41-43). */
 typedef struct disc_b200_gated_quantize_args {

@@ -42,6 +42,8 @@ def test_two_pass_row_quantize(ops, rows, cols, ld, gated, dtype):
     diff = np.abs(q.cpu().numpy().astype(np.int32) - want.astype(np.int32))
     assert diff.max() <= (1 if gated else 0) or (diff.max() <= 1 and (diff > 0).mean() < 1e-3)
     assert np.abs(q.cpu().numpy()).max() == 127  # the row maximum lands on the last level
+    q2, s2 = ops.quantize_rows_whole(gate, up)     # both passes in one kernel: the same bytes
+    assert torch.equal(q2, q) and torch.equal(s2, scale)
     assert (out[0] == 77).all() and (out[rows + 1] == 77).all() and (out[:, cols:] == 77).all()
 
 
