@@ -173,6 +173,9 @@ qgemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   cluster_sync_all();  // the peer's barriers exist before anything is sent to them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // set-up done while the kernel before this one may still have been finishing
+  grid_dep_launch();
+  grid_dep_wait();
 
   const int num_tiles = tiles_m * tiles_n;
   const int cluster_id = blockIdx.x >> 1;

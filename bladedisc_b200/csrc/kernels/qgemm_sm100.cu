@@ -384,6 +384,10 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // the set-up above ran while the kernel before this one may still have been
+  // finishing; everything below reads or writes what that kernel may touch
+  grid_dep_launch();
+  grid_dep_wait();
 
   const int num_tiles = tiles_m * tiles_n;
 
@@ -922,24 +926,6 @@ bool make_a_tmap(CUtensorMap* tm, const QGemmParams& p, int box_rows) {
   return make_tmap(tm, p.a, rows, p.a_slab_cols, p.lda, box_rows);
 }
 
-// Launch that may overlap the tail of the kernel before it on the stream
-// (programmatic dependent launch); the kernel orders itself with grid_dep_wait().
-template <typename... KArgs, typename... Args>
-cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                             Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
-}
-
 int small_mt(int64_t M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
 
 int small_split(const QGemmParams& p) {
@@ -975,9 +961,8 @@ cudaError_t launch_tiled_t(const QGemmParams& p, cudaStream_t stream, const char
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
   const int eb = out_elem_bytes(p.out_dtype);
   const int vec_ok = ((p.ldo * eb) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
-  kern<<<grid, kTiledThreads, L::kDynamic, stream>>>(ta, tw, make_epi(p), num_kb, tiles_m, tiles_n, vec_ok,
-                                                   slab_of(p));
-  return cudaGetLastError();
+  return launch_dependent(kern, dim3(grid), dim3(kTiledThreads), L::kDynamic, stream, ta, tw, make_epi(p), num_kb,
+                          tiles_m, tiles_n, vec_ok, slab_of(p));
 }
 
 template <typename OutT>
@@ -1051,10 +1036,8 @@ cudaError_t launch_pair(const QGemmParams& p, cudaStream_t stream, const char** 
   const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n;
   const int max_clusters = pair_max_clusters<OutT>();
   const int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
-  kern<<<2 * clusters, kTiledThreads, PairSmem::kDynamic, stream>>>(ta, tw, to, make_epi(p), num_kb,
-                                                                   tiles_m, tiles_n, use_tma_store,
-                                                                   out_aligned ? 1 : 0, slab_of(p));
-  return cudaGetLastError();
+  return launch_dependent(kern, dim3(2 * clusters), dim3(kTiledThreads), PairSmem::kDynamic, stream, ta, tw, to,
+                          make_epi(p), num_kb, tiles_m, tiles_n, use_tma_store, out_aligned ? 1 : 0, slab_of(p));
 }
 
 template <typename OutT>

@@ -355,6 +355,8 @@ __device__ __forceinline__ void quant_vec(const float* y, const Divisor& d, floa
 template <typename T, int G, int NV, int R, bool ALIGNED>
 __global__ void __launch_bounds__(kBlock, (NV * R <= 4 ? 3 : (NV * R <= 8 ? 2 : 1)))
 norm_kernel(NormParams p) {
+  grid_dep_launch();  // the next kernel may begin its own set-up
+  grid_dep_wait();    // the kernel before this one has finished and its writes are visible
   constexpr int E = VecT<T>::kElems;
   __shared__ float red[R * 8];
   const RowIndex<G, R> ix;
@@ -501,6 +503,8 @@ norm_kernel(NormParams p) {
 template <typename T, int G, int NV, int R>
 __global__ void __launch_bounds__(kBlock, (NV * R <= 4 ? 3 : (NV * R <= 8 ? 2 : 1)))
 dynquant_kernel(DynQuantParams p, int aligned) {
+  grid_dep_launch();  // the next kernel may begin its own set-up
+  grid_dep_wait();    // the kernel before this one has finished and its writes are visible
   constexpr int E = VecT<T>::kElems;
   __shared__ float red[R * 8];
   const RowIndex<G, R> ix;
@@ -572,6 +576,8 @@ __device__ __forceinline__ float swiglu_value(float g, float u) {
 template <typename T, int G, int NV, int R, int PASS>
 __global__ void __launch_bounds__(kBlock, (NV * R <= 4 ? 3 : (NV * R <= 8 ? 2 : 1)))
 gated_quant_kernel(GatedQuantParams p, int aligned) {
+  grid_dep_launch();  // the next kernel may begin its own set-up
+  grid_dep_wait();    // the kernel before this one has finished and its writes are visible
   constexpr int E = VecT<T>::kElems;
   __shared__ float red[R * 8];
   const RowIndex<G, R> ix;
@@ -657,6 +663,8 @@ __device__ __forceinline__ float ex2_approx(float x) {
 template <typename T, int G, int NV, int R>
 __global__ void __launch_bounds__(kBlock, (NV * R <= 4 ? 3 : (NV * R <= 8 ? 2 : 1)))
 softmax_kernel(SoftmaxParams p, int aligned) {
+  grid_dep_launch();  // the next kernel may begin its own set-up
+  grid_dep_wait();    // the kernel before this one has finished and its writes are visible
   // Issue bound unless lean: the logits are unpacked once, the exponentials are
   // kept (one special-function op per element, not one per pass), whole vectors
   // inside the valid length take a path without per-element predicates.
@@ -861,7 +869,7 @@ __global__ void __launch_bounds__(kBlock) rope_kv_kernel(RopeParams p) {
     const int64_t groups_per_block = kBlock / (G);                                                     \
     const int64_t rows_per_block = groups_per_block * (R);                                             \
     const unsigned grid = static_cast<unsigned>(((rows) + rows_per_block - 1) / rows_per_block);       \
-    KERNEL<T, G, NV, R><<<grid, kBlock, 0, stream>>>(__VA_ARGS__);                                     \
+    launch_dependent(KERNEL<T, G, NV, R>, dim3(grid), dim3(kBlock), 0, stream, __VA_ARGS__);           \
   } while (0)
 
 #define DISC_ROW_DISPATCH(KERNEL, T, nvec, rows, stream, ...)                                          \
@@ -894,7 +902,8 @@ __global__ void __launch_bounds__(kBlock) rope_kv_kernel(RopeParams p) {
     }                                                                                                  \
     const int64_t cap = static_cast<int64_t>(sm_count()) * resident;                                   \
     if (grid > cap) grid = cap;                                                                        \
-    KERNEL<T, G, NV, R><<<static_cast<unsigned>(grid), kBlock, 0, stream>>>(__VA_ARGS__);              \
+    launch_dependent(KERNEL<T, G, NV, R>, dim3(static_cast<unsigned>(grid)), dim3(kBlock), 0, stream,  \
+                     __VA_ARGS__);                                                                     \
   } while (0)
 
 #define DISC_ROW_DISPATCH_P(KERNEL, T, nvec, rows, stream, ...)                                        \

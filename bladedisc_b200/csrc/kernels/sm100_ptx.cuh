@@ -309,4 +309,23 @@ __host__ __device__ constexpr uint32_t make_i8_idesc(int mma_m, int mma_n) {
          (static_cast<uint32_t>(mma_m >> 4) << 24);
 }
 
+// Launch that may overlap the tail of the kernel before it on the stream
+// (programmatic dependent launch); the kernel orders itself with grid_dep_wait().
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+
 }  // namespace disc_b200
