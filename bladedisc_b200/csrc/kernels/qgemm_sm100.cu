@@ -1170,7 +1170,7 @@ int qgemm_choose_path(const QGemmParams& p) {
   // Few rows: fine channel blocks over the full K, as long as one wave of CTAs
   // covers the output.
   const int64_t skinny_ctas = ((p.N + skinny_bn(p) - 1) / skinny_bn(p)) * ((p.M + kTileM - 1) / kTileM);
-  if (p.M <= 128 || (p.M <= 512 && skinny_ctas <= sm_count())) return kPathSkinny;
+  if (p.M <= 128 || (p.M <= 1024 && skinny_ctas <= sm_count())) return kPathSkinny;
   // CTA pairs compute 256 x 256 tiles: worth it once there are enough of them
   // to occupy every pair of SMs.
   const int64_t pair_tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);

@@ -239,5 +239,10 @@ def shard_batch(ids: torch.Tensor, lens: torch.Tensor, world: int, rank: int):
         return ids[:0, :1], lens[:0], assign
     idx = torch.tensor(assign, device=ids.device)
     my_lens = lens[idx]
-    L = int(my_lens.max())
-    return ids[idx][:, :L].contiguous(), my_lens.contiguous(), assign
+    # Padded to a multiple of 8 tokens: rows of the attention scores are then whole 16-byte
+    # vectors and the softmax takes its aligned path (the padding is masked by the lengths).
+    L = -(-int(my_lens.max()) // 8) * 8
+    mine = ids[idx][:, :L]
+    if mine.shape[1] < L:
+        mine = torch.nn.functional.pad(mine, (0, L - mine.shape[1]))
+    return mine.contiguous(), my_lens.contiguous(), assign
