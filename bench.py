@@ -3,7 +3,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 One step = one int8 quantized linear over one batch of M activation rows
-(configuration 1 of BASELINE.json at M = 16384, K = 4096, N = 4096, per-channel
+(the dynamic-shape sweep's largest square point: M = 16384, K = 4096, N = 4096, per-channel
 weight scales, fp32 bias, int8 output requantized at 0.05).  With N > 1 ranks
 (torchrun) every rank runs the same step on its own rows: the rows of a linear
 are independent, so there is no collective and the scaling is "weak".

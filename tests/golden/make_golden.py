@@ -1,7 +1,7 @@
 """Generates tests/golden/qpath_golden.npz.
 
-Run in the build container only (it imports the reference's Python front end
-from /root/reference and CPU torch):
+Run where the reference tree is checked out (REF_TQ below; it imports the
+reference's Python front end and CPU torch):
 
     python tests/golden/make_golden.py
 
