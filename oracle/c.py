@@ -226,3 +226,34 @@ def softmax(x, scale=1.0, lens=None, mask=None, log=False):
     lib().oracle_softmax_f32(_ptr(x2), c_int64(rows), c_int64(cols), c_int64(rpb), _ptr(ln), _ptr(mk),
                              c_float(scale), c_int(1 if log else 0), _ptr(y))
     return y.reshape(x.shape)
+
+
+def gated_quantize(gate, up=None):
+    """oracle_gated_quantize_f32: (q int8, row_scale) of silu(gate) * up (of gate without up)."""
+    g = _f32(gate)
+    u = _f32(up)
+    rows, cols = g.shape
+    q = np.empty((rows, cols), dtype=np.int8)
+    s = np.empty(rows, dtype=np.float32)
+    lib().oracle_gated_quantize_f32(_ptr(g), _ptr(u), c_int64(rows), c_int64(cols), c_int64(cols), _ptr(q), _ptr(s))
+    return q, s
+
+
+def rope(x, pos, cos_t, sin_t):
+    """oracle_rope_f32: x [tokens, heads, dim], pos [tokens], tables [positions, dim / 2]."""
+    x = _f32(x)
+    tokens, heads, dim = x.shape
+    p = np.ascontiguousarray(pos, dtype=np.int64)
+    y = np.empty_like(x)
+    lib().oracle_rope_f32(_ptr(x), _ptr(p), _ptr(_f32(cos_t)), _ptr(_f32(sin_t)), c_int64(tokens), c_int64(heads),
+                          c_int64(dim), _ptr(y))
+    return y
+
+
+def gathered_layout(x, ranks):
+    """oracle_gathered_layout: row-major [rows, cols] -> [ranks, rows, cols / ranks]."""
+    x = np.ascontiguousarray(x)
+    rows, cols = x.shape
+    out = np.empty((ranks, rows, cols // ranks), dtype=x.dtype)
+    lib().oracle_gathered_layout(_ptr(x), c_int64(rows), c_int64(cols), c_int64(ranks), c_int64(x.itemsize), _ptr(out))
+    return out

@@ -313,3 +313,74 @@ ORACLE_API void oracle_qgemm_ral_i8(const int8_t* a, const int8_t* w, int64_t M,
     }
   }
 }
+
+/* ---- configuration 4 (column-parallel decoder): the glue around the linears.
+ * None of this exists as named code in the reference (its quantize op rejects
+ * dynamic scales, disc_lower_quantize_and_dequantize.cc:41-43; RoPE and SwiGLU
+ * reach it as generated elementwise kernels), so these restate the defining
+ * formulas; the collective itself is ral_all_gather's rank-major concatenation
+ * (tao_compiler/mlir/ral/collective.cu.cc:226-309). */
+
+/* h = up ? silu(gate) * up : gate, per-row symmetric int8:
+ * row_scale[r] = max(max|h[r,:]| / 127, FLT_EPSILON), q = sat(rne(h / row_scale[r])).
+ * gate / up are [rows, cols] with row stride ld.  silu in double, so that the
+ * restatement adds no error of its own (the GPU kernel uses the approximate
+ * exponential and reciprocal: compare within 1 LSB). */
+ORACLE_API void oracle_gated_quantize_f32(const float* gate, const float* up, int64_t rows, int64_t cols,
+                                          int64_t ld, int8_t* q, float* row_scale) {
+  for (int64_t r = 0; r < rows; ++r) {
+    float m = 0.f;
+    for (int64_t c = 0; c < cols; ++c) {
+      const double g = gate[r * ld + c];
+      const float h = up ? (float)(g / (1.0 + exp(-g)) * (double)up[r * ld + c]) : (float)g;
+      if (fabsf(h) > m) m = fabsf(h);
+    }
+    float s = m / 127.f;
+    if (s < 1.1920928955078125e-07f) s = 1.1920928955078125e-07f;
+    row_scale[r] = s;
+    for (int64_t c = 0; c < cols; ++c) {
+      const double g = gate[r * ld + c];
+      const float h = up ? (float)(g / (1.0 + exp(-g)) * (double)up[r * ld + c]) : (float)g;
+      q[r * cols + c] = (int8_t)(int32_t)clampf(rintf(h / s), -128.f, 127.f);
+    }
+  }
+}
+
+/* Rotary position embedding of x [tokens, heads, dim] at positions pos[token]:
+ * pairs (i, i + dim/2), out1 = x1 cos - x2 sin, out2 = x2 cos + x1 sin with
+ * cos / sin [positions, dim/2]; every product and sum rounded to fp32 on its own
+ * (this file is built with -ffp-contract=off), as an unfused elementwise graph
+ * computes them. */
+ORACLE_API void oracle_rope_f32(const float* x, const int64_t* pos, const float* cos_t, const float* sin_t,
+                                int64_t tokens, int64_t heads, int64_t dim, float* y) {
+  const int64_t half = dim / 2;
+  for (int64_t t = 0; t < tokens; ++t) {
+    const float* cs = cos_t + pos[t] * half;
+    const float* sn = sin_t + pos[t] * half;
+    for (int64_t h = 0; h < heads; ++h) {
+      const float* xr = x + (t * heads + h) * dim;
+      float* yr = y + (t * heads + h) * dim;
+      for (int64_t i = 0; i < half; ++i) {
+        const float a = xr[i] * cs[i];
+        const float b = xr[i + half] * sn[i];
+        const float c = xr[i + half] * cs[i];
+        const float d = xr[i] * sn[i];
+        yr[i] = a - b;
+        yr[i + half] = c + d;
+      }
+    }
+  }
+}
+
+/* What an all-gather of column-parallel results leaves on every rank: slot r of
+ * out [ranks, rows, cols / ranks] holds columns [r * cols / ranks, ...) of the
+ * row-major matrix x [rows, cols] (byte-wise; elem = element size). */
+ORACLE_API void oracle_gathered_layout(const void* x, int64_t rows, int64_t cols, int64_t ranks, int64_t elem,
+                                       void* out) {
+  const int64_t share = cols / ranks;
+  const char* src = (const char*)x;
+  char* dst = (char*)out;
+  for (int64_t r = 0; r < ranks; ++r)
+    for (int64_t m = 0; m < rows; ++m)
+      memcpy(dst + ((r * rows + m) * share) * elem, src + (m * cols + r * share) * elem, (size_t)(share * elem));
+}

@@ -44,6 +44,14 @@ def test_two_pass_row_quantize(ops, rows, cols, ld, gated, dtype):
     assert np.abs(q.cpu().numpy()).max() == 127  # the row maximum lands on the last level
     q2, s2 = ops.quantize_rows_whole(gate, up)     # both passes in one kernel: the same bytes
     assert torch.equal(q2, q) and torch.equal(s2, scale)
+    # the C oracle: exact without gating, within one level on a few values with it (approximate exp / reciprocal)
+    from oracle import c
+    oq, os_ = c.gated_quantize(gate.float().cpu().numpy(), up.float().cpu().numpy() if gated else None)
+    odiff = np.abs(q.cpu().numpy().astype(np.int32) - oq.astype(np.int32))
+    if gated:
+        assert np.allclose(scale.cpu().numpy(), os_, rtol=1e-5) and odiff.max() <= 1 and (odiff > 0).mean() < 2e-3
+    else:
+        assert (scale.cpu().numpy() == os_).all() and odiff.max() == 0
     assert (out[0] == 77).all() and (out[rows + 1] == 77).all() and (out[:, cols:] == 77).all()
 
 
@@ -60,6 +68,8 @@ def test_norm_reads_gathered_slabs(ops, rows, g, slab):
     q1, s1, sum1 = ops.rmsnorm_dynamic_quant(xg, gamma, 1e-5, residual=res, x_gathered=True)
     assert torch.equal(q0, q1) and torch.equal(s0, s1) and torch.equal(sum0, sum1)
     assert torch.equal(tp.gathered_to_rowmajor(xg), x)
+    from oracle import c
+    assert (xg.cpu().numpy() == c.gathered_layout(x.cpu().numpy(), g)).all()
     y0 = ops.rmsnorm(x, gamma, 1e-5, residual=res)
     y1 = ops.rmsnorm(xg, gamma, 1e-5, residual=res, x_gathered=True)
     assert torch.equal(y0, y1)
@@ -238,6 +248,12 @@ def test_rope_and_cache_append_match_the_elementwise_form(ops, batch, seq, heads
     got = work.view(batch, seq, 3, heads, dim)
     assert torch.equal(got[:, :, 0], want_q)
     assert torch.equal(got[:, :, 1], k) and torch.equal(got[:, :, 2], v)          # k, v of the input stay as they were
+    # the C oracle (fp32 restatement, rounded to fp16 as the kernel stores it)
+    from oracle import c
+    pos = np.tile(np.arange(pos0, pos0 + seq), batch)
+    oq = c.rope(q.float().cpu().numpy().reshape(batch * seq, heads, dim), pos, dec._cos.cpu().numpy(),
+                dec._sin.cpu().numpy())
+    assert (got[:, :, 0].float().cpu().numpy().reshape(batch * seq, heads, dim) == oq.astype(np.float16).astype(np.float32)).all()
     assert torch.equal(kc[:, :, pos0:pos0 + seq], want_k.transpose(1, 2))
     assert torch.equal(vc[:, :, pos0:pos0 + seq], v.transpose(1, 2))
     assert (kc[:, :, :pos0] == 7).all() and (kc[:, :, pos0 + seq:] == 7).all() and (vc[:, :, pos0 + seq:] == 7).all()

@@ -189,3 +189,40 @@ def test_rmsnorm_and_residual():
     want = h / np.sqrt((h * h).mean(-1, keepdims=True) + 1e-6) * gm
     assert np.allclose(y, want, rtol=1e-6, atol=1e-6)
     assert (s == x + r).all()
+
+
+def test_decoder_glue_restatements():
+    """The restatements behind the column-parallel decoder tests, pinned to their
+    defining formulas in numpy / eager torch."""
+    import torch
+    rng = np.random.default_rng(4)
+    g = (rng.standard_normal((9, 40)) * 3).astype(np.float32)
+    u = (rng.standard_normal((9, 40)) * 3).astype(np.float32)
+    q, s = c.gated_quantize(g, u)
+    h = (g.astype(np.float64) / (1 + np.exp(-g.astype(np.float64))) * u).astype(np.float32)
+    want_s = np.maximum(np.abs(h).max(axis=1) / np.float32(127), np.finfo(np.float32).eps).astype(np.float32)
+    assert (s == want_s).all()
+    assert (q == np.clip(np.rint(h / want_s[:, None]), -128, 127)).all()
+    assert (q == torch.nn.functional.silu(torch.from_numpy(g).double()).mul(torch.from_numpy(u).double()).float()
+            .div(torch.from_numpy(want_s)[:, None]).round().clamp(-128, 127).to(torch.int8).numpy()).all()
+    q1, s1 = c.gated_quantize(g)
+    q2, s2 = c.dynamic_quantize(g)
+    assert (q1 == q2).all() and (s1 == s2).all()
+    # rotary embedding against the eager elementwise form
+    tokens, heads, dim = 6, 3, 16
+    x = rng.standard_normal((tokens, heads, dim)).astype(np.float32)
+    pos = np.array([0, 1, 5, 9, 2, 7])
+    inv = 10000.0 ** (-np.arange(dim // 2, dtype=np.float32) / np.float32(dim // 2))
+    ang = torch.arange(12, dtype=torch.float32)[:, None] * torch.from_numpy(inv.astype(np.float32))[None, :]
+    cos_t, sin_t = ang.cos().numpy(), ang.sin().numpy()
+    y = c.rope(x, pos, cos_t, sin_t)
+    xt = torch.from_numpy(x)
+    cs, sn = torch.from_numpy(cos_t)[pos][:, None, :], torch.from_numpy(sin_t)[pos][:, None, :]
+    x1, x2 = xt[..., :dim // 2], xt[..., dim // 2:]
+    want = torch.cat([x1 * cs - x2 * sn, x2 * cs + x1 * sn], dim=-1).numpy()
+    assert (y == want).all()
+    # the layout an all-gather of column shards leaves
+    m = rng.integers(-128, 128, (5, 12), dtype=np.int8)
+    lay = c.gathered_layout(m, 3)
+    assert lay.shape == (3, 5, 4) and (lay[1] == m[:, 4:8]).all()
+    assert (lay.transpose(1, 0, 2).reshape(5, 12) == m).all()
