@@ -318,7 +318,9 @@ ORACLE_API void oracle_qgemm_ral_i8(const int8_t* a, const int8_t* w, int64_t M,
  * None of this exists as named code in the reference (its quantize op rejects
  * dynamic scales, disc_lower_quantize_and_dequantize.cc:41-43; RoPE and SwiGLU
  * reach it as generated elementwise kernels), so these restate the defining
- * formulas; the collective itself is ral_all_gather's rank-major concatenation
+ * formulas -- parity unpinned against the reference for these three, pinned to
+ * numpy / eager torch in tests/test_oracle.py -- and the collective itself is
+ * ral_all_gather's rank-major concatenation
  * (tao_compiler/mlir/ral/collective.cu.cc:226-309). */
 
 /* h = up ? silu(gate) * up : gate, per-row symmetric int8:
