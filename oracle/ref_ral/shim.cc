@@ -152,6 +152,14 @@ MemRefType<T, N> stub_recv_input(ExecutionContext*, int64_t) {
 template <typename T, int N>
 void stub_send_output(ExecutionContext*, int64_t, MemRefType<T, N>) {}
 
+// The collective calls of tao_compiler/mlir/ral/collective.cu.cc:60-440, with
+// that file's signatures (it cannot be compiled here: CUDA, NCCL and
+// TensorFlow headers), so that the names its registrations mangle are known.
+template <typename T, int N>
+MemRefType<T, N> stub_collective(ExecutionContext*, void*, MemRefType<T, N> input, void*) {
+  return input;
+}
+
 template <typename F>
 void note(const char* api, const char* device, F f) {
   g_names.push_back(
@@ -189,6 +197,25 @@ REF("ral_recv_input", "cpu", stub_recv_input<float, 2>);
 REF("ral_recv_input", "cpu", stub_recv_input<int8_t, 3>);
 REF("ral_send_output", "cpu", stub_send_output<float, 2>);
 REF("ral_send_output", "cpu", stub_send_output<int8_t, 3>);
+
+#define REF_COLLECTIVES(T)                                              \
+  REF("ral_all_reduce", "gpu", stub_collective<T, 0>);                    \
+  REF("ral_all_reduce", "gpu", stub_collective<T, 1>);                    \
+  REF("ral_all_reduce", "gpu", stub_collective<T, 2>);                    \
+  REF("ral_all_reduce", "gpu", stub_collective<T, 3>);                    \
+  REF("ral_all_reduce", "gpu", stub_collective<T, 4>);                    \
+  REF("ral_all_gather", "gpu", stub_collective<T, 1>);                    \
+  REF("ral_all_gather", "gpu", stub_collective<T, 2>);                    \
+  REF("ral_all_gather", "gpu", stub_collective<T, 3>);                    \
+  REF("ral_all_gather", "gpu", stub_collective<T, 4>);                    \
+  REF("ral_async_collective_done", "gpu", stub_collective<T, 0>);         \
+  REF("ral_async_collective_done", "gpu", stub_collective<T, 1>);         \
+  REF("ral_async_collective_done", "gpu", stub_collective<T, 2>);         \
+  REF("ral_async_collective_done", "gpu", stub_collective<T, 3>);         \
+  REF("ral_async_collective_done", "gpu", stub_collective<T, 4>)
+REF_COLLECTIVES(float);
+REF_COLLECTIVES(tao::ral::float16);
+REF_COLLECTIVES(tao::ral::bfloat16);
 
 extern "C" {
 

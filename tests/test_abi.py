@@ -71,6 +71,7 @@ def test_registry_lists_new_calls(built_lib):
                 "disc_b200_quantize", "disc_b200_dynamic_quantize", "disc_b200_dequantize",
                 "disc_b200_layernorm", "disc_b200_add_layernorm", "disc_b200_add_layernorm_quant",
                 "disc_b200_rmsnorm", "disc_b200_softmax", "disc_b200_masked_softmax",
+                "ral_all_gather", "ral_all_reduce", "ral_async_collective_done", "disc_b200_qgemm_all_gather",
                 "alloc", "dealloc", "ral_recv_input", "ral_send_output"):
         assert api in apis
     # bare api names resolve too (first registration keeps the nickname: ral_helper.cc:43-51)
