@@ -173,6 +173,15 @@ def test_attr_blob_roundtrip(built_lib):
              struct.pack("<I", 8) + struct.pack("<q", 1) + struct.pack("<q", 3) + b"\x01" + s(b"\x07"))
     assert lib.disc_b200_attrs_describe(dense, out, 4096) > 0
     assert out.value == b"{rank1UI8DenseAttr: dense<uint8[3]:3B>}"
+    # the attributes of a collective call as the Python writer serialises them
+    # (replica_groups is a dense [groups, ranks per group] tensor: collective.cu.cc:236-237)
+    import numpy as np
+    coll = pack_attrs({"all_gather_dim": 1, "replica_groups": np.arange(8, dtype=np.int64).reshape(2, 4),
+                       "is_async": True, "async_token_key": 3})
+    assert lib.disc_b200_attrs_describe(coll, out, 4096) > 0
+    text = out.value.decode()
+    assert "all_gather_dim: 1" in text and "is_async: true" in text and "async_token_key: 3" in text
+    assert "replica_groups: dense<int64[2x4]:64B>" in text
     # garbage is rejected, not trusted
     assert lib.disc_b200_attrs_describe(struct.pack("<q", 3) + b"xyz", out, 4096) == -1
     assert lib.disc_b200_attrs_describe(struct.pack("<q", -5), out, 4096) == -1
