@@ -3,8 +3,12 @@
 // functions.
 #include <cstdio>
 #include <cstring>
+#include <mutex>
+#include <vector>
 #include <string>
 
+#include "ral/context.h"
+#include "ral/metadata.h"
 #include "ral/nccl_dyn.h"
 #include "../../include/disc_b200_ral.h"
 #include "kernels/qgemm.h"
@@ -359,6 +363,59 @@ int32_t disc_b200_all_reduce_f32(void* comm, const float* send, float* recv, int
   const int st = api.AllReduce(send, recv, static_cast<size_t>(count), disc_b200::ral::kNcclFloat32, op,
                                comm, static_cast<cudaStream_t>(stream));
   return st == 0 ? 0 : nccl_fail("ncclAllReduce", st);
+}
+
+int32_t disc_b200_context_load_metadata(disc_b200_context* handle, const char* path) {
+  auto* ctx = reinterpret_cast<disc_b200::ral::Context*>(handle);
+  if (!ctx || !path) {
+    g_last_error = "load_metadata: null context or path";
+    return 1;
+  }
+  std::string why;
+  auto file = disc_b200::ral::MetadataFile::load(path, &why);
+  if (!file) {
+    g_last_error = why;
+    return 1;
+  }
+  std::lock_guard<std::mutex> l(ctx->mu);
+  ctx->metadata = std::move(file);
+  return 0;
+}
+
+int32_t disc_b200_metadata_write(const char* path, int32_t n, const char* const* names, const int32_t* is_host,
+                                 const void* const* data, const int64_t* bytes) {
+  if (!path || n < 0 || (n > 0 && (!names || !is_host || !data || !bytes))) {
+    g_last_error = "metadata_write: null argument";
+    return 1;
+  }
+  disc_b200::ral::MetadataWriter w(path);
+  if (!w.ok()) {
+    g_last_error = std::string("metadata_write: cannot create ") + path;
+    return 1;
+  }
+  for (int32_t i = 0; i < n; ++i) {
+    if (!names[i] || bytes[i] < 0 || !w.add(names[i], is_host[i] != 0, data[i], static_cast<size_t>(bytes[i]))) {
+      g_last_error = std::string("metadata_write: duplicated key or write error at ") + (names[i] ? names[i] : "?");
+      return 1;
+    }
+  }
+  if (!w.finish()) {
+    g_last_error = "metadata_write: write error";
+    return 1;
+  }
+  return 0;
+}
+
+int32_t disc_b200_const_name_info(const char* unique_name, int32_t* rank, int64_t* sizes8, int64_t* elem_bytes) {
+  std::vector<int64_t> shape;
+  int64_t width = 0;
+  if (!unique_name || !disc_b200::ral::parse_const_name(unique_name, &shape, &width) || shape.size() > 8) return 1;
+  if (rank) *rank = static_cast<int32_t>(shape.size());
+  if (sizes8) {
+    for (size_t i = 0; i < shape.size(); ++i) sizes8[i] = shape[i];
+  }
+  if (elem_bytes) *elem_bytes = width;
+  return 0;
 }
 
 const char* disc_b200_last_error_string(void) { return g_last_error.c_str(); }

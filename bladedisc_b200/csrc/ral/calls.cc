@@ -949,6 +949,56 @@ MemRef<OutT, 3> qgemm_all_gather(ExecContext* ctx, void* stream_handle, MemRef<i
 DISC_B200_REGISTER_QGEMM_AG(2);
 DISC_B200_REGISTER_QGEMM_AG(3);
 
+
+// --------------------------------------------------------- 5. constants
+// ral_const: the constants of the compiled graph (for the quantized path the
+// int8 weights, scale vectors and biases) by unique name, decoded from the
+// metadata file on first use; device constants are uploaded once and live as
+// long as the context.  Reference: ral_base_cuda_const_host / _cuda
+// (tao_compiler/mlir/ral/context/common_context_impl.cc:279-420,
+// common_context_impl_cuda.cc:61-200), both registered as "ral_const".
+template <typename T, int N, bool kDevice>
+MemRef<T, N> ral_const(ExecContext* ctx, void* stream_handle, const char* unique_name,
+                       int32_t unique_index_in_module) {
+  int64_t zeros[N > 0 ? N : 1] = {0};
+  MemRef<T, N> none = make_memref<T, N>(nullptr, zeros);
+  const ConstEntry* e = ctx->ctx->get_const(kDevice, unique_name, unique_index_in_module);
+  if (!e) return none;
+  if (static_cast<int>(e->shape.size()) != N) {
+    ctx->signal_error("unexpected shape string in unique_name");
+    return none;
+  }
+  return make_memref<T, N>(static_cast<T*>(e->ptr), e->shape.data());
+}
+
+#define DISC_B200_REGISTER_CONST(T, N)                                   \
+  DISC_B200_RAL_API("ral_const", "cpu", ral_const<T, N, false>);          \
+  DISC_B200_RAL_API("ral_const", "gpu", ral_const<T, N, true>)
+// ranks 0..8 and the element types the reference instantiates
+// (common_context_impl.cc:392-480 and :985-1000, common_context_impl_cuda.cc:177-290)
+#define DISC_B200_REGISTER_CONST_RANKS(T) \
+  DISC_B200_REGISTER_CONST(T, 0);         \
+  DISC_B200_REGISTER_CONST(T, 1);         \
+  DISC_B200_REGISTER_CONST(T, 2);         \
+  DISC_B200_REGISTER_CONST(T, 3);         \
+  DISC_B200_REGISTER_CONST(T, 4);         \
+  DISC_B200_REGISTER_CONST(T, 5);         \
+  DISC_B200_REGISTER_CONST(T, 6);         \
+  DISC_B200_REGISTER_CONST(T, 7);         \
+  DISC_B200_REGISTER_CONST(T, 8)
+DISC_B200_REGISTER_CONST_RANKS(double);
+DISC_B200_REGISTER_CONST_RANKS(float);
+DISC_B200_REGISTER_CONST_RANKS(f16_t);
+DISC_B200_REGISTER_CONST_RANKS(bf16_t);
+DISC_B200_REGISTER_CONST_RANKS(int8_t);
+DISC_B200_REGISTER_CONST_RANKS(uint8_t);
+DISC_B200_REGISTER_CONST_RANKS(int16_t);
+DISC_B200_REGISTER_CONST_RANKS(uint16_t);
+DISC_B200_REGISTER_CONST_RANKS(int32_t);
+DISC_B200_REGISTER_CONST_RANKS(uint32_t);
+DISC_B200_REGISTER_CONST_RANKS(int64_t);
+DISC_B200_REGISTER_CONST_RANKS(bool);
+
 }  // namespace
 }  // namespace ral
 }  // namespace disc_b200

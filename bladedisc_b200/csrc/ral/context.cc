@@ -1,3 +1,7 @@
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
 #include "context.h"
 #include "nccl_dyn.h"
 
@@ -94,6 +98,71 @@ void* Context::get_splitk_ws(int64_t bytes) {
   return splitk_ws;
 }
 
+const ConstEntry* Context::get_const(bool on_device, const char* unique_name, int32_t index) {
+  std::lock_guard<std::mutex> l(mu);
+  auto& by_index = on_device ? device_by_index : host_by_index;
+  if (index >= 0 && index < static_cast<int32_t>(by_index.size()) && by_index[index]) return by_index[index];
+  auto fail = [&](const std::string& msg) -> const ConstEntry* {
+    if (status == 0) {  // mu is held: record the first error here
+      status = 1;
+      message = msg;
+    }
+    return nullptr;
+  };
+  if (!unique_name) return fail("ral_const: null unique_name");
+  const std::string key(unique_name);
+  auto& store = on_device ? device_consts : host_consts;
+  auto it = store.find(key);
+  if (it == store.end()) {
+    if (!metadata) return fail("ral_const: no metadata file loaded (disc_b200_context_load_metadata)");
+    const std::string_view hex = on_device ? metadata->device_constant(key) : metadata->host_constant(key);
+    if (hex.data() == nullptr) return fail("const unique_name " + key + " not found in metadata file");
+    ConstEntry e;
+    int64_t width = 0;
+    if (!parse_const_name(key, &e.shape, &width)) return fail("unexpected const unique_name format: " + key);
+    std::vector<uint8_t> data;
+    if (!decode_hex(hex, &data)) return fail("constant " + key + " is not hexadecimal");
+    int64_t elems = 1;
+    for (int64_t d : e.shape) elems *= d;
+    const int64_t want = elems * width;
+    if (static_cast<int64_t>(data.size()) < want) {
+      // a splat: the stored element repeats (common_context_impl_cuda.cc:97-105)
+      if (data.empty()) return fail("constant " + key + " is empty");
+      const std::vector<uint8_t> unit = data;
+      data.resize(static_cast<size_t>(want));
+      for (int64_t off = static_cast<int64_t>(unit.size()); off < want; off += static_cast<int64_t>(unit.size())) {
+        const int64_t n = std::min<int64_t>(static_cast<int64_t>(unit.size()), want - off);
+        std::memcpy(data.data() + off, unit.data(), static_cast<size_t>(n));
+      }
+    }
+    e.bytes = static_cast<int64_t>(data.size());
+    if (on_device) {
+      e.ptr = raw_alloc(data.size());
+      if (!e.ptr) return fail("device allocation of constant " + key + " failed");
+      // the staging bytes die with this call: wait for the copy (as the reference does, :116-118)
+      cudaError_t st = cudaMemcpyAsync(e.ptr, data.data(), data.size(), cudaMemcpyHostToDevice, stream);
+      if (st == cudaSuccess) st = cudaStreamSynchronize(stream);
+      if (st != cudaSuccess) {
+        raw_free(e.ptr);
+        return fail(std::string("upload of constant ") + key + ": " + cudaGetErrorString(st));
+      }
+      persistent.insert(e.ptr);
+      metadata->release_device(key);
+    } else {
+      e.ptr = std::malloc(data.empty() ? 1 : data.size());
+      if (!e.ptr) return fail("host allocation of constant " + key + " failed");
+      std::memcpy(e.ptr, data.data(), data.size());
+      metadata->release_host(key);
+    }
+    it = store.emplace(key, std::move(e)).first;
+  }
+  if (index >= 0 && index < (1 << 20)) {
+    if (static_cast<int32_t>(by_index.size()) <= index) by_index.resize(index + 1, nullptr);
+    by_index[index] = &it->second;  // unordered_map nodes do not move
+  }
+  return &it->second;
+}
+
 bool Context::comm_info(int* size, int* rank) {
   if (!nccl_comm) {
     signal_error(1, "no NCCL communicator in this context (disc_b200_context_options.nccl_comm)");
@@ -122,6 +191,7 @@ bool Context::comm_info(int* size, int* rank) {
 }
 
 Context::~Context() {
+  for (auto& kv : host_consts) std::free(kv.second.ptr);
   for (void* p : persistent) raw_free(p);
   if (splitk_ws) raw_free(splitk_ws);
   magic = 0;

@@ -19,12 +19,20 @@
 #include <vector>
 
 #include "../../../include/disc_b200_ral.h"
+#include "metadata.h"
 
 namespace disc_b200 {
 namespace ral {
 
 constexpr uint32_t kContextMagic = 0xD15CB200u;
 constexpr uint32_t kExecMagic = 0xD15CE8ECu;
+
+// A constant of the compiled graph once it has been materialised.
+struct ConstEntry {
+  void* ptr = nullptr;
+  std::vector<int64_t> shape;
+  int64_t bytes = 0;
+};
 
 struct Context {
   uint32_t magic = kContextMagic;
@@ -55,6 +63,17 @@ struct Context {
   // Size and rank of nccl_comm (queried once); false, with an error signalled,
   // when there is no communicator or NCCL cannot be reached.
   bool comm_info(int* size, int* rank);
+
+  // Constants of the executable (reference: RalGlobalConstantState,
+  // tao_compiler/mlir/ral/context/common_context_impl.cc:279-346 and
+  // common_context_impl_cuda.cc:61-132): decoded from the metadata file on first
+  // use, device ones uploaded once and kept until the context dies; looked up by
+  // the module-unique index first, by name otherwise.
+  std::unique_ptr<MetadataFile> metadata;
+  std::unordered_map<std::string, ConstEntry> device_consts, host_consts;
+  std::vector<const ConstEntry*> device_by_index, host_by_index;
+  // nullptr after signalling an error
+  const ConstEntry* get_const(bool on_device, const char* unique_name, int32_t index);
   ~Context();
 };
 

@@ -196,14 +196,15 @@ class RalContext:
         return ctypes.addressof(buf)
 
     def call(self, api: str, device: str, args: Sequence, results: Sequence[MemRefSpec] = (),
-             scalar_result: Optional[str] = None):
+             scalar_result: Optional[str] = None, raw: bool = False):
         """Calls ``api`` through tao_ral_call_impl.
 
         ``args`` entries: torch tensors (memrefs), ``("pvoid", int)``,
         ``("i64", int)``, ``("i32", int)``, ``("i1", bool)``, or ``("m<N>d<tag>", None)``
         for a null memref.  The leading context argument is added here.
         Returns torch tensors that view the returned device buffers (rank-N
-        results) without taking ownership.
+        results) without taking ownership; with ``raw`` the packed memref
+        descriptors themselves (results in host memory).
         """
         if not self.exec_handle:
             self.begin()
@@ -267,6 +268,8 @@ class RalContext:
         self._raise_if_error()
         if scalar_result == "pvoid":
             return r.value
+        if raw:
+            return [m for _, m in outs]
         tensors = [self._view(spec, m) for spec, m in outs]
         if not results:
             return None
@@ -281,6 +284,34 @@ class RalContext:
         if m.data == 0 or numel == 0:
             return torch.empty(shape, dtype=dtype, device=f"cuda:{self.device}")
         return _tensor_from_ptr(m.data, shape, dtype, self.device)
+
+    # ----------------------------------------------------------- constants
+    def load_metadata(self, path: str):
+        """Attaches the metadata file of a compiled executable (its constants);
+        the reference does this when it builds the context from the artefact
+        (BaseContextOption::metadata_file_path, tao_compiler/mlir/ral/context/base/base_context.cc:30-52)."""
+        if self._L.disc_b200_context_load_metadata(self.handle, str(path).encode()) != 0:
+            raise RalError(self._L.disc_b200_last_error_string().decode())
+
+    def const(self, unique_name: str, index: int, tag: str, rank: int, device: str = "gpu"):
+        """``ral_const``: the constant ``unique_name`` as a device tensor
+        (``device="gpu"``) or as a numpy copy of the host constant (``"cpu"``)."""
+        name = ctypes.create_string_buffer(unique_name.encode())
+        args = [("pvoid", 0), ("pvoid", ctypes.addressof(name)), ("i32", index)]
+        spec = MemRefSpec(tag, rank)
+        if device == "gpu":
+            return self.call("ral_const", "gpu", args, results=[spec])
+        import numpy as np
+        from .metadata import TAG_NUMPY
+        (m,) = self.call("ral_const", "cpu", args, results=[spec], raw=True)
+        dt = np.dtype(TAG_NUMPY[tag])
+        n = 1
+        for d in m.sizes:
+            n *= d
+        if m.data == 0 or n == 0:
+            return np.empty(m.sizes, dt)
+        buf = (ctypes.c_char * (n * dt.itemsize)).from_address(m.data)
+        return np.frombuffer(buf, dtype=dt).reshape(m.sizes).copy()
 
     def dealloc(self, t_or_ptr):
         ptr = t_or_ptr.data_ptr() if isinstance(t_or_ptr, torch.Tensor) else int(t_or_ptr)

@@ -309,6 +309,25 @@ int32_t disc_b200_all_gather_rows(void* comm, void* buf, int32_t nranks, int64_t
 int32_t disc_b200_all_reduce_f32(void* comm, const float* send, float* recv, int64_t count,
                                  int32_t op, void* stream);
 
+/* ---- Constants of a compiled executable.
+ * A DISC executable asks for its constants (the int8 weights, scale vectors and
+ * biases of the quantized path among them) through the custom call ral_const
+ * (ctx, stream handle, unique name, module-unique index) -> memref, on "cpu" for
+ * host constants and "gpu" for device ones
+ * (tao_compiler/mlir/ral/context/common_context_impl.cc:279-420,
+ * common_context_impl_cuda.cc:61-200).  The values live in the metadata file
+ * written next to the executable (tao_compiler/mlir/ral/ral_metadata.cc:65-167:
+ * magic, {is_host, key, hexadecimal value} entries, count); a unique name is
+ * "<id>_<type tag>_<d0xd1x...>".  The host loads the file into the context once;
+ * constants are decoded on first use, device constants uploaded once and kept
+ * until the context is destroyed. */
+int32_t disc_b200_context_load_metadata(disc_b200_context* ctx, const char* path);
+/* Writes a metadata file in the reference's format (tools, tests). */
+int32_t disc_b200_metadata_write(const char* path, int32_t n, const char* const* names, const int32_t* is_host,
+                                 const void* const* data, const int64_t* bytes);
+/* Shape (up to 8 dims) and element width encoded in a constant's unique name. */
+int32_t disc_b200_const_name_info(const char* unique_name, int32_t* rank, int64_t* sizes8, int64_t* elem_bytes);
+
 /* ------------------------------------------------------------------------
  * 4. Diagnostics.
  * ---------------------------------------------------------------------- */

@@ -1,13 +1,15 @@
 // TEST INFRASTRUCTURE.  Linked together with the reference's own RAL core
-// (ral_api.cc, ral_context.cc, ral_helper.cc, ral_logging.cc, compiled from
-// the reference tree where it lies) into oracle/_ref/libref_ral.so.
+// (ral_api.cc, ral_context.cc, ral_helper.cc, ral_logging.cc, ral_metadata.cc,
+// compiled from the reference tree where it lies) into oracle/_ref/libref_ral.so.
 //
 // It registers recording stubs, with the reference's registration macro and
 // the reference's C++ signatures, for the custom calls our library implements
 // under reference names.  Tests then (1) compare the names the reference
 // mangles with the names our registry holds and (2) send one packed argument
 // array through the reference's tao_ral_call_impl and read back what its
-// unpacking produced, which pins the packing our own tests use.
+// unpacking produced, which pins the packing our own tests use.  (3) The
+// reference's metadata file emitter and loader are exported as they are, so
+// that files written by either side can be read by the other.
 #include <cstdint>
 #include <cstring>
 #include <string>
@@ -16,6 +18,7 @@
 #include "mlir/ral/ral_api.h"
 #include "mlir/ral/ral_context.h"
 #include "mlir/ral/ral_helper.h"
+#include "mlir/ral/ral_metadata.h"
 
 using tao::ral::ExecutionContext;
 using tao::ral::MemRefType;
@@ -160,6 +163,14 @@ MemRefType<T, N> stub_collective(ExecutionContext*, void*, MemRefType<T, N> inpu
   return input;
 }
 
+// ral_const with the signature of ral_base_cuda_const_host / _cuda
+// (tao_compiler/mlir/ral/context/common_context_impl.cc:279-283; the file needs
+// the whole runtime to compile, so only its signature is restated).
+template <typename T, int N>
+MemRefType<T, N> stub_const(ExecutionContext*, void*, const char*, int32_t) {
+  return MemRefType<T, N>();
+}
+
 template <typename F>
 void note(const char* api, const char* device, F f) {
   g_names.push_back(
@@ -217,6 +228,29 @@ REF_COLLECTIVES(float);
 REF_COLLECTIVES(tao::ral::float16);
 REF_COLLECTIVES(tao::ral::bfloat16);
 
+#define REF_CONSTS(T)                             \
+  REF("ral_const", "cpu", stub_const<T, 0>);        \
+  REF("ral_const", "cpu", stub_const<T, 1>);        \
+  REF("ral_const", "cpu", stub_const<T, 2>);        \
+  REF("ral_const", "cpu", stub_const<T, 8>);        \
+  REF("ral_const", "gpu", stub_const<T, 0>);        \
+  REF("ral_const", "gpu", stub_const<T, 1>);        \
+  REF("ral_const", "gpu", stub_const<T, 2>);        \
+  REF("ral_const", "gpu", stub_const<T, 4>);        \
+  REF("ral_const", "gpu", stub_const<T, 8>)
+REF_CONSTS(double);
+REF_CONSTS(float);
+REF_CONSTS(tao::ral::float16);
+REF_CONSTS(tao::ral::bfloat16);
+REF_CONSTS(int8_t);
+REF_CONSTS(uint8_t);
+REF_CONSTS(int16_t);
+REF_CONSTS(uint16_t);
+REF_CONSTS(int32_t);
+REF_CONSTS(uint32_t);
+REF_CONSTS(int64_t);
+REF_CONSTS(bool);
+
 extern "C" {
 
 int ref_num_names() { return static_cast<int>(g_names.size()); }
@@ -233,4 +267,31 @@ int ref_dispatch(const char* name, void** args) {
   return static_cast<int>(g_record.size());
 }
 int64_t ref_recorded(int i) { return g_record[i]; }
+
+// The reference's emitter (ral_metadata.cc:117-167): header, constants, tailer.
+// Values are the hexadecimal strings the compiler would have produced.
+int ref_metadata_write(const char* path, int n, const char* const* names, const int* is_host,
+                       const char* const* hex_values) {
+  tao::ral::MetadataFileEmitter emitter(path);
+  if (!emitter.emitHeader()) return 1;
+  for (int i = 0; i < n; ++i) {
+    const bool ok = is_host[i] ? emitter.emitHostConstant(names[i], hex_values[i])
+                               : emitter.emitDeviceConstant(names[i], hex_values[i]);
+    if (!ok) return 2;
+  }
+  return emitter.emitTailer() ? 0 : 3;
+}
+
+// The reference's loader (ral_metadata.cc:65-115): length of the value, or -1 if
+// the file does not load, -2 if there is no such constant; the value is copied
+// into buf when it fits.
+int64_t ref_metadata_get(const char* path, const char* name, int is_host, char* buf, int64_t cap) {
+  auto file = tao::ral::MetadataFile::loadFromFile(path);
+  if (!file) return -1;
+  const std::string* value = nullptr;
+  const bool found = is_host ? file->getHostConstant(name, value) : file->getDeviceConstant(name, value);
+  if (!found || !value) return -2;
+  if (static_cast<int64_t>(value->size()) <= cap) std::memcpy(buf, value->data(), value->size());
+  return static_cast<int64_t>(value->size());
+}
 }

@@ -179,3 +179,47 @@ def test_errors_are_recorded_not_fatal(ral):
     q = ral.call("ral_pdll_qgemm", "gpu", _qgemm_args(e, w2, torch.zeros(8, device="cuda"), 1, 1, 1, ral.attr_blob({})),
                  [MemRefSpec("i8", 2)])
     assert tuple(q.shape) == (0, 8)
+
+
+def test_constants_from_the_metadata_file(ral, tmp_path):
+    """A quantized linear the way the executable runs it: weight, scales and bias
+    come from the metadata file through ral_const (uploaded once, owned by the
+    context), then ral_pdll_qgemm (common_context_impl_cuda.cc:61-160)."""
+    from bladedisc_b200 import metadata as M
+    from bladedisc_b200.ral import MemRefSpec, RalError
+    from oracle import c
+    rng = np.random.default_rng(11)
+    x = rng.integers(-127, 128, (140, 256), dtype=np.int8)
+    w = rng.integers(-127, 128, (192, 256), dtype=np.int8)
+    bias = (rng.standard_normal(192) * 30).astype(np.float32)
+    s_x, s_w, s_out = np.float32(0.1), np.float32(0.3), np.float32(50.0)
+    zero = np.int32(0)
+    consts = [(M.const_name(0, w), False, w), (M.const_name(1, bias), False, bias),
+              ("2_f32_", False, s_x), ("3_f32_", False, s_w), ("4_f32_", False, s_out), ("5_i32_", False, zero),
+              ("6_f16_4x8", False, np.float16(1.5)),                       # splat
+              (M.const_name(7, np.zeros(2, np.int64)), True, np.array([140, 256], np.int64))]
+    path = tmp_path / "model.so.pbtxt"
+    M.write_metadata(path, consts)
+    with pytest.raises(RalError, match="no metadata file"):
+        ral.const(consts[0][0], 0, "i8", 2)
+    ral.load_metadata(path)
+    wd = ral.const(consts[0][0], 0, "i8", 2)
+    assert wd.shape == (192, 256) and (wd.cpu().numpy() == w).all()
+    assert ral.const("anything", 0, "i8", 2).data_ptr() == wd.data_ptr()   # by index: no second upload
+    bd = ral.const(consts[1][0], 1, "f32", 1)
+    sx, sw, so, zp = (ral.const(f"{i}_{t}_", i, t, 0) for i, t in ((2, "f32"), (3, "f32"), (4, "f32"), (5, "i32")))
+    assert float(sx) == float(s_x) and int(zp) == 0
+    half = ral.const("6_f16_4x8", 6, "f16", 2)
+    assert half.shape == (4, 8) and (half == 1.5).all()
+    assert (ral.const(consts[7][0], 7, "i64", 1, device="cpu") == [140, 256]).all()
+    q = ral.call("ral_pdll_qgemm", "gpu", [("pvoid", 0), _dev(x), wd, bd, sx, zp, sw, zp, so, zp,
+                                           ("pvoid", ral.attr_blob({}))], [MemRefSpec("i8", 2)])
+    _, want = c.qgemm_epilogue(c.qgemm_acc(x, w), x_scale=s_x, w_scale=s_w, out_scale=s_out, bias=bias, fold_out=True)
+    assert (q.cpu().numpy() == want).all()
+    ral.dealloc(q)
+    ral.dealloc(wd)                        # constants are persistent: a dealloc from generated code is ignored
+    assert (wd.cpu().numpy() == w).all()
+    with pytest.raises(RalError, match="not found in metadata file"):
+        ral.const("9_f32_4", 9, "f32", 1)
+    with pytest.raises(RalError, match="unexpected shape string"):
+        ral.const(consts[1][0], 1, "f32", 2)
