@@ -1,11 +1,13 @@
 // Direct (non-dispatched) C entry points: plain pointers and sizes in, a
 // status code out.  The custom calls of ral/calls.cc land on the same launch
 // functions.
+#include <dlfcn.h>
+
 #include <cstdio>
 #include <cstring>
 #include <mutex>
-#include <vector>
 #include <string>
+#include <vector>
 
 #include "ral/context.h"
 #include "ral/metadata.h"
@@ -363,6 +365,78 @@ int32_t disc_b200_all_reduce_f32(void* comm, const float* send, float* recv, int
   const int st = api.AllReduce(send, recv, static_cast<size_t>(count), disc_b200::ral::kNcclFloat32, op,
                                comm, static_cast<cudaStream_t>(stream));
   return st == 0 ? 0 : nccl_fail("ncclAllReduce", st);
+}
+
+struct disc_b200_executable {
+  void* lib = nullptr;
+  void (*entry)(void**) = nullptr;
+  disc_b200_context* ctx = nullptr;
+};
+
+disc_b200_executable* disc_b200_executable_open(const char* so_path, const char* metadata_path,
+                                                const disc_b200_context_options* opts) {
+  if (!so_path) {
+    g_last_error = "executable_open: null path";
+    return nullptr;
+  }
+  void* lib = dlopen(so_path, RTLD_NOW | RTLD_LOCAL);
+  if (!lib) {
+    const char* why = dlerror();
+    g_last_error = std::string("executable_open: ") + (why ? why : so_path);
+    return nullptr;
+  }
+  void* entry = dlsym(lib, kMlirLoweredEntry);
+  if (!entry) {
+    g_last_error = std::string("executable_open: no entry point \"") + kMlirLoweredEntry + "\" in " + so_path;
+    dlclose(lib);
+    return nullptr;
+  }
+  disc_b200_context* ctx = disc_b200_context_create(opts);
+  if (metadata_path && disc_b200_context_load_metadata(ctx, metadata_path) != 0) {
+    disc_b200_context_destroy(ctx);
+    dlclose(lib);
+    return nullptr;
+  }
+  auto* exe = new disc_b200_executable;
+  exe->lib = lib;
+  exe->entry = reinterpret_cast<void (*)(void**)>(entry);
+  exe->ctx = ctx;
+  return exe;
+}
+
+disc_b200_context* disc_b200_executable_context(disc_b200_executable* exe) { return exe ? exe->ctx : nullptr; }
+
+disc_b200_exec* disc_b200_executable_run(disc_b200_executable* exe, int32_t n_inputs,
+                                         const disc_b200_buffer_ref* inputs) {
+  if (!exe || n_inputs < 0 || (n_inputs > 0 && !inputs)) {
+    g_last_error = "executable_run: null argument";
+    return nullptr;
+  }
+  disc_b200_exec* exec = disc_b200_exec_create(exe->ctx);
+  for (int32_t i = 0; i < n_inputs; ++i) {
+    if (disc_b200_exec_bind_input(exec, i, inputs[i].data, inputs[i].rank, inputs[i].sizes) != 0) {
+      g_last_error = "executable_run: bad input " + std::to_string(i);
+      disc_b200_exec_destroy(exec);
+      return nullptr;
+    }
+  }
+  // what the generated disc_ral_call stub expects: { execution context, dispatcher }
+  void* ctx_struct[2] = {exec, reinterpret_cast<void*>(&tao_ral_call_impl)};
+  exe->entry(ctx_struct);
+  const char* msg = nullptr;
+  if (tao_ral_last_error(exe->ctx, &msg) != 0) {
+    g_last_error = msg ? msg : "executable_run: a custom call failed";
+    disc_b200_exec_destroy(exec);
+    return nullptr;
+  }
+  return exec;
+}
+
+void disc_b200_executable_close(disc_b200_executable* exe) {
+  if (!exe) return;
+  disc_b200_context_destroy(exe->ctx);
+  dlclose(exe->lib);
+  delete exe;
 }
 
 int32_t disc_b200_context_load_metadata(disc_b200_context* handle, const char* path) {

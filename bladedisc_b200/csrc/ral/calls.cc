@@ -108,6 +108,22 @@ DISC_B200_RAL_API("sync_on_stream", "gpu", ral_sync_on_stream);
 DISC_B200_RAL_API("ral_gpu_sync_all", "gpu", ral_sync_all);
 DISC_B200_RAL_API("ral_kernel_launch", "gpu", ral_kernel_launch);
 
+// Host buffers of generated code (cpu_context_impl.cc:120-215: "alloc", "dealloc" and
+// "ral_cpu_alloc_persistent" on "cpu").
+void* ral_host_alloc(ExecContext* ctx, uint64_t bytes) { return ctx->host_alloc(bytes); }
+void ral_host_dealloc(ExecContext* ctx, void* p) { ctx->host_dealloc(p); }
+void* ral_host_alloc_persistent(ExecContext* ctx, uint64_t bytes) {
+  void* p = ctx->host_alloc(bytes);
+  if (!p) return nullptr;
+  ctx->host_refcount.erase(p);
+  std::lock_guard<std::mutex> l(ctx->ctx->mu);
+  ctx->ctx->host_persistent.insert(p);
+  return p;
+}
+DISC_B200_RAL_API("alloc", "cpu", ral_host_alloc);
+DISC_B200_RAL_API("dealloc", "cpu", ral_host_dealloc);
+DISC_B200_RAL_API("ral_cpu_alloc_persistent", "cpu", ral_host_alloc_persistent);
+
 template <typename T, int N>
 MemRef<T, N> ral_recv_input(ExecContext* ctx, int64_t idx) {
   MemRef<T, N> m;

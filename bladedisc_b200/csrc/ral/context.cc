@@ -192,6 +192,7 @@ bool Context::comm_info(int* size, int* rank) {
 
 Context::~Context() {
   for (auto& kv : host_consts) std::free(kv.second.ptr);
+  for (void* p : host_persistent) std::free(p);
   for (void* p : persistent) raw_free(p);
   if (splitk_ws) raw_free(splitk_ws);
   magic = 0;
@@ -218,6 +219,34 @@ void ExecContext::dealloc(void* p) {
   if (--it->second == 0) {
     refcount.erase(it);
     ctx->raw_free(p);
+  }
+}
+
+// Host buffers of generated code (shape arithmetic, scalars read back): 64-byte
+// aligned, zero-byte requests still get a pointer, counted like device buffers
+// (tao_compiler/mlir/ral/context/base/cpu/cpu_context_impl.cc:120-180).
+void* ExecContext::host_alloc(size_t bytes) {
+  void* p = nullptr;
+  const size_t rounded = ((bytes ? bytes : 1) + 63) / 64 * 64;
+  if (posix_memalign(&p, 64, rounded) != 0 || !p) {
+    signal_error("host allocation of " + std::to_string(bytes) + " bytes failed");
+    return nullptr;
+  }
+  host_refcount[p] = 1;
+  return p;
+}
+
+void ExecContext::host_dealloc(void* p) {
+  if (!p) return;
+  {
+    std::lock_guard<std::mutex> l(ctx->mu);
+    if (ctx->host_persistent.count(p)) return;
+  }
+  auto it = host_refcount.find(p);
+  if (it == host_refcount.end()) return;  // an input or a constant
+  if (--it->second == 0) {
+    host_refcount.erase(it);
+    std::free(p);
   }
 }
 
@@ -313,6 +342,9 @@ void disc_b200_exec_destroy(disc_b200_exec* handle) {
   for (auto& kv : e->refcount) {
     if (!handed_out.count(kv.first)) e->ctx->raw_free(kv.first);
   }
+  for (auto& kv : e->host_refcount) {
+    if (!handed_out.count(kv.first)) std::free(kv.first);
+  }
   for (auto& kv : e->async_tokens) cudaEventDestroy(kv.second);
   e->magic = 0;
   delete e;
@@ -344,11 +376,12 @@ int32_t disc_b200_exec_get_output(disc_b200_exec* handle, int32_t idx, void** da
   if (owned) {
     // An output that aliases an input, a persistent buffer, or a buffer that
     // is also another output with a smaller index stays with its first owner.
-    bool mine = e->refcount.count(it->second.data) != 0;
+    const bool host = e->host_refcount.count(it->second.data) != 0;
+    bool mine = host || e->refcount.count(it->second.data) != 0;
     for (auto& kv : e->outputs) {
       if (kv.first < idx && kv.second.data == it->second.data) mine = false;
     }
-    *owned = mine ? 1 : 0;
+    *owned = mine ? (host ? 2 : 1) : 0;
   }
   return 0;
 }
@@ -356,6 +389,8 @@ int32_t disc_b200_exec_get_output(disc_b200_exec* handle, int32_t idx, void** da
 void disc_b200_exec_free_output(disc_b200_context* ctx, void* data) {
   if (ctx) reinterpret_cast<Context*>(ctx)->raw_free(data);
 }
+
+void disc_b200_exec_free_host_output(void* data) { std::free(data); }
 
 int32_t disc_b200_registry_size(void) { return disc_b200::ral::registry_size(); }
 const char* disc_b200_registry_name(int32_t i) { return disc_b200::ral::registry_name_at(i); }

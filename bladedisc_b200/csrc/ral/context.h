@@ -50,6 +50,7 @@ struct Context {
   int32_t status = 0;
   std::string message;
   std::unordered_set<void*> persistent;  // survive executions, freed with the context
+  std::unordered_set<void*> host_persistent;  // the same for host buffers
   // Scratch of the small-M qgemm path (grown on demand, counters kept zero).
   void* splitk_ws = nullptr;
   int64_t splitk_ws_bytes = 0;
@@ -87,7 +88,8 @@ struct ExecContext {
   Context* ctx = nullptr;
   std::unordered_map<int64_t, BoundTensor> inputs;
   std::unordered_map<int64_t, BoundTensor> outputs;
-  std::unordered_map<void*, int> refcount;  // buffers allocated during this execution
+  std::unordered_map<void*, int> refcount;  // device buffers allocated during this execution
+  std::unordered_map<void*, int> host_refcount;  // host buffers ("alloc" on "cpu"), same rules
   std::unordered_set<void*> input_ptrs;
   // Completion events of asynchronous collectives, by async_token_key
   // (reference: async_pair_tokens, tao_compiler/mlir/ral/collective.cu.cc:134,431).
@@ -95,6 +97,8 @@ struct ExecContext {
 
   void* alloc(size_t bytes);
   void dealloc(void* p);
+  void* host_alloc(size_t bytes);
+  void host_dealloc(void* p);
   void signal_error(const std::string& msg) { ctx->signal_error(1, msg); }
 };
 

@@ -112,6 +112,11 @@ SIGNATURES = {
     "disc_b200_all_gather": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "disc_b200_all_gather_rows": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int64, c_void_p]),
     "disc_b200_all_reduce_f32": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
+    "disc_b200_exec_free_host_output": (None, [c_void_p]),
+    "disc_b200_executable_open": (c_void_p, [c_char_p, c_char_p, POINTER(ContextOptions)]),
+    "disc_b200_executable_context": (c_void_p, [c_void_p]),
+    "disc_b200_executable_run": (c_void_p, [c_void_p, c_int32, c_void_p]),
+    "disc_b200_executable_close": (None, [c_void_p]),
     "disc_b200_context_load_metadata": (c_int32, [c_void_p, c_char_p]),
     "disc_b200_metadata_write": (c_int32, [c_char_p, c_int32, POINTER(c_char_p), POINTER(c_int32),
                                            POINTER(c_void_p), POINTER(c_int64)]),

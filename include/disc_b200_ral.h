@@ -81,12 +81,41 @@ void disc_b200_exec_destroy(disc_b200_exec* exec);
  * (ExecutionContext::bindInput, tao_compiler/mlir/ral/ral_context.h:164-170). */
 int32_t disc_b200_exec_bind_input(disc_b200_exec* exec, int32_t idx, const void* data, int32_t rank,
                                   const int64_t* sizes);
-/* Output idx after the executable ran.  *owned = 1 when the buffer was
- * allocated by this execution and is now the caller's to free with
- * disc_b200_exec_free_output (ExecutionContext::bindOutput). */
+/* Output idx after the executable ran.  *owned = 1 when the buffer is a device
+ * buffer allocated by this execution and now the caller's to free with
+ * disc_b200_exec_free_output, 2 when it is a host buffer of this execution
+ * (disc_b200_exec_free_host_output), 0 when it aliases an input, a constant or
+ * an earlier output (ExecutionContext::bindOutput). */
 int32_t disc_b200_exec_get_output(disc_b200_exec* exec, int32_t idx, void** data, int32_t* rank,
                                   int64_t* sizes8, int32_t* owned);
 void disc_b200_exec_free_output(disc_b200_context* ctx, void* data);
+void disc_b200_exec_free_host_output(void* data);
+
+/* ---- A compiled executable: the shared object DISC emits plus its metadata
+ * file.  Replaces RalContext's constructor, LoadEngine and Execute
+ * (pytorch_blade/pytorch_blade/compiler/mlir/runtime/ral_context.cpp:104-166,
+ * 293-321): dlopen, entry point "main" (kMlirLoweredEntry), one context, and per
+ * run an execution context whose address travels to the entry together with
+ * this library's dispatcher (tao_compiler/mlir/disc/disc_compiler.cc:95-131). */
+typedef struct disc_b200_executable disc_b200_executable;
+typedef struct disc_b200_buffer_ref {
+  const void* data;
+  int32_t rank;
+  const int64_t* sizes;
+} disc_b200_buffer_ref;
+
+/* NULL on failure (disc_b200_last_error_string says why).  metadata_path may be
+ * NULL for an executable without constants. */
+disc_b200_executable* disc_b200_executable_open(const char* so_path, const char* metadata_path,
+                                                const disc_b200_context_options* opts);
+disc_b200_context* disc_b200_executable_context(disc_b200_executable* exe);
+/* One inference: binds the inputs, calls the entry.  Returns the execution
+ * context to read the outputs from (disc_b200_exec_get_output; the caller
+ * destroys it) or NULL when a custom call failed; the error then stays on the
+ * context until tao_ral_clear_error. */
+disc_b200_exec* disc_b200_executable_run(disc_b200_executable* exe, int32_t n_inputs,
+                                         const disc_b200_buffer_ref* inputs);
+void disc_b200_executable_close(disc_b200_executable* exe);
 
 /* Registry inspection (the reference keeps its registry private:
  * tao_compiler/mlir/ral/ral_helper.h:254-269). */

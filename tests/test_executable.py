@@ -1,0 +1,93 @@
+"""Loading and running a compiled executable without a GPU: a hand-written stand-in
+for the compiler's shared object (tests/fake_executable/program.c, host program)
+goes through dlopen -> "main" -> dispatcher -> recv_input / ral_const / alloc /
+send_output, as the reference's RalContext drives a real one."""
+import ctypes
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from bladedisc_b200 import metadata as M
+
+SRC = Path(__file__).parent / "fake_executable" / "program.c"
+
+
+def build_program(tmp_path, host: bool):
+    so = tmp_path / ("host_program.so" if host else "gpu_program.so")
+    cmd = ["gcc", "-shared", "-fPIC", "-O1", "-Wno-main"] + (["-DHOST_PROGRAM"] if host else []) + ["-o", str(so), str(SRC)]
+    subprocess.run(cmd, check=True)
+    return so
+
+
+def test_host_program_runs_through_the_dispatcher(built_lib, tmp_path):
+    from bladedisc_b200.executable import Executable, ExecutableError
+    so = build_program(tmp_path, host=True)
+    c = np.arange(8, dtype=np.float32) * 0.5
+    meta = tmp_path / "meta"
+    M.write_metadata(meta, [("0_f32_8", True, c)])
+    outs = [("f32", "cpu")] * 3
+    with Executable(so, meta, outs) as exe:
+        for seed in range(3):                       # one context, several executions
+            x = np.random.default_rng(seed).standard_normal(8).astype(np.float32)
+            y, c_out, x_out = exe.run([x])
+            assert np.array_equal(y, x + c) and np.array_equal(c_out, c) and np.array_equal(x_out, x)
+        short = np.ones(5, np.float32)              # dynamic shape: the program sizes its result from the input
+        assert exe.run([short])[0].shape == (5,)
+        # wrong rank for the compiled signature: reported, and the executable stays usable
+        with pytest.raises(ExecutableError, match="input rank does not match"):
+            exe.run([np.ones((2, 4), np.float32)])
+        with pytest.raises(ExecutableError, match="invalid input index"):
+            exe.run([])
+        assert np.array_equal(exe.run([x])[0], x + c)
+    # the constant is missing from the file: first error kept, later calls skipped, no crash
+    M.write_metadata(meta, [("9_f32_8", True, c)])
+    with Executable(so, meta, outs) as exe:
+        with pytest.raises(ExecutableError, match="0_f32_8 not found in metadata file"):
+            exe.run([x])
+
+
+def test_open_errors(built_lib, tmp_path):
+    from bladedisc_b200.executable import Executable, ExecutableError
+    with pytest.raises(ExecutableError, match="executable_open"):
+        Executable(tmp_path / "nothing.so")
+    # a shared object without the entry point
+    src = tmp_path / "empty.c"
+    src.write_text("int not_main(void) { return 0; }\n")
+    so = tmp_path / "empty.so"
+    subprocess.run(["gcc", "-shared", "-fPIC", "-o", str(so), str(src)], check=True)
+    with pytest.raises(ExecutableError, match='no entry point "main"'):
+        Executable(so)
+    good = build_program(tmp_path, host=True)
+    with pytest.raises(ExecutableError, match="cannot open"):
+        Executable(good, tmp_path / "no_such_metadata")
+
+
+def test_output_ownership_codes(built_lib, tmp_path):
+    """owned = 2 for a host buffer the program allocated, 0 for a constant and for an input."""
+    from bladedisc_b200 import lib as L
+    from bladedisc_b200.executable import BufferRef
+    lib = L.load()
+    so = build_program(tmp_path, host=True)
+    meta = tmp_path / "meta"
+    M.write_metadata(meta, [("0_f32_8", True, np.zeros(8, np.float32))])
+    exe = lib.disc_b200_executable_open(str(so).encode(), str(meta).encode(), None)
+    assert exe
+    x = np.ones(8, np.float32)
+    sizes = (ctypes.c_int64 * 1)(8)
+    ref = BufferRef(x.ctypes.data, 1, sizes)
+    ex = lib.disc_b200_executable_run(exe, 1, ctypes.addressof(ref))
+    assert ex
+    got = []
+    for k in range(3):
+        data, rank, owned = ctypes.c_void_p(), ctypes.c_int32(), ctypes.c_int32()
+        s8 = (ctypes.c_int64 * 8)()
+        assert lib.disc_b200_exec_get_output(ex, k, ctypes.byref(data), ctypes.byref(rank), s8, ctypes.byref(owned)) == 0
+        got.append((owned.value, rank.value, s8[0], data.value))
+    assert [g[0] for g in got] == [2, 0, 0] and all(g[1:3] == (1, 8) for g in got)
+    assert got[2][3] == x.ctypes.data
+    assert lib.disc_b200_exec_get_output(ex, 3, None, None, None, None) != 0
+    lib.disc_b200_exec_destroy(ex)
+    lib.disc_b200_exec_free_host_output(got[0][3])
+    lib.disc_b200_executable_close(exe)

@@ -223,3 +223,30 @@ def test_constants_from_the_metadata_file(ral, tmp_path):
         ral.const("9_f32_4", 9, "f32", 1)
     with pytest.raises(RalError, match="unexpected shape string"):
         ral.const(consts[1][0], 1, "f32", 2)
+
+
+def test_compiled_executable_stand_in_runs_a_quantized_linear(tmp_path):
+    """dlopen -> "main" -> dispatcher: input bound by the host, weight / bias / scales from
+    the metadata file, ral_pdll_qgemm, outputs collected (ral_context.cpp:293-321).  The
+    program is tests/fake_executable/program.c, written the way generated code calls."""
+    from bladedisc_b200 import metadata as M
+    from bladedisc_b200.executable import Executable
+    from oracle import c
+    from test_executable import build_program
+    so = build_program(tmp_path, host=False)
+    rng = np.random.default_rng(5)
+    w = rng.integers(-127, 128, (192, 256), dtype=np.int8)
+    bias = (rng.standard_normal(192) * 30).astype(np.float32)
+    s_x, s_w, s_out = np.float32(0.1), np.float32(0.3), np.float32(50.0)
+    meta = tmp_path / "meta"
+    M.write_metadata(meta, [("0_i8_192x256", False, w), ("1_f32_192", False, bias), ("2_f32_", False, s_x),
+                            ("3_f32_", False, s_w), ("4_f32_", False, s_out), ("5_i32_", False, np.int32(0)),
+                            ("6_i64_2", True, np.array([192, 256], np.int64))])
+    with Executable(so, meta, [("i8", "cuda"), ("i64", "cpu"), ("i64", "cpu")], device=torch.cuda.current_device()) as exe:
+        for m in (140, 7, 1500):                     # dynamic batch: one executable, any M
+            x = rng.integers(-127, 128, (m, 256), dtype=np.int8)
+            q, dims, shape = exe.run([_dev(x)])
+            _, want = c.qgemm_epilogue(c.qgemm_acc(x, w), x_scale=s_x, w_scale=s_w, out_scale=s_out, bias=bias,
+                                       fold_out=True)
+            assert (q.cpu().numpy() == want).all()
+            assert list(dims) == [192, 256] and list(shape) == [m, 192]
