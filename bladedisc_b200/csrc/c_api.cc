@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "ral/context.h"
+#include "ral/cu_driver_dyn.h"
 #include "ral/metadata.h"
 #include "ral/nccl_dyn.h"
 #include "../../include/disc_b200_ral.h"
@@ -490,6 +491,10 @@ int32_t disc_b200_const_name_info(const char* unique_name, int32_t* rank, int64_
   }
   if (elem_bytes) *elem_bytes = width;
   return 0;
+}
+
+int32_t disc_b200_select_device_image(int64_t num_images, int32_t cc_major, int32_t cc_minor) {
+  return num_images < 0 ? -1 : disc_b200::ral::select_blob(static_cast<size_t>(num_images), cc_major, cc_minor);
 }
 
 const char* disc_b200_last_error_string(void) { return g_last_error.c_str(); }

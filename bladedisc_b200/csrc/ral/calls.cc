@@ -18,6 +18,7 @@
 #include "../kernels/rowops.h"
 #include "abi.h"
 #include "context.h"
+#include "cu_driver_dyn.h"
 #include "nccl_dyn.h"
 #include "pdl_attr.h"
 
@@ -86,13 +87,80 @@ void ral_sync_on_stream(ExecContext* ctx, void* handle) {
 }
 void ral_sync_all(ExecContext* ctx) { report(ctx, cudaDeviceSynchronize(), "DeviceSync", nullptr); }
 
-// Launching a compiler-generated cubin is the reference compiler's own code
-// generation; this runtime replaces those kernels with the calls of part 3.
+// A kernel the compiler generated (kLoop / kStitch fusions and everything else
+// that is not a library call), embedded in the executable as one or several
+// device images.  Same selection, caching and launch as the reference
+// (cuda_context_impl.cc:348-445).  Images built for sm_60..sm_86 carry no code a
+// B200 can run; what runs here is the PTX of image 0, compiled by the driver on
+// first use, or an image a newer compiler built for sm_100.  The quantized path
+// itself does not come through here: its kernels are the custom calls of part 3.
 void ral_kernel_launch(ExecContext* ctx, void** blobs, uint64_t num_blobs, const char* name,
                        int64_t gx, int64_t gy, int64_t gz, int64_t bx, int64_t by, int64_t bz,
                        int32_t smem, void* stream, int32_t num_args, void** params) {
-  ctx->signal_error(std::string("ral_kernel_launch: generated kernel '") + (name ? name : "?") +
-                    "' cannot run here; lower it to a disc_b200_* custom call");
+  if (!gx || !gy || !gz || !bx || !by || !bz) return;  // empty tensor: nothing to launch (:356-359)
+  if (!blobs || !name || num_blobs == 0) {
+    ctx->signal_error("ral_kernel_launch: no device image or no kernel name");
+    return;
+  }
+  if (gx < 0 || gy < 0 || gz < 0 || bx < 0 || by < 0 || bz < 0 || smem < 0 || bx * by * bz > 1024) {
+    ctx->signal_error(std::string("ral_kernel_launch: invalid launch dimensions for ") + name);
+    return;
+  }
+  const CuDriverApi& cu = cu_driver_api();
+  if (!cu.ok) {
+    ctx->signal_error("ral_kernel_launch: CUDA driver unavailable: " + cu.error);
+    return;
+  }
+  Context* c = ctx->ctx;
+  void* function = nullptr;
+  {
+    std::lock_guard<std::mutex> l(c->mu);
+    if (c->cc_major == 0) {
+      cudaFree(nullptr);  // binds the device's primary context to this thread for the driver calls
+      cudaDeviceGetAttribute(&c->cc_major, cudaDevAttrComputeCapabilityMajor, c->device);
+      cudaDeviceGetAttribute(&c->cc_minor, cudaDevAttrComputeCapabilityMinor, c->device);
+    }
+    const int pick = select_blob(num_blobs, c->cc_major, c->cc_minor);
+    const void* image = blobs[pick];
+    auto key = std::make_pair(image, std::string(name));
+    auto it = c->kernels.find(key);
+    if (it == c->kernels.end()) {
+      auto mod = c->modules.find(image);
+      if (mod == c->modules.end()) {
+        void* module = nullptr;
+        const int st = image ? cu.ModuleLoadData(&module, image) : 1;
+        if (st != 0 || !module) {
+          const std::string why = "ral_kernel_launch: ModuleLoad of image " + std::to_string(pick) + " of " +
+                                  std::to_string(num_blobs) + " for kernel '" + name + "': " + cu.describe(st) +
+                                  " (device is sm_" + std::to_string(c->cc_major) + std::to_string(c->cc_minor) +
+                                  "; the image needs code for it or PTX the driver can compile)";
+          if (c->status == 0) {  // mu is held
+            c->status = 1;
+            c->message = why;
+          }
+          return;
+        }
+        mod = c->modules.emplace(image, module).first;
+      }
+      void* fn = nullptr;
+      const int st = cu.ModuleGetFunction(&fn, mod->second, name);
+      if (st != 0 || !fn) {
+        if (c->status == 0) {
+          c->status = 1;
+          c->message = std::string("ral_kernel_launch: GetFunction '") + name + "': " + cu.describe(st);
+        }
+        return;
+      }
+      if (smem > 48 * 1024) cu.FuncSetAttribute(fn, kCuFuncAttrMaxDynamicShared, smem);
+      it = c->kernels.emplace(key, fn).first;
+    }
+    function = it->second;
+  }
+  const int st = cu.LaunchKernel(function, static_cast<unsigned>(gx), static_cast<unsigned>(gy),
+                                 static_cast<unsigned>(gz), static_cast<unsigned>(bx), static_cast<unsigned>(by),
+                                 static_cast<unsigned>(bz), static_cast<unsigned>(smem), stream_of(ctx), params,
+                                 nullptr);
+  if (st != 0) ctx->signal_error(std::string("ral_kernel_launch: LaunchKernel '") + name + "': " + cu.describe(st));
 }
 
 DISC_B200_RAL_API("alloc", "gpu", ral_alloc);

@@ -1,14 +1,13 @@
+#include "context.h"
+
 #include <algorithm>
 #include <cstdlib>
-#include <cstring>
-
-#include "context.h"
-#include "nccl_dyn.h"
-
 #include <cstring>
 #include <map>
 
 #include "abi.h"
+#include "cu_driver_dyn.h"
+#include "nccl_dyn.h"
 
 namespace disc_b200 {
 namespace ral {
@@ -193,6 +192,9 @@ bool Context::comm_info(int* size, int* rank) {
 Context::~Context() {
   for (auto& kv : host_consts) std::free(kv.second.ptr);
   for (void* p : host_persistent) std::free(p);
+  if (!modules.empty() && cu_driver_api().ok) {
+    for (auto& kv : modules) cu_driver_api().ModuleUnload(kv.second);
+  }
   for (void* p : persistent) raw_free(p);
   if (splitk_ws) raw_free(splitk_ws);
   magic = 0;

@@ -12,6 +12,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <map>
 #include <mutex>
 #include <string>
 #include <unordered_map>
@@ -51,6 +52,11 @@ struct Context {
   std::string message;
   std::unordered_set<void*> persistent;  // survive executions, freed with the context
   std::unordered_set<void*> host_persistent;  // the same for host buffers
+  // Generated kernels: image address -> loaded module, (image, name) -> function
+  // (reference: BaseCudaContextState::blobs / kernels, cuda_context_impl.cc:60-75).
+  std::unordered_map<const void*, void*> modules;
+  std::map<std::pair<const void*, std::string>, void*> kernels;
+  int cc_major = 0, cc_minor = 0;  // of `device`, 0 until first asked
   // Scratch of the small-M qgemm path (grown on demand, counters kept zero).
   void* splitk_ws = nullptr;
   int64_t splitk_ws_bytes = 0;

@@ -121,6 +121,7 @@ SIGNATURES = {
     "disc_b200_metadata_write": (c_int32, [c_char_p, c_int32, POINTER(c_char_p), POINTER(c_int32),
                                            POINTER(c_void_p), POINTER(c_int64)]),
     "disc_b200_const_name_info": (c_int32, [c_char_p, POINTER(c_int32), POINTER(c_int64), POINTER(c_int64)]),
+    "disc_b200_select_device_image": (c_int32, [c_int64, c_int32, c_int32]),
     "disc_b200_last_error_string": (c_char_p, []),
     "disc_b200_kernel_status": (c_int32, []),
     "disc_b200_version": (c_char_p, []),

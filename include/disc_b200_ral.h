@@ -357,6 +357,15 @@ int32_t disc_b200_metadata_write(const char* path, int32_t n, const char* const*
 /* Shape (up to 8 dims) and element width encoded in a constant's unique name. */
 int32_t disc_b200_const_name_info(const char* unique_name, int32_t* rank, int64_t* sizes8, int64_t* elem_bytes);
 
+/* ---- Compiler-generated kernels.  ral_kernel_launch (blobs, num_blobs, kernel
+ * name, grid, block, shared memory, stream, params) loads one of the device
+ * images the executable embeds and launches the named kernel
+ * (tao_compiler/mlir/ral/context/base/cuda/cuda_context_impl.cc:348-445).  This is
+ * the reference's choice of image for a device (common_context_impl.cc:209-215:
+ * image 0 carries PTX, images 1..4 are sm_70 / 75 / 80 / 86 code): a B200 gets
+ * image 0 and the driver compiles its PTX.  -1 if there is no image. */
+int32_t disc_b200_select_device_image(int64_t num_images, int32_t cc_major, int32_t cc_minor);
+
 /* ------------------------------------------------------------------------
  * 4. Diagnostics.
  * ---------------------------------------------------------------------- */

@@ -91,3 +91,55 @@ def test_output_ownership_codes(built_lib, tmp_path):
     lib.disc_b200_exec_destroy(ex)
     lib.disc_b200_exec_free_host_output(got[0][3])
     lib.disc_b200_executable_close(exe)
+
+
+def test_device_image_selection(built_lib):
+    """The reference's table (tao_compiler/mlir/ral/context/common_context_impl.cc:209-215,
+    cuda_context_impl.cc:375-395): one image -> it; several -> sm_70/75/80/86 take 1..4 when
+    present, everything else (sm_60, Hopper, Blackwell) the PTX-bearing image 0."""
+    from bladedisc_b200 import lib as L
+    sel = L.load().disc_b200_select_device_image
+    assert sel(0, 10, 0) == -1 and sel(-3, 8, 0) == -1
+    assert sel(1, 8, 0) == 0 and sel(1, 10, 0) == 0
+    assert [sel(5, *cc) for cc in ((7, 0), (7, 5), (8, 0), (8, 6))] == [1, 2, 3, 4]
+    assert [sel(5, *cc) for cc in ((6, 0), (6, 1), (8, 9), (9, 0), (10, 0), (12, 0))] == [0] * 6
+    assert sel(3, 8, 0) == 0 and sel(3, 7, 5) == 2       # an index past the images falls back to 0
+    assert sel(4, 8, 6) == 0 and sel(4, 8, 0) == 3
+
+
+def test_kernel_launch_without_a_driver_reports(built_lib):
+    """No GPU here: an empty launch is skipped silently, a real one is reported, nothing aborts."""
+    from bladedisc_b200 import lib as L
+    lib = L.load()
+    try:
+        ctypes.CDLL("libcuda.so.1")
+        pytest.skip("a CUDA driver is installed on this host")
+    except OSError:
+        pass
+    c = lib.disc_b200_context_create(None)
+    e = lib.disc_b200_exec_create(c)
+    name = b"ral_kernel_launch___gpu___pvoid_ppvoid_i64_pvoid_i64_i64_i64_i64_i64_i64_i32_pvoid_i32_ppvoid___void"
+
+    def launch(grid_x):
+        slot = ctypes.c_void_p(e)
+        image = ctypes.create_string_buffer(b"\x00" * 64)
+        blobs = (ctypes.c_void_p * 1)(ctypes.addressof(image))
+        pblobs = ctypes.c_void_p(ctypes.addressof(blobs))
+        nblobs = ctypes.c_int64(1)
+        kname = ctypes.create_string_buffer(b"axpb")
+        pname = ctypes.c_void_p(ctypes.addressof(kname))
+        dims = [ctypes.c_int64(v) for v in (grid_x, 1, 1, 128, 1, 1)]
+        smem, nargs = ctypes.c_int32(0), ctypes.c_int32(0)
+        stream, params = ctypes.c_void_p(0), ctypes.c_void_p(0)
+        vals = [slot, pblobs, nblobs, pname] + dims + [smem, stream, nargs, params]
+        arr = (ctypes.c_void_p * len(vals))(*[ctypes.addressof(v) for v in vals])
+        buf = ctypes.create_string_buffer(name)
+        lib.tao_ral_call_impl(e, ctypes.cast(buf, ctypes.c_void_p), arr)
+        msg = ctypes.c_char_p()
+        return lib.tao_ral_last_error(c, ctypes.byref(msg)), (msg.value or b"").decode()
+
+    assert launch(0) == (0, "")
+    code, msg = launch(4)
+    assert code != 0 and "CUDA driver unavailable" in msg
+    lib.disc_b200_exec_destroy(e)
+    lib.disc_b200_context_destroy(c)

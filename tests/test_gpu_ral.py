@@ -169,7 +169,7 @@ def test_errors_are_recorded_not_fatal(ral):
                  [MemRefSpec("i8", 2)])
     with pytest.raises(RalError, match="multi-stream not supported"):
         ral.call("ral_gpu_get_stream", "gpu", [("i32", 1)], scalar_result="pvoid")
-    with pytest.raises(RalError, match="cannot run here"):
+    with pytest.raises(RalError, match="no device image"):
         ral.call("ral_kernel_launch", "gpu", [("ppvoid", 0), ("i64", 0), ("pvoid", 0), ("i64", 1), ("i64", 1), ("i64", 1),
                                               ("i64", 1), ("i64", 1), ("i64", 1), ("i32", 0), ("pvoid", 0), ("i32", 0),
                                               ("ppvoid", 0)])
@@ -250,3 +250,58 @@ def test_compiled_executable_stand_in_runs_a_quantized_linear(tmp_path):
                                        fold_out=True)
             assert (q.cpu().numpy() == want).all()
             assert list(dims) == [192, 256] and list(shape) == [m, 192]
+
+
+def _nvcc_image(tmp_path, name, *flags):
+    import subprocess
+    from pathlib import Path
+    src = Path(__file__).parent / "fake_executable" / "generated_kernel.cu"
+    out = tmp_path / name
+    subprocess.run(["nvcc", "-Wno-deprecated-gpu-targets", *flags, "-o", str(out), str(src)], check=True)
+    return out.read_bytes()
+
+
+def test_generated_kernel_launch(ral, tmp_path):
+    """ral_kernel_launch: image selection, module / function cache and launch
+    (cuda_context_impl.cc:348-445).  A B200 takes image 0 of a multi-image executable and
+    the driver compiles its PTX; an image built for sm_100a loads directly; an image with
+    only sm_80 code is refused by the driver at load time and reported as an error."""
+    import ctypes
+    from bladedisc_b200.ral import RalError
+    ptx_image = _nvcc_image(tmp_path, "ptx.fatbin", "-fatbin", "-gencode", "arch=compute_60,code=compute_60")
+    native = _nvcc_image(tmp_path, "native.cubin", "-cubin", "-gencode", "arch=compute_100a,code=sm_100a")
+    ampere = _nvcc_image(tmp_path, "sm80.cubin", "-cubin", "-gencode", "arch=compute_80,code=sm_80")
+    n = 100_000
+    x = torch.randn(n, device="cuda")
+
+    def mapped(images):
+        """Images at fixed addresses, like the data section of an executable."""
+        bufs = [ctypes.create_string_buffer(im, len(im)) for im in images]
+        return bufs, (ctypes.c_void_p * len(bufs))(*[ctypes.addressof(bf) for bf in bufs])
+
+    def launch(section, a, b, grid=None, name=b"axpb"):
+        bufs, blobs = section
+        y = torch.zeros(n, device="cuda")
+        kname = ctypes.create_string_buffer(name)
+        vals = [ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(y.data_ptr()), ctypes.c_float(a), ctypes.c_float(b),
+                ctypes.c_int64(n)]
+        params = (ctypes.c_void_p * len(vals))(*[ctypes.addressof(v) for v in vals])
+        g = (n + 255) // 256 if grid is None else grid
+        ral.call("ral_kernel_launch", "gpu",
+                 [("ppvoid", ctypes.addressof(blobs)), ("i64", len(bufs)), ("pvoid", ctypes.addressof(kname)),
+                  ("i64", g), ("i64", 1), ("i64", 1), ("i64", 256), ("i64", 1), ("i64", 1), ("i32", 0), ("pvoid", 0),
+                  ("i32", len(vals)), ("ppvoid", ctypes.addressof(params))])
+        torch.cuda.synchronize()
+        return y
+
+    one = mapped([native])
+    assert torch.equal(launch(one, 2.0, 1.0), 2.0 * x + 1.0)
+    assert torch.equal(launch(one, -1.0, 0.5), -1.0 * x + 0.5)                      # module and function from the cache
+    five = mapped([ptx_image, ampere, ampere, ampere, ampere])                      # the layout the compiler emits
+    assert torch.equal(launch(five, 3.0, 0.0), 3.0 * x)
+    assert (launch(one, 2.0, 1.0, grid=0) == 0).all()                               # empty launch: skipped
+    with pytest.raises(RalError, match="GetFunction 'nope'"):
+        launch(one, 1.0, 0.0, name=b"nope")
+    with pytest.raises(RalError, match="ModuleLoad of image 0 of 1"):
+        launch(mapped([ampere]), 1.0, 0.0)
+    assert torch.equal(launch(one, 2.0, 1.0), 2.0 * x + 1.0)                        # the context stays usable
