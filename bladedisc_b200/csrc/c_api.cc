@@ -16,6 +16,7 @@
 #include "../../include/disc_b200_ral.h"
 #include "kernels/qgemm.h"
 #include "kernels/rowops.h"
+#include "kernels/woq_gemm.h"
 #include "ral/pdl_attr.h"
 
 namespace {
@@ -491,6 +492,36 @@ int32_t disc_b200_const_name_info(const char* unique_name, int32_t* rank, int64_
   }
   if (elem_bytes) *elem_bytes = width;
   return 0;
+}
+
+int64_t disc_b200_weight_only_qgemm_scratch_bytes(int64_t m, int64_t n, int64_t k) {
+  return disc_b200::woq_gemm_scratch_bytes(m, n, k);
+}
+
+int32_t disc_b200_weight_only_qgemm(const disc_b200_weight_only_qgemm_args* a, void* stream) {
+  if (!a) {
+    g_last_error = "weight-only qgemm: null args";
+    return 1;
+  }
+  disc_b200::WoqGemmParams p;
+  p.x = a->x;
+  p.w = a->w;
+  p.scale = a->scale;
+  p.zp = a->zero_point;
+  p.bias = a->bias;
+  p.out = a->out;
+  p.M = a->m;
+  p.N = a->n;
+  p.K = a->k;
+  p.ldx = a->ldx;
+  p.ldw = a->ldw;
+  p.ldo = a->ldo;
+  p.type = a->type;
+  p.ws = a->scratch;
+  p.ws_bytes = a->scratch_bytes;
+  const char* detail = nullptr;
+  const cudaError_t st = disc_b200::woq_gemm_launch(p, static_cast<cudaStream_t>(stream), &detail);
+  return finish(st, "weight_only_qgemm", detail);
 }
 
 int32_t disc_b200_select_device_image(int64_t num_images, int32_t cc_major, int32_t cc_minor) {

@@ -16,6 +16,7 @@
 
 #include "../kernels/qgemm.h"
 #include "../kernels/rowops.h"
+#include "../kernels/woq_gemm.h"
 #include "abi.h"
 #include "context.h"
 #include "cu_driver_dyn.h"
@@ -1082,6 +1083,97 @@ DISC_B200_REGISTER_CONST_RANKS(int32_t);
 DISC_B200_REGISTER_CONST_RANKS(uint32_t);
 DISC_B200_REGISTER_CONST_RANKS(int64_t);
 DISC_B200_REGISTER_CONST_RANKS(bool);
+
+
+// ------------------------------------------------- 6. weight-only qgemm
+// ral_pdll_weight_only_qgemm(input, weight [K, N] ui8, [bias,] weight_scale [N],
+// weight_zero_point [N]) -> input @ ((weight - zp) * scale) [+ bias]: the call the
+// pattern pytorch_blade/tests/disc/pdl/pdll_files/gpu/weight_only_qgemm.pdll:2-106
+// emits (operand order :27 and :90); f16 is what the reference's weight pass
+// expects, f32 what its front-end test produces
+// (test_torchscipt_to_mhlo/test_quantization.py:501-618).  The weights are used
+// as the pattern leaves them.  weight_should_be_reordered = false means the
+// compiler has already permuted them for its sm_75/80 kernel
+// (disc_transform_weight_data_layout_for_weight_only_gemm.cc): that layout is
+// refused, the pass has to stay off for this runtime.
+template <typename T, int N, bool kBias>
+MemRef<T, N> weight_only_qgemm_impl(ExecContext* ctx, void* stream_handle, MemRef<T, N> input,
+                                    MemRef<uint8_t, 2> weight, const T* bias, int64_t bias_len,
+                                    MemRef<T, 1> scale, MemRef<int32_t, 1> zp, void* custom_attrs) {
+  static_assert(N == 2 || N == 3, "rank 2 or 3 input");
+  int64_t rs[N];
+  int64_t m = 1;
+  for (int i = 0; i < N - 1; ++i) {
+    rs[i] = input.sizes[i];
+    m *= input.sizes[i];
+  }
+  const int64_t k = weight.sizes[0];
+  const int64_t n = weight.sizes[1];
+  rs[N - 1] = n;
+  if (!check_stream_handle(ctx, stream_handle)) return make_memref<T, N>(nullptr, rs);
+  const Attr* at = attrs_of(ctx, custom_attrs);
+  if (!at) return make_memref<T, N>(nullptr, rs);
+  if (!at->get_bool("weight_should_be_reordered", true)) {
+    ctx->signal_error(
+        "ral_pdll_weight_only_qgemm: weights already permuted by the compiler's weight-layout pass are not "
+        "supported; keep weight_should_be_reordered = true (plain [K, N] weights)");
+    return make_memref<T, N>(nullptr, rs);
+  }
+  if (input.sizes[N - 1] != k || scale.sizes[0] != n || zp.sizes[0] != n || (kBias && bias_len != n)) {
+    ctx->signal_error("ral_pdll_weight_only_qgemm: operand extents disagree");
+    return make_memref<T, N>(nullptr, rs);
+  }
+  if (m == 0 || n == 0) return make_memref<T, N>(nullptr, rs);
+  T* out = static_cast<T*>(ctx->alloc(static_cast<size_t>(m * n) * sizeof(T)));
+  auto result = make_memref<T, N>(out, rs);
+  if (!out) return result;
+  WoqGemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.x = input.data;
+  p.w = weight.data;
+  p.scale = scale.data;
+  p.zp = zp.data;
+  p.bias = kBias ? bias : nullptr;
+  p.out = out;
+  p.M = m;
+  p.N = n;
+  p.K = k;
+  p.ldx = k;
+  p.ldw = n;
+  p.ldo = n;
+  p.type = std::is_same_v<T, float> ? kF32 : kF16;
+  p.ws_bytes = woq_gemm_scratch_bytes(m, n, k);
+  p.ws = ctx->ctx->get_splitk_ws(p.ws_bytes);
+  if (!p.ws) {
+    ctx->signal_error("ral_pdll_weight_only_qgemm: scratch allocation failed");
+    return result;
+  }
+  const char* detail = nullptr;
+  const cudaError_t st = woq_gemm_launch(p, stream_of(ctx), &detail);
+  if (st != cudaSuccess) report(ctx, st, "ral_pdll_weight_only_qgemm", detail);
+  return result;
+}
+template <typename T, int N>
+MemRef<T, N> weight_only_qgemm(ExecContext* ctx, void* stream_handle, MemRef<T, N> input,
+                               MemRef<uint8_t, 2> weight, MemRef<T, 1> scale, MemRef<int32_t, 1> zp,
+                               void* custom_attrs) {
+  return weight_only_qgemm_impl<T, N, false>(ctx, stream_handle, input, weight, nullptr, 0, scale, zp, custom_attrs);
+}
+template <typename T, int N>
+MemRef<T, N> weight_only_qgemm_bias(ExecContext* ctx, void* stream_handle, MemRef<T, N> input,
+                                    MemRef<uint8_t, 2> weight, MemRef<T, 1> bias, MemRef<T, 1> scale,
+                                    MemRef<int32_t, 1> zp, void* custom_attrs) {
+  return weight_only_qgemm_impl<T, N, true>(ctx, stream_handle, input, weight, bias.data, bias.sizes[0], scale, zp,
+                                            custom_attrs);
+}
+DISC_B200_RAL_API("ral_pdll_weight_only_qgemm", "gpu", weight_only_qgemm<f16_t, 2>);
+DISC_B200_RAL_API("ral_pdll_weight_only_qgemm", "gpu", weight_only_qgemm<f16_t, 3>);
+DISC_B200_RAL_API("ral_pdll_weight_only_qgemm", "gpu", weight_only_qgemm<float, 2>);
+DISC_B200_RAL_API("ral_pdll_weight_only_qgemm", "gpu", weight_only_qgemm<float, 3>);
+DISC_B200_RAL_API("ral_pdll_weight_only_qgemm", "gpu", weight_only_qgemm_bias<f16_t, 2>);
+DISC_B200_RAL_API("ral_pdll_weight_only_qgemm", "gpu", weight_only_qgemm_bias<f16_t, 3>);
+DISC_B200_RAL_API("ral_pdll_weight_only_qgemm", "gpu", weight_only_qgemm_bias<float, 2>);
+DISC_B200_RAL_API("ral_pdll_weight_only_qgemm", "gpu", weight_only_qgemm_bias<float, 3>);
 
 }  // namespace
 }  // namespace ral

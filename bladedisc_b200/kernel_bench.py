@@ -112,6 +112,29 @@ def bench_qgemm(M, K, N, out_dtype, hbm, tops_peak, iters):
             "tops": tops, "gbs": gbs, "bound": bound, "frac": frac, "sets": n_sets}
 
 
+def bench_weight_only(M, K, N, hbm, iters):
+    """Weight-only linear: algorithmic bytes = the uint8 weights once + activations in and out + per-column vectors."""
+    dev = "cuda"
+    algo_bytes = K * N + 2 * M * K + 2 * M * N + (2 + 4 + 2) * N
+    n_sets = copies_for(algo_bytes)
+    g = torch.Generator(device=dev).manual_seed(M + K + N)
+    sets = []
+    for _ in range(n_sets):
+        x = torch.randn((M, K), dtype=torch.float16, device=dev, generator=g)
+        w = torch.randint(0, 256, (K, N), dtype=torch.uint8, device=dev, generator=g)
+        o = torch.empty((M, N), dtype=torch.float16, device=dev)
+        sets.append((x, w, o))
+    scale = (torch.rand(N, device=dev, generator=g) * 0.02 + 0.002).half()
+    zp = torch.full((N,), 128, dtype=torch.int32, device=dev)
+    bias = torch.randn(N, device=dev, generator=g).half()
+    torch.cuda.synchronize()
+    fns = [(lambda x=x, w=w, o=o: ops.weight_only_qgemm(x, w, scale, zp, bias, out=o)) for x, w, o in sets]
+    ms = time_ms(fns, iters)
+    gbs = algo_bytes / (ms * 1e-3) / 1e9
+    return {"kernel": "weight_only_qgemm", "M": M, "K": K, "N": N, "out": "float16", "us": ms * 1e3,
+            "tops": 2.0 * M * N * K / (ms * 1e-3) / 1e12, "gbs": gbs, "bound": "hbm", "frac": gbs / hbm, "sets": n_sets}
+
+
 def bench_rows(name, rows, cols, dtype, hbm, iters):
     dev = "cuda"
     eb = 2 if dtype == torch.float16 else 4
@@ -205,6 +228,17 @@ def main():
                 r = bench_qgemm(M, K, N, od, hbm, tops_peak, iters)
                 out["rows"].append(r)
                 print(f"{r['kernel']:<16}{M:>6}{K:>6}{N:>7}{r['out']:>9}{r['us']:>10.2f}{r['tops']:>9.1f}{r['gbs']:>9.0f}"
+                      f"{r['bound']:>8}{r['frac']:>7.2f}", flush=True)
+    if not only or any("weight_only" in o for o in only):
+        wo_ms = [1, 4, 16] if args.quick else [1, 2, 4, 8, 16]
+        wo_kns = [(4096, 4096)] if args.quick else [(4096, 4096), (4096, 11008), (11008, 4096), (4096, 12288)]
+        if args.shape:
+            wo_ms, wo_kns = ms_list, kns
+        for K, N in wo_kns:
+            for M in wo_ms:
+                r = bench_weight_only(M, K, N, hbm, 3 if args.eager else 100)
+                out["rows"].append(r)
+                print(f"{r['kernel']:<18}{M:>4}{K:>6}{N:>7}{r['out']:>9}{r['us']:>10.2f}{r['tops']:>9.1f}{r['gbs']:>9.0f}"
                       f"{r['bound']:>8}{r['frac']:>7.2f}", flush=True)
     row_cases = [("quantize", 16384, 768, torch.float32), ("quantize", 16384, 3072, torch.float16),
                  ("dynamic_quantize", 16384, 4096, torch.float16), ("layernorm", 16384, 768, torch.float16),

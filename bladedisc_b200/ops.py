@@ -6,6 +6,7 @@ memory and streams only.  Nothing here computes on the CPU and nothing falls
 back to torch operators.
 """
 import ctypes
+import math
 from typing import Optional, Tuple
 
 import torch
@@ -354,6 +355,45 @@ def quantize_rows(gate: torch.Tensor, row_scale: torch.Tensor, up: Optional[torc
     elif out.dtype != torch.int8 or tuple(out.shape) != tuple(gate.shape) or out.stride(1) != 1:
         raise ValueError("out must be int8 of gate's shape with unit column stride")
     _gated(gate, up, out, row_scale, 1)
+    return out
+
+
+def weight_only_qgemm(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, zero_point: Optional[torch.Tensor] = None,
+                      bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ ((w - zero_point) * scale) + bias`` with ``w`` uint8 ``[K, N]`` (the transposed
+    weight the reference's pattern hands to ``ral_pdll_weight_only_qgemm``), ``scale`` /
+    ``bias`` of ``x``'s dtype (float16 or float32) ``[N]``, ``zero_point`` int32 ``[N]``.
+    Dequantization happens in the kernel; sums are fp32."""
+    x = _cuda(x, "x")
+    w = _cuda(w, "w", torch.uint8)
+    if w.dim() != 2 or x.shape[-1] != w.shape[0]:
+        raise ValueError("w must be [K, N] with K = x.shape[-1]")
+    K, N = w.shape
+    M = math.prod(x.shape[:-1])
+    scale = _cuda(scale, "scale", x.dtype)
+    if scale.numel() != N:
+        raise ValueError("one scale per output column expected")
+    if zero_point is not None:
+        zero_point = _cuda(zero_point, "zero_point", torch.int32)
+        if zero_point.numel() != N:
+            raise ValueError("one zero point per output column expected")
+    if bias is not None:
+        bias = _cuda(bias, "bias", x.dtype)
+        if bias.numel() != N:
+            raise ValueError("one bias per output column expected")
+    if out is None:
+        out = torch.empty(x.shape[:-1] + (N,), dtype=x.dtype, device=x.device)
+    elif out.dtype != x.dtype or not out.is_contiguous() or out.numel() != M * N:
+        raise ValueError("out must be contiguous, of x's dtype and [..., N]")
+    L = _lib.load()
+    a = _lib.WeightOnlyQGemmArgs()
+    a.x, a.w, a.scale, a.zero_point, a.bias, a.out = x.data_ptr(), w.data_ptr(), scale.data_ptr(), _p(zero_point), \
+        _p(bias), out.data_ptr()
+    a.m, a.n, a.k, a.ldx, a.ldw, a.ldo = M, N, K, K, N, N
+    a.type = _etype(x)
+    ws = qgemm_scratch(x.device, L.disc_b200_weight_only_qgemm_scratch_bytes(M, N, K))
+    a.scratch, a.scratch_bytes = ws.data_ptr(), ws.numel()
+    _lib.check(L.disc_b200_weight_only_qgemm(ctypes.byref(a), _stream()))
     return out
 
 

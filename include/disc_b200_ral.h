@@ -299,6 +299,32 @@ int32_t disc_b200_rope_kv_append(void* qkv, void* k_cache, void* v_cache, const 
                                  const float* sin_table, int64_t batch, int64_t seq, int64_t heads, int64_t dim,
                                  int64_t pos0, int64_t cache_len, void* stream);
 
+/* Weight-only quantized linear: out[m, n] = sum_k x[m, k] * (w[k, n] - zp[n]) * scale[n]
+ * + bias[n]; x / scale / bias / out all f32 or all f16 (`type`), w uint8 [K, N]
+ * row-major exactly as the pattern of the reference leaves it (weight_only_qgemm.pdll:2-106;
+ * custom call ral_pdll_weight_only_qgemm, for which the reference has no open kernel),
+ * zero_point int32 [N] or NULL.  Sums are fp32.  Built for a few rows (decode):
+ * up to 16 rows stream the weights once, more rows re-read them per group of 16.
+ * scratch: device memory of at least disc_b200_weight_only_qgemm_scratch_bytes(m, n, k)
+ * bytes whose first 16 KiB are zero before the first use (they are left zero);
+ * may be shared with disc_b200_qgemm's scratch; launches that share it must not
+ * overlap on the GPU. */
+typedef struct disc_b200_weight_only_qgemm_args {
+  const void* x;
+  const uint8_t* w;
+  const void* scale;
+  const int32_t* zero_point;
+  const void* bias; /* may be NULL */
+  void* out;
+  int64_t m, n, k;
+  int64_t ldx, ldw, ldo;
+  int32_t type; /* DISC_B200_F32 / DISC_B200_F16 */
+  void* scratch;
+  int64_t scratch_bytes;
+} disc_b200_weight_only_qgemm_args;
+int64_t disc_b200_weight_only_qgemm_scratch_bytes(int64_t m, int64_t n, int64_t k);
+int32_t disc_b200_weight_only_qgemm(const disc_b200_weight_only_qgemm_args* args, void* stream);
+
 /* softmax(x * scale + mask) over the last axis; lens / mask may be NULL
  * (kStitch softmax; same reference files as above). */
 int32_t disc_b200_softmax(const void* x, void* y, int32_t type, int64_t rows, int64_t cols,

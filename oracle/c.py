@@ -257,3 +257,16 @@ def gathered_layout(x, ranks):
     out = np.empty((ranks, rows, cols // ranks), dtype=x.dtype)
     lib().oracle_gathered_layout(_ptr(x), c_int64(rows), c_int64(cols), c_int64(ranks), c_int64(x.itemsize), _ptr(out))
     return out
+
+
+def weight_only_qgemm(x, w, scale, zp=None, bias=None):
+    """oracle_weight_only_qgemm_f32: x [M, K] float, w uint8 [K, N], scale / bias [N], zp int32 [N] -> float32 [M, N]."""
+    x = _f32(x)
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    m, k = x.shape
+    n = w.shape[1]
+    z = None if zp is None else np.ascontiguousarray(zp, dtype=np.int32)
+    out = np.empty((m, n), dtype=np.float32)
+    lib().oracle_weight_only_qgemm_f32(_ptr(x), _ptr(w), _ptr(_f32(scale)), _ptr(z), _ptr(_f32(bias)), c_int64(m),
+                                       c_int64(n), c_int64(k), _ptr(out))
+    return out

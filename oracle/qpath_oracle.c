@@ -386,3 +386,27 @@ ORACLE_API void oracle_gathered_layout(const void* x, int64_t rows, int64_t cols
     for (int64_t m = 0; m < rows; ++m)
       memcpy(dst + ((r * rows + m) * share) * elem, src + (m * cols + r * share) * elem, (size_t)(share * elem));
 }
+
+/* ---- Weight-only quantized linear.
+ * The reference has the front end and the custom call name but no open kernel
+ * (pytorch_blade/tests/disc/pdl/pdll_files/gpu/weight_only_qgemm.pdll:2-106), so
+ * the definition restated here is the model its tests compile
+ * (pytorch_blade/tests/disc/pdl/test_torchscipt_to_mhlo/test_quantization.py:501-618):
+ *   F.linear(x, fake_quantize_per_channel_affine(weight, scale, zp, 0, 0, 255), bias)
+ * i.e. out[m, n] = sum_k x[m, k] * ((q[k, n] - zp[n]) * scale[n]) + bias[n] with
+ * q the uint8 weight, stored transposed [K, N] as the pattern passes it.  The sum
+ * is taken in double over the exact products x * (q - zp); scale and bias are
+ * applied once, in float.  Pinned to that eager torch model on the CPU in
+ * tests/test_oracle.py; there is no reference kernel output to pin to. */
+ORACLE_API void oracle_weight_only_qgemm_f32(const float* x, const uint8_t* w, const float* scale, const int32_t* zp,
+                                             const float* bias, int64_t m, int64_t n, int64_t k, float* out) {
+  for (int64_t i = 0; i < m; ++i) {
+    for (int64_t j = 0; j < n; ++j) {
+      const int32_t z = zp ? zp[j] : 0;
+      double acc = 0.0;
+      for (int64_t t = 0; t < k; ++t) acc += (double)x[i * k + t] * (double)((int32_t)w[t * n + j] - z);
+      const float v = (float)acc * scale[j];
+      out[i * n + j] = bias ? v + bias[j] : v;
+    }
+  }
+}

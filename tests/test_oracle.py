@@ -226,3 +226,33 @@ def test_decoder_glue_restatements():
     lay = c.gathered_layout(m, 3)
     assert lay.shape == (3, 5, 4) and (lay[1] == m[:, 4:8]).all()
     assert (lay.transpose(1, 0, 2).reshape(5, 12) == m).all()
+
+
+def test_weight_only_restatement_is_the_eager_model_the_reference_compiles():
+    """F.linear over fake_quantize_per_channel_affine(weight, scale, 128, axis 0, 0, 255), the module of
+    pytorch_blade/tests/disc/pdl/test_torchscipt_to_mhlo/test_quantization.py:501-618; the custom call
+    receives the uint8 weight transposed to [K, N], the scales and the zero points."""
+    import torch
+    import torch.nn.functional as F
+    torch.manual_seed(0)
+    for (m, k, n, with_bias) in ((2, 3, 5, False), (2, 3, 5, True), (7, 96, 40, True), (1, 300, 17, False)):
+        weight = torch.randn(n, k)
+        scale = torch.rand(n) * 0.02 + 0.005
+        zp = torch.full((n,), 128, dtype=torch.int32)
+        bias = torch.randn(n) if with_bias else None
+        x = torch.randn(m, k)
+        want = F.linear(x, torch.fake_quantize_per_channel_affine(weight, scale, zp, 0, 0, 255), bias).numpy()
+        q = torch.clamp(torch.round(weight / scale[:, None]) + 128, 0, 255).to(torch.uint8)     # [N, K]
+        got = c.weight_only_qgemm(x.numpy(), q.t().contiguous().numpy(), scale.numpy(), zp.numpy(),
+                                  None if bias is None else bias.numpy())
+        bound = (np.abs(x.numpy()) @ np.abs(q.t().numpy().astype(np.float32) - 128)) * scale.numpy()
+        assert np.all(np.abs(got - want) <= 2e-6 * bound + 1e-6)
+    # zero points other than 128 and a missing zero point
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((3, 33)).astype(np.float32)
+    w = rng.integers(0, 256, (33, 12), dtype=np.uint8)
+    s = (rng.random(12) * 0.1).astype(np.float32)
+    z = rng.integers(0, 256, 12).astype(np.int32)
+    want = (x.astype(np.float64) @ (w.astype(np.float64) - z)) * s
+    assert np.allclose(c.weight_only_qgemm(x, w, s, z), want, rtol=1e-6, atol=1e-6)
+    assert np.allclose(c.weight_only_qgemm(x, w, s), (x.astype(np.float64) @ w.astype(np.float64)) * s, rtol=1e-6)
