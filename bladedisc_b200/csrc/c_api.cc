@@ -494,10 +494,6 @@ int32_t disc_b200_const_name_info(const char* unique_name, int32_t* rank, int64_
   return 0;
 }
 
-int64_t disc_b200_weight_only_qgemm_scratch_bytes(int64_t m, int64_t n, int64_t k) {
-  return disc_b200::woq_gemm_scratch_bytes(m, n, k);
-}
-
 int32_t disc_b200_weight_only_qgemm(const disc_b200_weight_only_qgemm_args* a, void* stream) {
   if (!a) {
     g_last_error = "weight-only qgemm: null args";
@@ -517,8 +513,6 @@ int32_t disc_b200_weight_only_qgemm(const disc_b200_weight_only_qgemm_args* a, v
   p.ldw = a->ldw;
   p.ldo = a->ldo;
   p.type = a->type;
-  p.ws = a->scratch;
-  p.ws_bytes = a->scratch_bytes;
   const char* detail = nullptr;
   const cudaError_t st = disc_b200::woq_gemm_launch(p, static_cast<cudaStream_t>(stream), &detail);
   return finish(st, "weight_only_qgemm", detail);

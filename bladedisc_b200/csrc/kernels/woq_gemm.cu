@@ -1,24 +1,39 @@
 // Weight-only quantized linear for a few rows of activations (see woq_gemm.h).
 //
 // The work is reading K x N bytes of weights once; everything is arranged around
-// that stream:
-//   * a block owns a strip of 32*C columns and a chunk of k rows; its 8 warps take
-//     interleaved groups of U rows, every lane C adjacent columns, so a warp reads
-//     whole 32*C-byte row segments and has U of them in flight per lane;
+// that stream, and around the fact that on the SIMT pipes the cost is counted in
+// instructions per weight byte (a B200 SM issues about 5.5 per byte at full HBM
+// rate):
+//   * a block owns a strip of 128 columns and a chunk of k rows.  A lane loads C
+//     adjacent bytes of one row (C = 16, 8 or 4: the widest the alignment and the
+//     accumulator registers allow), so 128 / C lanes cover the strip's 128-byte
+//     row segment and a warp load spans R = C / 4 rows; wide loads keep the
+//     address arithmetic at a fraction of an instruction per byte;
+//   * no predicates in the loop: rows past K are clamped to the last row (their
+//     activations are staged as zero), lanes past N to column 0 (never stored);
+//   * the loads of the next group of U warp loads are issued before the current
+//     group is consumed, so the memory system never waits for the arithmetic (a
+//     variant that streamed through asynchronous copies into a shared-memory ring
+//     measured the same from 2 rows on and slower for 1 row, and was dropped);
 //   * a byte becomes a float with one byte permute (the byte dropped into the
 //     mantissa of 2^23) and one subtraction of the column's (2^23 + zero point),
-//     which yields w - zp exactly; the activation comes from shared memory as a
-//     warp broadcast; products and sums are fp32, so a product is exact and the
-//     result differs from real arithmetic only by the order of the fp32 sums;
-//   * warps of a block reduce through shared memory; blocks that share a strip
-//     (split over k to fill the GPU) leave fp32 partials in scratch and the last
-//     one to arrive adds them in k order and applies scale and bias, so the
-//     result does not depend on scheduling.
-// Instruction budget per weight byte: 2 + MT (MT = rows of activations, padded to
-// 1/2/4/8/16), against about 5.5 per byte that a B200 SM can issue at full HBM
-// rate: memory-bound up to 4 rows, issue-bound beyond.
+//     which yields w - zp exactly; the activation comes from shared memory;
+//     products and sums are fp32, so a product is exact and the result differs
+//     from real arithmetic only by the order of the fp32 sums;
+//   * the k range is split over the blocks of a thread-block cluster (up to 8) to
+//     fill the GPU.  Lanes that hold different rows of the same columns combine by
+//     shuffles, warps through shared memory, blocks of a cluster through
+//     distributed shared memory: every block leaves its tile in its own shared
+//     memory, and after a cluster barrier each block adds, in rank order, one
+//     slice of the tile and applies scale and bias.  No partial sums travel
+//     through global memory, nothing depends on scheduling, and there is no flag
+//     to wait on (only hardware barriers).
+// Per weight byte: 2 (convert) + MT (multiply-add; MT = rows of activations padded
+// to 1/2/4/8/16) + about 0.3 (loads, addresses): memory-bound up to 2 rows,
+// issue-bound beyond.
 #include "woq_gemm.h"
 
+#include <cooperative_groups.h>
 #include <cuda_fp16.h>
 
 #include <algorithm>
@@ -26,13 +41,15 @@
 #include "rowops.h"
 #include "sm100_ptx.cuh"
 
+namespace cg = cooperative_groups;
+
 namespace disc_b200 {
 namespace {
 
+constexpr int kMaxCluster = 8;  // portable cluster size
+constexpr int kStrip = 128;     // columns per block
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int64_t kCounterBytes = 16 * 1024;
-constexpr int kMaxStrips = static_cast<int>(kCounterBytes / sizeof(int));
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
@@ -53,68 +70,132 @@ __device__ __forceinline__ float byte_plus_magic(uint32_t word) {
   return __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7650u | I));
 }
 
-struct Plan {
-  int mt;       // rows of activations per launch, padded (1, 2, 4, 8, 16)
-  int c;        // columns per lane (8 or 4)
-  int u;        // rows in flight per lane
-  int strips;   // blocks along N
-  int ksplit;   // blocks along K
-  int kc;       // k rows per block, a multiple of kWarps * u
-  bool vec;     // the vector kernel applies (alignment), else the simple kernel
-  size_t smem;
-  int64_t ws_bytes;
+template <int WORDS>
+struct RawVec;
+template <>
+struct RawVec<1> {
+  using type = uint32_t;
+  static __device__ __forceinline__ void split(uint32_t v, uint32_t (&o)[1]) { o[0] = v; }
+};
+template <>
+struct RawVec<2> {
+  using type = uint2;
+  static __device__ __forceinline__ void split(uint2 v, uint32_t (&o)[2]) { o[0] = v.x; o[1] = v.y; }
+};
+template <>
+struct RawVec<4> {
+  using type = uint4;
+  static __device__ __forceinline__ void split(uint4 v, uint32_t (&o)[4]) { o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; }
 };
 
-Plan make_plan(int64_t m, int64_t n, int64_t k, int sm_count) {
+// Bytes per lane and load, and warp loads per group, by rows of activations: the
+// accumulators (MT * C) and two groups of raw words (2 * U * C / 4) have to leave
+// the compiler room to keep the next group's loads in flight across the arithmetic
+// (with 64 accumulators it stopped doing so and exposed the memory latency).
+__host__ __device__ constexpr int widest_for(int mt) { return mt <= 2 ? 16 : mt <= 4 ? 8 : 4; }
+__host__ __device__ constexpr int group_for(int mt, int c) {
+  return c == 16 ? 8 : c == 8 ? 8 : (mt <= 8 ? 16 : 8);
+}
+
+struct Plan {
+  int mt;       // rows of activations per launch, padded (1, 2, 4, 8, 16)
+  int c;        // bytes per lane and load (16, 8 or 4)
+  int strips;   // blocks along N
+  int cluster;  // blocks along K = cluster size (1, 2, 4, 8)
+  int kc;       // k rows per block, a multiple of the rows the block covers per step
+  size_t smem;
+};
+
+Plan make_plan(int64_t m, int64_t n, int64_t k, int align, int sm_count) {
   Plan pl{};
   pl.mt = m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : m <= 8 ? 8 : 16;
-  pl.c = pl.mt <= 4 ? 8 : 4;
-  pl.u = pl.mt <= 4 ? 8 : 16;
-  const int strip_w = 32 * pl.c;
-  pl.strips = static_cast<int>((n + strip_w - 1) / strip_w);
-  const int step = kWarps * pl.u;
-  const int64_t target = static_cast<int64_t>(sm_count) * 3;
-  int64_t ks = std::max<int64_t>(1, (target + pl.strips - 1) / pl.strips);
-  ks = std::min<int64_t>(ks, (k + step - 1) / step);
-  int64_t kc = (k + ks - 1) / ks;
-  kc = (kc + step - 1) / step * step;
+  pl.c = std::min(widest_for(pl.mt), align);
+  pl.strips = static_cast<int>((n + kStrip - 1) / kStrip);
+  const int step = kWarps * (pl.c / 4) * group_for(pl.mt, pl.c);  // rows a block covers per step
+  // How far to split k: two blocks fit an SM; the time is about (waves of blocks) x (rows per
+  // block + a fixed cost worth ~512 rows: launch, staging, the two cluster barriers).
+  const int64_t slots = 2 * static_cast<int64_t>(sm_count);
+  int best = 1;
+  int64_t best_cost = -1;
+  for (int cs = 1; cs <= kMaxCluster; cs *= 2) {
+    if (cs > 1 && k <= static_cast<int64_t>(cs / 2) * step) break;  // every block keeps at least one step
+    const int64_t blocks = static_cast<int64_t>(pl.strips) * cs;
+    const int64_t waves = (blocks + slots - 1) / slots;
+    const int64_t rows = (k + cs - 1) / cs;
+    // fewer blocks than SMs leave SMs idle: count the missing share as extra time
+    const int64_t idle = blocks < sm_count ? (sm_count + blocks - 1) / blocks : 1;
+    const int64_t cost = waves * (rows + 512) * idle;
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = cs;
+    }
+  }
+  pl.cluster = best;
+  int64_t kc = (k + best - 1) / best;
+  kc = std::max<int64_t>(step, (kc + step - 1) / step * step);
   pl.kc = static_cast<int>(kc);
-  pl.ksplit = static_cast<int>((k + kc - 1) / kc);
-  pl.smem = sizeof(float) * (static_cast<size_t>(pl.mt) * pl.kc + static_cast<size_t>(kWarps) * pl.mt * strip_w);
-  pl.ws_bytes = kCounterBytes +
-                (pl.ksplit > 1 ? static_cast<int64_t>(pl.ksplit) * pl.strips * pl.mt * strip_w * 4 : 0);
+  const size_t tile = sizeof(float) * pl.mt * kStrip;
+  const size_t xs = sizeof(float) * pl.mt * pl.kc;
+  const size_t red = sizeof(float) * kWarps * pl.mt * kStrip;
+  pl.smem = tile + std::max(xs, red);
   return pl;
 }
 
-template <typename T, int MT, int C, int U>
-__global__ void __launch_bounds__(kThreads)
-woq_gemm_kernel(WoqGemmParams p, int64_t m0, int kc, int ksplit) {
-  constexpr int STRIP = 32 * C;
+template <typename T, int MT, int C>
+__global__ void __launch_bounds__(kThreads, 2)
+woq_gemm_kernel(WoqGemmParams p, int64_t m0, int kc) {
+  constexpr int U = group_for(MT, C);
   constexpr int WORDS = C / 4;
+  constexpr int LPR = kStrip / C;  // lanes per row segment
+  constexpr int R = 32 / LPR;      // rows per warp load
+  constexpr int TILE = MT * kStrip;
+  using Vec = typename RawVec<WORDS>::type;
   extern __shared__ __align__(16) float woq_smem[];
-  float* xs = woq_smem;                                  // [MT][kc]
-  float* red = woq_smem + static_cast<size_t>(MT) * kc;  // [kWarps][MT][STRIP]
-  __shared__ int last_block;
+  float* tile = woq_smem;        // [MT][128], read by the other blocks of the cluster
+  float* xs = woq_smem + TILE;   // [MT][kc]; reused as red [kWarps][MT][128] after the k loop
+  float* red = xs;
 
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = static_cast<int>(cluster.block_rank());   // == blockIdx.y: the cluster spans y
+  const int csize = static_cast<int>(cluster.num_blocks());
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int strip = blockIdx.x;
-  const int ks = blockIdx.y;
-  const int64_t k_begin = static_cast<int64_t>(ks) * kc;
-  const int64_t n0 = static_cast<int64_t>(strip) * STRIP + lane * C;
+  const int col = (lane % LPR) * C;  // within the strip
+  const int sub = lane / LPR;        // row within a warp load
+  const int k_begin = rank * kc;
+  const int64_t n0 = static_cast<int64_t>(strip) * kStrip + col;
   const bool active = n0 < p.N;  // N is a multiple of C: a lane is wholly inside or outside
   const int rows = static_cast<int>(min(static_cast<int64_t>(MT), p.M - m0));
+  const int last_row = static_cast<int>(p.K) - 1;
+  const uint8_t* wcol = p.w + (active ? n0 : 0);
+
+  // group of U warp loads starting at row kk0 (relative to the chunk) of this warp
+  auto load_group = [&](Vec (&raw)[U], int kk0) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = min(k_begin + kk0 + u * R + sub, last_row);
+      raw[u] = __ldcs(reinterpret_cast<const Vec*>(wcol + static_cast<int64_t>(k) * p.ldw));
+    }
+  };
+
+  // the weights do not depend on the kernel before this one: the first group is on its way
+  // while the activations are staged
+  Vec cur[U];
+  load_group(cur, warp * (R * U));
 
   grid_dep_launch();
   grid_dep_wait();
 
   // activations of this k chunk as fp32; zero beyond M and K, so that padding rows and
-  // the tail of the last chunk add nothing
+  // clamped weight rows add nothing
   const T* x = static_cast<const T*>(p.x);
-  for (int i = threadIdx.x; i < MT * kc; i += kThreads) {
-    const int m = i / kc;
-    const int64_t k = k_begin + (i - m * kc);
-    xs[i] = (m < rows && k < p.K) ? to_f32<T>(x[(m0 + m) * p.ldx + k]) : 0.f;
+#pragma unroll
+  for (int m = 0; m < MT; ++m) {
+    const T* xr = x + (m0 + m) * p.ldx + k_begin;
+    for (int kk = threadIdx.x; kk < kc; kk += kThreads) {
+      xs[m * kc + kk] = (m < rows && k_begin + kk <= last_row) ? to_f32<T>(xr[kk]) : 0.f;
+    }
   }
   float zpm[C];
 #pragma unroll
@@ -129,99 +210,81 @@ woq_gemm_kernel(WoqGemmParams p, int64_t m0, int kc, int ksplit) {
 #pragma unroll
     for (int c = 0; c < C; ++c) acc[m][c] = 0.f;
   }
-  const uint8_t* wcol = p.w + n0;
-  for (int kk0 = warp * U; kk0 < kc; kk0 += kWarps * U) {
-    uint32_t raw[U][WORDS];
+  for (int kk0 = warp * (R * U); kk0 < kc; kk0 += kWarps * R * U) {
+    Vec next[U];
+    if (kk0 + kWarps * R * U < kc) load_group(next, kk0 + kWarps * R * U);  // warp-uniform
+    const float* xrow = xs + kk0 + sub;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int64_t k = k_begin + kk0 + u;
-      if (active && k < p.K) {
-        if constexpr (WORDS == 2) {
-          const uint2 v = __ldcs(reinterpret_cast<const uint2*>(wcol + k * p.ldw));
-          raw[u][0] = v.x;
-          raw[u][1] = v.y;
-        } else {
-          raw[u][0] = __ldcs(reinterpret_cast<const uint32_t*>(wcol + k * p.ldw));
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < WORDS; ++j) raw[u][j] = 0u;
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
+      uint32_t words[WORDS];
+      RawVec<WORDS>::split(cur[u], words);
       float wv[C];
 #pragma unroll
       for (int j = 0; j < WORDS; ++j) {
-        wv[4 * j + 0] = byte_plus_magic<0>(raw[u][j]) - zpm[4 * j + 0];
-        wv[4 * j + 1] = byte_plus_magic<1>(raw[u][j]) - zpm[4 * j + 1];
-        wv[4 * j + 2] = byte_plus_magic<2>(raw[u][j]) - zpm[4 * j + 2];
-        wv[4 * j + 3] = byte_plus_magic<3>(raw[u][j]) - zpm[4 * j + 3];
+        wv[4 * j + 0] = byte_plus_magic<0>(words[j]) - zpm[4 * j + 0];
+        wv[4 * j + 1] = byte_plus_magic<1>(words[j]) - zpm[4 * j + 1];
+        wv[4 * j + 2] = byte_plus_magic<2>(words[j]) - zpm[4 * j + 2];
+        wv[4 * j + 3] = byte_plus_magic<3>(words[j]) - zpm[4 * j + 3];
       }
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
-        const float xv = xs[m * kc + kk0 + u];
+        const float xv = xrow[m * kc + u * R];
 #pragma unroll
         for (int c = 0; c < C; ++c) acc[m][c] = fmaf(xv, wv[c], acc[m][c]);
       }
     }
+#pragma unroll
+    for (int u = 0; u < U; ++u) cur[u] = next[u];
   }
 
-  // warps -> block
+  // lanes that hold other rows of the same columns -> the lanes of the first row
+  if constexpr (R > 1) {
 #pragma unroll
-  for (int m = 0; m < MT; ++m) {
-    float* dst = red + (static_cast<size_t>(warp) * MT + m) * STRIP + lane * C;
+    for (int m = 0; m < MT; ++m) {
 #pragma unroll
-    for (int c = 0; c < C; c += 4) {
-      *reinterpret_cast<float4*>(dst + c) = make_float4(acc[m][c], acc[m][c + 1], acc[m][c + 2], acc[m][c + 3]);
-    }
-  }
-  __syncthreads();
-
-  const T* scale = static_cast<const T*>(p.scale);
-  const T* bias = static_cast<const T*>(p.bias);
-  T* out = static_cast<T*>(p.out);
-  float* partials = reinterpret_cast<float*>(static_cast<uint8_t*>(p.ws) + kCounterBytes);
-  const size_t tile = static_cast<size_t>(MT) * STRIP;
-  float* mine = partials + (static_cast<size_t>(ks) * gridDim.x + strip) * tile;
-  for (int i = threadIdx.x; i < MT * STRIP; i += kThreads) {
-    float v = 0.f;
+      for (int c = 0; c < C; ++c) {
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) v += red[static_cast<size_t>(w) * tile + i];
-    if (ksplit > 1) {
-      mine[i] = v;
-    } else {
-      const int m = i / STRIP;
-      const int64_t n = static_cast<int64_t>(strip) * STRIP + (i - m * STRIP);
-      if (m < rows && n < p.N) {
-        v = v * to_f32<T>(scale[n]) + (bias ? to_f32<T>(bias[n]) : 0.f);
-        out[(m0 + m) * p.ldo + n] = from_f32<T>(v);
+        for (int o = LPR; o < 32; o <<= 1) acc[m][c] += __shfl_xor_sync(0xffffffffu, acc[m][c], o);
       }
     }
   }
-  if (ksplit == 1) return;
-
-  // blocks of a strip -> result: the last block to arrive adds the partials in k order
-  __threadfence();
+  // warps -> block (the activations are no longer needed: their space takes the partials)
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int* counter = static_cast<int*>(p.ws) + strip;
-    const int before = atomicAdd(counter, 1);
-    last_block = before == ksplit - 1;
-    if (last_block) atomicExch(counter, 0);  // everyone has arrived: leave the counter as it was found
+  if (sub == 0) {
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      float* dst = red + (warp * MT + m) * kStrip + col;
+#pragma unroll
+      for (int c = 0; c < C; c += 4) {
+        *reinterpret_cast<float4*>(dst + c) = make_float4(acc[m][c], acc[m][c + 1], acc[m][c + 2], acc[m][c + 3]);
+      }
+    }
   }
   __syncthreads();
-  if (!last_block) return;
-  __threadfence();
-  for (int i = threadIdx.x; i < MT * STRIP; i += kThreads) {
-    const int m = i / STRIP;
-    const int64_t n = static_cast<int64_t>(strip) * STRIP + (i - m * STRIP);
-    if (m >= rows || n >= p.N) continue;
+  for (int i = threadIdx.x; i < TILE; i += kThreads) {
     float v = 0.f;
-    for (int j = 0; j < ksplit; ++j) v += __ldcg(partials + (static_cast<size_t>(j) * gridDim.x + strip) * tile + i);
-    v = v * to_f32<T>(scale[n]) + (bias ? to_f32<T>(bias[n]) : 0.f);
-    out[(m0 + m) * p.ldo + n] = from_f32<T>(v);
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) v += red[w * TILE + i];
+    tile[i] = v;
   }
+
+  // blocks -> result: every block adds its slice of the tile over the cluster, in rank order
+  cluster.sync();
+  const T* scale = static_cast<const T*>(p.scale);
+  const T* bias = static_cast<const T*>(p.bias);
+  T* out = static_cast<T*>(p.out);
+  const int slice = TILE / csize;  // csize is a power of two <= 8, TILE a multiple of 128
+  for (int i = rank * slice + threadIdx.x; i < (rank + 1) * slice; i += kThreads) {
+    const int m = i / kStrip;
+    const int64_t n = static_cast<int64_t>(strip) * kStrip + (i - m * kStrip);
+    float v = 0.f;
+    for (int j = 0; j < csize; ++j) v += cluster.map_shared_rank(tile, j)[i];
+    if (m < rows && n < p.N) {
+      v = v * to_f32<T>(scale[n]) + (bias ? to_f32<T>(bias[n]) : 0.f);
+      out[(m0 + m) * p.ldo + n] = from_f32<T>(v);
+    }
+  }
+  cluster.sync();  // no block leaves while its tile may still be read
 }
 
 // Any shape and alignment: one thread per output element, k in order.
@@ -256,25 +319,52 @@ int sm_count() {
   return n;
 }
 
-template <typename T, int MT, int C, int U>
+template <typename T, int MT, int C>
 cudaError_t launch_tile(const WoqGemmParams& p, int64_t m0, const Plan& pl, cudaStream_t s) {
-  auto kern = woq_gemm_kernel<T, MT, C, U>;
+  auto kern = woq_gemm_kernel<T, MT, C>;
   static bool configured = false;  // per instantiation; the attribute is per function, set once
   if (!configured) {
-    cudaError_t st = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    cudaError_t st = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (st != cudaSuccess) return st;
     configured = true;
   }
-  return launch_dependent(kern, dim3(pl.strips, pl.ksplit), dim3(kThreads), pl.smem, s, p, m0, pl.kc, pl.ksplit);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(pl.strips, pl.cluster);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = 1;
+  attrs[0].val.clusterDim.y = pl.cluster;
+  attrs[0].val.clusterDim.z = 1;
+  attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = 2;
+  return cudaLaunchKernelEx(&cfg, kern, p, m0, pl.kc);
+}
+
+template <typename T, int MT>
+cudaError_t launch_mt(const WoqGemmParams& p, int64_t m0, const Plan& pl, cudaStream_t s) {
+  if constexpr (widest_for(MT) >= 16) {
+    if (pl.c == 16) return launch_tile<T, MT, 16>(p, m0, pl, s);
+  }
+  if constexpr (widest_for(MT) >= 8) {
+    if (pl.c == 8) return launch_tile<T, MT, 8>(p, m0, pl, s);
+  }
+  return launch_tile<T, MT, 4>(p, m0, pl, s);
 }
 
 template <typename T>
 cudaError_t launch_typed(const WoqGemmParams& p, cudaStream_t s, const char** err) {
-  const bool aligned8 = p.N % 8 == 0 && p.ldw % 8 == 0 && reinterpret_cast<uintptr_t>(p.w) % 8 == 0;
-  const bool aligned4 = p.N % 4 == 0 && p.ldw % 4 == 0 && reinterpret_cast<uintptr_t>(p.w) % 4 == 0;
-  if (p.K == 0 || !aligned4 || (p.M <= 4 && !aligned8)) {
+  int align = 16;  // bytes a lane may load at once: columns, row pitch and base all multiples of it
+  while (align >= 4 && (p.N % align != 0 || p.ldw % align != 0 || reinterpret_cast<uintptr_t>(p.w) % align != 0)) {
+    align /= 2;
+  }
+  if (p.K == 0 || align < 4 || p.K > (int64_t{1} << 30)) {
     if (p.M > 65535) {
-      *err = "weight-only qgemm: more than 65535 rows with a weight matrix that is not 8-byte aligned";
+      *err = "weight-only qgemm: more than 65535 rows with a weight matrix that is not 4-byte aligned";
       return cudaErrorInvalidValue;
     }
     return launch_dependent(woq_gemm_simple_kernel<T>, dim3(static_cast<unsigned>((p.N + 255) / 256),
@@ -284,26 +374,18 @@ cudaError_t launch_typed(const WoqGemmParams& p, cudaStream_t s, const char** er
   // more than 16 rows: 16 at a time, the weights re-read for each group
   for (int64_t m0 = 0; m0 < p.M; m0 += 16) {
     const int64_t rows = std::min<int64_t>(16, p.M - m0);
-    const Plan pl = make_plan(rows, p.N, p.K, sm_count());
-    if (pl.strips > kMaxStrips) {
-      *err = "weight-only qgemm: N too large for the arrival counters";
-      return cudaErrorInvalidValue;
-    }
-    if (pl.smem > 160 * 1024) {
-      *err = "weight-only qgemm: k chunk does not fit shared memory";
-      return cudaErrorInvalidValue;
-    }
-    if (pl.ws_bytes > kCounterBytes && (!p.ws || p.ws_bytes < pl.ws_bytes)) {
-      *err = "weight-only qgemm: scratch missing or smaller than woq_gemm_scratch_bytes";
+    const Plan pl = make_plan(rows, p.N, p.K, align, sm_count());
+    if (pl.smem > 200 * 1024) {
+      *err = "weight-only qgemm: K too large for the shared-memory staging of the activations";
       return cudaErrorInvalidValue;
     }
     cudaError_t st;
     switch (pl.mt) {
-      case 1: st = launch_tile<T, 1, 8, 8>(p, m0, pl, s); break;
-      case 2: st = launch_tile<T, 2, 8, 8>(p, m0, pl, s); break;
-      case 4: st = launch_tile<T, 4, 8, 8>(p, m0, pl, s); break;
-      case 8: st = launch_tile<T, 8, 4, 16>(p, m0, pl, s); break;
-      default: st = launch_tile<T, 16, 4, 16>(p, m0, pl, s); break;
+      case 1: st = launch_mt<T, 1>(p, m0, pl, s); break;
+      case 2: st = launch_mt<T, 2>(p, m0, pl, s); break;
+      case 4: st = launch_mt<T, 4>(p, m0, pl, s); break;
+      case 8: st = launch_mt<T, 8>(p, m0, pl, s); break;
+      default: st = launch_mt<T, 16>(p, m0, pl, s); break;
     }
     if (st != cudaSuccess) return st;
   }
@@ -311,17 +393,6 @@ cudaError_t launch_typed(const WoqGemmParams& p, cudaStream_t s, const char** er
 }
 
 }  // namespace
-
-int64_t woq_gemm_scratch_bytes(int64_t M, int64_t N, int64_t K) {
-  if (M <= 0 || N <= 0 || K <= 0) return kCounterBytes;
-  // the device's SM count is not known to a caller without a GPU context: size for the
-  // largest split any B200-class part would choose
-  int64_t worst = kCounterBytes;
-  for (int64_t rows : {std::min<int64_t>(M, 16), M % 16 == 0 ? int64_t{16} : M % 16}) {
-    for (int sms : {148, 160, 192}) worst = std::max(worst, make_plan(rows, N, K, sms).ws_bytes);
-  }
-  return worst;
-}
 
 cudaError_t woq_gemm_launch(const WoqGemmParams& p, cudaStream_t s, const char** err) {
   static const char* none = "";

@@ -11,7 +11,8 @@
 // pre-permutes the weights for a closed sm_75/80 kernel
 // (tao_compiler/mlir/disc/transforms/disc_transform_weight_data_layout_for_weight_only_gemm.cc:36-110).
 // Here the weights stay in the plain [K, N] row-major layout the pattern
-// produces: a warp reads whole rows, which is already the best HBM pattern.
+// produces: a warp reads whole row segments, which is already the best HBM pattern.
+// Needs no scratch memory: partial sums are exchanged inside thread-block clusters.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -28,14 +29,10 @@ struct WoqGemmParams {
   int64_t M, N, K;
   int64_t ldx, ldw, ldo;
   int type;             // ElemType of rowops.h: 0 = f32, 1 = f16
-  // Device scratch of at least woq_gemm_scratch_bytes(M, N, K) bytes.  Its first
-  // 16 KiB are arrival counters: zero before the first use, left zero; launches
-  // that share it must not overlap on the GPU.
-  void* ws;
-  int64_t ws_bytes;
 };
 
-int64_t woq_gemm_scratch_bytes(int64_t M, int64_t N, int64_t K);
+// The weights are constants of the model: the kernel may start reading them before
+// the kernel launched ahead of it on the stream has finished.
 cudaError_t woq_gemm_launch(const WoqGemmParams& p, cudaStream_t s, const char** err);
 
 }  // namespace disc_b200

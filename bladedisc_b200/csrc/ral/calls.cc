@@ -235,14 +235,21 @@ DISC_B200_REGISTER_IO_RANKS(bool);
 
 // ------------------------------------------------------------ attr cache
 struct AttrCache {
+  struct Entry {
+    std::unique_ptr<Attr> attr;
+    std::string bytes;  // the blob as it was when parsed
+  };
   std::mutex mu;
-  std::unordered_map<void*, std::unique_ptr<Attr>> map;
+  std::unordered_map<void*, Entry> map;
+  std::vector<std::unique_ptr<Attr>> retired;  // replaced entries stay alive: a caller may still hold one
 };
 AttrCache& attr_cache() {
   static AttrCache* c = new AttrCache;
   return *c;
 }
-// Parsed once per blob address, like the reference (pdll_util.h:190-220).
+// Parsed once per blob address, like the reference (pdll_util.h:190-220).  In a
+// compiled executable a blob is constant data; a host that builds blobs at run
+// time may reuse an address for other content, so a hit also compares the bytes.
 const Attr* attrs_of(ExecContext* ctx, void* blob) {
   static const Attr kEmpty = [] {
     Attr a;
@@ -253,16 +260,25 @@ const Attr* attrs_of(ExecContext* ctx, void* blob) {
   AttrCache& c = attr_cache();
   std::lock_guard<std::mutex> l(c.mu);
   auto it = c.map.find(blob);
-  if (it == c.map.end()) {
-    const uint8_t* cur = static_cast<const uint8_t*>(blob);
-    auto a = parse_attr(&cur);
-    if (!a || a->kind != Attr::kDict) {
-      ctx->signal_error("fail to parse custom_attrs");
-      return nullptr;
-    }
-    it = c.map.emplace(blob, std::move(a)).first;
+  if (it != c.map.end() && std::memcmp(blob, it->second.bytes.data(), it->second.bytes.size()) == 0) {
+    return it->second.attr.get();
   }
-  return it->second.get();
+  const uint8_t* cur = static_cast<const uint8_t*>(blob);
+  auto a = parse_attr(&cur);
+  if (!a || a->kind != Attr::kDict) {
+    ctx->signal_error("fail to parse custom_attrs");
+    return nullptr;
+  }
+  AttrCache::Entry e;
+  e.attr = std::move(a);
+  e.bytes.assign(static_cast<const char*>(blob), static_cast<size_t>(cur - static_cast<const uint8_t*>(blob)));
+  if (it != c.map.end()) {
+    c.retired.push_back(std::move(it->second.attr));
+    it->second = std::move(e);
+  } else {
+    it = c.map.emplace(blob, std::move(e)).first;
+  }
+  return it->second.attr.get();
 }
 
 // ---------------------------------------------------- 2. reference qgemm
@@ -1142,12 +1158,6 @@ MemRef<T, N> weight_only_qgemm_impl(ExecContext* ctx, void* stream_handle, MemRe
   p.ldw = n;
   p.ldo = n;
   p.type = std::is_same_v<T, float> ? kF32 : kF16;
-  p.ws_bytes = woq_gemm_scratch_bytes(m, n, k);
-  p.ws = ctx->ctx->get_splitk_ws(p.ws_bytes);
-  if (!p.ws) {
-    ctx->signal_error("ral_pdll_weight_only_qgemm: scratch allocation failed");
-    return result;
-  }
   const char* detail = nullptr;
   const cudaError_t st = woq_gemm_launch(p, stream_of(ctx), &detail);
   if (st != cudaSuccess) report(ctx, st, "ral_pdll_weight_only_qgemm", detail);

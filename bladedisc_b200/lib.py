@@ -77,7 +77,6 @@ class WeightOnlyQGemmArgs(Structure):
         ("x", c_void_p), ("w", c_void_p), ("scale", c_void_p), ("zero_point", c_void_p), ("bias", c_void_p),
         ("out", c_void_p), ("m", c_int64), ("n", c_int64), ("k", c_int64),
         ("ldx", c_int64), ("ldw", c_int64), ("ldo", c_int64), ("type", c_int32),
-        ("scratch", c_void_p), ("scratch_bytes", c_int64),
     ]
 
 
@@ -130,7 +129,6 @@ SIGNATURES = {
     "disc_b200_metadata_write": (c_int32, [c_char_p, c_int32, POINTER(c_char_p), POINTER(c_int32),
                                            POINTER(c_void_p), POINTER(c_int64)]),
     "disc_b200_const_name_info": (c_int32, [c_char_p, POINTER(c_int32), POINTER(c_int64), POINTER(c_int64)]),
-    "disc_b200_weight_only_qgemm_scratch_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "disc_b200_weight_only_qgemm": (c_int32, [POINTER(WeightOnlyQGemmArgs), c_void_p]),
     "disc_b200_select_device_image": (c_int32, [c_int64, c_int32, c_int32]),
     "disc_b200_last_error_string": (c_char_p, []),

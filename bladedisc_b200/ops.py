@@ -391,8 +391,6 @@ def weight_only_qgemm(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, zer
         _p(bias), out.data_ptr()
     a.m, a.n, a.k, a.ldx, a.ldw, a.ldo = M, N, K, K, N, N
     a.type = _etype(x)
-    ws = qgemm_scratch(x.device, L.disc_b200_weight_only_qgemm_scratch_bytes(M, N, K))
-    a.scratch, a.scratch_bytes = ws.data_ptr(), ws.numel()
     _lib.check(L.disc_b200_weight_only_qgemm(ctypes.byref(a), _stream()))
     return out
 

@@ -305,10 +305,8 @@ int32_t disc_b200_rope_kv_append(void* qkv, void* k_cache, void* v_cache, const 
  * custom call ral_pdll_weight_only_qgemm, for which the reference has no open kernel),
  * zero_point int32 [N] or NULL.  Sums are fp32.  Built for a few rows (decode):
  * up to 16 rows stream the weights once, more rows re-read them per group of 16.
- * scratch: device memory of at least disc_b200_weight_only_qgemm_scratch_bytes(m, n, k)
- * bytes whose first 16 KiB are zero before the first use (they are left zero);
- * may be shared with disc_b200_qgemm's scratch; launches that share it must not
- * overlap on the GPU. */
+ * No scratch memory.  w holds constants of the model: the kernel may read it
+ * before the preceding kernel on the stream has finished. */
 typedef struct disc_b200_weight_only_qgemm_args {
   const void* x;
   const uint8_t* w;
@@ -319,10 +317,7 @@ typedef struct disc_b200_weight_only_qgemm_args {
   int64_t m, n, k;
   int64_t ldx, ldw, ldo;
   int32_t type; /* DISC_B200_F32 / DISC_B200_F16 */
-  void* scratch;
-  int64_t scratch_bytes;
 } disc_b200_weight_only_qgemm_args;
-int64_t disc_b200_weight_only_qgemm_scratch_bytes(int64_t m, int64_t n, int64_t k);
 int32_t disc_b200_weight_only_qgemm(const disc_b200_weight_only_qgemm_args* args, void* stream);
 
 /* softmax(x * scale + mask) over the last axis; lens / mask may be NULL
