@@ -28,13 +28,15 @@ SOURCES = [
     "ral/pdl_attr.cc",
     "ral/nccl_dyn.cc",
     "kernels/woq_gemm.cu",
+    "kernels/qconv.cu",
+    "ral/conv_plan.cc",
     "ral/metadata.cc",
     "ral/cu_driver_dyn.cc",
     "ral/calls.cc",
     "c_api.cc",
 ]
 HEADERS = [
-    "kernels/qgemm.h", "kernels/rowops.h", "kernels/woq_gemm.h", "kernels/sm100_ptx.cuh",
+    "kernels/qgemm.h", "kernels/rowops.h", "kernels/woq_gemm.h", "kernels/qconv.h", "ral/conv_plan.h", "kernels/sm100_ptx.cuh",
     "kernels/qgemm_pair.inl", "kernels/qgemm_gemv.inl", "kernels/qgemm_skinny.inl",
     "kernels/rownorm_staged.inl",
     "ral/abi.h", "ral/context.h", "ral/pdl_attr.h", "ral/nccl_dyn.h", "ral/metadata.h", "ral/cu_driver_dyn.h",

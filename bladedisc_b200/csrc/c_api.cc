@@ -10,10 +10,12 @@
 #include <vector>
 
 #include "ral/context.h"
+#include "ral/conv_plan.h"
 #include "ral/cu_driver_dyn.h"
 #include "ral/metadata.h"
 #include "ral/nccl_dyn.h"
 #include "../../include/disc_b200_ral.h"
+#include "kernels/qconv.h"
 #include "kernels/qgemm.h"
 #include "kernels/rowops.h"
 #include "kernels/woq_gemm.h"
@@ -516,6 +518,70 @@ int32_t disc_b200_weight_only_qgemm(const disc_b200_weight_only_qgemm_args* a, v
   const char* detail = nullptr;
   const cudaError_t st = disc_b200::woq_gemm_launch(p, static_cast<cudaStream_t>(stream), &detail);
   return finish(st, "weight_only_qgemm", detail);
+}
+
+namespace {
+// geometry of a direct call; fills g or returns the reason it cannot
+std::string geometry_of(const disc_b200_qconv2d_args* a, disc_b200::ConvGeometry* g) {
+  return disc_b200::ral::conv2d_geometry(a->input_sizes, a->kernel_sizes, a->output_sizes, a->padding, a->metadata, 16,
+                                         g);
+}
+}  // namespace
+
+int32_t disc_b200_qconv2d_plan(const char* data_format, const int64_t* strides, int32_t n_strides,
+                               const int64_t* dilations, int32_t n_dilations, const char* padding,
+                               const int64_t* explicit_paddings, int32_t n_explicit, int32_t weight_is_const,
+                               const int64_t* input_sizes4, const int64_t* weight_sizes4, int32_t* padding_out4,
+                               int64_t* result_sizes4, int32_t* metadata_out17) {
+  if (!data_format || !padding || !input_sizes4 || !weight_sizes4 || !padding_out4 || !result_sizes4 ||
+      !metadata_out17 || n_strides < 0 || n_dilations < 0 || n_explicit < 0 || (n_strides > 0 && !strides) ||
+      (n_dilations > 0 && !dilations) || (n_explicit > 0 && !explicit_paddings)) {
+    g_last_error = "qconv2d_plan: null argument";
+    return 1;
+  }
+  const std::string why = disc_b200::ral::plan_conv2d_from_attrs(
+      data_format, std::vector<int64_t>(strides, strides + n_strides),
+      std::vector<int64_t>(dilations, dilations + n_dilations), padding,
+      std::vector<int64_t>(explicit_paddings, explicit_paddings + n_explicit), weight_is_const != 0, input_sizes4,
+      weight_sizes4, padding_out4, result_sizes4, metadata_out17);
+  if (!why.empty()) {
+    g_last_error = why;
+    return 1;
+  }
+  return 0;
+}
+
+int64_t disc_b200_qconv2d_workspace_bytes(const disc_b200_qconv2d_args* a) {
+  disc_b200::ConvGeometry g;
+  if (!a || !geometry_of(a, &g).empty()) return -1;
+  return disc_b200::qconv_workspace_bytes(g);
+}
+
+int32_t disc_b200_qconv2d(const disc_b200_qconv2d_args* a, void* stream) {
+  if (!a) {
+    g_last_error = "qconv2d: null args";
+    return 1;
+  }
+  disc_b200::QConvParams p;
+  const std::string why = geometry_of(a, &p.g);
+  if (!why.empty()) {
+    g_last_error = "qconv2d: " + why;
+    return 1;
+  }
+  p.x = a->x;
+  p.w = a->w;
+  p.out = a->out;
+  p.x_scale = a->x_scale;
+  p.w_scale = a->w_scale;
+  p.w_scale_per_channel = a->w_scale_per_channel;
+  p.out_scale = a->out_scale;
+  p.workspace = a->workspace;
+  p.workspace_bytes = a->workspace_bytes;
+  p.splitk_ws = static_cast<int32_t*>(a->splitk_ws);
+  p.splitk_ws_bytes = a->splitk_ws_bytes;
+  const char* detail = nullptr;
+  const cudaError_t st = disc_b200::qconv_launch(p, static_cast<cudaStream_t>(stream), &detail);
+  return finish(st, "qconv2d", detail);
 }
 
 int32_t disc_b200_select_device_image(int64_t num_images, int32_t cc_major, int32_t cc_minor) {

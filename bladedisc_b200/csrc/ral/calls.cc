@@ -14,11 +14,13 @@
 #include <memory>
 #include <tuple>
 
+#include "../kernels/qconv.h"
 #include "../kernels/qgemm.h"
 #include "../kernels/rowops.h"
 #include "../kernels/woq_gemm.h"
 #include "abi.h"
 #include "context.h"
+#include "conv_plan.h"
 #include "cu_driver_dyn.h"
 #include "nccl_dyn.h"
 #include "pdl_attr.h"
@@ -1184,6 +1186,125 @@ DISC_B200_RAL_API("ral_pdll_weight_only_qgemm", "gpu", weight_only_qgemm_bias<f1
 DISC_B200_RAL_API("ral_pdll_weight_only_qgemm", "gpu", weight_only_qgemm_bias<f16_t, 3>);
 DISC_B200_RAL_API("ral_pdll_weight_only_qgemm", "gpu", weight_only_qgemm_bias<float, 2>);
 DISC_B200_RAL_API("ral_pdll_weight_only_qgemm", "gpu", weight_only_qgemm_bias<float, 3>);
+
+
+// ------------------------------------------------------ 7. quantized conv
+// Runs the convolution described by `geo` into `out` (device, preallocated).
+bool run_qconv(ExecContext* ctx, const ConvGeometry& geo, const int8_t* x, const int8_t* w, int8_t* out,
+               const float* x_scale, const float* w_scale, bool per_channel, const float* out_scale,
+               const char* what) {
+  QConvParams p;
+  p.g = geo;
+  p.x = x;
+  p.w = w;
+  p.out = out;
+  p.x_scale = x_scale;
+  p.w_scale = w_scale;
+  p.w_scale_per_channel = per_channel ? 1 : 0;
+  p.out_scale = out_scale;
+  p.workspace_bytes = qconv_workspace_bytes(geo);
+  p.workspace = ctx->alloc(static_cast<size_t>(p.workspace_bytes));
+  if (!p.workspace) return false;
+  p.splitk_ws = nullptr;
+  p.splitk_ws_bytes = 0;
+  const int64_t rows = geo.batch * geo.out_h * geo.out_w;
+  if (rows <= 128) {
+    const int64_t kp = (geo.k_h * geo.k_w * geo.in_ch + 15) / 16 * 16;
+    p.splitk_ws = static_cast<int32_t*>(ctx->ctx->get_splitk_ws(qgemm_splitk_ws_bytes(rows, geo.out_ch, kp)));
+    p.splitk_ws_bytes = p.splitk_ws ? ctx->ctx->splitk_ws_bytes : 0;
+  }
+  const char* detail = nullptr;
+  const cudaError_t st = qconv_launch(p, stream_of(ctx), &detail);
+  // the allocator hands the block out again only to work queued behind these kernels
+  ctx->dealloc(p.workspace);
+  if (st != cudaSuccess) {
+    report(ctx, st, what, detail);
+    return false;
+  }
+  return true;
+}
+
+// ral_qconv on "gpu" with the reference's operands
+// (tao_compiler/mlir/ral/context/stream_executor_based_impl.cc:1832-1950): output
+// preallocated by the caller, padding and metadata in host memory, scales on the
+// device.  Like the reference it uses one weight scale (the first) and ignores the
+// zero points; unlike it, nothing is read back to the host.
+void ral_qconv(ExecContext* ctx, void* stream_handle, MemRef<int8_t, 4> input, MemRef<int8_t, 4> kernel,
+               MemRef<int32_t, 1> padding, MemRef<float, 0> input_scale, MemRef<int32_t, 0> input_zp,
+               MemRef<float, 1> weight_scale, MemRef<int32_t, 1> weight_zp, MemRef<float, 0> result_scale,
+               MemRef<int32_t, 0> result_zp, MemRef<int8_t, 4> output, MemRef<int32_t, 1> metadata) {
+  if (!check_stream_handle(ctx, stream_handle)) return;
+  if (memref_numel(input) == 0 || memref_numel(kernel) == 0 || memref_numel(output) == 0) return;
+  if (padding.sizes[0] != 4 || !padding.data || !metadata.data) {
+    ctx->signal_error("ral_qconv: invalid conv params");
+    return;
+  }
+  ConvGeometry geo;
+  const std::string why = conv2d_geometry(input.sizes, kernel.sizes, output.sizes, padding.data, metadata.data,
+                                          metadata.sizes[0], &geo);
+  if (!why.empty()) {
+    ctx->signal_error("ral_qconv: " + why);
+    return;
+  }
+  run_qconv(ctx, geo, input.data, kernel.data, output.data, input_scale.data, weight_scale.data, false,
+            result_scale.data, "ral_qconv");
+}
+DISC_B200_RAL_API("ral_qconv", "gpu", ral_qconv);
+
+// ral_pdll_qconv2d with the operands and attributes of the reference's pattern
+// (tao_compiler/mlir/disc/tests/pdll/data/quantized_conv2d_i8.pdll; implementation
+// for aarch64 hosts: common_context_impl_quantization.cc:363-607): kernel
+// [out, y, x, in], per-channel weight scales, attributes data_format / strides /
+// dilations / padding / explicit_paddings / weight_is_const; the result is
+// allocated here.  The reference registers it on "cpu" only; this is the same
+// call for device tensors.
+MemRef<int8_t, 4> pdll_qconv2d(ExecContext* ctx, void* stream_handle, MemRef<int8_t, 4> input,
+                               MemRef<int8_t, 4> weight, MemRef<float, 0> input_scale,
+                               MemRef<int32_t, 0> input_zp, MemRef<float, 1> weight_scale,
+                               MemRef<int32_t, 1> weight_zp, MemRef<float, 0> result_scale,
+                               MemRef<int32_t, 0> result_zp, void* custom_attrs) {
+  int64_t zeros[4] = {0, 0, 0, 0};
+  auto none = make_memref<int8_t, 4>(nullptr, zeros);
+  if (!check_stream_handle(ctx, stream_handle)) return none;
+  if (memref_numel(input) == 0 || memref_numel(weight) == 0) return none;
+  const Attr* at = attrs_of(ctx, custom_attrs);
+  if (!at) return none;
+  auto ints = [&](const char* key) {
+    const Attr* a = at->find(key);
+    return a && a->kind == Attr::kIntArray ? a->ints : std::vector<int64_t>();
+  };
+  int32_t padding[4];
+  int32_t metadata[17];
+  int64_t result_sizes[4];
+  const std::string why = plan_conv2d_from_attrs(at->get_str("data_format", "NHWC"), ints("strides"), ints("dilations"),
+                                                 at->get_str("padding", ""), ints("explicit_paddings"),
+                                                 at->get_bool("weight_is_const", false), input.sizes, weight.sizes,
+                                                 padding, result_sizes, metadata);
+  if (!why.empty()) {
+    ctx->signal_error("ral_pdll_qconv2d: " + why);
+    return none;
+  }
+  ConvGeometry geo;
+  const std::string bad = conv2d_geometry(input.sizes, weight.sizes, result_sizes, padding, metadata, 17, &geo);
+  if (!bad.empty()) {
+    ctx->signal_error("ral_pdll_qconv2d: " + bad);
+    return none;
+  }
+  if (weight_scale.sizes[0] != geo.out_ch && weight_scale.sizes[0] != 1) {
+    ctx->signal_error("ral_pdll_qconv2d: one weight scale per output channel (or one in all) expected");
+    return none;
+  }
+  int64_t total = 1;
+  for (int i = 0; i < 4; ++i) total *= result_sizes[i];
+  if (total == 0) return make_memref<int8_t, 4>(nullptr, result_sizes);
+  int8_t* out = static_cast<int8_t*>(ctx->alloc(static_cast<size_t>(total)));
+  auto result = make_memref<int8_t, 4>(out, result_sizes);
+  if (!out) return result;
+  run_qconv(ctx, geo, input.data, weight.data, out, input_scale.data, weight_scale.data,
+            weight_scale.sizes[0] == geo.out_ch && geo.out_ch > 1, result_scale.data, "ral_pdll_qconv2d");
+  return result;
+}
+DISC_B200_RAL_API("ral_pdll_qconv2d", "gpu", pdll_qconv2d);
 
 }  // namespace
 }  // namespace ral

@@ -80,6 +80,16 @@ class WeightOnlyQGemmArgs(Structure):
     ]
 
 
+class QConv2dArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("w", c_void_p), ("out", c_void_p),
+        ("input_sizes", c_int64 * 4), ("kernel_sizes", c_int64 * 4), ("output_sizes", c_int64 * 4),
+        ("padding", c_int32 * 4), ("metadata", c_int32 * 16),
+        ("x_scale", c_void_p), ("w_scale", c_void_p), ("w_scale_per_channel", c_int32), ("out_scale", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_int64), ("splitk_ws", c_void_p), ("splitk_ws_bytes", c_int64),
+    ]
+
+
 # name -> (restype, argtypes): every function include/disc_b200_ral.h declares.
 SIGNATURES = {
     "tao_ral_call_impl": (None, [c_void_p, c_void_p, POINTER(c_void_p)]),
@@ -130,6 +140,11 @@ SIGNATURES = {
                                            POINTER(c_void_p), POINTER(c_int64)]),
     "disc_b200_const_name_info": (c_int32, [c_char_p, POINTER(c_int32), POINTER(c_int64), POINTER(c_int64)]),
     "disc_b200_weight_only_qgemm": (c_int32, [POINTER(WeightOnlyQGemmArgs), c_void_p]),
+    "disc_b200_qconv2d_workspace_bytes": (c_int64, [POINTER(QConv2dArgs)]),
+    "disc_b200_qconv2d": (c_int32, [POINTER(QConv2dArgs), c_void_p]),
+    "disc_b200_qconv2d_plan": (c_int32, [c_char_p, POINTER(c_int64), c_int32, POINTER(c_int64), c_int32, c_char_p,
+                                         POINTER(c_int64), c_int32, c_int32, POINTER(c_int64), POINTER(c_int64),
+                                         POINTER(c_int32), POINTER(c_int64), POINTER(c_int32)]),
     "disc_b200_select_device_image": (c_int32, [c_int64, c_int32, c_int32]),
     "disc_b200_last_error_string": (c_char_p, []),
     "disc_b200_kernel_status": (c_int32, []),

@@ -395,6 +395,63 @@ def weight_only_qgemm(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, zer
     return out
 
 
+def qconv2d_plan(data_format: str, input_shape, weight_shape, strides=(1,), dilations=(1,), padding="VALID",
+                 explicit_paddings=(), weight_is_const: bool = True):
+    """(padding (top, bottom, left, right), result shape, metadata) of a quantized convolution from the
+    attributes of ``ral_pdll_qconv2d``; host only."""
+    L = _lib.load()
+    arr = lambda v: (ctypes.c_int64 * max(len(v), 1))(*[int(i) for i in v])
+    pad = (ctypes.c_int32 * 4)()
+    res = (ctypes.c_int64 * 4)()
+    meta = (ctypes.c_int32 * 17)()
+    _lib.check(L.disc_b200_qconv2d_plan(data_format.encode(), arr(strides), len(strides), arr(dilations),
+                                        len(dilations), padding.encode(), arr(explicit_paddings),
+                                        len(explicit_paddings), 1 if weight_is_const else 0, arr(input_shape),
+                                        arr(weight_shape), pad, res, meta))
+    return tuple(pad), tuple(res), tuple(meta)
+
+
+def qconv2d(x: torch.Tensor, w: torch.Tensor, x_scale: torch.Tensor, w_scale: torch.Tensor, out_scale: torch.Tensor,
+            data_format: str = "NHWC", strides=(1,), dilations=(1,), padding="VALID",
+            explicit_paddings=()) -> torch.Tensor:
+    """int8 convolution ``sat(rne(conv(x, w) * (x_scale * w_scale / out_scale)))``: ``x`` int8 in ``data_format``,
+    ``w`` int8 ``[out, y, x, in]``, scales float32 CUDA tensors (``w_scale``: one value or one per output
+    channel); ``padding`` "SAME" | "VALID" | "EXPLICIT" with the reference's rules."""
+    x = _cuda(x, "x", torch.int8)
+    w = _cuda(w, "w", torch.int8)
+    if x.dim() != 4 or w.dim() != 4:
+        raise ValueError("rank-4 input and kernel expected")
+    x_scale, w_scale, out_scale = (_cuda(t, n, torch.float32) for t, n in
+                                   ((x_scale, "x_scale"), (w_scale, "w_scale"), (out_scale, "out_scale")))
+    pad, res, meta = qconv2d_plan(data_format, x.shape, w.shape, strides, dilations, padding, explicit_paddings)
+    out = torch.empty(res, dtype=torch.int8, device=x.device)
+    if out.numel() == 0 or x.numel() == 0:
+        return out
+    if w_scale.numel() not in (1, w.shape[0]):
+        raise ValueError("w_scale must hold one value or one per output channel")
+    L = _lib.load()
+    a = _lib.QConv2dArgs()
+    a.x, a.w, a.out = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    a.input_sizes[:] = list(x.shape)
+    a.kernel_sizes[:] = list(w.shape)
+    a.output_sizes[:] = list(res)
+    a.padding[:] = list(pad)
+    a.metadata[:] = list(meta[:16])
+    a.x_scale, a.w_scale, a.out_scale = x_scale.data_ptr(), w_scale.data_ptr(), out_scale.data_ptr()
+    a.w_scale_per_channel = 1 if w_scale.numel() > 1 else 0
+    need = L.disc_b200_qconv2d_workspace_bytes(ctypes.byref(a))
+    if need < 0:
+        raise ValueError("shapes, padding and metadata do not describe a convolution (one group only)")
+    work = torch.empty(need, dtype=torch.uint8, device=x.device)
+    rows = out.numel() // w.shape[0]
+    kp = (w.shape[1] * w.shape[2] * w.shape[3] + 15) // 16 * 16
+    ws = qgemm_scratch(x.device, L.disc_b200_qgemm_scratch_bytes(rows, w.shape[0], kp))
+    a.workspace, a.workspace_bytes = work.data_ptr(), need
+    a.splitk_ws, a.splitk_ws_bytes = ws.data_ptr(), ws.numel()
+    _lib.check(L.disc_b200_qconv2d(ctypes.byref(a), _stream()))
+    return out
+
+
 def softmax(x: torch.Tensor, scale: float = 1.0, lens: Optional[torch.Tensor] = None,
             mask: Optional[torch.Tensor] = None, log: bool = False) -> torch.Tensor:
     """softmax(x * scale + mask) over the last axis.

@@ -320,6 +320,51 @@ typedef struct disc_b200_weight_only_qgemm_args {
 } disc_b200_weight_only_qgemm_args;
 int32_t disc_b200_weight_only_qgemm(const disc_b200_weight_only_qgemm_args* args, void* stream);
 
+/* Quantized 2-D convolution, int8 x int8 -> int8, symmetric:
+ *   out = sat_s8(rne( conv(x, w) * (x_scale * w_scale(o) / out_scale) ))
+ * (ral_qconv on "gpu": tao_compiler/mlir/ral/context/stream_executor_based_impl.cc:1832-1950;
+ * ral_pdll_qconv2d: common_context_impl_quantization.cc:363-607).  Operands are dense
+ * row-major tensors of rank 4 whose dimension roles come from `metadata`, in the
+ * reference's order (stream_executor_based_impl.cc:1127-1152): input (batch, channel,
+ * y, x dims), kernel (in-feature, out-feature, y, x dims), output (batch, channel, y,
+ * x dims), strides (y, x), dilations (y, x); `padding` = (top, bottom, left, right).
+ * One group.  Scales are device pointers.  The receptive fields are gathered into
+ * `workspace` (device, 256-byte aligned, at least disc_b200_qconv2d_workspace_bytes)
+ * and multiplied on the int8 tensor cores by the quantized linear; splitk_ws is that
+ * linear's scratch (see disc_b200_qgemm_args), needed when batch * out_h * out_w <= 128. */
+typedef struct disc_b200_qconv2d_args {
+  const int8_t* x;
+  const int8_t* w;
+  int8_t* out;
+  int64_t input_sizes[4];
+  int64_t kernel_sizes[4];
+  int64_t output_sizes[4];
+  int32_t padding[4];
+  int32_t metadata[16];
+  const float* x_scale;
+  const float* w_scale;
+  int32_t w_scale_per_channel; /* 0: one value, 1: one per output channel */
+  const float* out_scale;
+  void* workspace;
+  int64_t workspace_bytes;
+  void* splitk_ws;
+  int64_t splitk_ws_bytes;
+} disc_b200_qconv2d_args;
+/* -1 if the shapes, padding and metadata do not describe a convolution. */
+int64_t disc_b200_qconv2d_workspace_bytes(const disc_b200_qconv2d_args* args);
+int32_t disc_b200_qconv2d(const disc_b200_qconv2d_args* args, void* stream);
+/* Host only: padding (top, bottom, left, right), result sizes (in the data format)
+ * and metadata (17 entries: the 16 above + weight_is_const) from the attributes of
+ * ral_pdll_qconv2d, by the reference's rules (common_context_impl_quantization.h:45-215):
+ * data_format "NHWC" | "NCHW"; strides / dilations of 1, 2 or 4 entries; padding
+ * "SAME" | "VALID" | "EXPLICIT" (explicit_paddings of 4 or 8 entries); kernel
+ * [out, y, x, in]. */
+int32_t disc_b200_qconv2d_plan(const char* data_format, const int64_t* strides, int32_t n_strides,
+                               const int64_t* dilations, int32_t n_dilations, const char* padding,
+                               const int64_t* explicit_paddings, int32_t n_explicit, int32_t weight_is_const,
+                               const int64_t* input_sizes4, const int64_t* weight_sizes4, int32_t* padding_out4,
+                               int64_t* result_sizes4, int32_t* metadata_out17);
+
 /* softmax(x * scale + mask) over the last axis; lens / mask may be NULL
  * (kStitch softmax; same reference files as above). */
 int32_t disc_b200_softmax(const void* x, void* y, int32_t type, int64_t rows, int64_t cols,

@@ -270,3 +270,44 @@ def weight_only_qgemm(x, w, scale, zp=None, bias=None):
     lib().oracle_weight_only_qgemm_f32(_ptr(x), _ptr(w), _ptr(_f32(scale)), _ptr(z), _ptr(_f32(bias)), c_int64(m),
                                        c_int64(n), c_int64(k), _ptr(out))
     return out
+
+
+def conv2d_roles(data_format, input_shape, weight_shape, strides, dilations, padding):
+    """Geometry of a convolution by role for ``qconv2d``: input in ``data_format`` ("NHWC" | "NCHW"),
+    kernel [out, y, x, in], ``strides`` / ``dilations`` = (y, x), ``padding`` = (top, bottom, left, right).
+    Returns (dims9, x_stride4, w_stride4, o_stride4, conv8, output_shape)."""
+    def dense(shape):
+        st, s = [0] * 4, 1
+        for i in range(3, -1, -1):
+            st[i] = s
+            s *= shape[i]
+        return st
+    pos = {ch: data_format.index(ch) for ch in "NCHW"}
+    n, c = input_shape[pos["N"]], input_shape[pos["C"]]
+    h, w = input_shape[pos["H"]], input_shape[pos["W"]]
+    o, kh, kw, ci = weight_shape
+    assert ci == c
+    (sh, sw), (dh, dw), (pt, pb, pl, pr) = strides, dilations, padding
+    oh = (h + pt + pb - ((kh - 1) * dh + 1)) // sh + 1
+    ow = (w + pl + pr - ((kw - 1) * dw + 1)) // sw + 1
+    out_shape = [0] * 4
+    out_shape[pos["N"]], out_shape[pos["C"]], out_shape[pos["H"]], out_shape[pos["W"]] = n, o, oh, ow
+    xs, os_, ws = dense(input_shape), dense(out_shape), dense(weight_shape)
+    role = lambda st: [st[pos["N"]], st[pos["C"]], st[pos["H"]], st[pos["W"]]]
+    return ([n, c, h, w, o, kh, kw, oh, ow], role(xs), [ws[0], ws[3], ws[1], ws[2]], role(os_),
+            [sh, sw, dh, dw, pt, pb, pl, pr], tuple(out_shape))
+
+
+def qconv2d(x, w, x_scale, w_scale, out_scale, data_format="NHWC", strides=(1, 1), dilations=(1, 1),
+            padding=(0, 0, 0, 0)):
+    """oracle_qconv2d_s8: int8 input in ``data_format``, int8 kernel [out, y, x, in] -> int8 output in ``data_format``."""
+    x = np.ascontiguousarray(x, dtype=np.int8)
+    w = np.ascontiguousarray(w, dtype=np.int8)
+    dims, xs, ws, os_, conv, out_shape = conv2d_roles(data_format, x.shape, w.shape, strides, dilations, padding)
+    out = np.zeros(out_shape, dtype=np.int8)
+    ws_arr = np.ascontiguousarray(np.atleast_1d(w_scale), dtype=np.float32)
+    i64 = lambda v: np.ascontiguousarray(v, dtype=np.int64)
+    a = [i64(dims), i64(xs), i64(ws), i64(os_), i64(conv)]
+    lib().oracle_qconv2d_s8(_ptr(x), _ptr(w), _ptr(out), *[_ptr(v) for v in a], c_float(float(x_scale)), _ptr(ws_arr),
+                            c_int(1 if ws_arr.size > 1 else 0), c_float(float(out_scale)))
+    return out

@@ -410,3 +410,47 @@ ORACLE_API void oracle_weight_only_qgemm_f32(const float* x, const uint8_t* w, c
     }
   }
 }
+
+/* ---- Quantized 2-D convolution, int8 x int8 -> int8, symmetric.
+ * out = sat_s8(rne( acc * (s_x * s_w[o] / s_out) )), acc the int32 convolution sum,
+ * zero outside the input.  Restates what ral_qconv computes through cuDNN with
+ * scale = s_in * s_w / s_out (tao_compiler/mlir/ral/context/stream_executor_based_impl.cc:1866-1873)
+ * and ral_pdll_qconv2d with per-channel weight scales
+ * (common_context_impl_quantization.cc:363-607).  Operands by role: element strides
+ * for (batch, channel, y, x) of input and output and (out, in, y, x) of the kernel,
+ * so that every layout of the reference's tests (NHWC / NCHW data, OHWI kernel) is
+ * one code path.  Pinned to the known answers of
+ * tao_compiler/mlir/disc/tests/pdll/quantized_conv2d.cc in tests/test_oracle.py. */
+ORACLE_API void oracle_qconv2d_s8(const int8_t* x, const int8_t* w, int8_t* out, const int64_t* dims9,
+                                  const int64_t* x_stride4, const int64_t* w_stride4, const int64_t* o_stride4,
+                                  const int64_t* conv8, float x_scale, const float* w_scale, int w_scale_per_channel,
+                                  float out_scale) {
+  const int64_t batch = dims9[0], in_ch = dims9[1], in_h = dims9[2], in_w = dims9[3];
+  const int64_t out_ch = dims9[4], k_h = dims9[5], k_w = dims9[6], out_h = dims9[7], out_w = dims9[8];
+  const int64_t sh = conv8[0], sw = conv8[1], dh = conv8[2], dw = conv8[3], pt = conv8[4], pl = conv8[6];
+  for (int64_t n = 0; n < batch; ++n) {
+    for (int64_t o = 0; o < out_ch; ++o) {
+      /* the "kernel scale" in the reference's order: (s_x * s_w) / s_out, in float */
+      const float cs = x_scale * w_scale[w_scale_per_channel ? o : 0] / out_scale;
+      for (int64_t oy = 0; oy < out_h; ++oy) {
+        for (int64_t ox = 0; ox < out_w; ++ox) {
+          int32_t acc = 0;
+          for (int64_t ky = 0; ky < k_h; ++ky) {
+            const int64_t iy = oy * sh - pt + ky * dh;
+            if (iy < 0 || iy >= in_h) continue;
+            for (int64_t kx = 0; kx < k_w; ++kx) {
+              const int64_t ix = ox * sw - pl + kx * dw;
+              if (ix < 0 || ix >= in_w) continue;
+              for (int64_t c = 0; c < in_ch; ++c) {
+                acc += (int32_t)x[n * x_stride4[0] + c * x_stride4[1] + iy * x_stride4[2] + ix * x_stride4[3]] *
+                       (int32_t)w[o * w_stride4[0] + c * w_stride4[1] + ky * w_stride4[2] + kx * w_stride4[3]];
+              }
+            }
+          }
+          out[n * o_stride4[0] + o * o_stride4[1] + oy * o_stride4[2] + ox * o_stride4[3]] =
+              sat_s8(fmaf((float)acc, cs, 0.f));
+        }
+      }
+    }
+  }
+}

@@ -171,6 +171,13 @@ MemRefType<T, N> stub_const(ExecutionContext*, void*, const char*, int32_t) {
   return MemRefType<T, N>();
 }
 
+// ral_qconv with the signature of gpu_conv_impl::ral_qconv<int8_t, 4>
+// (tao_compiler/mlir/ral/context/stream_executor_based_impl.cc:1831-1841; that file needs
+// TensorFlow's StreamExecutor and cuDNN, so only the signature is restated).
+void stub_qconv(ExecutionContext*, void*, MemRefType<int8_t, 4>, MemRefType<int8_t, 4>, MemRefType<int32_t, 1>,
+                MemRefType<float, 0>, MemRefType<int32_t, 0>, MemRefType<float, 1>, MemRefType<int32_t, 1>,
+                MemRefType<float, 0>, MemRefType<int32_t, 0>, MemRefType<int8_t, 4>, MemRefType<int32_t, 1>) {}
+
 template <typename F>
 void note(const char* api, const char* device, F f) {
   g_names.push_back(
@@ -227,6 +234,8 @@ REF("ral_send_output", "cpu", stub_send_output<int8_t, 3>);
 REF_COLLECTIVES(float);
 REF_COLLECTIVES(tao::ral::float16);
 REF_COLLECTIVES(tao::ral::bfloat16);
+
+REF("ral_qconv", "gpu", stub_qconv);
 
 #define REF_CONSTS(T)                             \
   REF("ral_const", "cpu", stub_const<T, 0>);        \
