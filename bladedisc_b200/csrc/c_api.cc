@@ -15,6 +15,7 @@
 #include "ral/metadata.h"
 #include "ral/nccl_dyn.h"
 #include "../../include/disc_b200_ral.h"
+#include "kernels/observer.h"
 #include "kernels/qconv.h"
 #include "kernels/qgemm.h"
 #include "kernels/rowops.h"
@@ -582,6 +583,46 @@ int32_t disc_b200_qconv2d(const disc_b200_qconv2d_args* a, void* stream) {
   const char* detail = nullptr;
   const cudaError_t st = disc_b200::qconv_launch(p, static_cast<cudaStream_t>(stream), &detail);
   return finish(st, "qconv2d", detail);
+}
+
+int64_t disc_b200_observe_minmax_scratch_floats(int64_t outer, int64_t channels, int64_t inner) {
+  return disc_b200::minmax_scratch_floats(outer, channels, inner);
+}
+
+int32_t disc_b200_observe_minmax(const void* x, int32_t type, int64_t outer, int64_t channels, int64_t inner,
+                                 float* min_val, float* max_val, float* scratch, int64_t scratch_floats,
+                                 void* stream) {
+  disc_b200::MinMaxParams p;
+  p.x = x;
+  p.type = type;
+  p.outer = outer;
+  p.channels = channels;
+  p.inner = inner;
+  p.min_val = min_val;
+  p.max_val = max_val;
+  p.scratch = scratch;
+  p.scratch_floats = scratch_floats;
+  const char* detail = nullptr;
+  const cudaError_t st = disc_b200::minmax_observe_launch(p, static_cast<cudaStream_t>(stream), &detail);
+  return finish(st, "observe_minmax", detail);
+}
+
+int32_t disc_b200_minmax_qparams(const float* min_val, const float* max_val, int64_t n, int32_t qmin, int32_t qmax,
+                                 int32_t symmetric, int32_t symmetric_zero_point, float* scale, int32_t* zero_point,
+                                 void* stream) {
+  disc_b200::QParamsParams p;
+  p.min_val = min_val;
+  p.max_val = max_val;
+  p.n = n;
+  p.qmin = qmin;
+  p.qmax = qmax;
+  p.symmetric = symmetric;
+  p.symmetric_zero_point = symmetric_zero_point;
+  p.scale = scale;
+  p.zero_point = zero_point;
+  const char* detail = nullptr;
+  const cudaError_t st = disc_b200::minmax_qparams_launch(p, static_cast<cudaStream_t>(stream), &detail);
+  return finish(st, "minmax_qparams", detail);
 }
 
 int32_t disc_b200_select_device_image(int64_t num_images, int32_t cc_major, int32_t cc_minor) {

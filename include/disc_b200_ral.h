@@ -365,6 +365,26 @@ int32_t disc_b200_qconv2d_plan(const char* data_format, const int64_t* strides, 
                                const int64_t* input_sizes4, const int64_t* weight_sizes4, int32_t* padding_out4,
                                int64_t* result_sizes4, int32_t* metadata_out17);
 
+/* Calibration observers on the device (the reference runs them as eager torch ops:
+ * MinMaxObserver, PerChannelMinMaxObserver and Observer._calculate_qparams,
+ * tools/torch_quant/torch_quant/observer.py:134-165, 230-297).
+ * observe: min_val[c] = min(min_val[c], min x[:, c, :]), max_val likewise, x f32 / f16
+ * viewed as [outer, channels, inner]; the caller starts the state at +inf / -inf;
+ * scratch: at least disc_b200_observe_minmax_scratch_floats floats.
+ * qparams: lo = min(min_val, 0), hi = max(max_val, 0);
+ *   symmetric: scale = max(max(-lo, hi) / ((qmax - qmin) / 2), eps), zero point as given
+ *              (0 for signed, 128 for unsigned 8-bit);
+ *   affine:    scale = max((hi - lo) / (qmax - qmin), eps),
+ *              zero point = clamp(qmin - rne(lo / scale), qmin, qmax);
+ *   a range never observed (min > max) gives scale 1, zero point 0. */
+int64_t disc_b200_observe_minmax_scratch_floats(int64_t outer, int64_t channels, int64_t inner);
+int32_t disc_b200_observe_minmax(const void* x, int32_t type, int64_t outer, int64_t channels, int64_t inner,
+                                 float* min_val, float* max_val, float* scratch, int64_t scratch_floats,
+                                 void* stream);
+int32_t disc_b200_minmax_qparams(const float* min_val, const float* max_val, int64_t n, int32_t qmin, int32_t qmax,
+                                 int32_t symmetric, int32_t symmetric_zero_point, float* scale, int32_t* zero_point,
+                                 void* stream);
+
 /* softmax(x * scale + mask) over the last axis; lens / mask may be NULL
  * (kStitch softmax; same reference files as above). */
 int32_t disc_b200_softmax(const void* x, void* y, int32_t type, int64_t rows, int64_t cols,

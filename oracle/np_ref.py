@@ -76,3 +76,35 @@ def softmax(x, scale=1.0):
     x = (np.asarray(x, dtype=f32) * f32(scale)).astype(np.float64)
     e = np.exp(x - x.max(axis=-1, keepdims=True))
     return (e / e.sum(axis=-1, keepdims=True)).astype(f32)
+
+
+def observe_minmax(batches, ch_axis=None):
+    """Running range of MinMaxObserver (ch_axis None) / PerChannelMinMaxObserver after the batches
+    (tools/torch_quant/torch_quant/observer.py:239-245, 262-285): float32 minimum and maximum, per channel
+    over every other axis."""
+    lo = hi = None
+    for b in batches:
+        b = np.asarray(b, dtype=np.float32)
+        if ch_axis is None:
+            mn, mx = b.min(keepdims=True).reshape(1), b.max(keepdims=True).reshape(1)
+        else:
+            axes = tuple(i for i in range(b.ndim) if i != ch_axis % b.ndim)
+            mn, mx = b.min(axis=axes), b.max(axis=axes)
+        lo = mn if lo is None else np.minimum(lo, mn)
+        hi = mx if hi is None else np.maximum(hi, mx)
+    return lo.astype(np.float32), hi.astype(np.float32)
+
+
+def minmax_qparams(min_val, max_val, qmin=-128, qmax=127, symmetric=True, symmetric_zero_point=0):
+    """Observer._calculate_qparams (observer.py:134-165) in float32: the range widened to include zero,
+    scale floored at the float32 epsilon, affine zero point = clamp(qmin - rne(lo / scale))."""
+    lo = np.minimum(np.asarray(min_val, np.float32), np.float32(0))
+    hi = np.maximum(np.asarray(max_val, np.float32), np.float32(0))
+    eps = np.finfo(np.float32).eps
+    if symmetric:
+        scale = np.maximum(np.maximum(-lo, hi) / np.float32((qmax - qmin) / 2), eps).astype(np.float32)
+        zp = np.full(scale.shape, symmetric_zero_point, np.int32)
+    else:
+        scale = np.maximum((hi - lo) / np.float32(qmax - qmin), eps).astype(np.float32)
+        zp = np.clip(qmin - np.rint(lo / scale).astype(np.int32), qmin, qmax).astype(np.int32)
+    return scale, zp

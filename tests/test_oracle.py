@@ -256,3 +256,34 @@ def test_weight_only_restatement_is_the_eager_model_the_reference_compiles():
     want = (x.astype(np.float64) @ (w.astype(np.float64) - z)) * s
     assert np.allclose(c.weight_only_qgemm(x, w, s, z), want, rtol=1e-6, atol=1e-6)
     assert np.allclose(c.weight_only_qgemm(x, w, s), (x.astype(np.float64) @ w.astype(np.float64)) * s, rtol=1e-6)
+
+
+def test_observer_restatement_matches_the_reference_observers():
+    """oracle/np_ref.py against tests/golden/observer_golden.npz, which holds what the reference's own
+    MinMaxObserver / PerChannelMinMaxObserver computed (tests/golden/make_observer_golden.py)."""
+    from pathlib import Path
+    from oracle import np_ref
+    g = np.load(Path(__file__).parent / "golden" / "observer_golden.npz")
+    schemes = {"sym": (-128, 127, True, 0), "affine": (0, 255, False, 0), "affine_s8": (-128, 127, False, 0)}
+    for tag, (qmin, qmax, sym, szp) in schemes.items():
+        lo, hi = np_ref.observe_minmax(list(g["act_batches"]))
+        assert (lo == g[f"act_{tag}_min"]).all() and (hi == g[f"act_{tag}_max"]).all()
+        s, z = np_ref.minmax_qparams(lo, hi, qmin, qmax, sym, szp)
+        assert (s == g[f"act_{tag}_scale"]).all() and (z == g[f"act_{tag}_zp"]).all()
+    lo, hi = np_ref.observe_minmax([g["pos_x"]])
+    s, z = np_ref.minmax_qparams(lo, hi, 0, 255, False)
+    assert (s == g["pos_scale"]).all() and (z == g["pos_zp"]).all() and z[0] == 0      # range widened to zero
+    for tag, key, axis, (qmin, qmax, sym) in (("w_ax0", "w", 0, (-128, 127, True)), ("w_ax1", "w", 1, (-128, 127, True)),
+                                              ("k4_ax3", "k4", 3, (-128, 127, True)),
+                                              ("w_ax0_affine", "w", 0, (0, 255, False))):
+        t = g[key]
+        lo, hi = np_ref.observe_minmax([t, t * np.float32(0.5) + np.float32(0.01)], ch_axis=axis)
+        assert (lo == g[f"{tag}_min"]).all() and (hi == g[f"{tag}_max"]).all()
+        s, z = np_ref.minmax_qparams(lo, hi, qmin, qmax, sym)
+        assert (s == g[f"{tag}_scale"]).all() and (z == g[f"{tag}_zp"]).all()
+    # and the scales the encoder goldens were calibrated with (same observers, other data)
+    q = np.load(Path(__file__).parent / "golden" / "qpath_golden.npz")
+    lo, hi = np_ref.observe_minmax(list(q["tq_calib"]))
+    assert (np_ref.minmax_qparams(lo, hi)[0] == q["tq_s_x"]).all()
+    lo, hi = np_ref.observe_minmax([q["tq_w1"]], ch_axis=0)
+    assert (np_ref.minmax_qparams(lo, hi)[0] == q["tq_s_w1"]).all()
