@@ -1,0 +1,89 @@
+"""Argument checks of the direct C entry points that answer before anything touches a GPU:
+status code + message, never a crash.  (What needs a device is covered by the -m gpu tests.)"""
+import ctypes
+
+import pytest
+
+from bladedisc_b200 import lib as L
+
+
+@pytest.fixture(scope="module")
+def lib(built_lib):
+    return L.load()
+
+
+def _err(lib):
+    return lib.disc_b200_last_error_string().decode()
+
+
+def test_weight_only_qgemm(lib):
+    a = L.WeightOnlyQGemmArgs()
+    a.x = a.w = a.scale = a.out = 0x1000          # never dereferenced on these paths
+    a.m, a.n, a.k, a.ldx, a.ldw, a.ldo, a.type = 4, 64, 32, 32, 64, 64, L.F16
+    assert lib.disc_b200_weight_only_qgemm(None, None) != 0 and "null args" in _err(lib)
+    a.m = -1
+    assert lib.disc_b200_weight_only_qgemm(ctypes.byref(a), None) != 0 and "negative size" in _err(lib)
+    a.m = 0
+    assert lib.disc_b200_weight_only_qgemm(ctypes.byref(a), None) == 0         # nothing to do
+    a.m, a.w = 4, None
+    assert lib.disc_b200_weight_only_qgemm(ctypes.byref(a), None) != 0 and "null operand" in _err(lib)
+    a.w, a.ldw = 0x1000, 63
+    assert lib.disc_b200_weight_only_qgemm(ctypes.byref(a), None) != 0 and "row stride" in _err(lib)
+    a.ldw, a.type = 64, 7
+    assert lib.disc_b200_weight_only_qgemm(ctypes.byref(a), None) != 0 and "element type" in _err(lib)
+
+
+def _conv_args():
+    a = L.QConv2dArgs()
+    a.x = a.w = a.out = a.x_scale = a.w_scale = a.out_scale = 0x1000
+    a.input_sizes[:] = [2, 8, 8, 16]
+    a.kernel_sizes[:] = [4, 3, 3, 16]
+    a.output_sizes[:] = [2, 6, 6, 4]
+    a.padding[:] = [0, 0, 0, 0]
+    a.metadata[:] = [0, 3, 1, 2, 3, 0, 1, 2, 0, 3, 1, 2, 1, 1, 1, 1]
+    return a
+
+
+def test_qconv2d(lib):
+    assert lib.disc_b200_qconv2d(None, None) != 0 and "null args" in _err(lib)
+    a = _conv_args()
+    need = lib.disc_b200_qconv2d_workspace_bytes(ctypes.byref(a))
+    # K = 144 needs no padding, the OHWI kernel no packing, the NHWC output no scatter: the gathered matrix only
+    assert need == (2 * 6 * 6 * 144 + 255) // 256 * 256
+    assert lib.disc_b200_qconv2d(ctypes.byref(a), None) != 0 and "workspace" in _err(lib)
+    a.workspace, a.workspace_bytes = 0x1008, need   # not 256-byte aligned
+    assert lib.disc_b200_qconv2d(ctypes.byref(a), None) != 0 and "misaligned" in _err(lib)
+    a.workspace, a.x = 0x1000, None
+    assert lib.disc_b200_qconv2d(ctypes.byref(a), None) != 0 and "null operand" in _err(lib)
+    a = _conv_args()
+    a.output_sizes[:] = [2, 7, 6, 4]
+    assert lib.disc_b200_qconv2d(ctypes.byref(a), None) != 0 and "output shape does not match" in _err(lib)
+    a = _conv_args()
+    a.metadata[12] = 0                              # stride 0
+    assert lib.disc_b200_qconv2d(ctypes.byref(a), None) != 0 and "invalid conv params" in _err(lib)
+    a = _conv_args()
+    a.kernel_sizes[:] = [4, 3, 3, 8]
+    assert lib.disc_b200_qconv2d(ctypes.byref(a), None) != 0 and "grouped convolution" in _err(lib)
+    a = _conv_args()
+    a.input_sizes[0] = 0
+    a.output_sizes[0] = 0
+    assert lib.disc_b200_qconv2d(ctypes.byref(a), None) == 0                    # empty batch
+
+
+def test_observers(lib):
+    f = lib.disc_b200_observe_minmax
+    assert lib.disc_b200_observe_minmax_scratch_floats(1, 1, 16384) == 2
+    assert lib.disc_b200_observe_minmax_scratch_floats(1, 1, 16385) == 4
+    assert lib.disc_b200_observe_minmax_scratch_floats(3, 5, 1 << 30) == 2 * 5 * 1024   # capped blocks per channel
+    assert lib.disc_b200_observe_minmax_scratch_floats(0, 5, 7) == 0
+    assert f(0x1000, L.F32, -1, 1, 4, 0x1000, 0x1000, 0x1000, 8, None) != 0 and "negative size" in _err(lib)
+    assert f(0x1000, L.F32, 0, 1, 4, 0x1000, 0x1000, 0x1000, 8, None) == 0     # nothing observed
+    assert f(None, L.F32, 1, 1, 4, 0x1000, 0x1000, 0x1000, 8, None) != 0 and "null operand" in _err(lib)
+    assert f(0x1000, L.F32, 1, 70000, 4, 0x1000, 0x1000, 0x1000, 1 << 20, None) != 0 and "65535 channels" in _err(lib)
+    assert f(0x1000, L.F32, 1, 2, 4, 0x1000, 0x1000, 0x1000, 3, None) != 0 and "scratch" in _err(lib)
+    assert f(0x1000, 9, 1, 2, 4, 0x1000, 0x1000, 0x1000, 4, None) != 0 and "element type" in _err(lib)
+    q = lib.disc_b200_minmax_qparams
+    assert q(0x1000, 0x1000, -1, -128, 127, 1, 0, 0x1000, 0x1000, None) != 0 and "invalid channel count" in _err(lib)
+    assert q(0x1000, 0x1000, 4, 5, 5, 1, 0, 0x1000, 0x1000, None) != 0 and "quantized range" in _err(lib)
+    assert q(0x1000, 0x1000, 0, -128, 127, 1, 0, 0x1000, 0x1000, None) == 0
+    assert q(None, 0x1000, 4, -128, 127, 1, 0, 0x1000, 0x1000, None) != 0 and "null operand" in _err(lib)
