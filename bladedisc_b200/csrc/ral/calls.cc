@@ -262,8 +262,15 @@ const Attr* attrs_of(ExecContext* ctx, void* blob) {
   AttrCache& c = attr_cache();
   std::lock_guard<std::mutex> l(c.mu);
   auto it = c.map.find(blob);
-  if (it != c.map.end() && std::memcmp(blob, it->second.bytes.data(), it->second.bytes.size()) == 0) {
-    return it->second.attr.get();
+  if (it != c.map.end()) {
+    // Byte by byte, stopping at the first difference: the blob's own length is not known before
+    // it is parsed, and a well-formed blob that agrees with the cached one on all of its bytes
+    // has the cached one's length (every length is part of the bytes), so nothing past it is read.
+    const char* now = static_cast<const char*>(blob);
+    const std::string& was = it->second.bytes;
+    size_t i = 0;
+    while (i < was.size() && now[i] == was[i]) ++i;
+    if (i == was.size()) return it->second.attr.get();
   }
   const uint8_t* cur = static_cast<const uint8_t*>(blob);
   auto a = parse_attr(&cur);
