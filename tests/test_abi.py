@@ -224,3 +224,56 @@ def test_dispatcher_error_convention_without_gpu(built_lib):
     assert lib.tao_ral_last_error(ctx, ctypes.byref(msg)) != 0 and b"invalid input index" in msg.value
     lib.disc_b200_exec_destroy(ex)
     lib.disc_b200_context_destroy(ctx)
+
+
+def test_attr_cache_follows_the_bytes_at_an_address(built_lib):
+    """Parsed attributes are cached by blob address, as the reference does for the constant blobs of an
+    executable (tao_compiler/mlir/ral/context/pdll_util.h:190-220); a host that rebuilds a blob in place
+    gets the new content.  Driven through ral_pdll_qconv2d, whose attribute errors surface before any
+    device work, so this runs without a GPU."""
+    from bladedisc_b200 import lib as L
+    from bladedisc_b200.ral import PackedMemRef, pack_attrs
+    lib = L.load()
+    ctx = lib.disc_b200_context_create(None)
+    ex = lib.disc_b200_exec_create(ctx)
+    buf = ctypes.create_string_buffer(512)
+
+    def call(attrs):
+        blob = pack_attrs(attrs)
+        ctypes.memset(buf, 0, 512)
+        ctypes.memmove(buf, blob, len(blob))
+        slot, stream, pattrs = ctypes.c_void_p(ex), ctypes.c_void_p(0), ctypes.c_void_p(ctypes.addressof(buf))
+        x, w = PackedMemRef(4), PackedMemRef(4)
+        for m, shape in ((x, (1, 4, 4, 8)), (w, (4, 1, 1, 8))):
+            m.words[0] = m.words[1] = 0x1000               # never dereferenced on the error paths
+            for i, d in enumerate(shape):
+                m.words[3 + i] = d
+        s0, z0, s1, z1 = PackedMemRef(0), PackedMemRef(0), PackedMemRef(1), PackedMemRef(1)
+        s1.words[3] = z1.words[3] = 4
+        res = PackedMemRef(4)
+        slots = [ctypes.addressof(slot), ctypes.addressof(stream)]
+        for m in (x, w, s0, z0, s1, z1, s0, z0):
+            slots.extend(m.slots())
+        slots += [ctypes.addressof(pattrs), ctypes.addressof(res.words)]
+        arr = (ctypes.c_void_p * len(slots))(*slots)
+        name = ctypes.create_string_buffer(
+            b"ral_pdll_qconv2d___gpu___pvoid_pvoid_m4di8_m4di8_m0df32_m0di32_m1df32_m1di32_m0df32_m0di32_pvoid___m4di8")
+        lib.tao_ral_call_impl(ex, ctypes.cast(name, ctypes.c_void_p), arr)
+        msg = ctypes.c_char_p()
+        code = lib.tao_ral_last_error(ctx, ctypes.byref(msg))
+        text = (msg.value or b"").decode()
+        lib.tao_ral_clear_error(ctx)
+        return code, text
+
+    base = {"data_format": "NHWC", "strides": [1], "dilations": [1], "padding": "VALID", "explicit_paddings": [],
+            "weight_is_const": True}
+    code, text = call(dict(base, padding="FULL"))
+    assert code != 0 and "fail to generate paddings" in text
+    code, text = call(dict(base, padding="FULL"))                  # same bytes: served from the cache
+    assert code != 0 and "fail to generate paddings" in text
+    code, text = call(dict(base, data_format="NHW"))               # other bytes at the same address
+    assert code != 0 and "fail to generate spatial dims" in text
+    code, text = call(dict(base, strides=[1, 2, 3]))
+    assert code != 0 and "fail to generate strides and dilations" in text
+    lib.disc_b200_exec_destroy(ex)
+    lib.disc_b200_context_destroy(ctx)
