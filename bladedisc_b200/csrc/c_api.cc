@@ -497,6 +497,12 @@ int32_t disc_b200_const_name_info(const char* unique_name, int32_t* rank, int64_
   return 0;
 }
 
+int32_t disc_b200_weight_only_qgemm_plan(int64_t m, int64_t n, int64_t k, int32_t align, int32_t sm_count,
+                                         int64_t* out7) {
+  if (!out7) return 1;
+  return disc_b200::woq_gemm_plan_describe(m, n, k, align, sm_count, out7);
+}
+
 int32_t disc_b200_weight_only_qgemm(const disc_b200_weight_only_qgemm_args* a, void* stream) {
   if (!a) {
     g_last_error = "weight-only qgemm: null args";

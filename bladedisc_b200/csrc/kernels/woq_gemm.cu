@@ -97,6 +97,8 @@ __host__ __device__ constexpr int group_for(int mt, int c) {
   return c == 16 ? 8 : c == 8 ? 8 : (mt <= 8 ? 16 : 8);
 }
 
+constexpr size_t kSmemLimit = 200 * 1024;
+
 struct Plan {
   int mt;       // rows of activations per launch, padded (1, 2, 4, 8, 16)
   int c;        // bytes per lane and load (16, 8 or 4)
@@ -130,15 +132,27 @@ Plan make_plan(int64_t m, int64_t n, int64_t k, int align, int sm_count) {
       best = cs;
     }
   }
-  pl.cluster = best;
-  int64_t kc = (k + best - 1) / best;
-  kc = std::max<int64_t>(step, (kc + step - 1) / step * step);
-  pl.kc = static_cast<int>(kc);
   const size_t tile = sizeof(float) * pl.mt * kStrip;
-  const size_t xs = sizeof(float) * pl.mt * pl.kc;
   const size_t red = sizeof(float) * kWarps * pl.mt * kStrip;
-  pl.smem = tile + std::max(xs, red);
+  for (;;) {
+    int64_t kc = (k + best - 1) / best;
+    kc = std::max<int64_t>(step, (kc + step - 1) / step * step);
+    pl.cluster = best;
+    pl.kc = static_cast<int>(kc);
+    pl.smem = tile + std::max(sizeof(float) * pl.mt * static_cast<size_t>(kc), red);
+    // a k chunk whose activations do not fit shared memory: split further before giving up rows
+    if (pl.smem <= kSmemLimit || best == kMaxCluster || k <= static_cast<int64_t>(best) * step) break;
+    best *= 2;
+  }
   return pl;
+}
+
+// Rows of activations per pass: 16, or fewer when the fp32 copy of a k chunk of that many
+// rows would not fit shared memory (K beyond ~25k); 0 if not even one row fits.
+int64_t rows_per_pass(int64_t m, int64_t n, int64_t k, int align, int sms) {
+  int64_t group = 16;
+  while (group > 1 && make_plan(std::min(group, m), n, k, align, sms).smem > kSmemLimit) group /= 2;
+  return make_plan(std::min(group, m), n, k, align, sms).smem > kSmemLimit ? 0 : group;
 }
 
 template <typename T, int MT, int C>
@@ -324,7 +338,7 @@ cudaError_t launch_tile(const WoqGemmParams& p, int64_t m0, const Plan& pl, cuda
   auto kern = woq_gemm_kernel<T, MT, C>;
   static bool configured = false;  // per instantiation; the attribute is per function, set once
   if (!configured) {
-    cudaError_t st = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t st = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemLimit));
     if (st != cudaSuccess) return st;
     configured = true;
   }
@@ -371,14 +385,15 @@ cudaError_t launch_typed(const WoqGemmParams& p, cudaStream_t s, const char** er
                                                            static_cast<unsigned>(p.M)),
                             dim3(256), 0, s, p);
   }
-  // more than 16 rows: 16 at a time, the weights re-read for each group
-  for (int64_t m0 = 0; m0 < p.M; m0 += 16) {
-    const int64_t rows = std::min<int64_t>(16, p.M - m0);
+  // more rows than one pass takes: a group at a time, the weights re-read for each group
+  const int64_t group = rows_per_pass(p.M, p.N, p.K, align, sm_count());
+  if (group == 0) {
+    *err = "weight-only qgemm: K too large for the shared-memory staging of the activations";
+    return cudaErrorInvalidValue;
+  }
+  for (int64_t m0 = 0; m0 < p.M; m0 += group) {
+    const int64_t rows = std::min<int64_t>(group, p.M - m0);
     const Plan pl = make_plan(rows, p.N, p.K, align, sm_count());
-    if (pl.smem > 200 * 1024) {
-      *err = "weight-only qgemm: K too large for the shared-memory staging of the activations";
-      return cudaErrorInvalidValue;
-    }
     cudaError_t st;
     switch (pl.mt) {
       case 1: st = launch_mt<T, 1>(p, m0, pl, s); break;
@@ -393,6 +408,21 @@ cudaError_t launch_typed(const WoqGemmParams& p, cudaStream_t s, const char** er
 }
 
 }  // namespace
+
+int woq_gemm_plan_describe(int64_t m, int64_t n, int64_t k, int align, int sm_count, int64_t out7[7]) {
+  if (m <= 0 || n <= 0 || k <= 0 || (align != 4 && align != 8 && align != 16) || sm_count <= 0) return 1;
+  const int64_t group = rows_per_pass(m, n, k, align, sm_count);
+  if (group == 0) return 2;
+  const Plan pl = make_plan(std::min(group, m), n, k, align, sm_count);
+  out7[0] = group;
+  out7[1] = pl.mt;
+  out7[2] = pl.c;
+  out7[3] = pl.strips;
+  out7[4] = pl.cluster;
+  out7[5] = pl.kc;
+  out7[6] = static_cast<int64_t>(pl.smem);
+  return 0;
+}
 
 cudaError_t woq_gemm_launch(const WoqGemmParams& p, cudaStream_t s, const char** err) {
   static const char* none = "";

@@ -33,6 +33,12 @@ struct WoqGemmParams {
 
 // The weights are constants of the model: the kernel may start reading them before
 // the kernel launched ahead of it on the stream has finished.
+// How a problem would be launched on a GPU of `sm_count` SMs with weights aligned to
+// `align` (4, 8 or 16) bytes: {rows per pass, padded rows, bytes per lane and load, strips
+// along N, cluster size along K, k rows per block, dynamic shared memory}.  Host only.
+// 0 = ok, 1 = bad argument, 2 = K too large for shared memory.
+int woq_gemm_plan_describe(int64_t m, int64_t n, int64_t k, int align, int sm_count, int64_t out7[7]);
+
 cudaError_t woq_gemm_launch(const WoqGemmParams& p, cudaStream_t s, const char** err);
 
 }  // namespace disc_b200

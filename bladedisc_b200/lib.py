@@ -140,6 +140,7 @@ SIGNATURES = {
                                            POINTER(c_void_p), POINTER(c_int64)]),
     "disc_b200_const_name_info": (c_int32, [c_char_p, POINTER(c_int32), POINTER(c_int64), POINTER(c_int64)]),
     "disc_b200_weight_only_qgemm": (c_int32, [POINTER(WeightOnlyQGemmArgs), c_void_p]),
+    "disc_b200_weight_only_qgemm_plan": (c_int32, [c_int64, c_int64, c_int64, c_int32, c_int32, POINTER(c_int64)]),
     "disc_b200_qconv2d_workspace_bytes": (c_int64, [POINTER(QConv2dArgs)]),
     "disc_b200_qconv2d": (c_int32, [POINTER(QConv2dArgs), c_void_p]),
     "disc_b200_qconv2d_plan": (c_int32, [c_char_p, POINTER(c_int64), c_int32, POINTER(c_int64), c_int32, c_char_p,

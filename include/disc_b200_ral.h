@@ -319,6 +319,12 @@ typedef struct disc_b200_weight_only_qgemm_args {
   int32_t type; /* DISC_B200_F32 / DISC_B200_F16 */
 } disc_b200_weight_only_qgemm_args;
 int32_t disc_b200_weight_only_qgemm(const disc_b200_weight_only_qgemm_args* args, void* stream);
+/* Host only: the launch plan for a problem on a GPU with sm_count SMs and weights aligned to
+ * `align` (4, 8 or 16) bytes: out7 = {rows per pass, rows padded to 1/2/4/8/16, weight bytes per
+ * lane and load, blocks along N, cluster size along K, k rows per block, dynamic shared memory
+ * bytes}.  0 = ok, 1 = bad argument, 2 = K too large for the shared-memory staging. */
+int32_t disc_b200_weight_only_qgemm_plan(int64_t m, int64_t n, int64_t k, int32_t align, int32_t sm_count,
+                                         int64_t* out7);
 
 /* Quantized 2-D convolution, int8 x int8 -> int8, symmetric:
  *   out = sat_s8(rne( conv(x, w) * (x_scale * w_scale(o) / out_scale) ))

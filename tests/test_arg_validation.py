@@ -87,3 +87,43 @@ def test_observers(lib):
     assert q(0x1000, 0x1000, 4, 5, 5, 1, 0, 0x1000, 0x1000, None) != 0 and "quantized range" in _err(lib)
     assert q(0x1000, 0x1000, 0, -128, 127, 1, 0, 0x1000, 0x1000, None) == 0
     assert q(None, 0x1000, 4, -128, 127, 1, 0, 0x1000, 0x1000, None) != 0 and "null operand" in _err(lib)
+
+
+def test_weight_only_plan_invariants(lib):
+    """The launch plan of the weight-only linear over a sweep of shapes: every k row is covered, blocks get whole
+    steps, shared memory fits, the cluster is a portable size, and long K falls back to fewer rows per pass."""
+    def plan(m, n, k, align=16, sms=148):
+        out = (ctypes.c_int64 * 7)()
+        rc = lib.disc_b200_weight_only_qgemm_plan(m, n, k, align, sms, out)
+        return rc, list(out)
+
+    steps = {(16, 1): 8 * 4 * 8, (16, 2): 8 * 4 * 8, (8, 4): 8 * 2 * 8, (4, 8): 8 * 1 * 16, (4, 16): 8 * 1 * 8}
+    for m in (1, 2, 3, 4, 5, 8, 9, 16, 17, 100):
+        for n in (8, 128, 264, 4096, 11008, 12288, 32000):
+            for k in (1, 64, 100, 4096, 11008, 28672):
+                for align in (4, 8, 16):
+                    rc, (group, mt, c, strips, cluster, kc, smem) = plan(m, n, k, align)
+                    assert rc == 0, (m, n, k, align)
+                    rows = min(group, m)
+                    assert group in (1, 2, 4, 8, 16) and mt >= rows and mt in (1, 2, 4, 8, 16)
+                    assert c <= align and c in (4, 8, 16) and mt * c <= 64          # accumulators per lane
+                    assert strips == (n + 127) // 128
+                    assert cluster in (1, 2, 4, 8) and cluster * kc >= k
+                    step = 8 * (c // 4) * {16: 8, 8: 8, 4: 16 if mt <= 8 else 8}[c]
+                    assert kc % step == 0 and kc >= step
+                    assert (cluster - 1) * kc < k or cluster == 1                   # no block without rows
+                    assert smem <= 200 * 1024
+                    assert smem == 4 * (mt * 128 + max(mt * kc, 8 * mt * 128))
+    assert (16, 1) in steps                                                         # (documentation of the table above)
+    # the 7B shapes the kernel was measured on keep 16 rows per pass and fill the GPU in one wave
+    for n, k in ((4096, 4096), (11008, 4096), (4096, 11008)):
+        rc, (group, mt, c, strips, cluster, kc, smem) = plan(16, n, k)
+        assert group == 16 and strips * cluster <= 2 * 148
+        rc, p1 = plan(1, n, k)
+        assert p1[2] == 16 and 148 <= p1[3] * p1[4] <= 2 * 148
+    # a 70B-sized down projection: 16 rows of 28672 / 8 activations do not fit, 8 rows do
+    rc, (group, mt, *_rest) = plan(16, 8192, 28672)
+    assert rc == 0 and group == 8 and mt == 8
+    # K so long that a single row's chunk does not fit
+    assert plan(1, 128, 1 << 22)[0] == 2
+    assert plan(0, 128, 128)[0] == 1 and plan(1, 128, 128, align=3)[0] == 1
