@@ -222,15 +222,24 @@ void ral_send_output(ExecContext* ctx, int64_t idx, MemRef<T, N> m) {
 #define DISC_B200_REGISTER_IO(T, N)                                     \
   DISC_B200_RAL_API("ral_recv_input", "cpu", ral_recv_input<T, N>);     \
   DISC_B200_RAL_API("ral_send_output", "cpu", ral_send_output<T, N>)
+// ranks 0..8 and the element types of the reference (base_context.cc:222-300), plus the
+// 16-bit floats at every rank (the reference has them for rank 0 only, and in its CUDA build)
 #define DISC_B200_REGISTER_IO_RANKS(T) \
   DISC_B200_REGISTER_IO(T, 0);         \
   DISC_B200_REGISTER_IO(T, 1);         \
   DISC_B200_REGISTER_IO(T, 2);         \
   DISC_B200_REGISTER_IO(T, 3);         \
-  DISC_B200_REGISTER_IO(T, 4)
+  DISC_B200_REGISTER_IO(T, 4);         \
+  DISC_B200_REGISTER_IO(T, 5);         \
+  DISC_B200_REGISTER_IO(T, 6);         \
+  DISC_B200_REGISTER_IO(T, 7);         \
+  DISC_B200_REGISTER_IO(T, 8)
 DISC_B200_REGISTER_IO_RANKS(float);
+DISC_B200_REGISTER_IO_RANKS(double);
 DISC_B200_REGISTER_IO_RANKS(f16_t);
+DISC_B200_REGISTER_IO_RANKS(bf16_t);
 DISC_B200_REGISTER_IO_RANKS(int8_t);
+DISC_B200_REGISTER_IO_RANKS(uint8_t);
 DISC_B200_REGISTER_IO_RANKS(int32_t);
 DISC_B200_REGISTER_IO_RANKS(int64_t);
 DISC_B200_REGISTER_IO_RANKS(bool);

@@ -215,6 +215,10 @@ REF("ral_recv_input", "cpu", stub_recv_input<float, 2>);
 REF("ral_recv_input", "cpu", stub_recv_input<int8_t, 3>);
 REF("ral_send_output", "cpu", stub_send_output<float, 2>);
 REF("ral_send_output", "cpu", stub_send_output<int8_t, 3>);
+REF("ral_recv_input", "cpu", stub_recv_input<uint8_t, 2>);
+REF("ral_recv_input", "cpu", stub_recv_input<double, 8>);
+REF("ral_send_output", "cpu", stub_send_output<bool, 5>);
+REF("ral_send_output", "cpu", stub_send_output<int64_t, 0>);
 
 #define REF_COLLECTIVES(T)                                              \
   REF("ral_all_reduce", "gpu", stub_collective<T, 0>);                    \
