@@ -33,6 +33,7 @@ SOURCES = [
     "ral/conv_plan.cc",
     "ral/metadata.cc",
     "ral/cu_driver_dyn.cc",
+    "ral/views.cc",
     "ral/calls.cc",
     "c_api.cc",
 ]
@@ -61,28 +62,44 @@ def _digest(src: Path) -> str:
     return h.hexdigest()[:16]
 
 
+# no device code and heavy on templates: the host compiler alone (through nvcc for the CUDA include paths)
+HOST_ONLY = {"ral/views.cc"}
+
+
+def _compile(nvcc: str, rel: str, obj: Path, verbose: bool) -> None:
+    src = CSRC / rel
+    if rel in HOST_ONLY:
+        cmd = [nvcc, "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-c", str(src), "-o", str(obj)]
+    else:
+        cmd = [nvcc, *NVCC_FLAGS, "-x", "cu", "-c", str(src), "-o", str(obj)]
+        if verbose:
+            cmd.insert(1, "-Xptxas")
+            cmd.insert(2, "-v")
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    subprocess.run(cmd, check=True)
+
+
 def build(verbose: bool = False, force: bool = False) -> Path:
     """Compiles (if needed) and returns the path of the shared library."""
+    from concurrent.futures import ThreadPoolExecutor
     OUT.mkdir(exist_ok=True)
     nvcc = _nvcc()
     objs = []
-    rebuilt = False
+    todo = []
     for rel in SOURCES:
-        src = CSRC / rel
-        obj = OUT / (rel.replace("/", "_") + "." + _digest(src) + ".o")
+        obj = OUT / (rel.replace("/", "_") + "." + _digest(CSRC / rel) + ".o")
         objs.append(obj)
         if obj.exists() and not force:
             continue
         for stale in OUT.glob(rel.replace("/", "_") + ".*.o"):
             stale.unlink()
-        cmd = [nvcc, *NVCC_FLAGS, "-x", "cu", "-c", str(src), "-o", str(obj)]
-        if verbose:
-            cmd.insert(1, "-Xptxas")
-            cmd.insert(2, "-v")
-            print(" ".join(cmd), flush=True)
-        subprocess.run(cmd, check=True)
-        rebuilt = True
-    if rebuilt or not LIB.exists() or force:
+        todo.append((rel, obj))
+    if todo:
+        with ThreadPoolExecutor(max_workers=min(len(todo), os.cpu_count() or 1, 8)) as pool:
+            for f in [pool.submit(_compile, nvcc, rel, obj, verbose) for rel, obj in todo]:
+                f.result()
+    if todo or not LIB.exists() or force:
         cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB), *map(str, objs), "-ldl"]
         if verbose:
             print(" ".join(cmd), flush=True)

@@ -178,6 +178,20 @@ void stub_qconv(ExecutionContext*, void*, MemRefType<int8_t, 4>, MemRefType<int8
                 MemRefType<float, 0>, MemRefType<int32_t, 0>, MemRefType<float, 1>, MemRefType<int32_t, 1>,
                 MemRefType<float, 0>, MemRefType<int32_t, 0>, MemRefType<int8_t, 4>, MemRefType<int32_t, 1>) {}
 
+// "inc_ref" (alias and reshape) and the memref copies, with the signatures of
+// tao_compiler/mlir/ral/context/base/cuda/cuda_context_impl.cc:544-625 and
+// common_context_impl_cuda.cc:380-420 (files that need the whole CUDA runtime of the reference).
+template <typename T, int N>
+MemRefType<T, N> stub_alias(ExecutionContext*, void*, MemRefType<T, N> input) {
+  return input;
+}
+template <typename T, int N, int M>
+MemRefType<T, M> stub_reshape(ExecutionContext*, void*, MemRefType<T, N>, MemRefType<int64_t, 1>) {
+  return MemRefType<T, M>();
+}
+template <typename T, int N>
+void stub_copy(ExecutionContext*, void*, MemRefType<T, N>, MemRefType<T, N>) {}
+
 template <typename F>
 void note(const char* api, const char* device, F f) {
   g_names.push_back(
@@ -240,6 +254,16 @@ REF_COLLECTIVES(tao::ral::float16);
 REF_COLLECTIVES(tao::ral::bfloat16);
 
 REF("ral_qconv", "gpu", stub_qconv);
+REF("inc_ref", "gpu", stub_alias<float, 2>);
+REF("inc_ref", "gpu", stub_alias<tao::ral::float16, 0>);
+REF("inc_ref", "cpu", stub_alias<int64_t, 1>);
+REF("inc_ref", "gpu", stub_reshape<float, 3, 2>);
+REF("inc_ref", "gpu", stub_reshape<tao::ral::bfloat16, 8, 1>);
+REF("inc_ref", "gpu", stub_reshape<bool, 1, 0>);
+REF("inc_ref", "cpu", stub_reshape<int32_t, 0, 4>);
+REF("h2d", "gpu", stub_copy<float, 2>);
+REF("d2h", "gpu", stub_copy<int64_t, 0>);
+REF("d2d", "gpu", stub_copy<double, 8>);
 
 #define REF_CONSTS(T)                             \
   REF("ral_const", "cpu", stub_const<T, 0>);        \

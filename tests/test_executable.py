@@ -143,3 +143,76 @@ def test_kernel_launch_without_a_driver_reports(built_lib):
     assert code != 0 and "CUDA driver unavailable" in msg
     lib.disc_b200_exec_destroy(e)
     lib.disc_b200_context_destroy(c)
+
+
+def test_inc_ref_keeps_a_host_buffer_alive_for_its_other_name(built_lib):
+    """alloc -> inc_ref (reshape [6] -> [2, 3]) -> dealloc of the first name: the buffer is still
+    this execution's (cpu_context_impl.cc:234-330); without the inc_ref the same dealloc releases it.
+    An alias of an input counts nothing; a pointer nobody knows is an error."""
+    from bladedisc_b200 import lib as L
+    from bladedisc_b200.ral import PackedMemRef
+    lib = L.load()
+    ctx = lib.disc_b200_context_create(None)
+
+    def call(ex, name, slots):
+        arr = (ctypes.c_void_p * len(slots))(*slots)
+        buf = ctypes.create_string_buffer(name)
+        lib.tao_ral_call_impl(ex, ctypes.cast(buf, ctypes.c_void_p), arr)
+        msg = ctypes.c_char_p()
+        return lib.tao_ral_last_error(ctx, ctypes.byref(msg)), (msg.value or b"").decode()
+
+    def run(with_inc_ref):
+        ex = lib.disc_b200_exec_create(ctx)
+        slot, stream = ctypes.c_void_p(ex), ctypes.c_void_p(0)
+        nbytes, p = ctypes.c_uint64(24), ctypes.c_void_p(0)
+        assert call(ex, b"alloc___cpu___pvoid_i64___pvoid", [ctypes.addressof(slot), ctypes.addressof(nbytes),
+                                                             ctypes.addressof(p)])[0] == 0 and p.value
+        flat = PackedMemRef(1)
+        flat.words[0] = flat.words[1] = p.value
+        flat.words[3], flat.words[4] = 6, 1
+        view = PackedMemRef(2)
+        if with_inc_ref:
+            shape = (ctypes.c_int64 * 2)(2, 3)
+            sm = PackedMemRef(1)
+            sm.words[0] = sm.words[1] = ctypes.addressof(shape)
+            sm.words[3], sm.words[4] = 2, 1
+            code, msg = call(ex, b"inc_ref___cpu___pvoid_pvoid_m1df32_m1di64___m2df32",
+                             [ctypes.addressof(slot), ctypes.addressof(stream)] + flat.slots() + sm.slots() +
+                             [ctypes.addressof(view.words)])
+            assert code == 0, msg
+            assert view.data == p.value and view.sizes == (2, 3) and (view.words[5], view.words[6]) == (3, 1)
+        assert call(ex, b"dealloc___cpu___pvoid_pvoid___void", [ctypes.addressof(slot), ctypes.addressof(p)])[0] == 0
+        # what the execution still owns shows in the ownership code of an output
+        idx = ctypes.c_int64(0)
+        out = PackedMemRef(2)
+        out.words[0] = out.words[1] = p.value
+        out.words[3], out.words[4], out.words[5], out.words[6] = 2, 3, 3, 1
+        assert call(ex, b"ral_send_output___cpu___pvoid_i64_m2df32___void",
+                    [ctypes.addressof(slot), ctypes.addressof(idx)] + out.slots())[0] == 0
+        owned = ctypes.c_int32(-1)
+        assert lib.disc_b200_exec_get_output(ex, 0, None, None, None, ctypes.byref(owned)) == 0
+        lib.disc_b200_exec_destroy(ex)
+        if owned.value == 2:
+            lib.disc_b200_exec_free_host_output(p)
+        return owned.value
+
+    assert run(with_inc_ref=True) == 2       # still owned: the second name keeps it
+    assert run(with_inc_ref=False) == 0      # released by the dealloc
+    # an input may be aliased freely; an unknown pointer may not
+    ex = lib.disc_b200_exec_create(ctx)
+    slot, stream = ctypes.c_void_p(ex), ctypes.c_void_p(0)
+    sizes = (ctypes.c_int64 * 1)(4)
+    assert lib.disc_b200_exec_bind_input(ex, 0, 0x7000, 1, sizes) == 0
+    for ptr, ok in ((0x7000, True), (0x9000, False)):
+        m, res = PackedMemRef(1), PackedMemRef(1)
+        m.words[0] = m.words[1] = ptr
+        m.words[3], m.words[4] = 4, 1
+        code, msg = call(ex, b"inc_ref___gpu___pvoid_pvoid_m1di8___m1di8",
+                         [ctypes.addressof(slot), ctypes.addressof(stream)] + m.slots() + [ctypes.addressof(res.words)])
+        assert (code == 0) == ok, msg
+        if ok:
+            assert res.data == ptr and res.sizes == (4,)
+        else:
+            assert "neither an input, a constant nor owned" in msg
+    lib.disc_b200_exec_destroy(ex)
+    lib.disc_b200_context_destroy(ctx)
