@@ -3,7 +3,9 @@
 // functions.
 #include <dlfcn.h>
 
+#include <cctype>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -450,14 +452,38 @@ int32_t disc_b200_context_load_metadata(disc_b200_context* handle, const char* p
     g_last_error = "load_metadata: null context or path";
     return 1;
   }
+  // the reference's switch for the process-level store (common_context_impl.cc:57-64)
+  const char* env = std::getenv("DISC_USE_GLOBAL_CONST_STORE");
+  std::string flag = env ? env : "";
+  for (char& c : flag) c = static_cast<char>(std::tolower(static_cast<unsigned char>(c)));
+  if (flag == "true" || flag == "1") return disc_b200_context_share_metadata(handle, path);
   std::string why;
   auto file = disc_b200::ral::MetadataFile::load(path, &why);
   if (!file) {
     g_last_error = why;
     return 1;
   }
+  auto store = std::make_shared<disc_b200::ral::ConstStore>();
+  store->metadata = std::move(file);
   std::lock_guard<std::mutex> l(ctx->mu);
-  ctx->metadata = std::move(file);
+  ctx->consts = std::move(store);
+  return 0;
+}
+
+int32_t disc_b200_context_share_metadata(disc_b200_context* handle, const char* path) {
+  auto* ctx = reinterpret_cast<disc_b200::ral::Context*>(handle);
+  if (!ctx || !path) {
+    g_last_error = "share_metadata: null context or path";
+    return 1;
+  }
+  std::string why;
+  auto store = disc_b200::ral::shared_const_store(path, ctx->device, &why);
+  if (!store) {
+    g_last_error = why;
+    return 1;
+  }
+  std::lock_guard<std::mutex> l(ctx->mu);
+  ctx->consts = std::move(store);
   return 0;
 }
 

@@ -97,24 +97,61 @@ void* Context::get_splitk_ws(int64_t bytes) {
   return splitk_ws;
 }
 
+ConstStore::~ConstStore() {
+  for (auto& kv : host_consts) std::free(kv.second.ptr);
+  if (shared) {
+    for (auto& kv : device_consts) cudaFree(kv.second.ptr);
+  }
+}
+
+namespace {
+struct SharedStores {
+  std::mutex mu;
+  std::map<std::pair<std::string, int>, std::weak_ptr<ConstStore>> by_file;
+};
+SharedStores& shared_stores() {
+  static SharedStores* s = new SharedStores;  // never destroyed: contexts may die during process exit
+  return *s;
+}
+}  // namespace
+
+std::shared_ptr<ConstStore> shared_const_store(const std::string& path, int device, std::string* error) {
+  SharedStores& reg = shared_stores();
+  std::lock_guard<std::mutex> l(reg.mu);
+  auto key = std::make_pair(path, device);
+  auto it = reg.by_file.find(key);
+  if (it != reg.by_file.end()) {
+    if (auto live = it->second.lock()) return live;
+  }
+  auto file = MetadataFile::load(path, error);
+  if (!file) return nullptr;
+  auto store = std::make_shared<ConstStore>();
+  store->metadata = std::move(file);
+  store->shared = true;
+  reg.by_file[key] = store;
+  return store;
+}
+
 const ConstEntry* Context::get_const(bool on_device, const char* unique_name, int32_t index) {
-  std::lock_guard<std::mutex> l(mu);
-  auto& by_index = on_device ? device_by_index : host_by_index;
-  if (index >= 0 && index < static_cast<int32_t>(by_index.size()) && by_index[index]) return by_index[index];
   auto fail = [&](const std::string& msg) -> const ConstEntry* {
-    if (status == 0) {  // mu is held: record the first error here
-      status = 1;
-      message = msg;
-    }
+    signal_error(1, msg);
     return nullptr;
   };
+  std::shared_ptr<ConstStore> st;
+  {
+    std::lock_guard<std::mutex> l(mu);
+    st = consts;
+  }
+  if (!st) return fail("ral_const: no metadata file loaded (disc_b200_context_load_metadata)");
+  std::lock_guard<std::mutex> l(st->mu);
+  auto& by_index = on_device ? st->device_by_index : st->host_by_index;
+  if (index >= 0 && index < static_cast<int32_t>(by_index.size()) && by_index[index]) return by_index[index];
   if (!unique_name) return fail("ral_const: null unique_name");
   const std::string key(unique_name);
-  auto& store = on_device ? device_consts : host_consts;
+  auto& store = on_device ? st->device_consts : st->host_consts;
   auto it = store.find(key);
   if (it == store.end()) {
-    if (!metadata) return fail("ral_const: no metadata file loaded (disc_b200_context_load_metadata)");
-    const std::string_view hex = on_device ? metadata->device_constant(key) : metadata->host_constant(key);
+    const std::string_view hex = on_device ? st->metadata->device_constant(key) : st->metadata->host_constant(key);
     if (hex.data() == nullptr) return fail("const unique_name " + key + " not found in metadata file");
     ConstEntry e;
     int64_t width = 0;
@@ -136,22 +173,34 @@ const ConstEntry* Context::get_const(bool on_device, const char* unique_name, in
     }
     e.bytes = static_cast<int64_t>(data.size());
     if (on_device) {
-      e.ptr = raw_alloc(data.size());
-      if (!e.ptr) return fail("device allocation of constant " + key + " failed");
-      // the staging bytes die with this call: wait for the copy (as the reference does, :116-118)
-      cudaError_t st = cudaMemcpyAsync(e.ptr, data.data(), data.size(), cudaMemcpyHostToDevice, stream);
-      if (st == cudaSuccess) st = cudaStreamSynchronize(stream);
-      if (st != cudaSuccess) {
-        raw_free(e.ptr);
-        return fail(std::string("upload of constant ") + key + ": " + cudaGetErrorString(st));
+      if (st->shared) {
+        if (cudaMalloc(&e.ptr, data.empty() ? 1 : data.size()) != cudaSuccess) e.ptr = nullptr;
+      } else {
+        e.ptr = raw_alloc(data.size());
       }
-      persistent.insert(e.ptr);
-      metadata->release_device(key);
+      if (!e.ptr) return fail("device allocation of constant " + key + " failed");
+      // the staging bytes die with this call: wait for the copy (as the reference does, :116-118);
+      // after the wait the constant is visible to every stream, which a shared store relies on
+      cudaError_t err = cudaMemcpyAsync(e.ptr, data.data(), data.size(), cudaMemcpyHostToDevice, stream);
+      if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+      if (err != cudaSuccess) {
+        if (st->shared) {
+          cudaFree(e.ptr);
+        } else {
+          raw_free(e.ptr);
+        }
+        return fail(std::string("upload of constant ") + key + ": " + cudaGetErrorString(err));
+      }
+      if (!st->shared) {
+        std::lock_guard<std::mutex> lc(mu);
+        persistent.insert(e.ptr);  // freed with this context
+      }
+      st->metadata->release_device(key);
     } else {
       e.ptr = std::malloc(data.empty() ? 1 : data.size());
       if (!e.ptr) return fail("host allocation of constant " + key + " failed");
       std::memcpy(e.ptr, data.data(), data.size());
-      metadata->release_host(key);
+      st->metadata->release_host(key);
     }
     it = store.emplace(key, std::move(e)).first;
   }
@@ -190,7 +239,7 @@ bool Context::comm_info(int* size, int* rank) {
 }
 
 Context::~Context() {
-  for (auto& kv : host_consts) std::free(kv.second.ptr);
+  consts.reset();  // a private store frees its host constants; its device ones are in `persistent`
   for (void* p : host_persistent) std::free(p);
   if (!modules.empty() && cu_driver_api().ok) {
     for (auto& kv : modules) cu_driver_api().ModuleUnload(kv.second);

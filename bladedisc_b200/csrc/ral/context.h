@@ -35,6 +35,27 @@ struct ConstEntry {
   int64_t bytes = 0;
 };
 
+// The constants of one executable: its metadata file and what has been decoded from it
+// (reference: RalGlobalConstantState, tao_compiler/mlir/ral/context/common_context_impl.cc:279-346
+// and common_context_impl_cuda.cc:61-132).  Decoded on first use, device ones uploaded once;
+// looked up by the module-unique index first, by name otherwise.  A store is private to a
+// context, or shared by every context of the process that runs the same file on the same
+// device (reference: ProcessLevelConstStore / ConstStoreRegistrar, :152-185, switched on by
+// DISC_USE_GLOBAL_CONST_STORE): weights are then uploaded once per process, not per context.
+struct ConstStore {
+  std::mutex mu;
+  std::unique_ptr<MetadataFile> metadata;
+  std::unordered_map<std::string, ConstEntry> device_consts, host_consts;
+  std::vector<const ConstEntry*> device_by_index, host_by_index;
+  // A shared store owns its device constants (cudaMalloc / cudaFree), because it may outlive
+  // the context that first asked for one; a private store's live in its context's allocator.
+  bool shared = false;
+  ~ConstStore();
+};
+// The process-wide store for (path, device): the live one if any context still holds it, else a
+// new one.  nullptr (and `error` filled) if the file does not load.
+std::shared_ptr<ConstStore> shared_const_store(const std::string& path, int device, std::string* error);
+
 struct Context {
   uint32_t magic = kContextMagic;
   int device = 0;
@@ -71,14 +92,8 @@ struct Context {
   // when there is no communicator or NCCL cannot be reached.
   bool comm_info(int* size, int* rank);
 
-  // Constants of the executable (reference: RalGlobalConstantState,
-  // tao_compiler/mlir/ral/context/common_context_impl.cc:279-346 and
-  // common_context_impl_cuda.cc:61-132): decoded from the metadata file on first
-  // use, device ones uploaded once and kept until the context dies; looked up by
-  // the module-unique index first, by name otherwise.
-  std::unique_ptr<MetadataFile> metadata;
-  std::unordered_map<std::string, ConstEntry> device_consts, host_consts;
-  std::vector<const ConstEntry*> device_by_index, host_by_index;
+  // Constants of the executable; null until a metadata file is attached.
+  std::shared_ptr<ConstStore> consts;
   // nullptr after signalling an error
   const ConstEntry* get_const(bool on_device, const char* unique_name, int32_t index);
   ~Context();

@@ -45,10 +45,15 @@ bool retain(ExecContext* ctx, void* p) {
     return true;
   }
   if (ctx->input_ptrs.count(p)) return true;
+  std::shared_ptr<ConstStore> consts;
   {
     std::lock_guard<std::mutex> l(ctx->ctx->mu);
     if ((kHost ? ctx->ctx->host_persistent : ctx->ctx->persistent).count(p)) return true;
-    for (const auto& kv : (kHost ? ctx->ctx->host_consts : ctx->ctx->device_consts)) {
+    consts = ctx->ctx->consts;
+  }
+  if (consts) {
+    std::lock_guard<std::mutex> l(consts->mu);
+    for (const auto& kv : (kHost ? consts->host_consts : consts->device_consts)) {
       if (kv.second.ptr == p) return true;
     }
   }

@@ -136,6 +136,7 @@ SIGNATURES = {
     "disc_b200_executable_run": (c_void_p, [c_void_p, c_int32, c_void_p]),
     "disc_b200_executable_close": (None, [c_void_p]),
     "disc_b200_context_load_metadata": (c_int32, [c_void_p, c_char_p]),
+    "disc_b200_context_share_metadata": (c_int32, [c_void_p, c_char_p]),
     "disc_b200_metadata_write": (c_int32, [c_char_p, c_int32, POINTER(c_char_p), POINTER(c_int32),
                                            POINTER(c_void_p), POINTER(c_int64)]),
     "disc_b200_const_name_info": (c_int32, [c_char_p, POINTER(c_int32), POINTER(c_int64), POINTER(c_int64)]),

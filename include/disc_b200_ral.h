@@ -443,6 +443,12 @@ int32_t disc_b200_all_reduce_f32(void* comm, const float* send, float* recv, int
  * constants are decoded on first use, device constants uploaded once and kept
  * until the context is destroyed. */
 int32_t disc_b200_context_load_metadata(disc_b200_context* ctx, const char* path);
+/* The same, with the constants shared by every context of this process that attaches the
+ * same file on the same device: each constant is decoded and uploaded once per process and
+ * lives until the last such context is destroyed (the reference's process-level store,
+ * common_context_impl.cc:152-185).  disc_b200_context_load_metadata does this too when the
+ * environment has DISC_USE_GLOBAL_CONST_STORE=true|1, the reference's switch. */
+int32_t disc_b200_context_share_metadata(disc_b200_context* ctx, const char* path);
 /* Writes a metadata file in the reference's format (tools, tests). */
 int32_t disc_b200_metadata_write(const char* path, int32_t n, const char* const* names, const int32_t* is_host,
                                  const void* const* data, const int64_t* bytes);

@@ -171,3 +171,58 @@ def test_files_are_interchangeable_with_the_reference(ctx, ref_ral, tmp_path):
     rc = ref_ral.ref_metadata_write(str(theirs).encode(), 2, (ctypes.c_char_p * 2)(*[x.encode() for x in names[:2]]),
                                     (ctypes.c_int * 2)(1, 1), (ctypes.c_char_p * 2)(*[h.encode() for h in hexes[:2]]))
     assert rc == 0 and same.read_bytes() == theirs.read_bytes()
+
+
+def test_contexts_can_share_the_constants_of_one_file(built_lib, tmp_path, monkeypatch):
+    """The process-level store of the reference (common_context_impl.cc:152-185): contexts that attach
+    the same file share decoded constants, which live until the last of them is gone."""
+    lib = L.load()
+    scale = np.linspace(0.5, 2.0, 48).astype(np.float32)
+    path = tmp_path / "shared.pbtxt"
+    M.write_metadata(path, [(M.const_name(0, scale), True, scale)])
+    name = M.const_name(0, scale)
+
+    def attach(share):
+        c = lib.disc_b200_context_create(None)
+        e = lib.disc_b200_exec_create(c)
+        f = lib.disc_b200_context_share_metadata if share else lib.disc_b200_context_load_metadata
+        assert f(c, str(path).encode()) == 0
+        return c, e
+
+    def drop(c, e):
+        lib.disc_b200_exec_destroy(e)
+        lib.disc_b200_context_destroy(c)
+
+    c1, e1 = attach(True)
+    c2, e2 = attach(True)
+    c3, e3 = attach(False)                                   # a private store next to them
+    _, _, r1 = _host_const(lib, c1, e1, name, 0, 1)
+    _, _, r2 = _host_const(lib, c2, e2, name, 0, 1)
+    _, _, r3 = _host_const(lib, c3, e3, name, 0, 1)
+    assert r1.data == r2.data and r3.data != r1.data         # one copy for the sharing contexts
+    assert np.array_equal(_array(r2, np.float32), scale) and np.array_equal(_array(r3, np.float32), scale)
+    drop(c1, e1)                                             # the store outlives the context that filled it
+    code, msg, again = _host_const(lib, c2, e2, name, 0, 1)
+    assert code == 0 and again.data == r2.data and np.array_equal(_array(again, np.float32), scale)
+    c4, e4 = attach(True)                                    # a later context joins the live store
+    _, _, r4 = _host_const(lib, c4, e4, "by index only", 0, 1)
+    assert r4.data == r2.data
+    drop(c2, e2)
+    drop(c4, e4)
+    drop(c3, e3)
+    c5, e5 = attach(True)                                    # everything released: a fresh store decodes again
+    code, msg, r5 = _host_const(lib, c5, e5, name, 0, 1)
+    assert code == 0 and np.array_equal(_array(r5, np.float32), scale)
+    drop(c5, e5)
+    # the reference's environment switch routes the plain call to the shared store
+    monkeypatch.setenv("DISC_USE_GLOBAL_CONST_STORE", "True")
+    c6, e6 = attach(False)
+    c7, e7 = attach(False)
+    assert _host_const(lib, c6, e6, name, 0, 1)[2].data == _host_const(lib, c7, e7, name, 0, 1)[2].data
+    drop(c6, e6)
+    drop(c7, e7)
+    assert lib.disc_b200_context_share_metadata(None, b"x") != 0
+    c8 = lib.disc_b200_context_create(None)
+    assert lib.disc_b200_context_share_metadata(c8, str(tmp_path / "missing").encode()) != 0
+    assert b"cannot open" in lib.disc_b200_last_error_string()
+    lib.disc_b200_context_destroy(c8)
