@@ -9,8 +9,12 @@
 // array through the reference's tao_ral_call_impl and read back what its
 // unpacking produced, which pins the packing our own tests use.  (3) The
 // reference's metadata file emitter and loader are exported as they are, so
-// that files written by either side can be read by the other.
+// that files written by either side can be read by the other.  (4) The reference's
+// parser of custom_attrs blobs (context/pdll_util.cc) renders what it understood of a
+// blob, so that the writer and the parser of this repository are checked against it.
+#include <algorithm>
 #include <cstdint>
+#include <cstdio>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -18,6 +22,7 @@
 #include "mlir/ral/ral_api.h"
 #include "mlir/ral/ral_context.h"
 #include "mlir/ral/ral_helper.h"
+#include "mlir/ral/context/pdll_util.h"
 #include "mlir/ral/ral_metadata.h"
 
 using tao::ral::ExecutionContext;
@@ -192,6 +197,55 @@ MemRefType<T, M> stub_reshape(ExecutionContext*, void*, MemRefType<T, N>, MemRef
 template <typename T, int N>
 void stub_copy(ExecutionContext*, void*, MemRefType<T, N>, MemRefType<T, N>) {}
 
+// What the reference's parser made of a blob, as text: keys sorted, strings quoted,
+// floats with 17 significant digits, dense tensors as dense<type bits[shape]:bytes B>.
+void render_ref(tao::ral::PDLAttr& a, std::string& o) {
+  const std::string& t = a.getType();
+  if (t == "dict") {
+    auto& items = a.as<tao::ral::DictPDLAttr>().getValue();
+    std::vector<std::string> keys;
+    for (auto& kv : items) keys.push_back(kv.first);
+    std::sort(keys.begin(), keys.end());
+    o += "{";
+    for (size_t i = 0; i < keys.size(); ++i) {
+      o += (i ? ", " : "") + keys[i] + ": ";
+      render_ref(*items[keys[i]], o);
+    }
+    o += "}";
+  } else if (t == "str") {
+    o += "\"" + a.as<tao::ral::StrPDLAttr>().getValue() + "\"";
+  } else if (t == "bool") {
+    o += a.as<tao::ral::BoolPDLAttr>().getValue() ? "true" : "false";
+  } else if (t == "int") {
+    o += std::to_string(a.as<tao::ral::IntPDLAttr>().getValue());
+  } else if (t == "float") {
+    char buf[64];
+    snprintf(buf, sizeof(buf), "%.17g", a.as<tao::ral::FloatPDLAttr>().getValue());
+    o += buf;
+  } else if (t == "intArray") {
+    auto& v = a.as<tao::ral::IntArrayPDLAttr>().getValue();
+    o += "[";
+    for (size_t i = 0; i < v.size(); ++i) o += (i ? ", " : "") + std::to_string(v[i]);
+    o += "]";
+  } else if (t == "array") {
+    auto& v = a.as<tao::ral::ArrayPDLAttr>().getValue();
+    o += "[";
+    for (size_t i = 0; i < v.size(); ++i) {
+      if (i) o += ", ";
+      render_ref(*v[i], o);
+    }
+    o += "]";
+  } else if (t == "denseElementsAttr") {
+    auto& d = a.as<tao::ral::DenseElementsPDLAttr>();
+    o += "dense<" + d.getElementType() + std::to_string(d.getNumBits()) + "[";
+    auto shape = d.getShape();
+    for (size_t i = 0; i < shape.size(); ++i) o += (i ? "x" : "") + std::to_string(shape[i]);
+    o += "]:" + std::to_string(d.getRawData().size()) + "B>";
+  } else {
+    o += "?" + t;
+  }
+}
+
 template <typename F>
 void note(const char* api, const char* device, F f) {
   g_names.push_back(
@@ -304,6 +358,18 @@ int ref_dispatch(const char* name, void** args) {
   return static_cast<int>(g_record.size());
 }
 int64_t ref_recorded(int i) { return g_record[i]; }
+
+// The reference's parser on a custom_attrs blob (context/pdll_util.cc:20-170): length of the
+// rendering, -1 if it could not parse; the text is copied into out when it fits.
+int ref_attrs_describe(const void* blob, char* out, int capacity) {
+  uint8_t* cur = const_cast<uint8_t*>(static_cast<const uint8_t*>(blob));
+  auto attr = tao::ral::parsePDLAttr(cur);
+  if (!attr) return -1;
+  std::string text;
+  render_ref(*attr, text);
+  if (static_cast<int>(text.size()) < capacity) std::memcpy(out, text.c_str(), text.size() + 1);
+  return static_cast<int>(text.size());
+}
 
 // The reference's emitter (ral_metadata.cc:117-167): header, constants, tailer.
 // Values are the hexadecimal strings the compiler would have produced.

@@ -277,3 +277,47 @@ def test_attr_cache_follows_the_bytes_at_an_address(built_lib):
     assert code != 0 and "fail to generate strides and dilations" in text
     lib.disc_b200_exec_destroy(ex)
     lib.disc_b200_context_destroy(ctx)
+
+
+def test_attribute_blobs_read_the_same_by_the_reference_parser(built_lib, ref_ral):
+    """pack_attrs (the writer hosts and tests use) and this library's parser against the reference's own
+    parser (tao_compiler/mlir/ral/context/pdll_util.cc, compiled into oracle/_ref): both must make the
+    same of every blob, the dense-tensor splat included."""
+    import numpy as np
+    from bladedisc_b200 import lib as L
+    from bladedisc_b200.ral import pack_attrs
+    lib = L.load()
+    ref_ral.ref_attrs_describe.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int]
+
+    def both(blob):
+        buf = ctypes.create_string_buffer(blob, len(blob))
+        mine, theirs = ctypes.create_string_buffer(8192), ctypes.create_string_buffer(8192)
+        n1 = lib.disc_b200_attrs_describe(buf, mine, 8192)
+        n2 = ref_ral.ref_attrs_describe(ctypes.addressof(buf), theirs, 8192)
+        return n1, mine.value.decode(), n2, theirs.value.decode()
+
+    cases = [
+        {},
+        {"activation": "gelu", "requant": True, "per_channel": False},
+        {"name": "disc.custom_call.test.tf_fused_add_mul", "trueBoolAttr": True, "falseBoolAttr": False, "int127": 127,
+         "intNegative123456": -123456, "float0_001": 0.001, "intArray3int128intNegative32int0": [128, -32, 0],
+         "array2strtest0strtest1": ["test0", "test1"], "array3float0_001float23_0floatNegative0_5": [0.001, 23.0, -0.5],
+         "array5intNegative5floatNegative0_5strtestint30float0_5": [-5, -0.5, "test", 30, 0.5]},
+        {"data_format": "NHWC", "strides": [1, 2, 2, 1], "dilations": [1, 1, 1, 1], "padding": "SAME",
+         "explicit_paddings": [], "weight_is_const": True},
+        {"all_gather_dim": 1, "replica_groups": np.arange(8, dtype=np.int64).reshape(2, 4), "is_async": True,
+         "async_token_key": 3, "reduction_kind": "max"},
+        {"weight_should_be_reordered": True, "nested": {"a": 1, "b": [1.5, "x"]},
+         "f32": np.array([[1.5, -2.0]], dtype=np.float32), "u8": np.arange(5, dtype=np.uint8)},
+    ]
+    for attrs in cases:
+        n1, mine, n2, theirs = both(pack_attrs(attrs))
+        assert n1 > 0 and n1 == n2 and mine == theirs, (mine, theirs)
+
+    def s(x):
+        return struct.pack("<q", len(x)) + x
+    # a splat written by hand (the Python writer always stores every element): one element for a [3, 2] tensor
+    splat = (s(b"dict") + struct.pack("<q", 1) + s(b"w") + s(b"denseElementsAttr") + s(b"float") + struct.pack("<I", 32) +
+             struct.pack("<q", 2) + struct.pack("<q", 3) + struct.pack("<q", 2) + b"\x01" + s(struct.pack("<f", -0.01)))
+    n1, mine, n2, theirs = both(splat)
+    assert mine == theirs == "{w: dense<float32[3x2]:24B>}"
