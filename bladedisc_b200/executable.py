@@ -85,12 +85,20 @@ class Executable:
             msg = L.disc_b200_last_error_string().decode()
             L.tao_ral_clear_error(self.context)
             raise ExecutableError(msg)
+        # Copy every output first and release the buffers this host now owns afterwards: a later
+        # output may be the same buffer under a second name (it is then reported as not owned).
+        release = []
         try:
-            return [self._collect(ex, k, tag, where) for k, (tag, where) in enumerate(self.outputs)]
+            return [self._collect(ex, k, tag, where, release) for k, (tag, where) in enumerate(self.outputs)]
         finally:
+            for kind, ptr in release:
+                if kind == 1:
+                    L.disc_b200_exec_free_output(self.context, ptr)
+                else:
+                    L.disc_b200_exec_free_host_output(ptr)
             L.disc_b200_exec_destroy(ex)
 
-    def _collect(self, ex, k: int, tag: str, where: str):
+    def _collect(self, ex, k: int, tag: str, where: str, release: list):
         L = self._L
         data = ctypes.c_void_p()
         rank = ctypes.c_int32()
@@ -98,26 +106,21 @@ class Executable:
         owned = ctypes.c_int32()
         if L.disc_b200_exec_get_output(ex, k, ctypes.byref(data), ctypes.byref(rank), sizes, ctypes.byref(owned)) != 0:
             raise ExecutableError(f"the program sent no output {k}")
+        if owned.value in (1, 2):
+            release.append((owned.value, data))
         shape = tuple(sizes[i] for i in range(rank.value))
         n = int(np.prod(shape)) if shape else 1
-        try:
-            if where == "cpu":
-                dt = np.dtype(TAG_NUMPY[tag])
-                if not data.value or n == 0:
-                    return np.empty(shape, dt)
-                buf = (ctypes.c_char * (n * dt.itemsize)).from_address(data.value)
-                return np.frombuffer(buf, dtype=dt).reshape(shape).copy()
-            import torch
-            from .ral import _TAG_DTYPE, _tensor_from_ptr
-            dtype = _TAG_DTYPE[tag]
+        if where == "cpu":
+            dt = np.dtype(TAG_NUMPY[tag])
             if not data.value or n == 0:
-                return torch.empty(shape, dtype=dtype, device=f"cuda:{self.device}")
-            return _tensor_from_ptr(data.value, shape, dtype, self.device).clone()
-        finally:
-            if owned.value == 1:
-                if where != "cpu":
-                    import torch
-                    torch.cuda.current_stream(self.device).synchronize()   # the clone read the buffer
-                L.disc_b200_exec_free_output(self.context, data)
-            elif owned.value == 2:
-                L.disc_b200_exec_free_host_output(data)
+                return np.empty(shape, dt)
+            buf = (ctypes.c_char * (n * dt.itemsize)).from_address(data.value)
+            return np.frombuffer(buf, dtype=dt).reshape(shape).copy()
+        import torch
+        from .ral import _TAG_DTYPE, _tensor_from_ptr
+        dtype = _TAG_DTYPE[tag]
+        if not data.value or n == 0:
+            return torch.empty(shape, dtype=dtype, device=f"cuda:{self.device}")
+        out = _tensor_from_ptr(data.value, shape, dtype, self.device).clone()
+        torch.cuda.current_stream(self.device).synchronize()   # the clone has read the buffer before it may be freed
+        return out

@@ -8,7 +8,9 @@
  *
  * It links against nothing: every runtime service comes through the dispatcher.
  *   -DHOST_PROGRAM: out0 = in0 + const "0_f32_8" computed on the host in a buffer
- *     from "alloc" on "cpu"; out1 = the constant; out2 = in0 itself.
+ *     from "alloc" on "cpu"; out1 = the constant; out2 = in0 itself; out3 = out0's
+ *     buffer under a second name ([1, n], made by "inc_ref") after the first name
+ *     was released with "dealloc".
  *   default: a quantized linear on the GPU; weight, bias and scales from ral_const,
  *     the product from ral_pdll_qgemm; out0 = the int8 result, out1 = a host
  *     constant, out2 = a host buffer holding the result's shape. */
@@ -73,14 +75,34 @@ void main(void** cs) {
   { void* args[2] = {&ctx, &scratch}; disc_ral_call(cs, "dealloc___cpu___pvoid_pvoid___void", args); }
   (void)host_alloc(cs, 64);                 /* and one it forgets: freed with the execution */
   y.base = y.data = out; y.offset = 0; y.sizes[0] = n; y.strides[0] = 1;
-  void* args[8];
+  void* args[16];
   int64_t o;
+  /* a second name for the result, [1, n], by the reshape call; the first name is then released */
+  memref2 view;
+  memset(&view, 0, sizeof(view));
+  {
+    int64_t dims[2] = {1, n};
+    memref1 shape;
+    void* stream = 0;
+    shape.base = shape.data = dims; shape.offset = 0; shape.sizes[0] = 2; shape.strides[0] = 1;
+    int i = 0;
+    args[i++] = &ctx; args[i++] = &stream;
+    i = put1(args, i, &y);
+    i = put1(args, i, &shape);
+    args[i++] = &view;
+    disc_ral_call(cs, "inc_ref___cpu___pvoid_pvoid_m1df32_m1di64___m2df32", args);
+    void* first_name = out;
+    void* dargs[2] = {&ctx, &first_name};
+    disc_ral_call(cs, "dealloc___cpu___pvoid_pvoid___void", dargs);
+  }
   o = 0; args[0] = &ctx; args[1] = &o; put1(args, 2, &y);
   disc_ral_call(cs, "ral_send_output___cpu___pvoid_i64_m1df32___void", args);
   o = 1; args[0] = &ctx; args[1] = &o; put1(args, 2, &c);
   disc_ral_call(cs, "ral_send_output___cpu___pvoid_i64_m1df32___void", args);
   o = 2; args[0] = &ctx; args[1] = &o; put1(args, 2, &x);
   disc_ral_call(cs, "ral_send_output___cpu___pvoid_i64_m1df32___void", args);
+  o = 3; args[0] = &ctx; args[1] = &o; put2(args, 2, &view);
+  disc_ral_call(cs, "ral_send_output___cpu___pvoid_i64_m2df32___void", args);
 }
 #else
 void main(void** cs) {

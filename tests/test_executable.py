@@ -65,7 +65,7 @@ def test_open_errors(built_lib, tmp_path):
 
 
 def test_output_ownership_codes(built_lib, tmp_path):
-    """owned = 2 for a host buffer the program allocated, 0 for a constant and for an input."""
+    """owned = 2 for a host buffer the program allocated, 0 for a constant, an input and a second name."""
     from bladedisc_b200 import lib as L
     from bladedisc_b200.executable import BufferRef
     lib = L.load()
@@ -80,14 +80,16 @@ def test_output_ownership_codes(built_lib, tmp_path):
     ex = lib.disc_b200_executable_run(exe, 1, ctypes.addressof(ref))
     assert ex
     got = []
-    for k in range(3):
+    for k in range(4):
         data, rank, owned = ctypes.c_void_p(), ctypes.c_int32(), ctypes.c_int32()
         s8 = (ctypes.c_int64 * 8)()
         assert lib.disc_b200_exec_get_output(ex, k, ctypes.byref(data), ctypes.byref(rank), s8, ctypes.byref(owned)) == 0
         got.append((owned.value, rank.value, s8[0], data.value))
-    assert [g[0] for g in got] == [2, 0, 0] and all(g[1:3] == (1, 8) for g in got)
+    # out3 is out0's buffer under a second name: the earlier output owns it
+    assert [g[0] for g in got] == [2, 0, 0, 0] and all(g[1:3] == (1, 8) for g in got[:3])
+    assert got[3][1:3] == (2, 1) and got[3][3] == got[0][3]
     assert got[2][3] == x.ctypes.data
-    assert lib.disc_b200_exec_get_output(ex, 3, None, None, None, None) != 0
+    assert lib.disc_b200_exec_get_output(ex, 4, None, None, None, None) != 0
     lib.disc_b200_exec_destroy(ex)
     lib.disc_b200_exec_free_host_output(got[0][3])
     lib.disc_b200_executable_close(exe)
@@ -216,3 +218,65 @@ def test_inc_ref_keeps_a_host_buffer_alive_for_its_other_name(built_lib):
             assert "neither an input, a constant nor owned" in msg
     lib.disc_b200_exec_destroy(ex)
     lib.disc_b200_context_destroy(ctx)
+
+
+def test_the_same_program_on_the_reference_runtime_and_on_this_one(built_lib, tmp_path):
+    """One compiled shared object, two runtimes: the reference's own host runtime (BaseCpuContext with its
+    constants, host buffers, reshape and input / output binding, compiled from the reference tree into
+    oracle/_ref/libref_host.so) and this library.  Same inputs and metadata file -> same outputs, shapes and
+    aliasing."""
+    from bladedisc_b200.executable import Executable, ExecutableError
+    so_ref = Path(__file__).resolve().parent.parent / "oracle" / "_ref" / "libref_host.so"
+    if not so_ref.exists():
+        pytest.skip("reference host runtime not built (reference tree absent)")
+    ref = ctypes.CDLL(str(so_ref))
+    program = build_program(tmp_path, host=True)
+    rng = np.random.default_rng(3)
+    const = rng.standard_normal(8).astype(np.float32)
+    meta = tmp_path / "meta"
+    M.write_metadata(meta, [("0_f32_8", True, const)])
+    meta_splat = tmp_path / "meta_splat"
+    M.write_metadata(meta_splat, [("0_f32_8", True, np.float32(0.375))])          # one element for eight
+
+    def run_ref(x, metadata):
+        n_out = 4
+        bufs = [np.zeros(64, np.float32) for _ in range(n_out)]
+        in_data = (ctypes.c_void_p * 1)(x.ctypes.data)
+        in_rank = (ctypes.c_int32 * 1)(x.ndim)
+        in_sizes = (ctypes.c_int64 * 8)(*x.shape)
+        out_ptrs = (ctypes.c_void_p * n_out)(*[b.ctypes.data for b in bufs])
+        caps = (ctypes.c_int64 * n_out)(*[b.nbytes for b in bufs])
+        widths = (ctypes.c_int32 * n_out)(*([4] * n_out))
+        ranks, owned, alias = (ctypes.c_int32 * n_out)(), (ctypes.c_int32 * n_out)(), (ctypes.c_int32 * n_out)()
+        sizes = (ctypes.c_int64 * (8 * n_out))()
+        err = ctypes.create_string_buffer(512)
+        rc = ref.ref_host_run(str(program).encode(), str(metadata).encode(), 1, in_data, in_rank, in_sizes, n_out,
+                              out_ptrs, caps, widths, ranks, sizes, owned, alias, err, 512)
+        if rc != 0:
+            return rc, err.value.decode(), None
+        outs = []
+        for i in range(n_out):
+            shape = tuple(sizes[8 * i + d] for d in range(ranks[i]))
+            outs.append((bufs[i][:int(np.prod(shape))].reshape(shape).copy(), owned[i], alias[i]))
+        return 0, "", outs
+
+    for metadata, want_c in ((meta, const), (meta_splat, np.full(8, 0.375, np.float32))):
+        for n in (8, 5):                                    # the program sizes its result from the input
+            x = rng.standard_normal(n).astype(np.float32)
+            rc, msg, theirs = run_ref(x, metadata)
+            assert rc == 0, msg
+            with Executable(program, metadata, [("f32", "cpu")] * 4) as exe:
+                ours = exe.run([x])
+            for (t, _, _), o in zip(theirs, ours):
+                assert t.shape == o.shape and np.array_equal(t, o)
+            assert np.array_equal(ours[0], x + want_c[:n]) and ours[3].shape == (1, n)
+            assert theirs[2][2] == 0 and theirs[1][2] == -1  # out2 is input 0 itself, out1 (the constant) is not
+    # The constant is missing from the file: here an error that names it.  (The reference records the same
+    # message and then reads through the pointer it did not get, common_context_impl.cc:309-315, so that
+    # case is not run on it.)
+    other = tmp_path / "other"
+    M.write_metadata(other, [("9_f32_8", True, const)])
+    x = np.ones(8, np.float32)
+    with Executable(program, other, [("f32", "cpu")] * 4) as exe:
+        with pytest.raises(ExecutableError, match="0_f32_8 not found in metadata file"):
+            exe.run([x])
