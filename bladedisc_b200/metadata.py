@@ -14,20 +14,24 @@ import numpy as np
 
 from . import lib as _lib
 
-# element type tags as the compiler spells them in a unique name
+# element type tags of memref operands (the call's types), by numpy dtype
 TAG_NUMPY = {"i1": np.bool_, "i8": np.int8, "ui8": np.uint8, "i16": np.int16, "ui16": np.uint16,
              "i32": np.int32, "ui32": np.uint32, "i64": np.int64, "f16": np.float16, "f32": np.float32,
              "f64": np.float64}
-_NUMPY_TAG = {np.dtype(v): k for k, v in TAG_NUMPY.items()}
 
 
 def const_name(uid, array_or_tag, shape: Sequence[int] = None) -> str:
-    """Unique name of a constant: ``const_name(3, w)`` or ``const_name(3, "i8", (4096, 4096))``."""
+    """Unique name of a constant: ``const_name(3, w)`` or ``const_name(3, "i8", (4096, 4096))``.
+
+    The compiler writes ``<md5 of the data>_<i|f><bits>_<d0xd1x...>``
+    (tao_compiler/mlir/disc/transforms/disc_convert_const_to_ral.cc:53-80): every integer type, signed or
+    not, is ``i<bits>``, every float ``f<bits>``; the runtime reads the element width from the digits."""
     if isinstance(array_or_tag, str):
         tag = array_or_tag
     else:
         a = np.asarray(array_or_tag)
-        tag, shape = _NUMPY_TAG[a.dtype], a.shape
+        bits = 1 if a.dtype == np.bool_ else a.dtype.itemsize * 8
+        tag, shape = f"{'f' if a.dtype.kind == 'f' else 'i'}{bits}", a.shape
     return f"{uid}_{tag}_{'x'.join(str(int(d)) for d in shape)}"
 
 

@@ -99,4 +99,40 @@ int ref_host_run(const char* so_path, const char* metadata_path, int n_in, const
   return rc;
 }
 
+// One constant through the reference's own ral_const on "cpu" (ral_base_cuda_const_host,
+// context/common_context_impl.cc:279-380): `call` is the full mangled name for the element type
+// and rank.  Copies the bytes into out (capacity cap) and the sizes into sizes8.
+int ref_host_const(const char* metadata_path, const char* call, const char* unique_name, int32_t index, int rank,
+                   int elem_bytes, void* out, int64_t cap, int64_t* sizes8, char* err, int err_cap) {
+  auto fail = [&](int code, const std::string& why) {
+    if (err && err_cap > 0) {
+      std::strncpy(err, why.c_str(), err_cap - 1);
+      err[err_cap - 1] = 0;
+    }
+    return code;
+  };
+  tao::ral::BaseContextOption opt;
+  opt.metadata_file_path = metadata_path;
+  tao::ral::cpu::BaseCpuContextOption cpu_opt;
+  std::unique_ptr<tao::ral::BaseContext> ctx = tao::ral::cpu::MakeBaseCpuContext(opt, cpu_opt);
+  auto exec = tao::ral::MakeExecutionContext<tao::ral::cpu::BaseCpuExecutionContext>(ctx.get());
+  void* ctx_slot = exec.get();
+  void* stream = nullptr;
+  const char* name = unique_name;
+  int64_t result[3 + 2 * 8] = {0};  // base, data, offset, sizes, strides of a rank <= 8 memref
+  void* args[5] = {&ctx_slot, &stream, &name, &index, result};
+  std::string mangled(call);
+  tao_ral_call_impl(exec.get(), const_cast<char*>(mangled.c_str()), args);
+  const char* msg = nullptr;
+  if (ctx->getLastError(&msg) != 0) return fail(-3, msg ? msg : "error");
+  int64_t n = 1;
+  for (int d = 0; d < rank; ++d) {
+    sizes8[d] = result[3 + d];
+    n *= result[3 + d];
+  }
+  if (n * elem_bytes > cap) return fail(-5, "output buffer too small");
+  std::memcpy(out, reinterpret_cast<void*>(result[1]), static_cast<size_t>(n * elem_bytes));
+  return 0;
+}
+
 }  // extern "C"

@@ -226,3 +226,64 @@ def test_contexts_can_share_the_constants_of_one_file(built_lib, tmp_path, monke
     assert lib.disc_b200_context_share_metadata(c8, str(tmp_path / "missing").encode()) != 0
     assert b"cannot open" in lib.disc_b200_last_error_string()
     lib.disc_b200_context_destroy(c8)
+
+
+def test_host_constants_equal_the_reference_runtime(ctx, tmp_path):
+    """Every kind of constant through the reference's own ral_const on "cpu" (its host runtime compiled into
+    oracle/_ref/libref_host.so) and through this library's: same bytes, same shape.  Element widths from the
+    tag, rank 0, sub-byte types, splats and a value with an odd number of hex digits."""
+    from pathlib import Path
+    so = Path(__file__).resolve().parent.parent / "oracle" / "_ref" / "libref_host.so"
+    if not so.exists():
+        pytest.skip("reference host runtime not built (reference tree absent)")
+    ref = ctypes.CDLL(str(so))
+    ref.ref_host_const.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p, ctypes.c_int32, ctypes.c_int,
+                                   ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64),
+                                   ctypes.c_char_p, ctypes.c_int]
+    lib, c, e = ctx
+    rng = np.random.default_rng(8)
+    consts = [
+        ("0_f32_6x7", "f32", np.float32, rng.standard_normal((6, 7)).astype(np.float32)),
+        ("1_i8_3x5x2", "i8", np.int8, rng.integers(-128, 128, (3, 5, 2), dtype=np.int8)),
+        ("2_i64_", "i64", np.int64, np.array(-123456789012, np.int64)),                 # rank 0
+        ("3_i1_9", "i1", np.bool_, rng.integers(0, 2, 9).astype(np.bool_)),             # one byte per element
+        ("4_i8_4", "ui8", np.uint8, np.array([0, 1, 254, 255], np.uint8)),       # unsigned: the name says i8 too
+        ("5_f64_2x2", "f64", np.float64, rng.standard_normal((2, 2))),
+        ("6_i32_5x3", "i32", np.int32, np.int32(-7)),                                   # splat
+        ("7_f32_1x2x3x4", "f32", np.float32, rng.standard_normal((1, 2, 3, 4)).astype(np.float32)),
+    ]
+    path = tmp_path / "kinds"
+    M.write_metadata(path, [(name, True, value) for name, _, _, value in consts])
+    # one more, written by the reference's emitter because the hex has an odd number of digits: 0x7 then 3 zero bytes
+    odd = tmp_path / "odd"
+    ref_ral = ctypes.CDLL(str(so.parent / "libref_ral.so"))
+    ref_ral.ref_metadata_write.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(ctypes.c_char_p),
+                                           ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_char_p)]
+    assert ref_ral.ref_metadata_write(str(odd).encode(), 1, (ctypes.c_char_p * 1)(b"0_i32_2"), (ctypes.c_int * 1)(1),
+                                      (ctypes.c_char_p * 1)(b"7000000")) == 0
+
+    def theirs(meta, name, tag, dtype, rank, index):
+        out = np.zeros(64, np.float64)
+        sizes = (ctypes.c_int64 * 8)()
+        err = ctypes.create_string_buffer(256)
+        call = f"ral_const___cpu___pvoid_pvoid_pvoid_i32___m{rank}d{tag}".encode()
+        rc = ref.ref_host_const(str(meta).encode(), call, name.encode(), index, rank, np.dtype(dtype).itemsize,
+                                out.ctypes.data, out.nbytes, sizes, err, 256)
+        assert rc == 0, err.value
+        shape = tuple(sizes[d] for d in range(rank))
+        n = int(np.prod(shape)) if shape else 1
+        return np.frombuffer(out.tobytes()[: n * np.dtype(dtype).itemsize], dtype=dtype).reshape(shape)
+
+    assert lib.disc_b200_context_load_metadata(c, str(path).encode()) == 0
+    for index, (name, tag, dtype, value) in enumerate(consts):
+        shape, _ = M.name_info(name)
+        want = theirs(path, name, tag, dtype, len(shape), index)
+        code, msg, r = _host_const(lib, c, e, name, index, len(shape), tag)
+        assert code == 0, msg
+        got = _array(r, dtype)
+        assert got.shape == want.shape == shape and got.tobytes() == want.tobytes(), name
+        assert np.array_equal(got, np.broadcast_to(value, shape))
+    assert lib.disc_b200_context_load_metadata(c, str(odd).encode()) == 0
+    want = theirs(odd, "0_i32_2", "i32", np.int32, 1, 0)
+    code, msg, r = _host_const(lib, c, e, "0_i32_2", 0, 1, "i32")
+    assert code == 0 and np.array_equal(_array(r, np.int32), want) and list(want) == [7, 7]
