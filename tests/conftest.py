@@ -44,3 +44,18 @@ def ref_ral():
     lib.ref_recorded.restype = ctypes.c_int64
     lib.ref_dispatch.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
     return lib
+
+
+@pytest.fixture(scope="session")
+def ref_host():
+    """The reference's own host runtime (contexts, constants, host buffers, input / output binding),
+    when it could be built here."""
+    import ctypes
+    import subprocess
+    so = ROOT / "oracle" / "_ref" / "libref_host.so"
+    if not so.exists() and Path("/root/reference/tao_compiler/mlir/ral/ral_api.cc").exists():
+        subprocess.run(["make", "-C", str(ROOT / "oracle"), "ref"], check=False,
+                       stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    if not so.exists():
+        pytest.skip("reference host runtime not built (reference tree absent)")
+    return ctypes.CDLL(str(so))

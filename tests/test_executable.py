@@ -220,16 +220,13 @@ def test_inc_ref_keeps_a_host_buffer_alive_for_its_other_name(built_lib):
     lib.disc_b200_context_destroy(ctx)
 
 
-def test_the_same_program_on_the_reference_runtime_and_on_this_one(built_lib, tmp_path):
+def test_the_same_program_on_the_reference_runtime_and_on_this_one(built_lib, ref_host, tmp_path):
     """One compiled shared object, two runtimes: the reference's own host runtime (BaseCpuContext with its
     constants, host buffers, reshape and input / output binding, compiled from the reference tree into
     oracle/_ref/libref_host.so) and this library.  Same inputs and metadata file -> same outputs, shapes and
     aliasing."""
     from bladedisc_b200.executable import Executable, ExecutableError
-    so_ref = Path(__file__).resolve().parent.parent / "oracle" / "_ref" / "libref_host.so"
-    if not so_ref.exists():
-        pytest.skip("reference host runtime not built (reference tree absent)")
-    ref = ctypes.CDLL(str(so_ref))
+    ref = ref_host
     program = build_program(tmp_path, host=True)
     rng = np.random.default_rng(3)
     const = rng.standard_normal(8).astype(np.float32)

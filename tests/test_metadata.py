@@ -228,15 +228,11 @@ def test_contexts_can_share_the_constants_of_one_file(built_lib, tmp_path, monke
     lib.disc_b200_context_destroy(c8)
 
 
-def test_host_constants_equal_the_reference_runtime(ctx, tmp_path):
+def test_host_constants_equal_the_reference_runtime(ctx, ref_host, ref_ral, tmp_path):
     """Every kind of constant through the reference's own ral_const on "cpu" (its host runtime compiled into
     oracle/_ref/libref_host.so) and through this library's: same bytes, same shape.  Element widths from the
     tag, rank 0, sub-byte types, splats and a value with an odd number of hex digits."""
-    from pathlib import Path
-    so = Path(__file__).resolve().parent.parent / "oracle" / "_ref" / "libref_host.so"
-    if not so.exists():
-        pytest.skip("reference host runtime not built (reference tree absent)")
-    ref = ctypes.CDLL(str(so))
+    ref = ref_host
     ref.ref_host_const.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p, ctypes.c_int32, ctypes.c_int,
                                    ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64),
                                    ctypes.c_char_p, ctypes.c_int]
@@ -256,7 +252,6 @@ def test_host_constants_equal_the_reference_runtime(ctx, tmp_path):
     M.write_metadata(path, [(name, True, value) for name, _, _, value in consts])
     # one more, written by the reference's emitter because the hex has an odd number of digits: 0x7 then 3 zero bytes
     odd = tmp_path / "odd"
-    ref_ral = ctypes.CDLL(str(so.parent / "libref_ral.so"))
     ref_ral.ref_metadata_write.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(ctypes.c_char_p),
                                            ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_char_p)]
     assert ref_ral.ref_metadata_write(str(odd).encode(), 1, (ctypes.c_char_p * 1)(b"0_i32_2"), (ctypes.c_int * 1)(1),
