@@ -69,7 +69,7 @@ class Executable:
         keep = []
         for i, t in enumerate(inputs):
             if isinstance(t, np.ndarray):
-                a = np.ascontiguousarray(t)
+                a = t if t.flags.c_contiguous else np.ascontiguousarray(t)   # (ascontiguousarray makes rank 0 rank 1)
                 ptr, shape = a.ctypes.data, a.shape
             else:
                 a = t.contiguous()

@@ -11,6 +11,8 @@
  *     from "alloc" on "cpu"; out1 = the constant; out2 = in0 itself; out3 = out0's
  *     buffer under a second name ([1, n], made by "inc_ref") after the first name
  *     was released with "dealloc".
+ *   -DHOST_PROGRAM2: rank-3 and rank-0 inputs, a persistent buffer, a reshape of an input
+ *     and a second name for a scalar (see the comment at that entry point).
  *   default: a quantized linear on the GPU; weight, bias and scales from ral_const,
  *     the product from ral_pdll_qgemm; out0 = the int8 result, out1 = a host
  *     constant, out2 = a host buffer holding the result's shape. */
@@ -103,6 +105,71 @@ void main(void** cs) {
   disc_ral_call(cs, "ral_send_output___cpu___pvoid_i64_m1df32___void", args);
   o = 3; args[0] = &ctx; args[1] = &o; put2(args, 2, &view);
   disc_ral_call(cs, "ral_send_output___cpu___pvoid_i64_m2df32___void", args);
+}
+#elif defined(HOST_PROGRAM2)
+/* in0: f32 [a, b, c], in1: i64 scalar.
+ * out0: i64 [3] = in0's shape, in a buffer from "ral_cpu_alloc_persistent";
+ * out1: i64 scalar = in1 + 1, in a buffer from "alloc";
+ * out2: f32 [a * b, c] = in0 itself under a new shape ("inc_ref" with a shape operand);
+ * out3: i64 scalar = out1's buffer under a second name ("inc_ref" without a shape operand). */
+typedef struct { void* base; void* data; int64_t offset; int64_t sizes[3]; int64_t strides[3]; } memref3;
+void main(void** cs) {
+  void* ctx = 0;
+  void* stream = 0;
+  int64_t idx;
+  memref3 x;
+  memref0 s;
+  memset(&x, 0, sizeof(x));
+  memset(&s, 0, sizeof(s));
+  idx = 0;
+  { void* args[3] = {&ctx, &idx, &x}; disc_ral_call(cs, "ral_recv_input___cpu___pvoid_i64___m3df32", args); }
+  idx = 1;
+  { void* args[3] = {&ctx, &idx, &s}; disc_ral_call(cs, "ral_recv_input___cpu___pvoid_i64___m0di64", args); }
+  if (!s.data) return;
+  uint64_t bytes = 3 * sizeof(int64_t);
+  int64_t* dims = 0;
+  { void* args[3] = {&ctx, &bytes, &dims}; disc_ral_call(cs, "ral_cpu_alloc_persistent___cpu___pvoid_i64___pvoid", args); }
+  int64_t* next = (int64_t*)host_alloc(cs, sizeof(int64_t));
+  if (!dims || !next) return;
+  dims[0] = x.sizes[0]; dims[1] = x.sizes[1]; dims[2] = x.sizes[2];
+  *next = *(int64_t*)s.data + 1;
+  memref1 d;
+  d.base = d.data = dims; d.offset = 0; d.sizes[0] = 3; d.strides[0] = 1;
+  memref0 n0;
+  n0.base = n0.data = next; n0.offset = 0;
+  /* in0 as [a * b, c] */
+  int64_t flat[2];
+  flat[0] = x.sizes[0] * x.sizes[1]; flat[1] = x.sizes[2];
+  memref1 shape;
+  shape.base = shape.data = flat; shape.offset = 0; shape.sizes[0] = 2; shape.strides[0] = 1;
+  memref2 x2;
+  memset(&x2, 0, sizeof(x2));
+  void* args[24];
+  int i = 0;
+  args[i++] = &ctx; args[i++] = &stream;
+  args[i++] = &x.base; args[i++] = &x.data; args[i++] = &x.offset;
+  args[i++] = &x.sizes[0]; args[i++] = &x.sizes[1]; args[i++] = &x.sizes[2];
+  args[i++] = &x.strides[0]; args[i++] = &x.strides[1]; args[i++] = &x.strides[2];
+  i = put1(args, i, &shape);
+  args[i++] = &x2;
+  disc_ral_call(cs, "inc_ref___cpu___pvoid_pvoid_m3df32_m1di64___m2df32", args);
+  /* a second name for the scalar */
+  memref0 n1;
+  memset(&n1, 0, sizeof(n1));
+  i = 0;
+  args[i++] = &ctx; args[i++] = &stream;
+  i = put0(args, i, &n0);
+  args[i++] = &n1;
+  disc_ral_call(cs, "inc_ref___cpu___pvoid_pvoid_m0di64___m0di64", args);
+  int64_t o;
+  o = 0; args[0] = &ctx; args[1] = &o; put1(args, 2, &d);
+  disc_ral_call(cs, "ral_send_output___cpu___pvoid_i64_m1di64___void", args);
+  o = 1; args[0] = &ctx; args[1] = &o; put0(args, 2, &n0);
+  disc_ral_call(cs, "ral_send_output___cpu___pvoid_i64_m0di64___void", args);
+  o = 2; args[0] = &ctx; args[1] = &o; put2(args, 2, &x2);
+  disc_ral_call(cs, "ral_send_output___cpu___pvoid_i64_m2df32___void", args);
+  o = 3; args[0] = &ctx; args[1] = &o; put0(args, 2, &n1);
+  disc_ral_call(cs, "ral_send_output___cpu___pvoid_i64_m0di64___void", args);
 }
 #else
 void main(void** cs) {

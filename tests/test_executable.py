@@ -14,9 +14,11 @@ from bladedisc_b200 import metadata as M
 SRC = Path(__file__).parent / "fake_executable" / "program.c"
 
 
-def build_program(tmp_path, host: bool):
-    so = tmp_path / ("host_program.so" if host else "gpu_program.so")
-    cmd = ["gcc", "-shared", "-fPIC", "-O1", "-Wno-main"] + (["-DHOST_PROGRAM"] if host else []) + ["-o", str(so), str(SRC)]
+def build_program(tmp_path, host, variant: int = 1):
+    """host: the host program (variant 1 or 2); else the GPU program."""
+    define = [] if not host else ["-DHOST_PROGRAM" if variant == 1 else "-DHOST_PROGRAM2"]
+    so = tmp_path / (f"host_program{variant}.so" if host else "gpu_program.so")
+    cmd = ["gcc", "-shared", "-fPIC", "-O1", "-Wno-main"] + define + ["-o", str(so), str(SRC)]
     subprocess.run(cmd, check=True)
     return so
 
@@ -277,3 +279,64 @@ def test_the_same_program_on_the_reference_runtime_and_on_this_one(built_lib, re
     with Executable(program, other, [("f32", "cpu")] * 4) as exe:
         with pytest.raises(ExecutableError, match="0_f32_8 not found in metadata file"):
             exe.run([x])
+
+
+def test_second_program_on_both_runtimes(built_lib, ref_host, tmp_path):
+    """Rank-3 and rank-0 inputs, a persistent host buffer as an output, an input under a new shape and a
+    scalar under a second name: the reference's host runtime and this library agree on every output, and
+    this library reports who owns what (persistent buffer: nobody; scalar: the first output; input: nobody)."""
+    from bladedisc_b200 import lib as L
+    from bladedisc_b200.executable import BufferRef, Executable
+    program = build_program(tmp_path, host=True, variant=2)
+    meta = tmp_path / "no_constants"
+    M.write_metadata(meta, [])                      # the reference's context wants a metadata file, even an empty one
+    rng = np.random.default_rng(12)
+    elem = [8, 8, 4, 8]
+    dtypes = [np.int64, np.int64, np.float32, np.int64]
+    for shape, scalar in (((2, 3, 4), 41), ((1, 5, 1), -7)):
+        x = rng.standard_normal(shape).astype(np.float32)
+        s = np.array(scalar, np.int64)
+        bufs = [np.zeros(256, np.uint8) for _ in range(4)]
+        in_data = (ctypes.c_void_p * 2)(x.ctypes.data, s.ctypes.data)
+        in_rank = (ctypes.c_int32 * 2)(3, 0)
+        in_sizes = (ctypes.c_int64 * 16)(*(list(shape) + [0] * 5 + [0] * 8))
+        out_ptrs = (ctypes.c_void_p * 4)(*[b.ctypes.data for b in bufs])
+        caps = (ctypes.c_int64 * 4)(*[b.nbytes for b in bufs])
+        widths = (ctypes.c_int32 * 4)(*elem)
+        ranks, owned, alias = (ctypes.c_int32 * 4)(), (ctypes.c_int32 * 4)(), (ctypes.c_int32 * 4)()
+        sizes = (ctypes.c_int64 * 32)()
+        err = ctypes.create_string_buffer(512)
+        rc = ref_host.ref_host_run(str(program).encode(), str(meta).encode(), 2, in_data, in_rank, in_sizes, 4, out_ptrs, caps, widths,
+                                   ranks, sizes, owned, alias, err, 512)
+        assert rc == 0, err.value
+        theirs = []
+        for i in range(4):
+            shp = tuple(sizes[8 * i + d] for d in range(ranks[i]))
+            n = int(np.prod(shp)) if shp else 1
+            theirs.append(np.frombuffer(bufs[i].tobytes()[: n * elem[i]], dtype=dtypes[i]).reshape(shp))
+        with Executable(program, None, [("i64", "cpu"), ("i64", "cpu"), ("f32", "cpu"), ("i64", "cpu")]) as exe:
+            ours = exe.run([x, s])
+        for t, o in zip(theirs, ours):
+            assert t.shape == o.shape and np.array_equal(t, o)
+        assert list(ours[0]) == list(shape) and int(ours[1]) == scalar + 1 == int(ours[3])
+        assert ours[2].shape == (shape[0] * shape[1], shape[2]) and np.array_equal(ours[2].ravel(), x.ravel())
+        assert alias[2] == 0 and alias[0] == alias[1] == alias[3] == -1       # the reference sees out2 as input 0 too
+    # ownership as this library reports it
+    lib = L.load()
+    exe = lib.disc_b200_executable_open(str(program).encode(), None, None)
+    x = np.zeros((2, 2, 2), np.float32)
+    s = np.array(1, np.int64)
+    sizes3 = (ctypes.c_int64 * 3)(2, 2, 2)
+    refs = (BufferRef * 2)(BufferRef(x.ctypes.data, 3, sizes3), BufferRef(s.ctypes.data, 0, None))
+    ex = lib.disc_b200_executable_run(exe, 2, ctypes.cast(refs, ctypes.c_void_p))
+    assert ex
+    codes, ptrs = [], []
+    for k in range(4):
+        data, owned = ctypes.c_void_p(), ctypes.c_int32()
+        assert lib.disc_b200_exec_get_output(ex, k, ctypes.byref(data), None, None, ctypes.byref(owned)) == 0
+        codes.append(owned.value)
+        ptrs.append(data.value)
+    assert codes == [0, 2, 0, 0] and ptrs[2] == x.ctypes.data and ptrs[3] == ptrs[1]
+    lib.disc_b200_exec_destroy(ex)
+    lib.disc_b200_exec_free_host_output(ptrs[1])
+    lib.disc_b200_executable_close(exe)
