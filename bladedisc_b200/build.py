@@ -34,6 +34,7 @@ SOURCES = [
     "ral/metadata.cc",
     "ral/cu_driver_dyn.cc",
     "ral/views.cc",
+    "ral/selfcheck_calls.cc",
     "ral/calls.cc",
     "c_api.cc",
 ]
@@ -63,7 +64,7 @@ def _digest(src: Path) -> str:
 
 
 # no device code and heavy on templates: the host compiler alone (through nvcc for the CUDA include paths)
-HOST_ONLY = {"ral/views.cc"}
+HOST_ONLY = {"ral/views.cc", "ral/selfcheck_calls.cc"}
 
 
 def _compile(nvcc: str, rel: str, obj: Path, verbose: bool) -> None:

@@ -13,6 +13,7 @@
  *     was released with "dealloc".
  *   -DHOST_PROGRAM2: rank-3 and rank-0 inputs, a persistent buffer, a reshape of an input
  *     and a second name for a scalar (see the comment at that entry point).
+ *   -DHOST_PROGRAM3: the reference's two custom_call_v2 test kernels, attributes and a tuple result.
  *   default: a quantized linear on the GPU; weight, bias and scales from ral_const,
  *     the product from ral_pdll_qgemm; out0 = the int8 result, out1 = a host
  *     constant, out2 = a host buffer holding the result's shape. */
@@ -104,6 +105,55 @@ void main(void** cs) {
   o = 2; args[0] = &ctx; args[1] = &o; put1(args, 2, &x);
   disc_ral_call(cs, "ral_send_output___cpu___pvoid_i64_m1df32___void", args);
   o = 3; args[0] = &ctx; args[1] = &o; put2(args, 2, &view);
+  disc_ral_call(cs, "ral_send_output___cpu___pvoid_i64_m2df32___void", args);
+}
+#elif defined(HOST_PROGRAM3)
+/* in0, in1: f32 [r, c].  Calls the two custom_call_v2 test kernels with an attribute blob that is
+ * part of the executable's constant data (ATTRS_BLOB_H defines `static const unsigned char
+ * attrs_blob[]`, generated by the test): out0 = (in0 + in1)^2 from the single-result call,
+ * out1 = in0 + in1 and out2 = (in0 + in1)^2 from the call that returns a tuple: one result slot
+ * per element of the tuple. */
+#include ATTRS_BLOB_H
+void main(void** cs) {
+  void* ctx = 0;
+  void* stream = 0;
+  const void* attrs = attrs_blob;
+  int64_t idx;
+  memref2 a, b, sq, sum2, sq2;
+  memset(&a, 0, sizeof(a));
+  memset(&b, 0, sizeof(b));
+  memset(&sq, 0, sizeof(sq));
+  memset(&sum2, 0, sizeof(sum2));
+  memset(&sq2, 0, sizeof(sq2));
+  idx = 0;
+  { void* args[3] = {&ctx, &idx, &a}; disc_ral_call(cs, "ral_recv_input___cpu___pvoid_i64___m2df32", args); }
+  idx = 1;
+  { void* args[3] = {&ctx, &idx, &b}; disc_ral_call(cs, "ral_recv_input___cpu___pvoid_i64___m2df32", args); }
+  void* args[24];
+  int i = 0;
+  args[i++] = &ctx; args[i++] = &stream;
+  i = put2(args, i, &a);
+  i = put2(args, i, &b);
+  args[i++] = &attrs;
+  args[i++] = &sq;
+  disc_ral_call(cs, "disc.custom_call.test.tf_fused_add_mul___cpu___pvoid_pvoid_m2df32_m2df32_pvoid___m2df32", args);
+  i = 0;
+  args[i++] = &ctx; args[i++] = &stream;
+  i = put2(args, i, &a);
+  i = put2(args, i, &b);
+  args[i++] = &attrs;
+  args[i++] = &sum2;   /* first element of the tuple */
+  args[i++] = &sq2;    /* second element */
+  disc_ral_call(cs,
+                "disc.custom_call.test.tf_fused_add_mul_multi_results___cpu___pvoid_pvoid_m2df32_m2df32_pvoid___"
+                "m2df32_m2df32",
+                args);
+  int64_t o;
+  o = 0; args[0] = &ctx; args[1] = &o; put2(args, 2, &sq);
+  disc_ral_call(cs, "ral_send_output___cpu___pvoid_i64_m2df32___void", args);
+  o = 1; args[0] = &ctx; args[1] = &o; put2(args, 2, &sum2);
+  disc_ral_call(cs, "ral_send_output___cpu___pvoid_i64_m2df32___void", args);
+  o = 2; args[0] = &ctx; args[1] = &o; put2(args, 2, &sq2);
   disc_ral_call(cs, "ral_send_output___cpu___pvoid_i64_m2df32___void", args);
 }
 #elif defined(HOST_PROGRAM2)

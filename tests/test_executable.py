@@ -14,9 +14,10 @@ from bladedisc_b200 import metadata as M
 SRC = Path(__file__).parent / "fake_executable" / "program.c"
 
 
-def build_program(tmp_path, host, variant: int = 1):
-    """host: the host program (variant 1 or 2); else the GPU program."""
-    define = [] if not host else ["-DHOST_PROGRAM" if variant == 1 else "-DHOST_PROGRAM2"]
+def build_program(tmp_path, host, variant: int = 1, extra=()):
+    """host: the host program (variant 1, 2 or 3); else the GPU program."""
+    define = [] if not host else [{1: "-DHOST_PROGRAM", 2: "-DHOST_PROGRAM2", 3: "-DHOST_PROGRAM3"}[variant]]
+    define += list(extra)
     so = tmp_path / (f"host_program{variant}.so" if host else "gpu_program.so")
     cmd = ["gcc", "-shared", "-fPIC", "-O1", "-Wno-main"] + define + ["-o", str(so), str(SRC)]
     subprocess.run(cmd, check=True)
@@ -340,3 +341,55 @@ def test_second_program_on_both_runtimes(built_lib, ref_host, tmp_path):
     lib.disc_b200_exec_destroy(ex)
     lib.disc_b200_exec_free_host_output(ptrs[1])
     lib.disc_b200_executable_close(exe)
+
+
+def test_attributes_and_tuple_results_on_both_runtimes(built_lib, ref_host, tmp_path):
+    """The reference's own custom_call_v2 test kernels (tao_compiler/mlir/ral/context/common_context_impl_pdll.cc)
+    on its runtime, the same-named calls of this library on ours, driven by one program whose attribute blob was
+    written by pack_attrs.  The reference's kernel checks every value of its fixture (and, in its host build, runs
+    its convolution-geometry self-check) before it computes, so finishing at all vouches for the writer; equal
+    outputs vouch for the result-slot convention of a call that returns a tuple."""
+    from bladedisc_b200.executable import Executable
+    from bladedisc_b200.ral import pack_attrs
+    fixture = {
+        "name": "disc.custom_call.test.tf_fused_add_mul", "trueBoolAttr": True, "falseBoolAttr": False, "int127": 127,
+        "intNegative123456": -123456, "float0_001": 0.001, "intArray3int128intNegative32int0": [128, -32, 0],
+        "array2strtest0strtest1": ["test0", "test1"], "array3float0_001float23_0floatNegative0_5": [0.001, 23.0, -0.5],
+        "array5intNegative5floatNegative0_5strtestint30float0_5": [-5, -0.5, "test", 30, 0.5],
+        "rank0I64DenseAttr": np.array(1, np.int64), "rank1UI8DenseAttr": np.array([1], np.uint8),
+        "rank2Shape2x3SplatBoolDenseAttr": np.ones((2, 3), np.int8),
+        "rank2Shape2x3SplatFloatDenseAttr": np.full((2, 3), -0.01, np.float32),
+        "data_format_nhwc": "NHWC", "data_format_nchw": "NCHW", "padding_same": "SAME", "padding_valid": "VALID",
+        "strides1": [1], "strides22": [2, 2], "strides1231": [1, 2, 3, 1],
+        "dilations1": [1], "dilations22": [2, 2], "dilations1231": [1, 2, 3, 1],
+        "explicit_paddings": [0, 0, 1, 2, 3, 4, 0, 0],
+    }
+    blob = pack_attrs(fixture)
+    header = tmp_path / "attrs_blob.h"
+    header.write_text("static const unsigned char attrs_blob[] = {" + ", ".join(str(b) for b in blob) + "};\n")
+    program = build_program(tmp_path, host=True, variant=3, extra=[f'-DATTRS_BLOB_H="{header}"'])
+    meta = tmp_path / "no_constants"
+    M.write_metadata(meta, [])
+    rng = np.random.default_rng(21)
+    a = rng.standard_normal((3, 5)).astype(np.float32)
+    b = rng.standard_normal((3, 5)).astype(np.float32)
+    bufs = [np.zeros(64, np.float32) for _ in range(3)]
+    in_data = (ctypes.c_void_p * 2)(a.ctypes.data, b.ctypes.data)
+    in_rank = (ctypes.c_int32 * 2)(2, 2)
+    in_sizes = (ctypes.c_int64 * 16)(3, 5, 0, 0, 0, 0, 0, 0, 3, 5, 0, 0, 0, 0, 0, 0)
+    out_ptrs = (ctypes.c_void_p * 3)(*[x.ctypes.data for x in bufs])
+    caps = (ctypes.c_int64 * 3)(*[x.nbytes for x in bufs])
+    widths = (ctypes.c_int32 * 3)(4, 4, 4)
+    ranks, owned, alias = (ctypes.c_int32 * 3)(), (ctypes.c_int32 * 3)(), (ctypes.c_int32 * 3)()
+    sizes = (ctypes.c_int64 * 24)()
+    err = ctypes.create_string_buffer(512)
+    rc = ref_host.ref_host_run(str(program).encode(), str(meta).encode(), 2, in_data, in_rank, in_sizes, 3, out_ptrs, caps,
+                               widths, ranks, sizes, owned, alias, err, 512)
+    assert rc == 0, err.value
+    theirs = [bufs[i][:15].reshape(3, 5).copy() for i in range(3)]
+    assert all((ranks[i], sizes[8 * i], sizes[8 * i + 1]) == (2, 3, 5) for i in range(3))
+    with Executable(program, None, [("f32", "cpu")] * 3) as exe:
+        ours = exe.run([a, b])
+    for t, o in zip(theirs, ours):
+        assert np.array_equal(t, o)
+    assert np.array_equal(ours[1], a + b) and np.array_equal(ours[0], (a + b) * (a + b)) and np.array_equal(ours[2], ours[0])
