@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "mlir/ral/context/base/cpu/cpu_context_impl.h"
+#include "mlir/ral/context/common_context_impl_quantization.h"
 #include "mlir/ral/ral_api.h"
 #include "mlir/ral/ral_context.h"
 
@@ -132,6 +133,48 @@ int ref_host_const(const char* metadata_path, const char* call, const char* uniq
   }
   if (n * elem_bytes > cap) return fail(-5, "output buffer too small");
   std::memcpy(out, reinterpret_cast<void*>(result[1]), static_cast<size_t>(n * elem_bytes));
+  return 0;
+}
+
+// The reference's own rules for a convolution's geometry from the attributes of
+// ral_pdll_qconv2d (context/common_context_impl_quantization.h:45-215), called exactly as
+// ral_pdll_qconv_acl_s8_s8_s8_per_channel calls them (common_context_impl_quantization.cc:393-440).
+// Returns 0, or the number of the step that refused the attributes.
+int ref_conv_plan(const char* data_format, const int64_t* strides, int n_strides, const int64_t* dilations,
+                  int n_dilations, const char* padding_str, const int64_t* explicit_paddings, int n_explicit,
+                  int weight_is_const, const int64_t* input_sizes4, const int64_t* weight_sizes4,
+                  int32_t* padding_out4, int64_t* result_sizes4, int32_t* metadata_out17) {
+  using namespace tao::ral;
+  constexpr int NDims = 4;
+  MemRefType<int8_t, NDims> input, weight;
+  for (int i = 0; i < NDims; ++i) {
+    input.sizes[i] = input_sizes4[i];
+    weight.sizes[i] = weight_sizes4[i];
+  }
+  std::vector<int32_t> reorderDims(NDims, 0);
+  if (!generateReorderDims<NDims>(data_format, reorderDims)) return 1;
+  std::vector<int32_t> st(NDims - 2, 0), dl(NDims - 2, 0);
+  if (!generateStrides<NDims>(reorderDims, std::vector<int64_t>(strides, strides + n_strides), st)) return 2;
+  if (!generateDilations<NDims>(reorderDims, std::vector<int64_t>(dilations, dilations + n_dilations), dl)) return 3;
+  MemRefType<int32_t, 1> padding;
+  padding.sizes[0] = (NDims - 2) * 2;
+  padding.data = padding_out4;
+  for (int i = 0; i < 4; ++i) padding_out4[i] = 0;
+  if (std::string(padding_str) == "EXPLICIT") {
+    if (!generateExplicitPaddings<NDims>(reorderDims,
+                                         std::vector<int64_t>(explicit_paddings, explicit_paddings + n_explicit),
+                                         padding))
+      return 4;
+  } else if (!generatePadding<NDims>(input, weight, padding_str, reorderDims, st, dl, padding)) {
+    return 5;
+  }
+  MemRefType<int32_t, 1> metadata;
+  metadata.sizes[0] = NDims * 3 + (NDims - 2) * 2 + 1;
+  metadata.data = metadata_out17;
+  if (!generateMetadata<NDims>(st, dl, reorderDims, weight_is_const != 0, metadata)) return 6;
+  std::vector<int64_t> result(NDims, 0);
+  generateResultShape<NDims>(input, weight, reorderDims, padding, st, dl, result);
+  for (int i = 0; i < NDims; ++i) result_sizes4[i] = result[i];
   return 0;
 }
 

@@ -149,3 +149,45 @@ def test_oracle_against_plain_numpy(built_lib):
     assert (q == want).all()
     q2 = c.qconv2d(x.transpose(0, 3, 1, 2), w, 0.05, sw, 0.3, "NCHW", strides, dil, pad)
     assert (q2 == want.transpose(0, 3, 1, 2)).all()
+
+
+def test_plan_equals_the_reference_functions_on_random_attributes(built_lib, ref_host):
+    """The reference's own generateReorderDims / generateStrides / generateDilations / generatePadding /
+    generateExplicitPaddings / generateMetadata / generateResultShape (compiled from its tree into the host
+    oracle) against disc_b200_qconv2d_plan on a few thousand random attribute sets."""
+    rng = np.random.default_rng(5)
+    arr = lambda v: (ctypes.c_int64 * max(len(v), 1))(*[int(i) for i in v])
+    checked = 0
+    for _ in range(3000):
+        fmt = ["NHWC", "NCHW"][rng.integers(2)]
+        n, c, h, w = (int(rng.integers(1, 5)), int(rng.integers(1, 9)), int(rng.integers(1, 40)), int(rng.integers(1, 40)))
+        in_sizes = (n, h, w, c) if fmt == "NHWC" else (n, c, h, w)
+        kh, kw = int(rng.integers(1, 6)), int(rng.integers(1, 6))
+        w_sizes = (int(rng.integers(1, 9)), kh, kw, c)
+        form = int(rng.integers(3))
+        pick = lambda: int(rng.integers(1, 4))
+        def attr():
+            a, b = pick(), pick()
+            if form == 0:
+                return [a]
+            if form == 1:
+                return [a, b]
+            return [1, a, b, 1] if fmt == "NHWC" else [1, 1, a, b]
+        strides, dilations = attr(), attr()
+        padding = ["SAME", "VALID", "EXPLICIT"][rng.integers(3)]
+        explicit = []
+        if padding == "EXPLICIT":
+            p4 = [int(v) for v in rng.integers(0, 4, 4)]
+            explicit = p4 if rng.integers(2) else ([0, 0] + p4 + [0, 0] if fmt == "NHWC" else [0, 0, 0, 0] + p4)
+        pad_r, res_r, meta_r = (ctypes.c_int32 * 4)(), (ctypes.c_int64 * 4)(), (ctypes.c_int32 * 17)()
+        rc = ref_host.ref_conv_plan(fmt.encode(), arr(strides), len(strides), arr(dilations), len(dilations),
+                                    padding.encode(), arr(explicit), len(explicit), 1, arr(in_sizes), arr(w_sizes), pad_r,
+                                    res_r, meta_r)
+        assert rc == 0
+        pad, res, meta = plan(fmt, strides, dilations, padding, explicit, in_sizes, w_sizes)
+        assert pad == list(pad_r) and meta == list(meta_r), (fmt, strides, dilations, padding, explicit)
+        # (the shape formula is the reference's even where the window does not fit the image and it goes to
+        # zero or below; the convolution call itself refuses such shapes)
+        assert res == list(res_r), (fmt, in_sizes, w_sizes, strides, dilations, padding, explicit)
+        checked += all(v > 0 for v in res_r)
+    assert checked > 2000
