@@ -158,8 +158,14 @@ const ConstEntry* Context::get_const(bool on_device, const char* unique_name, in
     if (!parse_const_name(key, &e.shape, &width)) return fail("unexpected const unique_name format: " + key);
     std::vector<uint8_t> data;
     if (!decode_hex(hex, &data)) return fail("constant " + key + " is not hexadecimal");
+    // the shape comes from a string: refuse what cannot be a tensor in memory before multiplying
+    constexpr int64_t kMaxConstBytes = int64_t{1} << 40;
     int64_t elems = 1;
-    for (int64_t d : e.shape) elems *= d;
+    for (int64_t d : e.shape) {
+      if (d != 0 && elems > kMaxConstBytes / d) return fail("constant " + key + " is larger than 1 TiB");
+      elems *= d;
+    }
+    if (width != 0 && elems > kMaxConstBytes / width) return fail("constant " + key + " is larger than 1 TiB");
     const int64_t want = elems * width;
     if (static_cast<int64_t>(data.size()) < want) {
       // a splat: the stored element repeats (common_context_impl_cuda.cc:97-105)

@@ -282,3 +282,13 @@ def test_host_constants_equal_the_reference_runtime(ctx, ref_host, ref_ral, tmp_
     want = theirs(odd, "0_i32_2", "i32", np.int32, 1, 0)
     code, msg, r = _host_const(lib, c, e, "0_i32_2", 0, 1, "i32")
     assert code == 0 and np.array_equal(_array(r, np.int32), want) and list(want) == [7, 7]
+
+
+def test_a_name_that_claims_an_impossible_shape_is_refused(ctx, tmp_path):
+    lib, c, e = ctx
+    name = "0_f32_1099511627776x1099511627776"          # 2^80 elements: the product must not be trusted
+    path = tmp_path / "huge"
+    M.write_metadata(path, [(name, True, np.float32(1.0))])
+    assert lib.disc_b200_context_load_metadata(c, str(path).encode()) == 0
+    code, msg, r = _host_const(lib, c, e, name, 0, 2)
+    assert code != 0 and "larger than 1 TiB" in msg and r.data == 0
