@@ -668,9 +668,13 @@ int32_t disc_b200_kernel_status(void) { return disc_b200::kernel_status_fetch_an
 const char* disc_b200_version(void) { return "disc-b200-ral 0.1 (sm_100a)"; }
 
 int32_t disc_b200_attrs_describe(const void* blob, char* out, int32_t capacity) {
-  if (!blob || !out || capacity <= 0) return -1;
+  return disc_b200_attrs_describe_bounded(blob, int64_t{1} << 30, out, capacity);
+}
+
+int32_t disc_b200_attrs_describe_bounded(const void* blob, int64_t blob_bytes, char* out, int32_t capacity) {
+  if (!blob || !out || capacity <= 0 || blob_bytes < 0) return -1;
   const uint8_t* cur = static_cast<const uint8_t*>(blob);
-  auto a = disc_b200::ral::parse_attr(&cur);
+  auto a = disc_b200::ral::parse_attr(&cur, blob_bytes);
   if (!a) return -1;
   std::string text;
   render(*a, text);

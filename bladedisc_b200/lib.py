@@ -157,6 +157,7 @@ SIGNATURES = {
     "disc_b200_kernel_status": (c_int32, []),
     "disc_b200_version": (c_char_p, []),
     "disc_b200_attrs_describe": (c_int32, [c_void_p, c_char_p, c_int32]),
+    "disc_b200_attrs_describe_bounded": (c_int32, [c_void_p, c_int64, c_char_p, c_int32]),
 }
 
 _lib = None

@@ -479,6 +479,8 @@ const char* disc_b200_version(void);
  * {a: true, b: 127, c: "s", d: [1, 2], e: dense<int64[2]>} into `out`.
  * Returns the length written, or -1 if the blob does not parse. */
 int32_t disc_b200_attrs_describe(const void* blob, char* out, int32_t capacity);
+/* The same for a blob whose size is known: nothing past blob_bytes is read. */
+int32_t disc_b200_attrs_describe_bounded(const void* blob, int64_t blob_bytes, char* out, int32_t capacity);
 
 #ifdef __cplusplus
 }
