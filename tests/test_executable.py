@@ -393,3 +393,30 @@ def test_attributes_and_tuple_results_on_both_runtimes(built_lib, ref_host, tmp_
     for t, o in zip(theirs, ours):
         assert np.array_equal(t, o)
     assert np.array_equal(ours[1], a + b) and np.array_equal(ours[0], (a + b) * (a + b)) and np.array_equal(ours[2], ours[0])
+
+
+def test_concurrent_executions_share_one_context(built_lib, tmp_path):
+    """One context, one execution context per inference, several threads at once
+    (the reference's threading contract: tao_compiler/mlir/ral/ral_context.cc:83-93)."""
+    import threading
+    from bladedisc_b200.executable import Executable
+    program = build_program(tmp_path, host=True)
+    const = np.linspace(0, 1, 8).astype(np.float32)
+    meta = tmp_path / "meta"
+    M.write_metadata(meta, [("0_f32_8", True, const)])
+    wrong = []
+    with Executable(program, meta, [("f32", "cpu")] * 4) as exe:
+        def worker(seed):
+            rng = np.random.default_rng(seed)
+            for _ in range(100):
+                n = int(rng.integers(1, 9))
+                x = rng.standard_normal(n).astype(np.float32)
+                y, c, same, view = exe.run([x])
+                if not (np.array_equal(y, x + const[:n]) and np.array_equal(same, x) and view.shape == (1, n)):
+                    wrong.append(seed)
+        threads = [threading.Thread(target=worker, args=(s,)) for s in range(4)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+    assert not wrong
