@@ -135,6 +135,46 @@ def bench_weight_only(M, K, N, hbm, iters):
             "tops": 2.0 * M * N * K / (ms * 1e-3) / 1e12, "gbs": gbs, "bound": "hbm", "frac": gbs / hbm, "sets": n_sets}
 
 
+def bench_qconv(n, h, w, c, o, k, stride, hbm, tops_peak, iters):
+    """int8 NHWC convolution, SAME padding: algorithmic bytes = input + kernel + output once."""
+    dev = "cuda"
+    oh, ow = (h + stride - 1) // stride, (w + stride - 1) // stride
+    algo_bytes = n * h * w * c + o * k * k * c + n * oh * ow * o + 4 * o
+    n_sets = copies_for(algo_bytes)
+    g = torch.Generator(device=dev).manual_seed(n + h + c + o)
+    xs = [torch.randint(-127, 128, (n, h, w, c), dtype=torch.int8, device=dev, generator=g) for _ in range(n_sets)]
+    wt = torch.randint(-127, 128, (o, k, k, c), dtype=torch.int8, device=dev, generator=g)
+    sw = torch.rand(o, device=dev, generator=g) * 4e-3 + 1e-3
+    sx, so = torch.tensor([0.02], device=dev), torch.tensor([0.1], device=dev)
+    torch.cuda.synchronize()
+    fns = [(lambda x=x: ops.qconv2d(x, wt, sx, sw, so, "NHWC", [stride], [1], "SAME")) for x in xs]
+    ms = time_ms(fns, iters)
+    macs = n * oh * ow * o * k * k * c
+    t_tensor = 2.0 * macs / (tops_peak * 1e12)
+    t_hbm = algo_bytes / (hbm * 1e9)
+    return {"kernel": "qconv2d", "M": n * oh * ow, "K": k * k * c, "N": o, "out": "int8", "us": ms * 1e3,
+            "tops": 2.0 * macs / (ms * 1e-3) / 1e12, "gbs": algo_bytes / (ms * 1e-3) / 1e9,
+            "bound": "tensor" if t_tensor >= t_hbm else "hbm", "frac": max(t_tensor, t_hbm) / (ms * 1e-3), "sets": n_sets}
+
+
+def bench_observer(shape, axis, dtype, hbm, iters):
+    """Min / max observer: one read of the tensor."""
+    from bladedisc_b200.observer import MinMaxObserver, PerChannelMinMaxObserver
+    dev = "cuda"
+    nbytes = int(torch.tensor(shape).prod()) * (2 if dtype == torch.float16 else 4)
+    n_sets = copies_for(nbytes)
+    g = torch.Generator(device=dev).manual_seed(7)
+    xs = [torch.randn(shape, device=dev, generator=g).to(dtype) for _ in range(n_sets)]
+    ob = MinMaxObserver() if axis is None else PerChannelMinMaxObserver(ch_axis=axis)
+    ob(xs[0])
+    torch.cuda.synchronize()
+    fns = [(lambda x=x: ob(x)) for x in xs]
+    ms = time_ms(fns, iters)
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"kernel": "observe_minmax" + ("" if axis is None else f"_axis{axis}"), "rows": shape[0], "cols": shape[-1],
+            "dtype": str(dtype).split(".")[-1], "us": ms * 1e3, "gbs": gbs, "frac": gbs / hbm}
+
+
 def bench_rows(name, rows, cols, dtype, hbm, iters):
     dev = "cuda"
     eb = 2 if dtype == torch.float16 else 4
@@ -240,6 +280,21 @@ def main():
                 out["rows"].append(r)
                 print(f"{r['kernel']:<18}{M:>4}{K:>6}{N:>7}{r['out']:>9}{r['us']:>10.2f}{r['tops']:>9.1f}{r['gbs']:>9.0f}"
                       f"{r['bound']:>8}{r['frac']:>7.2f}", flush=True)
+    if only and any("qconv" in o for o in only):
+        # (batch, height, width, channels in, channels out, window, stride): ResNet-50-shaped layers
+        for n, h, w, c, o, k, st in ((32, 56, 56, 64, 64, 3, 1), (32, 28, 28, 128, 128, 3, 1), (32, 14, 14, 256, 256, 3, 1),
+                                     (32, 56, 56, 64, 256, 1, 1), (32, 56, 56, 256, 128, 1, 2)):
+            r = bench_qconv(n, h, w, c, o, k, st, hbm, tops_peak, 3 if args.eager else 30)
+            out["rows"].append(r)
+            print(f"{r['kernel']:<16}{r['M']:>7}{r['K']:>6}{r['N']:>6}{r['out']:>9}{r['us']:>10.2f}{r['tops']:>9.1f}{r['gbs']:>9.0f}"
+                  f"{r['bound']:>8}{r['frac']:>7.2f}", flush=True)
+    if only and any("observe" in o for o in only):
+        for shape, axis, dt in (((16384, 4096), None, torch.float16), ((16384, 4096), None, torch.float32),
+                                ((4096, 4096), 0, torch.float32), ((16384, 768), 1, torch.float16)):
+            r = bench_observer(shape, axis, dt, hbm, 3 if args.eager else 50)
+            out["rows"].append(r)
+            print(f"{r['kernel']:<22}{r['rows']:>8}{r['cols']:>7}{r['dtype']:>9}{r['us']:>10.2f}{r['gbs']:>9.0f}{r['frac']:>7.2f}",
+                  flush=True)
     row_cases = [("quantize", 16384, 768, torch.float32), ("quantize", 16384, 3072, torch.float16),
                  ("dynamic_quantize", 16384, 4096, torch.float16), ("layernorm", 16384, 768, torch.float16),
                  ("add_layernorm_quant", 16384, 768, torch.float16), ("add_layernorm_quant", 32768, 1024, torch.float16),
