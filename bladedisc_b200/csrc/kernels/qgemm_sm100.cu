@@ -26,6 +26,7 @@
 #include <mutex>
 #include <type_traits>
 
+#include "device_info.h"
 #include "qgemm.h"
 #include "rowops.h"
 #include "sm100_ptx.cuh"
@@ -844,16 +845,7 @@ bool make_tmap(CUtensorMap* tm, const int8_t* base, int64_t rows, int64_t K, int
   return r == CUDA_SUCCESS;
 }
 
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
+int sm_count() { return device_sm_count(); }
 
 EpiParams make_epi(const QGemmParams& p) {
   EpiParams e;
@@ -878,6 +870,7 @@ EpiParams make_epi(const QGemmParams& p) {
 int out_elem_bytes(int dt) { return dt == kOutI8 ? 1 : (dt == kOutF16 ? 2 : 4); }
 
 bool tma_ok(const QGemmParams& p) {
+  if (p.lda <= 0 || p.ldw <= 0) return false;
   if (p.a_slabs > 1 && (p.a_slab_cols % 16 != 0 || p.a_slab_stride % p.lda != 0)) return false;
   return p.K % 16 == 0 && p.lda % 16 == 0 && p.ldw % 16 == 0 &&
          (reinterpret_cast<uintptr_t>(p.a) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.w) & 15) == 0;
@@ -988,7 +981,9 @@ bool make_out_tmap(CUtensorMap* tm, void* base, int64_t rows, int64_t row_bytes,
 
 template <typename OutT>
 int pair_max_clusters() {
-  static int n = 0;
+  static std::atomic<int> cache[kMaxDeviceOrdinals];  // per instantiation and device
+  const int dev = current_device_ordinal();
+  int n = cache[dev].load(std::memory_order_relaxed);
   if (n == 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 74);
@@ -1007,6 +1002,7 @@ int pair_max_clusters() {
       c = sm_count() / 2;
     }
     n = c;
+    cache[dev].store(n, std::memory_order_relaxed);
   }
   return n;
 }
@@ -1279,12 +1275,27 @@ cudaError_t qgemm_small_m_noalloc_launch(const QGemmParams& in, cudaStream_t str
     if (err) *err = "no-alloc small-M qgemm: extent exceeds 2^31-1";
     return cudaErrorInvalidValue;
   }
+  // The small-M kernel reads a plain row-major activation: the gathered slab
+  // layout would be taken for overlapping rows, so it is refused here (the
+  // regular entry point routes slabs to other kernels).
+  if (in.a_slabs > 1) {
+    if (err) *err = "no-alloc small-M qgemm: the gathered (slab) activation layout is not supported";
+    return cudaErrorInvalidValue;
+  }
+  if (in.lda < in.K || in.ldw < in.K || in.ldo < in.N) {
+    if (err) *err = "no-alloc small-M qgemm: a row stride is smaller than the row";
+    return cudaErrorInvalidValue;
+  }
   if (!tma_ok(in)) {
     if (err) *err = "no-alloc small-M qgemm: K and the row strides must be multiples of 16, bases 16-byte aligned";
     return cudaErrorInvalidValue;
   }
   if ((in.fold_out_scale || in.div_out_scale) && !in.out_scale) {
     if (err) *err = "no-alloc small-M qgemm: out_scale required";
+    return cudaErrorInvalidValue;
+  }
+  if (in.div_out_scale && in.out_scale_kind == kScalePerCol) {
+    if (err) *err = "no-alloc small-M qgemm: per-channel out_scale only in folded form";
     return cudaErrorInvalidValue;
   }
   QGemmParams p = in;

@@ -23,6 +23,7 @@
 #include <cuda_runtime.h>
 #include <float.h>
 
+#include "device_info.h"
 #include "rowops.h"
 #include "sm100_ptx.cuh"
 
@@ -32,16 +33,7 @@ namespace {
 constexpr int kBlock = 256;
 constexpr float kRoundMagic = 12582912.f;  // 1.5 * 2^23: (x + m) - m rounds half-to-even for |x| < 2^22
 
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
+int sm_count() { return device_sm_count(); }
 
 // x / s wherever the exact IEEE quotient decides the integer result.  The
 // product with the (correctly rounded) reciprocal is within 2 ulp of the true

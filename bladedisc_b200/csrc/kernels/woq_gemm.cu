@@ -33,6 +33,8 @@
 // issue-bound beyond.
 #include "woq_gemm.h"
 
+#include "device_info.h"
+
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
 
@@ -321,27 +323,14 @@ __global__ void __launch_bounds__(256) woq_gemm_simple_kernel(WoqGemmParams p) {
   static_cast<T*>(p.out)[m * p.ldo + n] = from_f32<T>(acc);
 }
 
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
-      n = 148;
-    }
-  }
-  return n;
-}
+int sm_count() { return device_sm_count(); }
 
 template <typename T, int MT, int C>
 cudaError_t launch_tile(const WoqGemmParams& p, int64_t m0, const Plan& pl, cudaStream_t s) {
   auto kern = woq_gemm_kernel<T, MT, C>;
-  static bool configured = false;  // per instantiation; the attribute is per function, set once
-  if (!configured) {
-    cudaError_t st = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemLimit));
-    if (st != cudaSuccess) return st;
-    configured = true;
-  }
+  // the attribute belongs to the function on the current device: set on every launch (cheap), never cached
+  cudaError_t st = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemLimit));
+  if (st != cudaSuccess) return st;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(pl.strips, pl.cluster);
   cfg.blockDim = dim3(kThreads);

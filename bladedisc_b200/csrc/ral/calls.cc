@@ -314,8 +314,9 @@ int64_t leading_rows(const MemRef<int8_t, N>& in, int64_t* result_sizes, int64_t
 bool run_qgemm(ExecContext* ctx, QGemmParams& p) {
   if (p.M <= 128) {
     const int64_t need = qgemm_splitk_ws_bytes(p.M, p.N, p.K);
-    p.splitk_ws = static_cast<int32_t*>(ctx->ctx->get_splitk_ws(need));
-    p.splitk_ws_bytes = p.splitk_ws ? ctx->ctx->splitk_ws_bytes : 0;
+    int64_t have = 0;
+    p.splitk_ws = static_cast<int32_t*>(ctx->ctx->get_splitk_ws(need, &have));
+    p.splitk_ws_bytes = p.splitk_ws ? have : 0;
   }
   const char* detail = nullptr;
   cudaError_t st = qgemm_launch(p, stream_of(ctx), &detail);
@@ -1226,8 +1227,9 @@ bool run_qconv(ExecContext* ctx, const ConvGeometry& geo, const int8_t* x, const
   const int64_t rows = geo.batch * geo.out_h * geo.out_w;
   if (rows <= 128) {
     const int64_t kp = (geo.k_h * geo.k_w * geo.in_ch + 15) / 16 * 16;
-    p.splitk_ws = static_cast<int32_t*>(ctx->ctx->get_splitk_ws(qgemm_splitk_ws_bytes(rows, geo.out_ch, kp)));
-    p.splitk_ws_bytes = p.splitk_ws ? ctx->ctx->splitk_ws_bytes : 0;
+    int64_t have = 0;
+    p.splitk_ws = static_cast<int32_t*>(ctx->ctx->get_splitk_ws(qgemm_splitk_ws_bytes(rows, geo.out_ch, kp), &have));
+    p.splitk_ws_bytes = p.splitk_ws ? have : 0;
   }
   const char* detail = nullptr;
   const cudaError_t st = qconv_launch(p, stream_of(ctx), &detail);

@@ -84,16 +84,19 @@ bool Context::ok() {
   return status == 0;
 }
 
-void* Context::get_splitk_ws(int64_t bytes) {
+void* Context::get_splitk_ws(int64_t bytes, int64_t* have) {
   std::lock_guard<std::mutex> l(mu);
-  if (bytes <= splitk_ws_bytes) return splitk_ws;
-  // Work queued on the stream may still use the old block.
-  cudaStreamSynchronize(stream);
-  if (splitk_ws) raw_free(splitk_ws);
-  int64_t want = bytes < (8 << 20) ? (8 << 20) : bytes;
-  splitk_ws = raw_alloc(static_cast<size_t>(want));
-  splitk_ws_bytes = splitk_ws ? want : 0;
-  if (splitk_ws) cudaMemsetAsync(splitk_ws, 0, static_cast<size_t>(want), stream);
+  if (bytes > splitk_ws_bytes) {
+    // Another thread may already hold the old block for a launch it has not
+    // issued yet, and launches queued on the stream may still use it: the old
+    // block is kept until the context dies instead of being freed here.
+    if (splitk_ws) retired_splitk_ws.push_back(splitk_ws);
+    int64_t want = bytes < (8 << 20) ? (8 << 20) : bytes;
+    splitk_ws = raw_alloc(static_cast<size_t>(want));
+    splitk_ws_bytes = splitk_ws ? want : 0;
+    if (splitk_ws) cudaMemsetAsync(splitk_ws, 0, static_cast<size_t>(want), stream);
+  }
+  if (have) *have = splitk_ws_bytes;
   return splitk_ws;
 }
 
@@ -252,6 +255,7 @@ Context::~Context() {
   }
   for (void* p : persistent) raw_free(p);
   if (splitk_ws) raw_free(splitk_ws);
+  for (void* old : retired_splitk_ws) raw_free(old);
   magic = 0;
 }
 

@@ -81,13 +81,15 @@ struct Context {
   // Scratch of the small-M qgemm path (grown on demand, counters kept zero).
   void* splitk_ws = nullptr;
   int64_t splitk_ws_bytes = 0;
+  std::vector<void*> retired_splitk_ws;  // outgrown blocks, freed with the context
 
   void* raw_alloc(size_t bytes);
   void raw_free(void* p);
   void signal_error(int32_t code, const std::string& msg);
   bool ok();
   // Returns scratch of at least `bytes`, zeroed when (re)allocated.
-  void* get_splitk_ws(int64_t bytes);
+  // Scratch of at least `bytes`; `have` receives its size (pointer and size are read under one lock).
+  void* get_splitk_ws(int64_t bytes, int64_t* have);
   // Size and rank of nccl_comm (queried once); false, with an error signalled,
   // when there is no communicator or NCCL cannot be reached.
   bool comm_info(int* size, int* rank);

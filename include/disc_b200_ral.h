@@ -206,7 +206,9 @@ int32_t disc_b200_qgemm_path(const disc_b200_qgemm_args* args);
  * caller still provides inputs and outputs.
  *   - Limits: M <= 128, K and row strides multiples of 16 with 16-byte aligned
  *     bases (the TMA rules), and split * M * round_up(N, 128) * 4 + 16 KiB must
- *     fit the array (disc_b200_qgemm_small_m_noalloc_capacity() bytes);
+ *     fit the array (disc_b200_qgemm_small_m_noalloc_capacity() bytes); the
+ *     activation must be plain row-major (a_slabs <= 1), every row stride at
+ *     least its row, and a per-channel out_scale only in folded form;
  *     anything else is refused with a message, never silently redirected.
  *   - The first call on each device looks up the array's device address; make
  *     that first call before starting any stream capture.

@@ -7,7 +7,11 @@ heap, ...).  For them `disc_b200_qgemm_small_m_noalloc` keeps the scratch in an
 array built into the library.  The test checks it against the ordinary entry
 point `disc_b200_qgemm` on two calls in a row (the second call sees whatever
 the first left in the shared array), bit for bit: both compute exact integer
-sums followed by the same epilogue.
+sums followed by the same epilogue.  Because both entry points end in the same
+kernel, the results are also compared with the CPU oracle, differently shaped
+problems are interleaved on the shared array, and the property the entry point
+exists for is checked directly: device memory in use does not change across
+calls after the first.
 
 The file name sorts last on purpose: a run that stops at the first failure has
 then already run every other test.
@@ -74,6 +78,58 @@ def test_noalloc_matches_regular_entry_point_twice(M, K, N, split):
                 lib.disc_b200_last_error_string()
             torch.cuda.synchronize()
             assert torch.equal(got, want), f"call {call}, out dtype {tdtype}"
+            # and against the CPU oracle, not only against the other entry point
+            from oracle import c
+            acc = c.qgemm_acc(a.cpu().numpy(), w.cpu().numpy())
+            if out_dtype == L.OUT_I32:
+                assert (got.cpu().numpy() == acc).all(), f"call {call}: accumulators differ from the oracle"
+            else:
+                f_want, q_want = c.qgemm_epilogue(acc, x_scale=np.float32(0.02), w_scale=sw.cpu().numpy(),
+                                                  out_scale=np.float32(0.05) if div else None,
+                                                  bias=bias.cpu().numpy(), div_out=div)
+                if out_dtype == L.OUT_I8:
+                    assert (got.cpu().numpy() == q_want).all(), f"call {call}: int8 result differs from the oracle"
+                else:
+                    assert np.allclose(got.float().cpu().numpy(), f_want, rtol=1e-2, atol=1e-3)
+    assert lib.disc_b200_kernel_status() == 0
+
+
+def test_noalloc_interleaved_shapes_share_the_array_and_allocate_nothing():
+    """A large split followed by a small one (and back) on the one shared array: stale partial sums and
+    counters of the other shape must not leak into a result, and no call may change the device memory in use."""
+    from bladedisc_b200 import lib as L
+    from oracle import c
+    lib = L.load()
+    rng = np.random.default_rng(99)
+    dev = "cuda"
+    stream = torch.cuda.current_stream().cuda_stream
+    shapes = [(128, 2048, 1024, 8), (16, 512, 256, 2), (64, 4096, 384, 8), (3, 256, 128, 2)]
+    ops = []
+    for M, K, N, split in shapes:
+        a = rng.integers(-127, 128, (M, K), dtype=np.int8)
+        w = rng.integers(-127, 128, (N, K), dtype=np.int8)
+        ops.append((torch.from_numpy(a).to(dev), torch.from_numpy(w).to(dev),
+                    torch.empty((M, N), dtype=torch.int32, device=dev), c.qgemm_acc(a, w), split))
+
+    def run_all():
+        for a, w, out, _, split in ops:
+            out.fill_(-1)
+            g = _args(L, a, w, out, out_dtype=L.OUT_I32, split=split)
+            assert lib.disc_b200_qgemm_small_m_noalloc(ctypes.byref(g), stream) == 0, \
+                lib.disc_b200_last_error_string()
+
+    run_all()  # the first call on a device looks up the array's address
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    alloc0 = torch.cuda.memory_allocated()
+    for _ in range(3):
+        run_all()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, "device memory in use changed across no-alloc calls"
+    assert torch.cuda.memory_allocated() == alloc0
+    for a, w, out, want, split in ops:
+        assert (out.cpu().numpy() == want).all(), f"shape {tuple(a.shape)} x {tuple(w.shape)} split {split}"
     assert lib.disc_b200_kernel_status() == 0
 
 
@@ -103,4 +159,31 @@ def test_noalloc_rejects_what_it_cannot_hold():
     g = _args(L, a, w, out, out_dtype=L.OUT_I32)
     assert lib.disc_b200_qgemm_small_m_noalloc(ctypes.byref(g), stream) != 0
     assert b"multiples of 16" in lib.disc_b200_last_error_string()
+    # the gathered (slab) activation layout belongs to other kernels: refused, not misread
+    a = torch.zeros((2, 16, 128), dtype=torch.int8, device=dev)
+    w = torch.zeros((128, 256), dtype=torch.int8, device=dev)
+    out = torch.full((16, 128), 55, dtype=torch.int32, device=dev)
+    g = _args(L, a[0], w, out, out_dtype=L.OUT_I32)
+    g.K, g.lda, g.a_slabs, g.a_slab_cols, g.a_slab_stride = 256, 128, 2, 128, 16 * 128
+    assert lib.disc_b200_qgemm_small_m_noalloc(ctypes.byref(g), stream) != 0
+    assert b"slab" in lib.disc_b200_last_error_string()
+    # ... also with a zero row stride, which must not reach a division
+    g.lda = 0
+    assert lib.disc_b200_qgemm_small_m_noalloc(ctypes.byref(g), stream) != 0
+    # row strides below the row length
+    a = torch.zeros((4, 256), dtype=torch.int8, device=dev)
+    out = torch.full((4, 128), 55, dtype=torch.int32, device=dev)
+    for field in ("lda", "ldw", "ldo"):
+        g = _args(L, a, w, out, out_dtype=L.OUT_I32)
+        setattr(g, field, 0)
+        assert lib.disc_b200_qgemm_small_m_noalloc(ctypes.byref(g), stream) != 0
+        assert b"row stride" in lib.disc_b200_last_error_string()
+    # division by a per-channel output scale exists only in folded form
+    so = torch.full((128,), 0.05, device=dev)
+    out8 = torch.full((4, 128), 55, dtype=torch.int8, device=dev)
+    g = _args(L, a, w, out8, out_scale=so, div_out=True, out_dtype=L.OUT_I8)
+    g.out_scale_kind = L.SCALE_PER_COL
+    assert lib.disc_b200_qgemm_small_m_noalloc(ctypes.byref(g), stream) != 0
+    assert b"folded form" in lib.disc_b200_last_error_string()
     torch.cuda.synchronize()
+    assert (out == 55).all() and (out8 == 55).all()  # a refused call writes nothing
