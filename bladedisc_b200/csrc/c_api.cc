@@ -106,6 +106,7 @@ disc_b200::QGemmParams to_params(const disc_b200_qgemm_args* a) {
   p.bias_kind = a->bias ? a->bias_kind : disc_b200::kBiasNone;
   p.fold_out_scale = a->fold_out_scale;
   p.div_out_scale = a->div_out_scale;
+  p.div_exact = a->div_exact;
   p.act = a->act;
   p.out_dtype = a->out_dtype;
   p.path = a->path;

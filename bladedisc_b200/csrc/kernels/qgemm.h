@@ -28,7 +28,10 @@ enum QGemmPath : int {
 //                                           host-side "kernel scale", computed here
 //                                           on the device in the same order)
 //   v  = fma(t, cs, bias[n]);  v = act(v)
-//   v  = v / out_scale                      when div_out_scale (quantize-op form)
+//   v  = v / out_scale                      when div_out_scale (quantize-op form);
+//                                           as v * (1 / out_scale) unless div_exact,
+//                                           which differs from the quotient by at most
+//                                           one int8 level, at rounding ties only
 //   out = int8: sat(rne(v)) | f16 | f32 ; kOutI32 stores acc unchanged.
 struct QGemmParams {
   const int8_t* a;
@@ -46,6 +49,7 @@ struct QGemmParams {
   int bias_kind;       // QGemmBias
   int fold_out_scale;
   int div_out_scale;
+  int div_exact;  // with div_out_scale: the correctly rounded IEEE quotient instead of the reciprocal product
   int act;        // QGemmAct
   int out_dtype;  // QGemmOut
   int path;       // QGemmPath (tests force a path; callers leave kPathAuto)

@@ -94,7 +94,9 @@ qgemm_gemv_kernel(const int8_t* __restrict__ a, const int8_t* __restrict__ w, in
         if (lane == m) mine = acc[r][m];
       if (lane < M && n < N) {
         if (ctx.has_rs) ctx.rs = __ldg(ep.x_scale + lane);
-        const float v = epi_value(mine, col_scale(ep, n), col_bias(ep, n), ctx);
+        float cs, cb;
+        col_consts(ep, ctx, n, cs, cb);
+        const float v = epi_value(mine, cs, cb, ctx);
         store_one<OutT>(out + static_cast<int64_t>(lane) * ep.ldo + n, v, mine);
       }
     }

@@ -35,7 +35,7 @@ struct PairSmem {
 // One epilogue warp's share of a pair tile: 64 columns of its 32 rows, handed
 // to TMA stores in pieces of 32 rows x 64 bytes (or stored directly when the
 // output rows are not 16-byte aligned).
-template <typename OutT, int ACT, bool DIV, bool RS>
+template <typename OutT, int ACT, int DIV, bool RS>
 __device__ __forceinline__ void pair_epilogue_cols(uint32_t t_row, const float* cs, const float* cb,
                                                    const EpiCtx& ctx, OutT* out, int64_t row0, int lane,
                                                    int64_t col0, int64_t M, int64_t N, int64_t ldo,
@@ -259,17 +259,33 @@ qgemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     bool ok = true;
     EpiCtx ctx = make_epi_ctx(ep);
     OutT* out = reinterpret_cast<OutT*>(ep.out);
+    // Column constants of the tile after the current one travel in registers:
+    // their loads are issued before the current tile's arithmetic and finished
+    // after it.  Fetched in line they were four dependent trips to L2 per tile
+    // on the epilogue warps' critical path, more than a short-K main loop takes.
+    constexpr int CPL = CW / 32;  // columns per lane
+    ColRaw raw[CPL];
+    auto request_consts = [&](int tile) {
+      const int64_t c0 = static_cast<int64_t>(tile % tiles_n) * BN + g * CW;
+#pragma unroll
+      for (int i = 0; i < CPL; ++i) {
+        const int64_t n = c0 + lane + 32 * i;
+        raw[i] = col_raw_load(ep, n < ep.N ? n : ep.N - 1);
+      }
+    };
+    if (cluster_id < num_tiles) request_consts(cluster_id);
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       const int m_blk = tile / tiles_n;
       const int n_blk = tile % tiles_n;
       const int64_t col0 = static_cast<int64_t>(n_blk) * BN + g * CW;
       __syncwarp();
-      for (int j = lane; j < CW; j += 32) {
-        const int64_t n = col0 + j;
-        cs[j] = n < ep.N ? col_scale(ep, n) : 0.f;
-        cb[j] = n < ep.N ? col_bias(ep, n) : 0.f;
+#pragma unroll
+      for (int i = 0; i < CPL; ++i) {
+        const int j = lane + 32 * i;
+        col_raw_finish(ep, ctx, raw[i], col0 + j < ep.N, cs[j], cb[j]);
       }
       __syncwarp();
+      if (tile + num_clusters < num_tiles) request_consts(tile + num_clusters);
       ok = mbar_wait(tfull_bar(acc_buf), acc_phase, abort_flag, &g_kernel_status,
                      kStatusTimeoutTmemFull);
       if (!ok) break;

@@ -24,7 +24,7 @@ constexpr int kSkinnyScaleOffset = kSkinnyBarOffset + 256;
 constexpr int kSkinnyDynamic = kSkinnyScaleOffset + 2 * 128 * 4 + 1024;
 constexpr int kSkinnyMaxBN = 128;
 
-template <typename OutT, int ACT, bool DIV, bool RS>
+template <typename OutT, int ACT, int DIV, bool RS>
 __device__ __forceinline__ void skinny_epilogue_cols(uint32_t t_row, const float* cs, const float* cb,
                                                      const EpiCtx& ctx, OutT* out, int64_t m,
                                                      bool row_ok, int64_t col0, int64_t N,
@@ -196,13 +196,14 @@ qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const int et = threadIdx.x - 64;
     grid_dep_wait();  // scales may come from the kernel before this one; the output may still be read by it
     // Column constants while the weight streams.
+    EpiCtx ctx = make_epi_ctx(ep);
     for (int i = et; i < BN; i += kThreads - 64) {
       const int64_t n = n0 + i;
-      const bool n_ok = n < ep.N;
-      s_cs[i] = n_ok ? col_scale(ep, n) : 0.f;
-      s_cb[i] = n_ok ? col_bias(ep, n) : 0.f;
+      float cs = 0.f, cb = 0.f;
+      if (n < ep.N) col_consts(ep, ctx, n, cs, cb);
+      s_cs[i] = cs;
+      s_cb[i] = cb;
     }
-    EpiCtx ctx = make_epi_ctx(ep);
     const int64_t m = m0 + q * 32 + lane;
     const bool row_ok = m < ep.M;
     if (ctx.has_rs && row_ok) ctx.rs = __ldg(ep.x_scale + m);

@@ -45,7 +45,7 @@ struct EpiParams {
   const float* w_scale;
   const float* out_scale;
   const void* bias;
-  int x_kind, w_kind, o_kind, bias_kind, fold_out, div_out, act;
+  int x_kind, w_kind, o_kind, bias_kind, fold_out, div_out, div_exact, act;
 };
 
 // Where K block `kb` of the two operands starts when the activation is stored
@@ -108,21 +108,80 @@ struct EpiCtx {
   float so_inv;  // correctly rounded 1 / so
   int act;
   bool has_rs;
-  bool div_out;
+  int div;        // kDivNone, kDivRecip (product with 1 / so) or kDivExact (the IEEE quotient)
+  bool folded;    // kDivRecip without an activation: 1 / so already sits in the column constants
   bool div_fast;  // so is in the range where the reciprocal sequence below is safe
 };
+
+// How the value is brought to the output scale before rounding to int8.
+//   kDivRecip  v * (1 / so) with the correctly rounded reciprocal: a few ulp from
+//              the quotient, so the int8 result can differ from the divide-based
+//              formula only for quotients that close to a rounding tie, and then
+//              by one level (the tolerance the quantized path states for
+//              requantized outputs).  Without an activation the factor is folded
+//              into the column scale and bias and costs nothing per element.
+//   kDivExact  bit for bit what the reference's divide-based quantize computes.
+enum DivMode : int { kDivNone = 0, kDivRecip = 1, kDivExact = 2 };
 
 __device__ __forceinline__ EpiCtx make_epi_ctx(const EpiParams& e) {
   EpiCtx c;
   c.rs = 1.f;
   c.has_rs = e.x_kind == kScalePerRow;
   c.act = e.act;
-  c.div_out = e.div_out != 0;
-  c.so = c.div_out ? __ldg(e.out_scale) : 1.f;
+  c.div = e.div_out ? (e.div_exact ? kDivExact : kDivRecip) : kDivNone;
+  c.so = c.div != kDivNone ? __ldg(e.out_scale) : 1.f;
   c.so_inv = __frcp_rn(c.so);
   const float a = fabsf(c.so);
   c.div_fast = a > 1e-15f && a < 1e15f;
+  // a reciprocal that is zero, infinite or subnormal would not stand for the division
+  if (c.div == kDivRecip && !c.div_fast) c.div = kDivExact;
+  c.folded = c.div == kDivRecip && c.act == kActNone;
   return c;
+}
+
+// Scale and bias of output channel n as the epilogue uses them.
+__device__ __forceinline__ void col_consts(const EpiParams& e, const EpiCtx& c, int64_t n, float& cs, float& cb) {
+  cs = col_scale(e, n);
+  cb = col_bias(e, n);
+  if (c.folded) {
+    cs = __fmul_rn(cs, c.so_inv);
+    cb = __fmul_rn(cb, c.so_inv);
+  }
+}
+
+// The same in two steps for kernels that walk many tiles: the loads of the next
+// tile's constants are issued before the current tile's arithmetic and finished
+// (products, the folded division) after it, so their latency stays off the
+// epilogue warps' critical path.
+struct ColRaw {
+  float sx, sw, so, b;
+};
+__device__ __forceinline__ ColRaw col_raw_load(const EpiParams& e, int64_t n) {
+  ColRaw r;
+  r.sx = 1.f;
+  if (e.x_kind == kScaleScalar) r.sx = __ldg(e.x_scale);
+  else if (e.x_kind == kScalePerCol) r.sx = __ldg(e.x_scale + n);
+  r.sw = 1.f;
+  if (e.w_kind == kScaleScalar) r.sw = __ldg(e.w_scale);
+  else if (e.w_kind == kScalePerCol) r.sw = __ldg(e.w_scale + n);
+  r.so = 1.f;
+  if (e.fold_out) r.so = (e.o_kind == kScalePerCol) ? __ldg(e.out_scale + n) : __ldg(e.out_scale);
+  r.b = 0.f;
+  if (e.bias_kind == kBiasF32) r.b = __ldg(reinterpret_cast<const float*>(e.bias) + n);
+  else if (e.bias_kind == kBiasI8) r.b = static_cast<float>(__ldg(reinterpret_cast<const int8_t*>(e.bias) + n));
+  return r;
+}
+__device__ __forceinline__ void col_raw_finish(const EpiParams& e, const EpiCtx& c, const ColRaw& r, bool ok,
+                                               float& cs, float& cb) {
+  float s = __fmul_rn(r.sx, r.sw);
+  if (e.fold_out) s = __fdiv_rn(s, r.so);
+  float b = r.b;
+  if (c.folded) {
+    s = __fmul_rn(s, c.so_inv);
+    b = __fmul_rn(b, c.so_inv);
+  }
+  cs = ok ? s : 0.f;
+  cb = ok ? b : 0.f;
 }
 
 // v / so, correctly rounded wherever it decides the int8 result.  One IEEE
@@ -154,7 +213,8 @@ __device__ __forceinline__ float epi_value(int32_t acc, float cs, float cb, cons
   if (c.has_rs) t = __fmul_rn(t, c.rs);
   float v = __fmaf_rn(t, cs, cb);
   v = act_apply(v, c.act);
-  if (c.div_out) v = div_out_scale(v, c);
+  if (c.div == kDivExact) v = div_out_scale(v, c);
+  else if (c.div == kDivRecip && !c.folded) v = __fmul_rn(v, c.so_inv);
   return v;
 }
 
@@ -164,37 +224,38 @@ __device__ __forceinline__ float epi_value(int32_t acc, float cs, float cb, cons
 // loop instead of sixteen unrolled copies of every branch (erf, exp, the
 // division fix-up): with 18 warps in three roles the instruction cache was
 // the first thing to run out.
-template <int ACT, bool DIV, bool RS>
+template <int ACT, int DIV, bool RS>
 __device__ __forceinline__ float epi_value_t(int32_t acc, float cs, float cb, const EpiCtx& c) {
   float t = __int2float_rn(acc);
   if (RS) t = __fmul_rn(t, c.rs);
   float v = __fmaf_rn(t, cs, cb);
   if (ACT == kActGelu) v = 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
   if (ACT == kActSilu) v = v / (1.f + __expf(-v));
-  if (DIV) v = div_out_scale(v, c);
+  if (DIV == kDivExact) v = div_out_scale(v, c);
+  if (DIV == kDivRecip && ACT != kActNone) v = __fmul_rn(v, c.so_inv);  // folded into cs / cb otherwise
   return v;
 }
 
 __device__ __forceinline__ int epi_mode(const EpiCtx& c) {
-  return c.act | (c.div_out ? 4 : 0) | (c.has_rs ? 8 : 0);
+  return c.act | (c.div << 2) | (c.has_rs ? 16 : 0);
 }
 
 // Calls BODY with ACT / DIV / RS bound as compile-time constants for `mode`.
 #define DISC_EPI_CASE(A, D, R, BODY)                 \
-  case ((A) | ((D) ? 4 : 0) | ((R) ? 8 : 0)): {      \
+  case ((A) | ((D) << 2) | ((R) ? 16 : 0)): {        \
     constexpr int ACT = (A);                         \
-    constexpr bool DIV = (D);                        \
+    constexpr int DIV = (D);                         \
     constexpr bool RS = (R);                         \
     BODY;                                            \
   } break;
+#define DISC_EPI_CASES_RS(R, BODY)                                                         \
+  DISC_EPI_CASE(0, 0, R, BODY) DISC_EPI_CASE(1, 0, R, BODY) DISC_EPI_CASE(2, 0, R, BODY)   \
+  DISC_EPI_CASE(0, 1, R, BODY) DISC_EPI_CASE(1, 1, R, BODY) DISC_EPI_CASE(2, 1, R, BODY)   \
+  DISC_EPI_CASE(0, 2, R, BODY) DISC_EPI_CASE(1, 2, R, BODY) DISC_EPI_CASE(2, 2, R, BODY)
 #define DISC_EPI_SWITCH(mode, BODY)                                                        \
   switch (mode) {                                                                          \
-    DISC_EPI_CASE(0, false, false, BODY) DISC_EPI_CASE(1, false, false, BODY)              \
-    DISC_EPI_CASE(2, false, false, BODY) DISC_EPI_CASE(0, true, false, BODY)               \
-    DISC_EPI_CASE(1, true, false, BODY) DISC_EPI_CASE(2, true, false, BODY)                \
-    DISC_EPI_CASE(0, false, true, BODY) DISC_EPI_CASE(1, false, true, BODY)                \
-    DISC_EPI_CASE(2, false, true, BODY) DISC_EPI_CASE(0, true, true, BODY)                 \
-    DISC_EPI_CASE(1, true, true, BODY) DISC_EPI_CASE(2, true, true, BODY)                  \
+    DISC_EPI_CASES_RS(false, BODY)                                                         \
+    DISC_EPI_CASES_RS(true, BODY)                                                          \
     default: break;                                                                        \
   }
 
@@ -307,7 +368,7 @@ struct TiledSmem {
 
 // One epilogue warp's share of a tile: CW columns of its 32 rows, 16 columns
 // per TMEM load, converted and stored straight from registers.
-template <typename OutT, int ACT, bool DIV, bool RS, int CW>
+template <typename OutT, int ACT, int DIV, bool RS, int CW>
 __device__ __forceinline__ void tiled_epilogue_cols(uint32_t t_row, const float* cs, const float* cb,
                                                     const EpiCtx& ctx, OutT* out, int64_t m,
                                                     bool row_ok, int64_t col0, int64_t N,
@@ -467,17 +528,31 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     bool ok = true;
     EpiCtx ctx = make_epi_ctx(ep);
     OutT* out = reinterpret_cast<OutT*>(ep.out);
+    // Column constants of the tile after the current one travel in registers:
+    // requested before the current tile's arithmetic, finished after it.
+    constexpr int CPL = (CW + 31) / 32;  // columns per lane
+    ColRaw raw[CPL];
+    auto request_consts = [&](int tile) {
+      const int64_t c0 = static_cast<int64_t>(tile % tiles_n) * BN + g * CW;
+#pragma unroll
+      for (int i = 0; i < CPL; ++i) {
+        const int64_t n = c0 + lane + 32 * i;
+        raw[i] = col_raw_load(ep, n < ep.N ? n : ep.N - 1);
+      }
+    };
+    if (static_cast<int>(blockIdx.x) < num_tiles) request_consts(blockIdx.x);
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int m_blk = tile / tiles_n;
       const int n_blk = tile % tiles_n;
       const int64_t col0 = static_cast<int64_t>(n_blk) * BN + g * CW;  // first column of this warp
       __syncwarp();
-      for (int j = lane; j < CW; j += 32) {
-        const int64_t n = col0 + j;
-        cs[j] = n < ep.N ? col_scale(ep, n) : 0.f;
-        cb[j] = n < ep.N ? col_bias(ep, n) : 0.f;
+#pragma unroll
+      for (int i = 0; i < CPL; ++i) {
+        const int j = lane + 32 * i;
+        if (j < CW) col_raw_finish(ep, ctx, raw[i], col0 + j < ep.N, cs[j], cb[j]);
       }
       __syncwarp();
+      if (tile + static_cast<int>(gridDim.x) < num_tiles) request_consts(tile + gridDim.x);
       ok = mbar_wait(tfull_bar(acc_buf), acc_phase, abort_flag, &g_kernel_status,
                      kStatusTimeoutTmemFull);
       if (!ok) break;
@@ -662,14 +737,13 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int64_t n4 = static_cast<int64_t>(n_blk) * kTileM + lane * 4;
     float cs = 0.f, cb = 0.f, cs4[4], cb4[4];
     if (split == 1) {
-      cs = n_ok ? col_scale(ep, n) : 0.f;
-      cb = n_ok ? col_bias(ep, n) : 0.f;
+      if (n_ok) col_consts(ep, ctx, n, cs, cb);
     } else {
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const bool c_ok = n4 + c < ep.N;
-        cs4[c] = c_ok ? col_scale(ep, n4 + c) : 0.f;
-        cb4[c] = c_ok ? col_bias(ep, n4 + c) : 0.f;
+        cs4[c] = cb4[c] = 0.f;
+        if (c_ok) col_consts(ep, ctx, n4 + c, cs4[c], cb4[c]);
       }
     }
 
@@ -805,8 +879,9 @@ __global__ void qgemm_simt_kernel(const int8_t* __restrict__ a, const int8_t* __
   }
   EpiCtx ctx = make_epi_ctx(ep);
   if (ctx.has_rs) ctx.rs = ep.x_scale[m];
-  const float v = epi_value(acc, col_scale(ep, n), col_bias(ep, n), ctx);
-  store_one<OutT>(reinterpret_cast<OutT*>(ep.out) + m * ep.ldo + n, v, acc);
+  float cs, cb;
+  col_consts(ep, ctx, n, cs, cb);
+  store_one<OutT>(reinterpret_cast<OutT*>(ep.out) + m * ep.ldo + n, epi_value(acc, cs, cb, ctx), acc);
 }
 
 // ------------------------------------------------------------------- host
@@ -863,6 +938,7 @@ EpiParams make_epi(const QGemmParams& p) {
   e.bias_kind = p.bias_kind;
   e.fold_out = p.fold_out_scale;
   e.div_out = p.div_out_scale;
+  e.div_exact = p.div_exact;
   e.act = p.act;
   return e;
 }

@@ -508,6 +508,7 @@ MemRef<OutT, N> fused_qgemm(ExecContext* ctx, void* stream_handle, MemRef<int8_t
     p.out_scale = out_scale.data;
     p.out_scale_kind = kScaleScalar;
     p.div_out_scale = 1;
+    p.div_exact = at->get_bool("exact_division", false) ? 1 : 0;
     p.out_dtype = kOutI8;
   } else {
     p.out_dtype = kOutF16;
@@ -1051,6 +1052,7 @@ MemRef<OutT, 3> qgemm_all_gather(ExecContext* ctx, void* stream_handle, MemRef<i
     p.out_scale = out_scale.data;
     p.out_scale_kind = kScaleScalar;
     p.div_out_scale = 1;
+    p.div_exact = at->get_bool("exact_division", false) ? 1 : 0;
     p.out_dtype = kOutI8;
   } else {
     p.out_dtype = kOutF16;

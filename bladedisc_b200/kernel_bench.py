@@ -80,7 +80,27 @@ def copies_for(nbytes):
     return max(2, min(400, (2 * L2_BYTES + nbytes - 1) // max(nbytes, 1)))
 
 
-def bench_qgemm(M, K, N, out_dtype, hbm, tops_peak, iters):
+def bench_int_mm(M, K, N, iters):
+    """cuBLASLt's int8 GEMM with int32 output (torch._int_mm), the library call the reference's GPU custom call
+    makes (quantized_gpu_kernel_impl.cc:130-159): the kernel to compare with, not part of this library.
+    Returns microseconds per launch, or None for shapes the library call does not take."""
+    if M <= 16 or K % 8 or N % 8 or not hasattr(torch, "_int_mm"):
+        return None
+    dev = "cuda"
+    n_sets = copies_for(M * K + N * K + 4 * M * N)
+    g = torch.Generator(device=dev).manual_seed(M + K + N)
+    sets = [(torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev, generator=g),
+             torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev, generator=g),
+             torch.empty((M, N), dtype=torch.int32, device=dev)) for _ in range(n_sets)]
+    try:
+        fns = [(lambda a=a, w=w, o=o: torch._int_mm(a, w.t(), out=o)) for a, w, o in sets]
+        return time_ms(fns, iters) * 1e3
+    except Exception:
+        torch.cuda.synchronize()
+        return None
+
+
+def bench_qgemm(M, K, N, out_dtype, hbm, tops_peak, iters, exact=False):
     dev = "cuda"
     b_out = 1 if out_dtype == torch.int8 else 2
     algo_bytes = M * K + N * K + M * N * b_out + 8 * N
@@ -98,7 +118,8 @@ def bench_qgemm(M, K, N, out_dtype, hbm, tops_peak, iters):
     so = torch.tensor([0.05], device=dev) if out_dtype == torch.int8 else None
     torch.cuda.synchronize()  # the weights are final from here on, as inference weights are
     fns = [(lambda a=a, w=w, o=o: ops.qgemm(a, w, x_scale=sx, w_scale=sw, out_scale=so, bias=bias,
-                                            out_dtype=out_dtype, out=o, weights_static=True)) for a, w, o in sets]
+                                            out_dtype=out_dtype, out=o, weights_static=True,
+                                            exact_division=exact)) for a, w, o in sets]
     ms = time_ms(fns, iters)
     tops = 2.0 * M * N * K / (ms * 1e-3) / 1e12
     gbs = algo_bytes / (ms * 1e-3) / 1e9
@@ -108,7 +129,8 @@ def bench_qgemm(M, K, N, out_dtype, hbm, tops_peak, iters):
     t_hbm = algo_bytes / (hbm * 1e9)
     bound = "tensor" if t_tensor >= t_hbm else "hbm"
     frac = max(t_tensor, t_hbm) / (ms * 1e-3)
-    return {"kernel": f"qgemm_{path}", "M": M, "K": K, "N": N, "out": str(out_dtype).split(".")[-1], "us": ms * 1e3,
+    return {"kernel": f"qgemm_{path}", "M": M, "K": K, "N": N,
+            "out": str(out_dtype).split(".")[-1] + ("/exact" if exact else ""), "us": ms * 1e3,
             "tops": tops, "gbs": gbs, "bound": bound, "frac": frac, "sets": n_sets}
 
 
@@ -244,6 +266,10 @@ def main():
     ap.add_argument("--only", default=None, help="comma-separated substrings: run only the cases whose kernel name contains one (qgemm, quantize, norm, softmax ...)")
     ap.add_argument("--eager", action="store_true", help="no CUDA graph (for ncu captures); few iterations")
     ap.add_argument("--shape", default=None, help="M,K,N: only this quantized-linear point (with --only qgemm)")
+    ap.add_argument("--min-rows", type=int, default=0, help="quantized-linear points with at least this many rows")
+    ap.add_argument("--max-rows", type=int, default=1 << 30, help="quantized-linear points with at most this many rows")
+    ap.add_argument("--exact", action="store_true", help="also time int8 output with the exact-division epilogue")
+    ap.add_argument("--int-mm", action="store_true", help="also time cuBLASLt int8 -> int32 (torch._int_mm) per point")
     args = ap.parse_args()
     global EAGER
     EAGER = args.eager
@@ -256,19 +282,27 @@ def main():
         m, k, n = (int(v) for v in args.shape.split(","))
         ms_list, kns = [m], [(k, n)]
     print(f"# peaks ({src}): HBM {hbm:.0f} GB/s, int8 tensor {tops_peak:.0f} TOPS (2 x bf16)")
-    print(f"{'kernel':<16}{'M':>6}{'K':>6}{'N':>7}{'out':>9}{'us':>10}{'TOPS':>9}{'GB/s':>9}{'bound':>8}{'frac':>7}")
+    print(f"{'kernel':<16}{'M':>6}{'K':>6}{'N':>7}{'out':>14}{'us':>10}{'TOPS':>9}{'GB/s':>9}{'bound':>8}{'frac':>7}"
+          + (f"{'int_mm us':>11}{'vs':>6}" if args.int_mm else ""))
+    ms_list = [m for m in ms_list if args.min_rows <= m <= args.max_rows]
     for K, N in kns:
         for M in ms_list:
-            for od in (torch.int8, torch.float16):
-                if only and "qgemm" not in only:
+            if only and "qgemm" not in only:
+                continue
+            iters = 200 if M <= 1024 else 30
+            if args.eager:
+                iters = 3
+            lib_us = bench_int_mm(M, K, N, iters) if args.int_mm else None
+            for od, exact in ((torch.int8, False), (torch.int8, True), (torch.float16, False)):
+                if exact and not args.exact:
                     continue
-                iters = 200 if M <= 1024 else 30
-                if args.eager:
-                    iters = 3
-                r = bench_qgemm(M, K, N, od, hbm, tops_peak, iters)
+                r = bench_qgemm(M, K, N, od, hbm, tops_peak, iters, exact)
+                if lib_us:
+                    r["int_mm_us"] = lib_us
                 out["rows"].append(r)
-                print(f"{r['kernel']:<16}{M:>6}{K:>6}{N:>7}{r['out']:>9}{r['us']:>10.2f}{r['tops']:>9.1f}{r['gbs']:>9.0f}"
-                      f"{r['bound']:>8}{r['frac']:>7.2f}", flush=True)
+                print(f"{r['kernel']:<16}{M:>6}{K:>6}{N:>7}{r['out']:>14}{r['us']:>10.2f}{r['tops']:>9.1f}{r['gbs']:>9.0f}"
+                      f"{r['bound']:>8}{r['frac']:>7.2f}"
+                      + (f"{lib_us:>11.2f}{lib_us / r['us']:>6.2f}" if lib_us else ""), flush=True)
     if not only or any("weight_only" in o for o in only):
         wo_ms = [1, 4, 16] if args.quick else [1, 2, 4, 8, 16]
         wo_kns = [(4096, 4096)] if args.quick else [(4096, 4096), (4096, 11008), (11008, 4096), (4096, 12288)]

@@ -49,7 +49,7 @@ class QGemmArgs(Structure):
         ("path", c_int32), ("split_k", c_int32),
         ("splitk_ws", c_void_p), ("splitk_ws_bytes", c_int64),
         ("a_slabs", c_int32), ("a_slab_cols", c_int64), ("a_slab_stride", c_int64),
-        ("weights_static", c_int32),
+        ("weights_static", c_int32), ("div_exact", c_int32),
     ]
 
 

@@ -76,13 +76,16 @@ def qgemm(a: torch.Tensor, w: torch.Tensor, *, x_scale: Optional[torch.Tensor] =
           out_dtype: torch.dtype = torch.int8, fold_out_scale: bool = False,
           x_scale_per_col: bool = False, path: Optional[str] = None, split_k: int = 0,
           out: Optional[torch.Tensor] = None, a_gathered: bool = False,
-          weights_static: bool = False) -> torch.Tensor:
+          weights_static: bool = False, exact_division: bool = False) -> torch.Tensor:
     """out = epilogue(a[..., K] @ w[N, K]^T) with int8 operands and int32 accumulation.
 
     ``fold_out_scale=True`` is the reference custom call ``ral_pdll_qgemm``:
     ``sat_s8(rne(acc * (x_scale * w_scale / out_scale) + bias))``.  Otherwise
     ``v = act(acc * x_scale * w_scale + bias)`` and int8 output divides ``v`` by
-    ``out_scale`` before rounding.  Scales and bias are device tensors.
+    ``out_scale`` before rounding: as a product with the correctly rounded
+    reciprocal (at most one int8 level from the quotient, at rounding ties only),
+    or, with ``exact_division=True``, as the IEEE quotient the reference's
+    quantize computes, bit for bit.  Scales and bias are device tensors.
 
     ``a_gathered=True``: ``a`` is ``[g, M, K / g]``, the buffer an all-gather of
     column-parallel outputs leaves (slab ``r`` holds columns ``r * K / g ...``);
@@ -145,6 +148,7 @@ def qgemm(a: torch.Tensor, w: torch.Tensor, *, x_scale: Optional[torch.Tensor] =
         args.bias = bias.data_ptr()
     args.fold_out_scale = 1 if fold_out_scale else 0
     args.div_out_scale = 1 if (out_dtype == torch.int8 and out_scale is not None and not fold_out_scale) else 0
+    args.div_exact = 1 if exact_division else 0
     args.act = _ACT[act]
     args.out_dtype = _OUT[out_dtype]
     args.path = _PATH[path]

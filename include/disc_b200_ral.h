@@ -149,7 +149,7 @@ enum { DISC_B200_F32 = 0, DISC_B200_F16 = 1 };
  *   cs = x_scale(n) * w_scale(n)                 [x_scale left out if PER_ROW]
  *   cs = cs / out_scale(n)                       if fold_out_scale
  *   v  = fma(t, cs, bias[n]);  v = act(v)
- *   v  = v / out_scale                           if div_out_scale
+ *   v  = v / out_scale                           if div_out_scale (see div_exact)
  *   out = sat_s8(rne(v)) | f16(v) | f32(v) ; OUT_I32 stores acc itself.
  *
  * The reference's ral_pdll_qgemm (quantized_gpu_kernel_impl.cc:328-422) is
@@ -187,6 +187,15 @@ typedef struct disc_b200_qgemm_args {
    * (the reference's ral_qgemm carries the same promise as weight_is_const,
    * stream_executor_based_impl.cc:427-433). */
   int32_t weights_static;
+  /* With div_out_scale.  0: v * (1 / out_scale) with the correctly rounded
+   * reciprocal (folded into the column scale and bias when there is no
+   * activation): the int8 result equals the divide-based one except for values
+   * within a few ulp of a rounding tie, where it may land on the neighbouring
+   * level (at most 1 LSB, the tolerance of requantized outputs).  Non-zero: the
+   * correctly rounded IEEE quotient, bit for bit the divide-based quantize of
+   * disc_lower_quantize_and_dequantize.cc:77-93, at about twice the epilogue
+   * arithmetic. */
+  int32_t div_exact;
 } disc_b200_qgemm_args;
 
 int32_t disc_b200_qgemm(const disc_b200_qgemm_args* args, void* stream);

@@ -142,7 +142,7 @@ def test_ral_collective_calls_one_rank(ops):
     assert tuple(out.shape) == (1, 40, 96)
     assert np.allclose(out[0].float().cpu().numpy(), want, rtol=1e-2, atol=1e-3)
     # int8 result, gathered asynchronously, then fed to the next linear as a gathered activation
-    later = ("pvoid", blob({"activation": "none", "is_async": True, "async_token_key": 1}))
+    later = ("pvoid", blob({"activation": "none", "is_async": True, "async_token_key": 1, "exact_division": True}))
     out8 = ctx.call("disc_b200_qgemm_all_gather", "gpu", args[:-1] + [later], [MemRefSpec("i8", 3)])
     out8 = ctx.call("ral_async_collective_done", "gpu",
                     [("pvoid", 0), out8, ("pvoid", blob({"is_async": True, "async_token_key": 1}))],
