@@ -97,7 +97,7 @@ qgemm_gemv_kernel(const int8_t* __restrict__ a, const int8_t* __restrict__ w, in
         float cs, cb;
         col_consts(ep, ctx, n, cs, cb);
         const float v = epi_value(mine, cs, cb, ctx);
-        store_one<OutT>(out + static_cast<int64_t>(lane) * ep.ldo + n, v, mine);
+        store_one_rt<OutT>(out + static_cast<int64_t>(lane) * ep.ldo + n, v, mine, ctx);
       }
     }
   }

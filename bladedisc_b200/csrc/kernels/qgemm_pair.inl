@@ -32,95 +32,147 @@ struct PairSmem {
   static constexpr int kDynamic = kTotal + 1024;
 };
 
-// One epilogue warp's share of a pair tile: 64 columns of its 32 rows, handed
-// to TMA stores in pieces of 32 rows x 64 bytes (or stored directly when the
-// output rows are not 16-byte aligned).
+// Where an epilogue warp reports that it has read its part of an accumulator
+// buffer: the leader CTA's "accumulator empty" barrier.
+struct PairRelease {
+  uint32_t local_bar;   // this CTA's copy (used by the leader)
+  uint32_t leader_bar;  // the leader's copy as a shared::cluster address
+  bool is_leader;
+};
+__device__ __forceinline__ void pair_release(const PairRelease& rel, int lane) {
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) {
+    // the accumulator left TMEM through registers, not through memory: no release of earlier writes is needed,
+    // and a cluster-scope release made the peer CTA's epilogue 0.7 us per tile slower than the leader's
+    if (rel.is_leader) mbar_arrive(rel.local_bar);
+    else mbar_arrive_remote_relaxed(rel.leader_bar);
+  }
+}
+
+// One epilogue warp's share of a pair tile: 64 columns of its 32 rows in four
+// chunks of 16 columns.  The TMEM load of chunk c + 1 is in flight while chunk
+// c is converted, and the accumulator buffer is handed back to the MMA warp as
+// soon as the last load has landed in registers, before the arithmetic and the
+// stores of the last chunk.  Results leave through a 32-row x 64-byte staging
+// buffer (64-byte swizzle) and a TMA store per 64 bytes of row, or by direct
+// stores when the output rows are not 16-byte aligned.
 template <typename OutT, int ACT, int DIV, bool RS>
 __device__ __forceinline__ void pair_epilogue_cols(uint32_t t_row, const float* cs, const float* cb,
-                                                   const EpiCtx& ctx, OutT* out, int64_t row0, int lane,
-                                                   int64_t col0, int64_t M, int64_t N, int64_t ldo,
+                                                   const EpiCtx& ctx, OutT* out, int row0, int lane,
+                                                   int col0, int M, int N, int64_t ldo,
                                                    uint8_t* stg, uint32_t stg_addr,
                                                    const CUtensorMap* tmap_out, int use_tma_store,
-                                                   int vec_ok) {
+                                                   int vec_ok, const PairRelease& rel) {
   constexpr int CW = kPairColsPerWarp;
-  constexpr int EB = static_cast<int>(sizeof(OutT));
-  constexpr int SUB_COLS = 64 / EB;     // columns in one 64-byte staging row
-  constexpr int SUBS = CW / SUB_COLS;   // staging rounds per tile and warp
-  constexpr int LOADS = SUB_COLS / 16;  // 16-column TMEM loads per round
-  const int64_t m = row0 + lane;
-  const bool row_ok = m < M;
-#pragma unroll 1
-      for (int sub = 0; sub < SUBS; ++sub) {
-        const int64_t n_sub = col0 + sub * SUB_COLS;
-        if (n_sub >= N || row0 >= M) break;  // uniform across the warp
-        if (use_tma_store) {
-          // the previous round's store must have read the staging buffer
-          if (lane == 0) tma_store_wait_read();
-          __syncwarp();
-        }
-#pragma unroll 1
-        for (int ld = 0; ld < LOADS; ++ld) {
-          uint32_t r[16];
-          tmem_ld_x16(t_row + sub * SUB_COLS + ld * 16, r);
-          tmem_ld_wait();
-          float v[16];
+  constexpr int EB = static_cast<int>(sizeof(OutT));  // 16 columns = EB units of 16 bytes
+  int nchunks = 0;
+  if (row0 < M && col0 < N) {
+    const int left = (N - col0 + 15) / 16;
+    nchunks = left < CW / 16 ? left : CW / 16;
+  }
+  if (nchunks == 0) {  // uniform across the warp: nothing of this warp's share is inside the tensor
+    pair_release(rel, lane);
+    return;
+  }
+
+  auto process = [&](int c, uint32_t (&r)[16]) {
+    const float4* cs4 = reinterpret_cast<const float4*>(cs + c * 16);
+    const float4* cb4 = reinterpret_cast<const float4*>(cb + c * 16);
+    if (!use_tma_store) {
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 s4 = cs4[i], b4 = cb4[i];
+        v[4 * i + 0] = epi_value_t<ACT, DIV, RS, kUnitForm<OutT, DIV>>(static_cast<int32_t>(r[4 * i + 0]), s4.x, b4.x, ctx);
+        v[4 * i + 1] = epi_value_t<ACT, DIV, RS, kUnitForm<OutT, DIV>>(static_cast<int32_t>(r[4 * i + 1]), s4.y, b4.y, ctx);
+        v[4 * i + 2] = epi_value_t<ACT, DIV, RS, kUnitForm<OutT, DIV>>(static_cast<int32_t>(r[4 * i + 2]), s4.z, b4.z, ctx);
+        v[4 * i + 3] = epi_value_t<ACT, DIV, RS, kUnitForm<OutT, DIV>>(static_cast<int32_t>(r[4 * i + 3]), s4.w, b4.w, ctx);
+      }
+      if (row0 + lane < M) {
+        const int n0 = col0 + c * 16;
+        OutT* dst = out + static_cast<int64_t>(row0 + lane) * ldo + n0;
+        if (vec_ok && n0 + 16 <= N) {
+          store_row16_vec<OutT, kUnitForm<OutT, DIV>>(dst, v, r);
+        } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int c = sub * SUB_COLS + ld * 16 + j;
-            v[j] = epi_value_t<ACT, DIV, RS>(static_cast<int32_t>(r[j]), cs[c], cb[c], ctx);
-          }
-          if (use_tma_store) {
-            // 16 values = 16 * EB bytes = EB chunks of 16 bytes; chunk index inside
-            // the 64-byte row is xor-ed with ((row >> 1) & 3): the 64-byte TMA swizzle.
-            uint32_t w[4 * EB];
-            if constexpr (EB == 1) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) w[i] = pack4_s8(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-            } else if constexpr (EB == 2) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-                w[i] = *reinterpret_cast<uint32_t*>(&h);
-              }
-            } else if constexpr (std::is_same_v<OutT, float>) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) w[i] = __float_as_uint(v[i]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) w[i] = r[i];
-            }
-#pragma unroll
-            for (int ch = 0; ch < EB; ++ch) {
-              const int chunk = ld * EB + ch;  // 0..3 inside the 64-byte row
-              const uint32_t off = lane * 64 + ((chunk ^ ((lane >> 1) & 3)) << 4);
-              *reinterpret_cast<uint4*>(stg + off) =
-                  make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
-            }
-          } else if (row_ok) {
-            const int64_t n0 = n_sub + ld * 16;
-            OutT* dst = out + m * ldo + n0;
-            if (vec_ok && n0 + 16 <= N) {
-              store_row16_vec<OutT>(dst, v, r);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (n0 + j < N) store_one<OutT>(dst + j, v[j], static_cast<int32_t>(r[j]));
-              }
-            }
-          }
-        }
-        if (use_tma_store) {
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(tmap_out, stg_addr, static_cast<int>(n_sub * EB), static_cast<int>(row0));
-            tma_store_commit();
+            if (n0 + j < N) store_one<OutT, kUnitForm<OutT, DIV>>(dst + j, v[j], static_cast<int32_t>(r[j]));
           }
         }
       }
+      return;
+    }
+    const int unit0 = (c * EB) & 3;  // first 16-byte unit of this chunk inside the 64-byte staging row
+    if (unit0 == 0) {
+      // a new 64-byte round: the previous round's store must have read the staging buffer
+      if (lane == 0) tma_store_wait_read();
+      __syncwarp();
+    }
+    // four values at a time, packed at once, so that few converted values are live together
+    uint32_t w[4 * EB];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if constexpr (std::is_same_v<OutT, int32_t>) {
+        w[4 * i] = r[4 * i], w[4 * i + 1] = r[4 * i + 1], w[4 * i + 2] = r[4 * i + 2], w[4 * i + 3] = r[4 * i + 3];
+      } else {
+        const float4 s4 = cs4[i], b4 = cb4[i];
+        const float v0 = epi_value_t<ACT, DIV, RS, kUnitForm<OutT, DIV>>(static_cast<int32_t>(r[4 * i + 0]), s4.x, b4.x, ctx);
+        const float v1 = epi_value_t<ACT, DIV, RS, kUnitForm<OutT, DIV>>(static_cast<int32_t>(r[4 * i + 1]), s4.y, b4.y, ctx);
+        const float v2 = epi_value_t<ACT, DIV, RS, kUnitForm<OutT, DIV>>(static_cast<int32_t>(r[4 * i + 2]), s4.z, b4.z, ctx);
+        const float v3 = epi_value_t<ACT, DIV, RS, kUnitForm<OutT, DIV>>(static_cast<int32_t>(r[4 * i + 3]), s4.w, b4.w, ctx);
+        if constexpr (EB == 1) {
+          w[i] = pack4_s8<kUnitForm<OutT, DIV>>(v0, v1, v2, v3);
+        } else if constexpr (EB == 2) {
+          __half2 h0 = __floats2half2_rn(v0, v1), h1 = __floats2half2_rn(v2, v3);
+          w[2 * i] = *reinterpret_cast<uint32_t*>(&h0);
+          w[2 * i + 1] = *reinterpret_cast<uint32_t*>(&h1);
+        } else {
+          w[4 * i] = __float_as_uint(v0), w[4 * i + 1] = __float_as_uint(v1);
+          w[4 * i + 2] = __float_as_uint(v2), w[4 * i + 3] = __float_as_uint(v3);
+        }
+      }
+    }
+    // unit index inside the 64-byte row is xor-ed with ((row >> 1) & 3): the 64-byte TMA swizzle
+#pragma unroll
+    for (int u = 0; u < EB; ++u) {
+      const uint32_t off = lane * 64 + (((unit0 + u) ^ ((lane >> 1) & 3)) << 4);
+      *reinterpret_cast<uint4*>(stg + off) = make_uint4(w[4 * u], w[4 * u + 1], w[4 * u + 2], w[4 * u + 3]);
+    }
+    const bool round_ends = ((unit0 + EB) & 3) == 0 || c + 1 == nchunks;
+    if (round_ends) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const int first_col = (c * 16 * EB / 64) * (64 / EB);  // first column of this round
+        tma_store_2d(tmap_out, stg_addr, (col0 + first_col) * EB, row0);
+        tma_store_commit();
+      }
+    }
+  };
+
+  uint32_t ra[16], rb[16];
+  tmem_ld_x16(t_row, ra);
+#pragma unroll 1
+  for (int c = 0; c < nchunks; c += 2) {
+    tmem_ld_wait_regs(ra);
+    if (c + 1 < nchunks) tmem_ld_x16(t_row + (c + 1) * 16, rb);
+    else pair_release(rel, lane);
+    process(c, ra);
+    if (c + 1 < nchunks) {
+      tmem_ld_wait_regs(rb);
+      if (c + 2 < nchunks) tmem_ld_x16(t_row + (c + 2) * 16, ra);
+      else pair_release(rel, lane);
+      process(c + 1, rb);
+    }
+  }
 }
 
-template <typename OutT>
+// The epilogue mode (activation, requantisation form, per-row scales) is a
+// template parameter of the kernel, chosen by the host: with every mode inlined
+// behind one switch the compiler kept the union of all modes' temporaries live
+// and spilled in each of them.
+template <typename OutT, int ACT, int DIV, bool RS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTiledThreads, 1)
 qgemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_w,
@@ -277,7 +329,7 @@ qgemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       const int m_blk = tile / tiles_n;
       const int n_blk = tile % tiles_n;
-      const int64_t col0 = static_cast<int64_t>(n_blk) * BN + g * CW;
+      const int col0 = n_blk * BN + g * CW;
       __syncwarp();
 #pragma unroll
       for (int i = 0; i < CPL; ++i) {
@@ -290,20 +342,15 @@ qgemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      kStatusTimeoutTmemFull);
       if (!ok) break;
       tc_fence_after();
-      const int64_t row0 = static_cast<int64_t>(m_blk) * 2 * kTileM + rank * kTileM + q * 32;
+      const int row0 = m_blk * 2 * kTileM + static_cast<int>(rank) * kTileM + q * 32;
       if (ctx.has_rs) ctx.rs = (row0 + lane < ep.M) ? __ldg(ep.x_scale + row0 + lane) : 1.f;
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc_buf * BN + g * CW;
-      const int mode = std::is_same_v<OutT, int32_t> ? 0 : epi_mode(ctx);
-      DISC_EPI_SWITCH(mode, (pair_epilogue_cols<OutT, ACT, DIV, RS>(t_row, cs, cb, ctx, out, row0, lane, col0,
-                                                                    ep.M, ep.N, ep.ldo, stg, stg_addr, &tmap_out,
-                                                                    use_tma_store, vec_ok)))
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if (rank == 0) mbar_arrive(tempty_bar(acc_buf));
-        else mbar_arrive_remote(acc_buf == 0 ? tempty_leader0 : tempty_leader1);
-      }
+      // the accumulator buffer is handed back inside, as soon as it has been read
+      const PairRelease rel = {tempty_bar(acc_buf), acc_buf == 0 ? tempty_leader0 : tempty_leader1, rank == 0};
+      pair_epilogue_cols<OutT, ACT, DIV, RS>(t_row, cs, cb, ctx, out, row0, lane, col0, static_cast<int>(ep.M),
+                                             static_cast<int>(ep.N), ep.ldo, stg, stg_addr, &tmap_out,
+                                             use_tma_store, vec_ok, rel);
       acc_buf ^= 1;
       if (acc_buf == 0) acc_phase ^= 1;
     }

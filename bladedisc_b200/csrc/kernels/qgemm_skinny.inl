@@ -40,15 +40,16 @@ __device__ __forceinline__ void skinny_epilogue_cols(uint32_t t_row, const float
       float v[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        v[j] = epi_value_t<ACT, DIV, RS>(static_cast<int32_t>(r[j]), cs[c * 16 + j], cb[c * 16 + j], ctx);
+        v[j] = epi_value_t<ACT, DIV, RS, kUnitForm<OutT, DIV>>(static_cast<int32_t>(r[j]), cs[c * 16 + j],
+                                                               cb[c * 16 + j], ctx);
       }
       OutT* dst = out + m * ldo + n0;
       if (vec_ok && n0 + 16 <= N) {
-        store_row16_vec<OutT>(dst, v, r);
+        store_row16_vec<OutT, kUnitForm<OutT, DIV>>(dst, v, r);
       } else {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          if (n0 + j < N) store_one<OutT>(dst + j, v[j], static_cast<int32_t>(r[j]));
+          if (n0 + j < N) store_one<OutT, kUnitForm<OutT, DIV>>(dst + j, v[j], static_cast<int32_t>(r[j]));
         }
       }
     }

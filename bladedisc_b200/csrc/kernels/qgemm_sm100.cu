@@ -45,7 +45,7 @@ struct EpiParams {
   const float* w_scale;
   const float* out_scale;
   const void* bias;
-  int x_kind, w_kind, o_kind, bias_kind, fold_out, div_out, div_exact, act;
+  int x_kind, w_kind, o_kind, bias_kind, fold_out, div_out, div_exact, act, out_kind;
 };
 
 // Where K block `kb` of the two operands starts when the activation is stored
@@ -108,8 +108,10 @@ struct EpiCtx {
   float so_inv;  // correctly rounded 1 / so
   int act;
   bool has_rs;
+  float k1, k0;   // unit form: u = v * k1 + k0 with k1 = (1 / so) / 255, k0 = 128 / 255
   int div;        // kDivNone, kDivRecip (product with 1 / so) or kDivExact (the IEEE quotient)
-  bool folded;    // kDivRecip without an activation: 1 / so already sits in the column constants
+  bool folded;    // kDivRecip without an activation: the factor already sits in the column constants
+  bool unit;      // kDivRecip with int8 output: values travel as u = (q + 128) / 255, see below
   bool div_fast;  // so is in the range where the reciprocal sequence below is safe
 };
 
@@ -120,6 +122,15 @@ struct EpiCtx {
 //              by one level (the tolerance the quantized path states for
 //              requantized outputs).  Without an activation the factor is folded
 //              into the column scale and bias and costs nothing per element.
+//              (Holds while so and 1 / so are normal floats, 2^-126 <= |so| <=
+//              2^126; a scale outside that range wants kDivExact.)
+//              With int8 output the value is carried as u = (q + 128) / 255: the
+//              saturating fused multiply-add clamps u to [0, 1], which is the
+//              clamp of q to [-128, 127], and one more fused multiply-add,
+//              255 u - 128 + 1.5 * 2^23, leaves the rounded (half to even) int8
+//              in the low byte of the sum.  Two instructions on the FMA pipe
+//              replace two min/max, an add and the reciprocal product; every
+//              kernel uses the same sequence, so all paths agree bit for bit.
 //   kDivExact  bit for bit what the reference's divide-based quantize computes.
 enum DivMode : int { kDivNone = 0, kDivRecip = 1, kDivExact = 2 };
 
@@ -133,9 +144,10 @@ __device__ __forceinline__ EpiCtx make_epi_ctx(const EpiParams& e) {
   c.so_inv = __frcp_rn(c.so);
   const float a = fabsf(c.so);
   c.div_fast = a > 1e-15f && a < 1e15f;
-  // a reciprocal that is zero, infinite or subnormal would not stand for the division
-  if (c.div == kDivRecip && !c.div_fast) c.div = kDivExact;
   c.folded = c.div == kDivRecip && c.act == kActNone;
+  c.unit = c.div == kDivRecip && e.out_kind == kOutI8;
+  c.k1 = c.unit ? __fdiv_rn(c.so_inv, 255.f) : c.so_inv;
+  c.k0 = c.unit ? __fdiv_rn(128.f, 255.f) : 0.f;
   return c;
 }
 
@@ -144,8 +156,8 @@ __device__ __forceinline__ void col_consts(const EpiParams& e, const EpiCtx& c, 
   cs = col_scale(e, n);
   cb = col_bias(e, n);
   if (c.folded) {
-    cs = __fmul_rn(cs, c.so_inv);
-    cb = __fmul_rn(cb, c.so_inv);
+    cs = __fmul_rn(cs, c.k1);
+    cb = __fmaf_rn(cb, c.k1, c.k0);
   }
 }
 
@@ -177,8 +189,8 @@ __device__ __forceinline__ void col_raw_finish(const EpiParams& e, const EpiCtx&
   if (e.fold_out) s = __fdiv_rn(s, r.so);
   float b = r.b;
   if (c.folded) {
-    s = __fmul_rn(s, c.so_inv);
-    b = __fmul_rn(b, c.so_inv);
+    s = __fmul_rn(s, c.k1);
+    b = __fmaf_rn(b, c.k1, c.k0);
   }
   cs = ok ? s : 0.f;
   cb = ok ? b : 0.f;
@@ -214,7 +226,8 @@ __device__ __forceinline__ float epi_value(int32_t acc, float cs, float cb, cons
   float v = __fmaf_rn(t, cs, cb);
   v = act_apply(v, c.act);
   if (c.div == kDivExact) v = div_out_scale(v, c);
-  else if (c.div == kDivRecip && !c.folded) v = __fmul_rn(v, c.so_inv);
+  else if (c.div == kDivRecip && !c.folded) v = __fmaf_rn(v, c.k1, c.k0);
+  if (c.unit) v = __saturatef(v);
   return v;
 }
 
@@ -224,15 +237,28 @@ __device__ __forceinline__ float epi_value(int32_t acc, float cs, float cb, cons
 // loop instead of sixteen unrolled copies of every branch (erf, exp, the
 // division fix-up): with 18 warps in three roles the instruction cache was
 // the first thing to run out.
-template <int ACT, int DIV, bool RS>
+// float(acc), correctly rounded like the conversion instruction, from integer and
+// floating-point adds only.  acc = hi * 2048 + lo with hi = acc >> 11 (|hi| < 2^20)
+// and lo = acc & 2047; both become floats exactly through the mantissa of a
+// magic constant, and one fused multiply-add rounds their exact sum once.  The
+// conversion instruction runs on the 16-lane special-function pipe; tile
+// epilogues convert every other value this way so that neither pipe limits them.
+__device__ __forceinline__ float int2float_by_adds(int32_t acc) {
+  const float lo = __uint_as_float((static_cast<uint32_t>(acc) & 0x7FFu) | 0x4B000000u) - 8388608.f;
+  const float hi = __int_as_float((acc >> 11) + 0x4B400000) - 12582912.f;
+  return __fmaf_rn(hi, 2048.f, lo);
+}
+
+template <int ACT, int DIV, bool RS, bool UNIT, bool CVT_BY_ADDS = false>
 __device__ __forceinline__ float epi_value_t(int32_t acc, float cs, float cb, const EpiCtx& c) {
-  float t = __int2float_rn(acc);
+  float t = CVT_BY_ADDS ? int2float_by_adds(acc) : __int2float_rn(acc);
   if (RS) t = __fmul_rn(t, c.rs);
   float v = __fmaf_rn(t, cs, cb);
   if (ACT == kActGelu) v = 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
   if (ACT == kActSilu) v = v / (1.f + __expf(-v));
   if (DIV == kDivExact) v = div_out_scale(v, c);
-  if (DIV == kDivRecip && ACT != kActNone) v = __fmul_rn(v, c.so_inv);  // folded into cs / cb otherwise
+  if (DIV == kDivRecip && ACT != kActNone) v = __fmaf_rn(v, c.k1, c.k0);  // folded into cs / cb otherwise
+  if (DIV == kDivRecip && UNIT) v = __saturatef(v);
   return v;
 }
 
@@ -248,6 +274,9 @@ __device__ __forceinline__ int epi_mode(const EpiCtx& c) {
     constexpr bool RS = (R);                         \
     BODY;                                            \
   } break;
+// Whether values of this (output type, division form) travel in unit form.
+template <typename OutT, int DIV>
+inline constexpr bool kUnitForm = std::is_same_v<OutT, int8_t> && DIV == kDivRecip;
 #define DISC_EPI_CASES_RS(R, BODY)                                                         \
   DISC_EPI_CASE(0, 0, R, BODY) DISC_EPI_CASE(1, 0, R, BODY) DISC_EPI_CASE(2, 0, R, BODY)   \
   DISC_EPI_CASE(0, 1, R, BODY) DISC_EPI_CASE(1, 1, R, BODY) DISC_EPI_CASE(2, 1, R, BODY)   \
@@ -265,77 +294,74 @@ __device__ __forceinline__ int8_t to_s8(float v) {
   return static_cast<int8_t>(r);
 }
 
-// Four saturated, round-half-to-even int8 values packed into one word without
-// float-to-int conversions: after clamping to [-128, 127], adding 1.5 * 2^23
-// leaves the rounded integer in the low mantissa bits (the add itself rounds
-// to nearest even), so the low byte of each sum is the two's-complement result.
-__device__ __forceinline__ uint32_t pack4_s8(float a, float b, float c, float d) {
+// A word whose low byte is the int8 result.  Plain form: clamp to [-128, 127],
+// then adding 1.5 * 2^23 leaves the rounded integer in the low mantissa bits
+// (the add itself rounds to nearest even), so the low byte of the sum is the
+// two's-complement result; no float-to-int conversion.  Unit form (u in [0, 1]
+// stands for 255 u - 128): the same magic sum in one fused multiply-add.
+template <bool UNIT>
+__device__ __forceinline__ uint32_t s8_word(float v) {
   const float kMagic = 12582912.f;
-  a = fminf(fmaxf(a, -128.f), 127.f) + kMagic;
-  b = fminf(fmaxf(b, -128.f), 127.f) + kMagic;
-  c = fminf(fmaxf(c, -128.f), 127.f) + kMagic;
-  d = fminf(fmaxf(d, -128.f), 127.f) + kMagic;
-  const uint32_t ab = __byte_perm(__float_as_uint(a), __float_as_uint(b), 0x0040);
-  const uint32_t cd = __byte_perm(__float_as_uint(c), __float_as_uint(d), 0x0040);
+  if (UNIT) return __float_as_uint(__fmaf_rn(v, 255.f, kMagic - 128.f));
+  return __float_as_uint(fminf(fmaxf(v, -128.f), 127.f) + kMagic);
+}
+
+// Four of them packed into one word.
+template <bool UNIT = false>
+__device__ __forceinline__ uint32_t pack4_s8(float a, float b, float c, float d) {
+  const uint32_t ab = __byte_perm(s8_word<UNIT>(a), s8_word<UNIT>(b), 0x0040);
+  const uint32_t cd = __byte_perm(s8_word<UNIT>(c), s8_word<UNIT>(d), 0x0040);
   return __byte_perm(ab, cd, 0x5410);
 }
 
+// UNIT: `v` of an int8 output is in unit form (see DivMode).
+template <typename OutT, bool UNIT = false>
+__device__ __forceinline__ void store_one(OutT* p, float v, int32_t acc) {
+  if constexpr (std::is_same_v<OutT, int8_t>) {
+    *p = UNIT ? static_cast<int8_t>(s8_word<true>(v) & 0xFFu) : to_s8(v);
+  } else if constexpr (std::is_same_v<OutT, __half>) {
+    *p = __float2half_rn(v);
+  } else if constexpr (std::is_same_v<OutT, float>) {
+    *p = v;
+  } else {
+    *p = acc;
+  }
+}
+// The same for kernels that learn the mode at run time.
 template <typename OutT>
-__device__ __forceinline__ void store_one(OutT* p, float v, int32_t acc);
-template <>
-__device__ __forceinline__ void store_one<int8_t>(int8_t* p, float v, int32_t) {
-  *p = to_s8(v);
-}
-template <>
-__device__ __forceinline__ void store_one<__half>(__half* p, float v, int32_t) {
-  *p = __float2half_rn(v);
-}
-template <>
-__device__ __forceinline__ void store_one<float>(float* p, float v, int32_t) {
-  *p = v;
-}
-template <>
-__device__ __forceinline__ void store_one<int32_t>(int32_t* p, float, int32_t acc) {
-  *p = acc;
+__device__ __forceinline__ void store_one_rt(OutT* p, float v, int32_t acc, const EpiCtx& c) {
+  if (std::is_same_v<OutT, int8_t> && c.unit) store_one<OutT, true>(p, v, acc);
+  else store_one<OutT, false>(p, v, acc);
 }
 
 // Stores 16 consecutive outputs of one row with 16-byte stores.
-template <typename OutT>
-__device__ __forceinline__ void store_row16_vec(OutT* p, const float* v, const uint32_t* acc);
-template <>
-__device__ __forceinline__ void store_row16_vec<int8_t>(int8_t* p, const float* v,
-                                                        const uint32_t*) {
-  uint32_t w[4];
+template <typename OutT, bool UNIT = false>
+__device__ __forceinline__ void store_row16_vec(OutT* p, const float* v, const uint32_t* acc) {
+  if constexpr (std::is_same_v<OutT, int8_t>) {
+    uint32_t w[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) w[i] = pack4_s8(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
-}
-template <>
-__device__ __forceinline__ void store_row16_vec<__half>(__half* p, const float* v,
-                                                        const uint32_t*) {
-  uint4* q = reinterpret_cast<uint4*>(p);
+    for (int i = 0; i < 4; ++i) w[i] = pack4_s8<UNIT>(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else if constexpr (std::is_same_v<OutT, __half>) {
+    uint4* q = reinterpret_cast<uint4*>(p);
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    __half2 h0 = __floats2half2_rn(v[8 * i + 0], v[8 * i + 1]);
-    __half2 h1 = __floats2half2_rn(v[8 * i + 2], v[8 * i + 3]);
-    __half2 h2 = __floats2half2_rn(v[8 * i + 4], v[8 * i + 5]);
-    __half2 h3 = __floats2half2_rn(v[8 * i + 6], v[8 * i + 7]);
-    q[i] = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
-                      *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
+    for (int i = 0; i < 2; ++i) {
+      __half2 h0 = __floats2half2_rn(v[8 * i + 0], v[8 * i + 1]);
+      __half2 h1 = __floats2half2_rn(v[8 * i + 2], v[8 * i + 3]);
+      __half2 h2 = __floats2half2_rn(v[8 * i + 4], v[8 * i + 5]);
+      __half2 h3 = __floats2half2_rn(v[8 * i + 6], v[8 * i + 7]);
+      q[i] = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
+                        *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
+    }
+  } else if constexpr (std::is_same_v<OutT, float>) {
+    float4* q = reinterpret_cast<float4*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+    uint4* q = reinterpret_cast<uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = make_uint4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
   }
-}
-template <>
-__device__ __forceinline__ void store_row16_vec<float>(float* p, const float* v, const uint32_t*) {
-  float4* q = reinterpret_cast<float4*>(p);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) q[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-}
-template <>
-__device__ __forceinline__ void store_row16_vec<int32_t>(int32_t* p, const float*,
-                                                         const uint32_t* acc) {
-  uint4* q = reinterpret_cast<uint4*>(p);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) q[i] = make_uint4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
 }
 
 // ------------------------------------------------------------------ tiled
@@ -384,15 +410,16 @@ __device__ __forceinline__ void tiled_epilogue_cols(uint32_t t_row, const float*
       float v[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        v[j] = epi_value_t<ACT, DIV, RS>(static_cast<int32_t>(r[j]), cs[c * 16 + j], cb[c * 16 + j], ctx);
+        v[j] = epi_value_t<ACT, DIV, RS, kUnitForm<OutT, DIV>>(static_cast<int32_t>(r[j]), cs[c * 16 + j],
+                                                               cb[c * 16 + j], ctx);
       }
       OutT* dst = out + m * ldo + n0;
       if (vec_ok && n0 + 16 <= N) {
-        store_row16_vec<OutT>(dst, v, r);
+        store_row16_vec<OutT, kUnitForm<OutT, DIV>>(dst, v, r);
       } else {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          if (n0 + j < N) store_one<OutT>(dst + j, v[j], static_cast<int32_t>(r[j]));
+          if (n0 + j < N) store_one<OutT, kUnitForm<OutT, DIV>>(dst + j, v[j], static_cast<int32_t>(r[j]));
         }
       }
     }
@@ -764,7 +791,7 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
             if (m < Mrows && n_ok) {
               if (ctx.has_rs) ctx.rs = __ldg(ep.x_scale + m);
               const int32_t acc = static_cast<int32_t>(r[j]);
-              store_one<OutT>(out + static_cast<int64_t>(m) * ep.ldo + n, epi_value(acc, cs, cb, ctx), acc);
+              store_one_rt<OutT>(out + static_cast<int64_t>(m) * ep.ldo + n, epi_value(acc, cs, cb, ctx), acc, ctx);
             }
           }
         }
@@ -834,7 +861,7 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 OutT* orow = out + static_cast<int64_t>(m) * ep.ldo + n4;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                  if (n4 + c < ep.N) store_one<OutT>(orow + c, epi_value(a4[c], cs4[c], cb4[c], ctx), a4[c]);
+                  if (n4 + c < ep.N) store_one_rt<OutT>(orow + c, epi_value(a4[c], cs4[c], cb4[c], ctx), a4[c], ctx);
                 }
               }
             }
@@ -881,7 +908,7 @@ __global__ void qgemm_simt_kernel(const int8_t* __restrict__ a, const int8_t* __
   if (ctx.has_rs) ctx.rs = ep.x_scale[m];
   float cs, cb;
   col_consts(ep, ctx, n, cs, cb);
-  store_one<OutT>(reinterpret_cast<OutT*>(ep.out) + m * ep.ldo + n, epi_value(acc, cs, cb, ctx), acc);
+  store_one_rt<OutT>(reinterpret_cast<OutT*>(ep.out) + m * ep.ldo + n, epi_value(acc, cs, cb, ctx), acc, ctx);
 }
 
 // ------------------------------------------------------------------- host
@@ -939,6 +966,7 @@ EpiParams make_epi(const QGemmParams& p) {
   e.fold_out = p.fold_out_scale;
   e.div_out = p.div_out_scale;
   e.div_exact = p.div_exact;
+  e.out_kind = p.out_dtype;
   e.act = p.act;
   return e;
 }
@@ -1073,7 +1101,9 @@ int pair_max_clusters() {
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int c = 0;
-    if (cudaOccupancyMaxActiveClusters(&c, qgemm_pair_kernel<OutT>, &cfg) != cudaSuccess || c <= 0) {
+    // every mode of one output type has the same launch shape and resource use
+    if (cudaOccupancyMaxActiveClusters(&c, qgemm_pair_kernel<OutT, kActNone, kDivNone, false>, &cfg) != cudaSuccess ||
+        c <= 0) {
       (void)cudaGetLastError();
       c = sm_count() / 2;
     }
@@ -1083,8 +1113,8 @@ int pair_max_clusters() {
   return n;
 }
 
-template <typename OutT>
-cudaError_t launch_pair(const QGemmParams& p, cudaStream_t stream, const char** err) {
+template <typename OutT, int ACT, int DIV, bool RS>
+cudaError_t launch_pair_mode(const QGemmParams& p, cudaStream_t stream, const char** err) {
   CUtensorMap ta, tw, to;
   if (!make_a_tmap(&ta, p, kTileM) || !make_tmap(&tw, p.w, p.N, p.K, p.ldw, kTileM)) {
     if (err) *err = "cuTensorMapEncodeTiled failed";
@@ -1098,7 +1128,7 @@ cudaError_t launch_pair(const QGemmParams& p, cudaStream_t stream, const char** 
     use_tma_store = 0;
     to = ta;  // never dereferenced when stores are direct
   }
-  auto kern = qgemm_pair_kernel<OutT>;
+  auto kern = qgemm_pair_kernel<OutT, ACT, DIV, RS>;
   cudaError_t st =
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kDynamic);
   if (st != cudaSuccess) return st;
@@ -1110,6 +1140,36 @@ cudaError_t launch_pair(const QGemmParams& p, cudaStream_t stream, const char** 
   const int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   return launch_dependent(kern, dim3(2 * clusters), dim3(kTiledThreads), PairSmem::kDynamic, stream, ta, tw, to,
                           make_epi(p), num_kb, tiles_m, tiles_n, use_tma_store, out_aligned ? 1 : 0, slab_of(p));
+}
+
+// Host-side view of the epilogue mode a launch asks for.
+int host_epi_mode(const QGemmParams& p) {
+  const int div = p.div_out_scale ? (p.div_exact ? kDivExact : kDivRecip) : kDivNone;
+  return p.act | (div << 2) | (p.x_scale_kind == kScalePerRow ? 16 : 0);
+}
+
+// The pair kernel exists for the modes each output type is used with: every
+// mode for int8, no division for the floating-point outputs, the raw sum for
+// int32 (qgemm_choose_path sends other combinations to the single-CTA kernel).
+template <typename OutT>
+cudaError_t launch_pair(const QGemmParams& p, cudaStream_t stream, const char** err) {
+  if constexpr (std::is_same_v<OutT, int32_t>) {
+    return launch_pair_mode<OutT, kActNone, kDivNone, false>(p, stream, err);
+  } else if constexpr (std::is_same_v<OutT, int8_t>) {
+    DISC_EPI_SWITCH(host_epi_mode(p), return (launch_pair_mode<OutT, ACT, DIV, RS>(p, stream, err)))
+  } else {
+    switch (host_epi_mode(p)) {
+      DISC_EPI_CASE(0, 0, false, return (launch_pair_mode<OutT, ACT, DIV, RS>(p, stream, err)))
+      DISC_EPI_CASE(1, 0, false, return (launch_pair_mode<OutT, ACT, DIV, RS>(p, stream, err)))
+      DISC_EPI_CASE(2, 0, false, return (launch_pair_mode<OutT, ACT, DIV, RS>(p, stream, err)))
+      DISC_EPI_CASE(0, 0, true, return (launch_pair_mode<OutT, ACT, DIV, RS>(p, stream, err)))
+      DISC_EPI_CASE(1, 0, true, return (launch_pair_mode<OutT, ACT, DIV, RS>(p, stream, err)))
+      DISC_EPI_CASE(2, 0, true, return (launch_pair_mode<OutT, ACT, DIV, RS>(p, stream, err)))
+      default: break;
+    }
+  }
+  if (err) *err = "pair qgemm path: epilogue mode not available for this output type";
+  return cudaErrorInvalidValue;
 }
 
 template <typename OutT>
@@ -1226,12 +1286,18 @@ cudaError_t dispatch(const QGemmParams& p, int path, cudaStream_t stream, const 
 
 }  // namespace
 
+// The CTA-pair kernel is built for the epilogue modes in use (see launch_pair).
+static bool pair_mode_ok(const QGemmParams& p) {
+  if (p.act < kActNone || p.act > kActSilu) return false;
+  return p.out_dtype == kOutI8 || !p.div_out_scale;
+}
+
 int qgemm_choose_path(const QGemmParams& p) {
   if (!tma_ok(p)) return kPathSimt;
   if (p.path == kPathSimt) return kPathSimt;
   if (p.path == kPathSmallM && p.M <= 128 && p.a_slabs <= 1) return kPathSmallM;
   if (p.path == kPathTiled) return kPathTiled;
-  if (p.path == kPathPair) return kPathPair;
+  if (p.path == kPathPair) return pair_mode_ok(p) ? kPathPair : kPathTiled;
   if (p.path == kPathSkinny && p.M <= 65535 * kTileM) return kPathSkinny;
   if (p.path == kPathGemv && p.M <= 8 && p.K <= kGemvMaxK && p.a_slabs <= 1) return kPathGemv;
   // One to a few rows: the dp4a stream; from five rows on a large weight is
@@ -1243,10 +1309,11 @@ int qgemm_choose_path(const QGemmParams& p) {
   // covers the output.
   const int64_t skinny_ctas = ((p.N + skinny_bn(p) - 1) / skinny_bn(p)) * ((p.M + kTileM - 1) / kTileM);
   if (p.M <= 128 || (p.M <= 1024 && skinny_ctas <= sm_count())) return kPathSkinny;
-  // CTA pairs compute 256 x 256 tiles: worth it once there are enough of them
-  // to occupy every pair of SMs.
+  // CTA pairs compute 256 x 256 tiles and move a third less data per operation
+  // than single-CTA tiles, which are bound by the L2 feed for long K: they win
+  // as soon as a quarter of the SM pairs have a tile.
   const int64_t pair_tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
-  return pair_tiles >= sm_count() / 2 ? kPathPair : kPathTiled;
+  return pair_tiles >= sm_count() / 4 && pair_mode_ok(p) ? kPathPair : kPathTiled;
 }
 
 int64_t qgemm_splitk_ws_bytes(int64_t M, int64_t N, int64_t K) {

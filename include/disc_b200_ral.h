@@ -191,7 +191,8 @@ typedef struct disc_b200_qgemm_args {
    * reciprocal (folded into the column scale and bias when there is no
    * activation): the int8 result equals the divide-based one except for values
    * within a few ulp of a rounding tie, where it may land on the neighbouring
-   * level (at most 1 LSB, the tolerance of requantized outputs).  Non-zero: the
+   * level (at most 1 LSB, the tolerance of requantized outputs; out_scale and
+   * its reciprocal must be normal floats, 2^-126 <= |out_scale| <= 2^126).  Non-zero: the
    * correctly rounded IEEE quotient, bit for bit the divide-based quantize of
    * disc_lower_quantize_and_dequantize.cc:77-93, at about twice the epilogue
    * arithmetic. */
