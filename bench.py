@@ -28,9 +28,11 @@ sys.path.insert(0, str(ROOT))
 M_ROWS, K_DIM, N_DIM = 16384, 4096, 4096
 S_X, S_OUT = 0.02, 0.05
 NOMINAL_INT8_TOPS = 4500.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one qgemm_tiled launch at the
-# bench shape, from the ncu capture summarised under profiles/ (None = not captured yet).
-NCU_DRAM_BYTES_PER_LAUNCH = 1.04e8  # captured at rows=8192 (60.4 MB), reads and writes scaled by the row count
+# dram__bytes_read.sum + dram__bytes_write.sum of one qgemm_pair_kernel launch at the
+# bench shape, from the ncu capture summarised under profiles/ (captured at rows=8192: 60.4 MB;
+# the activation and output terms scaled by the row count, the weight term kept).
+NCU_DRAM_BYTES_PER_LAUNCH = 1.04e8
+VERIFY_ROWS = 64
 
 
 def _args():
@@ -41,6 +43,7 @@ def _args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=M_ROWS, help="activation rows per rank and step")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-encoder", action="store_true", help="qlinear workload: leave out the BERT-base record")
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the llama7b workload")
     ap.add_argument("--tp-row-blocks", type=int, default=None,
                     help="llama7b workload: row blocks per column-parallel linear (gather of one block overlaps "
@@ -186,7 +189,7 @@ def _cpu_oracle_port(a, w, w_scale, bias, seconds):
 def cpu_baseline(torch, seconds=12.0, sample_rows=1024):
     """TOPS of the CPU path on a bounded sample of the same workload (first `sample_rows` rows)."""
     a, w, w_scale, bias = _make_problem(torch, sample_rows, "cpu", 1234 + 1)
-    threads = os.cpu_count() or 1
+    threads = _host_threads()
     ops_ = 2.0 * sample_rows * K_DIM * N_DIM
     try:
         t = _cpu_onednn(torch, a, w, w_scale, bias, seconds, threads)
@@ -199,14 +202,39 @@ def cpu_baseline(torch, seconds=12.0, sample_rows=1024):
             "engine": engine, "ms_per_sample": t * 1e3}
 
 
+def _host_threads():
+    """Threads the CPU arm may use: the cores this process is allowed to run on."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def _reexec_with_all_threads():
+    """A launcher (torch.distributed.run) exports OMP_NUM_THREADS=1 to its workers; the OpenMP runtime
+    and oneDNN size their pools from it when they are loaded, before any later call can raise it.  The CPU arm is
+    meant to use every host thread it can, so it starts itself again once with the variable set."""
+    want = str(_host_threads())
+    if os.environ.get("OMP_NUM_THREADS") == want or os.environ.get("DISC_BENCH_CPU_ARM") == "1":
+        return
+    env = dict(os.environ, OMP_NUM_THREADS=want, MKL_NUM_THREADS=want, DISC_BENCH_CPU_ARM="1")
+    os.execve(sys.executable, [sys.executable] + sys.argv, env)
+
+
+def _workload_config(rows):
+    return {"workload": f"cfg1 quantized linear M={rows} K={K_DIM} N={N_DIM}, per-channel w scales, "
+                        f"f32 bias, int8 out @ {S_OUT}"}
+
+
 def run_reference(args):
-    import torch
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    _reexec_with_all_threads()
+    import torch
     sample_rows = 1024
     a, w, w_scale, bias = _make_problem(torch, sample_rows, "cpu", 1234 + 1)
-    threads = os.cpu_count() or 1
+    threads = _host_threads()
     torch.set_num_threads(threads)
     ops_ = 2.0 * sample_rows * K_DIM * N_DIM
     try:
@@ -228,19 +256,39 @@ def run_reference(args):
         step()
     dt = (time.perf_counter() - t0) / args.steps
     tops = ops_ / dt / 1e12
+    cfg = _workload_config(args.rows)
+    cfg["sample"] = f"each step times the first {sample_rows} of the {args.rows} rows (TOPS is per operation, so the " \
+                    "sample does not change the metric)"
     line = {
         "impl": "reference", "metric": "qgemm_int8_tops", "value": tops, "unit": "TOPS", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
-        "config": {"workload": f"cfg1 quantized linear M={M_ROWS} K={K_DIM} N={N_DIM}, per-channel w scales, "
-                               f"f32 bias, int8 out @ {S_OUT}", "sample_rows_per_step": sample_rows},
+        "config": cfg,
         "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": threads, "kind": "port", "engine": engine,
-                         "sample": f"first {sample_rows} of {M_ROWS} rows per step"},
+                         "threads_used": torch.get_num_threads(),
+                         "sample": f"first {sample_rows} of {args.rows} rows per step"},
         "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference's own x86 executable cannot be built (oneDNN v2 submodule empty, bazel/TF absent); "
                 "this arm runs the same library (oneDNN) on the same int8 operands on all host cores",
     }
     print(json.dumps(line), flush=True)
+
+
+def _verify_rows(torch, out_d, a_h, w_h, w_scale_h, bias_h, seed):
+    """Sampled rows of a step's int8 output against the CPU oracle's statement of the same epilogue
+    (divide-based).  The launch uses the reciprocal form, so a value may sit one level off at a rounding
+    tie.  Returns (rows checked, largest difference in int8 levels, share of values that differ)."""
+    import numpy as np
+    from oracle import c
+    rows = a_h.shape[0]
+    g = torch.Generator().manual_seed(seed)
+    pick = torch.unique(torch.cat([torch.tensor([0, rows - 1]), torch.randint(0, rows, (VERIFY_ROWS,), generator=g)]))
+    got = out_d[pick.to(out_d.device)].cpu().numpy()
+    acc = c.qgemm_acc(a_h[pick].numpy(), w_h.numpy())
+    _, want = c.qgemm_epilogue(acc, x_scale=np.float32(S_X), w_scale=w_scale_h.numpy(), out_scale=np.float32(S_OUT),
+                               bias=bias_h.numpy(), div_out=True)
+    d = np.abs(got.astype(np.int32) - want.astype(np.int32))
+    return int(pick.numel()), int(d.max()), float((d > 0).mean())
 
 
 def run_ours(args):
@@ -279,9 +327,14 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
+    for i in range(max(1, args.warmup)):
         step(i)
     barrier()
+    # Outside the timed region: sampled rows of the first step's output against the CPU oracle.
+    verified_rows, max_lsb_diff, flip_share = _verify_rows(torch, o_sets[0], a_sets[0].cpu(), w_h, ws_h, b_h, 77 + rank)
+    if max_lsb_diff > 1 or flip_share > 1e-3:
+        raise SystemExit(f"rank {rank}: the timed kernel's output differs from the oracle (max {max_lsb_diff} levels, "
+                         f"{flip_share:.2e} of the values): not printing a number for a wrong result")
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -312,6 +365,28 @@ def run_ours(args):
         print(json.dumps({"profile_run": True, "ms_per_step": total_ms / args.steps, "rows": rows}), flush=True)
         return
 
+    # ---- the library kernel the reference's GPU custom call runs (cuBLASLt int8 -> int32 through
+    # torch._int_mm, quantized_gpu_kernel_impl.cc:130-159), same shape and rotating operand sets
+    lib_ms = None
+    if hasattr(torch, "_int_mm"):
+        try:
+            acc_sets = [torch.empty((rows, N_DIM), dtype=torch.int32, device=dev) for _ in range(n_sets)]
+            wt = w.t()
+            for i in range(3):
+                torch._int_mm(a_sets[i % n_sets], wt, out=acc_sets[i % n_sets])
+            torch.cuda.synchronize()
+            l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            l0.record()
+            for i in range(args.steps):
+                torch._int_mm(a_sets[i % n_sets], wt, out=acc_sets[i % n_sets])
+            l1.record()
+            torch.cuda.synchronize()
+            lib_ms = l0.elapsed_time(l1) / args.steps
+            del acc_sets
+        except Exception:
+            lib_ms = None
+            torch.cuda.synchronize()
+
     # ---- end to end through the host-buffer API
     layer = HostQLinear(w, w_scale, x_scale, bias=bias, out_scale=out_scale, chunk_rows=2048)
     a_pin = a_h.pin_memory()
@@ -336,35 +411,49 @@ def run_ours(args):
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     total_ms, e2e_ms = times.tolist()
 
+    # ---- second record in the same process group: the W8A8 BERT-base encoder over a fixed global batch
+    # split over the ranks (the other half of the headline metric); the linear's operands are released first
+    del a_sets, o_sets, layer, a_pin, o_pin
+    torch.cuda.empty_cache()
+    encoder = None
+    if not args.skip_encoder:
+        enc_steps = max(5, min(args.steps, 30))
+        encoder = _encoder_measure(torch, dist, "bert_base", enc_steps, args.warmup, rank, world, local, dev, False)
+
     if rank == 0:
         ops_per_step = 2.0 * rows * K_DIM * N_DIM
         value = world * ops_per_step * args.steps / (total_ms * 1e-3) / 1e12
         e2e_value = world * ops_per_step * e2e_steps / (e2e_ms * 1e-3) / 1e12
         peaks = _peaks()
-        # The timed steps follow half a second of the same kernel back to back, so the GPU runs
-        # under its power cap like the seconds-long GEMM loop behind the "sustained" peak; the
-        # burst peak applies only if the cap never engaged.
+        # The timed region is one kernel launched back to back for a few milliseconds: the burst figure is
+        # the denominator.  When the power cap engaged during the half second of the same kernel before it,
+        # the fraction of the sustained figure is printed beside it.
         capped = bool(clocks and "sw_power_cap" in clocks.get("reasons", []))
-        peak_kind = "sustained" if capped else "burst"
-        peak_bf16 = peaks["bf16_sustained"] if capped else peaks["bf16"]
-        peak_i8 = 2.0 * peak_bf16
+        peak_i8 = 2.0 * peaks["bf16"]
         launch_ms = total_ms / args.steps
         achieved = ops_per_step / (launch_ms * 1e-3) / 1e12
         algo_bytes = rows * K_DIM + N_DIM * K_DIM + rows * N_DIM + 8 * N_DIM
+        lib_tops = ops_per_step / (lib_ms * 1e-3) / 1e12 if lib_ms else None
+        cfg = _workload_config(rows)
+        cfg.update({"rows_per_gpu": rows, "path": ops.qgemm_path(rows, N_DIM, K_DIM),
+                    "requantisation": "reciprocal form (at most 1 int8 level from the divide-based formula)",
+                    "l2": f"{n_sets} rotating operand sets ({n_sets * (rows * K_DIM + rows * N_DIM) >> 20} MiB) > 126 MB L2"})
         line = {
             "metric": "qgemm_int8_tops", "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": launch_ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "i8", "data": "synthetic",
-            "config": {"workload": f"cfg1 quantized linear M={rows} K={K_DIM} N={N_DIM}, per-channel w scales, "
-                                   f"f32 bias, int8 out @ {S_OUT}",
-                       "rows_per_gpu": rows, "path": ops.qgemm_path(rows, N_DIM, K_DIM),
-                       "l2": f"{n_sets} rotating operand sets ({n_sets * (rows * K_DIM + rows * N_DIM) >> 20} MiB) > 126 MB L2"},
+            "config": cfg,
+            "verified_rows": verified_rows, "max_lsb_diff": max_lsb_diff, "lsb_flip_share": flip_share,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_i8, "unit": "TOPS",
                          "frac": achieved / peak_i8, "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
-                         "peak_source": f"2 x {peaks['source']} cuBLAS bf16 {peak_kind} ({peak_bf16} TF/s): int8 issues "
+                         "peak_source": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16']} TF/s): int8 issues "
                                         f"at twice the bf16 rate; of {peaks['source']}",
-                         "frac_of_burst_peak": achieved / (2.0 * peaks["bf16"]),
+                         "frac_of_sustained_peak": achieved / (2.0 * peaks["bf16_sustained"]),
+                         "power_capped_before_timing": capped,
                          "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS,
+                         "cublaslt_int8_tops": lib_tops,
+                         "vs_cublaslt": (achieved / lib_tops) if lib_tops else None,
+                         "cublaslt_note": "torch._int_mm, int32 output, no epilogue; ours writes requantized int8",
                          "algorithmic_bytes": algo_bytes, "algorithmic_ops": ops_per_step,
                          "launch_ms_median": per_launch_ms[len(per_launch_ms) // 2]},
             "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": rows * K_DIM,
@@ -372,6 +461,8 @@ def run_ours(args):
             "gpu_launches": args.steps, "e2e_gpu_launches": e2e_launches,
             "clocks": clocks,
         }
+        if encoder is not None:
+            line["encoder"] = encoder
         if world == 1 and not args.skip_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(torch)
         print(json.dumps(line), flush=True)
@@ -380,25 +471,15 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def run_encoder(args):
+def _encoder_measure(torch, dist, workload, steps, warmup, rank, world, local, dev, profile):
     """Configurations 2 / 3: one step = one forward of the W8A8 encoder over the global batch
     (32 sequences of length U[16,512] for BERT-base, 64 of U[64,512] for BERT-large), the
-    sequences split over the ranks by length (no collective; total work fixed: "strong")."""
-    import torch
-    import torch.distributed as dist
+    sequences split over the ranks by length (no collective; total work fixed: "strong").
+    Every rank calls this; rank 0 gets the record (a dict), the others None."""
     from bladedisc_b200 import encoder as E
     from bladedisc_b200 import ops
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the quantized path has no CPU fallback")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    if args.workload == "bert_base":
+    if workload == "bert_base":
         cfg, batch, lo = E.EncoderConfig.bert_base(), 32, 16
     else:
         cfg, batch, lo = E.EncoderConfig.bert_large(), 64, 64
@@ -412,13 +493,14 @@ def run_encoder(args):
     lens_d = torch.empty_like(lens_pin, device=dev)
     cls_pin = torch.empty((max(len(assign), 1), cfg.hidden), dtype=torch.float16).pin_memory()
 
-    # The forward is a fixed sequence of ~100 short launches: capture it once per batch shape
+    # The forward is a fixed sequence of short launches: capture it once per batch shape
     # and replay it, so that launch latency does not dominate small per-GPU batches.
     side = torch.cuda.Stream(dev)
     graph, out_ref = None, [None]
     if have_work:
         ids_d.copy_(ids_pin)
         lens_d.copy_(lens_pin)
+        qenc.prepare(ids_d, lens_d)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(2):
@@ -449,7 +531,7 @@ def run_encoder(args):
         ids_d.copy_(ids_pin, non_blocking=True)
         lens_d.copy_(lens_pin, non_blocking=True)
         device_step()
-        cls_pin[:len(assign)].copy_(out_ref[0][:, 0, :], non_blocking=True)
+        cls_pin[:len(assign)].copy_(qenc.first_tokens(out_ref[0]), non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     def barrier():
@@ -457,63 +539,78 @@ def run_encoder(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    def timed(fn, n):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
+        for _ in range(n):
             fn()
         e1.record()
         barrier()
         return e0.elapsed_time(e1)
 
-    for _ in range(max(3, args.warmup)):
+    for _ in range(max(3, warmup)):
         device_step()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     t_hold = time.perf_counter()
-    while not args.profile and time.perf_counter() - t_hold < 0.5:
+    while not profile and time.perf_counter() - t_hold < 0.5:
         device_step()
         torch.cuda.synchronize()
-    dev_ms = timed(device_step, args.steps)
+    dev_ms = timed(device_step, steps)
     clocks = sampler.stop() if rank == 0 else None
-    if args.profile:
-        if rank == 0:
-            print(json.dumps({"profile_run": True, "ms_per_step": dev_ms / args.steps, "workload": args.workload}))
-        return
+    if profile:
+        return {"profile_run": True, "ms_per_step": dev_ms / steps, "workload": workload} if rank == 0 else None
     for _ in range(3):
         e2e_step()
-    e2e_steps = max(3, min(args.steps, 20))
+    e2e_steps = max(3, min(steps, 20))
     e2e_ms = timed(e2e_step, e2e_steps)
     if ops.kernel_status() != 0:
         raise SystemExit("kernel status non-zero: a bounded wait ran out")
     times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
-    tokens = torch.tensor([float(my_ids_h.numel()), float(my_lens_h.sum())], dtype=torch.float64, device=dev)
+    tokens = torch.tensor([float(qenc.rows_processed if have_work else 0), float(my_lens_h.sum())],
+                          dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
         dist.all_reduce(tokens, op=dist.ReduceOp.SUM)
     dev_ms, e2e_ms = times.tolist()
+    if rank != 0:
+        return None
+    return {
+        "metric": f"quant_{workload}_seqs_per_s", "value": batch * steps / (dev_ms * 1e-3), "unit": "sequences/s",
+        "n_gpus": world, "steps": steps, "warmup": max(3, warmup), "ms_per_step": dev_ms / steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
+        "config": {"workload": f"{workload} W8A8 encoder forward, {cfg.layers} layers, hidden {cfg.hidden}, "
+                               f"global batch {batch}, lengths U[{lo},512], masked attention",
+                   "sharding": "sequences split by length over ranks, no collective",
+                   "rows_through_the_linears_all_ranks": int(tokens[0]), "real_tokens": int(tokens[1]),
+                   "cuda_graph": graph is not None,
+                   "l2": "activations of a forward are rewritten every step",
+                   "note": qenc.describe()},
+        "e2e": {"value": batch * e2e_steps / (e2e_ms * 1e-3), "unit": "sequences/s",
+                "h2d_bytes_per_step": int(ids_pin.numel() * 8 + lens_pin.numel() * 4),
+                "d2h_bytes_per_step": int(len(assign) * cfg.hidden * 2), "steps": e2e_steps},
+        "gpu_launches": launches_per_fwd * steps, "launches_per_forward": launches_per_fwd,
+        "clocks": clocks,
+    }
+
+
+def run_encoder(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the quantized path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    line = _encoder_measure(torch, dist, args.workload, args.steps, args.warmup, rank, world, local, dev, args.profile)
     if rank == 0:
-        name = args.workload
-        line = {
-            "metric": f"quant_{name}_seqs_per_s", "value": batch * args.steps / (dev_ms * 1e-3), "unit": "sequences/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": dev_ms / args.steps,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
-            "config": {"workload": f"{name} W8A8 encoder forward, {cfg.layers} layers, hidden {cfg.hidden}, "
-                                   f"global batch {batch}, lengths U[{lo},512], padded-mask attention",
-                       "sharding": "sequences split by length over ranks, no collective",
-                       "padded_tokens_all_ranks": int(tokens[0]), "real_tokens": int(tokens[1]),
-                       "cuda_graph": graph is not None,
-                       "l2": "activations of a forward (> 126 MB for the full batch) are rewritten every step",
-                       "note": "the two attention batched GEMMs per layer run on cuBLAS (torch.matmul), as the "
-                               "reference runs them through ral_gemm; every other kernel is this library's"},
-            "e2e": {"value": batch * e2e_steps / (e2e_ms * 1e-3), "unit": "sequences/s",
-                    "h2d_bytes_per_step": int(ids_pin.numel() * 8 + lens_pin.numel() * 4),
-                    "d2h_bytes_per_step": int(len(assign) * cfg.hidden * 2), "steps": e2e_steps},
-            "gpu_launches": launches_per_fwd * args.steps, "launches_per_forward": launches_per_fwd,
-            "clocks": clocks,
-        }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

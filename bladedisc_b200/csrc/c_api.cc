@@ -17,6 +17,7 @@
 #include "ral/metadata.h"
 #include "ral/nccl_dyn.h"
 #include "../../include/disc_b200_ral.h"
+#include "kernels/attention.h"
 #include "kernels/observer.h"
 #include "kernels/qconv.h"
 #include "kernels/qgemm.h"
@@ -250,6 +251,28 @@ int32_t disc_b200_softmax(const void* x, void* y, int32_t type, int64_t rows, in
   const char* detail = nullptr;
   const cudaError_t st = disc_b200::softmax_launch(p, static_cast<cudaStream_t>(stream), &detail);
   return finish(st, "softmax", detail);
+}
+
+int32_t disc_b200_attention(const disc_b200_attention_args* a, void* stream) {
+  if (!a) {
+    g_last_error = "attention: null args";
+    return 1;
+  }
+  static_assert(sizeof(disc_b200::AttnBlock) == 4 * sizeof(int32_t), "block entries are four int32");
+  disc_b200::AttentionParams p;
+  p.qkv = a->qkv;
+  p.tokens = a->tokens;
+  p.ld_qkv = a->ld_qkv;
+  p.heads = a->heads;
+  p.blocks = reinterpret_cast<const disc_b200::AttnBlock*>(a->blocks);
+  p.num_blocks = a->num_blocks;
+  p.scale = a->scale;
+  p.out = a->out;
+  p.ld_out = a->ld_out;
+  p.out_scale = a->out_scale;
+  const char* detail = nullptr;
+  const cudaError_t st = disc_b200::attention_launch(p, static_cast<cudaStream_t>(stream), &detail);
+  return finish(st, "attention", detail);
 }
 
 int32_t disc_b200_gated_quantize(const disc_b200_gated_quantize_args* a, void* stream) {

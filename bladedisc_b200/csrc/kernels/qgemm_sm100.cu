@@ -26,6 +26,7 @@
 #include <mutex>
 #include <type_traits>
 
+#include "attention.h"
 #include "device_info.h"
 #include "qgemm.h"
 #include "rowops.h"
@@ -1479,7 +1480,8 @@ int kernel_status_fetch_and_clear() {
     cudaMemcpyToSymbol(g_kernel_status, &z, sizeof(int));
   }
   const int r = rowops_status_fetch_and_clear();
-  return h != 0 ? h : r;
+  const int a = attention_status_fetch_and_clear();
+  return h != 0 ? h : (r != 0 ? r : a);
 }
 
 }  // namespace disc_b200

@@ -72,6 +72,14 @@ class GatedQuantArgs(Structure):
     ]
 
 
+class AttentionArgs(Structure):
+    _fields_ = [
+        ("qkv", c_void_p), ("tokens", c_int64), ("ld_qkv", c_int64), ("heads", c_int32),
+        ("blocks", c_void_p), ("num_blocks", c_int32), ("scale", c_float),
+        ("out", c_void_p), ("ld_out", c_int64), ("out_scale", c_void_p),
+    ]
+
+
 class WeightOnlyQGemmArgs(Structure):
     _fields_ = [
         ("x", c_void_p), ("w", c_void_p), ("scale", c_void_p), ("zero_point", c_void_p), ("bias", c_void_p),
@@ -123,6 +131,7 @@ SIGNATURES = {
                                            c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "disc_b200_softmax": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int64, c_void_p,
                                     c_void_p, c_float, c_int32, c_void_p]),
+    "disc_b200_attention": (c_int32, [POINTER(AttentionArgs), c_void_p]),
     "disc_b200_nccl_available": (c_int32, []),
     "disc_b200_nccl_unique_id": (c_int32, [c_void_p]),
     "disc_b200_nccl_comm_create": (c_int32, [c_void_p, c_int32, c_int32, POINTER(c_void_p)]),

@@ -484,6 +484,51 @@ def softmax(x: torch.Tensor, scale: float = 1.0, lens: Optional[torch.Tensor] = 
     return y
 
 
+def attention_blocks(lens) -> torch.Tensor:
+    """Work list of `attention`: one row {first token of the sequence, length, first query row of the block, 0}
+    per 128 query rows of each sequence, for sequences packed one after the other (host tensor, int32 [n, 4]).
+    Longer sequences come first so that the last wave of thread blocks holds the short ones."""
+    rows = []
+    tok0 = 0
+    for n in (int(v) for v in lens):
+        if n < 1 or n > 512:
+            raise ValueError(f"sequence length {n} outside 1..512")
+        rows += [(tok0, n, q0, 0) for q0 in range(0, n, 128)]
+        tok0 += n
+    rows.sort(key=lambda r: -r[1])
+    return torch.tensor(rows, dtype=torch.int32).reshape(-1, 4)
+
+
+def attention(qkv: torch.Tensor, blocks: torch.Tensor, heads: int, scale: float,
+              out_scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """softmax(q k^T * scale) v per head over packed sequences, in one kernel.
+
+    ``qkv``: f16 [tokens, 3 * heads * 64]; ``blocks``: device copy of ``attention_blocks(lens)``.
+    Returns [tokens, heads * 64]: int8 quantized at ``out_scale`` (a device scalar), f16 without it."""
+    qkv = _cuda(qkv, "qkv", torch.float16)
+    if qkv.dim() != 2 or qkv.shape[1] != 3 * heads * 64:
+        raise ValueError(f"qkv must be [tokens, {3 * heads * 64}], got {tuple(qkv.shape)}")
+    if not blocks.is_cuda or blocks.dtype != torch.int32 or blocks.dim() != 2 or blocks.shape[1] != 4:
+        raise ValueError("blocks must be a CUDA int32 [n, 4] tensor (see attention_blocks)")
+    tokens = qkv.shape[0]
+    hidden = heads * 64
+    dtype = torch.int8 if out_scale is not None else torch.float16
+    if out is None:
+        out = torch.empty((tokens, hidden), dtype=dtype, device=qkv.device)
+    elif out.dtype != dtype or tuple(out.shape) != (tokens, hidden) or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [tokens, hidden] tensor of the result's dtype")
+    args = _lib.AttentionArgs()
+    args.qkv, args.tokens, args.ld_qkv, args.heads = qkv.data_ptr(), tokens, qkv.shape[1], heads
+    blocks = blocks.contiguous()
+    args.blocks, args.num_blocks, args.scale = blocks.data_ptr(), blocks.shape[0], float(scale)
+    args.out, args.ld_out = out.data_ptr(), hidden
+    if out_scale is not None:
+        out_scale = _cuda(out_scale, "out_scale", torch.float32)
+        args.out_scale = out_scale.data_ptr()
+    _lib.check(_lib.load().disc_b200_attention(ctypes.byref(args), _stream()))
+    return out
+
+
 def rope_kv_append(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cos: torch.Tensor,
                    sin: torch.Tensor, batch: int, seq: int, pos0: int) -> None:
     """Rotates q and k inside ``qkv`` (fp16 ``[batch * seq, 3 * heads * dim]``, q in place) and

@@ -409,6 +409,33 @@ int32_t disc_b200_softmax(const void* x, void* y, int32_t type, int64_t rows, in
                           int64_t rows_per_batch, const int32_t* lens, const void* mask,
                           float scale, int32_t log_softmax, void* stream);
 
+/* Masked self-attention over packed sequences in one kernel:
+ * out = quantize(softmax(Q K^T * scale) V) per head, the scores never leaving the
+ * SM.  It stands for the chain the reference's compiled encoder runs there:
+ * two library GEMMs (ral_gemm,
+ * tao_compiler/mlir/ral/context/stream_executor_based_impl.cc:551-637), the
+ * generated softmax between them and the quantize after them.
+ * qkv: f16 [tokens, 3 * heads * 64] (q | k | v, head h in columns h * 64 .. of
+ * each third), sequences stored one after the other without padding rows.
+ * blocks: device array with one entry per block of 128 query rows of one
+ * sequence ({first token of the sequence, its length 1..512, first row of the
+ * block inside the sequence, 0}); a sequence of length n has ceil(n / 128).
+ * out: [tokens, heads * 64], int8 quantized at *out_scale (reciprocal form,
+ * at most one level from the divide-based quantize) or f16 when out_scale is NULL. */
+typedef struct disc_b200_attention_args {
+  const void* qkv;
+  int64_t tokens;
+  int64_t ld_qkv;
+  int32_t heads;
+  const int32_t* blocks;
+  int32_t num_blocks;
+  float scale;
+  void* out;
+  int64_t ld_out;
+  const float* out_scale;
+} disc_b200_attention_args;
+int32_t disc_b200_attention(const disc_b200_attention_args* args, void* stream);
+
 /* ---- Collectives of the column-parallel (N-split) configuration.
  * One process per GPU.  NCCL is reached through dlopen (the copy already
  * mapped into the process, else the system's libnccl.so.2), so the library

@@ -108,3 +108,32 @@ def minmax_qparams(min_val, max_val, qmin=-128, qmax=127, symmetric=True, symmet
         scale = np.maximum((hi - lo) / np.float32(qmax - qmin), eps).astype(np.float32)
         zp = np.clip(qmin - np.rint(lo / scale).astype(np.int32), qmin, qmax).astype(np.int32)
     return scale, zp
+
+
+def attention_packed(qkv, lens, heads, scale):
+    """softmax(q k^T * scale) v per sequence and head over packed sequences, float32.
+
+    qkv: [tokens, 3 * heads * d] (q | k | v), sequences one after the other.  This is the
+    arithmetic of the chain the reference's compiled encoder runs for self-attention: a batched
+    GEMM (ral_gemm, stream_executor_based_impl.cc:551-637), the row softmax its compiler
+    generates (lhlo_legalize_roots_to_loops.cc:1263-1289, max-subtracted) and a second GEMM.
+    No reference source states the chain as one function, so this restates the defining formula;
+    tests pin it to eager torch."""
+    qkv = np.asarray(qkv, dtype=f32)
+    hidden = qkv.shape[1] // 3
+    d = hidden // heads
+    out = np.empty((qkv.shape[0], hidden), dtype=f32)
+    t0 = 0
+    for n in (int(v) for v in lens):
+        blk = qkv[t0:t0 + n]
+        for h in range(heads):
+            q = blk[:, h * d:(h + 1) * d]
+            k = blk[:, hidden + h * d:hidden + (h + 1) * d]
+            v = blk[:, 2 * hidden + h * d:2 * hidden + (h + 1) * d]
+            s = (q @ k.T).astype(f32) * f32(scale)
+            s = s - s.max(axis=1, keepdims=True)
+            p = np.exp(s).astype(f32)
+            p = p / p.sum(axis=1, keepdims=True)
+            out[t0:t0 + n, h * d:(h + 1) * d] = (p @ v).astype(f32)
+        t0 += n
+    return out

@@ -287,3 +287,21 @@ def test_observer_restatement_matches_the_reference_observers():
     assert (np_ref.minmax_qparams(lo, hi)[0] == q["tq_s_x"]).all()
     lo, hi = np_ref.observe_minmax([q["tq_w1"]], ch_axis=0)
     assert (np_ref.minmax_qparams(lo, hi)[0] == q["tq_s_w1"]).all()
+
+
+def test_attention_restatement_is_eager_torch_attention():
+    """oracle/np_ref.py:attention_packed restates softmax(q k^T * scale) v; the reference has no single
+    function for it (two library GEMMs and a generated softmax), so it is pinned to eager torch."""
+    import torch
+    rng = np.random.default_rng(3)
+    lens, heads, d = [5, 33, 70], 3, 64
+    qkv = rng.standard_normal((sum(lens), 3 * heads * d)).astype(np.float32)
+    got = np_ref.attention_packed(qkv, lens, heads, 0.125)
+    t0 = 0
+    for n in lens:
+        blk = torch.from_numpy(qkv[t0:t0 + n])
+        q, k, v = (blk[:, i * heads * d:(i + 1) * heads * d].view(n, heads, d).transpose(0, 1) for i in range(3))
+        want = torch.softmax(q @ k.transpose(-1, -2) * 0.125, dim=-1) @ v
+        want = want.transpose(0, 1).reshape(n, heads * d).numpy()
+        assert np.allclose(got[t0:t0 + n], want, rtol=1e-5, atol=1e-6)
+        t0 += n
