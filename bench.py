@@ -504,13 +504,13 @@ def _encoder_measure(torch, dist, workload, steps, warmup, rank, world, local, d
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(2):
-                out_ref[0] = qenc.forward(ids_d, lens_d)
+                out_ref[0] = qenc.forward_packed(ids_d, lens_d)
         torch.cuda.synchronize()
         launches_per_fwd = qenc.kernel_launches // 2
         try:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
-                out_ref[0] = qenc.forward(ids_d, lens_d)
+                out_ref[0] = qenc.forward_packed(ids_d, lens_d)
         except Exception:
             graph = None
             torch.cuda.synchronize()
@@ -523,7 +523,7 @@ def _encoder_measure(torch, dist, workload, steps, warmup, rank, world, local, d
         if graph is not None:
             graph.replay()
         else:
-            out_ref[0] = qenc.forward(ids_d, lens_d)
+            out_ref[0] = qenc.forward_packed(ids_d, lens_d)
 
     def e2e_step():
         if not have_work:

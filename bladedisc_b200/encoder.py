@@ -7,11 +7,14 @@ activation scales from calibration), LayerNorm / softmax / quantize are the
 row kernels, and the epilogues carry the fusions the reference needs separate
 generated kernels for (dequantize + bias [+ GELU] [+ quantize]).
 
-The two batched attention products (Q K^T and P V) are ordinary fp16 batched
-GEMMs; in the reference they are `ral_gemm` = cuBLAS through StreamExecutor
-(tao_compiler/mlir/ral/context/stream_executor_based_impl.cc:551-637), outside
-the quantized path, and here they are torch.matmul (cuBLAS) as well.  The
-embedding gather is torch indexing.  Everything else is this library.
+Sequences are packed: the rows of every linear, LayerNorm and quantize are
+the real tokens of the batch, one sequence after the other, without padding
+rows.  Self-attention is one fused kernel per layer (`ops.attention`: Q K^T,
+masked softmax, P V and the quantize of the context, scores kept on chip); in
+the reference the two products are `ral_gemm` = cuBLAS through StreamExecutor
+(tao_compiler/mlir/ral/context/stream_executor_based_impl.cc:551-637) with a
+generated softmax between them.  The embedding gather is torch indexing.
+Everything else is this library.
 
 Weights are random (N(0, 0.02)) and token ids synthetic: there is no network
 for checkpoints or datasets.
@@ -46,7 +49,7 @@ class EncoderConfig:
 
     @staticmethod
     def tiny():
-        return EncoderConfig(layers=2, hidden=128, heads=4, ffn=256, vocab=1000, max_len=64)
+        return EncoderConfig(layers=2, hidden=128, heads=2, ffn=256, vocab=1000, max_len=64)
 
 
 @dataclass
@@ -187,26 +190,58 @@ class QuantEncoder:
                 d[name] = getattr(lw, name).to(h)
             self.layers.append(d)
         self.kernel_launches = 0
+        self.rows_processed = 0
 
-    def forward(self, ids: torch.Tensor, lens: torch.Tensor) -> torch.Tensor:
-        cfg = self.cfg
+    # ------------------------------------------------------------------ batch plan
+    def prepare(self, ids: torch.Tensor, lens: torch.Tensor) -> None:
+        """Host-side plan for one batch shape: where every real token sits in the padded `ids`, the work list
+        of the attention kernel, and the first token of every sequence.  Reads `lens` on the host (one
+        synchronisation), so it is called once per batch shape, outside any stream capture; `forward_packed`
+        then only launches kernels."""
+        lens_h = [int(v) for v in lens.cpu().tolist()]
         B, L = ids.shape
+        if len(lens_h) != B or any(n < 1 or n > L for n in lens_h):
+            raise ValueError("lens must hold one length in 1..L per sequence")
+        dev = ids.device
+        flat = torch.cat([torch.arange(n, dtype=torch.int64) + b * L for b, n in enumerate(lens_h)])
+        pos = torch.cat([torch.arange(n, dtype=torch.int64) for n in lens_h])
+        starts = torch.tensor([0] + lens_h[:-1], dtype=torch.int64).cumsum(0)
+        self._plan = {
+            "key": (B, L, tuple(lens_h)), "flat": flat.to(dev), "pos": pos.to(dev), "first": starts.to(dev),
+            "blocks": ops.attention_blocks(lens_h).to(dev), "tokens": int(sum(lens_h)), "lens": lens_h,
+        }
+        self.rows_processed = self._plan["tokens"]
+
+    def _plan_for(self, ids, lens):
+        plan = getattr(self, "_plan", None)
+        if plan is None or plan["key"][:2] != tuple(ids.shape):
+            self.prepare(ids, lens)
+        return self._plan
+
+    def describe(self) -> str:
+        return ("sequences packed (rows of the linears = real tokens); self-attention is this library's fused "
+                "kernel (tcgen05 kind::f16, scores in TMEM, int8 context out); embedding gather by torch indexing; "
+                "every other kernel is this library's")
+
+    def first_tokens(self, packed: torch.Tensor) -> torch.Tensor:
+        """Row of the first token of every sequence ([CLS]) of a packed result."""
+        return packed[self._plan["first"]]
+
+    def forward_packed(self, ids: torch.Tensor, lens: torch.Tensor) -> torch.Tensor:
+        """[tokens, hidden] f16, sequences one after the other."""
+        cfg = self.cfg
+        plan = self._plan_for(ids, lens)
         H, heads = cfg.hidden, cfg.heads
-        d = H // heads
         sc = self.scales
         n = 0
-        emb = self.word[ids] + self.pos[:L][None]
-        x, xq = ops.layernorm_quant(emb.view(B * L, H), self.emb_g, self.emb_b, sc["l0.attn_in"], eps=cfg.eps)
+        emb = self.word[ids.reshape(-1)[plan["flat"]]] + self.pos[plan["pos"]]
+        x, xq = ops.layernorm_quant(emb, self.emb_g, self.emb_b, sc["l0.attn_in"], eps=cfg.eps)
         n += 1
-        inv_sqrt_d = 1.0 / math.sqrt(d)
+        inv_sqrt_d = 1.0 / math.sqrt(H // heads)
         for i, lw in enumerate(self.layers):
             qkv = ops.qgemm(xq, lw["wqkv"], x_scale=sc[f"l{i}.attn_in"], w_scale=lw["wqkv_s"], bias=lw["bqkv"],
                             out_dtype=torch.float16)
-            qkv = qkv.view(B, L, 3, heads, d).permute(2, 0, 3, 1, 4)  # [3, B, heads, L, d]
-            scores = torch.matmul(qkv[0], qkv[1].transpose(-1, -2))   # cuBLAS, [B, heads, L, L]
-            probs = ops.softmax(scores, scale=inv_sqrt_d, lens=lens)
-            ctx = torch.matmul(probs, qkv[2]).transpose(1, 2).reshape(B * L, H)  # cuBLAS
-            ctxq = ops.quantize(ctx, sc[f"l{i}.ctx"])
+            ctxq = ops.attention(qkv, plan["blocks"], heads, inv_sqrt_d, out_scale=sc[f"l{i}.ctx"])
             attn = ops.qgemm(ctxq, lw["wo"], x_scale=sc[f"l{i}.ctx"], w_scale=lw["wo_s"], bias=lw["bo"],
                              out_dtype=torch.float16)
             h1, h1q = ops.layernorm_quant(attn, lw["ln1_g"], lw["ln1_b"], sc[f"l{i}.ffn_in"], eps=cfg.eps, residual=x)
@@ -216,9 +251,18 @@ class QuantEncoder:
                             out_dtype=torch.float16)
             nxt = sc[f"l{i + 1}.attn_in"] if i + 1 < len(self.layers) else sc[f"l{i}.attn_in"]
             x, xq = ops.layernorm_quant(ffn, lw["ln2_g"], lw["ln2_b"], nxt, eps=cfg.eps, residual=h1)
-            n += 8
+            n += 7
         self.kernel_launches += n
-        return x.view(B, L, H)
+        return x
+
+    def forward(self, ids: torch.Tensor, lens: torch.Tensor) -> torch.Tensor:
+        """[B, L, hidden] f16 with the packed result scattered back to the padded layout (padding rows zero)."""
+        B, L = ids.shape
+        self.prepare(ids, lens)
+        packed = self.forward_packed(ids, lens)
+        out = torch.zeros((B * L, self.cfg.hidden), dtype=packed.dtype, device=packed.device)
+        out[self._plan["flat"]] = packed
+        return out.view(B, L, self.cfg.hidden)
 
 
 def build_quant_encoder(cfg: EncoderConfig, seed: int = 1234, device="cuda", calib_batches: int = 4,
@@ -239,9 +283,7 @@ def shard_batch(ids: torch.Tensor, lens: torch.Tensor, world: int, rank: int):
         return ids[:0, :1], lens[:0], assign
     idx = torch.tensor(assign, device=ids.device)
     my_lens = lens[idx]
-    # Padded to a multiple of 8 tokens: rows of the attention scores are then whole 16-byte
-    # vectors and the softmax takes its aligned path (the padding is masked by the lengths).
-    L = -(-int(my_lens.max()) // 8) * 8
+    L = int(my_lens.max())
     mine = ids[idx][:, :L]
     if mine.shape[1] < L:
         mine = torch.nn.functional.pad(mine, (0, L - mine.shape[1]))

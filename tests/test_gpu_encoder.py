@@ -45,9 +45,17 @@ def test_quantized_mlp_config0():
                                  out_scale=s_mid.numpy(), bias=b1.numpy(), act="gelu", div_out=True)
     d_mid = np.abs(midq.cpu().numpy().astype(int) - midq_o.astype(int))
     assert d_mid.max() <= 1 and (d_mid > 0).mean() < 1e-3  # erf of libdevice vs libm
-    y_o, _ = c.qgemm_epilogue(c.qgemm_acc(midq_o, w2q.numpy()), x_scale=s_mid.numpy(), w_scale=s_w2.numpy(),
-                              bias=b2.numpy())
-    assert np.allclose(y.cpu().numpy(), y_o, rtol=1e-2, atol=1e-3)
+    # the second linear, stage by stage: on the int8 activations the GPU produced it equals the oracle within
+    # the floating-point tolerance; against the oracle's own activations it may differ by what the few
+    # one-level differences of `mid` carry through the weights (one level = s_mid, times |w2|, per flipped value)
+    y_same_in, _ = c.qgemm_epilogue(c.qgemm_acc(midq.cpu().numpy().reshape(-1, 3072), w2q.numpy()),
+                                    x_scale=s_mid.numpy(), w_scale=s_w2.numpy(), bias=b2.numpy())
+    assert np.allclose(y.cpu().numpy().reshape(-1, 768), y_same_in, rtol=1e-2, atol=1e-3)
+    y_o, _ = c.qgemm_epilogue(c.qgemm_acc(midq_o.reshape(-1, 3072), w2q.numpy()), x_scale=s_mid.numpy(),
+                              w_scale=s_w2.numpy(), bias=b2.numpy())
+    flips_per_row = (d_mid.reshape(-1, 3072) > 0).sum(axis=1).max()
+    bound = 1e-3 + flips_per_row * float(s_mid) * float(w2.abs().max())
+    assert np.abs(y.cpu().numpy().reshape(-1, 768) - y_o).max() <= bound
     # and the eager fake-quant model built the way the reference's tests build it
     fq = torch.fake_quantize_per_tensor_affine
     zp1, zp2 = torch.zeros(3072, dtype=torch.int32), torch.zeros(768, dtype=torch.int32)
@@ -79,7 +87,7 @@ def test_small_encoder_matches_fake_quant_model():
     assert float(d_q.max()) < 0.35, float(d_q.max())
     assert float(d_q.mean()) < float(d_fp.mean()) * 1.5 + 0.01
     assert torch.isfinite(got).all()
-    assert qenc.kernel_launches == 1 + 8 * cfg.layers
+    assert qenc.kernel_launches == 1 + 7 * cfg.layers
 
 
 def test_sharded_batches_cover_the_batch_and_agree():
@@ -97,9 +105,8 @@ def test_sharded_batches_cover_the_batch_and_agree():
         out = qenc.forward(my_ids, my_lens)
         for j, seq in enumerate(assign):
             n = int(lens[seq])
-            # the attention products run on cuBLAS, which may order its sums differently for a
-            # different batch shape; everything else is bitwise independent of the batch
-            diff = (out[j, :n].float() - full[seq, :n].float()).abs()
-            assert float(diff.mean()) < 5e-3 and float(diff.max()) < 0.15, f"sequence {seq} differs when sharded"
+            # every kernel computes a row (and the attention a sequence) independently of what else is in the
+            # batch, and all linear paths share one epilogue arithmetic: the result is the same bytes
+            assert torch.equal(out[j, :n], full[seq, :n]), f"sequence {seq} differs when sharded"
         seen += assign
     assert sorted(seen) == list(range(9))
