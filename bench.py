@@ -44,6 +44,8 @@ def _args():
     ap.add_argument("--rows", type=int, default=M_ROWS, help="activation rows per rank and step")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-encoder", action="store_true", help="qlinear workload: leave out the BERT-base record")
+    ap.add_argument("--shard-of", type=int, default=None,
+                    help="encoder workloads on one GPU: run the share rank 0 of this many ranks would get")
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the llama7b workload")
     ap.add_argument("--tp-row-blocks", type=int, default=None,
                     help="llama7b workload: row blocks per column-parallel linear (gather of one block overlaps "
@@ -372,9 +374,15 @@ def run_ours(args):
         try:
             acc_sets = [torch.empty((rows, N_DIM), dtype=torch.int32, device=dev) for _ in range(n_sets)]
             wt = w.t()
-            for i in range(3):
-                torch._int_mm(a_sets[i % n_sets], wt, out=acc_sets[i % n_sets])
-            torch.cuda.synchronize()
+            # the same treatment as the kernel above: half a second of itself first, so that both are timed
+            # in the clock state their own load produces
+            t_hold = time.perf_counter()
+            j = 0
+            while time.perf_counter() - t_hold < 0.5:
+                for _ in range(20):
+                    torch._int_mm(a_sets[j % n_sets], wt, out=acc_sets[j % n_sets])
+                    j += 1
+                torch.cuda.synchronize()
             l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             l0.record()
             for i in range(args.steps):
@@ -471,7 +479,7 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def _encoder_measure(torch, dist, workload, steps, warmup, rank, world, local, dev, profile):
+def _encoder_measure(torch, dist, workload, steps, warmup, rank, world, local, dev, profile, shard_of=None):
     """Configurations 2 / 3: one step = one forward of the W8A8 encoder over the global batch
     (32 sequences of length U[16,512] for BERT-base, 64 of U[64,512] for BERT-large), the
     sequences split over the ranks by length (no collective; total work fixed: "strong").
@@ -486,7 +494,10 @@ def _encoder_measure(torch, dist, workload, steps, warmup, rank, world, local, d
     enc, qenc, scales = E.build_quant_encoder(cfg, seed=1234, device=dev, min_len=lo)
     del enc
     ids_h, lens_h = E.synthetic_batch(cfg, batch, lo, 512, seed=4321, device="cpu")
-    my_ids_h, my_lens_h, assign = E.shard_batch(ids_h, lens_h, world, rank)
+    if shard_of:   # one process standing in for rank 0 of `shard_of` ranks (for profiling one shard)
+        my_ids_h, my_lens_h, assign = E.shard_batch(ids_h, lens_h, shard_of, 0)
+    else:
+        my_ids_h, my_lens_h, assign = E.shard_batch(ids_h, lens_h, world, rank)
     ids_pin, lens_pin = my_ids_h.pin_memory(), my_lens_h.pin_memory()
     have_work = len(assign) > 0
     ids_d = torch.empty_like(ids_pin, device=dev)
@@ -561,7 +572,8 @@ def _encoder_measure(torch, dist, workload, steps, warmup, rank, world, local, d
     dev_ms = timed(device_step, steps)
     clocks = sampler.stop() if rank == 0 else None
     if profile:
-        return {"profile_run": True, "ms_per_step": dev_ms / steps, "workload": workload} if rank == 0 else None
+        return {"profile_run": True, "ms_per_step": dev_ms / steps, "workload": workload, "sequences": len(assign),
+                "tokens": int(my_lens_h.sum()), "launches_per_forward": launches_per_fwd} if rank == 0 else None
     for _ in range(3):
         e2e_step()
     e2e_steps = max(3, min(steps, 20))
@@ -609,7 +621,8 @@ def run_encoder(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    line = _encoder_measure(torch, dist, args.workload, args.steps, args.warmup, rank, world, local, dev, args.profile)
+    line = _encoder_measure(torch, dist, args.workload, args.steps, args.warmup, rank, world, local, dev, args.profile,
+                            args.shard_of)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -276,9 +276,9 @@ def build_quant_encoder(cfg: EncoderConfig, seed: int = 1234, device="cuda", cal
 
 
 def shard_batch(ids: torch.Tensor, lens: torch.Tensor, world: int, rank: int):
-    """This rank's sequences (length-balanced, see sharding.balance_sequences), re-padded to its own longest."""
-    from .sharding import balance_sequences
-    assign = balance_sequences(lens.tolist(), world)[rank]
+    """This rank's sequences (balanced by packed work, see sharding.balance_packed), re-padded to its own longest."""
+    from .sharding import balance_packed
+    assign = balance_packed(lens.tolist(), world)[rank]
     if not assign:
         return ids[:0, :1], lens[:0], assign
     idx = torch.tensor(assign, device=ids.device)

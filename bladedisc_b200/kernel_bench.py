@@ -100,7 +100,7 @@ def bench_int_mm(M, K, N, iters):
         return None
 
 
-def bench_qgemm(M, K, N, out_dtype, hbm, tops_peak, iters, exact=False):
+def bench_qgemm(M, K, N, out_dtype, hbm, tops_peak, iters, exact=False, path=None):
     dev = "cuda"
     b_out = 1 if out_dtype == torch.int8 else 2
     algo_bytes = M * K + N * K + M * N * b_out + 8 * N
@@ -119,11 +119,11 @@ def bench_qgemm(M, K, N, out_dtype, hbm, tops_peak, iters, exact=False):
     torch.cuda.synchronize()  # the weights are final from here on, as inference weights are
     fns = [(lambda a=a, w=w, o=o: ops.qgemm(a, w, x_scale=sx, w_scale=sw, out_scale=so, bias=bias,
                                             out_dtype=out_dtype, out=o, weights_static=True,
-                                            exact_division=exact)) for a, w, o in sets]
+                                            exact_division=exact, path=path)) for a, w, o in sets]
     ms = time_ms(fns, iters)
     tops = 2.0 * M * N * K / (ms * 1e-3) / 1e12
     gbs = algo_bytes / (ms * 1e-3) / 1e9
-    path = ops.qgemm_path(M, N, K)
+    path = path or ops.qgemm_path(M, N, K)
     # the bound that applies: time cannot beat max(ops / tensor peak, bytes / hbm peak)
     t_tensor = 2.0 * M * N * K / (tops_peak * 1e12)
     t_hbm = algo_bytes / (hbm * 1e9)
@@ -268,6 +268,7 @@ def main():
     ap.add_argument("--shape", default=None, help="M,K,N: only this quantized-linear point (with --only qgemm)")
     ap.add_argument("--min-rows", type=int, default=0, help="quantized-linear points with at least this many rows")
     ap.add_argument("--max-rows", type=int, default=1 << 30, help="quantized-linear points with at most this many rows")
+    ap.add_argument("--path", default=None, help="force a quantized-linear path (tiled, pair, skinny, small_m, gemv)")
     ap.add_argument("--exact", action="store_true", help="also time int8 output with the exact-division epilogue")
     ap.add_argument("--int-mm", action="store_true", help="also time cuBLASLt int8 -> int32 (torch._int_mm) per point")
     args = ap.parse_args()
@@ -296,7 +297,7 @@ def main():
             for od, exact in ((torch.int8, False), (torch.int8, True), (torch.float16, False)):
                 if exact and not args.exact:
                     continue
-                r = bench_qgemm(M, K, N, od, hbm, tops_peak, iters, exact)
+                r = bench_qgemm(M, K, N, od, hbm, tops_peak, iters, exact, args.path)
                 if lib_us:
                     r["int_mm_us"] = lib_us
                 out["rows"].append(r)

@@ -158,3 +158,21 @@ def test_two_rank_column_parallel_on_cpu(golden):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert got == [(0, True, True, True), (1, True, True, True)]
+
+
+def test_balance_packed_properties():
+    """Every sequence exactly once, the same answer on every call, no rank idle while sequences remain, and the
+    heaviest rank within one longest sequence of the mean."""
+    import random
+    rnd = random.Random(7)
+    for world in (1, 2, 4, 8):
+        for n in (0, 1, 3, 8, 32, 64):
+            lens = [rnd.randint(16, 512) for _ in range(n)]
+            a = sharding.balance_packed(lens, world)
+            assert a == sharding.balance_packed(lens, world)
+            assert sorted(i for part in a for i in part) == list(range(n))
+            assert sum(1 for part in a if part) == min(world, n)
+            if n:
+                loads = [sum(sharding.packed_cost(lens[i]) for i in part) for part in a]
+                mean = sum(loads) / world
+                assert max(loads) <= mean + sharding.packed_cost(max(lens)) + 1e-9
