@@ -253,6 +253,21 @@ int32_t disc_b200_softmax(const void* x, void* y, int32_t type, int64_t rows, in
   return finish(st, "softmax", detail);
 }
 
+int32_t disc_b200_observe_histogram(const void* x, int32_t type, int64_t n, float lo, float hi, int32_t bins,
+                                    uint32_t* counts, void* stream) {
+  disc_b200::HistogramParams p;
+  p.x = x;
+  p.type = type;
+  p.n = n;
+  p.lo = lo;
+  p.hi = hi;
+  p.bins = bins;
+  p.counts = counts;
+  const char* detail = nullptr;
+  const cudaError_t st = disc_b200::histogram_observe_launch(p, static_cast<cudaStream_t>(stream), &detail);
+  return finish(st, "observe_histogram", detail);
+}
+
 int32_t disc_b200_attention(const disc_b200_attention_args* a, void* stream) {
   if (!a) {
     g_last_error = "attention: null args";
@@ -686,6 +701,15 @@ int32_t disc_b200_select_device_image(int64_t num_images, int32_t cc_major, int3
 }
 
 const char* disc_b200_last_error_string(void) { return g_last_error.c_str(); }
+
+int32_t disc_b200_selftest_wait_expiry(uint64_t limit_ns, int64_t* waited_ns, void* stream) {
+  const char* detail = nullptr;
+  long long waited = 0;
+  const cudaError_t st = disc_b200::wait_expiry_selftest(limit_ns, waited_ns ? &waited : nullptr,
+                                                         static_cast<cudaStream_t>(stream), &detail);
+  if (waited_ns) *waited_ns = waited;
+  return finish(st, "selftest_wait_expiry", detail);
+}
 
 int32_t disc_b200_kernel_status(void) { return disc_b200::kernel_status_fetch_and_clear(); }
 

@@ -193,4 +193,70 @@ cudaError_t minmax_qparams_launch(const QParamsParams& p, cudaStream_t s, const 
                           dim3(kThreads), 0, s, p);
 }
 
+// --------------------------------------------------------------------- histogram
+namespace {
+constexpr int kHistMaxBins = 4096;
+
+// One read of the tensor.  A private histogram sits in shared memory; a block adds its counts to the
+// global ones once, at the end.  A thread walks 16-byte vectors with a grid stride.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) histogram_kernel(HistogramParams p) {
+  extern __shared__ uint32_t hist_smem[];
+  uint32_t* h = hist_smem;   // [bins]
+  grid_dep_launch();
+  grid_dep_wait();
+  for (int i = threadIdx.x; i < p.bins; i += kThreads) h[i] = 0;
+  __syncthreads();
+  const float lo = p.lo, hi = p.hi;
+  const float span = hi - lo;
+  const float fbins = static_cast<float>(p.bins);
+
+  auto count = [&](float v) {
+    if (!(v >= lo && v <= hi)) return;   // outside the range, or NaN
+    // the order of operations of the CPU kernel: (x - lo) * bins, then / (hi - lo), truncated
+    int pos = static_cast<int>(__fdiv_rn(__fmul_rn(__fsub_rn(v, lo), fbins), span));
+    if (pos == p.bins) pos -= 1;         // the last bin is closed on the right
+    if (pos >= 0 && pos < p.bins) atomicAdd(&h[pos], 1u);
+  };
+
+  constexpr int V = 16 / static_cast<int>(sizeof(T));
+  const T* x = static_cast<const T*>(p.x);
+  const int64_t nvec = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) ? p.n / V : 0;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < nvec; i += stride) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x) + i);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int j = 0; j < V; ++j) count(static_cast<float>(e[j]));
+  }
+  for (int64_t i = nvec * V + static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < p.n; i += stride) {
+    count(static_cast<float>(x[i]));
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < p.bins; i += kThreads) {
+    if (h[i]) atomicAdd(&p.counts[i], h[i]);
+  }
+}
+}  // namespace
+
+cudaError_t histogram_observe_launch(const HistogramParams& p, cudaStream_t s, const char** err) {
+  static const char* none = "";
+  const char** e = err ? err : &none;
+  if (p.n <= 0) return cudaSuccess;
+  if (!p.x || !p.counts || p.bins < 1 || p.bins > kHistMaxBins || !(p.lo <= p.hi)) {
+    *e = "observer: histogram needs x, counts, lo <= hi and 1 .. 4096 bins";
+    return cudaErrorInvalidValue;
+  }
+  const size_t smem = static_cast<size_t>(p.bins) * 4;
+  int sms = 148;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t want = (p.n / 8 + kThreads - 1) / kThreads;
+  const unsigned blocks = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(want, 8LL * sms)));
+  if (p.type == kF32) return launch_dependent(histogram_kernel<float>, dim3(blocks), dim3(kThreads), smem, s, p);
+  if (p.type == kF16) return launch_dependent(histogram_kernel<__half>, dim3(blocks), dim3(kThreads), smem, s, p);
+  *e = "observer: element type must be f32 or f16";
+  return cudaErrorInvalidValue;
+}
+
 }  // namespace disc_b200

@@ -46,4 +46,17 @@ struct QParamsParams {
 };
 cudaError_t minmax_qparams_launch(const QParamsParams& p, cudaStream_t s, const char** err);
 
+// counts[b] += number of x in bin b of `bins` equal bins over [lo, hi], the binning torch.histc does
+// (HistogramObserver, observer.py:447-744, calls it once per batch): bin (int)((x - lo) * bins / (hi - lo)) in
+// float32, the last bin includes hi; values outside [lo, hi] and NaN are not counted.  bins <= 4096.
+struct HistogramParams {
+  const void* x;
+  int type;  // 0 = f32, 1 = f16
+  int64_t n;
+  float lo, hi;
+  int bins;
+  uint32_t* counts;     // [bins], accumulated into
+};
+cudaError_t histogram_observe_launch(const HistogramParams& p, cudaStream_t s, const char** err);
+
 }  // namespace disc_b200

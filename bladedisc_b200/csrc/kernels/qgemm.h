@@ -92,6 +92,11 @@ int64_t qgemm_small_m_noalloc_capacity();
 // Which path kPathAuto resolves to (exposed for tests and the bench).
 int qgemm_choose_path(const QGemmParams& p);
 
+// Self-test of the bounded waits: launches one warp that waits `limit_ns` (at most 100 ms) on a barrier nobody
+// arrives on, synchronises, and stores how long the wait lasted (-1 if it did not run out).  The status word
+// then holds the self-test's code (9) until kernel_status_fetch_and_clear() reads it.
+cudaError_t wait_expiry_selftest(uint64_t limit_ns, long long* waited_ns_host, cudaStream_t stream, const char** err);
+
 // Reads and clears the device status word the kernels set when a bounded wait
 // ran out (0 = ok).  Synchronises the device.
 int kernel_status_fetch_and_clear();

@@ -1471,6 +1471,47 @@ cudaError_t qgemm_small_m_noalloc_launch(const QGemmParams& in, cudaStream_t str
   }
 }
 
+// ------------------------------------------------------ wait-expiry self-test
+// One warp waits, with the kernels' own bounded wait, on a barrier that nobody
+// will ever arrive on: nothing is in flight (no copies, no TMEM), the wait runs
+// out after `limit_ns`, records its code in the status word and the kernel
+// returns.  It shows on a live GPU what a broken pipeline would do: give up and
+// report, never spin on.
+namespace {
+__global__ void wait_expiry_selftest_kernel(uint64_t limit_ns, long long* waited_ns) {
+  __shared__ __align__(8) uint64_t bar_storage;
+  __shared__ int abort_flag_storage;
+  const uint32_t bar = smem_u32(&bar_storage);
+  volatile int* abort_flag = &abort_flag_storage;
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const uint64_t t0 = global_timer_ns();
+  const bool ok = mbar_wait_limited(bar, 0, abort_flag, &g_kernel_status, kStatusTimeoutSelfTest, limit_ns);
+  if (threadIdx.x == 0) waited_ns[0] = ok ? -1 : static_cast<long long>(global_timer_ns() - t0);
+}
+}  // namespace
+
+cudaError_t wait_expiry_selftest(uint64_t limit_ns, long long* waited_ns_host, cudaStream_t stream, const char** err) {
+  if (err) *err = nullptr;
+  if (limit_ns == 0 || limit_ns > 100000000ull || !waited_ns_host) {   // at most 100 ms: this is a test, not a sleep
+    if (err) *err = "wait self-test: limit must be 1 ns .. 100 ms and the result pointer set";
+    return cudaErrorInvalidValue;
+  }
+  long long* d = nullptr;
+  cudaError_t st = cudaMalloc(&d, sizeof(long long));
+  if (st != cudaSuccess) return st;
+  wait_expiry_selftest_kernel<<<1, 32, 0, stream>>>(limit_ns, d);
+  st = cudaGetLastError();
+  if (st == cudaSuccess) st = cudaStreamSynchronize(stream);
+  if (st == cudaSuccess) st = cudaMemcpy(waited_ns_host, d, sizeof(long long), cudaMemcpyDeviceToHost);
+  cudaFree(d);
+  return st;
+}
+
 int kernel_status_fetch_and_clear() {
   int h = 0;
   if (cudaDeviceSynchronize() != cudaSuccess) return -1;

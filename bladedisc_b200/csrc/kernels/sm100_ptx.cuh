@@ -19,6 +19,7 @@ enum KernelStatus : int {
   kStatusTimeoutTmemEmpty = 3,  // MMA issuer waited for the epilogue
   kStatusTimeoutTmemFull = 4,   // epilogue waited for the accumulator
   kStatusTimeoutSplitK = 5,     // split-K hand-off between epilogue warps
+  kStatusTimeoutSelfTest = 9,   // the self-test's wait on a barrier nobody arrives on
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -67,9 +68,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Bounded wait.  `abort_flag` lives in shared memory: once any role of the CTA
-// has given up, the others stop waiting too.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+// has given up, the others stop waiting too.  `limit_ns` is the patience in
+// nanoseconds of %globaltimer.
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  int* status, int code, uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
@@ -77,13 +79,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0xFF) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;
       }
     }
   }
+}
+// The form the kernels use: the default patience.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+  return mbar_wait_limited(bar, parity, abort_flag, status, code, kWaitLimitNs);
 }
 
 // ---------------------------------------------------------------------- TMA

@@ -159,11 +159,14 @@ SIGNATURES = {
     "disc_b200_observe_minmax_scratch_floats": (c_int64, [c_int64, c_int64, c_int64]),
     "disc_b200_observe_minmax": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                            c_int64, c_void_p]),
+    "disc_b200_observe_histogram": (c_int32, [c_void_p, c_int32, c_int64, c_float, c_float, c_int32, c_void_p,
+                                              c_void_p]),
     "disc_b200_minmax_qparams": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p,
                                            c_void_p, c_void_p]),
     "disc_b200_select_device_image": (c_int32, [c_int64, c_int32, c_int32]),
     "disc_b200_last_error_string": (c_char_p, []),
     "disc_b200_kernel_status": (c_int32, []),
+    "disc_b200_selftest_wait_expiry": (c_int32, [ctypes.c_uint64, POINTER(c_int64), c_void_p]),
     "disc_b200_version": (c_char_p, []),
     "disc_b200_attrs_describe": (c_int32, [c_void_p, c_char_p, c_int32]),
     "disc_b200_attrs_describe_bounded": (c_int32, [c_void_p, c_int64, c_char_p, c_int32]),

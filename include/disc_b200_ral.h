@@ -403,6 +403,13 @@ int32_t disc_b200_minmax_qparams(const float* min_val, const float* max_val, int
                                  int32_t symmetric, int32_t symmetric_zero_point, float* scale, int32_t* zero_point,
                                  void* stream);
 
+/* counts[b] += number of x in bin b of `bins` equal bins over [lo, hi], the binning of torch.histc, which the
+ * reference's HistogramObserver runs once per calibration batch
+ * (tools/torch_quant/torch_quant/observer.py:674-724): bin (int)((x - lo) * bins / (hi - lo)) in float32, the
+ * last bin includes hi, values outside [lo, hi] and NaN are skipped.  counts (uint32, device) is accumulated into. */
+int32_t disc_b200_observe_histogram(const void* x, int32_t type, int64_t n, float lo, float hi, int32_t bins,
+                                    uint32_t* counts, void* stream);
+
 /* softmax(x * scale + mask) over the last axis; lens / mask may be NULL
  * (kStitch softmax; same reference files as above). */
 int32_t disc_b200_softmax(const void* x, void* y, int32_t type, int64_t rows, int64_t cols,
@@ -512,6 +519,12 @@ const char* disc_b200_last_error_string(void);
 /* Synchronises the device, returns and clears the status word kernels set when
  * one of their bounded waits ran out (0 = none did). */
 int32_t disc_b200_kernel_status(void);
+/* Self-test of that mechanism on a live GPU: one warp waits, with the kernels' own bounded wait, on a
+ * barrier that nobody arrives on.  Nothing is in flight and nothing faults: after limit_ns (1 ns .. 100 ms) the
+ * wait gives up, the kernel returns and the status word holds code 9 until disc_b200_kernel_status() reads it.
+ * *waited_ns (host) receives the time the wait lasted.  Synchronises the stream.  No counterpart in the
+ * reference, whose runtime has no device-side waits of its own. */
+int32_t disc_b200_selftest_wait_expiry(uint64_t limit_ns, int64_t* waited_ns, void* stream);
 const char* disc_b200_version(void);
 /* Parses a serialized custom_attrs blob (wire format of tao_compiler/mlir/ral/
  * context/pdll_util.cc:20-170) and writes a canonical text rendering such as

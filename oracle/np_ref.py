@@ -137,3 +137,16 @@ def attention_packed(qkv, lens, heads, scale):
             out[t0:t0 + n, h * d:(h + 1) * d] = (p @ v).astype(f32)
         t0 += n
     return out
+
+
+def histc(x, lo, hi, bins):
+    """Counts per bin as torch.histc computes them on the CPU (aten/src/ATen/native/cpu/HistogramKernel.cpp,
+    linear interpolation), which the reference's HistogramObserver calls once per batch
+    (tools/torch_quant/torch_quant/observer.py:693,712): bin (int)((x - lo) * bins / (hi - lo)) in float32,
+    the last bin includes hi; values outside [lo, hi] and NaN are skipped."""
+    x = np.asarray(x, dtype=f32).reshape(-1)
+    lo, hi = f32(lo), f32(hi)
+    x = x[(x >= lo) & (x <= hi)]
+    pos = (((x - lo).astype(f32) * f32(bins)).astype(f32) / f32(hi - lo)).astype(f32).astype(np.int64)
+    pos[pos == bins] = bins - 1
+    return np.bincount(pos, minlength=bins).astype(np.int64)[:bins]

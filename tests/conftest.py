@@ -9,6 +9,8 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 GOLDEN = ROOT / "tests" / "golden" / "qpath_golden.npz"
+# where the reference project is checked out (only the tests that build or import it need it)
+REFERENCE_ROOT = Path(os.environ.get("DISC_REFERENCE_ROOT", "/root/reference"))
 
 
 def pytest_configure(config):
@@ -34,7 +36,7 @@ def ref_ral():
     import ctypes
     import subprocess
     so = ROOT / "oracle" / "_ref" / "libref_ral.so"
-    if not so.exists() and Path("/root/reference/tao_compiler/mlir/ral/ral_api.cc").exists():
+    if not so.exists() and (REFERENCE_ROOT / "tao_compiler/mlir/ral/ral_api.cc").exists():
         subprocess.run(["make", "-C", str(ROOT / "oracle"), "ref"], check=False,
                        stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
     if not so.exists():
@@ -53,7 +55,7 @@ def ref_host():
     import ctypes
     import subprocess
     so = ROOT / "oracle" / "_ref" / "libref_host.so"
-    if not so.exists() and Path("/root/reference/tao_compiler/mlir/ral/ral_api.cc").exists():
+    if not so.exists() and (REFERENCE_ROOT / "tao_compiler/mlir/ral/ral_api.cc").exists():
         subprocess.run(["make", "-C", str(ROOT / "oracle"), "ref"], check=False,
                        stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
     if not so.exists():

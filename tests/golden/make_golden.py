@@ -21,6 +21,7 @@ that the tests need neither the reference tree nor torch's RNG to agree):
 * onednn_*: torch.ops.onednn.qlinear_pointwise (oneDNN, the library the
   reference's x86 custom call uses) on a small int8 case.
 """
+import os
 import sys
 import types
 from pathlib import Path
@@ -30,7 +31,7 @@ import torch
 import torch.nn.functional as F
 
 OUT = Path(__file__).resolve().parent / "qpath_golden.npz"
-REF_TQ = Path("/root/reference/tools/torch_quant")
+REF_TQ = Path(os.environ.get("DISC_REFERENCE_ROOT", "/root/reference")) / "tools" / "torch_quant"
 
 
 def fq(x, s, zp=0):

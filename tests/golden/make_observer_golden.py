@@ -8,8 +8,11 @@ front end and CPU torch):
 Stored: seeded calibration batches together with the running min / max, scale and
 zero point that the reference's MinMaxObserver / PerChannelMinMaxObserver
 (tools/torch_quant/torch_quant/observer.py:230-297) hold after observing them, for
-the symmetric signed, affine unsigned and per-channel schemes.
+the symmetric signed, affine unsigned and per-channel schemes; and for its
+HistogramObserver (observer.py:447-744) the histogram and range after every batch
+and the clipping range, scale and zero point its search arrives at.
 """
+import os
 import sys
 import types
 from pathlib import Path
@@ -18,14 +21,14 @@ import numpy as np
 import torch
 
 OUT = Path(__file__).resolve().parent / "observer_golden.npz"
-REF_TQ = Path("/root/reference/tools/torch_quant")
+REF_TQ = Path(os.environ.get("DISC_REFERENCE_ROOT", "/root/reference")) / "tools" / "torch_quant"
 
 
 def main():
     sys.path.insert(0, str(REF_TQ))
     for name in ("torch_quant.mnn", "torch_quant.mnn.export", "torch_quant.mnn.MNN_compression_pb2"):
         sys.modules.setdefault(name, types.ModuleType(name))  # needs `onnx`, absent here
-    from torch_quant.observer import MinMaxObserver, PerChannelMinMaxObserver
+    from torch_quant.observer import HistogramObserver, MinMaxObserver, PerChannelMinMaxObserver
 
     g = torch.Generator().manual_seed(77)
     out = {}
@@ -66,6 +69,31 @@ def main():
         out[f"{tag}_max"] = ob.max_val.numpy()
         out[f"{tag}_scale"] = ob.scale.numpy()
         out[f"{tag}_zp"] = ob.zero_point.numpy().astype(np.int32)
+    # histogram observer (observer.py:447-744): state after every batch and the searched range at the end.
+    # Case a: each batch widens the range (the old histogram is re-gridded); case b: the second and third
+    # batch stay inside the first one's range; case c: a long-tailed distribution, where the search clips.
+    hist_cases = {
+        "a": [torch.randn(4, 300, generator=g) * (1 + 0.5 * i) + 0.3 * i for i in range(3)],
+        "b": [torch.randn(2000, generator=g) * 2, torch.randn(2000, generator=g) * 0.5, torch.rand(777, generator=g)],
+        "c": [torch.randn(5000, generator=g) ** 3, torch.randn(5000, generator=g) ** 3 * 0.9],
+    }
+    for tag, batches in hist_cases.items():
+        for kind, kwargs in (("affine", dict(dtype=torch.quint8, qscheme=torch.per_tensor_affine)),
+                             ("sym", dict(dtype=torch.qint8, qscheme=torch.per_tensor_symmetric))):
+            ob = HistogramObserver(**kwargs)
+            ob.set_mode(observe=True, fake_quant=False)
+            for i, b in enumerate(batches):
+                ob(b)
+                if kind == "affine":
+                    out[f"hist_{tag}_batch{i}"] = b.numpy()
+                    out[f"hist_{tag}_after{i}_hist"] = ob.histogram.numpy().copy()
+                    out[f"hist_{tag}_after{i}_minmax"] = np.array([float(ob.min_val), float(ob.max_val)], np.float32)
+            new_min, new_max = ob._non_linear_param_search()
+            ob._calculate()
+            out[f"hist_{tag}_{kind}_range"] = np.array([float(new_min), float(new_max)], np.float32)
+            out[f"hist_{tag}_{kind}_scale"] = ob.scale.reshape(1).numpy().copy()
+            out[f"hist_{tag}_{kind}_zp"] = ob.zero_point.reshape(1).numpy().astype(np.int32)
+        out[f"hist_{tag}_batches"] = np.array([len(batches)], np.int32)
     np.savez_compressed(OUT, **out)
     print("wrote", OUT, OUT.stat().st_size, "bytes;", len(out), "arrays")
 

@@ -88,3 +88,46 @@ def test_edges():
         pc(torch.ones(5, 4, device="cuda"))
     with pytest.raises(TypeError):
         ob(torch.zeros(4, dtype=torch.int32, device="cuda"))
+
+
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
+def test_histogram_observer_equals_the_reference_observer(tag):
+    """State after every batch (2048-bin histogram, range) and the searched clipping range, scale and zero
+    point equal what the reference's own HistogramObserver held for the same batches
+    (tests/golden/observer_golden.npz, written by tests/golden/make_observer_golden.py)."""
+    from pathlib import Path
+    from bladedisc_b200.observer import HistogramObserver
+    gold = np.load(Path(__file__).parent / "golden" / "observer_golden.npz")
+    for kind, kwargs in (("affine", dict(dtype="quint8", symmetric=False)), ("sym", dict(dtype="qint8", symmetric=True))):
+        ob = HistogramObserver(**kwargs)
+        for i in range(int(gold[f"hist_{tag}_batches"][0])):
+            ob(torch.from_numpy(gold[f"hist_{tag}_batch{i}"]).cuda())
+            assert (np.array([ob.min_val, ob.max_val], np.float32) == gold[f"hist_{tag}_after{i}_minmax"]).all()
+            assert (ob.histogram == gold[f"hist_{tag}_after{i}_hist"]).all(), f"histogram after batch {i}"
+        lo, hi = ob.clipping_range()
+        assert (np.array([lo, hi], np.float32) == gold[f"hist_{tag}_{kind}_range"]).all()
+        scale, zp = ob.qparams()
+        assert (scale.cpu().numpy() == gold[f"hist_{tag}_{kind}_scale"]).all()
+        assert (zp.cpu().numpy() == gold[f"hist_{tag}_{kind}_zp"]).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("n", [1, 1000, 4 * 1024 * 1024 + 3])
+def test_histogram_kernel_counts(dtype, n):
+    """The counting kernel against the numpy statement of torch.histc on large, unaligned and f16 tensors, with
+    values on the range ends, outside it and NaN."""
+    import ctypes
+    from bladedisc_b200 import lib as L
+    from bladedisc_b200 import ops
+    from oracle import np_ref
+    g = torch.Generator(device="cuda").manual_seed(n)
+    x = (torch.randn(n + 1, generator=g, device="cuda") * 2).to(dtype)[1:]   # not 16-byte aligned
+    if n > 8:
+        x[:4] = torch.tensor([-3.0, 3.5, float("nan"), 100.0], dtype=dtype)
+    lo, hi = np.float32(-3.0), np.float32(3.5)
+    counts = torch.zeros(2048, dtype=torch.int32, device="cuda")
+    for _ in range(2):   # accumulates
+        L.check(L.load().disc_b200_observe_histogram(x.data_ptr(), ops._etype(x), n, float(lo), float(hi), 2048,
+                                                     counts.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    want = np_ref.histc(x.float().cpu().numpy(), lo, hi, 2048)
+    assert (counts.cpu().numpy().astype(np.int64) == 2 * want).all()
