@@ -52,8 +52,8 @@ struct AttnSmem {
   static constexpr int kV = kK + kMaxKeyBlocks * kTileBytes;       // 4 key blocks
   static constexpr int kP = kV + kMaxKeyBlocks * kTileBytes;       // 2 buffers x 2 sub-tiles of 64 keys
   static constexpr int kBars = kP + 4 * kTileBytes;
-  // q_full, k_full[4], v_full[4], s_full[4], p_full[4], pv_done[4], o_full
-  static constexpr int kNumBars = 1 + 5 * kMaxKeyBlocks + 1;
+  // q_full, k_full[4], v_full[4], s_full[4], p_full[4], pv_done[4], o_full, q_free, o_read
+  static constexpr int kNumBars = 1 + 5 * kMaxKeyBlocks + 3;
   static constexpr int kMisc = kBars + kNumBars * 8;               // tmem slot, abort flag
   static constexpr int kRed = ((kMisc + 16) + 15) & ~15;           // max[2][128], sum[2][128]
   static constexpr int kTotal = kRed + 4 * kRows * 4;
@@ -117,6 +117,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttnBlock* 
   auto p_full = [&](int j) { return bar_base + 8u * (1 + 3 * kMaxKeyBlocks + j); };
   auto pv_done = [&](int j) { return bar_base + 8u * (1 + 4 * kMaxKeyBlocks + j); };
   const uint32_t o_full = bar_base + 8u * (1 + 5 * kMaxKeyBlocks);
+  const uint32_t q_free = o_full + 8u;   // the score products of a query block are done: its Q tile may be replaced
+  const uint32_t o_read = o_full + 16u;  // the epilogue has read O: the next query block's scores may overwrite it
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMisc + 4);
   float* red_max = reinterpret_cast<float*>(smem + L::kRed);   // [2][128]
@@ -131,6 +133,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttnBlock* 
     tma_prefetch_desc(&tmap_qkv);
     for (int i = 0; i < L::kNumBars; ++i) mbar_init(bar_base + 8u * i, 1);
     for (int j = 0; j < kMaxKeyBlocks; ++j) mbar_init(p_full(j), kSoftmaxWarps);
+    mbar_init(o_read, kSoftmaxWarps);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -145,9 +148,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttnBlock* 
   grid_dep_launch();
   grid_dep_wait();  // qkv comes from the kernel before this one
 
+  // A work item is `nq` consecutive blocks of 128 query rows of one sequence: K and V are fetched once and
+  // stay in shared memory, the barriers that cycle per query block are waited on with the block's parity.
   const AttnBlock blk = blocks[blockIdx.x];
   const int len = blk.len;
   const int nkb = (len + kKeyBlock - 1) / kKeyBlock;   // 1 .. 4
+  const int nq = blk.nq < 1 ? 1 : blk.nq;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -164,41 +170,53 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttnBlock* 
         tma_load_2d(smem_base + L::kV + j * kTileBytes, &tmap_qkv, v_full(j), 2 * hidden + head * kAttnHeadDim,
                     blk.tok0 + j * kKeyBlock);
       }
+      // the Q tiles of the following query blocks, each once the products that read the previous one are done
+      for (int it = 1; it < nq; ++it) {
+        if (!mbar_wait(q_free, (it - 1) & 1, abort_flag, &g_attn_status, 18)) break;
+        mbar_arrive_expect_tx(q_full, kTileBytes);
+        tma_load_2d(smem_base + L::kQ, &tmap_qkv, q_full, head * kAttnHeadDim, blk.tok0 + blk.q0 + it * kRows);
+      }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_f16_idesc(kRows, kKeyBlock, false);
       constexpr uint32_t idesc_o = make_f16_idesc(kRows, kAttnHeadDim, true);
-      bool ok = mbar_wait(q_full, 0, abort_flag, &g_attn_status, 11);
-      for (int j = 0; j < nkb && ok; ++j) {
-        ok = mbar_wait(k_full(j), 0, abort_flag, &g_attn_status, 12);
-        if (!ok) break;
-        tc_fence_after();
-        const uint64_t a_desc = make_kmajor_sw128_desc(smem_base + L::kQ);
-        const uint64_t b_desc = make_kmajor_sw128_desc(smem_base + L::kK + j * kTileBytes);
+      bool ok = true;
+      for (int it = 0; it < nq && ok; ++it) {
+        const uint32_t ph = it & 1;
+        ok = mbar_wait(q_full, ph, abort_flag, &g_attn_status, 11);
+        if (ok && it > 0) ok = mbar_wait(o_read, ph ^ 1, abort_flag, &g_attn_status, 19);   // O of the block before
+        for (int j = 0; j < nkb && ok; ++j) {
+          if (it == 0) ok = mbar_wait(k_full(j), 0, abort_flag, &g_attn_status, 12);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t a_desc = make_kmajor_sw128_desc(smem_base + L::kQ);
+          const uint64_t b_desc = make_kmajor_sw128_desc(smem_base + L::kK + j * kTileBytes);
 #pragma unroll
-        for (int k = 0; k < kAttnHeadDim / 16; ++k) {   // 16 f16 = 32 bytes per MMA along the head dimension
-          umma_f16(tmem_base + j * kKeyBlock, a_desc + 2 * k, b_desc + 2 * k, idesc_s, k != 0 ? 1u : 0u);
+          for (int k = 0; k < kAttnHeadDim / 16; ++k) {   // 16 f16 = 32 bytes per MMA along the head dimension
+            umma_f16(tmem_base + j * kKeyBlock, a_desc + 2 * k, b_desc + 2 * k, idesc_s, k != 0 ? 1u : 0u);
+          }
+          umma_commit(s_full(j));
         }
-        umma_commit(s_full(j));
-      }
-      for (int j = 0; j < nkb && ok; ++j) {
-        ok = mbar_wait(p_full(j), 0, abort_flag, &g_attn_status, 13);
-        if (!ok) break;
-        ok = mbar_wait(v_full(j), 0, abort_flag, &g_attn_status, 14);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t p_addr = smem_base + L::kP + (j & 1) * 2 * kTileBytes;
-        const uint32_t v_addr = smem_base + L::kV + j * kTileBytes;
+        if (ok) umma_commit(q_free);
+        for (int j = 0; j < nkb && ok; ++j) {
+          ok = mbar_wait(p_full(j), ph, abort_flag, &g_attn_status, 13);
+          if (!ok) break;
+          if (it == 0) ok = mbar_wait(v_full(j), 0, abort_flag, &g_attn_status, 14);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t p_addr = smem_base + L::kP + (j & 1) * 2 * kTileBytes;
+          const uint32_t v_addr = smem_base + L::kV + j * kTileBytes;
 #pragma unroll
-        for (int kk = 0; kk < kKeyBlock / 16; ++kk) {   // 16 keys per MMA
-          const uint64_t a_desc = make_kmajor_sw128_desc(p_addr + (kk >> 2) * kTileBytes) + 2 * (kk & 3);
-          const uint64_t b_desc = make_mnmajor_sw128_desc(v_addr + kk * 16 * 128);
-          umma_f16(tmem_base, a_desc, b_desc, idesc_o, (j | kk) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < kKeyBlock / 16; ++kk) {   // 16 keys per MMA
+            const uint64_t a_desc = make_kmajor_sw128_desc(p_addr + (kk >> 2) * kTileBytes) + 2 * (kk & 3);
+            const uint64_t b_desc = make_mnmajor_sw128_desc(v_addr + kk * 16 * 128);
+            umma_f16(tmem_base, a_desc, b_desc, idesc_o, (j | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(pv_done(j));
         }
-        umma_commit(pv_done(j));
+        if (ok) umma_commit(o_full);
       }
-      if (ok) umma_commit(o_full);
     }
   } else {
     // softmax + epilogue: TMEM lane quadrant = warp % 4 (a hardware rule), `half` = which 64 keys of every
@@ -208,11 +226,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttnBlock* 
     const int row = q * 32 + lane;
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     bool ok = true;
+    for (int it = 0; it < nq; ++it) {
+    const uint32_t ph = it & 1;
+    const int q_row0 = blk.q0 + it * kRows;
 
     // pass A: row maximum of the scaled scores over the valid keys
     float mx = -INFINITY;
     for (int j = 0; j < nkb && ok; ++j) {
-      ok = mbar_wait(s_full(j), 0, abort_flag, &g_attn_status, 15);
+      ok = mbar_wait(s_full(j), ph, abort_flag, &g_attn_status, 15);
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
@@ -236,7 +257,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttnBlock* 
     float sum = 0.f;
     for (int j = 0; j < nkb && ok; ++j) {
       if (j >= 2) {
-        ok = mbar_wait(pv_done(j - 2), 0, abort_flag, &g_attn_status, 16);   // the P buffer is free again
+        ok = mbar_wait(pv_done(j - 2), ph, abort_flag, &g_attn_status, 16);   // the P buffer is free again
         if (!ok) break;
       }
       uint8_t* p_tile = smem + L::kP + ((j & 1) * 2 + half) * kTileBytes + row * 128;
@@ -275,14 +296,18 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttnBlock* 
     const float inv = 1.f / (red_sum[row] + red_sum[kRows + row]);
 
     // epilogue: this thread's 32 columns of its row
-    if (ok) ok = mbar_wait(o_full, 0, abort_flag, &g_attn_status, 17);
+    if (ok) ok = mbar_wait(o_full, ph, abort_flag, &g_attn_status, 17);
     if (ok) {
       tc_fence_after();
       uint32_t r[32];
       tmem_ld_x32(t_row + half * 32, r);
       tmem_ld_wait();
-      if (blk.q0 + row < len) {
-        OutT* dst = out + static_cast<int64_t>(blk.tok0 + blk.q0 + row) * ld_out + head * kAttnHeadDim + half * 32;
+      // O is in registers: the next query block's score products may overwrite its columns
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_read);
+      if (q_row0 + row < len) {
+        OutT* dst = out + static_cast<int64_t>(blk.tok0 + q_row0 + row) * ld_out + head * kAttnHeadDim + half * 32;
         if constexpr (sizeof(OutT) == 1) {
           const float k = inv * __frcp_rn(__ldg(out_scale));
           uint32_t w[8];
@@ -315,6 +340,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttnBlock* 
         }
       }
     }
+    }   // query blocks
   }
 
   __syncwarp();

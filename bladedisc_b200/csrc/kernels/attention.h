@@ -11,12 +11,13 @@ constexpr int kAttnHeadDim = 64;
 constexpr int kAttnMaxKeys = 512;
 constexpr int kAttnRowsPerBlock = 128;
 
-// One entry per block of 128 query rows of one sequence.
+// One entry per work item: `nq` consecutive blocks of 128 query rows of one sequence (one thread block per
+// item and head; the keys and values of the sequence are fetched once per item).
 struct AttnBlock {
   int32_t tok0;  // first token (row of qkv) of the sequence
   int32_t len;   // tokens of the sequence (1 .. 512)
-  int32_t q0;    // first query row of this block inside the sequence (multiple of 128)
-  int32_t pad;
+  int32_t q0;    // first query row of the item inside the sequence (multiple of 128)
+  int32_t nq;    // query blocks of the item (0 is read as 1); q0 + 128 * nq covers at most the sequence
 };
 
 struct AttentionParams {

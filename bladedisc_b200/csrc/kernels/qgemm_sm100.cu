@@ -96,8 +96,33 @@ __device__ __forceinline__ float col_bias(const EpiParams& e, int64_t n) {
   return 0.f;
 }
 
+// erf(x) to 3e-7 absolute (Abramowitz & Stegun 7.1.28): 1 - (1 + a1 t + ... + a6 t^6)^-16 for t = |x|, six
+// fused multiply-adds, four squarings and one reciprocal.  libdevice's erff is exact to an ulp at about twice
+// the instructions, which the epilogue of a short-K tile cannot hide; 3e-7 is far inside every tolerance the
+// outputs are held to (the int8 step of a GELU output is four orders of magnitude larger).
+__device__ __forceinline__ float erf_fast(float x) {
+  const float t = fabsf(x);
+  float p = 0.0000430638f;
+  p = __fmaf_rn(p, t, 0.0002765672f);
+  p = __fmaf_rn(p, t, 0.0001520143f);
+  p = __fmaf_rn(p, t, 0.0092705272f);
+  p = __fmaf_rn(p, t, 0.0422820123f);
+  p = __fmaf_rn(p, t, 0.0705230784f);
+  p = __fmaf_rn(p, t, 1.f);
+  p *= p;
+  p *= p;
+  p *= p;
+  p *= p;   // overflows to +inf for |x| > ~13, where erf is 1 to every bit
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(p));
+  return copysignf(1.f - r, x);
+}
+__device__ __forceinline__ float gelu_erf(float v) {
+  return 0.5f * v * (1.f + erf_fast(v * 0.70710678118654752440f));
+}
+
 __device__ __forceinline__ float act_apply(float v, int act) {
-  if (act == kActGelu) return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
+  if (act == kActGelu) return gelu_erf(v);
   if (act == kActSilu) return v / (1.f + __expf(-v));
   return v;
 }
@@ -255,7 +280,7 @@ __device__ __forceinline__ float epi_value_t(int32_t acc, float cs, float cb, co
   float t = CVT_BY_ADDS ? int2float_by_adds(acc) : __int2float_rn(acc);
   if (RS) t = __fmul_rn(t, c.rs);
   float v = __fmaf_rn(t, cs, cb);
-  if (ACT == kActGelu) v = 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
+  if (ACT == kActGelu) v = gelu_erf(v);
   if (ACT == kActSilu) v = v / (1.f + __expf(-v));
   if (DIV == kDivExact) v = div_out_scale(v, c);
   if (DIV == kDivRecip && ACT != kActNone) v = __fmaf_rn(v, c.k1, c.k0);  // folded into cs / cb otherwise

@@ -208,7 +208,7 @@ class QuantEncoder:
         starts = torch.tensor([0] + lens_h[:-1], dtype=torch.int64).cumsum(0)
         self._plan = {
             "key": (B, L, tuple(lens_h)), "flat": flat.to(dev), "pos": pos.to(dev), "first": starts.to(dev),
-            "blocks": ops.attention_blocks(lens_h).to(dev), "tokens": int(sum(lens_h)), "lens": lens_h,
+            "blocks": ops.attention_blocks(lens_h, self.cfg.heads).to(dev), "tokens": int(sum(lens_h)), "lens": lens_h,
         }
         self.rows_processed = self._plan["tokens"]
 

@@ -484,18 +484,26 @@ def softmax(x: torch.Tensor, scale: float = 1.0, lens: Optional[torch.Tensor] = 
     return y
 
 
-def attention_blocks(lens) -> torch.Tensor:
-    """Work list of `attention`: one row {first token of the sequence, length, first query row of the block, 0}
-    per 128 query rows of each sequence, for sequences packed one after the other (host tensor, int32 [n, 4]).
-    Longer sequences come first so that the last wave of thread blocks holds the short ones."""
-    rows = []
-    tok0 = 0
-    for n in (int(v) for v in lens):
+def attention_blocks(lens, heads: int = 12, group: int = 1) -> torch.Tensor:
+    """Work list of `attention` for sequences packed one after the other (host tensor, int32 [n, 4]): one row
+    {first token of the sequence, length, first query row of the item, query blocks of the item} per item.
+    An item is `group` (or, at the end of a sequence, fewer) consecutive blocks of 128 query rows of a
+    sequence; its thread block fetches the sequence's keys and values once.  One block per item (the default)
+    measured fastest on batches of a few thousand tokens: the items are many and even, while whole-sequence
+    items leave the last wave to the longest sequences.  Longer sequences come first."""
+    lens = [int(v) for v in lens]
+    for n in lens:
         if n < 1 or n > 512:
             raise ValueError(f"sequence length {n} outside 1..512")
-        rows += [(tok0, n, q0, 0) for q0 in range(0, n, 128)]
+    group = max(1, min(4, int(group)))
+    rows = []
+    tok0 = 0
+    for n in lens:
+        nblk = (n + 127) // 128
+        for b0 in range(0, nblk, group):
+            rows.append((tok0, n, b0 * 128, min(group, nblk - b0)))
         tok0 += n
-    rows.sort(key=lambda r: -r[1])
+    rows.sort(key=lambda r: -(r[1] * r[3]))
     return torch.tensor(rows, dtype=torch.int32).reshape(-1, 4)
 
 

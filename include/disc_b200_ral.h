@@ -424,9 +424,10 @@ int32_t disc_b200_softmax(const void* x, void* y, int32_t type, int64_t rows, in
  * generated softmax between them and the quantize after them.
  * qkv: f16 [tokens, 3 * heads * 64] (q | k | v, head h in columns h * 64 .. of
  * each third), sequences stored one after the other without padding rows.
- * blocks: device array with one entry per block of 128 query rows of one
- * sequence ({first token of the sequence, its length 1..512, first row of the
- * block inside the sequence, 0}); a sequence of length n has ceil(n / 128).
+ * blocks: device array with one entry per work item = one or more consecutive
+ * blocks of 128 query rows of one sequence ({first token of the sequence, its
+ * length 1..512, first query row of the item inside the sequence, number of
+ * 128-row blocks of the item}); the items of a sequence cover its rows once.
  * out: [tokens, heads * 64], int8 quantized at *out_scale (reciprocal form,
  * at most one level from the divide-based quantize) or f16 when out_scale is NULL. */
 typedef struct disc_b200_attention_args {

@@ -38,8 +38,8 @@ def test_attention_matches_the_formula(ops, lens, heads):
     scale = 1.0 / math.sqrt(64)
     want = np_ref.attention_packed(qkv.astype(np.float32), lens, heads, scale)
     qkv_d = torch.from_numpy(qkv).cuda()
-    blocks = ops.attention_blocks(lens).cuda()
-    assert blocks.shape[0] == sum((n + 127) // 128 for n in lens)
+    blocks = ops.attention_blocks(lens, heads).cuda()
+    assert int(blocks[:, 3].sum()) == sum((n + 127) // 128 for n in lens)
     got = ops.attention(qkv_d, blocks, heads, scale).float().cpu().numpy()
     assert got.shape == want.shape
     assert np.isfinite(got).all()
@@ -50,6 +50,22 @@ def test_attention_matches_the_formula(ops, lens, heads):
     q_want = np.clip(np.rint(want / s_out), -128, 127).astype(np.int32)
     d = np.abs(q.astype(np.int32) - q_want)
     assert d.max() <= 1 and (d > 0).mean() < 0.05, f"int8: max {d.max()}, share off by one {(d > 0).mean():.3f}"
+
+
+@pytest.mark.parametrize("group", [4, 2, 1])
+def test_attention_is_the_same_however_the_query_blocks_are_grouped(ops, group):
+    """One item per 128 query rows, per pair of blocks or per sequence: the same bytes."""
+    heads, scale = 3, 0.125
+    lens = [512, 300, 129, 128, 40, 385]
+    qkv, tokens = _case(lens, heads, 9)
+    qkv_d = torch.from_numpy(qkv).cuda()
+    base = ops.attention(qkv_d, ops.attention_blocks(lens, heads).cuda(), heads, scale)
+    blocks = ops.attention_blocks(lens, heads, group=group)
+    assert int(blocks[:, 3].max()) == group
+    so = torch.tensor([0.02], device="cuda")
+    assert torch.equal(ops.attention(qkv_d, blocks.cuda(), heads, scale), base)
+    assert torch.equal(ops.attention(qkv_d, blocks.cuda(), heads, scale, out_scale=so),
+                       ops.attention(qkv_d, ops.attention_blocks(lens, heads).cuda(), heads, scale, out_scale=so))
 
 
 def test_attention_ignores_neighbouring_sequences_and_padding_rows(ops):
