@@ -276,6 +276,31 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def _build_boundary_executable(torch, w_h, w_scale_h, bias_h, device):
+    """Compiles the stand-in program (bladedisc_b200/standin/qlinear_program.c) with the host compiler, writes
+    its constants into a metadata file and opens both the way torch_blade opens an engine."""
+    import tempfile
+    import numpy as np
+    from bladedisc_b200 import metadata as M
+    from bladedisc_b200.executable import Executable
+    from bladedisc_b200.ral import pack_attrs
+    tmp = Path(tempfile.mkdtemp(prefix="disc_b200_bench_"))
+    blob = pack_attrs({"activation": "none"})
+    (tmp / "attrs_blob.h").write_text("static const unsigned char attrs_blob[] = {" + ",".join(str(b) for b in blob) + "};\n")
+    n, k = w_h.shape
+    names = {"CONST_W": f"0_i8_{n}x{k}", "CONST_B": f"1_f32_{n}", "CONST_SW": f"3_f32_{n}"}
+    so = tmp / "qlinear_program.so"
+    cmd = ["gcc", "-shared", "-fPIC", "-O1", "-Wno-main", f"-DATTRS_BLOB_H=\"{tmp / 'attrs_blob.h'}\""]
+    cmd += [f"-D{key}=\"{val}\"" for key, val in names.items()]
+    cmd += ["-o", str(so), str(ROOT / "bladedisc_b200" / "standin" / "qlinear_program.c")]
+    subprocess.run(cmd, check=True, capture_output=True)
+    meta = tmp / "meta"
+    M.write_metadata(meta, [(names["CONST_W"], False, w_h.numpy()), (names["CONST_B"], False, bias_h.numpy()),
+                            ("2_f32_", False, np.float32(S_X)), (names["CONST_SW"], False, w_scale_h.numpy()),
+                            ("4_f32_", False, np.float32(S_OUT))])
+    return Executable(so, meta, [("i8", "cuda")], device=device)
+
+
 def _verify_rows(torch, out_d, a_h, w_h, w_scale_h, bias_h, seed):
     """Sampled rows of a step's int8 output against the CPU oracle's statement of the same epilogue
     (divide-based).  The launch uses the reciprocal form, so a value may sit one level off at a rounding
@@ -414,10 +439,46 @@ def run_ours(args):
     e2e_ms = e0.elapsed_time(e1)
     e2e_launches = layer.kernel_launches - launches_before
 
-    times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    # ---- end to end through the boundary itself: a compiled executable (the stand-in program) run by the
+    # host mirror of torch_blade's engine, every runtime service through tao_ral_call_impl
+    ral_ms, ral_steps, ral_note = None, max(3, min(args.steps, 10)), None
+    try:
+        exe = _build_boundary_executable(torch, w_h, ws_h, b_h, local)
+        a_dev = torch.empty((rows, K_DIM), dtype=torch.int8, device=dev)
+
+        def ral_step():
+            a_dev.copy_(a_pin, non_blocking=True)
+            q = exe.run([a_dev])[0]
+            o_pin.copy_(q, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            return q
+        for _ in range(3):
+            q = ral_step()
+        if not torch.equal(q, o_sets[0]) and not torch.equal(q.cpu(), o_pin):
+            raise RuntimeError("the executable's output differs from the direct call's")
+        barrier()
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record()
+        for _ in range(ral_steps):
+            ral_step()
+        r1.record()
+        barrier()
+        ral_ms = r0.elapsed_time(r1)
+        exe.close()
+        del a_dev
+    except Exception as e:   # gcc missing on the box, for instance: the leg is reported as absent, with the reason
+        ral_note = f"{type(e).__name__}: {e}"
+        ral_ms = None
+        if world > 1:
+            barrier()
+            barrier()
+
+    times = torch.tensor([total_ms, e2e_ms, ral_ms if ral_ms is not None else -1.0], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms = times.tolist()
+    total_ms, e2e_ms, ral_ms_max = times.tolist()
+    if ral_ms is not None:
+        ral_ms = ral_ms_max
 
     # ---- second record in the same process group: the W8A8 BERT-base encoder over a fixed global batch
     # split over the ranks (the other half of the headline metric); the linear's operands are released first
@@ -469,6 +530,13 @@ def run_ours(args):
             "gpu_launches": args.steps, "e2e_gpu_launches": e2e_launches,
             "clocks": clocks,
         }
+        line["e2e_ral"] = ({"value": world * ops_per_step * ral_steps / (ral_ms * 1e-3) / 1e12, "unit": "TOPS",
+                            "ms_per_step": ral_ms / ral_steps, "steps": ral_steps,
+                            "h2d_bytes_per_step": rows * K_DIM, "d2h_bytes_per_step": rows * N_DIM,
+                            "path": "pinned host -> device copy, compiled stand-in executable (ral_recv_input, ral_const, "
+                                    "disc_b200_qgemm, ral_send_output through tao_ral_call_impl), device -> pinned host "
+                                    "copy; one copy each way, not overlapped with the kernel"}
+                           if ral_ms is not None else {"value": None, "unavailable": ral_note})
         if encoder is not None:
             line["encoder"] = encoder
         if world == 1 and not args.skip_cpu_baseline:
