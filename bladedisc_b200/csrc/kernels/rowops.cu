@@ -348,7 +348,6 @@ template <typename T, int G, int NV, int R, bool ALIGNED>
 __global__ void __launch_bounds__(kBlock, (NV * R <= 4 ? 3 : (NV * R <= 8 ? 2 : 1)))
 norm_kernel(NormParams p) {
   grid_dep_launch();  // the next kernel may begin its own set-up
-  grid_dep_wait();    // the kernel before this one has finished and its writes are visible
   constexpr int E = VecT<T>::kElems;
   __shared__ float red[R * 8];
   const RowIndex<G, R> ix;
@@ -356,6 +355,21 @@ norm_kernel(NormParams p) {
   const int cols = static_cast<int>(p.cols);
   const T* xb = reinterpret_cast<const T*>(p.x);
   const T* rb = reinterpret_cast<const T*>(p.residual);
+  // gamma and beta are parameters of the model, final long before this launch: short rows fetch them
+  // while the kernel before this one may still be running, which takes their latency (one more trip to
+  // L2 after the reductions) off the critical path of a launch that is a few microseconds long.
+  constexpr bool kEarlyParams = NV <= 4;
+  const T* gb = reinterpret_cast<const T*>(p.gamma);
+  const T* bb = (!p.rms && p.beta) ? reinterpret_cast<const T*>(p.beta) : nullptr;
+  uint4 gvs[kEarlyParams ? NV : 1], bvs[kEarlyParams ? NV : 1];
+  if (kEarlyParams) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      gvs[i] = load_vec<T>(gb, cols, t + i * G, ALIGNED, 0.f);
+      bvs[i] = bb ? load_vec<T>(bb, cols, t + i * G, ALIGNED, 0.f) : make_uint4(0, 0, 0, 0);
+    }
+  }
+  grid_dep_wait();    // the kernel before this one has finished and its writes are visible
   uint4 raw[R][NV];
   bool live[R];
   float mean[R], var[R];
@@ -435,8 +449,6 @@ norm_kernel(NormParams p) {
 #pragma unroll
   for (int r = 0; r < R; ++r) rstd[r] = 1.f / sqrtf(var[r] * inv_n + p.eps);
 
-  const T* gb = reinterpret_cast<const T*>(p.gamma);
-  const T* bb = (!p.rms && p.beta) ? reinterpret_cast<const T*>(p.beta) : nullptr;
   const bool dyn = p.q_out && !p.q_scale;
   // normalise in place: raw becomes y in the storage type (what the next op reads)
   float qs[R];
@@ -444,8 +456,8 @@ norm_kernel(NormParams p) {
   for (int r = 0; r < R; ++r) qs[r] = 0.f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    const uint4 gv = load_vec<T>(gb, cols, t + i * G, ALIGNED, 0.f);
-    const uint4 bv = bb ? load_vec<T>(bb, cols, t + i * G, ALIGNED, 0.f) : make_uint4(0, 0, 0, 0);
+    const uint4 gv = kEarlyParams ? gvs[i] : load_vec<T>(gb, cols, t + i * G, ALIGNED, 0.f);
+    const uint4 bv = kEarlyParams ? bvs[i] : (bb ? load_vec<T>(bb, cols, t + i * G, ALIGNED, 0.f) : make_uint4(0, 0, 0, 0));
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       float y[E];

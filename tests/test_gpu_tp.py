@@ -40,12 +40,10 @@ def test_two_pass_row_quantize(ops, rows, cols, ld, gated, dtype):
     q = ops.quantize_rows(gate, scale, up, out=out[1:rows + 1, :cols])
     want = np.clip(np.rint(h / scale.cpu().numpy().astype(np.float64)[:, None]), -128, 127)
     diff = np.abs(q.cpu().numpy().astype(np.int32) - want.astype(np.int32))
-    # without gating the division is exact; with it (approximate exp / reciprocal) a value may land one level
-    # off, but only a small fraction of them may
-    if gated:
-        assert diff.max() <= 1 and (diff > 0).mean() < 1e-2, ((diff > 0).mean(), diff.max())
-    else:
-        assert diff.max() == 0
+    # with gating (approximate exp / reciprocal) a value may land one level off, but only a small share may
+    # `want` divides in double: against it a float32 quotient on a rounding tie may land on the other level
+    # (the float32 oracle below is matched exactly without gating)
+    assert diff.max() <= 1 and (diff > 0).mean() < (1e-2 if gated else 1e-3), ((diff > 0).mean(), diff.max())
     assert np.abs(q.cpu().numpy()).max() == 127  # the row maximum lands on the last level
     q2, s2 = ops.quantize_rows_whole(gate, up)     # both passes in one kernel: the same bytes
     assert torch.equal(q2, q) and torch.equal(s2, scale)
