@@ -3,6 +3,7 @@
 // functions.
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <cctype>
 #include <cstdio>
 #include <cstdlib>
@@ -150,6 +151,129 @@ int64_t disc_b200_qgemm_small_m_noalloc_capacity(void) { return disc_b200::qgemm
 
 int64_t disc_b200_qgemm_scratch_bytes(int64_t M, int64_t N, int64_t K) {
   return disc_b200::qgemm_splitk_ws_bytes(M, N, K);
+}
+
+// ---- quantized linear on host buffers: rows streamed in, multiplied and streamed out in chunks
+struct disc_b200_host_linear {
+  int device = 0;
+  int64_t chunk_rows = 0, K = 0, N = 0;
+  int out_bytes = 1;
+  int slots = 0;
+  std::vector<int8_t*> a;       // device staging, one per slot
+  std::vector<char*> o;
+  cudaStream_t s_in = nullptr, s_mm = nullptr, s_out = nullptr;
+  std::vector<cudaEvent_t> in_done, mm_done, out_done;
+  cudaEvent_t start = nullptr, finished = nullptr;
+};
+
+void disc_b200_host_linear_destroy(disc_b200_host_linear* h) {
+  if (!h) return;
+  for (auto p : h->a) cudaFree(p);
+  for (auto p : h->o) cudaFree(p);
+  for (auto e : h->in_done) cudaEventDestroy(e);
+  for (auto e : h->mm_done) cudaEventDestroy(e);
+  for (auto e : h->out_done) cudaEventDestroy(e);
+  if (h->start) cudaEventDestroy(h->start);
+  if (h->finished) cudaEventDestroy(h->finished);
+  if (h->s_in) cudaStreamDestroy(h->s_in);
+  if (h->s_mm) cudaStreamDestroy(h->s_mm);
+  if (h->s_out) cudaStreamDestroy(h->s_out);
+  delete h;
+}
+
+disc_b200_host_linear* disc_b200_host_linear_create(int64_t chunk_rows, int64_t K, int64_t N, int32_t out_dtype,
+                                                    int32_t slots) {
+  if (chunk_rows <= 0 || K <= 0 || N <= 0 || slots < 2 || slots > 8 ||
+      (out_dtype != DISC_B200_OUT_I8 && out_dtype != DISC_B200_OUT_F16)) {
+    g_last_error = "host_linear_create: chunk_rows, K, N positive, 2..8 slots, int8 or f16 output";
+    return nullptr;
+  }
+  auto* h = new disc_b200_host_linear;
+  h->chunk_rows = chunk_rows;
+  h->K = K;
+  h->N = N;
+  h->out_bytes = out_dtype == DISC_B200_OUT_I8 ? 1 : 2;
+  h->slots = slots;
+  bool ok = cudaGetDevice(&h->device) == cudaSuccess;
+  ok = ok && cudaStreamCreateWithFlags(&h->s_in, cudaStreamNonBlocking) == cudaSuccess;
+  ok = ok && cudaStreamCreateWithFlags(&h->s_mm, cudaStreamNonBlocking) == cudaSuccess;
+  ok = ok && cudaStreamCreateWithFlags(&h->s_out, cudaStreamNonBlocking) == cudaSuccess;
+  ok = ok && cudaEventCreateWithFlags(&h->start, cudaEventDisableTiming) == cudaSuccess;
+  ok = ok && cudaEventCreateWithFlags(&h->finished, cudaEventDisableTiming) == cudaSuccess;
+  for (int i = 0; ok && i < slots; ++i) {
+    int8_t* a = nullptr;
+    char* o = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr, e2 = nullptr;
+    ok = cudaMalloc(&a, static_cast<size_t>(chunk_rows * K)) == cudaSuccess &&
+         cudaMalloc(&o, static_cast<size_t>(chunk_rows * N * h->out_bytes)) == cudaSuccess &&
+         cudaEventCreateWithFlags(&e0, cudaEventDisableTiming) == cudaSuccess &&
+         cudaEventCreateWithFlags(&e1, cudaEventDisableTiming) == cudaSuccess &&
+         cudaEventCreateWithFlags(&e2, cudaEventDisableTiming) == cudaSuccess;
+    if (a) h->a.push_back(a);
+    if (o) h->o.push_back(o);
+    if (e0) h->in_done.push_back(e0);
+    if (e1) h->mm_done.push_back(e1);
+    if (e2) h->out_done.push_back(e2);
+  }
+  if (!ok) {
+    g_last_error = std::string("host_linear_create: ") + cudaGetErrorString(cudaGetLastError());
+    disc_b200_host_linear_destroy(h);
+    return nullptr;
+  }
+  return h;
+}
+
+int32_t disc_b200_host_linear_run(disc_b200_host_linear* h, const disc_b200_qgemm_args* args, const int8_t* a_host,
+                                  void* out_host, int64_t M, void* stream) {
+  if (!h || !args || !a_host || !out_host || M < 0) {
+    g_last_error = "host_linear_run: null argument";
+    return 1;
+  }
+  if (args->K != h->K || args->N != h->N ||
+      (args->out_dtype == DISC_B200_OUT_I8 ? 1 : 2) != h->out_bytes || args->a_slabs > 1) {
+    g_last_error = "host_linear_run: the launch description does not match the pipeline (K, N, output type; no slabs)";
+    return 1;
+  }
+  cudaStream_t cur = static_cast<cudaStream_t>(stream);
+  cudaError_t st = cudaEventRecord(h->start, cur);
+  for (cudaStream_t s : {h->s_in, h->s_mm, h->s_out}) {
+    if (st == cudaSuccess) st = cudaStreamWaitEvent(s, h->start, 0);
+  }
+  const int64_t chunks = (M + h->chunk_rows - 1) / h->chunk_rows;
+  const char* detail = nullptr;
+  for (int64_t i = 0; st == cudaSuccess && i < chunks; ++i) {
+    const int64_t r0 = i * h->chunk_rows;
+    const int64_t rows = std::min(h->chunk_rows, M - r0);
+    const int k = static_cast<int>(i % h->slots);
+    // the slot's activation buffer is free once the product that read it is done
+    if (i >= h->slots) st = cudaStreamWaitEvent(h->s_in, h->mm_done[k], 0);
+    if (st == cudaSuccess)
+      st = cudaMemcpyAsync(h->a[k], a_host + r0 * h->K, static_cast<size_t>(rows * h->K), cudaMemcpyHostToDevice, h->s_in);
+    if (st == cudaSuccess) st = cudaEventRecord(h->in_done[k], h->s_in);
+    if (st == cudaSuccess) st = cudaStreamWaitEvent(h->s_mm, h->in_done[k], 0);
+    // and its result buffer once the copy that read it is done
+    if (st == cudaSuccess && i >= h->slots) st = cudaStreamWaitEvent(h->s_mm, h->out_done[k], 0);
+    if (st != cudaSuccess) break;
+    disc_b200::QGemmParams p = to_params(args);
+    p.a = h->a[k];
+    p.out = h->o[k];
+    p.M = rows;
+    p.lda = h->K;
+    p.ldo = h->N;
+    st = disc_b200::qgemm_launch(p, h->s_mm, &detail);
+    if (st == cudaSuccess) st = cudaEventRecord(h->mm_done[k], h->s_mm);
+    if (st == cudaSuccess) st = cudaStreamWaitEvent(h->s_out, h->mm_done[k], 0);
+    if (st == cudaSuccess)
+      st = cudaMemcpyAsync(static_cast<char*>(out_host) + r0 * h->N * h->out_bytes, h->o[k],
+                           static_cast<size_t>(rows * h->N * h->out_bytes), cudaMemcpyDeviceToHost, h->s_out);
+    if (st == cudaSuccess) st = cudaEventRecord(h->out_done[k], h->s_out);
+  }
+  // the caller's stream continues when everything has left the pipeline
+  for (cudaStream_t s : {h->s_in, h->s_mm, h->s_out}) {
+    if (st == cudaSuccess) st = cudaEventRecord(h->finished, s);
+    if (st == cudaSuccess) st = cudaStreamWaitEvent(cur, h->finished, 0);
+  }
+  return finish(st, "host_linear_run", detail);
 }
 
 int32_t disc_b200_qgemm_path(const disc_b200_qgemm_args* args) {

@@ -204,6 +204,21 @@ int64_t disc_b200_qgemm_scratch_bytes(int64_t M, int64_t N, int64_t K);
 /* Path (DISC_B200_PATH_*) the launch would take. */
 int32_t disc_b200_qgemm_path(const disc_b200_qgemm_args* args);
 
+/* The quantized linear on HOST buffers, for a serving process whose activations arrive in host memory: the
+ * rows are streamed host -> device, multiplied and the result streamed back in chunks of `chunk_rows` over three
+ * streams of the pipeline, so that both copy directions and the tensor-core work overlap (pin the host buffers,
+ * or the copies serialise).  The weight, scales and bias of `args` stay resident on the device, as the constants
+ * of a compiled graph do (tao_compiler/mlir/ral/context/common_context_impl_cuda.cc:61-132); `args->a`, `out`, `M`,
+ * `lda`, `ldo` are ignored in favour of the host buffers.  create allocates the staging buffers (slots x
+ * chunk_rows x (K + N * element size) bytes on the current device); run orders itself after `stream` and makes
+ * `stream` wait for its completion; it does not synchronise the host. */
+typedef struct disc_b200_host_linear disc_b200_host_linear;
+disc_b200_host_linear* disc_b200_host_linear_create(int64_t chunk_rows, int64_t K, int64_t N, int32_t out_dtype,
+                                                    int32_t slots);
+int32_t disc_b200_host_linear_run(disc_b200_host_linear* h, const disc_b200_qgemm_args* args, const int8_t* a_host,
+                                  void* out_host, int64_t M, void* stream);
+void disc_b200_host_linear_destroy(disc_b200_host_linear* h);
+
 /* The small-M path (M <= 128) of disc_b200_qgemm for callers that cannot
  * allocate device memory at the point of the call and so have no scratch to
  * pass: code that runs while a stream is being captured, servers that gave
