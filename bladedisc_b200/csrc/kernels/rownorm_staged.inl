@@ -20,10 +20,9 @@
 // Measured on 16384 x 4096 (RMSNorm + per-token quantize): 105 -> 77 us; rows of
 // 768 / 1024 columns are faster in the register-resident kernel and stay there.
 // The arithmetic is that of norm_kernel: fp32 accumulation, x + residual and y
-// rounded to fp16 where a separate kernel would have stored them, quotients
-// that decide an int8 value exact (reciprocal product with a tie test per
-// vector, IEEE division for ties).  Per-token quantization needs no clamp:
-// |y| / (max|y| / 127) cannot leave the int8 range.
+// rounded to fp16 where a separate kernel would have stored them, the int8
+// output in the reciprocal form (quant_vec_recip: within one level of the
+// divide-based formula).
 
 constexpr int kStagedWarps = 4;  // warps (rows in flight) per block
 
@@ -180,27 +179,13 @@ norm_staged_f16_kernel(NormParams p) {
         qs = fmaxf(__fdiv_rn(m, 127.f), FLT_EPSILON);
         if (lane == 0 && p.q_row_scale) p.q_row_scale[row] = qs;
       }
-      const Divisor d = make_divisor(qs);
+      const RecipQuant d = make_recip_quant(qs);
       int8_t* qrow = p.q_out + row * p.cols;
 #pragma unroll 2
       for (int v = lane; v < nvec; v += 32) {
         float y[E], q[E];
         VecT<__half>::unpack(xs[v], y);
-        if (dyn && d.fast) {
-          float worst = 0.f;
-#pragma unroll
-          for (int j = 0; j < E; ++j) {
-            const float t = y[j] * d.inv;
-            q[j] = t + kRoundMagic;
-            worst = fmaxf(worst, fabsf(t - (q[j] - kRoundMagic)));
-          }
-          if (worst > 0.499f) {  // some quotient sits on a rounding tie: divide for real
-#pragma unroll
-            for (int j = 0; j < E; ++j) q[j] = quant_biased(y[j], d, 0.f, -128.f, 127.f);
-          }
-        } else {
-          quant_vec<E>(y, d, q);
-        }
+        quant_vec_recip<E>(y, d, q);
         *reinterpret_cast<uint2*>(qrow + v * E) =
             make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
       }

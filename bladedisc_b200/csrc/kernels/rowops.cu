@@ -320,24 +320,29 @@ __device__ __forceinline__ int64_t row_blocks(int64_t rows) {
   return (rows + kRowsPerBlock - 1) / kRowsPerBlock;
 }
 
-// E values of one vector quantized at `d` (zero point 0, int8 range) into biased
-// floats for store_q.  The rounding constant is added first, the clamp works on
-// the biased value, and the tie test that decides whether the reciprocal
-// product may stand in for the division is taken once per vector.
+// The reciprocal form for quantization fused behind another row operation (zero
+// point 0, int8 range): one fused multiply-add forms x * (1 / s) under the
+// rounding constant -- a single rounding, to nearest even, so a quotient that is
+// exactly a tie (power-of-two scales on fp16 data produce many) goes where the
+// division sends it -- and the clamp works on the biased value.  Three
+// instructions per value against seven with the tie test above.  The rounded
+// reciprocal instead of the division can move a value whose quotient lies
+// within an ulp of a rounding tie to the neighbouring level, never further.
+struct RecipQuant {
+  float inv;
+};
+__device__ __forceinline__ RecipQuant make_recip_quant(float s) {
+  RecipQuant u;
+  u.inv = __frcp_rn(s);
+  return u;
+}
+__device__ __forceinline__ float quant_recip(float x, const RecipQuant& u) {
+  return fminf(fmaxf(__fmaf_rn(x, u.inv, kRoundMagic), kRoundMagic - 128.f), kRoundMagic + 127.f);
+}
 template <int E>
-__device__ __forceinline__ void quant_vec(const float* y, const Divisor& d, float* q) {
-  float worst = 0.f;
+__device__ __forceinline__ void quant_vec_recip(const float* y, const RecipQuant& u, float* q) {
 #pragma unroll
-  for (int j = 0; j < E; ++j) {
-    const float t = y[j] * d.inv;
-    const float r = t + kRoundMagic;
-    worst = fmaxf(worst, fabsf(t - (r - kRoundMagic)));
-    q[j] = fminf(fmaxf(r, kRoundMagic - 128.f), kRoundMagic + 127.f);
-  }
-  if (worst > 0.499f || !d.fast) {  // some quotient sits on a rounding tie: divide for real
-#pragma unroll
-    for (int j = 0; j < E; ++j) q[j] = quant_biased(y[j], d, 0.f, -128.f, 127.f);
-  }
+  for (int j = 0; j < E; ++j) q[j] = quant_recip(y[j], u);
 }
 
 // LayerNorm / RMSNorm over rows held in registers, with optional residual add,
@@ -491,14 +496,13 @@ norm_kernel(NormParams p) {
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     if (!live[r]) continue;
-    const Divisor d = make_divisor(qs[r]);
+    const RecipQuant d = make_recip_quant(qs[r]);
     const int64_t off = (ix.row0 + r) * p.cols;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       float y[E], q[E];
-#pragma unroll
-      for (int j = 0; j < E; ++j) y[j] = VecT<T>::get(raw[r][i], j);
-      quant_vec<E>(y, d, q);
+      VecT<T>::unpack(raw[r][i], y);
+      quant_vec_recip<E>(y, d, q);
       store_q<E>(p.q_out + off, cols, t + i * G, ALIGNED, q);
     }
   }
@@ -541,13 +545,13 @@ dynquant_kernel(DynQuantParams p, int aligned) {
     if (!live[r]) continue;
     const float s = fmaxf(__fdiv_rn(m[r], 127.f), FLT_EPSILON);
     if (t == 0) p.row_scale[ix.row0 + r] = s;
-    const Divisor d = make_divisor(s);
+    const RecipQuant d = make_recip_quant(s);
     const int64_t off = (ix.row0 + r) * p.cols;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      float q[E];
-#pragma unroll
-      for (int j = 0; j < E; ++j) q[j] = quant_biased(VecT<T>::get(raw[r][i], j), d, 0.f, -128.f, 127.f);
+      float y[E], q[E];
+      VecT<T>::unpack(raw[r][i], y);
+      quant_vec_recip<E>(y, d, q);
       store_q<E>(p.q + off, cols, t + i * G, al, q);
     }
   }
@@ -638,14 +642,14 @@ gated_quant_kernel(GatedQuantParams p, int aligned) {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       if (!live[r]) continue;
-      const Divisor d = make_divisor(PASS == 1 ? __ldg(p.row_scale + ix.row0 + r) : m[r]);
+      const RecipQuant d = make_recip_quant(PASS == 1 ? __ldg(p.row_scale + ix.row0 + r) : m[r]);
       const int64_t off = (ix.row0 + r) * p.ldq;
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
         if ((t + i * G) * E >= cols) continue;
         float h[E], q[E];
         values(r, i, h);
-        quant_vec<E>(h, d, q);
+        quant_vec_recip<E>(h, d, q);
         store_q<E>(p.q + off, cols, t + i * G, al, q);
       }
     }
@@ -882,7 +886,9 @@ __global__ void __launch_bounds__(kBlock) rope_kv_kernel(RopeParams p) {
     else if ((nvec) <= 16) DISC_ROW_LAUNCH(KERNEL, T, 8, 2, 2, rows, stream, __VA_ARGS__);             \
     else if ((nvec) <= 32) DISC_ROW_LAUNCH(KERNEL, T, 16, 2, 2, rows, stream, __VA_ARGS__);            \
     else if ((nvec) <= 64) DISC_ROW_LAUNCH(KERNEL, T, 32, 2, 2, rows, stream, __VA_ARGS__);            \
+    else if ((nvec) <= 96) DISC_ROW_LAUNCH(KERNEL, T, 32, 3, 1, rows, stream, __VA_ARGS__);            \
     else if ((nvec) <= 128) DISC_ROW_LAUNCH(KERNEL, T, 32, 4, 1, rows, stream, __VA_ARGS__);           \
+    else if ((nvec) <= 192) DISC_ROW_LAUNCH(KERNEL, T, 32, 6, 1, rows, stream, __VA_ARGS__);           \
     else if ((nvec) <= 256) DISC_ROW_LAUNCH(KERNEL, T, 32, 8, 1, rows, stream, __VA_ARGS__);           \
     else if ((nvec) <= 512) DISC_ROW_LAUNCH(KERNEL, T, 256, 2, 1, rows, stream, __VA_ARGS__);          \
     else if ((nvec) <= 1024) DISC_ROW_LAUNCH(KERNEL, T, 256, 4, 1, rows, stream, __VA_ARGS__);         \
@@ -916,7 +922,9 @@ __global__ void __launch_bounds__(kBlock) rope_kv_kernel(RopeParams p) {
     else if ((nvec) <= 16) DISC_ROW_LAUNCH_P(KERNEL, T, 8, 2, 2, rows, stream, __VA_ARGS__);           \
     else if ((nvec) <= 32) DISC_ROW_LAUNCH_P(KERNEL, T, 16, 2, 2, rows, stream, __VA_ARGS__);          \
     else if ((nvec) <= 64) DISC_ROW_LAUNCH_P(KERNEL, T, 32, 2, 2, rows, stream, __VA_ARGS__);          \
+    else if ((nvec) <= 96) DISC_ROW_LAUNCH_P(KERNEL, T, 32, 3, 1, rows, stream, __VA_ARGS__);          \
     else if ((nvec) <= 128) DISC_ROW_LAUNCH_P(KERNEL, T, 32, 4, 1, rows, stream, __VA_ARGS__);         \
+    else if ((nvec) <= 192) DISC_ROW_LAUNCH_P(KERNEL, T, 32, 6, 1, rows, stream, __VA_ARGS__);         \
     else if ((nvec) <= 256) DISC_ROW_LAUNCH_P(KERNEL, T, 32, 8, 1, rows, stream, __VA_ARGS__);         \
     else if ((nvec) <= 512) DISC_ROW_LAUNCH_P(KERNEL, T, 256, 2, 1, rows, stream, __VA_ARGS__);        \
     else if ((nvec) <= 1024) DISC_ROW_LAUNCH_P(KERNEL, T, 256, 4, 1, rows, stream, __VA_ARGS__);       \

@@ -202,7 +202,8 @@ class QuantDecoder:
 def reference_forward(dec: QuantDecoder, ids: torch.Tensor) -> torch.Tensor:
     """The same model in plain torch on ONE GPU from a world-1 decoder's
     weights: fp32 math with the quantization points of the kernel path restated
-    as fake-quant (per-token scale = max|x| / 127, round half to even).  Used by
+    as fake-quant (per-token scale s = max|x| / 127, level = x * fl(1 / s)
+    rounded once, half to even: the reciprocal form of the row kernels).  Used by
     the tests as the end-to-end oracle; no cache (prefill only)."""
     if dec.world != 1:
         raise ValueError("reference_forward takes an unsharded decoder")
@@ -211,7 +212,8 @@ def reference_forward(dec: QuantDecoder, ids: torch.Tensor) -> torch.Tensor:
 
     def fq_rows(x):
         s = (x.abs().amax(dim=1, keepdim=True) / 127.0).clamp_min(torch.finfo(torch.float32).eps)
-        return torch.round(x / s).clamp(-128, 127) * s
+        inv = (1.0 / s).double()  # fl(1 / s); the product in double is exact, so one rounding as in a fused multiply-add
+        return torch.round(x.double() * inv).clamp(-128, 127).float() * s
 
     def lin(layer: ColumnParallelQLinear, x):
         w = layer.wq.float() * layer.w_scale[:, None]

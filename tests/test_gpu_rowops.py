@@ -23,6 +23,13 @@ def _dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
+def _one_level(q, want, share=1e-3):
+    """int8 results of the quantization fused behind a row operation use the reciprocal form: at most one
+    level from the divide-based formula, and that on a small share of the values only."""
+    d = np.abs(q.cpu().numpy().astype(np.int32) - np.asarray(want).astype(np.int32))
+    assert d.max() <= 1 and (d > 0).mean() <= share, f"max {d.max()}, share off by one {(d > 0).mean():.2e}"
+
+
 @pytest.mark.parametrize("shape", [(8, 128, 768), (1,), (17,), (5, 33), (1024, 3072), (3, 1, 16)])
 @pytest.mark.parametrize("zp", [None, 3])
 def test_quantize_per_tensor_bit_exact(ops, shape, zp):
@@ -80,8 +87,10 @@ def test_dynamic_quantize(ops, rows, cols, dtype):
     q, s = ops.dynamic_quantize(_dev(x))
     qw, sw = c.dynamic_quantize(x.astype(np.float32))
     assert (s.cpu().numpy() == sw).all()
-    assert (q.cpu().numpy() == qw).all()
+    _one_level(q, qw)
     assert (q.cpu().numpy()[0] == 0).all()
+    if rows > 1:
+        assert np.abs(q.cpu().numpy()[1:]).max(axis=1).min() == 127  # every row's largest magnitude lands on the last level
 
 
 def test_layernorm_golden_fp32(ops, golden):
@@ -110,7 +119,7 @@ def test_layernorm_vs_oracle(ops, rows, cols, dtype, residual):
 
 
 def test_layernorm_quantized_second_output(ops):
-    """The int8 copy equals quantize(y) of the stored y, bit for bit."""
+    """The int8 copy is quantize(y) of the stored y in the reciprocal form: within one level of the divide."""
     from oracle import c
     rng = np.random.default_rng(1)
     x = torch.from_numpy(rng.standard_normal((130, 768)).astype(np.float32)).half().cuda()
@@ -119,7 +128,7 @@ def test_layernorm_quantized_second_output(ops):
     bt = torch.zeros(768, dtype=torch.float16, device="cuda")
     s = np.float32(4.0 / 127)
     y, q = ops.layernorm_quant(x, gm, bt, _dev(np.array([s])), residual=r)
-    assert (q.cpu().numpy() == c.quantize(y.float().cpu().numpy(), s)).all()
+    _one_level(q, c.quantize(y.float().cpu().numpy(), s))
     y2 = ops.layernorm(x, gm, bt, residual=r)
     assert torch.equal(y, y2)
 
@@ -138,7 +147,8 @@ def test_rmsnorm_sum_and_dynamic_quant(ops, cols):
     q, rs, s2 = ops.rmsnorm_dynamic_quant(x.cuda(), gm.cuda(), eps=1e-6, residual=r.cuda())
     assert torch.equal(s2, s)
     qw, sw = c.dynamic_quantize(y.float().cpu().numpy())
-    assert (rs.cpu().numpy() == sw).all() and (q.cpu().numpy() == qw).all()
+    assert (rs.cpu().numpy() == sw).all()
+    _one_level(q, qw)
 
 
 def test_softmax_golden_fp32(ops, golden):
