@@ -28,6 +28,7 @@ SOURCES = [
     "ral/pdl_attr.cc",
     "ral/nccl_dyn.cc",
     "kernels/woq_gemm.cu",
+    "kernels/woq_gemm_tc.cu",
     "kernels/qconv.cu",
     "kernels/observer.cu",
     "kernels/attention.cu",
@@ -40,7 +41,7 @@ SOURCES = [
     "c_api.cc",
 ]
 HEADERS = [
-    "kernels/qgemm.h", "kernels/rowops.h", "kernels/woq_gemm.h", "kernels/qconv.h", "kernels/observer.h", "kernels/attention.h", "ral/conv_plan.h", "kernels/sm100_ptx.cuh", "kernels/device_info.h",
+    "kernels/qgemm.h", "kernels/rowops.h", "kernels/woq_gemm.h", "kernels/qconv.h", "kernels/observer.h", "kernels/attention.h", "ral/conv_plan.h", "kernels/sm100_ptx.cuh", "kernels/device_info.h", "kernels/tensor_map.h",
     "kernels/qgemm_pair.inl", "kernels/qgemm_gemv.inl", "kernels/qgemm_skinny.inl",
     "kernels/rownorm_staged.inl",
     "ral/abi.h", "ral/context.h", "ral/pdl_attr.h", "ral/nccl_dyn.h", "ral/metadata.h", "ral/cu_driver_dyn.h",

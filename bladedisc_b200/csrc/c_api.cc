@@ -711,6 +711,7 @@ int32_t disc_b200_weight_only_qgemm(const disc_b200_weight_only_qgemm_args* a, v
   p.ldw = a->ldw;
   p.ldo = a->ldo;
   p.type = a->type;
+  p.path = a->path;
   const char* detail = nullptr;
   const cudaError_t st = disc_b200::woq_gemm_launch(p, static_cast<cudaStream_t>(stream), &detail);
   return finish(st, "weight_only_qgemm", detail);

@@ -32,6 +32,7 @@
 
 #include "device_info.h"
 #include "sm100_ptx.cuh"
+#include "tensor_map.h"
 
 namespace disc_b200 {
 
@@ -356,23 +357,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttnBlock* 
   }
 }
 
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess) {
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-  });
-  return fn;
-}
+EncodeTiledFn encode_fn() { return tensor_map_encode_fn(); }
 
 template <typename OutT>
 cudaError_t launch_t(const AttentionParams& p, const CUtensorMap& tm, cudaStream_t stream) {

@@ -31,6 +31,8 @@
 #include "qgemm.h"
 #include "rowops.h"
 #include "sm100_ptx.cuh"
+#include "tensor_map.h"
+#include "woq_gemm.h"
 
 namespace disc_b200 {
 
@@ -938,25 +940,7 @@ __global__ void qgemm_simt_kernel(const int8_t* __restrict__ a, const int8_t* __
 }
 
 // ------------------------------------------------------------------- host
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
-            cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess) {
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-  });
-  return fn;
-}
+EncodeTiledFn get_encode_fn() { return tensor_map_encode_fn(); }
 
 // int8 [rows, K] row-major (row stride ld bytes), box = box_rows x 128 bytes, 128B swizzle.
 bool make_tmap(CUtensorMap* tm, const int8_t* base, int64_t rows, int64_t K, int64_t ld,
@@ -1547,7 +1531,8 @@ int kernel_status_fetch_and_clear() {
   }
   const int r = rowops_status_fetch_and_clear();
   const int a = attention_status_fetch_and_clear();
-  return h != 0 ? h : (r != 0 ? r : a);
+  const int w = woq_tc_status_fetch_and_clear();
+  return h != 0 ? h : (r != 0 ? r : (a != 0 ? a : w));
 }
 
 }  // namespace disc_b200

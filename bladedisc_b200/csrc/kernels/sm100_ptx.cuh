@@ -69,17 +69,22 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Bounded wait.  `abort_flag` lives in shared memory: once any role of the CTA
 // has given up, the others stop waiting too.  `limit_ns` is the patience in
-// nanoseconds of %globaltimer.
+// nanoseconds of %globaltimer.  Reading %globaltimer takes a few hundred
+// nanoseconds, as long as a whole pipeline stage of the faster kernels, so the
+// clock is not looked at before 256 polls have failed, and then once per 256.
 __device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                   int* status, int code, uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0xFF) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > limit_ns) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;

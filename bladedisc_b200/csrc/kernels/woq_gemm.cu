@@ -433,6 +433,10 @@ cudaError_t woq_gemm_launch(const WoqGemmParams& p, cudaStream_t s, const char**
     *e = "weight-only qgemm: row stride smaller than the row";
     return cudaErrorInvalidValue;
   }
+  if (p.path == kWoqPathTensor ||
+      (p.path == kWoqPathAuto && p.type == kF16 && p.M >= kWoqTensorMinRows && woq_gemm_tc_usable(p))) {
+    return woq_gemm_tc_launch(p, s, e);
+  }
   if (p.type == kF16) return launch_typed<__half>(p, s, e);
   if (p.type == kF32) return launch_typed<float>(p, s, e);
   *e = "weight-only qgemm: element type must be f32 or f16";

@@ -29,7 +29,12 @@ struct WoqGemmParams {
   int64_t M, N, K;
   int64_t ldx, ldw, ldo;
   int type;             // ElemType of rowops.h: 0 = f32, 1 = f16
+  int path = 0;         // 0 = chosen by shape, 1 = streaming kernel, 2 = tensor cores (f16 only)
 };
+
+constexpr int kWoqPathAuto = 0, kWoqPathStream = 1, kWoqPathTensor = 2;
+// Rows from which the tensor-core kernel is chosen when `path` is 0.
+constexpr int kWoqTensorMinRows = 5;
 
 // The weights are constants of the model: the kernel may start reading them before
 // the kernel launched ahead of it on the stream has finished.
@@ -40,5 +45,12 @@ struct WoqGemmParams {
 int woq_gemm_plan_describe(int64_t m, int64_t n, int64_t k, int align, int sm_count, int64_t out7[7]);
 
 cudaError_t woq_gemm_launch(const WoqGemmParams& p, cudaStream_t s, const char** err);
+
+// The tensor-core kernel (woq_gemm_tc.cu): fp16 activations, N a multiple of 16, weights and
+// activations 16-byte aligned with row pitches to match; zero points within [-1024, 1024].
+bool woq_gemm_tc_usable(const WoqGemmParams& p);
+cudaError_t woq_gemm_tc_launch(const WoqGemmParams& p, cudaStream_t s, const char** err);
+// Reads and clears the status word the kernel sets when one of its bounded waits ran out (0 = ok).
+int woq_tc_status_fetch_and_clear();
 
 }  // namespace disc_b200

@@ -134,7 +134,7 @@ def bench_qgemm(M, K, N, out_dtype, hbm, tops_peak, iters, exact=False, path=Non
             "tops": tops, "gbs": gbs, "bound": bound, "frac": frac, "sets": n_sets}
 
 
-def bench_weight_only(M, K, N, hbm, iters):
+def bench_weight_only(M, K, N, hbm, iters, path=None):
     """Weight-only linear: algorithmic bytes = the uint8 weights once + activations in and out + per-column vectors."""
     dev = "cuda"
     algo_bytes = K * N + 2 * M * K + 2 * M * N + (2 + 4 + 2) * N
@@ -150,10 +150,10 @@ def bench_weight_only(M, K, N, hbm, iters):
     zp = torch.full((N,), 128, dtype=torch.int32, device=dev)
     bias = torch.randn(N, device=dev, generator=g).half()
     torch.cuda.synchronize()
-    fns = [(lambda x=x, w=w, o=o: ops.weight_only_qgemm(x, w, scale, zp, bias, out=o)) for x, w, o in sets]
+    fns = [(lambda x=x, w=w, o=o: ops.weight_only_qgemm(x, w, scale, zp, bias, out=o, path=path)) for x, w, o in sets]
     ms = time_ms(fns, iters)
     gbs = algo_bytes / (ms * 1e-3) / 1e9
-    return {"kernel": "weight_only_qgemm", "M": M, "K": K, "N": N, "out": "float16", "us": ms * 1e3,
+    return {"kernel": "weight_only_qgemm", "M": M, "K": K, "N": N, "out": "float16/" + (path or "auto"), "us": ms * 1e3,
             "tops": 2.0 * M * N * K / (ms * 1e-3) / 1e12, "gbs": gbs, "bound": "hbm", "frac": gbs / hbm, "sets": n_sets}
 
 
@@ -269,6 +269,7 @@ def main():
     ap.add_argument("--min-rows", type=int, default=0, help="quantized-linear points with at least this many rows")
     ap.add_argument("--max-rows", type=int, default=1 << 30, help="quantized-linear points with at most this many rows")
     ap.add_argument("--path", default=None, help="force a quantized-linear path (tiled, pair, skinny, small_m, gemv)")
+    ap.add_argument("--woq-path", default=None, help="weight-only linear: stream or tensor (default: both up to 16 rows, the library's choice above)")
     ap.add_argument("--exact", action="store_true", help="also time int8 output with the exact-division epilogue")
     ap.add_argument("--int-mm", action="store_true", help="also time cuBLASLt int8 -> int32 (torch._int_mm) per point")
     args = ap.parse_args()
@@ -305,16 +306,17 @@ def main():
                       f"{r['bound']:>8}{r['frac']:>7.2f}"
                       + (f"{lib_us:>11.2f}{lib_us / r['us']:>6.2f}" if lib_us else ""), flush=True)
     if not only or any("weight_only" in o for o in only):
-        wo_ms = [1, 4, 16] if args.quick else [1, 2, 4, 8, 16]
+        wo_ms = [1, 4, 16] if args.quick else [1, 2, 4, 8, 16, 64, 256, 2048]
         wo_kns = [(4096, 4096)] if args.quick else [(4096, 4096), (4096, 11008), (11008, 4096), (4096, 12288)]
         if args.shape:
             wo_ms, wo_kns = ms_list, kns
         for K, N in wo_kns:
             for M in wo_ms:
-                r = bench_weight_only(M, K, N, hbm, 3 if args.eager else 100)
-                out["rows"].append(r)
-                print(f"{r['kernel']:<18}{M:>4}{K:>6}{N:>7}{r['out']:>9}{r['us']:>10.2f}{r['tops']:>9.1f}{r['gbs']:>9.0f}"
-                      f"{r['bound']:>8}{r['frac']:>7.2f}", flush=True)
+                for wpath in ([args.woq_path] if args.woq_path else ([None] if M > 16 else ["stream", "tensor"])):
+                    r = bench_weight_only(M, K, N, hbm, 3 if args.eager else (100 if M <= 256 else 20), wpath)
+                    out["rows"].append(r)
+                    print(f"{r['kernel']:<18}{M:>5}{K:>6}{N:>7}{r['out']:>16}{r['us']:>10.2f}{r['tops']:>9.1f}{r['gbs']:>9.0f}"
+                          f"{r['bound']:>8}{r['frac']:>7.2f}", flush=True)
     if only and any("qconv" in o for o in only):
         # (batch, height, width, channels in, channels out, window, stride): ResNet-50-shaped layers
         for n, h, w, c, o, k, st in ((32, 56, 56, 64, 64, 3, 1), (32, 28, 28, 128, 128, 3, 1), (32, 14, 14, 256, 256, 3, 1),

@@ -84,7 +84,7 @@ class WeightOnlyQGemmArgs(Structure):
     _fields_ = [
         ("x", c_void_p), ("w", c_void_p), ("scale", c_void_p), ("zero_point", c_void_p), ("bias", c_void_p),
         ("out", c_void_p), ("m", c_int64), ("n", c_int64), ("k", c_int64),
-        ("ldx", c_int64), ("ldw", c_int64), ("ldo", c_int64), ("type", c_int32),
+        ("ldx", c_int64), ("ldw", c_int64), ("ldo", c_int64), ("type", c_int32), ("path", c_int32),
     ]
 
 

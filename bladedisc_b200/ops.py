@@ -363,11 +363,13 @@ def quantize_rows(gate: torch.Tensor, row_scale: torch.Tensor, up: Optional[torc
 
 
 def weight_only_qgemm(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, zero_point: Optional[torch.Tensor] = None,
-                      bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                      path: Optional[str] = None) -> torch.Tensor:
     """``x @ ((w - zero_point) * scale) + bias`` with ``w`` uint8 ``[K, N]`` (the transposed
     weight the reference's pattern hands to ``ral_pdll_weight_only_qgemm``), ``scale`` /
     ``bias`` of ``x``'s dtype (float16 or float32) ``[N]``, ``zero_point`` int32 ``[N]``.
-    Dequantization happens in the kernel; sums are fp32."""
+    Dequantization happens in the kernel; sums are fp32.  ``path``: None (by shape),
+    "stream" or "tensor" (fp16, 16-byte aligned operands, N a multiple of 16)."""
     x = _cuda(x, "x")
     w = _cuda(w, "w", torch.uint8)
     if w.dim() != 2 or x.shape[-1] != w.shape[0]:
@@ -395,6 +397,7 @@ def weight_only_qgemm(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, zer
         _p(bias), out.data_ptr()
     a.m, a.n, a.k, a.ldx, a.ldw, a.ldo = M, N, K, K, N, N
     a.type = _etype(x)
+    a.path = {None: 0, "stream": 1, "tensor": 2}[path]
     _lib.check(L.disc_b200_weight_only_qgemm(ctypes.byref(a), _stream()))
     return out
 

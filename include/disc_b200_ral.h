@@ -330,9 +330,14 @@ int32_t disc_b200_rope_kv_append(void* qkv, void* k_cache, void* v_cache, const 
  * + bias[n]; x / scale / bias / out all f32 or all f16 (`type`), w uint8 [K, N]
  * row-major exactly as the pattern of the reference leaves it (weight_only_qgemm.pdll:2-106;
  * custom call ral_pdll_weight_only_qgemm, for which the reference has no open kernel),
- * zero_point int32 [N] or NULL.  Sums are fp32.  Built for a few rows (decode):
- * up to 16 rows stream the weights once, more rows re-read them per group of 16.
- * No scratch memory.  w holds constants of the model: the kernel may read it
+ * zero_point int32 [N] or NULL.  Sums are fp32.  Two kernels: a streaming one (any
+ * type and alignment; up to 16 rows stream the weights once, more rows re-read them per
+ * group of 16) and, for f16 with 4 rows and more, one on the tensor cores (weights
+ * dequantized to fp16 on the way into shared memory, up to 256 rows per pass over the
+ * weights; needs n a multiple of 16, w and x 16-byte aligned with ldw a multiple of 16
+ * and ldx of 8, zero points within [-1024, 1024]).  `path`: 0 = chosen by shape,
+ * 1 = streaming, 2 = tensor cores (refused with a message when the operands do not
+ * qualify).  No scratch memory.  w holds constants of the model: the kernel may read it
  * before the preceding kernel on the stream has finished. */
 typedef struct disc_b200_weight_only_qgemm_args {
   const void* x;
@@ -344,6 +349,7 @@ typedef struct disc_b200_weight_only_qgemm_args {
   int64_t m, n, k;
   int64_t ldx, ldw, ldo;
   int32_t type; /* DISC_B200_F32 / DISC_B200_F16 */
+  int32_t path; /* 0 = by shape, 1 = streaming kernel, 2 = tensor cores */
 } disc_b200_weight_only_qgemm_args;
 int32_t disc_b200_weight_only_qgemm(const disc_b200_weight_only_qgemm_args* args, void* stream);
 /* Host only: the launch plan for a problem on a GPU with sm_count SMs and weights aligned to

@@ -32,10 +32,12 @@ def _check(out, x, w, scale, zp, bias, dtype):
     assert not bad.any(), (int(bad.sum()), float(np.abs(got - want).max()))
 
 
-def _run(x, w, scale, zp, bias):
+def _run(x, w, scale, zp, bias, path=None):
     from bladedisc_b200 import ops
     d = lambda a: None if a is None else torch.from_numpy(a).cuda()
-    return ops.weight_only_qgemm(d(x), d(w), d(scale), d(zp), d(bias))
+    out = ops.weight_only_qgemm(d(x), d(w), d(scale), d(zp), d(bias), path=path)
+    assert ops.kernel_status() == 0, "a bounded wait of a kernel ran out"
+    return out
 
 
 @pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8, 13, 16])
@@ -54,6 +56,37 @@ def test_shapes_match_oracle(shape):
     m, k, n = shape
     args = _case(m, k, n, k + n, np.float16, with_bias=(n % 16 == 0), zp_kind="random" if k < 2000 else "128")
     _check(_run(*args), *args, np.float16)
+
+
+@pytest.mark.parametrize("shape", [(5, 256, 128), (16, 1024, 768), (4, 4096, 4096), (16, 4096, 11008), (64, 4096, 4096),
+                                   (100, 512, 256), (128, 1024, 384), (129, 2048, 1024), (300, 1000, 144), (7, 72, 16),
+                                   (1, 64, 16), (2048, 512, 512)])
+@pytest.mark.parametrize("zp_kind", ["random", "none"])
+def test_tensor_core_path_matches_oracle(shape, zp_kind):
+    """The tensor-core kernel, forced: one and several row blocks, k split over clusters of every size the
+    planner picks, k and channel tails (k not a multiple of 64, N a multiple of 16 only), with and without
+    zero points and bias."""
+    m, k, n = shape
+    args = _case(m, k, n, m + k + n, np.float16, with_bias=(zp_kind == "random"), zp_kind=zp_kind)
+    _check(_run(*args, path="tensor"), *args, np.float16)
+
+
+def test_tensor_core_path_is_repeatable_and_refuses_what_it_cannot_take():
+    from bladedisc_b200 import ops
+    args = _case(16, 4096, 1024, 5, np.float16, zp_kind="random")
+    a = _run(*args, path="tensor")
+    for _ in range(3):                       # partial tiles are added in rank order: bit-identical between runs
+        assert torch.equal(_run(*args, path="tensor"), a)
+    b = _run(*args, path="stream")
+    assert torch.allclose(a.float(), b.float(), rtol=2e-3, atol=2e-3)  # two summation orders of the same products
+    x32 = torch.zeros(8, 64, dtype=torch.float32, device="cuda")
+    w = torch.zeros(64, 16, dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError, match="tensor cores"):
+        ops.weight_only_qgemm(x32, w, torch.ones(16, device="cuda"), path="tensor")          # fp32 activations
+    x16 = torch.zeros(8, 64, dtype=torch.float16, device="cuda")
+    w20 = torch.zeros(64, 20, dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError, match="tensor cores"):
+        ops.weight_only_qgemm(x16, w20, torch.ones(20, dtype=torch.float16, device="cuda"), path="tensor")  # N % 16
 
 
 @pytest.mark.parametrize("shape", [(2, 3, 5), (1, 17, 3), (6, 130, 250), (3, 64, 1001)])
