@@ -20,9 +20,9 @@
 //     exist are fetched, the other rows of the 128-row operand are whatever the shared
 //     memory holds and reach accumulator rows nobody reads;
 //   * one thread issues tcgen05.mma kind::f16 (M = 128 rows, N = 256 channels, K = 16),
-//     fp32 accumulators in TMEM: D[row, channel].  The wide operand is the weights: an
-//     MMA takes the tensor core a pass over its 128 M rows however narrow N is, so with
-//     the rows as N (16 of them) an MMA would cover 2 KB of raw weights instead of 4 KB;
+//     fp32 accumulators in TMEM: D[row, channel].  The weights are the wide operand, so
+//     that one MMA covers 4 KB of raw weights and the same block shape serves decode
+//     (a few rows) and prefill (128 rows per block);
 //   * the k range can be split over a thread-block cluster (few rows leave too few
 //     channel strips to fill the GPU); the partial tiles meet in distributed shared
 //     memory and every block finishes a slice, in rank order: no scratch, no atomics,
