@@ -223,6 +223,30 @@ disc_b200_host_linear* disc_b200_host_linear_create(int64_t chunk_rows, int64_t 
   return h;
 }
 
+namespace {
+// Row ranges of the chunks of a host-buffer linear.  The first copy in and the last copy out are not
+// overlapped with anything, so long inputs start and end with quarter- and half-size chunks; in between
+// full chunks, whose fixed cost per copy (some ten microseconds) is the smallest share.
+std::vector<int64_t> host_linear_bounds(int64_t c, int64_t M) {
+  std::vector<int64_t> bounds{0};
+  const bool taper = M >= 4 * c && c >= 64;
+  const int64_t head[3] = {c / 4, c / 4, c / 2};
+  int64_t r = 0;
+  if (taper)
+    for (int64_t x : head) bounds.push_back(r += x);
+  const int64_t tail_rows = taper ? c : 0;  // c / 2 + c / 4 + c / 4
+  while (M - tail_rows - r > 0) bounds.push_back(r += std::min(c, M - tail_rows - r));
+  if (taper)
+    for (int i = 2; i >= 0; --i) bounds.push_back(r += head[i]);
+  return bounds;
+}
+}  // namespace
+
+int64_t disc_b200_host_linear_chunks(const disc_b200_host_linear* h, int64_t M) {
+  if (!h || M <= 0) return 0;
+  return static_cast<int64_t>(host_linear_bounds(h->chunk_rows, M).size()) - 1;
+}
+
 int32_t disc_b200_host_linear_run(disc_b200_host_linear* h, const disc_b200_qgemm_args* args, const int8_t* a_host,
                                   void* out_host, int64_t M, void* stream) {
   if (!h || !args || !a_host || !out_host || M < 0) {
@@ -239,11 +263,12 @@ int32_t disc_b200_host_linear_run(disc_b200_host_linear* h, const disc_b200_qgem
   for (cudaStream_t s : {h->s_in, h->s_mm, h->s_out}) {
     if (st == cudaSuccess) st = cudaStreamWaitEvent(s, h->start, 0);
   }
-  const int64_t chunks = (M + h->chunk_rows - 1) / h->chunk_rows;
+  const std::vector<int64_t> bounds = host_linear_bounds(h->chunk_rows, M);
+  const int64_t chunks = static_cast<int64_t>(bounds.size()) - 1;
   const char* detail = nullptr;
   for (int64_t i = 0; st == cudaSuccess && i < chunks; ++i) {
-    const int64_t r0 = i * h->chunk_rows;
-    const int64_t rows = std::min(h->chunk_rows, M - r0);
+    const int64_t r0 = bounds[i];
+    const int64_t rows = bounds[i + 1] - r0;
     const int k = static_cast<int>(i % h->slots);
     // the slot's activation buffer is free once the product that read it is done
     if (i >= h->slots) st = cudaStreamWaitEvent(h->s_in, h->mm_done[k], 0);

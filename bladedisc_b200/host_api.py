@@ -10,7 +10,8 @@ directions and the tensor-core work overlap.  The chunk loop runs inside the
 library (``disc_b200_host_linear_run``), so a host written in another language
 gets the same pipeline.  Chunks of about 2048 rows measured best for a 4096-wide
 layer on PCIe Gen5: every copy carries a fixed cost of some ten microseconds, so
-finer chunks lose more to that than they gain in the fill and drain of the pipe.
+finer chunks lose more to that than they gain in the fill and drain of the pipe;
+only the first and the last chunks of a long input are smaller.
 """
 import ctypes
 from typing import Optional
@@ -82,7 +83,7 @@ class HostQLinear:
         with torch.cuda.device(self.device):
             _lib.check(self._L.disc_b200_host_linear_run(self._h, ctypes.byref(self._args), a_host.data_ptr(),
                                                          out_host.data_ptr(), M, stream))
-        self.kernel_launches += (M + self.chunk_rows - 1) // self.chunk_rows
+        self.kernel_launches += self._L.disc_b200_host_linear_chunks(self._h, M)
         return out_host
 
     @property

@@ -121,6 +121,7 @@ SIGNATURES = {
     "disc_b200_qgemm_path": (c_int32, [POINTER(QGemmArgs)]),
     "disc_b200_host_linear_create": (c_void_p, [c_int64, c_int64, c_int64, c_int32, c_int32]),
     "disc_b200_host_linear_run": (c_int32, [c_void_p, POINTER(QGemmArgs), c_void_p, c_void_p, c_int64, c_void_p]),
+    "disc_b200_host_linear_chunks": (c_int64, [c_void_p, c_int64]),
     "disc_b200_host_linear_destroy": (None, [c_void_p]),
     "disc_b200_quantize": (c_int32, [c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_void_p,
                                      c_int64, c_int64, c_int32, c_int32, c_void_p]),

@@ -217,6 +217,8 @@ disc_b200_host_linear* disc_b200_host_linear_create(int64_t chunk_rows, int64_t 
                                                     int32_t slots);
 int32_t disc_b200_host_linear_run(disc_b200_host_linear* h, const disc_b200_qgemm_args* args, const int8_t* a_host,
                                   void* out_host, int64_t M, void* stream);
+/* Chunks (= kernel launches) a call with M rows is cut into.  Host only. */
+int64_t disc_b200_host_linear_chunks(const disc_b200_host_linear* h, int64_t M);
 void disc_b200_host_linear_destroy(disc_b200_host_linear* h);
 
 /* The small-M path (M <= 128) of disc_b200_qgemm for callers that cannot
