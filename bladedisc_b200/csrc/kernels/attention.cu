@@ -127,7 +127,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttnBlock* 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int head = blockIdx.y;
+  const int head = blockIdx.x;  // heads vary fastest: the heads of the longest items start first and read the same rows
   constexpr uint32_t kTmemCols = 512;
 
   if (threadIdx.x == 0) {
@@ -151,7 +151,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttnBlock* 
 
   // A work item is `nq` consecutive blocks of 128 query rows of one sequence: K and V are fetched once and
   // stay in shared memory, the barriers that cycle per query block are waited on with the block's parity.
-  const AttnBlock blk = blocks[blockIdx.x];
+  const AttnBlock blk = blocks[blockIdx.y];
   const int len = blk.len;
   const int nkb = (len + kKeyBlock - 1) / kKeyBlock;   // 1 .. 4
   const int nq = blk.nq < 1 ? 1 : blk.nq;
@@ -365,7 +365,7 @@ cudaError_t launch_t(const AttentionParams& p, const CUtensorMap& tm, cudaStream
   cudaError_t st = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::kDynamic);
   if (st != cudaSuccess) return st;
   const float scale_log2e = p.scale * 1.4426950408889634f;
-  return launch_dependent(kern, dim3(static_cast<unsigned>(p.num_blocks), static_cast<unsigned>(p.heads)),
+  return launch_dependent(kern, dim3(static_cast<unsigned>(p.heads), static_cast<unsigned>(p.num_blocks)),
                           dim3(kAttnThreads), AttnSmem::kDynamic, stream, tm, p.blocks, p.heads * kAttnHeadDim,
                           scale_log2e, static_cast<OutT*>(p.out), p.ld_out, p.out_scale);
 }
