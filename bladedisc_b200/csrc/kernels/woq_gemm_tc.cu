@@ -77,7 +77,8 @@ struct TcArgs {
   __half* out;
   int M, N, K;
   int64_t ldo;
-  int rows;          // activation rows fetched per block (multiple of 16, <= 128)
+  int rows;          // activation rows fetched per row tile (multiple of 16, <= 128)
+  int row_tiles;     // row tiles (128 rows, one accumulator each) per block: 1, or 2 for long inputs
   int x_stages;      // activation tiles in the ring
   int raw_stages;    // raw weight boxes in the ring
   int kb_per_rank;   // 64-row k blocks per block of the cluster
@@ -138,11 +139,18 @@ __device__ __forceinline__ void store_channel(const uint32_t (&w)[8], __half2 zp
 struct Smem {
   // raw_full, raw_empty [kMaxRawStages]; w_full, w_empty [kWStages]; x_full, x_empty [kMaxXStages]; acc
   static constexpr int kNumBars = 2 * kMaxRawStages + 2 * kWStages + 2 * kMaxXStages + 1;
-  static __host__ __device__ int w_off(int rows, int x_stages) { return ((x_stages - 1) * rows * 128 + kXTileBytes + 1023) & ~1023; }
-  static __host__ __device__ int raw_off(int rows, int x_stages) { return w_off(rows, x_stages) + kWStages * kWBytes; }
-  static int bars(int rows, int x_stages, int raw_stages) { return raw_off(rows, x_stages) + raw_stages * kRawBytes; }
-  static size_t total(int rows, int x_stages, int raw_stages) {
-    return 1024 + bars(rows, x_stages, raw_stages) + kNumBars * 8 + 16;
+  // x_bytes = bytes of one activation stage (row tiles x rows x 128)
+  static __host__ __device__ int w_off(int x_bytes, int row_tiles, int x_stages) {
+    return ((x_stages - 1) * x_bytes + row_tiles * kXTileBytes + 1023) & ~1023;
+  }
+  static __host__ __device__ int raw_off(int x_bytes, int row_tiles, int x_stages) {
+    return w_off(x_bytes, row_tiles, x_stages) + kWStages * kWBytes;
+  }
+  static int bars(int x_bytes, int row_tiles, int x_stages, int raw_stages) {
+    return raw_off(x_bytes, row_tiles, x_stages) + raw_stages * kRawBytes;
+  }
+  static size_t total(int x_bytes, int row_tiles, int x_stages, int raw_stages) {
+    return 1024 + bars(x_bytes, row_tiles, x_stages, raw_stages) + kNumBars * 8 + 16;
   }
 };
 
@@ -152,8 +160,9 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   const uint32_t smem_base = smem_u32(smem);
-  const int x_bytes = a.rows * 128;
-  const int w_off = Smem::w_off(a.rows, a.x_stages);
+  const int tile_bytes = a.row_tiles > 1 ? kXTileBytes : a.rows * 128;  // one row tile of an activation stage
+  const int x_bytes = a.row_tiles * tile_bytes;
+  const int w_off = Smem::w_off(x_bytes, a.row_tiles, a.x_stages);
   const int raw_off = w_off + kWStages * kWBytes;
   const int bars_off = raw_off + a.raw_stages * kRawBytes;
   const uint32_t bar_base = smem_base + bars_off;
@@ -172,7 +181,7 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
   const int csize = static_cast<int>(cluster.num_blocks());
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * kRowsPerBlock;
+  const int m0 = blockIdx.x * kRowsPerBlock * a.row_tiles;
   const int strip = blockIdx.z;
   const int kb_begin = rank * a.kb_per_rank;
   const int kb_count = max(0, min(a.num_kb, kb_begin + a.kb_per_rank) - kb_begin);
@@ -197,7 +206,7 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     tma_prefetch_desc(&tmap_x);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), kStrip);
+    tmem_alloc(smem_u32(tmem_slot), static_cast<uint32_t>(kStrip * a.row_tiles));
     tmem_relinquish();
   }
   tc_fence_before();
@@ -242,7 +251,8 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
       for (int kb = 0; kb < kb_count; ++kb, k += kKB, xr.next(a.x_stages)) {
         if (!mbar_wait(x_empty(xr.stage), xr.phase ^ 1, abort_flag, &g_woq_tc_status, kStatusTimeoutWoq)) break;
         mbar_arrive_expect_tx(x_full(xr.stage), static_cast<uint32_t>(x_bytes));
-        tma_load_2d(smem_base + xr.stage * x_bytes, &tmap_x, x_full(xr.stage), k, m0);
+        for (int t = 0; t < a.row_tiles; ++t)  // rows past M read as zero and still count their bytes
+          tma_load_2d(smem_base + xr.stage * x_bytes + t * tile_bytes, &tmap_x, x_full(xr.stage), k, m0 + t * kRowsPerBlock);
       }
     }
   } else if (warp == 1) {
@@ -261,10 +271,14 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
           }
           tc_fence_after();
           const uint64_t b_desc = make_kmajor_sw64_desc(smem_base + w_off + wr.stage * kWBytes);
+          for (int t = 0; t < a.row_tiles; ++t) {
 #pragma unroll
-          for (int kk = 0; kk < kWK / 16; ++kk) {
-            // 16 k are 32 bytes further in both tiles; the second weight stage starts 32 k into the activation tile
-            umma_f16(tmem_base, a_desc + 4 * hf + 2 * kk, b_desc + 2 * kk, kIdesc, (kb | hf | kk) != 0 ? 1u : 0u);
+            for (int kk = 0; kk < kWK / 16; ++kk) {
+              // 16 k are 32 bytes further in both tiles; the second weight stage starts 32 k into the activation
+              // tile; the second row tile is kXTileBytes further and has its own accumulator
+              umma_f16(tmem_base + static_cast<uint32_t>(t * kStrip), a_desc + (t * kXTileBytes >> 4) + 4 * hf + 2 * kk,
+                       b_desc + 2 * kk, kIdesc, (kb | hf | kk) != 0 ? 1u : 0u);
+            }
           }
           umma_commit(w_empty(wr.stage));
         }
@@ -332,8 +346,10 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     const int q = warp & 3;
     const int half = (warp - 3) >> 2;  // which 128 channels of the strip
     const int r_local = q * 32 + lane;
-    const int m = m0 + r_local;
-    if (q * 32 < a.rows) {  // the same for the whole warp: rows of this quarter exist
+    for (int rt = 0; rt < a.row_tiles; ++rt) {
+    const int m = m0 + rt * kRowsPerBlock + r_local;
+    const uint32_t acc = tmem_base + static_cast<uint32_t>(rt * kStrip);
+    if (q * 32 < a.rows && m0 + rt * kRowsPerBlock < a.M) {  // the same for the whole warp: rows of this quarter exist
       __half* orow = a.out + static_cast<int64_t>(m) * a.ldo;
       for (int it = 0; it < 2; ++it) {
         // column c * 64 + g of the accumulator is channel 4 * g + c: four loads of 16 columns (g0 .. g0 + 15,
@@ -345,7 +361,7 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         if (ok && kb_count > 0) {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
-            tmem_ld_x16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c * 64 + g0), r[c]);
+            tmem_ld_x16(acc + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c * 64 + g0), r[c]);
           tmem_ld_wait();
         } else {
 #pragma unroll
@@ -393,6 +409,7 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         }
       }
     }
+    }  // row tiles
   }
   if (split) {
     // every block adds its slice of the tile over the cluster, in rank order
@@ -422,7 +439,7 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kStrip);
+    tmem_dealloc(tmem_base, static_cast<uint32_t>(kStrip * a.row_tiles));
   }
 }
 
@@ -456,15 +473,19 @@ cudaError_t woq_gemm_tc_launch(const WoqGemmParams& p, cudaStream_t s, const cha
   a.N = static_cast<int>(p.N);
   a.K = static_cast<int>(p.K);
   a.ldo = p.ldo;
-  a.rows = static_cast<int>((std::min<int64_t>(p.M, kRowsPerBlock) + 15) / 16 * 16);
-  a.x_stages = std::max(2, std::min(kMaxXStages, 16384 / (a.rows * 128)));
-  constexpr int kSmemBudget = 224 * 1024;
-  a.raw_stages = std::max(2, std::min(kMaxRawStages, (kSmemBudget - Smem::raw_off(a.rows, a.x_stages)) / kRawBytes));
-  a.raw_stages -= a.raw_stages % kConvGroups;
-  const int64_t m_groups = (p.M + kRowsPerBlock - 1) / kRowsPerBlock;
   const int64_t strips = (p.N + kStrip - 1) / kStrip;
+  // Long inputs: two row tiles per block share every converted weight tile (the conversion, not the tensor core,
+  // bounds the kernel), as long as that still leaves a block for every SM.
+  a.row_tiles = (p.M > kRowsPerBlock && strips * ((p.M + 2 * kRowsPerBlock - 1) / (2 * kRowsPerBlock)) >= sms) ? 2 : 1;
+  a.rows = a.row_tiles > 1 ? kRowsPerBlock : static_cast<int>((std::min<int64_t>(p.M, kRowsPerBlock) + 15) / 16 * 16);
+  const int x_bytes = a.row_tiles * a.rows * 128;
+  a.x_stages = std::max(2, std::min(kMaxXStages, 16384 / x_bytes));
+  constexpr int kSmemBudget = 224 * 1024;
+  a.raw_stages = std::max(2, std::min(kMaxRawStages, (kSmemBudget - Smem::raw_off(x_bytes, a.row_tiles, a.x_stages)) / kRawBytes));
+  a.raw_stages -= a.raw_stages % kConvGroups;
+  const int64_t m_groups = (p.M + kRowsPerBlock * a.row_tiles - 1) / (kRowsPerBlock * a.row_tiles);
   a.num_kb = static_cast<int>((p.K + kKB - 1) / kKB);
-  const size_t smem = Smem::total(a.rows, a.x_stages, a.raw_stages);
+  const size_t smem = Smem::total(x_bytes, a.row_tiles, a.x_stages, a.raw_stages);
   cudaError_t st = cudaFuncSetAttribute(woq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (st != cudaSuccess) return st;
   st = cudaFuncSetAttribute(woq_tc_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 0);
@@ -476,7 +497,7 @@ cudaError_t woq_gemm_tc_launch(const WoqGemmParams& p, cudaStream_t s, const cha
   {
     const int64_t base = strips * m_groups;
     double best = 1e30;
-    for (int sp = 1; sp <= 8 && (sp == 1 || a.num_kb / sp >= 2); ++sp) {
+    for (int sp = 1; sp <= (a.row_tiles > 1 ? 1 : 8) && (sp == 1 || a.num_kb / sp >= 2); ++sp) {
       cudaLaunchConfig_t q{};
       q.gridDim = dim3(static_cast<unsigned>(m_groups), static_cast<unsigned>(sp), static_cast<unsigned>(strips));
       q.blockDim = dim3(kThreads);

@@ -60,12 +60,13 @@ def test_shapes_match_oracle(shape):
 
 @pytest.mark.parametrize("shape", [(5, 256, 128), (16, 1024, 768), (4, 4096, 4096), (16, 4096, 11008), (64, 4096, 4096),
                                    (100, 512, 256), (128, 1024, 384), (129, 2048, 1024), (300, 1000, 144), (7, 72, 16),
-                                   (1, 64, 16), (2048, 512, 512)])
+                                   (1, 64, 16), (2048, 512, 512), (2400, 256, 4096), (2305, 128, 4096)])
 @pytest.mark.parametrize("zp_kind", ["random", "none"])
 def test_tensor_core_path_matches_oracle(shape, zp_kind):
     """The tensor-core kernel, forced: one and several row blocks, k split over clusters of every size the
     planner picks, k and channel tails (k not a multiple of 64, N a multiple of 16 only), with and without
-    zero points and bias."""
+    zero points and bias; the last two shapes are long enough for two row tiles per block (2400 rows end in a
+    block whose second tile is empty, 2305 in one with a single row)."""
     m, k, n = shape
     args = _case(m, k, n, m + k + n, np.float16, with_bias=(zp_kind == "random"), zp_kind=zp_kind)
     _check(_run(*args, path="tensor"), *args, np.float16)
