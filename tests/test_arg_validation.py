@@ -31,6 +31,13 @@ def test_weight_only_qgemm(lib):
     assert lib.disc_b200_weight_only_qgemm(ctypes.byref(a), None) != 0 and "row stride" in _err(lib)
     a.ldw, a.type = 64, 7
     assert lib.disc_b200_weight_only_qgemm(ctypes.byref(a), None) != 0 and "element type" in _err(lib)
+    # the tensor-core kernel, asked for by name, refuses what it cannot take instead of falling back
+    a.type, a.path = L.F32, 2
+    assert lib.disc_b200_weight_only_qgemm(ctypes.byref(a), None) != 0 and "tensor cores" in _err(lib)
+    a.type, a.n, a.ldw, a.ldo = L.F16, 24, 24, 24                                  # N not a multiple of 16
+    assert lib.disc_b200_weight_only_qgemm(ctypes.byref(a), None) != 0 and "tensor cores" in _err(lib)
+    a.n, a.ldw, a.ldo, a.x = 64, 64, 64, 0x1008                                    # activations not 16-byte aligned
+    assert lib.disc_b200_weight_only_qgemm(ctypes.byref(a), None) != 0 and "tensor cores" in _err(lib)
 
 
 def _conv_args():
@@ -127,3 +134,27 @@ def test_weight_only_plan_invariants(lib):
     # K so long that a single row's chunk does not fit
     assert plan(1, 128, 1 << 22)[0] == 2
     assert plan(0, 128, 128)[0] == 1 and plan(1, 128, 128, align=3)[0] == 1
+
+
+def test_attention_work_list():
+    """Host-side work list of the fused attention: items of 1, 2 or 4 query blocks, longest first, every query
+    block of every sequence exactly once."""
+    from bladedisc_b200 import ops
+    lens = [512, 16, 129, 300, 128, 1]
+    for group in (1, 2, 4):
+        b = ops.attention_blocks(lens, heads=12, group=group).tolist()
+        starts = [0, 512, 528, 657, 957, 1085]
+        seen = set()
+        for tok0, n, q0, nq in b:
+            i = starts.index(tok0)
+            assert n == lens[i] and q0 % 128 == 0 and 1 <= nq <= group
+            for blk in range(q0 // 128, q0 // 128 + nq):
+                assert blk * 128 < n and (i, blk) not in seen
+                seen.add((i, blk))
+        assert len(seen) == sum((n + 127) // 128 for n in lens)
+        cost = [n * nq for _, n, _, nq in b]
+        assert cost == sorted(cost, reverse=True)
+    with pytest.raises(ValueError):
+        ops.attention_blocks([513])
+    with pytest.raises(ValueError):
+        ops.attention_blocks([0])
