@@ -776,31 +776,43 @@ def run_decoder(args):
         dec.forward(ctx_ids)
         for _ in range(3):
             dec.forward(nxt)
-        # A decode step is ~40 short launches per layer.  On one GPU it is replayed from a CUDA
-        # graph (captured at one cache position, so every replay does the work of that position).
-        # With several ranks it runs eagerly: collectives are kept out of graph capture here, a
-        # capture that fails on one rank only would leave the ranks in different collectives.
+        # A decode step is ~40 short launches per layer: it is replayed from a CUDA graph (captured at one
+        # cache position, so every replay does the work of that position).  With several ranks the graph
+        # holds the NCCL collectives too.  Nothing of a capture executes, so a capture that fails on one
+        # rank stops nobody; but a replay on some ranks only would leave them waiting in a collective, so
+        # the ranks agree (minimum over ranks of "my capture succeeded") before anyone replays, and all run
+        # eagerly otherwise.  The capture is thread-local: NCCL's helper threads may call the runtime
+        # while this thread captures.
         step, graph = (lambda: dec.forward(nxt)), None
-        if world == 1:
-            side = torch.cuda.Stream(dev)
-            side.wait_stream(torch.cuda.current_stream())
-            try:
-                with torch.cuda.stream(side):
-                    dec.forward(nxt)
-                torch.cuda.synchronize()
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=side):
-                    dec.forward(nxt)
-                step = graph.replay
-            except Exception:
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream())
+        try:
+            with torch.cuda.stream(side):
+                dec.forward(nxt)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+                dec.forward(nxt)
+        except Exception:
+            graph = None
+        torch.cuda.synchronize()
+        if world > 1:
+            agreed = torch.tensor([1 if graph is not None else 0], device=dev, dtype=torch.int32)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            if int(agreed.item()) == 0:
                 graph = None
-                torch.cuda.synchronize()
+        if graph is not None:
+            step = graph.replay
         decode_graph = graph is not None
         for _ in range(3):
             step()
         ms = timed(step, 32)
         decode[b] = ms / 32
+        # the graph goes before the communicator: NCCL does not let go of a communicator while a graph
+        # that captured its collectives exists (`step` is a bound method of the graph)
+        step = None
         del graph
+        torch.cuda.synchronize()
     if ops.kernel_status() != 0:
         raise SystemExit("kernel status non-zero: a bounded wait ran out")
     vals = [dev_ms, e2e_ms] + [decode[b] for b in (1, 8, 64)]
