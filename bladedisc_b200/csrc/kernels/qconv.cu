@@ -106,6 +106,8 @@ __global__ void __launch_bounds__(256) qconv_scatter_kernel(ConvGeometry g, cons
 
 struct Layout {
   int64_t rows, k, kp;
+  bool pointwise;      // 1 x 1 window, unit strides, no padding, dense channels-last input: the input IS the
+                       // [pixels, channels] matrix of the product, nothing is gathered
   bool weight_ready;   // the kernel already is [out_ch, kp] in (ky, kx, c) order
   bool out_direct;     // the output is dense channels-last
   int64_t a_bytes, w_bytes, d_bytes;
@@ -120,7 +122,10 @@ Layout layout_of(const ConvGeometry& g) {
                    g.w_stride[0] == l.k;
   l.out_direct = g.o_stride[1] == 1 && g.o_stride[3] == g.out_ch && g.o_stride[2] == g.out_w * g.out_ch &&
                  g.o_stride[0] == g.out_h * g.out_w * g.out_ch;
-  l.a_bytes = round_up(l.rows * l.kp, 256);
+  l.pointwise = g.k_h == 1 && g.k_w == 1 && g.stride_h == 1 && g.stride_w == 1 && g.pad_top == 0 && g.pad_bottom == 0 &&
+                g.pad_left == 0 && g.pad_right == 0 && l.kp == l.k && g.x_stride[1] == 1 && g.x_stride[3] % kChunk == 0 &&
+                g.x_stride[3] >= g.in_ch && g.x_stride[2] == g.in_w * g.x_stride[3] && g.x_stride[0] == g.in_h * g.x_stride[2];
+  l.a_bytes = round_up(l.rows * l.kp, 256);  // also for pointwise layers: an input that is not 16-byte aligned is gathered
   l.w_bytes = l.weight_ready ? 0 : round_up(g.out_ch * l.kp, 256);
   l.d_bytes = l.out_direct ? 0 : round_up(l.rows * g.out_ch, 256);
   return l;
@@ -164,9 +169,14 @@ cudaError_t qconv_launch(const QConvParams& p, cudaStream_t stream, const char**
   const int vec = g.x_stride[1] == 1 && g.in_ch % kChunk == 0 && g.x_stride[0] % kChunk == 0 &&
                   g.x_stride[2] % kChunk == 0 && g.x_stride[3] % kChunk == 0 &&
                   reinterpret_cast<uintptr_t>(p.x) % kChunk == 0;
-  cudaError_t st = launch_dependent(qconv_gather_kernel, dim3(blocks_for(l.rows * (l.kp / kChunk))), dim3(256), 0, stream,
-                                    g, p.x, a, l.rows, l.kp, vec);
-  if (st != cudaSuccess) return st;
+  // a pointwise convolution over an input that is not 16-byte aligned still goes through the gather
+  const bool direct = l.pointwise && reinterpret_cast<uintptr_t>(p.x) % kChunk == 0;
+  cudaError_t st = cudaSuccess;
+  if (!direct) {
+    st = launch_dependent(qconv_gather_kernel, dim3(blocks_for(l.rows * (l.kp / kChunk))), dim3(256), 0, stream, g, p.x, a,
+                          l.rows, l.kp, vec);
+    if (st != cudaSuccess) return st;
+  }
   const int8_t* wmat = p.w;
   if (!l.weight_ready) {
     st = launch_dependent(qconv_pack_weight_kernel, dim3(blocks_for(g.out_ch * (l.kp / kChunk))), dim3(256), 0, stream, g,
@@ -176,13 +186,13 @@ cudaError_t qconv_launch(const QConvParams& p, cudaStream_t stream, const char**
   }
   QGemmParams q;
   std::memset(&q, 0, sizeof(q));
-  q.a = a;
+  q.a = direct ? p.x : a;
   q.w = wmat;
   q.out = l.out_direct ? p.out : d;
   q.M = l.rows;
   q.N = g.out_ch;
   q.K = l.kp;
-  q.lda = l.kp;
+  q.lda = direct ? g.x_stride[3] : l.kp;
   q.ldw = l.kp;
   q.ldo = g.out_ch;
   q.x_scale = p.x_scale;

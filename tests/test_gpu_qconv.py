@@ -24,6 +24,9 @@ CASES = [
     ("NCHW", (2, 32, 9, 8), (24, 3, 3), [1], [1], "SAME", (), True),            # strided gather, scattered output
     ("NCHW", (2, 25, 8, 8), (8, 3, 3), [1, 1, 2, 2], [1, 1, 2, 2], "VALID", (), False),
     ("NHWC", (4, 28, 28, 64), (128, 3, 3), [1], [1], "SAME", (), True),         # 3136 rows x 576: tensor-core tiles
+    ("NHWC", (4, 28, 28, 64), (128, 1, 1), [1], [1], "VALID", (), True),        # pointwise: the input is the matrix, no gather
+    ("NHWC", (2, 14, 14, 48), (32, 1, 1), [1], [1], "SAME", (), False),         # pointwise, SAME (no padding for a 1 x 1 window)
+    ("NHWC", (2, 14, 14, 64), (32, 1, 1), [1, 2, 2, 1], [1], "VALID", (), True),  # 1 x 1 with stride 2: gathered
 ]
 
 
