@@ -108,6 +108,8 @@ struct Layout {
   int64_t rows, k, kp;
   bool pointwise;      // 1 x 1 window, unit strides, no padding, dense channels-last input: the input IS the
                        // [pixels, channels] matrix of the product, nothing is gathered
+  bool implicit;       // channels-last input with a multiple of 128 channels and a ready kernel matrix: the product
+                       // fetches its activation tiles from the image (TMA im2col mode), nothing is gathered
   bool weight_ready;   // the kernel already is [out_ch, kp] in (ky, kx, c) order
   bool out_direct;     // the output is dense channels-last
   int64_t a_bytes, w_bytes, d_bytes;
@@ -125,6 +127,11 @@ Layout layout_of(const ConvGeometry& g) {
   l.pointwise = g.k_h == 1 && g.k_w == 1 && g.stride_h == 1 && g.stride_w == 1 && g.pad_top == 0 && g.pad_bottom == 0 &&
                 g.pad_left == 0 && g.pad_right == 0 && l.kp == l.k && g.x_stride[1] == 1 && g.x_stride[3] % kChunk == 0 &&
                 g.x_stride[3] >= g.in_ch && g.x_stride[2] == g.in_w * g.x_stride[3] && g.x_stride[0] == g.in_h * g.x_stride[2];
+  l.implicit = !l.pointwise && l.weight_ready && g.in_ch % 128 == 0 && g.x_stride[1] == 1 && g.x_stride[3] % kChunk == 0 &&
+               g.x_stride[2] % kChunk == 0 && g.x_stride[0] % kChunk == 0 && g.stride_h >= 1 && g.stride_h <= 8 &&
+               g.stride_w >= 1 && g.stride_w <= 8 && g.pad_top <= 64 && g.pad_left <= 64 && g.pad_bottom <= 64 &&
+               g.pad_right <= 64 && (g.k_h - 1) * g.dil_h < 128 && (g.k_w - 1) * g.dil_w < 128 &&
+               l.rows < (int64_t{1} << 31) && l.rows >= 128 && g.out_ch >= 16;
   l.a_bytes = round_up(l.rows * l.kp, 256);  // also for pointwise layers: an input that is not 16-byte aligned is gathered
   l.w_bytes = l.weight_ready ? 0 : round_up(g.out_ch * l.kp, 256);
   l.d_bytes = l.out_direct ? 0 : round_up(l.rows * g.out_ch, 256);
@@ -171,8 +178,9 @@ cudaError_t qconv_launch(const QConvParams& p, cudaStream_t stream, const char**
                   reinterpret_cast<uintptr_t>(p.x) % kChunk == 0;
   // a pointwise convolution over an input that is not 16-byte aligned still goes through the gather
   const bool direct = l.pointwise && reinterpret_cast<uintptr_t>(p.x) % kChunk == 0;
+  const bool implicit = l.implicit && reinterpret_cast<uintptr_t>(p.x) % kChunk == 0;
   cudaError_t st = cudaSuccess;
-  if (!direct) {
+  if (!direct && !implicit) {
     st = launch_dependent(qconv_gather_kernel, dim3(blocks_for(l.rows * (l.kp / kChunk))), dim3(256), 0, stream, g, p.x, a,
                           l.rows, l.kp, vec);
     if (st != cudaSuccess) return st;
@@ -186,8 +194,32 @@ cudaError_t qconv_launch(const QConvParams& p, cudaStream_t stream, const char**
   }
   QGemmParams q;
   std::memset(&q, 0, sizeof(q));
-  q.a = direct ? p.x : a;
+  q.a = (direct || implicit) ? p.x : a;
   q.w = wmat;
+  Im2colA ic{};
+  if (implicit) {
+    ic.x = p.x;
+    ic.batch = g.batch;
+    ic.in_h = g.in_h;
+    ic.in_w = g.in_w;
+    ic.in_ch = g.in_ch;
+    ic.stride_n = g.x_stride[0];
+    ic.stride_h = g.x_stride[2];
+    ic.stride_w = g.x_stride[3];
+    ic.out_h = static_cast<int>(g.out_h);
+    ic.out_w = static_cast<int>(g.out_w);
+    ic.k_h = static_cast<int>(g.k_h);
+    ic.k_w = static_cast<int>(g.k_w);
+    ic.conv_stride_h = static_cast<int>(g.stride_h);
+    ic.conv_stride_w = static_cast<int>(g.stride_w);
+    ic.dil_h = static_cast<int>(g.dil_h);
+    ic.dil_w = static_cast<int>(g.dil_w);
+    ic.pad_top = static_cast<int>(g.pad_top);
+    ic.pad_left = static_cast<int>(g.pad_left);
+    ic.pad_bottom = static_cast<int>(g.pad_bottom);
+    ic.pad_right = static_cast<int>(g.pad_right);
+    q.im2col = &ic;
+  }
   q.out = l.out_direct ? p.out : d;
   q.M = l.rows;
   q.N = g.out_ch;

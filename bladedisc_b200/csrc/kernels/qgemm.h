@@ -33,6 +33,19 @@ enum QGemmPath : int {
 //                                           which differs from the quotient by at most
 //                                           one int8 level, at rounding ties only
 //   out = int8: sat(rne(v)) | f16 | f32 ; kOutI32 stores acc unchanged.
+// Activation operand read straight from a channels-last int8 image (implicit GEMM of a convolution): row m of
+// the product is the output pixel (n, oy, ox), its K index ((ky * k_w + kx) * in_ch + c).  The tiles are
+// fetched by TMA in im2col mode, so the [pixels, k_h * k_w * in_ch] matrix never exists.  in_ch must be a
+// multiple of 128 (one K block = 128 channels of one window position).
+struct Im2colA {
+  const int8_t* x;                        // element strides below; the channel stride is 1
+  int64_t batch, in_h, in_w, in_ch;
+  int64_t stride_n, stride_h, stride_w;   // of x, in elements (= bytes), multiples of 16
+  int out_h, out_w, k_h, k_w;
+  int conv_stride_h, conv_stride_w, dil_h, dil_w;
+  int pad_top, pad_left, pad_bottom, pad_right;
+};
+
 struct QGemmParams {
   const int8_t* a;
   const int8_t* w;
@@ -73,6 +86,9 @@ struct QGemmParams {
   // launch) and wait for it only before they touch activations, scales or the
   // output.  0 = assume nothing.
   int weights_static;
+  // Non-null: `a` is not read; the activation tiles come from this image (tiled kernel only; K must equal
+  // k_h * k_w * in_ch and M batch * out_h * out_w).
+  const Im2colA* im2col = nullptr;
 };
 
 // Bytes of zeroed scratch the small-M path may need for a given problem.

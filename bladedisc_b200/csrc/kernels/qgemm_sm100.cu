@@ -53,6 +53,16 @@ struct EpiParams {
 
 // Where K block `kb` of the two operands starts when the activation is stored
 // as column slabs (kb_per_slab == 0: plain row-major, x = 128 * kb for both).
+// Geometry the producer of the tiled kernel needs when the activation tiles are fetched in im2col mode
+// (enabled = 0: plain 2-D tiles).
+struct Im2colDev {
+  int enabled;
+  int pixels_per_image;  // out_h * out_w
+  int out_w;
+  int k_w, cblks;        // window width; 128-channel blocks per window position
+  int stride_h, stride_w, dil_h, dil_w, pad_top, pad_left;
+};
+
 struct SlabA {
   int kb_per_slab;  // K blocks per slab = ceil(slab_cols / 128)
   int slab_rows;    // rows of the activation tensor map between two slabs
@@ -458,7 +468,7 @@ template <int BN, int STAGES, typename OutT>
 __global__ void __launch_bounds__(kTiledThreads, 1)
 qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
                    const __grid_constant__ CUtensorMap tmap_w, EpiParams ep, int num_kb, int tiles_m,
-                   int tiles_n, int vec_ok, SlabA slab) {
+                   int tiles_n, int vec_ok, SlabA slab, Im2colDev ic) {
   using L = TiledSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -516,15 +526,39 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m_blk = tile / tiles_n;
         const int n_blk = tile % tiles_n;
+        // im2col mode: base position of the tile's first output pixel in the image, and the window
+        // position / channel block of the K block, kept by increments
+        int img = 0, w_base = 0, h_base = 0, ky = 0, kx = 0, cb = 0;
+        if (ic.enabled) {
+          const int m0 = m_blk * kTileM;
+          img = m0 / ic.pixels_per_image;
+          const int rem = m0 - img * ic.pixels_per_image;
+          const int oy = rem / ic.out_w;
+          h_base = oy * ic.stride_h - ic.pad_top;
+          w_base = (rem - oy * ic.out_w) * ic.stride_w - ic.pad_left;
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, &g_kernel_status,
                          kStatusTimeoutEmpty);
           if (!ok) break;
           mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
           const uint32_t a_dst = smem_base + stage * L::kStageBytes;
+          if (ic.enabled) {
+            tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), cb * 128, w_base, h_base, img,
+                               static_cast<uint16_t>(kx * ic.dil_w), static_cast<uint16_t>(ky * ic.dil_h));
+            tma_load_2d(a_dst + L::kABytes, &tmap_w, full_bar(stage), kb * 128, n_blk * BN);
+            if (++cb == ic.cblks) {
+              cb = 0;
+              if (++kx == ic.k_w) {
+                kx = 0;
+                ++ky;
+              }
+            }
+          } else {
           const KCoord kc = k_coord(slab, kb);
           tma_load_2d(a_dst, &tmap_a, full_bar(stage), kc.ax, kc.ay + m_blk * kTileM);
           tma_load_2d(a_dst + L::kABytes, &tmap_w, full_bar(stage), kc.wx, n_blk * BN);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -957,6 +991,26 @@ bool make_tmap(CUtensorMap* tm, const int8_t* base, int64_t rows, int64_t K, int
   return r == CUDA_SUCCESS;
 }
 
+// int8 image {C, W, H, N} (channels-last), fetched in im2col mode: 128 output positions x 128 channels per
+// load, 128-byte swizzle (the tile the MMA's K-major descriptor expects).  The bounding box of the base
+// positions starts `pad` before the image and ends where the last window still begins.
+bool make_im2col_tmap(CUtensorMap* tm, const Im2colA& g) {
+  EncodeIm2colFn fn = tensor_map_encode_im2col_fn();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(g.in_ch), static_cast<cuuint64_t>(g.in_w),
+                        static_cast<cuuint64_t>(g.in_h), static_cast<cuuint64_t>(g.batch)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(g.stride_w), static_cast<cuuint64_t>(g.stride_h),
+                           static_cast<cuuint64_t>(g.stride_n)};
+  int lower[2] = {-g.pad_left, -g.pad_top};
+  int upper[2] = {g.pad_right - (g.k_w - 1) * g.dil_w, g.pad_bottom - (g.k_h - 1) * g.dil_h};
+  cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(g.conv_stride_w), static_cast<cuuint32_t>(g.conv_stride_h), 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(g.x), dims, strides, lower, upper,
+                  /*channelsPerPixel=*/128, /*pixelsPerColumn=*/static_cast<cuuint32_t>(kTileM), estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 int sm_count() { return device_sm_count(); }
 
 EpiParams make_epi(const QGemmParams& p) {
@@ -1053,7 +1107,29 @@ template <typename OutT, int BN, int STAGES>
 cudaError_t launch_tiled_t(const QGemmParams& p, cudaStream_t stream, const char** err) {
   using L = TiledSmem<BN, STAGES>;
   CUtensorMap ta, tw;
-  if (!make_a_tmap(&ta, p, kTileM) || !make_tmap(&tw, p.w, p.N, p.K, p.ldw, BN)) {
+  Im2colDev ic{};
+  if (p.im2col) {
+    if (!make_im2col_tmap(&ta, *p.im2col)) {
+      if (err) *err = "cuTensorMapEncodeIm2col failed or unavailable";
+      return cudaErrorInvalidValue;
+    }
+    const Im2colA& g = *p.im2col;
+    ic.enabled = 1;
+    ic.pixels_per_image = g.out_h * g.out_w;
+    ic.out_w = g.out_w;
+    ic.k_w = g.k_w;
+    ic.cblks = static_cast<int>(g.in_ch / 128);
+    ic.stride_h = g.conv_stride_h;
+    ic.stride_w = g.conv_stride_w;
+    ic.dil_h = g.dil_h;
+    ic.dil_w = g.dil_w;
+    ic.pad_top = g.pad_top;
+    ic.pad_left = g.pad_left;
+  } else if (!make_a_tmap(&ta, p, kTileM)) {
+    if (err) *err = "cuTensorMapEncodeTiled failed";
+    return cudaErrorInvalidValue;
+  }
+  if (!make_tmap(&tw, p.w, p.N, p.K, p.ldw, BN)) {
     if (err) *err = "cuTensorMapEncodeTiled failed";
     return cudaErrorInvalidValue;
   }
@@ -1069,7 +1145,7 @@ cudaError_t launch_tiled_t(const QGemmParams& p, cudaStream_t stream, const char
   const int eb = out_elem_bytes(p.out_dtype);
   const int vec_ok = ((p.ldo * eb) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
   return launch_dependent(kern, dim3(grid), dim3(kTiledThreads), L::kDynamic, stream, ta, tw, make_epi(p), num_kb,
-                          tiles_m, tiles_n, vec_ok, slab_of(p));
+                          tiles_m, tiles_n, vec_ok, slab_of(p), ic);
 }
 
 template <typename OutT>
@@ -1303,6 +1379,7 @@ static bool pair_mode_ok(const QGemmParams& p) {
 }
 
 int qgemm_choose_path(const QGemmParams& p) {
+  if (p.im2col) return kPathTiled;  // the only kernel whose producer fetches image tiles
   if (!tma_ok(p)) return kPathSimt;
   if (p.path == kPathSimt) return kPathSimt;
   if (p.path == kPathSmallM && p.M <= 128 && p.a_slabs <= 1) return kPathSmallM;
