@@ -8,10 +8,16 @@
 // and ral_pdll_qconv2d (per-channel weight scales,
 // tao_compiler/mlir/ral/context/common_context_impl_quantization.cc:363-607).
 //
-// Here: the receptive fields are gathered into a row-major int8 matrix
-// [batch * out_h * out_w, k_h * k_w * in_ch (padded to 16)], the kernel is used as
-// (or packed into) [out_ch, the same K], and the product with its requantizing
-// epilogue is the quantized linear of qgemm.h (tcgen05 int8 tensor-core path).
+// Here the product with its requantizing epilogue is the quantized linear of qgemm.h
+// (tcgen05 int8 tensor-core path) over [batch * out_h * out_w, k_h * k_w * in_ch]:
+//   * channels-last input, in_ch a multiple of 128, kernel already [out, y, x, in]:
+//     implicit GEMM, the linear's producer fetches 128 positions x 128 channels per
+//     K block from the image with TMA in im2col mode (padding and strides live in the
+//     tensor map, positions outside the image read as zero);
+//   * 1 x 1 window, unit strides, no padding, dense channels-last input: the input is
+//     the matrix;
+//   * otherwise the receptive fields are gathered into a row-major int8 matrix (K
+//     padded to 16) and the kernel is used as, or packed into, [out_ch, the same K].
 // Channels-last output is written by the GEMM itself; other layouts through a
 // scatter pass.
 #pragma once

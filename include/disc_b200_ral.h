@@ -369,10 +369,14 @@ int32_t disc_b200_weight_only_qgemm_plan(int64_t m, int64_t n, int64_t k, int32_
  * reference's order (stream_executor_based_impl.cc:1127-1152): input (batch, channel,
  * y, x dims), kernel (in-feature, out-feature, y, x dims), output (batch, channel, y,
  * x dims), strides (y, x), dilations (y, x); `padding` = (top, bottom, left, right).
- * One group.  Scales are device pointers.  The receptive fields are gathered into
- * `workspace` (device, 256-byte aligned, at least disc_b200_qconv2d_workspace_bytes)
- * and multiplied on the int8 tensor cores by the quantized linear; splitk_ws is that
- * linear's scratch (see disc_b200_qgemm_args), needed when batch * out_h * out_w <= 128. */
+ * One group.  Scales are device pointers.  The product runs on the int8 tensor cores as
+ * the quantized linear.  Channels-last inputs with a multiple of 128 channels (and a kernel
+ * already [out, y, x, in]) are read in place: the linear fetches its activation tiles from
+ * the image with TMA in im2col mode; 1 x 1 windows with unit strides over dense
+ * channels-last inputs are the linear itself.  Otherwise the receptive fields are gathered
+ * into `workspace` first.  `workspace` (device, 256-byte aligned, at least
+ * disc_b200_qconv2d_workspace_bytes) is required in every case; splitk_ws is the linear's
+ * scratch (see disc_b200_qgemm_args), needed when batch * out_h * out_w <= 128. */
 typedef struct disc_b200_qconv2d_args {
   const int8_t* x;
   const int8_t* w;
