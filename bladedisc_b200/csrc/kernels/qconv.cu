@@ -108,7 +108,7 @@ struct Layout {
   int64_t rows, k, kp;
   bool pointwise;      // 1 x 1 window, unit strides, no padding, dense channels-last input: the input IS the
                        // [pixels, channels] matrix of the product, nothing is gathered
-  bool implicit;       // channels-last input with a multiple of 128 channels and a ready kernel matrix: the product
+  bool implicit;       // channels-last input with a multiple of 64 channels and a ready kernel matrix: the product
                        // fetches its activation tiles from the image (TMA im2col mode), nothing is gathered
   bool weight_ready;   // the kernel already is [out_ch, kp] in (ky, kx, c) order
   bool out_direct;     // the output is dense channels-last
@@ -127,7 +127,7 @@ Layout layout_of(const ConvGeometry& g) {
   l.pointwise = g.k_h == 1 && g.k_w == 1 && g.stride_h == 1 && g.stride_w == 1 && g.pad_top == 0 && g.pad_bottom == 0 &&
                 g.pad_left == 0 && g.pad_right == 0 && l.kp == l.k && g.x_stride[1] == 1 && g.x_stride[3] % kChunk == 0 &&
                 g.x_stride[3] >= g.in_ch && g.x_stride[2] == g.in_w * g.x_stride[3] && g.x_stride[0] == g.in_h * g.x_stride[2];
-  l.implicit = !l.pointwise && l.weight_ready && g.in_ch % 128 == 0 && g.x_stride[1] == 1 && g.x_stride[3] % kChunk == 0 &&
+  l.implicit = !l.pointwise && l.weight_ready && g.in_ch % 64 == 0 && g.x_stride[1] == 1 && g.x_stride[3] % kChunk == 0 &&
                g.x_stride[2] % kChunk == 0 && g.x_stride[0] % kChunk == 0 && g.stride_h >= 1 && g.stride_h <= 8 &&
                g.stride_w >= 1 && g.stride_w <= 8 && g.pad_top <= 64 && g.pad_left <= 64 && g.pad_bottom <= 64 &&
                g.pad_right <= 64 && (g.k_h - 1) * g.dil_h < 128 && (g.k_w - 1) * g.dil_w < 128 &&

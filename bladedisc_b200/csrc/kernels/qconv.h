@@ -10,8 +10,8 @@
 //
 // Here the product with its requantizing epilogue is the quantized linear of qgemm.h
 // (tcgen05 int8 tensor-core path) over [batch * out_h * out_w, k_h * k_w * in_ch]:
-//   * channels-last input, in_ch a multiple of 128, kernel already [out, y, x, in]:
-//     implicit GEMM, the linear's producer fetches 128 positions x 128 channels per
+//   * channels-last input, in_ch a multiple of 64, kernel already [out, y, x, in]:
+//     implicit GEMM, the linear's producer fetches 128 positions x 128 (or 64) channels per
 //     K block from the image with TMA in im2col mode (padding and strides live in the
 //     tensor map, positions outside the image read as zero);
 //   * 1 x 1 window, unit strides, no padding, dense channels-last input: the input is

@@ -36,7 +36,7 @@ enum QGemmPath : int {
 // Activation operand read straight from a channels-last int8 image (implicit GEMM of a convolution): row m of
 // the product is the output pixel (n, oy, ox), its K index ((ky * k_w + kx) * in_ch + c).  The tiles are
 // fetched by TMA in im2col mode, so the [pixels, k_h * k_w * in_ch] matrix never exists.  in_ch must be a
-// multiple of 128 (one K block = 128 channels of one window position).
+// multiple of 64: a K block is 128 channels of one window position, or 64 when in_ch is not a multiple of 128.
 struct Im2colA {
   const int8_t* x;                        // element strides below; the channel stride is 1
   int64_t batch, in_h, in_w, in_ch;

@@ -59,7 +59,8 @@ struct Im2colDev {
   int enabled;
   int pixels_per_image;  // out_h * out_w
   int out_w;
-  int k_w, cblks;        // window width; 128-channel blocks per window position
+  int k_w, cblks;        // window width; channel blocks per window position
+  int kb_bytes;          // channels (= bytes) per K block: 128, or 64 with 64-byte-swizzled tiles and two MMAs per block
   int stride_h, stride_w, dil_h, dil_w, pad_top, pad_left;
 };
 
@@ -541,12 +542,12 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, &g_kernel_status,
                          kStatusTimeoutEmpty);
           if (!ok) break;
-          mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+          mbar_arrive_expect_tx(full_bar(stage), ic.enabled ? (kTileM + BN) * ic.kb_bytes : L::kStageBytes);
           const uint32_t a_dst = smem_base + stage * L::kStageBytes;
           if (ic.enabled) {
-            tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), cb * 128, w_base, h_base, img,
+            tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), cb * ic.kb_bytes, w_base, h_base, img,
                                static_cast<uint16_t>(kx * ic.dil_w), static_cast<uint16_t>(ky * ic.dil_h));
-            tma_load_2d(a_dst + L::kABytes, &tmap_w, full_bar(stage), kb * 128, n_blk * BN);
+            tma_load_2d(a_dst + L::kABytes, &tmap_w, full_bar(stage), kb * ic.kb_bytes, n_blk * BN);
             if (++cb == ic.cblks) {
               cb = 0;
               if (++kx == ic.k_w) {
@@ -569,6 +570,11 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else if (warp == kMmaWarp) {
     if (lane == 0) {
       constexpr uint32_t idesc = make_i8_idesc(kTileM, BN);
+      // everything of the shared-memory descriptors but the address.  Image tiles of 64 channels have rows of
+      // 64 bytes with 64-byte swizzle and take two MMAs per K block; all other tiles 128 bytes and four.
+      const bool half = ic.enabled && ic.kb_bytes == 64;
+      const uint64_t desc_hi = (half ? make_kmajor_sw64_desc(0) : make_kmajor_sw128_desc(0));
+      const int mmas_per_kb = half ? 2 : kTileKBytes / kMmaK;
       int stage = 0;
       uint32_t phase = 0;
       int acc_buf = 0;
@@ -585,11 +591,11 @@ qgemm_tiled_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_addr = smem_base + stage * L::kStageBytes;
-          const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
-          const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + L::kABytes);
+          const uint64_t a_desc = desc_hi | static_cast<uint64_t>((a_addr & 0x3FFFF) >> 4);
+          const uint64_t b_desc = desc_hi | static_cast<uint64_t>(((a_addr + L::kABytes) & 0x3FFFF) >> 4);
 #pragma unroll
           for (int k = 0; k < kTileKBytes / kMmaK; ++k) {
-            umma_i8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (k < mmas_per_kb) umma_i8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));
           if (++stage == STAGES) {
@@ -976,25 +982,26 @@ __global__ void qgemm_simt_kernel(const int8_t* __restrict__ a, const int8_t* __
 // ------------------------------------------------------------------- host
 EncodeTiledFn get_encode_fn() { return tensor_map_encode_fn(); }
 
-// int8 [rows, K] row-major (row stride ld bytes), box = box_rows x 128 bytes, 128B swizzle.
+// int8 [rows, K] row-major (row stride ld bytes), box = box_rows x 128 bytes, 128B swizzle (or 64 and 64).
 bool make_tmap(CUtensorMap* tm, const int8_t* base, int64_t rows, int64_t K, int64_t ld,
-               int box_rows) {
+               int box_rows, int box_bytes = kTileKBytes) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld)};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(kTileKBytes), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_bytes), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(base), dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  box_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
-// int8 image {C, W, H, N} (channels-last), fetched in im2col mode: 128 output positions x 128 channels per
-// load, 128-byte swizzle (the tile the MMA's K-major descriptor expects).  The bounding box of the base
-// positions starts `pad` before the image and ends where the last window still begins.
-bool make_im2col_tmap(CUtensorMap* tm, const Im2colA& g) {
+// int8 image {C, W, H, N} (channels-last), fetched in im2col mode: 128 output positions x `kb_bytes` (128 or
+// 64) channels per load, swizzled over the row length (the tile the MMA's K-major descriptor expects).  The
+// bounding box of the base positions starts `pad` before the image and ends where the last window still begins.
+bool make_im2col_tmap(CUtensorMap* tm, const Im2colA& g, int kb_bytes) {
   EncodeIm2colFn fn = tensor_map_encode_im2col_fn();
   if (!fn) return false;
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(g.in_ch), static_cast<cuuint64_t>(g.in_w),
@@ -1005,8 +1012,9 @@ bool make_im2col_tmap(CUtensorMap* tm, const Im2colA& g) {
   int upper[2] = {g.pad_right - (g.k_w - 1) * g.dil_w, g.pad_bottom - (g.k_h - 1) * g.dil_h};
   cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(g.conv_stride_w), static_cast<cuuint32_t>(g.conv_stride_h), 1};
   CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(g.x), dims, strides, lower, upper,
-                  /*channelsPerPixel=*/128, /*pixelsPerColumn=*/static_cast<cuuint32_t>(kTileM), estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  /*channelsPerPixel=*/static_cast<cuuint32_t>(kb_bytes), /*pixelsPerColumn=*/static_cast<cuuint32_t>(kTileM),
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  kb_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -1108,8 +1116,9 @@ cudaError_t launch_tiled_t(const QGemmParams& p, cudaStream_t stream, const char
   using L = TiledSmem<BN, STAGES>;
   CUtensorMap ta, tw;
   Im2colDev ic{};
+  const int kb_bytes = (p.im2col && p.im2col->in_ch % 128 != 0) ? 64 : 128;
   if (p.im2col) {
-    if (!make_im2col_tmap(&ta, *p.im2col)) {
+    if (!make_im2col_tmap(&ta, *p.im2col, kb_bytes)) {
       if (err) *err = "cuTensorMapEncodeIm2col failed or unavailable";
       return cudaErrorInvalidValue;
     }
@@ -1118,7 +1127,8 @@ cudaError_t launch_tiled_t(const QGemmParams& p, cudaStream_t stream, const char
     ic.pixels_per_image = g.out_h * g.out_w;
     ic.out_w = g.out_w;
     ic.k_w = g.k_w;
-    ic.cblks = static_cast<int>(g.in_ch / 128);
+    ic.cblks = static_cast<int>(g.in_ch / kb_bytes);
+    ic.kb_bytes = kb_bytes;
     ic.stride_h = g.conv_stride_h;
     ic.stride_w = g.conv_stride_w;
     ic.dil_h = g.dil_h;
@@ -1129,7 +1139,7 @@ cudaError_t launch_tiled_t(const QGemmParams& p, cudaStream_t stream, const char
     if (err) *err = "cuTensorMapEncodeTiled failed";
     return cudaErrorInvalidValue;
   }
-  if (!make_tmap(&tw, p.w, p.N, p.K, p.ldw, BN)) {
+  if (!make_tmap(&tw, p.w, p.N, p.K, p.ldw, BN, kb_bytes)) {
     if (err) *err = "cuTensorMapEncodeTiled failed";
     return cudaErrorInvalidValue;
   }
@@ -1139,7 +1149,7 @@ cudaError_t launch_tiled_t(const QGemmParams& p, cudaStream_t stream, const char
   if (st != cudaSuccess) return st;
   const int tiles_m = static_cast<int>((p.M + kTileM - 1) / kTileM);
   const int tiles_n = static_cast<int>((p.N + BN - 1) / BN);
-  const int num_kb = num_k_blocks(p);
+  const int num_kb = p.im2col ? static_cast<int>(p.K / kb_bytes) : num_k_blocks(p);
   const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
   const int eb = out_elem_bytes(p.out_dtype);

@@ -343,6 +343,17 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
   return d;
 }
 
+// K-major operand tile with 64-byte rows and 64-byte swizzle: 8-row groups are 512 bytes apart.
+__device__ __forceinline__ uint64_t make_kmajor_sw64_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(512 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(4) << 61;
+  return d;
+}
+
 // Instruction descriptor for kind::i8: D = s32 (bits [4,6) = 2), A and B signed
 // 8-bit (bits [7,10) and [10,13) = 1), both K-major, N >> 3 at [17,23), M >> 4 at [24,29).
 __host__ __device__ constexpr uint32_t make_i8_idesc(int mma_m, int mma_n) {

@@ -102,17 +102,6 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
 constexpr uint32_t kIdesc = (1u << 4) | (static_cast<uint32_t>(kStrip >> 3) << 17) |
                             (static_cast<uint32_t>(kRowsPerBlock >> 4) << 24);
 
-// K-major operand tile with 64-byte rows and 64-byte swizzle: 8-row groups are 512 bytes apart.
-__device__ __forceinline__ uint64_t make_kmajor_sw64_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
-  d |= static_cast<uint64_t>(1) << 16;
-  d |= static_cast<uint64_t>(512 >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(4) << 61;
-  return d;
-}
-
 // Two bytes (byte C of each word) -> the fp16 pair (1024 + a, 1024 + b) - zp2.
 template <int C>
 __device__ __forceinline__ uint32_t pair_to_half2(uint32_t wa, uint32_t wb, __half2 zp2) {

@@ -370,7 +370,7 @@ int32_t disc_b200_weight_only_qgemm_plan(int64_t m, int64_t n, int64_t k, int32_
  * y, x dims), kernel (in-feature, out-feature, y, x dims), output (batch, channel, y,
  * x dims), strides (y, x), dilations (y, x); `padding` = (top, bottom, left, right).
  * One group.  Scales are device pointers.  The product runs on the int8 tensor cores as
- * the quantized linear.  Channels-last inputs with a multiple of 128 channels (and a kernel
+ * the quantized linear.  Channels-last inputs with a multiple of 64 channels (and a kernel
  * already [out, y, x, in]) are read in place: the linear fetches its activation tiles from
  * the image with TMA in im2col mode; 1 x 1 windows with unit strides over dense
  * channels-last inputs are the linear itself.  Otherwise the receptive fields are gathered

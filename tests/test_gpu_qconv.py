@@ -27,12 +27,14 @@ CASES = [
     ("NHWC", (4, 28, 28, 64), (128, 1, 1), [1], [1], "VALID", (), True),        # pointwise: the input is the matrix, no gather
     ("NHWC", (2, 14, 14, 48), (32, 1, 1), [1], [1], "SAME", (), False),         # pointwise, SAME (no padding for a 1 x 1 window)
     ("NHWC", (2, 14, 14, 64), (32, 1, 1), [1, 2, 2, 1], [1], "VALID", (), True),  # 1 x 1 with stride 2: gathered
-    # multiples of 128 channels: the linear fetches its tiles from the image (TMA im2col), no gathered matrix
+    # multiples of 64 channels: the linear fetches its tiles from the image (TMA im2col), no gathered matrix
     ("NHWC", (2, 14, 14, 128), (32, 3, 3), [1], [1], "SAME", (), True),          # 392 rows: the last tile runs past the batch
     ("NHWC", (4, 16, 16, 256), (64, 3, 3), [1, 2, 2, 1], [1], "SAME", (), True),  # stride 2, two channel blocks per position
     ("NHWC", (2, 20, 20, 128), (16, 3, 3), [1], [1, 2, 2, 1], "VALID", (), False),  # dilation 2
     ("NHWC", (3, 12, 10, 128), (48, 3, 2), [1, 2, 1, 1], [1], "EXPLICIT", (2, 1, 0, 1), True),  # uneven padding and strides
     ("NHWC", (2, 16, 16, 128), (32, 1, 1), [1, 2, 2, 1], [1], "VALID", (), True),  # 1 x 1 with stride 2, from the image
+    ("NHWC", (2, 14, 14, 64), (32, 3, 3), [1], [1], "SAME", (), True),           # 64 channels: K blocks of 64 bytes
+    ("NHWC", (2, 13, 11, 192), (24, 3, 3), [1, 2, 2, 1], [1], "SAME", (), False),  # 192 channels: three 64-byte blocks per position
 ]
 
 
