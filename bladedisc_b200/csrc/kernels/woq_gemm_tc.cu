@@ -464,8 +464,13 @@ cudaError_t woq_gemm_tc_launch(const WoqGemmParams& p, cudaStream_t s, const cha
   a.ldo = p.ldo;
   const int64_t strips = (p.N + kStrip - 1) / kStrip;
   // Long inputs: two row tiles per block share every converted weight tile (the conversion, not the tensor core,
-  // bounds the kernel), as long as that still leaves a block for every SM.
-  a.row_tiles = (p.M > kRowsPerBlock && strips * ((p.M + 2 * kRowsPerBlock - 1) / (2 * kRowsPerBlock)) >= sms) ? 2 : 1;
+  // bounds the kernel).  A block with two tiles takes about 1.5 times as long (measured at 2048 rows), so it
+  // pays when it saves enough rounds of blocks over the SMs.
+  {
+    const int64_t rounds1 = (strips * ((p.M + kRowsPerBlock - 1) / kRowsPerBlock) + sms - 1) / sms;
+    const int64_t rounds2 = (strips * ((p.M + 2 * kRowsPerBlock - 1) / (2 * kRowsPerBlock)) + sms - 1) / sms;
+    a.row_tiles = (p.M > kRowsPerBlock && 3 * rounds2 <= 2 * rounds1) ? 2 : 1;
+  }
   a.rows = a.row_tiles > 1 ? kRowsPerBlock : static_cast<int>((std::min<int64_t>(p.M, kRowsPerBlock) + 15) / 16 * 16);
   const int x_bytes = a.row_tiles * a.rows * 128;
   a.x_stages = std::max(2, std::min(kMaxXStages, 16384 / x_bytes));
