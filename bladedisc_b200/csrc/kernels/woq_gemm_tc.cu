@@ -39,6 +39,9 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <map>
+#include <mutex>
+#include <tuple>
 
 #include "device_info.h"
 #include "rowops.h"
@@ -434,6 +437,29 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
 
 }  // namespace
 
+namespace {
+// Clusters of `sp` blocks with `smem` bytes the current device holds at once; asked of the runtime once per
+// (device, size, shared memory) and remembered (the query costs microseconds, a decode step has hundreds of calls).
+int max_active_clusters(const cudaLaunchConfig_t& q, int sp, size_t smem) {
+  static std::mutex mu;
+  static std::map<std::tuple<int, int, size_t>, int> cache;
+  const auto key = std::make_tuple(current_device_ordinal(), sp, smem);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+  }
+  int active = 0;
+  if (cudaOccupancyMaxActiveClusters(&active, woq_tc_kernel, &q) != cudaSuccess || active < 1) {
+    (void)cudaGetLastError();
+    active = 0;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  cache[key] = active;
+  return active;
+}
+}  // namespace
+
 bool woq_gemm_tc_usable(const WoqGemmParams& p) {
   return p.type == kF16 && p.K >= kKB && p.N % 16 == 0 && p.ldw % 16 == 0 && p.ldx % 8 == 0 && p.ldo % 8 == 0 &&
          (reinterpret_cast<uintptr_t>(p.w) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 &&
@@ -503,9 +529,9 @@ cudaError_t woq_gemm_tc_launch(const WoqGemmParams& p, cudaStream_t s, const cha
       qa[0].val.clusterDim.z = 1;
       q.attrs = qa;
       q.numAttrs = 1;
-      int active = 0;
-      if (cudaOccupancyMaxActiveClusters(&active, woq_tc_kernel, &q) != cudaSuccess || active < 1) {
-        (void)cudaGetLastError();
+      const int active_or_0 = max_active_clusters(q, sp, smem);
+      int active = active_or_0;
+      if (active < 1) {
         if (sp == 1) active = sms; else continue;
       }
       const int64_t waves = (base + active - 1) / active;
