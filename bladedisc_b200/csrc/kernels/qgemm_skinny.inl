@@ -17,12 +17,22 @@
 // Warp roles as in the small-M kernel: warp 0 TMA, warp 1 TMEM + MMA, warps
 // 2..17 epilogue (TMEM lane quadrant = warp & 3 = 32 rows; the four warps of a
 // quadrant interleave 16-column chunks).
+//
+// One row tile with long K and few channels (the launcher's rule): gridDim.z
+// blocks form a thread-block cluster along z and share a tile of 128 channels,
+// each walking 1/z of the K blocks.  Every block writes its partial int32 tile
+// from TMEM to its own shared memory (the stage ring is free by then), the
+// cluster meets, and block r finishes the r-th slice of the tile: it adds the
+// partial sums of all blocks in rank order through distributed shared memory,
+// runs the epilogue on them and stores.  A second cluster barrier keeps every
+// block's tile alive until all have read it.
 
 constexpr int kSkinnyStageRegion = 184 * 1024;  // a short activation tile is read up to 16 KB past its end
 constexpr int kSkinnyBarOffset = 200 * 1024;
 constexpr int kSkinnyScaleOffset = kSkinnyBarOffset + 256;
-constexpr int kSkinnyDynamic = kSkinnyScaleOffset + 2 * 128 * 4 + 1024;
 constexpr int kSkinnyMaxBN = 128;
+constexpr int kSkinnyDynamic = kSkinnyScaleOffset + 2 * kSkinnyMaxBN * 4 + 1024;
+constexpr int kSkinnyTilePad = 4;  // int32 words added to a row of the partial tile: 16-byte stores of a warp spread over the banks
 
 template <typename OutT, int ACT, int DIV, bool RS>
 __device__ __forceinline__ void skinny_epilogue_cols(uint32_t t_row, const float* cs, const float* cb,
@@ -60,7 +70,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
                     const __grid_constant__ CUtensorMap tmap_w, EpiParams ep, int MT, int BN,
-                    int stages, int kbs, int num_kb, int vec_ok, int k3d, SlabA slab, int early_w) {
+                    int stages, int kbs, int num_kb, int vec_ok, int k3d, SlabA slab, int early_w, int kb_per_rank) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -83,6 +93,12 @@ qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const uint32_t stage_bytes = kbs * (w_bytes + x_bytes);  // multiples of 1024
   uint32_t tmem_cols = 32;
   while (tmem_cols < static_cast<uint32_t>(BN)) tmem_cols <<= 1;
+  // K split over the thread-block cluster (gridDim.z blocks along z): rank r walks K blocks
+  // [r * kb_per_rank, (r + 1) * kb_per_rank); the partial tiles meet in distributed shared memory below.
+  const int ksplit = static_cast<int>(gridDim.z);
+  const int rank = static_cast<int>(blockIdx.z);
+  const int kb_lo = ksplit > 1 ? min(num_kb, rank * kb_per_rank) : 0;
+  const int kb_hi = ksplit > 1 ? min(num_kb, kb_lo + kb_per_rank) : num_kb;
 
   // Loads of one stage (K blocks kb0 .. kb0 + nk - 1).  which: 1 = weight, 2 =
   // activation, 3 = both; the call that brings the weight arms the barrier.
@@ -98,7 +114,7 @@ qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
       if (which & 2) tma_load_3d(x_dst, &tmap_x, full_bar(stage), 0, static_cast<int>(m0), kb0);
       return;
     }
-    const int nk = num_kb - kb0 < kbs ? num_kb - kb0 : kbs;
+    const int nk = kb_hi - kb0 < kbs ? kb_hi - kb0 : kbs;
     if (which & 1) mbar_arrive_expect_tx(full_bar(stage), nk * (w_bytes + x_bytes));
     for (int c = 0; c < nk; ++c) {
       const KCoord kc = k_coord(slab, kb0 + c);
@@ -111,7 +127,7 @@ qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
   // The producer needs nothing but its own barriers, so the first ring of
   // stages is on its way before the accumulator columns are allocated and the
   // CTA meets at the barrier below.
-  int first_kb = 0;
+  int first_kb = kb_lo;
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tmap_w);
@@ -127,13 +143,13 @@ qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
       if (early_w) {
         // The weight does not depend on the kernel before this one: its first
         // ring of stages is requested while that kernel may still be running.
-        int kb = 0;
-        for (int s = 0; s < stages && kb < num_kb; ++s, kb += kbs) issue_stage(s, kb, 1);
+        int kb = kb_lo;
+        for (int s = 0; s < stages && kb < kb_hi; ++s, kb += kbs) issue_stage(s, kb, 1);
         grid_dep_wait();
-        for (int s = 0; s < stages && first_kb < num_kb; ++s, first_kb += kbs) issue_stage(s, first_kb, 2);
+        for (int s = 0; s < stages && first_kb < kb_hi; ++s, first_kb += kbs) issue_stage(s, first_kb, 2);
       } else {
         grid_dep_wait();
-        for (int s = 0; s < stages && first_kb < num_kb; ++s, first_kb += kbs) issue_stage(s, first_kb, 3);
+        for (int s = 0; s < stages && first_kb < kb_hi; ++s, first_kb += kbs) issue_stage(s, first_kb, 3);
       }
     }
   } else if (warp == 1) {
@@ -151,7 +167,7 @@ qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
       // next, one phase later.
       int stage = 0;
       uint32_t phase = 1;
-      for (int kb0 = first_kb; kb0 < num_kb; kb0 += kbs) {
+      for (int kb0 = first_kb; kb0 < kb_hi; kb0 += kbs) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, &g_kernel_status,
                        kStatusTimeoutEmpty))
           break;
@@ -168,8 +184,8 @@ qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int kb0 = 0; kb0 < num_kb; kb0 += kbs) {
-        const int nk = num_kb - kb0 < kbs ? num_kb - kb0 : kbs;
+      for (int kb0 = kb_lo; kb0 < kb_hi; kb0 += kbs) {
+        const int nk = kb_hi - kb0 < kbs ? kb_hi - kb0 : kbs;
         ok = mbar_wait(full_bar(stage), phase, abort_flag, &g_kernel_status, kStatusTimeoutFull);
         if (!ok) break;
         tc_fence_after();
@@ -180,7 +196,7 @@ qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
           const uint64_t b_desc = make_kmajor_sw128_desc(w_addr + c * w_bytes);
 #pragma unroll
           for (int k = 0; k < kTileKBytes / kMmaK; ++k) {
-            umma_i8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb0 + c != 0 || k != 0) ? 1u : 0u);
+            umma_i8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb0 + c != kb_lo || k != 0) ? 1u : 0u);
           }
         }
         umma_commit(empty_bar(stage));
@@ -211,14 +227,86 @@ qgemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x,
     asm volatile("bar.sync 1, %0;" ::"r"(kThreads - 64) : "memory");
 
     const bool ok = mbar_wait(tfull_bar, 0, abort_flag, &g_kernel_status, kStatusTimeoutTmemFull);
-    if (ok && m0 + q * 32 < ep.M) {  // a quadrant without rows has nothing to read
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    if (ksplit == 1) {
+      if (ok && m0 + q * 32 < ep.M) {  // a quadrant without rows has nothing to read
+        tc_fence_after();
+        OutT* out = reinterpret_cast<OutT*>(ep.out);
+        const int mode = epi_mode(ctx);
+        DISC_EPI_SWITCH(mode, (skinny_epilogue_cols<OutT, ACT, DIV, RS>(
+                                  t_row, s_cs, s_cb, ctx, out, m, row_ok, n0, ep.N, ep.ldo, vec_ok, g, BN)));
+      }
+    } else if (q * 32 < MT) {
+      // partial sums of this block's K range -> its shared memory (the stages are free: every MMA has read them)
       tc_fence_after();
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-      OutT* out = reinterpret_cast<OutT*>(ep.out);
-      const int mode = epi_mode(ctx);
-      DISC_EPI_SWITCH(mode, (skinny_epilogue_cols<OutT, ACT, DIV, RS>(
-                                t_row, s_cs, s_cb, ctx, out, m, row_ok, n0, ep.N, ep.ldo, vec_ok, g, BN)));
+      int32_t* tile = reinterpret_cast<int32_t*>(smem);
+      const int pitch = BN + kSkinnyTilePad;
+      const int r_local = q * 32 + lane;
+      const bool have = ok && kb_hi > kb_lo;
+#pragma unroll 1
+      for (int c = g; c < BN / 16; c += 4) {
+        uint32_t r[16];
+        if (have) {
+          tmem_ld_x16(t_row + c * 16, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = 0u;
+        }
+        if (r_local < MT) {
+          int4* dst = reinterpret_cast<int4*>(tile + r_local * pitch + c * 16);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            dst[j] = make_int4(static_cast<int>(r[4 * j]), static_cast<int>(r[4 * j + 1]), static_cast<int>(r[4 * j + 2]),
+                               static_cast<int>(r[4 * j + 3]));
+        }
+      }
     }
+  }
+
+  if (ksplit > 1) {
+    // Every block finishes a slice of the tile: the partial sums of all ranks, added in rank order (int32: exact
+    // in any order), then the epilogue.  All threads of all blocks of the cluster meet at both barriers.
+    cluster_sync_all();
+    if (warp >= 2) {
+      const int et = threadIdx.x - 64;
+      const EpiCtx ctx0 = make_epi_ctx(ep);
+      const int pitch = BN + kSkinnyTilePad;
+      const int rows_valid = static_cast<int>(min(static_cast<int64_t>(MT), ep.M - m0));
+      const int groups = BN / 4;
+      const int items = rows_valid * groups;
+      const int per = (items + ksplit - 1) / ksplit;
+      const int i_end = min(items, (rank + 1) * per);
+      const uint32_t tile_addr = smem_base;
+      OutT* out = reinterpret_cast<OutT*>(ep.out);
+      for (int i = rank * per + et; i < i_end; i += kThreads - 64) {
+        const int row = i / groups;
+        const int col = (i - row * groups) * 4;
+        const uint32_t local = tile_addr + static_cast<uint32_t>(row * pitch + col) * 4u;
+        int a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+        for (int j = 0; j < ksplit; ++j) {
+          int v0, v1, v2, v3;
+          asm volatile("ld.shared::cluster.v4.s32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
+                       : "r"(map_to_cta(local, static_cast<uint32_t>(j))));
+          a0 += v0;
+          a1 += v1;
+          a2 += v2;
+          a3 += v3;
+        }
+        const int64_t mrow = m0 + row;
+        EpiCtx ctx = ctx0;
+        if (ctx.has_rs) ctx.rs = __ldg(ep.x_scale + mrow);
+        const int acc[4] = {a0, a1, a2, a3};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int64_t n = n0 + col + e;
+          if (n < ep.N)
+            store_one_rt<OutT>(out + mrow * ep.ldo + n, epi_value(acc[e], s_cs[col + e], s_cb[col + e], ctx), acc[e], ctx);
+        }
+      }
+    }
+    cluster_sync_all();  // no block leaves while its tile may still be read
   }
 
   __syncwarp();

@@ -1336,10 +1336,58 @@ int skinny_bn(const QGemmParams& p) {
   return static_cast<int>(bn);
 }
 
+// Clusters of `ks` blocks of the few-row kernel the current device holds at once (asked once per device and size).
+template <typename OutT>
+int skinny_max_clusters(int ks) {
+  static std::atomic<int> cache[kMaxDeviceOrdinals][5];
+  const int dev = current_device_ordinal();
+  int n = cache[dev][ks].load(std::memory_order_relaxed);
+  if (n != 0) return n < 0 ? 0 : n;
+  auto kern = qgemm_skinny_kernel<OutT>;
+  int active = 0;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkinnyDynamic) == cudaSuccess) {
+    cudaLaunchConfig_t q{};
+    q.gridDim = dim3(1, 1, static_cast<unsigned>(ks));
+    q.blockDim = dim3(kThreads);
+    q.dynamicSmemBytes = kSkinnyDynamic;
+    cudaLaunchAttribute qa[1];
+    qa[0].id = cudaLaunchAttributeClusterDimension;
+    qa[0].val.clusterDim.x = 1;
+    qa[0].val.clusterDim.y = 1;
+    qa[0].val.clusterDim.z = static_cast<unsigned>(ks);
+    q.attrs = qa;
+    q.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&active, kern, &q) != cudaSuccess) {
+      (void)cudaGetLastError();
+      active = 0;
+    }
+  }
+  cache[dev][ks].store(active > 0 ? active : -1, std::memory_order_relaxed);
+  return active;
+}
+
 template <typename OutT>
 cudaError_t launch_skinny(const QGemmParams& p, cudaStream_t stream, const char** err) {
   const int MT = p.M > 64 ? kTileM : small_mt(p.M);
-  const int BN = skinny_bn(p);
+  int BN = skinny_bn(p);
+  // One row tile, long K, few channels: a block's time is its K range (0.2 - 0.35 us per 128-byte K block,
+  // whatever the tile's width), so K is cut over a thread-block cluster of 4, 3 or 2 blocks with 128 channels
+  // each, as long as every cluster is resident at once.  The exchange costs about 3 us, so fewer ranks need a
+  // longer K to pay (measured, 64 rows, f16 out: 4096 x 4096 over 4: 9.4 -> 8.2 us; 11008 x 4096 over 4:
+  // 20.0 -> 13.1 us; 8192 x 8192 over 2: 20.5 -> 16.7 us; 4096 x 5120 over 3: 9.5 -> 10.0 us, not taken).
+  // More blocks than SMs lose to the exchange at every K measured.
+  int ksplit = 1;
+  if (p.M <= kTileM && !has_slabs(p)) {
+    static constexpr int64_t kMinK[5] = {0, 0, 8192, 6144, 4096};
+    const int64_t strips = (p.N + 127) / 128;
+    for (int ks = 4; ks >= 2; --ks) {
+      if (p.K >= kMinK[ks] && strips * ks <= sm_count() && strips <= skinny_max_clusters<OutT>(ks)) {
+        ksplit = ks;
+        BN = 128;
+        break;
+      }
+    }
+  }
   // K blocks per stage: as many as leave at least three stages in flight.
   int kbs = 4;
   while (kbs > 1 && 3 * kbs * (BN + MT) * kTileKBytes > kSkinnyStageRegion) kbs >>= 1;
@@ -1363,9 +1411,24 @@ cudaError_t launch_skinny(const QGemmParams& p, cudaStream_t stream, const char*
   const int num_kb = num_k_blocks(p);
   const int eb = out_elem_bytes(p.out_dtype);
   const int vec_ok = ((p.ldo * eb) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
-  dim3 grid(static_cast<unsigned>((p.N + BN - 1) / BN), static_cast<unsigned>((p.M + kTileM - 1) / kTileM));
-  return launch_dependent(kern, grid, dim3(kThreads), kSkinnyDynamic, stream, tx, tw, make_epi(p), MT, BN, stages,
-                          kbs, num_kb, vec_ok, k3d, slab_of(p), p.weights_static ? 1 : 0);
+  const int kb_per_rank = ((num_kb + ksplit - 1) / ksplit + kbs - 1) / kbs * kbs;  // whole stages
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>((p.N + BN - 1) / BN), static_cast<unsigned>((p.M + kTileM - 1) / kTileM),
+                     static_cast<unsigned>(ksplit));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSkinnyDynamic;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[0].val.programmaticStreamSerializationAllowed = 1;
+  attrs[1].id = cudaLaunchAttributeClusterDimension;
+  attrs[1].val.clusterDim.x = 1;
+  attrs[1].val.clusterDim.y = 1;
+  attrs[1].val.clusterDim.z = static_cast<unsigned>(ksplit);
+  cfg.attrs = attrs;
+  cfg.numAttrs = ksplit > 1 ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, tx, tw, make_epi(p), MT, BN, stages, kbs, num_kb, vec_ok, k3d, slab_of(p),
+                            p.weights_static ? 1 : 0, kb_per_rank);
 }
 
 template <typename OutT>

@@ -19,7 +19,7 @@ from . import ops
 ROOT = Path(__file__).resolve().parent.parent
 L2_BYTES = 126 << 20
 MS = [1, 7, 64, 333, 1024, 4096, 16384]
-KNS = [(768, 768), (768, 3072), (3072, 768), (4096, 4096), (4096, 11008)]
+KNS = [(768, 768), (768, 3072), (3072, 768), (4096, 4096), (4096, 11008), (11008, 4096)]
 
 
 def peaks():

@@ -113,13 +113,18 @@ def test_cta_pair_path(ops, M, K, N, out_dtype):
 
 @pytest.mark.parametrize("M,K,N", [(9, 768, 768), (16, 128, 16), (33, 144, 80), (64, 4096, 520), (100, 640, 392),
                                    (128, 2064, 264), (129, 256, 384), (300, 640, 1000), (333, 768, 3072),
-                                   (48, 3072, 72), (600, 1024, 777)])
+                                   (48, 3072, 72), (600, 1024, 777),
+                                   # one row tile, K >= 4096, few channels: K cut over a cluster of 4, 4 (K tail:
+                                   # 33 blocks, the last rank short), 3 and 2 blocks
+                                   (128, 8192, 1024), (16, 4112, 1000), (40, 6272, 5120), (33, 8192, 8200)])
 @pytest.mark.parametrize("out_dtype", [torch.int32, torch.int8, torch.float16, torch.float32])
 def test_skinny_path(ops, M, K, N, out_dtype):
     """The few-row kernel (fine channel blocks over the full K, one box per
     operand and stage when K is a multiple of 128, per-block boxes otherwise),
-    forced on ragged rows / columns / K tails, several row tiles, and both
-    store routes (N = 72 or 777 with int8 output leaves by scalar stores)."""
+    forced on ragged rows / columns / K tails, several row tiles, both
+    store routes (N = 72 or 777 with int8 output leaves by scalar stores), and
+    with K split over a thread-block cluster (partial tiles added through
+    distributed shared memory)."""
     from oracle import c
     rng = np.random.default_rng(M * 3 + K + N)
     a, w = _rand_i8(rng, (M, K)), _rand_i8(rng, (N, K))
