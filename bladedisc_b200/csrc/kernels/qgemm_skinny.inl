@@ -30,7 +30,7 @@
 constexpr int kSkinnyStageRegion = 184 * 1024;  // a short activation tile is read up to 16 KB past its end
 constexpr int kSkinnyBarOffset = 200 * 1024;
 constexpr int kSkinnyScaleOffset = kSkinnyBarOffset + 256;
-constexpr int kSkinnyMaxBN = 128;
+constexpr int kSkinnyMaxBN = 256;  // widest channel block: above 128 only where N needs it to stay in one wave
 constexpr int kSkinnyDynamic = kSkinnyScaleOffset + 2 * kSkinnyMaxBN * 4 + 1024;
 constexpr int kSkinnyTilePad = 4;  // int32 words added to a row of the partial tile: 16-byte stores of a warp spread over the banks
 

@@ -1332,7 +1332,9 @@ int skinny_bn(const QGemmParams& p) {
   int64_t bn = (p.N + ctas - 1) / ctas;
   bn = (bn + 15) / 16 * 16;
   if (bn < 16) bn = 16;
-  if (bn > kSkinnyMaxBN) bn = kSkinnyMaxBN;
+  // Blocks wider than 128 channels only for one row tile whose N would otherwise take a second wave.
+  const int64_t cap = tiles_m == 1 ? kSkinnyMaxBN : 128;
+  if (bn > cap) bn = cap;
   return static_cast<int>(bn);
 }
 
@@ -1461,7 +1463,9 @@ int qgemm_choose_path(const QGemmParams& p) {
   if (p.path == kPathSkinny && p.M <= 65535 * kTileM) return kPathSkinny;
   if (p.path == kPathGemv && p.M <= 8 && p.K <= kGemvMaxK && p.a_slabs <= 1) return kPathGemv;
   // One to a few rows: the dp4a stream; from five rows on a large weight is
-  // cheaper through the tensor cores.
+  // cheaper through the tensor cores.  (Back to back with itself the tensor-core stream is also 0.4 - 1.2 us
+  // ahead at one to four rows of a weight of 32 MB or more, because consecutive launches overlap their
+  // prologues; between the row kernels of a decoder step it is behind: 8 layers at batch 1 0.59 -> 0.67 ms.)
   const bool slabs = p.a_slabs > 1;  // read by the TMA paths (and the fallback) only
   if (!slabs && p.M <= 8 && p.K <= kGemvMaxK && (p.M <= 4 || p.N * p.K < (int64_t{1} << 25)))
     return kPathGemv;

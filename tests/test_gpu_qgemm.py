@@ -111,12 +111,14 @@ def test_cta_pair_path(ops, M, K, N, out_dtype):
             assert np.allclose(got[ok], want[ok], rtol=RTOL, atol=ATOL)
 
 
-@pytest.mark.parametrize("M,K,N", [(9, 768, 768), (16, 128, 16), (33, 144, 80), (64, 4096, 520), (100, 640, 392),
+@pytest.mark.parametrize("M,K,N", [(1, 256, 520), (3, 4096, 1000), (9, 768, 768), (16, 128, 16), (33, 144, 80), (64, 4096, 520), (100, 640, 392),
                                    (128, 2064, 264), (129, 256, 384), (300, 640, 1000), (333, 768, 3072),
                                    (48, 3072, 72), (600, 1024, 777),
                                    # one row tile, K >= 4096, few channels: K cut over a cluster of 4, 4 (K tail:
                                    # 33 blocks, the last rank short), 3 and 2 blocks
-                                   (128, 8192, 1024), (16, 4112, 1000), (40, 6272, 5120), (33, 8192, 8200)])
+                                   (128, 8192, 1024), (16, 4112, 1000), (40, 6272, 5120), (33, 8192, 8200),
+                                   # more channels than 148 blocks of 128 hold: blocks of 160, 224 and 256 channels
+                                   (16, 256, 22016), (64, 128, 32000), (33, 144, 37880)])
 @pytest.mark.parametrize("out_dtype", [torch.int32, torch.int8, torch.float16, torch.float32])
 def test_skinny_path(ops, M, K, N, out_dtype):
     """The few-row kernel (fine channel blocks over the full K, one box per
@@ -159,6 +161,9 @@ def test_skinny_path(ops, M, K, N, out_dtype):
 
 def test_auto_path_by_rows(ops):
     assert ops.qgemm_path(1, 4096, 4096) == "gemv"
+    assert ops.qgemm_path(8, 4096, 4096) == "gemv"
+    assert ops.qgemm_path(4, 4096, 11008) == "gemv"
+    assert ops.qgemm_path(5, 4096, 11008) == "skinny"
     assert ops.qgemm_path(7, 11008, 4096) == "skinny"
     assert ops.qgemm_path(64, 4096, 4096) == "skinny"
     assert ops.qgemm_path(128, 768, 3072) == "skinny"
