@@ -1332,8 +1332,12 @@ int skinny_bn(const QGemmParams& p) {
   int64_t bn = (p.N + ctas - 1) / ctas;
   bn = (bn + 15) / 16 * 16;
   if (bn < 16) bn = 16;
-  // Blocks wider than 128 channels only for one row tile whose N would otherwise take a second wave.
-  const int64_t cap = tiles_m == 1 ? kSkinnyMaxBN : 128;
+  // Blocks wider than 128 channels where they save a wave: one row tile whose N would otherwise take a second
+  // wave here, or several row tiles whose 256 x 256 pair tiles would take a second wave there
+  // (333 x 4096 x 11008: 86 pair tiles on 74 SM pairs, 26.5 us; 138 blocks of 240 channels here, 20.3 us).
+  // With one wave of pair tiles the pair kernel is ahead (256 x 4096 x 11008: 17.0 against 18.2 us).
+  const int64_t pair_tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
+  const int64_t cap = (tiles_m == 1 || pair_tiles > sm_count() / 2) ? kSkinnyMaxBN : 128;
   if (bn > cap) bn = cap;
   return static_cast<int>(bn);
 }

@@ -118,7 +118,9 @@ def test_cta_pair_path(ops, M, K, N, out_dtype):
                                    # 33 blocks, the last rank short), 3 and 2 blocks
                                    (128, 8192, 1024), (16, 4112, 1000), (40, 6272, 5120), (33, 8192, 8200),
                                    # more channels than 148 blocks of 128 hold: blocks of 160, 224 and 256 channels
-                                   (16, 256, 22016), (64, 128, 32000), (33, 144, 37880)])
+                                   (16, 256, 22016), (64, 128, 32000), (33, 144, 37880),
+                                   # three row tiles of 240-channel blocks
+                                   (333, 256, 11008)])
 @pytest.mark.parametrize("out_dtype", [torch.int32, torch.int8, torch.float16, torch.float32])
 def test_skinny_path(ops, M, K, N, out_dtype):
     """The few-row kernel (fine channel blocks over the full K, one box per
