@@ -18,7 +18,7 @@
 // 2..17 epilogue (TMEM lane quadrant = warp & 3 = 32 rows; the four warps of a
 // quadrant interleave 16-column chunks).
 //
-// One row tile with long K and few channels (the launcher's rule): gridDim.z
+// Long K and few tiles (the launcher's rule): gridDim.z
 // blocks form a thread-block cluster along z and share a tile of 128 channels,
 // each walking 1/z of the K blocks.  Every block writes its partial int32 tile
 // from TMEM to its own shared memory (the stage ring is free by then), the

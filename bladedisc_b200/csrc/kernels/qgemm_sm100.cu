@@ -1376,16 +1376,18 @@ template <typename OutT>
 cudaError_t launch_skinny(const QGemmParams& p, cudaStream_t stream, const char** err) {
   const int MT = p.M > 64 ? kTileM : small_mt(p.M);
   int BN = skinny_bn(p);
-  // One row tile, long K, few channels: a block's time is its K range (0.2 - 0.35 us per 128-byte K block,
-  // whatever the tile's width), so K is cut over a thread-block cluster of 4, 3 or 2 blocks with 128 channels
-  // each, as long as every cluster is resident at once.  The exchange costs about 3 us, so fewer ranks need a
-  // longer K to pay (measured, 64 rows, f16 out: 4096 x 4096 over 4: 9.4 -> 8.2 us; 11008 x 4096 over 4:
-  // 20.0 -> 13.1 us; 8192 x 8192 over 2: 20.5 -> 16.7 us; 4096 x 5120 over 3: 9.5 -> 10.0 us, not taken).
-  // More blocks than SMs lose to the exchange at every K measured.
+  // Long K, few tiles: a block's time is its K range (0.2 - 0.35 us per 128-byte K block, whatever the tile's
+  // width), so K is cut over a thread-block cluster of 4, 3 or 2 blocks with 128 channels each, as long as every
+  // cluster is resident at once.  The exchange costs about 3 us, so fewer ranks need a longer K to pay
+  // (measured, f16 out: 64 x 4096 x 4096 over 4: 9.4 -> 8.2 us; 64 x 11008 x 4096 over 4: 20.0 -> 13.1 us;
+  // 64 x 8192 x 8192 over 2: 20.5 -> 16.7 us; 64 x 4096 x 5120 over 3: 9.5 -> 10.0 us, not taken; several row
+  // tiles: 256 x 11008 x 2048 over 4: 25.8 -> 15.1 us, 512 x 8192 x 1024 over 4: 19.9 -> 12.8 us,
+  // 256 x 11008 x 4096 over 2: 26.5 -> 23.3 us).  More blocks than SMs lose to the exchange at every K measured.
   int ksplit = 1;
-  if (p.M <= kTileM && !has_slabs(p)) {
+  const int64_t tiles_m = (p.M + kTileM - 1) / kTileM;
+  if (!has_slabs(p)) {
     static constexpr int64_t kMinK[5] = {0, 0, 8192, 6144, 4096};
-    const int64_t strips = (p.N + 127) / 128;
+    const int64_t strips = ((p.N + 127) / 128) * tiles_m;
     for (int ks = 4; ks >= 2; --ks) {
       if (p.K >= kMinK[ks] && strips * ks <= sm_count() && strips <= skinny_max_clusters<OutT>(ks)) {
         ksplit = ks;

@@ -120,7 +120,9 @@ def test_cta_pair_path(ops, M, K, N, out_dtype):
                                    # more channels than 148 blocks of 128 hold: blocks of 160, 224 and 256 channels
                                    (16, 256, 22016), (64, 128, 32000), (33, 144, 37880),
                                    # three row tiles of 240-channel blocks
-                                   (333, 256, 11008)])
+                                   (333, 256, 11008),
+                                   # K split with 2, 2 (K tail), 3 and 4 row tiles
+                                   (256, 8192, 1024), (200, 4224, 2048), (384, 6272, 2000), (512, 4096, 1024)])
 @pytest.mark.parametrize("out_dtype", [torch.int32, torch.int8, torch.float16, torch.float32])
 def test_skinny_path(ops, M, K, N, out_dtype):
     """The few-row kernel (fine channel blocks over the full K, one box per
