@@ -17,7 +17,7 @@ enum QGemmPath : int {
   kPathSimt = 3,    // shapes TMA cannot address
   kPathPair = 4,    // CTA pairs, 256 x 256 tiles
   kPathGemv = 5,    // M <= 8: dp4a matrix-vector stream
-  kPathSkinny = 6   // few rows: BN = 16..128 channels per CTA, full K, no split
+  kPathSkinny = 6   // few rows: BN = 16..256 channels per CTA over the full K, or K cut over a thread-block cluster
 };
 
 // out[m, n] = epilogue( sum_k a[m, k] * w[n, k] ), a and w int8, K-contiguous.
